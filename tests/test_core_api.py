@@ -1,0 +1,299 @@
+"""Single-process checks of the facade, factory, options, hooks and work
+state machine on the ``fake`` backend and on Python-implemented backends.
+
+Modelled on the reference's unit suites (comms/torchcomms/tests/unit/py:
+test_factory, test_hooks, test_python_backend, test_copy).
+"""
+import copy
+import os
+from datetime import timedelta
+
+import pytest
+import torch
+
+import torchcomms_b200 as tc
+from torchcomms_b200 import _comms
+
+
+def _fake(name, **kw):
+    return tc.new_comm("fake", torch.device("cpu"), name=name, **kw)
+
+
+def test_registered_backends():
+    assert tc.is_backend_built("fake")
+    assert tc.is_backend_built("gloo")
+    assert "fake" in tc.built_backends()
+    assert not tc.is_backend_built("nonexistent")
+
+
+def test_unknown_backend_raises():
+    with pytest.raises(RuntimeError, match="unknown communication backend"):
+        tc.new_comm("nonexistent", torch.device("cpu"), name="x")
+
+
+def test_basic_accessors_and_finalize():
+    c = _fake("acc", timeout=timedelta(seconds=7), hints={"fake_rank": "2", "fake_size": "4"})
+    assert (c.get_rank(), c.get_size()) == (2, 4)
+    assert c.get_name() == "acc"
+    assert c.get_backend() == "fake"
+    assert c.get_device() == torch.device("cpu")
+    assert c.get_options().timeout == timedelta(seconds=7)
+    assert c.get_ranks() == [0, 1, 2, 3]
+    c.finalize()
+    with pytest.raises(RuntimeError, match="finalized"):
+        c.barrier(False)
+    with pytest.raises(RuntimeError, match="already finalized"):
+        c.finalize()
+
+
+def test_rank_validation():
+    c = _fake("rv", hints={"fake_size": "2"})
+    t = torch.zeros(2)
+    with pytest.raises(RuntimeError, match="outside"):
+        c.send(t, 5, False)
+    with pytest.raises(RuntimeError, match="outside"):
+        c.broadcast(t, -1, False)
+    c.finalize()
+
+
+def test_env_defaults(monkeypatch):
+    monkeypatch.setenv("TORCHCOMM_ABORT_ON_ERROR", "0")
+    monkeypatch.setenv("TORCHCOMM_TIMEOUT_SECONDS", "12.5")
+    o = tc.CommOptions()
+    assert o.abort_process_on_timeout_or_error is False
+    assert o.timeout == timedelta(seconds=12.5)
+    monkeypatch.setenv("TORCHCOMM_ABORT_ON_ERROR", "maybe")
+    with pytest.raises(RuntimeError):
+        tc.CommOptions()
+
+
+def test_query_ranksize_order(monkeypatch):
+    for k in ("TORCHCOMM_RANK", "TORCHCOMM_SIZE", "OMPI_COMM_WORLD_RANK", "OMPI_COMM_WORLD_SIZE",
+              "PMI_RANK", "PMI_SIZE", "RANK", "WORLD_SIZE", "TORCHCOMM_BOOTSTRAP_RANKSIZE_QUERY_METHOD"):
+        monkeypatch.delenv(k, raising=False)
+    with pytest.raises(RuntimeError, match="cannot determine rank"):
+        _comms._query_ranksize()
+    monkeypatch.setenv("RANK", "3")
+    monkeypatch.setenv("WORLD_SIZE", "8")
+    assert _comms._query_ranksize() == (3, 8)
+    monkeypatch.setenv("TORCHCOMM_RANK", "1")
+    monkeypatch.setenv("TORCHCOMM_SIZE", "2")
+    assert _comms._query_ranksize() == (1, 2)
+    monkeypatch.setenv("TORCHCOMM_BOOTSTRAP_RANKSIZE_QUERY_METHOD", "torchrun")
+    assert _comms._query_ranksize() == (3, 8)
+
+
+def test_op_ids_are_global_and_increasing():
+    a, b = _fake("ida"), _fake("idb")
+    ids = []
+    a.register_pre_hook(lambda op, i, args: ids.append(i))
+    b.register_pre_hook(lambda op, i, args: ids.append(i))
+    t = torch.ones(3)
+    a.all_reduce(t, tc.ReduceOp.SUM, False)
+    b.all_reduce(t, tc.ReduceOp.SUM, False)
+    a.barrier(False)
+    assert ids == sorted(ids) and len(set(ids)) == 3
+    a.finalize()
+    b.finalize()
+
+
+def test_hooks_typed_args_and_removal():
+    c = _fake("hooks", hints={"fake_size": "2"})
+    pre, post = [], []
+    h1 = c.register_pre_hook(lambda op, i, a: pre.append((op, a)))
+    h2 = c.register_post_hook(lambda i, a: post.append(a))
+    t = torch.arange(4.0)
+    out = torch.zeros(8)
+    c.all_reduce(t, tc.ReduceOp.MAX, True)
+    c.all_gather_single(out, t, False)
+    c.send(t, 1, False)
+    c.all_to_all_v_single(torch.zeros(4), t, [2, 2], [1, 3], False)
+    ops = [p[0] for p in pre]
+    assert ops == [tc.OpName.all_reduce, tc.OpName.all_gather_single, tc.OpName.send, tc.OpName.all_to_all_v_single]
+    ar = pre[0][1]
+    assert type(ar).__name__ == "AllReducePreHookArgs"
+    assert ar.tensor is t and ar.async_op is True and ar.op == tc.RedOpType.MAX
+    ag = pre[1][1]
+    assert ag.input is t and ag.output is out and ag.async_op is False
+    assert pre[2][1].peer == 1
+    assert pre[3][1].input_split_sizes == [1, 3] and pre[3][1].output_split_sizes == [2, 2]
+    assert type(post[0]).__name__ == "AllReducePostHookArgs"
+    assert isinstance(post[0], tc.CollectivePostHookArgs)
+    h1.remove()
+    h1.remove()  # idempotent
+    c.barrier(False)
+    assert len(pre) == 4 and len(post) == 5
+    h2.remove()
+    fin = []
+    c.register_pre_hook(lambda op, i, a: fin.append((op, i)))
+    c.finalize()
+    assert fin == [(tc.OpName.finalize, 2**64 - 1)]
+
+
+def test_split_semantics():
+    c = _fake("parent", hints={"fake_rank": "1", "fake_size": "4"})
+    assert c.split([], "none") is None
+    with pytest.raises(RuntimeError, match="not in the non-empty"):
+        c.split([0, 2], "bad")
+    with pytest.raises(RuntimeError, match="twice"):
+        c.split([1, 1], "dup")
+    with pytest.raises(RuntimeError, match="outside"):
+        c.split([1, 9], "oob")
+    child = c.split([3, 1], "kid")
+    assert child.get_size() == 2 and child.get_rank() == 1
+    assert child.get_ranks() == [3, 1]  # global ranks of the members
+    child.finalize()
+    c.finalize()
+
+
+def test_deepcopy_is_identity():
+    c = _fake("copy")
+    assert copy.copy(c) is c
+    assert copy.deepcopy(c) is c
+    holder = {"comm": c, "x": torch.ones(2)}
+    dup = copy.deepcopy(holder)
+    assert dup["comm"] is c and dup["x"] is not holder["x"]
+    c.finalize()
+
+
+def test_reduce_op_api():
+    assert tc.ReduceOp.SUM.type == tc.RedOpType.SUM
+    assert tc.ReduceOp.AVG == tc.ReduceOp(tc.RedOpType.AVG)
+    p = tc.ReduceOp.PREMUL_SUM(0.5)
+    assert p.type == tc.RedOpType.PREMUL_SUM and p.factor == 0.5
+    pt = tc.ReduceOp.PREMUL_SUM(torch.tensor([2.0]))
+    assert torch.equal(pt.factor, torch.tensor([2.0]))
+
+
+def test_work_state_machine_and_hooks():
+    w = _comms._completed_work()
+    assert w.is_completed() and w.status() == tc.WorkStatus.COMPLETED
+    fired = []
+    w.register_start_hook(lambda: fired.append("start"))  # already started: fires now
+    w.register_end_hook(lambda: fired.append("end"))
+    assert fired == ["start", "end"]
+    w.register_wait_pre_hook(lambda: fired.append("pre"))
+    w.register_wait_post_hook(lambda: fired.append("post"))
+    w.wait()
+    assert fired[-2:] == ["pre", "post"]
+    w._set_status(tc.WorkStatus.TIMEDOUT)
+    with pytest.raises(RuntimeError, match="timed out"):
+        w.wait()
+
+
+def test_batch_send_recv_records_ops():
+    c = _fake("batch", hints={"fake_size": "2"})
+    b = c.batch_op_create()
+    t1, t2 = torch.ones(2), torch.zeros(2)
+    b.send(t1, 1)
+    b.recv(t2, 1)
+    assert [op.type for op in b.ops] == [tc.P2POpType.SEND, tc.P2POpType.RECV]
+    seen = []
+    h = c.register_pre_hook(lambda op, i, a: seen.append((op, len(a.ops))))
+    b.issue(True).wait()
+    h.remove()
+    assert seen == [(tc.OpName.batch_op_issue, 2)]
+    assert "batch_op_issue" in c.get_backend_impl().calls
+    c.finalize()
+
+
+def test_per_op_option_classes():
+    o = tc.AllReduceOptions()
+    o.hints = {"k": "v"}
+    o.timeout = timedelta(seconds=3)
+    assert o.hints == {"k": "v"} and o.timeout == timedelta(seconds=3)
+    assert issubclass(tc.BarrierOptions, tc.OpOptions)
+
+
+class _Work:
+    def __init__(self):
+        self.waited = False
+
+    def wait(self):
+        self.waited = True
+
+
+class _PyBackend(tc.TorchCommBackend):
+    last_work = None
+
+    def __init__(self):
+        super().__init__()
+        self._rank, self._size, self._name = 0, 1, ""
+
+    def init(self, device, name, options):
+        self._name = name
+
+    def finalize(self):
+        pass
+
+    def get_rank(self):
+        return self._rank
+
+    def get_size(self):
+        return self._size
+
+    def get_backend_name(self):
+        return "pyb"
+
+    def get_comm_name(self):
+        return self._name
+
+    def all_reduce(self, tensor, op, async_op):
+        if op.type == tc.RedOpType.SUM:
+            tensor.mul_(3)
+        if async_op:
+            _PyBackend.last_work = _Work()
+            return _PyBackend.last_work
+        return None
+
+    def split(self, ranks, name, options):
+        b = _PyBackend()
+        b._size, b._name = len(ranks), name
+        return b
+
+    def set_timeout(self, timeout):
+        self.timeout = timeout
+
+
+def test_python_backend():
+    tc.register_backend("pyb", _PyBackend)
+    assert tc.is_backend_built("pyb")
+    c = tc.new_comm("pyb", torch.device("cpu"), name="py1")
+    assert c.get_backend() == "pyb" and c.get_name() == "py1"
+    t = torch.ones(2)
+    w = c.all_reduce(t, tc.ReduceOp.SUM, False)
+    assert torch.equal(t, torch.full((2,), 3.0)) and w.is_completed()
+    w = c.all_reduce(t, tc.ReduceOp.SUM, True)
+    assert not _PyBackend.last_work.waited
+    w.wait()
+    assert _PyBackend.last_work.waited and w.is_completed()
+    with pytest.raises(RuntimeError, match="does not implement"):
+        c.barrier(False)
+    kid = c.split([0], "kid")
+    assert kid.get_size() == 1 and kid.get_name() == "kid"
+    c.set_timeout(timedelta(seconds=2))
+    assert c.get_backend_impl().python_object().timeout == timedelta(seconds=2)
+    kid.finalize()
+    c.finalize()
+
+
+def test_dynamic_backend_env_missing_symbol(tmp_path, monkeypatch):
+    bogus = tmp_path / "libnothing.so"
+    bogus.write_bytes(b"not an elf")
+    monkeypatch.setenv("TORCHCOMMS_BACKEND_LIB_PATH_DYNX", str(bogus))
+    with pytest.raises(RuntimeError, match="cannot load backend library"):
+        tc.new_comm("dynx", torch.device("cpu"), name="d")
+
+
+def test_health_flag():
+    _comms._health_reset()
+    assert tc.healthy()
+    _comms._health_mark_unhealthy("watchdog saw a timeout")
+    assert not tc.healthy() and "timeout" in _comms._health_reason()
+    _comms._health_reset()
+
+
+def test_reconfigure_rejected_without_support():
+    tc.register_backend("pyb2", _PyBackend)
+    with pytest.raises(RuntimeError, match="does not support enable_reconfigure"):
+        tc.new_comm("pyb2", torch.device("cpu"), name="r", enable_reconfigure=True)

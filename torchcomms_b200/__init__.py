@@ -1,0 +1,200 @@
+"""torchcomms_b200 — a Blackwell-native communications framework for PyTorch.
+
+The public surface mirrors meta-pytorch/torchcomms (``comms/torchcomms/__init__.py:40-106``
+and ``comms/torchcomms/_comms.pyi:607-844``): ``new_comm(backend, device, name=...)``
+returns a ``TorchComm`` whose collectives return ``TorchWork`` handles.
+
+Backends registered in-tree:
+
+* ``"b200"`` (aliases ``"nccl"``, ``"ncclx"``): CUDA backend for NVLink/NVSwitch
+  machines — peer-memory kernels on a symmetric heap, NCCL for point-to-point
+  and as a selectable fallback.
+* ``"gloo"``: CPU backend over TCP (also accepts CUDA tensors, staged through
+  the host).
+* ``"fake"``: moves no data; for unit tests.
+
+Python-implemented backends are added with ``register_backend(name, cls)``.
+"""
+from __future__ import annotations
+
+import importlib
+import importlib.metadata
+import os
+import sys
+from datetime import timedelta
+from typing import Any, Dict, Optional
+
+import torch  # noqa: F401  (must be loaded before the extension)
+
+
+def _load_extension():
+    here = os.path.dirname(os.path.abspath(__file__))
+    so = os.path.join(here, "_comms.so")
+    if not os.path.exists(so):
+        if os.environ.get("B200COMMS_NO_AUTOBUILD", "0") == "1":
+            raise ImportError(
+                f"{so} is missing; run `python -m torchcomms_b200._build` first"
+            )
+        from . import _build
+
+        _build.build()
+    spec = importlib.util.spec_from_file_location("torchcomms_b200._comms", so)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["torchcomms_b200._comms"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+import importlib.util  # noqa: E402
+
+_comms = _load_extension()
+
+from ._comms import (  # noqa: E402,F401
+    AllGatherPHandle,
+    BatchSendRecv,
+    CommOptions,
+    OpName,
+    OpOptions,
+    P2POp,
+    P2POpType,
+    ReconfigureOptions,
+    RedOpType,
+    ReduceOp,
+    RemovableHandle,
+    TorchComm,
+    TorchCommBackend,
+    TorchCommWinAccessType,
+    TorchCommWindow,
+    TorchCommWindowAttr,
+    TorchWork,
+    WorkStatus,
+    _BackendWrapper,
+    _is_backend_registered,
+    register_backend,
+)
+from ._hook_args import *  # noqa: E402,F401,F403
+from ._hook_args import _to_post_args, _to_pre_args  # noqa: E402
+
+_comms._set_hook_arg_converters(_to_pre_args, _to_post_args)
+
+InitHandle = str
+Timeout = timedelta
+
+
+def _make_gloo_pg(store, rank, size, timeout):
+    import torch.distributed as dist
+
+    return dist.ProcessGroupGloo(store, rank, size, timeout)
+
+
+_comms._install_gloo_maker(_make_gloo_pg)
+
+
+# Per-operation option classes: all carry ``hints`` and ``timeout``.
+def _opt_class(name: str):
+    return type(name, (OpOptions,), {"__doc__": f"Options for {name[:-7]} (hints, timeout)."})
+
+
+for _n in (
+    "SendOptions RecvOptions BatchP2POptions BroadcastOptions AllReduceOptions ReduceOptions "
+    "AllGatherOptions AllGatherSingleOptions ReduceScatterOptions ReduceScatterSingleOptions "
+    "AllToAllOptions AllToAllSingleOptions AllToAllvSingleOptions BarrierOptions ScatterOptions "
+    "GatherOptions AllGatherPInitOptions AllGatherPExecOptions"
+).split():
+    globals()[_n] = _opt_class(_n)
+del _n
+
+_BUILTIN_BACKENDS = ("b200", "nccl", "ncclx", "gloo", "fake")
+
+
+def _load_backend(backend: str) -> None:
+    """Imports the module that registers ``backend`` if it is not known yet.
+
+    Out-of-tree backends announce themselves through the entry-point groups
+    ``torchcomms_b200.backends`` or ``torchcomms.backends``.
+    """
+    if _is_backend_registered(backend):
+        return
+    for group in ("torchcomms_b200.backends", "torchcomms.backends"):
+        try:
+            eps = importlib.metadata.entry_points(group=group)
+        except Exception:  # pragma: no cover - metadata backends differ
+            continue
+        for ep in eps:
+            if ep.name == backend:
+                ep.load()
+                return
+
+
+def is_backend_built(backend: str) -> bool:
+    return _is_backend_registered(backend)
+
+
+def built_backends() -> list[str]:
+    return list(_comms._registered_backends())
+
+
+_comm_counter = 0
+
+
+def new_comm(
+    backend: str,
+    device: Any,
+    abort_process_on_timeout_or_error: Optional[bool] = None,
+    timeout: Optional[timedelta] = None,
+    store: Any = None,
+    name: Optional[str] = None,
+    enable_reconfigure: bool = False,
+    hints: Optional[Dict[str, str]] = None,
+    is_high_priority_stream: Optional[bool] = None,
+) -> TorchComm:
+    """Creates a communicator.
+
+    Rank and world size come from the launcher environment (TORCHCOMM_RANK/SIZE,
+    Open MPI, PMI, PALS or torchrun's RANK/WORLD_SIZE).  Without ``store`` a
+    TCPStore on MASTER_ADDR:MASTER_PORT bootstraps the ranks.  ``name`` must be
+    unique per process and identical across ranks.
+    """
+    global _comm_counter
+    _load_backend(backend)
+    opts = CommOptions()
+    if abort_process_on_timeout_or_error is not None:
+        opts.abort_process_on_timeout_or_error = abort_process_on_timeout_or_error
+    if timeout is not None:
+        opts.timeout = timeout
+    if is_high_priority_stream is not None:
+        opts.is_high_priority_stream = is_high_priority_stream
+    if store is not None:
+        opts.store = store
+    opts.enable_reconfigure = enable_reconfigure
+    if hints:
+        opts.hints = dict(hints)
+    if name is None:
+        name = f"comm_{_comm_counter}"
+    _comm_counter += 1
+    if not isinstance(device, torch.device):
+        device = torch.device(device)
+    return _comms._new_comm(backend, device, name, opts)
+
+
+def get_mem_allocator(backend: str):
+    """Allocator whose memory is exportable to peers (symmetric heap)."""
+    from .mem import get_mem_allocator as _g
+
+    return _g(backend)
+
+
+def _comm_mem_allocator(self):
+    return get_mem_allocator(self.get_backend())
+
+
+TorchComm.get_mem_allocator = _comm_mem_allocator
+TorchComm.mem_allocator = property(_comm_mem_allocator)
+
+
+def healthy() -> bool:
+    """False once any watchdog of this process saw a timeout or an async error."""
+    return _comms._health_is_healthy()
+
+
+__all__ = [n for n in dir() if not n.startswith("_")] + ["_BackendWrapper"]
