@@ -1,0 +1,1505 @@
+// CUDA backend: bootstrap, stream/event protocol, watchdog, algorithm choice.
+#include "cuda_backend.hpp"
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+
+#include <cstring>
+
+#include "../core/logging.hpp"
+
+namespace b200c {
+
+namespace {
+
+size_t round_up(size_t v, size_t to) {
+  return (v + to - 1) / to * to;
+}
+
+constexpr size_t kMetaBytes = static_cast<size_t>(kMaxBlocks) * kMaxRanks * kMaxRanks * sizeof(uint64_t);
+constexpr size_t kSmallBytes = 2 * static_cast<size_t>(kSmallBlocks) * kSmallPiece + kMetaBytes;
+constexpr size_t kFlagBytes = static_cast<size_t>(kFlagSets) * kMaxBlocks * kMaxRanks * sizeof(uint32_t);
+
+bool to_dtype(at::ScalarType t, DType* out) {
+  switch (t) {
+    case at::kFloat: *out = DType::F32; return true;
+    case at::kHalf: *out = DType::F16; return true;
+    case at::kBFloat16: *out = DType::BF16; return true;
+    default: return false;
+  }
+}
+
+bool to_nccl_dtype(at::ScalarType t, NcclDataType* out) {
+  switch (t) {
+    case at::kChar: *out = kNcclInt8; return true;
+    case at::kByte: *out = kNcclUint8; return true;
+    case at::kBool: *out = kNcclUint8; return true;
+    case at::kInt: *out = kNcclInt32; return true;
+    case at::kLong: *out = kNcclInt64; return true;
+    case at::kHalf: *out = kNcclFloat16; return true;
+    case at::kFloat: *out = kNcclFloat32; return true;
+    case at::kDouble: *out = kNcclFloat64; return true;
+    case at::kBFloat16: *out = kNcclBfloat16; return true;
+    case at::kFloat8_e4m3fn: *out = kNcclFloat8e4m3; return true;
+    case at::kFloat8_e5m2: *out = kNcclFloat8e5m2; return true;
+    case at::kUInt32: *out = kNcclUint32; return true;
+    case at::kUInt64: *out = kNcclUint64; return true;
+    default: return false;
+  }
+}
+
+void check_tensor(const at::Tensor& t, const at::Device& dev, const char* what) {
+  TORCH_CHECK(t.defined(), what, ": undefined tensor");
+  TORCH_CHECK(t.is_contiguous(), "Tensor must be contiguous for ", what);
+  TORCH_CHECK(t.device() == dev, what, ": tensor is on ", t.device(), " but the communicator lives on ", dev);
+}
+
+Algo parse_algo(std::string s) {
+  for (auto& c : s) c = static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
+  if (s == "oneshot" || s == "one_shot") return Algo::ONESHOT;
+  if (s == "twoshot" || s == "two_shot") return Algo::TWOSHOT;
+  if (s == "staged" || s == "kernel") return Algo::STAGED;
+  if (s == "nccl" || s == "orig") return Algo::NCCL;
+  return Algo::AUTO;
+}
+
+} // namespace
+
+// ------------------------------------------------------------- CudaWork ----
+
+CudaWork::CudaWork(std::shared_ptr<CudaApi> api, cudaEvent_t start, cudaEvent_t end, bool pooled, int device,
+                   Millis timeout, std::vector<at::Tensor> keep_alive, std::weak_ptr<CudaBackend> owner,
+                   bool in_capture)
+    : api_(std::move(api)), start_(start), end_(end), pooled_(pooled), device_(device),
+      keep_alive_(std::move(keep_alive)), owner_(std::move(owner)), in_capture_(in_capture) {
+  set_timeout(timeout);
+}
+
+CudaWork::~CudaWork() {
+  if (start_ == nullptr && end_ == nullptr) {
+    return;
+  }
+  auto o = owner_.lock();
+  if (pooled_ && o) {
+    o->recycle_events(start_, end_);
+  } else {
+    if (start_) api_->eventDestroy(start_);
+    if (end_) api_->eventDestroy(end_);
+  }
+}
+
+void CudaWork::release_events(cudaEvent_t* start, cudaEvent_t* end) {
+  *start = start_;
+  *end = end_;
+  start_ = nullptr;
+  end_ = nullptr;
+}
+
+bool CudaWork::poll(std::chrono::steady_clock::time_point now) {
+  std::lock_guard<std::mutex> g(poll_mu_);
+  const WorkStatus s = status();
+  if (s == WorkStatus::COMPLETED || s == WorkStatus::TIMEDOUT || s == WorkStatus::ERROR) {
+    return true;
+  }
+  if (!started_seen_) {
+    const cudaError_t q = api_->eventQuery(start_);
+    if (q == cudaSuccess) {
+      started_seen_ = true;
+      started_at_ = now;
+      set_status(WorkStatus::INPROGRESS);
+    } else if (q != cudaErrorNotReady) {
+      set_error(std::string("start event: ") + api_->errorString(q));
+      set_status(WorkStatus::ERROR);
+      return true;
+    }
+  }
+  if (started_seen_) {
+    const cudaError_t q = api_->eventQuery(end_);
+    if (q == cudaSuccess) {
+      set_status(WorkStatus::COMPLETED);
+      return true;
+    }
+    if (q != cudaErrorNotReady) {
+      set_error(std::string("end event: ") + api_->errorString(q));
+      set_status(WorkStatus::ERROR);
+      return true;
+    }
+    const Millis t = timeout();
+    if (t != kNoTimeout && now - started_at_ > t) {
+      set_error("no completion " + std::to_string(t.count()) + " ms after the operation started on the device");
+      set_status(WorkStatus::TIMEDOUT);
+      return true;
+    }
+  }
+  return false;
+}
+
+void CudaWork::do_wait() {
+  // Stream-ordered: the caller's current stream waits for the end event.
+  c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
+  cudaStream_t cur = at::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(device_)).stream();
+  if (end_ != nullptr) {
+    const cudaError_t e = api_->streamWaitEvent(cur, end_);
+    if (e != cudaSuccess) {
+      set_error(std::string("cudaStreamWaitEvent: ") + api_->errorString(e));
+      set_status(WorkStatus::ERROR);
+    }
+  }
+  keep_alive_.clear();
+}
+
+void CudaWork::do_wait_blocking() {
+  do_wait();
+  if (in_capture_ || end_ == nullptr) {
+    return;
+  }
+  // Host-blocking with the work's own deadline.
+  const auto t0 = std::chrono::steady_clock::now();
+  while (true) {
+    const cudaError_t q = api_->eventQuery(end_);
+    if (q == cudaSuccess) {
+      set_status(WorkStatus::COMPLETED);
+      return;
+    }
+    if (q != cudaErrorNotReady) {
+      set_error(std::string("end event: ") + api_->errorString(q));
+      set_status(WorkStatus::ERROR);
+      return;
+    }
+    const WorkStatus s = status();
+    if (s == WorkStatus::TIMEDOUT || s == WorkStatus::ERROR) {
+      return;
+    }
+    const Millis t = timeout();
+    if (t != kNoTimeout && std::chrono::steady_clock::now() - t0 > t + Millis(1000)) {
+      set_error("host wait exceeded the operation timeout");
+      set_status(WorkStatus::TIMEDOUT);
+      return;
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+
+// ---------------------------------------------------------- CudaBackend ----
+
+CudaBackend::CudaBackend(std::string registered_as) : registered_as_(std::move(registered_as)) {
+  drv_ = DriverApi::real();
+  cuda_ = CudaApi::real();
+  nccl_ = NcclApi::real();
+}
+
+CudaBackend::~CudaBackend() {
+  if (initialized_ && !finalized_) {
+    B200C_LOG(WARN, name_, "CUDA communicator destroyed without finalize(); tearing down");
+    try {
+      finalize();
+    } catch (const std::exception& e) {
+      B200C_LOG(ERROR, name_, "teardown failed: " << e.what());
+    }
+  }
+}
+
+std::string CudaBackend::backend_version() const {
+  return std::string(kBackendAbiVersion) + "+nccl" + (nccl_ && nccl_->available() ? nccl_->version() : "-none");
+}
+
+void CudaBackend::parse_tuning(const Hints& h) {
+  Tuning t = tune_;
+  t.staging_bytes = static_cast<size_t>(hint_or<double>(h, "staging_mb", env_to_value<double>("B200COMMS_STAGING_MB", t.staging_bytes / 1048576.0)) * 1048576.0);
+  t.oneshot_max_bytes = hint_or<size_t>(h, "oneshot_max_bytes", env_to_value<size_t>("B200COMMS_ONESHOT_MAX_BYTES", t.oneshot_max_bytes));
+  t.max_blocks = hint_or<int>(h, "max_blocks", env_to_value<int>("B200COMMS_MAX_BLOCKS", t.max_blocks));
+  t.threads = hint_or<int>(h, "threads", env_to_value<int>("B200COMMS_THREADS", t.threads));
+  t.max_chunk_bytes = hint_or<size_t>(h, "max_chunk_bytes", env_to_value<size_t>("B200COMMS_MAX_CHUNK_BYTES", t.max_chunk_bytes));
+  t.use_multicast = hint_or<bool>(h, "use_multicast", env_to_value<bool>("B200COMMS_NVLS", t.use_multicast));
+  t.use_nccl = hint_or<bool>(h, "use_nccl", env_to_value<bool>("B200COMMS_USE_NCCL", t.use_nccl));
+  t.force = parse_algo(hint_or<std::string>(h, "algo", env_to_value<std::string>("B200COMMS_ALGO", "auto")));
+  t.device_wait_ns = static_cast<unsigned long long>(
+      hint_or<double>(h, "device_wait_ms", env_to_value<double>("B200COMMS_DEVICE_WAIT_MS", t.device_wait_ns / 1.0e6)) * 1.0e6);
+  t.watchdog_interval_ms = hint_or<int>(h, "garbage_collect_interval_ms", t.watchdog_interval_ms);
+  t.max_event_pool = hint_or<size_t>(h, "max_event_pool_size", t.max_event_pool);
+  t.max_blocks = std::max(1, std::min(t.max_blocks, kMaxBlocks));
+  t.threads = std::max(32, std::min(t.threads, 512));
+  t.staging_bytes = std::max<size_t>(t.staging_bytes, 1u << 20);
+  tune_ = t;
+}
+
+void CudaBackend::set_hints(const Hints& h) {
+  // Only knobs that do not change memory layout may move after init.
+  Tuning before = tune_;
+  parse_tuning(h);
+  tune_.staging_bytes = before.staging_bytes;
+  tune_.use_nccl = before.use_nccl;
+  for (auto& kv : h) {
+    opts_.hints[kv.first] = kv.second;
+  }
+}
+
+void CudaBackend::init(at::Device device, const std::string& name, const CommOptions& opts) {
+  TORCH_CHECK(device.is_cuda(), "the '", registered_as_, "' backend needs a CUDA device, got ", device);
+  TORCH_CHECK(!opts.enable_reconfigure, "the CUDA backend does not support enable_reconfigure");
+  auto [rank, size] = query_ranksize();
+  int ndev = 0;
+  B200C_CUDA_CHECK(cudaGetDeviceCount(&ndev));
+  TORCH_CHECK(ndev > 0, "no CUDA device is visible");
+  const int index = device.has_index() && device.index() >= 0 ? device.index() : rank % ndev;
+  device_ = at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(index));
+  name_ = name;
+  opts_ = opts;
+  parse_tuning(opts.hints);
+  auto store = opts.store ? scoped_store(opts.store, "b200c/cuda/" + name)
+                          : create_prefix_store("b200c/cuda/" + name, rank, size, opts.timeout);
+  bootstrap(store, rank, size);
+}
+
+void CudaBackend::bootstrap(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size) {
+  TORCH_CHECK(size >= 1 && size <= kMaxRanks, "the CUDA backend supports 1..", kMaxRanks, " ranks per communicator, got ", size);
+  rank_ = rank;
+  size_ = size;
+  store_ = store;
+  c10::cuda::CUDAGuard guard(device_);
+  B200C_CUDA_CHECK(cudaSetDevice(device_.index()));
+
+  symm_ = std::make_unique<SymmMemory>(store_, rank_, size_, device_.index(), drv_, opts_.timeout, tune_.use_multicast);
+  layout_.bulk_off = 0;
+  layout_.bulk_bytes = round_up(tune_.staging_bytes, 4096);
+  layout_.small_off = layout_.bulk_off + layout_.bulk_bytes;
+  layout_.small_bytes = round_up(kSmallBytes, 4096);
+  const size_t flags_off = layout_.small_off + layout_.small_bytes;
+  const size_t total = flags_off + round_up(kFlagBytes, 4096);
+  heap_ = symm_->allocate(total, tune_.use_multicast);
+
+  std::memset(&dev_, 0, sizeof(dev_));
+  dev_.rank = rank_;
+  dev_.nranks = size_;
+  for (int p = 0; p < size_; ++p) {
+    dev_.heap[p] = heap_->peer_ptrs[p];
+    dev_.flags[p] = reinterpret_cast<uint32_t*>(heap_->peer_ptrs[p] + flags_off);
+  }
+  dev_.mc_heap = heap_->mc_ptr;
+  dev_.mc_flags = heap_->mc_ptr ? reinterpret_cast<uint32_t*>(heap_->mc_ptr + flags_off) : nullptr;
+  dev_.heap_bytes = total;
+  dev_.timeout_ns = tune_.device_wait_ns;
+
+  const size_t epoch_bytes = static_cast<size_t>(kFlagSets) * kMaxBlocks * sizeof(uint32_t);
+  B200C_CUDA_CHECK(cudaMalloc(&epochs_dev_, epoch_bytes));
+  B200C_CUDA_CHECK(cudaMemset(epochs_dev_, 0, epoch_bytes));
+  dev_.epochs = epochs_dev_;
+  B200C_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped));
+  std::memset(status_host_, 0, 64);
+  B200C_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0));
+  dev_.status = status_dev_;
+  B200C_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&replay_pool_host_),
+                                 2 * kMaxGraphEntries * sizeof(unsigned long long), cudaHostAllocMapped));
+  std::memset(replay_pool_host_, 0, 2 * kMaxGraphEntries * sizeof(unsigned long long));
+  B200C_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&replay_pool_dev_), replay_pool_host_, 0));
+
+  int lo = 0, hi = 0;
+  B200C_CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+  B200C_CUDA_CHECK(cudaStreamCreateWithPriority(&internal_stream_, cudaStreamNonBlocking,
+                                                opts_.is_high_priority_stream ? hi : lo));
+  B200C_CUDA_CHECK(cuda_->eventCreate(&dep_event_, cudaEventDisableTiming));
+  B200C_CUDA_CHECK(cuda_->eventCreate(&last_end_, cudaEventDisableTiming));
+  B200C_CUDA_CHECK(cudaDeviceSynchronize());
+
+  if (size_ > 1 && tune_.use_nccl) {
+    init_nccl();
+  }
+  initialized_ = true;
+  start_watchdog();
+  B200C_LOG(INFO, name_, "rank " << rank_ << "/" << size_ << " on " << device_ << ": staging "
+                                 << (layout_.bulk_bytes >> 20) << " MiB, multicast " << (dev_.mc_heap != nullptr)
+                                 << ", nccl " << (nccl_comm_ != nullptr));
+}
+
+void CudaBackend::nccl_check(NcclResult r, const char* what) const {
+  if (r != kNcclSuccess && r != kNcclInProgress) {
+    throw std::runtime_error(std::string(what) + " failed: " + nccl_->errorString(r));
+  }
+}
+
+void CudaBackend::init_nccl() {
+  if (!nccl_->available()) {
+    B200C_LOG(WARN, name_, "libnccl is not loadable: point-to-point operations will be unavailable");
+    return;
+  }
+  NcclUniqueId id{};
+  if (rank_ == 0) {
+    nccl_check(nccl_->getUniqueId(&id), "ncclGetUniqueId");
+    store_set_string(*store_, "nccl_uid", std::string(id.internal, sizeof(id.internal)));
+  } else {
+    const std::string raw = store_get_string(*store_, "nccl_uid");
+    TORCH_CHECK(raw.size() == sizeof(id.internal), "malformed NCCL unique id in the store");
+    std::memcpy(id.internal, raw.data(), sizeof(id.internal));
+  }
+  nccl_check(nccl_->commInitRank(&nccl_comm_, size_, id, rank_), "ncclCommInitRank");
+}
+
+void CudaBackend::check_usable() const {
+  TORCH_CHECK(initialized_, "communicator '", name_, "' is not initialised");
+  TORCH_CHECK(!finalized_, "communicator '", name_, "' was finalized");
+  if (failed_.load()) {
+    throw std::runtime_error("communicator '" + name_ + "' is unusable after a failure: " + failure_text_);
+  }
+  TORCH_CHECK(!aborted_.load(), "communicator '", name_, "' was aborted");
+}
+
+void CudaBackend::on_failure(const std::string& what, bool timed_out) {
+  bool expected = false;
+  if (!failed_.compare_exchange_strong(expected, true)) {
+    return;
+  }
+  failure_text_ = (timed_out ? "operation timed out: " : "operation failed: ") + what;
+  HealthCheck::mark_unhealthy(name_ + ": " + failure_text_);
+  B200C_LOG(ERROR, name_, failure_text_);
+  if (status_host_ != nullptr) {
+    // Kernels that are still waiting see this and fall through to their exit.
+    reinterpret_cast<volatile uint32_t*>(status_host_)[0] |= kStatusAbort;
+  }
+  run_abort_hooks();
+  if (opts_.abort_process_on_timeout_or_error) {
+    B200C_LOG(ERROR, name_, "aborting the process (abort_process_on_timeout_or_error is set)");
+    std::abort();
+  }
+  aborted_ = true;
+}
+
+void CudaBackend::abort() {
+  aborted_ = true;
+  if (status_host_ != nullptr) {
+    reinterpret_cast<volatile uint32_t*>(status_host_)[0] |= kStatusAbort;
+  }
+  if (nccl_comm_ != nullptr) {
+    nccl_->commAbort(nccl_comm_);
+    nccl_comm_ = nullptr;
+  }
+  run_abort_hooks();
+}
+
+std::pair<cudaEvent_t, cudaEvent_t> CudaBackend::take_events() {
+  cudaEvent_t a = nullptr, b = nullptr;
+  {
+    std::lock_guard<std::mutex> g(pool_mu_);
+    if (event_pool_.size() >= 2) {
+      a = event_pool_.back();
+      event_pool_.pop_back();
+      b = event_pool_.back();
+      event_pool_.pop_back();
+    }
+  }
+  if (a == nullptr) {
+    B200C_CUDA_CHECK(cuda_->eventCreate(&a, cudaEventDisableTiming));
+    B200C_CUDA_CHECK(cuda_->eventCreate(&b, cudaEventDisableTiming));
+  }
+  return {a, b};
+}
+
+void CudaBackend::give_events(cudaEvent_t a, cudaEvent_t b) {
+  std::lock_guard<std::mutex> g(pool_mu_);
+  for (cudaEvent_t e : {a, b}) {
+    if (e == nullptr) continue;
+    if (event_pool_.size() < tune_.max_event_pool && !finalized_) {
+      event_pool_.push_back(e);
+    } else {
+      cuda_->eventDestroy(e);
+    }
+  }
+}
+
+WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, std::vector<at::Tensor> keep_alive,
+                         const std::function<void(cudaStream_t)>& launch) {
+  check_usable();
+  c10::cuda::CUDAGuard guard(device_);
+  cudaStream_t current = at::cuda::getCurrentCUDAStream(device_.index()).stream();
+  cudaStream_t stream = async_op ? internal_stream_ : current;
+  bool capturing = false;
+  unsigned long long graph_id = 0;
+  cuda_->streamIsCapturing(current, &capturing, &graph_id);
+
+  if (async_op) {
+    B200C_CUDA_CHECK(cuda_->eventRecord(dep_event_, current));
+    B200C_CUDA_CHECK(cuda_->streamWaitEvent(internal_stream_, dep_event_));
+  }
+  // Operations of one communicator share staging slots and flags: keep them
+  // in issue order even across streams. (Inside a capture only dependencies
+  // created inside the same capture are legal, and those are already there.)
+  if (have_last_ && last_stream_ != stream && !capturing) {
+    B200C_CUDA_CHECK(cuda_->streamWaitEvent(stream, last_end_));
+  }
+
+  cudaEvent_t ev_start = nullptr, ev_end = nullptr;
+  if (capturing) {
+    // Resource creation is not a capturable operation: step out of the strict
+    // capture mode for the two calls.
+    cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+    cudaThreadExchangeStreamCaptureMode(&mode);
+    const cudaError_t e1 = cuda_->eventCreate(&ev_start, cudaEventDisableTiming);
+    const cudaError_t e2 = cuda_->eventCreate(&ev_end, cudaEventDisableTiming);
+    cudaThreadExchangeStreamCaptureMode(&mode);
+    B200C_CUDA_CHECK(e1);
+    B200C_CUDA_CHECK(e2);
+  } else {
+    std::tie(ev_start, ev_end) = take_events();
+  }
+
+  unsigned long long* replay_counters = nullptr;  // device alias of this collective's replay counters
+  if (capturing) {
+    GraphEntry e{};
+    e.graph_id = graph_id;
+    e.index = graph_next_index_[graph_id]++;
+    e.stream = reinterpret_cast<uintptr_t>(stream);
+    e.timeout = effective_timeout(o);
+    std::lock_guard<std::mutex> g(wd_mu_);
+    TORCH_CHECK(graph_entries_.size() < kMaxGraphEntries,
+                "too many collectives captured into CUDA graphs on this communicator (", kMaxGraphEntries, ")");
+    // Counter pairs come from a page pinned at start-up: nothing is allocated
+    // while a capture is open.
+    e.counters_host = replay_pool_host_ + 2 * graph_entries_.size();
+    e.counters_dev = replay_pool_dev_ + 2 * graph_entries_.size();
+    e.counters_host[0] = e.counters_host[1] = 0;
+    replay_counters = e.counters_dev;
+    graph_entries_.push_back(e);
+  }
+
+  B200C_CUDA_CHECK(cuda_->eventRecord(ev_start, stream));
+  if (replay_counters != nullptr) {
+    B200C_CUDA_CHECK(launch_counter_increment(replay_counters, stream));
+  }
+  launch(stream);
+  if (replay_counters != nullptr) {
+    B200C_CUDA_CHECK(launch_counter_increment(replay_counters + 1, stream));
+  }
+  B200C_CUDA_CHECK(cuda_->eventRecord(ev_end, stream));
+  if (!capturing) {
+    B200C_CUDA_CHECK(cuda_->eventRecord(last_end_, stream));
+    last_stream_ = stream;
+    have_last_ = true;
+  }
+
+  auto self = std::static_pointer_cast<CudaBackend>(shared_from_this());
+  if (!async_op) {
+    keep_alive.clear();  // stream order already protects the tensors
+  }
+  auto work = c10::make_intrusive<CudaWork>(cuda_, ev_start, ev_end, !capturing, device_.index(), effective_timeout(o),
+                                            std::move(keep_alive), self, capturing);
+  ops_issued_++;
+  {
+    std::lock_guard<std::mutex> g(wd_mu_);
+    algo_counts_[what]++;
+    if (!capturing) {
+      inflight_.push_back(work);
+    }
+  }
+  return work;
+}
+
+void CudaBackend::start_watchdog() {
+  wd_stop_ = false;
+  watchdog_ = std::thread([this]() { watchdog_loop(); });
+}
+
+void CudaBackend::stop_watchdog() {
+  {
+    std::lock_guard<std::mutex> g(wd_mu_);
+    wd_stop_ = true;
+  }
+  wd_cv_.notify_all();
+  if (watchdog_.joinable()) {
+    watchdog_.join();
+  }
+}
+
+void CudaBackend::watchdog_loop() {
+  cudaSetDevice(device_.index());
+  std::unique_lock<std::mutex> lk(wd_mu_);
+  while (!wd_stop_) {
+    wd_cv_.wait_for(lk, std::chrono::milliseconds(tune_.watchdog_interval_ms));
+    if (wd_stop_) break;
+    const auto now = std::chrono::steady_clock::now();
+    std::string failure;
+    bool timed_out = false;
+    // Works complete in issue order per stream; scan the whole queue anyway
+    // (two streams interleave) and drop the terminal ones.
+    for (auto it = inflight_.begin(); it != inflight_.end();) {
+      auto& w = *it;
+      if (w->poll(now)) {
+        const WorkStatus s = w->status();
+        if (s == WorkStatus::TIMEDOUT || s == WorkStatus::ERROR) {
+          failure = w->error();
+          timed_out = s == WorkStatus::TIMEDOUT;
+        }
+        it = inflight_.erase(it);
+      } else {
+        ++it;
+      }
+    }
+    // Device-side bounded waits report through the status word.
+    if (failure.empty() && status_host_ != nullptr) {
+      const volatile uint32_t* s = reinterpret_cast<volatile uint32_t*>(status_host_);
+      if (s[0] & kStatusTimeout) {
+        std::ostringstream os;
+        os << "a device-side wait ran out (rank " << s[1] << ", block " << s[2] << ", waiting for rank "
+           << static_cast<int>(s[3]) << ", phase 0x" << std::hex << s[4] << ")";
+        failure = os.str();
+        timed_out = true;
+      } else if (s[0] & kStatusBadArg) {
+        failure = "a kernel rejected its arguments (bounds check)";
+      }
+    }
+    if (failure.empty() && nccl_comm_ != nullptr) {
+      NcclResult async = kNcclSuccess;
+      if (nccl_->commGetAsyncError(nccl_comm_, &async) == kNcclSuccess && async != kNcclSuccess && async != kNcclInProgress) {
+        failure = "NCCL asynchronous error: " + nccl_->errorString(async);
+      }
+    }
+    // Graph replays: counters tell how many times each captured collective
+    // started and ended.
+    std::vector<std::tuple<unsigned long long, unsigned long long, uintptr_t, size_t, char>> replay_events;
+    for (auto& e : graph_entries_) {
+      const unsigned long long st = reinterpret_cast<volatile unsigned long long*>(e.counters_host)[0];
+      const unsigned long long en = reinterpret_cast<volatile unsigned long long*>(e.counters_host)[1];
+      while (e.seen_start < st) {
+        replay_events.emplace_back(e.graph_id, e.seen_start, e.stream, e.index, 'S');
+        e.seen_start++;
+        e.open_since = now;
+      }
+      while (e.seen_end < en) {
+        replay_events.emplace_back(e.graph_id, e.seen_end, e.stream, e.index, 'E');
+        e.seen_end++;
+      }
+      if (failure.empty() && e.seen_start > e.seen_end && e.timeout != kNoTimeout && now - e.open_since > e.timeout) {
+        failure = "a captured collective (graph " + std::to_string(e.graph_id) + ", index " + std::to_string(e.index) +
+            ") did not finish within its timeout during replay";
+        timed_out = true;
+      }
+    }
+    lk.unlock();
+    if (!replay_events.empty() && replay_hooks_) {
+      for (auto& h : replay_hooks_->snapshot()) {
+        for (auto& ev : replay_events) {
+          h(std::get<0>(ev), std::get<1>(ev), std::get<2>(ev), std::get<3>(ev), std::get<4>(ev));
+        }
+      }
+    }
+    if (!failure.empty()) {
+      on_failure(failure, timed_out);
+    }
+    lk.lock();
+  }
+}
+
+void CudaBackend::finalize() {
+  TORCH_CHECK(initialized_, "communicator '", name_, "' is not initialised");
+  TORCH_CHECK(!finalized_, "communicator '", name_, "' was already finalized");
+  c10::cuda::CUDAGuard guard(device_);
+  const bool broken = failed_.load() || aborted_.load();
+  if (!broken) {
+    // Drain: every rank's kernels are done before any mapping disappears.
+    cudaStreamSynchronize(internal_stream_);
+    cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
+    if (size_ > 1) {
+      try {
+        store_barrier(*store_, "finalize", rank_, size_, std::min<Millis>(opts_.timeout, Millis(30000)));
+      } catch (const std::exception& e) {
+        // A peer that failed never arrives; its mappings are gone either way.
+        B200C_LOG(WARN, name_, "finalize: not every rank arrived at the closing barrier: " << e.what());
+      }
+    }
+  }
+  stop_watchdog();
+  finalized_ = true;
+  {
+    std::lock_guard<std::mutex> g(wd_mu_);
+    inflight_.clear();
+    graph_entries_.clear();
+  }
+  if (replay_pool_host_) cudaFreeHost(replay_pool_host_);
+  replay_pool_host_ = nullptr;
+  if (nccl_comm_ != nullptr) {
+    if (broken) {
+      nccl_->commAbort(nccl_comm_);
+    } else {
+      nccl_->commDestroy(nccl_comm_);
+    }
+    nccl_comm_ = nullptr;
+  }
+  if (heap_) {
+    symm_->release(heap_);
+    heap_.reset();
+  }
+  symm_.reset();
+  if (epochs_dev_) cudaFree(epochs_dev_);
+  if (status_host_) cudaFreeHost(status_host_);
+  epochs_dev_ = nullptr;
+  status_host_ = nullptr;
+  {
+    std::lock_guard<std::mutex> g(pool_mu_);
+    for (cudaEvent_t e : event_pool_) cuda_->eventDestroy(e);
+    event_pool_.clear();
+  }
+  if (dep_event_) cuda_->eventDestroy(dep_event_);
+  if (last_end_) cuda_->eventDestroy(last_end_);
+  if (internal_stream_) cudaStreamDestroy(internal_stream_);
+  dep_event_ = last_end_ = nullptr;
+  internal_stream_ = nullptr;
+  if (failed_.load()) {
+    throw std::runtime_error("communicator '" + name_ + "' finalized after a failure: " + failure_text_);
+  }
+}
+
+Algo CudaBackend::algo_override(const OpOptions& o) const {
+  auto it = o.hints.find("algo");
+  if (it != o.hints.end()) {
+    return parse_algo(it->second);
+  }
+  return tune_.force;
+}
+
+bool CudaBackend::kernels_can_reduce(at::ScalarType t, const ReduceOp& op) const {
+  DType d;
+  if (!to_dtype(t, &d)) return false;
+  switch (op.type()) {
+    case RedOpType::BAND:
+    case RedOpType::BOR:
+    case RedOpType::BXOR:
+      return false;
+    default:
+      return true;
+  }
+}
+
+// Blocks and per-block chunk for `bytes` of payload when one slot holds
+// `slot_multiplier` chunks (nranks for reduce-scatter / all-to-all, else 1).
+LaunchShape CudaBackend::shape_for(size_t bytes, size_t slot_multiplier) const {
+  LaunchShape s;
+  s.threads = tune_.threads;
+  const size_t max_chunk = std::max<size_t>(
+      256, std::min(tune_.max_chunk_bytes, layout_.bulk_bytes / (static_cast<size_t>(tune_.max_blocks) * slot_multiplier)));
+  // Aim for every block to run several steps on large payloads so that copy
+  // and link phases of different blocks overlap; small payloads use few blocks.
+  size_t chunk = round_up(std::max<size_t>(bytes / (static_cast<size_t>(tune_.max_blocks) * 4) + 1, tune_.min_chunk_bytes), 256);
+  chunk = std::min(chunk, max_chunk / 256 * 256);
+  chunk = std::max<size_t>(chunk, 256);
+  const size_t steps = (bytes + chunk - 1) / chunk;
+  s.chunk_bytes = chunk;
+  s.blocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(tune_.max_blocks, steps)));
+  return s;
+}
+
+static RedKind red_kind(const ReduceOp& op) {
+  switch (op.type()) {
+    case RedOpType::PRODUCT: return RedKind::PROD;
+    case RedOpType::MIN: return RedKind::MIN;
+    case RedOpType::MAX: return RedKind::MAX;
+    default: return RedKind::SUM;
+  }
+}
+
+static float red_scale(const ReduceOp& op, int nranks) {
+  if (op.type() == RedOpType::AVG) return 1.0f / static_cast<float>(nranks);
+  if (op.type() == RedOpType::PREMUL_SUM) return static_cast<float>(op.factor_as_double());
+  return 1.0f;
+}
+
+WorkPtr CudaBackend::all_reduce(at::Tensor& t, const ReduceOp& op, bool async_op, const OpOptions& o) {
+  check_tensor(t, device_, "all_reduce");
+  const size_t bytes = t.nbytes();
+  if (bytes == 0) return c10::make_intrusive<CompletedWork>();
+  Algo algo = algo_override(o);
+  const bool kernels_ok = kernels_can_reduce(t.scalar_type(), op);
+  if (!kernels_ok) {
+    TORCH_CHECK(op.type() != RedOpType::BAND && op.type() != RedOpType::BOR && op.type() != RedOpType::BXOR,
+                "bitwise reductions are not supported on the CUDA backend");
+    algo = Algo::NCCL;
+  }
+  if (algo == Algo::NCCL && (nccl_comm_ == nullptr || size_ == 1)) {
+    if (size_ == 1) {
+      // A lone rank: only PREMUL_SUM changes the data.
+      if (op.type() == RedOpType::PREMUL_SUM) t.mul_(op.factor_as_double());
+      return c10::make_intrusive<CompletedWork>();
+    }
+    TORCH_CHECK(kernels_ok, "all_reduce of ", t.scalar_type(), " needs NCCL, which is not available");
+    algo = Algo::AUTO;
+  }
+  if (algo == Algo::NCCL) {
+    NcclDataType dt;
+    TORCH_CHECK(to_nccl_dtype(t.scalar_type(), &dt), "all_reduce: unsupported dtype ", t.scalar_type());
+    const ReduceOp opc = op;
+    at::Tensor tt = t;
+    return run("all_reduce/nccl", async_op, o, {t}, [this, tt, dt, opc](cudaStream_t s) {
+      NcclRedOp rop = kNcclSum;
+      bool custom = false;
+      switch (opc.type()) {
+        case RedOpType::PRODUCT: rop = kNcclProd; break;
+        case RedOpType::MIN: rop = kNcclMin; break;
+        case RedOpType::MAX: rop = kNcclMax; break;
+        case RedOpType::AVG: rop = kNcclAvg; break;
+        case RedOpType::PREMUL_SUM: {
+          // Host-immediate scalar in the tensor's own dtype.
+          at::Tensor f = at::scalar_tensor(opc.factor_as_double(), at::TensorOptions().dtype(tt.scalar_type()));
+          nccl_check(nccl_->redOpCreatePreMulSum(&rop, f.data_ptr(), dt, nccl_comm_), "ncclRedOpCreatePreMulSum");
+          custom = true;
+          break;
+        }
+        default: break;
+      }
+      nccl_check(nccl_->allReduce(tt.data_ptr(), tt.data_ptr(), tt.numel(), dt, rop, nccl_comm_, s), "ncclAllReduce");
+      if (custom) nccl_->redOpDestroy(rop, nccl_comm_);
+    });
+  }
+  DType dt;
+  to_dtype(t.scalar_type(), &dt);
+  const bool sum_like = red_kind(op) == RedKind::SUM;
+  int kalgo;
+  if (algo == Algo::ONESHOT) kalgo = 0;
+  else if (algo == Algo::TWOSHOT || algo == Algo::STAGED) kalgo = 1;
+  else kalgo = bytes <= tune_.oneshot_max_bytes ? 0 : 1;
+  if (bytes > static_cast<size_t>(kSmallBlocks) * kSmallPiece) kalgo = 1;
+  const float scale = red_scale(op, size_);
+  const RedKind rk = red_kind(op);
+  const bool mc = tune_.use_multicast && sum_like && dev_.mc_heap != nullptr;
+  const LaunchShape shape = shape_for(bytes, 1);
+  at::Tensor tt = t;
+  bytes_issued_ += bytes;
+  return run(kalgo == 0 ? "all_reduce/oneshot" : "all_reduce/twoshot", async_op, o, {t},
+             [this, tt, dt, rk, scale, kalgo, mc, shape](cudaStream_t s) {
+               const void* in = tt.data_ptr();
+               void* out = tt.data_ptr();
+               B200C_CUDA_CHECK(launch_all_reduce(&dev_, layout_, 0, &in, &out, tt.numel(), dt, rk, scale, kalgo, mc, shape, s));
+             });
+}
+
+WorkPtr CudaBackend::reduce(const at::Tensor& t, int root, const ReduceOp& op, bool async_op, const OpOptions& o) {
+  check_tensor(t, device_, "reduce");
+  if (t.numel() == 0) return c10::make_intrusive<CompletedWork>();
+  NcclDataType ndt;
+  if (nccl_comm_ != nullptr && algo_override(o) == Algo::NCCL && to_nccl_dtype(t.scalar_type(), &ndt) &&
+      op.type() != RedOpType::PREMUL_SUM) {
+    NcclRedOp rop = kNcclSum;
+    switch (op.type()) {
+      case RedOpType::PRODUCT: rop = kNcclProd; break;
+      case RedOpType::MIN: rop = kNcclMin; break;
+      case RedOpType::MAX: rop = kNcclMax; break;
+      case RedOpType::AVG: rop = kNcclAvg; break;
+      default: break;
+    }
+    at::Tensor tt = t;
+    return run("reduce/nccl", async_op, o, {t}, [this, tt, ndt, rop, root](cudaStream_t s) {
+      nccl_check(nccl_->reduce(tt.data_ptr(), tt.data_ptr(), tt.numel(), ndt, rop, root, nccl_comm_, s), "ncclReduce");
+    });
+  }
+  TORCH_CHECK(kernels_can_reduce(t.scalar_type(), op), "reduce: unsupported dtype / reduction for the CUDA backend");
+  // All-reduce into the tensor on the root and into scratch elsewhere, so that
+  // non-root inputs stay untouched.
+  DType dt;
+  to_dtype(t.scalar_type(), &dt);
+  at::Tensor in = t;
+  at::Tensor out = rank_ == root ? t : at::empty_like(t);
+  const float scale = red_scale(op, size_);
+  const RedKind rk = red_kind(op);
+  const size_t bytes = t.nbytes();
+  const int kalgo = bytes <= std::min(tune_.oneshot_max_bytes, static_cast<size_t>(kSmallBlocks) * kSmallPiece) ? 0 : 1;
+  const bool mc = tune_.use_multicast && rk == RedKind::SUM && dev_.mc_heap != nullptr;
+  const LaunchShape shape = shape_for(bytes, 1);
+  return run("reduce/kernel", async_op, o, {in, out}, [this, in, out, dt, rk, scale, kalgo, mc, shape](cudaStream_t s) {
+    const void* ip = in.data_ptr();
+    void* op_ = out.data_ptr();
+    B200C_CUDA_CHECK(launch_all_reduce(&dev_, layout_, 0, &ip, &op_, in.numel(), dt, rk, scale, kalgo, mc, shape, s));
+  });
+}
+
+WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bool async_op, const OpOptions& o) {
+  check_tensor(out, device_, "all_gather_single");
+  check_tensor(in, device_, "all_gather_single");
+  TORCH_CHECK(out.numel() == in.numel() * size_, "all_gather_single: output numel must be input numel * size");
+  const bool cast = in.scalar_type() == at::kFloat && out.scalar_type() == at::kBFloat16;
+  TORCH_CHECK(cast || in.scalar_type() == out.scalar_type(),
+              "all_gather_single: dtypes must match (or float32 input with bfloat16 output for the fused cast)");
+  if (in.numel() == 0) return c10::make_intrusive<CompletedWork>();
+  if (algo_override(o) == Algo::NCCL && nccl_comm_ != nullptr && !cast) {
+    NcclDataType dt;
+    if (to_nccl_dtype(in.scalar_type(), &dt)) {
+      at::Tensor i = in, ot = out;
+      return run("all_gather/nccl", async_op, o, {in}, [this, i, ot, dt](cudaStream_t s) {
+        nccl_check(nccl_->allGather(i.data_ptr(), ot.data_ptr(), i.numel(), dt, nccl_comm_, s), "ncclAllGather");
+      });
+    }
+  }
+  const size_t bytes = in.nbytes();
+  const LaunchShape shape = shape_for(cast ? bytes / 2 : bytes, 1);
+  at::Tensor i = in, ot = out;
+  bytes_issued_ += bytes;
+  return run(cast ? "all_gather/kernel+cast" : "all_gather/kernel", async_op, o, {in}, [this, i, ot, bytes, cast, shape](cudaStream_t s) {
+    const void* ip = i.data_ptr();
+    void* op_ = ot.data_ptr();
+    B200C_CUDA_CHECK(launch_all_gather(&dev_, layout_, 0, &ip, &op_, bytes, cast, dev_.mc_heap != nullptr, shape, s));
+  });
+}
+
+WorkPtr CudaBackend::all_gather(const std::vector<at::Tensor>& outs, const at::Tensor& in, bool async_op, const OpOptions& o) {
+  TORCH_CHECK(static_cast<int>(outs.size()) == size_, "all_gather: need size() output tensors");
+  check_tensor(in, device_, "all_gather");
+  for (auto& t : outs) {
+    check_tensor(t, device_, "all_gather");
+    TORCH_CHECK(t.numel() == in.numel() && t.scalar_type() == in.scalar_type(),
+                "all_gather: every output must match the input's numel and dtype");
+  }
+  // Gather into one buffer, then fan out with device copies on the same stream.
+  at::Tensor flat = at::empty({static_cast<int64_t>(size_) * in.numel()}, in.options());
+  at::Tensor i = in;
+  auto dsts = outs;
+  const size_t bytes = in.nbytes();
+  const LaunchShape shape = shape_for(bytes, 1);
+  if (bytes == 0) return c10::make_intrusive<CompletedWork>();
+  return run("all_gather_list/kernel", async_op, o, {in, flat}, [this, i, flat, dsts, bytes, shape](cudaStream_t s) {
+    const void* ip = i.data_ptr();
+    void* op_ = flat.data_ptr();
+    B200C_CUDA_CHECK(launch_all_gather(&dev_, layout_, 0, &ip, &op_, bytes, false, false, shape, s));
+    for (int r = 0; r < size_; ++r) {
+      B200C_CUDA_CHECK(cudaMemcpyAsync(dsts[r].data_ptr(), static_cast<char*>(flat.data_ptr()) + r * bytes, bytes,
+                                       cudaMemcpyDeviceToDevice, s));
+    }
+  });
+}
+
+// Generic exchange through the all-to-all kernel. `send` / `recv` list, per
+// peer, (byte offset, byte length) into `in` / `out`.
+static WorkPtr exchange(CudaBackend* self, const char* what, at::Tensor in, at::Tensor out,
+                        std::vector<std::pair<size_t, size_t>> send, std::vector<std::pair<size_t, size_t>> recv,
+                        bool async_op, const OpOptions& o, std::vector<at::Tensor> keep,
+                        std::function<void(cudaStream_t)> after = nullptr) {
+  const int n = self->size();
+  // The grid must not depend on rank-local sizes (see launch_all_to_all).
+  LaunchShape shape;
+  shape.threads = self->tuning().threads;
+  shape.blocks = std::min(32, self->tuning().max_blocks);
+  shape.chunk_bytes = std::min<size_t>(self->tuning().max_chunk_bytes,
+                                       self->layout().bulk_bytes / (static_cast<size_t>(shape.blocks) * n)) / 256 * 256;
+  return self->run(what, async_op, o, std::move(keep), [self, in, out, send, recv, shape, n, after](cudaStream_t s) {
+    std::vector<size_t> so(n), sl(n), ro(n), rl(n);
+    size_t mx = 0;
+    for (int p = 0; p < n; ++p) {
+      so[p] = send[p].first;
+      sl[p] = send[p].second;
+      ro[p] = recv[p].first;
+      rl[p] = recv[p].second;
+      mx = std::max(mx, std::max(sl[p], rl[p]));
+    }
+    const void* ip = in.defined() ? in.data_ptr() : nullptr;
+    void* op_ = out.defined() ? out.data_ptr() : nullptr;
+    B200C_CUDA_CHECK(launch_all_to_all(&self->comm_dev(), self->layout(), 0, &ip, &op_, so.data(), sl.data(), ro.data(),
+                                       rl.data(), mx, shape, s));
+    if (after) after(s);
+  });
+}
+
+WorkPtr CudaBackend::all_gather_v(const std::vector<at::Tensor>& outs, const at::Tensor& in, bool async_op, const OpOptions& o) {
+  TORCH_CHECK(static_cast<int>(outs.size()) == size_, "all_gather_v: need size() output tensors");
+  check_tensor(in, device_, "all_gather_v");
+  TORCH_CHECK(outs[rank_].numel() == in.numel(), "all_gather_v: own output slot must match the input");
+  std::vector<std::pair<size_t, size_t>> send(size_), recv(size_);
+  size_t total = 0;
+  for (int r = 0; r < size_; ++r) {
+    check_tensor(outs[r], device_, "all_gather_v");
+    TORCH_CHECK(outs[r].scalar_type() == in.scalar_type(), "all_gather_v: dtype mismatch");
+    send[r] = {0, in.nbytes()};
+    recv[r] = {total, outs[r].nbytes()};
+    total += round_up(outs[r].nbytes(), 16);
+    recv[r].first = total - round_up(outs[r].nbytes(), 16);
+  }
+  at::Tensor flat = at::empty({static_cast<int64_t>(std::max<size_t>(total, 16))}, in.options().dtype(at::kByte));
+  auto dsts = outs;
+  auto offs = recv;
+  return exchange(this, "all_gather_v/kernel", in, flat, send, recv, async_op, o, {in, flat},
+                  [dsts, flat, offs](cudaStream_t s) {
+                    for (size_t r = 0; r < dsts.size(); ++r) {
+                      if (offs[r].second == 0) continue;
+                      B200C_CUDA_CHECK(cudaMemcpyAsync(dsts[r].data_ptr(), static_cast<char*>(flat.data_ptr()) + offs[r].first,
+                                                       offs[r].second, cudaMemcpyDeviceToDevice, s));
+                    }
+                  });
+}
+
+WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in, const ReduceOp& op, bool async_op, const OpOptions& o) {
+  check_tensor(out, device_, "reduce_scatter_single");
+  check_tensor(in, device_, "reduce_scatter_single");
+  TORCH_CHECK(in.numel() == out.numel() * size_, "reduce_scatter_single: input numel must be output numel * size");
+  if (out.numel() == 0) return c10::make_intrusive<CompletedWork>();
+  const bool same = in.scalar_type() == out.scalar_type();
+  Algo algo = algo_override(o);
+  if (!kernels_can_reduce(in.scalar_type(), op) || !kernels_can_reduce(out.scalar_type(), op)) {
+    algo = Algo::NCCL;
+  }
+  if (algo == Algo::NCCL && nccl_comm_ != nullptr && same) {
+    NcclDataType dt;
+    TORCH_CHECK(to_nccl_dtype(in.scalar_type(), &dt), "reduce_scatter_single: unsupported dtype ", in.scalar_type());
+    TORCH_CHECK(op.type() != RedOpType::PREMUL_SUM && op.type() != RedOpType::BAND && op.type() != RedOpType::BOR &&
+                    op.type() != RedOpType::BXOR,
+                "reduce_scatter_single: this reduction is not available on the NCCL path");
+    NcclRedOp rop = kNcclSum;
+    switch (op.type()) {
+      case RedOpType::PRODUCT: rop = kNcclProd; break;
+      case RedOpType::MIN: rop = kNcclMin; break;
+      case RedOpType::MAX: rop = kNcclMax; break;
+      case RedOpType::AVG: rop = kNcclAvg; break;
+      default: break;
+    }
+    at::Tensor i = in, ot = out;
+    return run("reduce_scatter/nccl", async_op, o, {in}, [this, i, ot, dt, rop](cudaStream_t s) {
+      nccl_check(nccl_->reduceScatter(i.data_ptr(), ot.data_ptr(), ot.numel(), dt, rop, nccl_comm_, s), "ncclReduceScatter");
+    });
+  }
+  TORCH_CHECK(kernels_can_reduce(in.scalar_type(), op) && kernels_can_reduce(out.scalar_type(), op),
+              "reduce_scatter_single: unsupported dtype / reduction (", in.scalar_type(), " -> ", out.scalar_type(), ")");
+  DType din, dout;
+  to_dtype(in.scalar_type(), &din);
+  to_dtype(out.scalar_type(), &dout);
+  // Wire dtype: the input's, unless the caller asks for bf16 on the wire
+  // (hint "wire_dtype") or mixes fp32 with bf16.
+  DType dwire = din;
+  auto it = o.hints.find("wire_dtype");
+  if (it != o.hints.end() && (it->second == "bf16" || it->second == "bfloat16")) dwire = DType::BF16;
+  if (!same) dwire = DType::BF16;
+  if (dwire != din || !same) {
+    TORCH_CHECK(red_kind(op) == RedKind::SUM, "mixed-precision reduce_scatter supports SUM / AVG / PREMUL_SUM only");
+    TORCH_CHECK((din == DType::F32 || din == DType::BF16) && (dout == DType::F32 || dout == DType::BF16),
+                "mixed-precision reduce_scatter supports float32 / bfloat16 only");
+  }
+  const float scale = red_scale(op, size_);
+  const RedKind rk = red_kind(op);
+  const bool mc = tune_.use_multicast && rk == RedKind::SUM && dev_.mc_heap != nullptr;
+  const size_t wire_bytes = out.numel() * dtype_size(dwire);
+  const LaunchShape shape = shape_for(wire_bytes, size_);
+  at::Tensor i = in, ot = out;
+  bytes_issued_ += in.nbytes();
+  return run("reduce_scatter/kernel", async_op, o, {in}, [this, i, ot, din, dwire, dout, rk, scale, mc, shape](cudaStream_t s) {
+    const void* ip = i.data_ptr();
+    void* op_ = ot.data_ptr();
+    B200C_CUDA_CHECK(launch_reduce_scatter(&dev_, layout_, 0, &ip, &op_, ot.numel(), din, dwire, dout, rk, scale, mc, shape, s));
+  });
+}
+
+WorkPtr CudaBackend::reduce_scatter(at::Tensor& out, const std::vector<at::Tensor>& ins, const ReduceOp& op, bool async_op, const OpOptions& o) {
+  TORCH_CHECK(static_cast<int>(ins.size()) == size_, "reduce_scatter: need size() input tensors");
+  for (auto& t : ins) {
+    check_tensor(t, device_, "reduce_scatter");
+    TORCH_CHECK(t.numel() == out.numel() && t.scalar_type() == out.scalar_type(),
+                "reduce_scatter: every input must match the output's numel and dtype");
+  }
+  std::vector<at::Tensor> flat_ins;
+  for (auto& t : ins) flat_ins.push_back(t.reshape({-1}));
+  at::Tensor flat = at::cat(flat_ins);
+  return reduce_scatter_single(out, flat, op, async_op, o);
+}
+
+WorkPtr CudaBackend::reduce_scatter_v(at::Tensor& out, const std::vector<at::Tensor>& ins, const ReduceOp& op, bool async_op, const OpOptions& o) {
+  TORCH_CHECK(static_cast<int>(ins.size()) == size_, "reduce_scatter_v: need size() input tensors");
+  check_tensor(out, device_, "reduce_scatter_v");
+  TORCH_CHECK(ins[rank_].numel() == out.numel(), "reduce_scatter_v: own input slot must match the output");
+  // Uneven shares: all-reduce the concatenation, keep the own share.
+  std::vector<at::Tensor> flat_ins;
+  int64_t my_off = 0, off = 0;
+  for (int r = 0; r < size_; ++r) {
+    check_tensor(ins[r], device_, "reduce_scatter_v");
+    if (r == rank_) my_off = off;
+    off += ins[r].numel();
+    flat_ins.push_back(ins[r].reshape({-1}));
+  }
+  at::Tensor flat = at::cat(flat_ins);
+  all_reduce(flat, op, async_op, o);
+  at::Tensor dst = out;
+  const int64_t len = out.numel();
+  // The copy-out is stream-ordered behind the all-reduce.
+  return run("reduce_scatter_v/copy", async_op, o, {flat}, [flat, dst, my_off, len](cudaStream_t s) {
+    B200C_CUDA_CHECK(cudaMemcpyAsync(dst.data_ptr(), static_cast<char*>(flat.data_ptr()) + my_off * flat.element_size(),
+                                     len * flat.element_size(), cudaMemcpyDeviceToDevice, s));
+  });
+}
+
+WorkPtr CudaBackend::all_to_all_single(at::Tensor& out, const at::Tensor& in, bool async_op, const OpOptions& o) {
+  check_tensor(out, device_, "all_to_all_single");
+  check_tensor(in, device_, "all_to_all_single");
+  TORCH_CHECK(out.numel() == in.numel() && out.scalar_type() == in.scalar_type(),
+              "all_to_all_single: input and output must have the same numel and dtype");
+  TORCH_CHECK(in.numel() % size_ == 0, "all_to_all_single: numel must divide by size()");
+  if (in.numel() == 0) return c10::make_intrusive<CompletedWork>();
+  const size_t blk = in.nbytes() / size_;
+  std::vector<std::pair<size_t, size_t>> send(size_), recv(size_);
+  for (int p = 0; p < size_; ++p) {
+    send[p] = {p * blk, blk};
+    recv[p] = {p * blk, blk};
+  }
+  bytes_issued_ += in.nbytes();
+  return exchange(this, "all_to_all_single/kernel", in, out, send, recv, async_op, o, {in});
+}
+
+WorkPtr CudaBackend::all_to_all_v_single(at::Tensor& out, const at::Tensor& in, const std::vector<int64_t>& out_splits,
+                                         const std::vector<int64_t>& in_splits, bool async_op, const OpOptions& o) {
+  check_tensor(out, device_, "all_to_all_v_single");
+  check_tensor(in, device_, "all_to_all_v_single");
+  TORCH_CHECK(out.scalar_type() == in.scalar_type(), "all_to_all_v_single: dtype mismatch");
+  TORCH_CHECK(static_cast<int>(out_splits.size()) == size_ && static_cast<int>(in_splits.size()) == size_,
+              "all_to_all_v_single: need size() split sizes on both sides");
+  // Split sizes count dim-0 slices.
+  const size_t in_row = in.dim() > 0 && in.size(0) > 0 ? in.nbytes() / in.size(0) : in.element_size();
+  const size_t out_row = out.dim() > 0 && out.size(0) > 0 ? out.nbytes() / out.size(0) : out.element_size();
+  std::vector<std::pair<size_t, size_t>> send(size_), recv(size_);
+  size_t so = 0, ro = 0;
+  for (int p = 0; p < size_; ++p) {
+    TORCH_CHECK(in_splits[p] >= 0 && out_splits[p] >= 0, "all_to_all_v_single: negative split size");
+    send[p] = {so, in_splits[p] * in_row};
+    recv[p] = {ro, out_splits[p] * out_row};
+    so += send[p].second;
+    ro += recv[p].second;
+  }
+  TORCH_CHECK(so <= in.nbytes(), "all_to_all_v_single: input splits exceed the input tensor");
+  TORCH_CHECK(ro <= out.nbytes(), "all_to_all_v_single: output splits exceed the output tensor");
+  bytes_issued_ += so;
+  return exchange(this, "all_to_all_v_single/kernel", in, out, send, recv, async_op, o, {in});
+}
+
+WorkPtr CudaBackend::all_to_all(const std::vector<at::Tensor>& outs, const std::vector<at::Tensor>& ins, bool async_op, const OpOptions& o) {
+  TORCH_CHECK(static_cast<int>(outs.size()) == size_ && static_cast<int>(ins.size()) == size_,
+              "all_to_all: need size() input and output tensors");
+  std::vector<std::pair<size_t, size_t>> send(size_), recv(size_);
+  std::vector<at::Tensor> flat_ins;
+  size_t so = 0, ro = 0;
+  for (int p = 0; p < size_; ++p) {
+    check_tensor(ins[p], device_, "all_to_all");
+    check_tensor(outs[p], device_, "all_to_all");
+    TORCH_CHECK(ins[p].scalar_type() == ins[0].scalar_type() && outs[p].scalar_type() == ins[0].scalar_type(),
+                "all_to_all: every tensor must have the same dtype");
+    send[p] = {so, ins[p].nbytes()};
+    recv[p] = {ro, outs[p].nbytes()};
+    so += ins[p].nbytes();
+    ro += round_up(outs[p].nbytes(), 16);
+    flat_ins.push_back(ins[p].reshape({-1}));
+  }
+  at::Tensor in = at::cat(flat_ins);
+  at::Tensor out = at::empty({static_cast<int64_t>(std::max<size_t>(ro, 16))}, in.options().dtype(at::kByte));
+  auto dsts = outs;
+  auto offs = recv;
+  return exchange(this, "all_to_all_list/kernel", in, out, send, recv, async_op, o, {in, out},
+                  [dsts, out, offs](cudaStream_t s) {
+                    for (size_t r = 0; r < dsts.size(); ++r) {
+                      if (offs[r].second == 0) continue;
+                      B200C_CUDA_CHECK(cudaMemcpyAsync(dsts[r].data_ptr(), static_cast<char*>(out.data_ptr()) + offs[r].first,
+                                                       offs[r].second, cudaMemcpyDeviceToDevice, s));
+                    }
+                  });
+}
+
+WorkPtr CudaBackend::device_alltoallv_single(at::Tensor& out, const at::Tensor& in, const at::Tensor& out_splits,
+                                             const at::Tensor& in_splits, bool async_op, const OpOptions& o) {
+  check_tensor(out, device_, "device_alltoallv_single");
+  check_tensor(in, device_, "device_alltoallv_single");
+  check_tensor(in_splits, device_, "device_alltoallv_single");
+  TORCH_CHECK(in_splits.scalar_type() == at::kLong && in_splits.numel() == size_,
+              "device_alltoallv_single: input_split_sizes must be an int64 device tensor of size() entries");
+  (void)out_splits;  // receive sizes are learnt from the senders on the device
+  const size_t row = in.dim() > 0 && in.size(0) > 0 ? in.nbytes() / in.size(0) : in.element_size();
+  LaunchShape shape;
+  shape.threads = tune_.threads;
+  shape.blocks = std::min(32, tune_.max_blocks);
+  shape.chunk_bytes = std::min<size_t>(tune_.max_chunk_bytes, layout_.bulk_bytes / (static_cast<size_t>(shape.blocks) * size_)) / 256 * 256;
+  at::Tensor i = in, ot = out, sp = in_splits;
+  return run("device_alltoallv/kernel", async_op, o, {in, in_splits}, [this, i, ot, sp, row, shape](cudaStream_t s) {
+    const void* ip = i.data_ptr();
+    void* op_ = ot.data_ptr();
+    const long long* counts = reinterpret_cast<const long long*>(sp.data_ptr<int64_t>());
+    B200C_CUDA_CHECK(launch_all_to_all_device_splits(&dev_, layout_, 0, &ip, &op_, &counts, row, shape, s));
+  });
+}
+
+WorkPtr CudaBackend::reduce_scatter_quantized(at::Tensor& out, const at::Tensor& in, const ReduceOp& op, int64_t seed,
+                                              bool async_op, const OpOptions& o) {
+  (void)seed;
+  TORCH_CHECK(in.scalar_type() == at::kFloat && out.scalar_type() == at::kFloat,
+              "reduce_scatter_quantized: float32 input and output");
+  OpOptions oo = o;
+  oo.hints["wire_dtype"] = "bf16";
+  return reduce_scatter_single(out, in, op, async_op, oo);
+}
+
+WorkPtr CudaBackend::broadcast(at::Tensor& t, int root, bool async_op, const OpOptions& o) {
+  check_tensor(t, device_, "broadcast");
+  if (t.numel() == 0 || size_ == 1) return c10::make_intrusive<CompletedWork>();
+  NcclDataType ndt;
+  if (algo_override(o) == Algo::NCCL && nccl_comm_ != nullptr && to_nccl_dtype(t.scalar_type(), &ndt)) {
+    at::Tensor tt = t;
+    return run("broadcast/nccl", async_op, o, {t}, [this, tt, ndt, root](cudaStream_t s) {
+      nccl_check(nccl_->broadcast(tt.data_ptr(), tt.data_ptr(), tt.numel(), ndt, root, nccl_comm_, s), "ncclBroadcast");
+    });
+  }
+  const size_t bytes = t.nbytes();
+  const LaunchShape shape = shape_for(bytes, 1);
+  at::Tensor tt = t;
+  bytes_issued_ += bytes;
+  return run("broadcast/kernel", async_op, o, {t}, [this, tt, bytes, root, shape](cudaStream_t s) {
+    void* p = tt.data_ptr();
+    B200C_CUDA_CHECK(launch_broadcast(&dev_, layout_, 0, &p, bytes, root, dev_.mc_heap != nullptr, shape, s));
+  });
+}
+
+WorkPtr CudaBackend::barrier(bool async_op, const OpOptions& o) {
+  return run("barrier/kernel", async_op, o, {}, [this](cudaStream_t s) {
+    B200C_CUDA_CHECK(launch_barrier(&dev_, 0, s));
+  });
+}
+
+WorkPtr CudaBackend::scatter(at::Tensor& out, const std::vector<at::Tensor>& ins, int root, bool async_op, const OpOptions& o) {
+  check_tensor(out, device_, "scatter");
+  std::vector<std::pair<size_t, size_t>> send(size_, {0, 0}), recv(size_, {0, 0});
+  at::Tensor in;
+  if (rank_ == root) {
+    TORCH_CHECK(static_cast<int>(ins.size()) == size_, "scatter: the root needs size() input tensors");
+    std::vector<at::Tensor> flat_ins;
+    size_t off = 0;
+    for (int p = 0; p < size_; ++p) {
+      check_tensor(ins[p], device_, "scatter");
+      TORCH_CHECK(ins[p].numel() == out.numel() && ins[p].scalar_type() == out.scalar_type(),
+                  "scatter: every input must match the output's numel and dtype");
+      send[p] = {off, ins[p].nbytes()};
+      off += ins[p].nbytes();
+      flat_ins.push_back(ins[p].reshape({-1}));
+    }
+    in = at::cat(flat_ins);
+  } else {
+    in = at::empty({0}, out.options());
+  }
+  recv[root] = {0, out.nbytes()};
+  return exchange(this, "scatter/kernel", in, out, send, recv, async_op, o, {in});
+}
+
+WorkPtr CudaBackend::gather(const std::vector<at::Tensor>& outs, const at::Tensor& in, int root, bool async_op, const OpOptions& o) {
+  check_tensor(in, device_, "gather");
+  std::vector<std::pair<size_t, size_t>> send(size_, {0, 0}), recv(size_, {0, 0});
+  send[root] = {0, in.nbytes()};
+  at::Tensor out;
+  std::function<void(cudaStream_t)> after;
+  if (rank_ == root) {
+    TORCH_CHECK(static_cast<int>(outs.size()) == size_, "gather: the root needs size() output tensors");
+    const size_t blk = round_up(in.nbytes(), 16);
+    for (int p = 0; p < size_; ++p) {
+      check_tensor(outs[p], device_, "gather");
+      TORCH_CHECK(outs[p].numel() == in.numel() && outs[p].scalar_type() == in.scalar_type(),
+                  "gather: every output must match the input's numel and dtype");
+      recv[p] = {p * blk, in.nbytes()};
+    }
+    out = at::empty({static_cast<int64_t>(std::max<size_t>(blk * size_, 16))}, in.options().dtype(at::kByte));
+    auto dsts = outs;
+    auto offs = recv;
+    at::Tensor flat = out;
+    after = [dsts, flat, offs](cudaStream_t s) {
+      for (size_t r = 0; r < dsts.size(); ++r) {
+        if (offs[r].second == 0) continue;
+        B200C_CUDA_CHECK(cudaMemcpyAsync(dsts[r].data_ptr(), static_cast<char*>(flat.data_ptr()) + offs[r].first,
+                                         offs[r].second, cudaMemcpyDeviceToDevice, s));
+      }
+    };
+  } else {
+    out = at::empty({16}, in.options().dtype(at::kByte));
+  }
+  return exchange(this, "gather/kernel", in, out, send, recv, async_op, o, {in, out}, after);
+}
+
+WorkPtr CudaBackend::send(const at::Tensor& t, int dst, bool async_op, const OpOptions& o) {
+  check_tensor(t, device_, "send");
+  TORCH_CHECK(nccl_comm_ != nullptr, "send needs NCCL (communicator created with use_nccl=0, or libnccl missing)");
+  NcclDataType dt;
+  TORCH_CHECK(to_nccl_dtype(t.scalar_type(), &dt), "send: unsupported dtype ", t.scalar_type());
+  at::Tensor tt = t;
+  return run("send/nccl", async_op, o, {t}, [this, tt, dt, dst](cudaStream_t s) {
+    nccl_check(nccl_->send(tt.data_ptr(), tt.numel(), dt, dst, nccl_comm_, s), "ncclSend");
+  });
+}
+
+WorkPtr CudaBackend::recv(at::Tensor& t, int src, bool async_op, const OpOptions& o) {
+  check_tensor(t, device_, "recv");
+  TORCH_CHECK(nccl_comm_ != nullptr, "recv needs NCCL (communicator created with use_nccl=0, or libnccl missing)");
+  NcclDataType dt;
+  TORCH_CHECK(to_nccl_dtype(t.scalar_type(), &dt), "recv: unsupported dtype ", t.scalar_type());
+  at::Tensor tt = t;
+  return run("recv/nccl", async_op, o, {t}, [this, tt, dt, src](cudaStream_t s) {
+    nccl_check(nccl_->recv(tt.data_ptr(), tt.numel(), dt, src, nccl_comm_, s), "ncclRecv");
+  });
+}
+
+WorkPtr CudaBackend::batch_op_issue(const std::vector<P2POp>& ops, bool async_op, const OpOptions& o) {
+  if (ops.empty()) return c10::make_intrusive<CompletedWork>();
+  TORCH_CHECK(nccl_comm_ != nullptr, "batched send/recv needs NCCL");
+  std::vector<at::Tensor> keep;
+  for (auto& op : ops) {
+    check_tensor(op.tensor, device_, "batch_op_issue");
+    keep.push_back(op.tensor);
+  }
+  auto copy = ops;
+  return run("batch_p2p/nccl", async_op, o, keep, [this, copy](cudaStream_t s) {
+    nccl_check(nccl_->groupStart(), "ncclGroupStart");
+    for (auto& op : copy) {
+      NcclDataType dt;
+      TORCH_CHECK(to_nccl_dtype(op.tensor.scalar_type(), &dt), "batch_op_issue: unsupported dtype");
+      if (op.kind == P2PKind::SEND) {
+        nccl_check(nccl_->send(op.tensor.data_ptr(), op.tensor.numel(), dt, op.peer, nccl_comm_, s), "ncclSend");
+      } else {
+        nccl_check(nccl_->recv(op.tensor.data_ptr(), op.tensor.numel(), dt, op.peer, nccl_comm_, s), "ncclRecv");
+      }
+    }
+    nccl_check(nccl_->groupEnd(), "ncclGroupEnd");
+  });
+}
+
+std::shared_ptr<Backend> CudaBackend::split(const std::vector<int>& ranks, const std::string& name, const CommOptions& opts) {
+  check_usable();
+  const uint64_t gen = split_counter_++;
+  if (ranks.empty()) {
+    return nullptr;
+  }
+  int color = ranks[0], idx = -1;
+  for (size_t i = 0; i < ranks.size(); ++i) {
+    color = std::min(color, ranks[i]);
+    if (ranks[i] == rank_) idx = static_cast<int>(i);
+  }
+  TORCH_CHECK(idx >= 0, "split: calling rank is not a member of the new group");
+  auto child = std::make_shared<CudaBackend>(registered_as_);
+  child->device_ = device_;
+  child->name_ = name_ + "::split::" + std::to_string(color) + "_" + name + "_" + std::to_string(gen);
+  child->opts_ = opts;
+  child->opts_.store = nullptr;
+  child->drv_ = drv_;
+  child->cuda_ = cuda_;
+  child->nccl_ = nccl_;
+  child->tune_ = tune_;
+  child->parse_tuning(opts.hints);
+  auto sub = scoped_store(store_, "split/" + std::to_string(gen) + "/" + std::to_string(color));
+  child->bootstrap(sub, idx, static_cast<int>(ranks.size()));
+  return child;
+}
+
+std::unordered_map<std::string, std::string> CudaBackend::comm_dump() const {
+  std::unordered_map<std::string, std::string> d;
+  d["name"] = name_;
+  d["backend"] = registered_as_;
+  d["rank"] = std::to_string(rank_);
+  d["size"] = std::to_string(size_);
+  d["device"] = std::to_string(device_.index());
+  d["symm_mode"] = symm_ ? (symm_->mode() == SymmMode::VMM_FD ? "vmm+fd" : symm_->mode() == SymmMode::CUDA_IPC ? "cuda-ipc" : "local") : "none";
+  d["multicast"] = dev_.mc_heap != nullptr ? "1" : "0";
+  d["nccl"] = nccl_comm_ != nullptr ? "1" : "0";
+  d["staging_bytes"] = std::to_string(layout_.bulk_bytes);
+  d["ops_issued"] = std::to_string(ops_issued_.load());
+  d["bytes_issued"] = std::to_string(bytes_issued_.load());
+  d["failed"] = failed_.load() ? failure_text_ : "";
+  {
+    std::lock_guard<std::mutex> g(const_cast<std::mutex&>(wd_mu_));
+    d["inflight"] = std::to_string(inflight_.size());
+    for (auto& kv : algo_counts_) {
+      d["count/" + kv.first] = std::to_string(kv.second);
+    }
+  }
+  return d;
+}
+
+std::shared_ptr<Window> CudaBackend::new_window(const std::optional<at::Tensor>& tensor) {
+  check_usable();
+  auto self = std::static_pointer_cast<CudaBackend>(shared_from_this());
+  auto w = std::make_shared<CudaWindow>(self);
+  if (tensor) {
+    w->tensor_register(*tensor, true);
+  }
+  return w;
+}
+
+// ----------------------------------------------------------- CudaWindow ----
+
+namespace {
+constexpr int kHostSignalId = 0;  // signal slot used by the host-side signal()/wait_signal()
+}
+
+CudaWindow::~CudaWindow() {
+  if (registered_) {
+    B200C_LOG(WARN, "window", "window destroyed while a tensor is still registered");
+  }
+}
+
+void CudaWindow::tensor_register(const at::Tensor& t, bool owning) {
+  TORCH_CHECK(!registered_, "window: a tensor is already registered");
+  check_tensor(t, owner_->device(), "window.tensor_register");
+  (void)owning;
+  tensor_ = t;  // keeps the storage alive for the lifetime of the registration
+  cache_meta(t);
+  data_seg_ = owner_->symm().attach_user_buffer(t.data_ptr(), t.nbytes());
+  registered_ = true;
+}
+
+void CudaWindow::tensor_deregister() {
+  TORCH_CHECK(registered_, "window: no tensor is registered");
+  c10::cuda::CUDAGuard guard(owner_->device());
+  bool capturing = false;
+  unsigned long long gid = 0;
+  owner_->cuda_api()->streamIsCapturing(at::cuda::getCurrentCUDAStream(owner_->device().index()).stream(), &capturing, &gid);
+  if (capturing) {
+    return;  // a captured region cannot change mappings
+  }
+  // Nobody may still be storing into this rank's buffer.
+  owner_->barrier(false, {})->wait_blocking();
+  cudaDeviceSynchronize();
+  if (dev_window_) {
+    cudaFree(dev_window_);
+    dev_window_ = nullptr;
+  }
+  if (local_state_) {
+    cudaFree(local_state_);
+    local_state_ = nullptr;
+  }
+  if (ctrl_seg_) {
+    owner_->symm().release(ctrl_seg_);
+    ctrl_seg_.reset();
+  }
+  owner_->symm().release(data_seg_);
+  data_seg_.reset();
+  for (auto& lb : local_buffers_) cudaFree(lb.first);
+  local_buffers_.clear();
+  tensor_.reset();
+  registered_ = false;
+  owner_->barrier(false, {})->wait_blocking();
+}
+
+std::shared_ptr<Window> CudaWindow::clone() {
+  auto w = std::make_shared<CudaWindow>(owner_);
+  if (registered_ && tensor_) {
+    // Memory from the same allocator class as the original where possible.
+    at::Tensor copy = tensor_->clone();
+    w->tensor_register(copy, true);
+  }
+  return w;
+}
+
+void CudaWindow::build_device_window(int signal_count, int counter_count, int barrier_count) {
+  TORCH_CHECK(registered_, "window: register a tensor first");
+  const int n = owner_->size();
+  if (signal_count < 0) signal_count = n;
+  if (counter_count < 0) counter_count = n;
+  if (barrier_count < 1) barrier_count = 1;
+  signal_count += 1;  // slot 0 belongs to the host API
+  c10::cuda::CUDAGuard guard(owner_->device());
+  const size_t sig_bytes = static_cast<size_t>(signal_count) * n * sizeof(uint64_t);
+  const size_t bar_bytes = static_cast<size_t>(barrier_count) * n * sizeof(uint64_t);
+  ctrl_seg_ = owner_->symm().allocate(sig_bytes + bar_bytes, false);
+  const size_t local_words = static_cast<size_t>(counter_count) + barrier_count + n;
+  B200C_CUDA_CHECK(cudaMalloc(&local_state_, local_words * sizeof(uint64_t)));
+  B200C_CUDA_CHECK(cudaMemset(local_state_, 0, local_words * sizeof(uint64_t)));
+  DeviceWindow w{};
+  w.rank = owner_->rank();
+  w.nranks = n;
+  w.bytes = data_seg_->bytes;
+  for (int p = 0; p < n; ++p) {
+    w.data[p] = data_seg_->peer_ptrs[p];
+    w.signals[p] = reinterpret_cast<uint64_t*>(ctrl_seg_->peer_ptrs[p]);
+    w.barrier_flags[p] = reinterpret_cast<uint64_t*>(ctrl_seg_->peer_ptrs[p] + sig_bytes);
+  }
+  w.mc_data = data_seg_->mc_ptr;
+  w.signal_count = signal_count;
+  w.counter_count = counter_count;
+  w.barrier_count = barrier_count;
+  w.counters = local_state_;
+  w.barrier_epochs = local_state_ + counter_count;
+  w.status = owner_->comm_dev().status;
+  w.timeout_ns = owner_->comm_dev().timeout_ns;
+  host_copy_ = w;
+  B200C_CUDA_CHECK(cudaMalloc(&dev_window_, sizeof(DeviceWindow)));
+  B200C_CUDA_CHECK(cudaMemcpy(dev_window_, &w, sizeof(DeviceWindow), cudaMemcpyHostToDevice));
+}
+
+uintptr_t CudaWindow::get_device_window(int signal_count, int counter_count, int barrier_count) {
+  if (dev_window_ == nullptr) {
+    build_device_window(signal_count, counter_count, barrier_count);
+  }
+  return reinterpret_cast<uintptr_t>(dev_window_);
+}
+
+WorkPtr CudaWindow::put(const at::Tensor& src, int dst_rank, int64_t target_offset_nelems, bool async_op, const OpOptions& o) {
+  TORCH_CHECK(registered_, "window.put: no tensor is registered");
+  check_tensor(src, owner_->device(), "window.put");
+  TORCH_CHECK(dst_rank >= 0 && dst_rank < owner_->size(), "window.put: bad destination rank ", dst_rank);
+  TORCH_CHECK(target_offset_nelems >= 0, "window.put: negative offset");
+  const size_t esz = c10::elementSize(dtype_);
+  TORCH_CHECK((static_cast<size_t>(target_offset_nelems) + src.numel()) * esz <= static_cast<size_t>(get_size()),
+              "window.put: ", src.numel(), " elements at offset ", target_offset_nelems, " do not fit the window");
+  get_device_window(-1, -1, 1);
+  at::Tensor s = src;
+  const size_t off = static_cast<size_t>(target_offset_nelems) * esz;
+  DeviceWindow* dw = dev_window_;
+  return owner_->run("window_put/kernel", async_op, o, {src}, [dw, s, dst_rank, off](cudaStream_t st) {
+    B200C_CUDA_CHECK(launch_window_put(dw, s.data_ptr(), s.nbytes(), dst_rank, off, st));
+  });
+}
+
+WorkPtr CudaWindow::signal(int dst_rank, bool async_op, const OpOptions& o) {
+  TORCH_CHECK(registered_, "window.signal: no tensor is registered");
+  TORCH_CHECK(dst_rank >= 0 && dst_rank < owner_->size(), "window.signal: bad rank ", dst_rank);
+  get_device_window(-1, -1, 1);
+  DeviceWindow* dw = dev_window_;
+  return owner_->run("window_signal/kernel", async_op, o, {}, [dw, dst_rank](cudaStream_t st) {
+    B200C_CUDA_CHECK(launch_window_signal(dw, dst_rank, kHostSignalId, st));
+  });
+}
+
+WorkPtr CudaWindow::wait_signal(int peer_rank, bool async_op, const OpOptions& o) {
+  TORCH_CHECK(registered_, "window.wait_signal: no tensor is registered");
+  TORCH_CHECK(peer_rank >= 0 && peer_rank < owner_->size(), "window.wait_signal: bad rank ", peer_rank);
+  get_device_window(-1, -1, 1);
+  DeviceWindow* dw = dev_window_;
+  uint64_t* expected = local_state_ + host_copy_.counter_count + host_copy_.barrier_count;
+  return owner_->run("window_wait/kernel", async_op, o, {}, [dw, peer_rank, expected](cudaStream_t st) {
+    B200C_CUDA_CHECK(launch_window_wait_signal(dw, peer_rank, kHostSignalId, expected, st));
+  });
+}
+
+at::Tensor CudaWindow::map_remote_tensor(int rank) {
+  TORCH_CHECK(registered_, "window.map_remote_tensor: no tensor is registered");
+  TORCH_CHECK(rank >= 0 && rank < owner_->size(), "window.map_remote_tensor: bad rank ", rank);
+  if (rank == owner_->rank()) {
+    return *tensor_;
+  }
+  auto keep = data_seg_;
+  return at::from_blob(data_seg_->peer_ptrs[rank], shape_, [keep](void*) {}, at::TensorOptions().dtype(dtype_).device(device_));
+}
+
+WindowAttr CudaWindow::get_attr(int peer_rank) {
+  TORCH_CHECK(peer_rank >= 0 && peer_rank < owner_->size(), "window.get_attr: bad rank ", peer_rank);
+  WindowAttr a;
+  a.access_type = WinAccessType::UNIFIED;  // every peer is reachable with loads and stores
+  return a;
+}
+
+uintptr_t CudaWindow::register_local_buffer(const at::Tensor& t) {
+  TORCH_CHECK(dev_window_ != nullptr, "register_local_buffer: call get_device_window() first");
+  check_tensor(t, owner_->device(), "register_local_buffer");
+  RegisteredBuffer host{static_cast<char*>(t.data_ptr()), static_cast<size_t>(t.nbytes())};
+  RegisteredBuffer* dev = nullptr;
+  B200C_CUDA_CHECK(cudaMalloc(&dev, sizeof(RegisteredBuffer)));
+  B200C_CUDA_CHECK(cudaMemcpy(dev, &host, sizeof(host), cudaMemcpyHostToDevice));
+  local_buffers_.emplace_back(dev, t);
+  return reinterpret_cast<uintptr_t>(dev);
+}
+
+void CudaWindow::deregister_local_buffer(uintptr_t handle) {
+  for (auto it = local_buffers_.begin(); it != local_buffers_.end(); ++it) {
+    if (reinterpret_cast<uintptr_t>(it->first) == handle) {
+      cudaFree(it->first);
+      local_buffers_.erase(it);
+      return;
+    }
+  }
+  TORCH_CHECK(false, "deregister_local_buffer: unknown handle");
+}
+
+void register_cuda_backends() {
+  for (const char* name : {"b200", "nccl", "ncclx"}) {
+    const std::string n = name;
+    Factory::get().register_backend(n, [n] { return std::make_shared<CudaBackend>(n); });
+  }
+}
+
+} // namespace b200c

@@ -1,0 +1,279 @@
+// The CUDA backend ("b200"; also answers to "nccl" and "ncclx").
+//
+// One process per GPU inside one NVLink/NVSwitch domain. Collectives run as
+// peer-memory kernels over a symmetric heap (see kernels/collectives.cu); NCCL
+// carries point-to-point traffic and whatever the kernels do not cover.
+//
+// Stream rules: a synchronous operation is enqueued on the caller's current
+// stream; an asynchronous one on the communicator's internal stream after an
+// event dependency on the current stream. `work.wait()` never blocks the
+// host: it makes the current stream wait for the operation's end event.
+// Operations of one communicator are serialised among themselves even when
+// they sit on different streams (they share staging memory and flags).
+//
+// A watchdog thread polls the end events (cudaEventQuery only), the device
+// status word written by bounded waits, and NCCL's asynchronous error state.
+// A failure marks the process unhealthy, runs abort hooks, and either aborts
+// the process or makes the next call raise, as configured.
+//
+// Parity: comms/torchcomms/ncclx/TorchCommNCCLX.hpp:86-561 (backend),
+// TorchCommNCCLXUtils.cpp:202-343 (watchdog), :456-478 (stream choice),
+// TorchWorkNCCLX.cpp:160-308 (events, wait), TorchCommNCCLXBootstrap.cpp:42-390
+// (bootstrap over a c10d store), GraphEventTracker.hpp:26-195 (graph replay
+// monitoring), TorchCommWindowNCCLX.hpp:59-246 (window).
+#pragma once
+
+#include <atomic>
+#include <condition_variable>
+#include <deque>
+#include <thread>
+
+#include "../core/comm.hpp"
+#include "../cuda/driver_api.hpp"
+#include "../cuda/nccl_api.hpp"
+#include "../kernels/collectives.h"
+#include "../kernels/window.h"
+#include "../mem/symm_memory.hpp"
+
+namespace b200c {
+
+class CudaBackend;
+
+// Asynchronous handle of a stream-ordered operation.
+class CudaWork final : public Work {
+ public:
+  CudaWork(std::shared_ptr<CudaApi> api, cudaEvent_t start, cudaEvent_t end, bool pooled, int device,
+           Millis timeout, std::vector<at::Tensor> keep_alive, std::weak_ptr<CudaBackend> owner, bool in_capture);
+  ~CudaWork() override;
+
+  // Called by the watchdog: advances NOT_STARTED -> INPROGRESS -> COMPLETED /
+  // TIMEDOUT from event queries. Returns true once the work is terminal.
+  bool poll(std::chrono::steady_clock::time_point now);
+  cudaEvent_t end_event() const { return end_; }
+  cudaEvent_t start_event() const { return start_; }
+  bool pooled() const { return pooled_; }
+  void release_events(cudaEvent_t* start, cudaEvent_t* end);
+
+ protected:
+  void do_wait() override;
+  void do_wait_blocking() override;
+
+ private:
+  std::shared_ptr<CudaApi> api_;
+  cudaEvent_t start_, end_;
+  bool pooled_;
+  int device_;
+  std::vector<at::Tensor> keep_alive_;
+  std::weak_ptr<CudaBackend> owner_;
+  bool in_capture_;
+  std::mutex poll_mu_;
+  bool started_seen_ = false;
+  std::chrono::steady_clock::time_point started_at_{};
+};
+
+// Which kernel family serves an operation.
+enum class Algo : int { AUTO = 0, ONESHOT = 1, TWOSHOT = 2, STAGED = 3, NCCL = 4 };
+
+struct Tuning {
+  size_t staging_bytes = 128ull << 20;     // bulk staging per rank
+  size_t oneshot_max_bytes = 256 * 1024;   // all-reduce: one-shot up to here
+  int max_blocks = 128;                    // bulk kernels
+  int threads = 512;
+  size_t max_chunk_bytes = 1u << 20;       // bytes staged per block per step
+  size_t min_chunk_bytes = 16 * 1024;
+  bool use_multicast = true;
+  bool use_nccl = true;                    // create the NCCL communicator at init
+  Algo force = Algo::AUTO;                 // B200COMMS_ALGO / hint "algo"
+  unsigned long long device_wait_ns = 10ull * 1000 * 1000 * 1000;  // budget of one device-side wait
+  int watchdog_interval_ms = 100;
+  size_t max_event_pool = 1000;
+};
+
+class CudaWindow;
+
+class CudaBackend final : public Backend {
+ public:
+  CudaBackend(std::string registered_as = "b200");
+  ~CudaBackend() override;
+
+  void init(at::Device device, const std::string& name, const CommOptions& opts) override;
+  void finalize() override;
+  int rank() const override { return rank_; }
+  int size() const override { return size_; }
+  std::string backend_name() const override { return registered_as_; }
+  std::string backend_version() const override;
+  std::string comm_name() const override { return name_; }
+  at::Device device() const override { return device_; }
+  const CommOptions& options() const override { return opts_; }
+
+  WorkPtr send(const at::Tensor& t, int dst, bool async_op, const OpOptions& o) override;
+  WorkPtr recv(at::Tensor& t, int src, bool async_op, const OpOptions& o) override;
+  WorkPtr batch_op_issue(const std::vector<P2POp>& ops, bool async_op, const OpOptions& o) override;
+  WorkPtr broadcast(at::Tensor& t, int root, bool async_op, const OpOptions& o) override;
+  WorkPtr all_reduce(at::Tensor& t, const ReduceOp& op, bool async_op, const OpOptions& o) override;
+  WorkPtr reduce(const at::Tensor& t, int root, const ReduceOp& op, bool async_op, const OpOptions& o) override;
+  WorkPtr all_gather(const std::vector<at::Tensor>& outs, const at::Tensor& in, bool async_op, const OpOptions& o) override;
+  WorkPtr all_gather_v(const std::vector<at::Tensor>& outs, const at::Tensor& in, bool async_op, const OpOptions& o) override;
+  WorkPtr all_gather_single(at::Tensor& out, const at::Tensor& in, bool async_op, const OpOptions& o) override;
+  WorkPtr reduce_scatter(at::Tensor& out, const std::vector<at::Tensor>& ins, const ReduceOp& op, bool async_op, const OpOptions& o) override;
+  WorkPtr reduce_scatter_v(at::Tensor& out, const std::vector<at::Tensor>& ins, const ReduceOp& op, bool async_op, const OpOptions& o) override;
+  WorkPtr reduce_scatter_single(at::Tensor& out, const at::Tensor& in, const ReduceOp& op, bool async_op, const OpOptions& o) override;
+  WorkPtr all_to_all_single(at::Tensor& out, const at::Tensor& in, bool async_op, const OpOptions& o) override;
+  WorkPtr all_to_all_v_single(at::Tensor& out, const at::Tensor& in, const std::vector<int64_t>& out_splits,
+                              const std::vector<int64_t>& in_splits, bool async_op, const OpOptions& o) override;
+  WorkPtr all_to_all(const std::vector<at::Tensor>& outs, const std::vector<at::Tensor>& ins, bool async_op, const OpOptions& o) override;
+  WorkPtr barrier(bool async_op, const OpOptions& o) override;
+  WorkPtr scatter(at::Tensor& out, const std::vector<at::Tensor>& ins, int root, bool async_op, const OpOptions& o) override;
+  WorkPtr gather(const std::vector<at::Tensor>& outs, const at::Tensor& in, int root, bool async_op, const OpOptions& o) override;
+  std::shared_ptr<Backend> split(const std::vector<int>& ranks, const std::string& name, const CommOptions& opts) override;
+  std::shared_ptr<Window> new_window(const std::optional<at::Tensor>& tensor) override;
+
+  void set_timeout(Millis t) override { opts_.timeout = t; }
+  void set_hints(const Hints& h) override;
+  void abort() override;
+  bool is_aborted() const override { return aborted_.load(); }
+  bool is_abort_supported() const override { return true; }
+
+  // Backend-specific operations (reached through get_backend_impl()).
+  // Split sizes live on the device (int64 counts of dim-0 slices).
+  WorkPtr device_alltoallv_single(at::Tensor& out, const at::Tensor& in, const at::Tensor& out_splits,
+                                  const at::Tensor& in_splits, bool async_op, const OpOptions& o);
+  // fp32 in / fp32 out, bf16 on the wire; optional stochastic rounding seed.
+  WorkPtr reduce_scatter_quantized(at::Tensor& out, const at::Tensor& in, const ReduceOp& op, int64_t seed,
+                                   bool async_op, const OpOptions& o);
+  std::unordered_map<std::string, std::string> comm_dump() const;
+  void set_config(const Hints& h) { set_hints(h); }
+  uintptr_t get_nccl_comm_ptr() const { return reinterpret_cast<uintptr_t>(nccl_comm_); }
+
+  // Shared with windows and fused ops.
+  const CommDev& comm_dev() const { return dev_; }
+  const HeapLayout& layout() const { return layout_; }
+  const Tuning& tuning() const { return tune_; }
+  SymmMemory& symm() { return *symm_; }
+  std::shared_ptr<CudaApi> cuda_api() const { return cuda_; }
+  cudaStream_t internal_stream() const { return internal_stream_; }
+
+  // Runs `launch(stream)` with the backend's stream / event / watchdog
+  // protocol and returns the work. `keep_alive` tensors are held until wait()
+  // for asynchronous operations.
+  WorkPtr run(const char* what, bool async_op, const OpOptions& o, std::vector<at::Tensor> keep_alive,
+              const std::function<void(cudaStream_t)>& launch);
+
+  // Test seams.
+  void set_cuda_api(std::shared_ptr<CudaApi> api) { cuda_ = std::move(api); }
+  void set_nccl_api(std::shared_ptr<NcclApi> api) { nccl_ = std::move(api); }
+
+  // Called by works / watchdog on failures.
+  void on_failure(const std::string& what, bool timed_out);
+  // Returns a finished work's events to the pool.
+  void recycle_events(cudaEvent_t a, cudaEvent_t b) { give_events(a, b); }
+
+ private:
+  friend class CudaWindow;
+  void check_usable() const;
+  void parse_tuning(const Hints& h);
+  void bootstrap(const c10::intrusive_ptr<c10d::Store>& store, int rank, int size);
+  void init_nccl();
+  void start_watchdog();
+  void stop_watchdog();
+  void watchdog_loop();
+  Millis effective_timeout(const OpOptions& o) const { return o.timeout_set ? o.timeout : opts_.timeout; }
+  Algo algo_override(const OpOptions& o) const;
+  bool kernels_can_reduce(at::ScalarType t, const ReduceOp& op) const;
+  LaunchShape shape_for(size_t bytes, size_t slot_multiplier) const;
+  std::pair<cudaEvent_t, cudaEvent_t> take_events();
+  void give_events(cudaEvent_t a, cudaEvent_t b);
+  void nccl_check(NcclResult r, const char* what) const;
+
+  std::string registered_as_;
+  int rank_ = -1, size_ = -1;
+  std::string name_;
+  at::Device device_{at::kCUDA, 0};
+  CommOptions opts_;
+  Tuning tune_;
+  c10::intrusive_ptr<c10d::Store> store_;
+  std::shared_ptr<DriverApi> drv_;
+  std::shared_ptr<CudaApi> cuda_;
+  std::shared_ptr<NcclApi> nccl_;
+  NcclComm* nccl_comm_ = nullptr;
+  std::unique_ptr<SymmMemory> symm_;
+  std::shared_ptr<SymmSegment> heap_;
+  HeapLayout layout_;
+  CommDev dev_{};
+  uint32_t* epochs_dev_ = nullptr;
+  uint32_t* status_host_ = nullptr;   // mapped pinned
+  uint32_t* status_dev_ = nullptr;    // device alias of status_host_
+  cudaStream_t internal_stream_ = nullptr;
+  cudaEvent_t dep_event_ = nullptr;
+  cudaStream_t last_stream_ = nullptr;
+  cudaEvent_t last_end_ = nullptr;
+  bool have_last_ = false;
+
+  std::mutex pool_mu_;
+  std::vector<cudaEvent_t> event_pool_;
+
+  std::thread watchdog_;
+  std::mutex wd_mu_;
+  std::condition_variable wd_cv_;
+  std::deque<c10::intrusive_ptr<CudaWork>> inflight_;
+  bool wd_stop_ = false;
+
+  // Graph replay monitoring: two counters in mapped pinned memory per
+  // captured collective (started / ended), bumped by one-thread kernels.
+  struct GraphEntry {
+    unsigned long long graph_id;
+    size_t index;
+    unsigned long long* counters_host;  // [2]
+    unsigned long long* counters_dev;
+    unsigned long long seen_start = 0, seen_end = 0;
+    std::chrono::steady_clock::time_point open_since{};
+    uintptr_t stream;
+    Millis timeout;
+  };
+  static constexpr size_t kMaxGraphEntries = 2048;
+  unsigned long long* replay_pool_host_ = nullptr;  // 2 x kMaxGraphEntries counters, mapped pinned
+  unsigned long long* replay_pool_dev_ = nullptr;
+  std::vector<GraphEntry> graph_entries_;
+  std::unordered_map<unsigned long long, size_t> graph_next_index_;
+
+  std::atomic<bool> aborted_{false};
+  std::atomic<bool> failed_{false};
+  std::string failure_text_;
+  bool finalized_ = false;
+  bool initialized_ = false;
+  uint64_t split_counter_ = 0;
+  std::atomic<uint64_t> ops_issued_{0}, bytes_issued_{0};
+  std::unordered_map<std::string, uint64_t> algo_counts_;
+};
+
+class CudaWindow final : public Window {
+ public:
+  explicit CudaWindow(std::shared_ptr<CudaBackend> owner) : owner_(std::move(owner)) {}
+  ~CudaWindow() override;
+  void tensor_register(const at::Tensor& t, bool owning) override;
+  void tensor_deregister() override;
+  std::shared_ptr<Window> clone() override;
+  WorkPtr put(const at::Tensor& src, int dst_rank, int64_t target_offset_nelems, bool async_op, const OpOptions& o) override;
+  WorkPtr signal(int dst_rank, bool async_op, const OpOptions& o) override;
+  WorkPtr wait_signal(int peer_rank, bool async_op, const OpOptions& o) override;
+  at::Tensor map_remote_tensor(int rank) override;
+  WindowAttr get_attr(int peer_rank) override;
+  uintptr_t get_device_window(int signal_count, int counter_count, int barrier_count) override;
+  uintptr_t register_local_buffer(const at::Tensor& t) override;
+  void deregister_local_buffer(uintptr_t handle) override;
+
+ private:
+  void build_device_window(int signal_count, int counter_count, int barrier_count);
+  std::shared_ptr<CudaBackend> owner_;
+  std::shared_ptr<SymmSegment> data_seg_;
+  std::shared_ptr<SymmSegment> ctrl_seg_;   // signals + barrier flags
+  DeviceWindow host_copy_{};
+  DeviceWindow* dev_window_ = nullptr;
+  uint64_t* local_state_ = nullptr;         // counters, barrier epochs, wait expectations
+  std::vector<std::pair<RegisteredBuffer*, at::Tensor>> local_buffers_;
+  bool registered_ = false;
+};
+
+void register_cuda_backends();
+
+} // namespace b200c

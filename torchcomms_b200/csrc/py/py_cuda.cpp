@@ -1,5 +1,308 @@
-// placeholder until the CUDA backend lands
+// Python bindings of the CUDA backend's extra operations and of a
+// single-GPU emulation world used by kernel tests.
+//
+// Parity: comms/torchcomms/ncclx/TorchCommNCCLXPy.cpp:22-204 (device_alltoallv_single,
+// reduce_scatter_quantized, comm_dump, set_config, get_nccl_comm_ptr).
 #include "py_common.hpp"
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "../backends/cuda_backend.hpp"
+
 namespace b200c {
-void bind_cuda_backend(py::module_&) {}
+
+namespace {
+
+using OptHints = std::optional<Hints>;
+using OptMillis = std::optional<Millis>;
+
+// N virtual ranks on one GPU: N private "heaps", one CommDev per rank whose
+// peer table points at all of them. Kernels run through the emulation launch
+// path (one cooperative launch, blockIdx.y = rank), which executes the same
+// device code as a real multi-GPU launch.
+class EmuWorld {
+ public:
+  EmuWorld(int nranks, size_t staging_bytes, double wait_ms) : n_(nranks) {
+    TORCH_CHECK(nranks >= 1 && nranks <= kMaxRanks, "emulation supports 1..", kMaxRanks, " ranks");
+    lay_.bulk_off = 0;
+    lay_.bulk_bytes = (staging_bytes + 4095) / 4096 * 4096;
+    lay_.small_off = lay_.bulk_bytes;
+    const size_t meta = static_cast<size_t>(kMaxBlocks) * kMaxRanks * kMaxRanks * sizeof(uint64_t);
+    lay_.small_bytes = (2 * static_cast<size_t>(kSmallBlocks) * kSmallPiece + meta + 4095) / 4096 * 4096;
+    flags_off_ = lay_.small_off + lay_.small_bytes;
+    const size_t flag_bytes = static_cast<size_t>(kFlagSets) * kMaxBlocks * kMaxRanks * sizeof(uint32_t);
+    total_ = flags_off_ + (flag_bytes + 4095) / 4096 * 4096;
+    heaps_.resize(n_);
+    epochs_.resize(n_);
+    for (int r = 0; r < n_; ++r) {
+      B200C_CUDA_CHECK(cudaMalloc(&heaps_[r], total_));
+      B200C_CUDA_CHECK(cudaMemset(heaps_[r], 0, total_));
+      B200C_CUDA_CHECK(cudaMalloc(&epochs_[r], kFlagSets * kMaxBlocks * sizeof(uint32_t)));
+      B200C_CUDA_CHECK(cudaMemset(epochs_[r], 0, kFlagSets * kMaxBlocks * sizeof(uint32_t)));
+    }
+    B200C_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped));
+    std::memset(status_host_, 0, 64);
+    B200C_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0));
+    comms_.resize(n_);
+    for (int r = 0; r < n_; ++r) {
+      CommDev& c = comms_[r];
+      std::memset(&c, 0, sizeof(c));
+      c.rank = r;
+      c.nranks = n_;
+      for (int p = 0; p < n_; ++p) {
+        c.heap[p] = static_cast<char*>(heaps_[p]);
+        c.flags[p] = reinterpret_cast<uint32_t*>(static_cast<char*>(heaps_[p]) + flags_off_);
+      }
+      c.epochs = static_cast<uint32_t*>(epochs_[r]);
+      c.status = status_dev_;
+      c.timeout_ns = static_cast<unsigned long long>(wait_ms * 1.0e6);
+      c.heap_bytes = total_;
+    }
+    B200C_CUDA_CHECK(cudaDeviceSynchronize());
+  }
+  ~EmuWorld() {
+    for (void* p : heaps_) cudaFree(p);
+    for (void* p : epochs_) cudaFree(p);
+    if (status_host_) cudaFreeHost(status_host_);
+  }
+
+  std::vector<uint32_t> status() const {
+    return std::vector<uint32_t>(status_host_, status_host_ + 5);
+  }
+  void clear_status() { std::memset(status_host_, 0, 64); }
+
+  static DType dtype_of(const at::Tensor& t) {
+    switch (t.scalar_type()) {
+      case at::kFloat: return DType::F32;
+      case at::kHalf: return DType::F16;
+      case at::kBFloat16: return DType::BF16;
+      default: TORCH_CHECK(false, "unsupported dtype ", t.scalar_type());
+    }
+  }
+  void check(const std::vector<at::Tensor>& v) const {
+    TORCH_CHECK(static_cast<int>(v.size()) == n_, "need one tensor per virtual rank");
+    for (auto& t : v) TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "tensors must be contiguous CUDA tensors");
+  }
+  LaunchShape shape(int blocks, size_t chunk) const {
+    LaunchShape s;
+    s.blocks = blocks;
+    s.threads = 256;
+    s.chunk_bytes = chunk;
+    return s;
+  }
+  cudaStream_t stream() const { return at::cuda::getCurrentCUDAStream().stream(); }
+
+  void all_reduce(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, int red, double scale, int algo,
+                  int blocks, size_t chunk) {
+    check(ins);
+    check(outs);
+    std::vector<const void*> ip(n_);
+    std::vector<void*> op(n_);
+    for (int r = 0; r < n_; ++r) {
+      ip[r] = ins[r].data_ptr();
+      op[r] = outs[r].data_ptr();
+    }
+    B200C_CUDA_CHECK(launch_all_reduce(comms_.data(), lay_, n_, ip.data(), op.data(), ins[0].numel(), dtype_of(ins[0]),
+                                       static_cast<RedKind>(red), static_cast<float>(scale), algo, false,
+                                       shape(blocks, chunk), stream()));
+  }
+  void reduce_scatter(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, const std::string& wire, int red,
+                      double scale, int blocks, size_t chunk) {
+    check(ins);
+    check(outs);
+    std::vector<const void*> ip(n_);
+    std::vector<void*> op(n_);
+    for (int r = 0; r < n_; ++r) {
+      ip[r] = ins[r].data_ptr();
+      op[r] = outs[r].data_ptr();
+    }
+    const DType din = dtype_of(ins[0]), dout = dtype_of(outs[0]);
+    const DType dwire = wire == "bf16" ? DType::BF16 : wire == "f16" ? DType::F16 : wire == "f32" ? DType::F32 : din;
+    B200C_CUDA_CHECK(launch_reduce_scatter(comms_.data(), lay_, n_, ip.data(), op.data(), outs[0].numel(), din, dwire, dout,
+                                           static_cast<RedKind>(red), static_cast<float>(scale), false,
+                                           shape(blocks, chunk), stream()));
+  }
+  void all_gather(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, bool cast, int blocks, size_t chunk) {
+    check(ins);
+    check(outs);
+    std::vector<const void*> ip(n_);
+    std::vector<void*> op(n_);
+    for (int r = 0; r < n_; ++r) {
+      ip[r] = ins[r].data_ptr();
+      op[r] = outs[r].data_ptr();
+    }
+    B200C_CUDA_CHECK(launch_all_gather(comms_.data(), lay_, n_, ip.data(), op.data(), ins[0].nbytes(), cast, false,
+                                       shape(blocks, chunk), stream()));
+  }
+  // splits[r][p]: bytes rank r sends to rank p (blocks packed back to back on both sides).
+  void all_to_all(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, std::vector<std::vector<int64_t>> splits,
+                  int blocks, size_t chunk) {
+    check(ins);
+    check(outs);
+    std::vector<const void*> ip(n_);
+    std::vector<void*> op(n_);
+    std::vector<size_t> so(n_ * n_), sl(n_ * n_), ro(n_ * n_), rl(n_ * n_);
+    size_t mx = 0;
+    for (int r = 0; r < n_; ++r) {
+      ip[r] = ins[r].data_ptr();
+      op[r] = outs[r].data_ptr();
+      size_t s = 0, d = 0;
+      for (int p = 0; p < n_; ++p) {
+        so[r * n_ + p] = s;
+        sl[r * n_ + p] = static_cast<size_t>(splits[r][p]);
+        s += sl[r * n_ + p];
+        ro[r * n_ + p] = d;
+        rl[r * n_ + p] = static_cast<size_t>(splits[p][r]);
+        d += rl[r * n_ + p];
+        mx = std::max(mx, sl[r * n_ + p]);
+      }
+    }
+    B200C_CUDA_CHECK(launch_all_to_all(comms_.data(), lay_, n_, ip.data(), op.data(), so.data(), sl.data(), ro.data(),
+                                       rl.data(), mx, shape(blocks, chunk), stream()));
+  }
+  void all_to_all_device_splits(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs,
+                                std::vector<at::Tensor> counts, size_t elem_bytes, int blocks, size_t chunk) {
+    check(ins);
+    check(outs);
+    check(counts);
+    std::vector<const void*> ip(n_);
+    std::vector<void*> op(n_);
+    std::vector<const long long*> cp(n_);
+    for (int r = 0; r < n_; ++r) {
+      ip[r] = ins[r].data_ptr();
+      op[r] = outs[r].data_ptr();
+      TORCH_CHECK(counts[r].scalar_type() == at::kLong && counts[r].numel() == n_, "counts: int64[nranks] per rank");
+      cp[r] = reinterpret_cast<const long long*>(counts[r].data_ptr<int64_t>());
+    }
+    B200C_CUDA_CHECK(launch_all_to_all_device_splits(comms_.data(), lay_, n_, ip.data(), op.data(), cp.data(), elem_bytes,
+                                                     shape(blocks, chunk), stream()));
+  }
+  void broadcast(std::vector<at::Tensor> bufs, int root, int blocks, size_t chunk) {
+    check(bufs);
+    std::vector<void*> bp(n_);
+    for (int r = 0; r < n_; ++r) bp[r] = bufs[r].data_ptr();
+    B200C_CUDA_CHECK(launch_broadcast(comms_.data(), lay_, n_, bp.data(), bufs[0].nbytes(), root, false,
+                                      shape(blocks, chunk), stream()));
+  }
+  void barrier() { B200C_CUDA_CHECK(launch_barrier(comms_.data(), n_, stream())); }
+  // Runs the kernel whose wait can never be satisfied; returns the status words.
+  std::vector<uint32_t> wait_unset_flag() {
+    B200C_CUDA_CHECK(launch_wait_unset_flag(comms_.data(), n_, stream()));
+    B200C_CUDA_CHECK(cudaStreamSynchronize(stream()));
+    return status();
+  }
+
+  // DeviceWindow self-test: ring put + signal + barrier through the device API.
+  std::vector<at::Tensor> window_ring(std::vector<at::Tensor> srcs, std::vector<at::Tensor> dsts) {
+    check(srcs);
+    check(dsts);
+    const size_t bytes = srcs[0].nbytes();
+    const int sigs = 2;
+    std::vector<void*> ctrl(n_), local(n_);
+    const size_t sig_bytes = static_cast<size_t>(sigs) * n_ * 8, bar_bytes = static_cast<size_t>(n_) * 8;
+    for (int r = 0; r < n_; ++r) {
+      B200C_CUDA_CHECK(cudaMalloc(&ctrl[r], sig_bytes + bar_bytes));
+      B200C_CUDA_CHECK(cudaMemset(ctrl[r], 0, sig_bytes + bar_bytes));
+      B200C_CUDA_CHECK(cudaMalloc(&local[r], 64 * 8));
+      B200C_CUDA_CHECK(cudaMemset(local[r], 0, 64 * 8));
+    }
+    std::vector<DeviceWindow> wins(n_);
+    std::vector<RegisteredBuffer> regs(n_);
+    for (int r = 0; r < n_; ++r) {
+      DeviceWindow& w = wins[r];
+      std::memset(&w, 0, sizeof(w));
+      w.rank = r;
+      w.nranks = n_;
+      w.bytes = dsts[r].nbytes();
+      for (int p = 0; p < n_; ++p) {
+        w.data[p] = static_cast<char*>(dsts[p].data_ptr());
+        w.signals[p] = static_cast<uint64_t*>(ctrl[p]);
+        w.barrier_flags[p] = reinterpret_cast<uint64_t*>(static_cast<char*>(ctrl[p]) + sig_bytes);
+      }
+      w.signal_count = sigs;
+      w.counter_count = 1;
+      w.barrier_count = 1;
+      w.counters = static_cast<uint64_t*>(local[r]);
+      w.barrier_epochs = static_cast<uint64_t*>(local[r]) + 8;
+      w.status = status_dev_;
+      w.timeout_ns = comms_[0].timeout_ns;
+      regs[r] = RegisteredBuffer{static_cast<char*>(srcs[r].data_ptr()), static_cast<size_t>(srcs[r].nbytes())};
+    }
+    DeviceWindow* dwins = nullptr;
+    RegisteredBuffer* dregs = nullptr;
+    B200C_CUDA_CHECK(cudaMalloc(&dwins, sizeof(DeviceWindow) * n_));
+    B200C_CUDA_CHECK(cudaMalloc(&dregs, sizeof(RegisteredBuffer) * n_));
+    B200C_CUDA_CHECK(cudaMemcpy(dwins, wins.data(), sizeof(DeviceWindow) * n_, cudaMemcpyHostToDevice));
+    B200C_CUDA_CHECK(cudaMemcpy(dregs, regs.data(), sizeof(RegisteredBuffer) * n_, cudaMemcpyHostToDevice));
+    B200C_CUDA_CHECK(launch_window_selftest(dwins, n_, dregs, bytes, stream()));
+    B200C_CUDA_CHECK(cudaStreamSynchronize(stream()));
+    // Report each rank's put counter so the test can check it was bumped.
+    std::vector<at::Tensor> counters;
+    for (int r = 0; r < n_; ++r) {
+      at::Tensor c = at::empty({1}, at::TensorOptions().dtype(at::kLong).device(at::kCUDA));
+      B200C_CUDA_CHECK(cudaMemcpy(c.data_ptr(), local[r], 8, cudaMemcpyDeviceToDevice));
+      counters.push_back(c);
+    }
+    cudaFree(dwins);
+    cudaFree(dregs);
+    for (int r = 0; r < n_; ++r) {
+      cudaFree(ctrl[r]);
+      cudaFree(local[r]);
+    }
+    return counters;
+  }
+
+ private:
+  int n_;
+  HeapLayout lay_;
+  size_t flags_off_ = 0, total_ = 0;
+  std::vector<void*> heaps_, epochs_;
+  uint32_t* status_host_ = nullptr;
+  uint32_t* status_dev_ = nullptr;
+  std::vector<CommDev> comms_;
+};
+
+} // namespace
+
+void bind_cuda_backend(py::module_& m) {
+  register_cuda_backends();
+
+  py::class_<CudaBackend, Backend, std::shared_ptr<CudaBackend>>(m, "CudaBackend")
+      .def("device_alltoallv_single", [](CudaBackend& b, at::Tensor out, const at::Tensor& in, const at::Tensor& os,
+                                         const at::Tensor& is, bool a, OptHints h, OptMillis to) {
+        return b.device_alltoallv_single(out, in, os, is, a, make_op_options(h, to));
+      }, py::arg("output"), py::arg("input"), py::arg("output_split_sizes"), py::arg("input_split_sizes"),
+         py::arg("async_op"), py::arg("hints") = py::none(), py::arg("timeout") = py::none(),
+         py::call_guard<py::gil_scoped_release>())
+      .def("reduce_scatter_quantized", [](CudaBackend& b, at::Tensor out, const at::Tensor& in, const ReduceOp& op,
+                                          int64_t seed, bool a, OptHints h, OptMillis to) {
+        return b.reduce_scatter_quantized(out, in, op, seed, a, make_op_options(h, to));
+      }, py::arg("output"), py::arg("input"), py::arg("op"), py::arg("seed") = 0, py::arg("async_op") = false,
+         py::arg("hints") = py::none(), py::arg("timeout") = py::none(), py::call_guard<py::gil_scoped_release>())
+      .def("comm_dump", &CudaBackend::comm_dump)
+      .def("set_config", &CudaBackend::set_config)
+      .def("get_nccl_comm_ptr", &CudaBackend::get_nccl_comm_ptr)
+      .def("internal_stream", [](CudaBackend& b) { return reinterpret_cast<uintptr_t>(b.internal_stream()); })
+      .def("has_multicast", [](CudaBackend& b) { return b.comm_dev().mc_heap != nullptr; });
+
+  py::class_<EmuWorld>(m, "_EmuWorld")
+      .def(py::init<int, size_t, double>(), py::arg("nranks"), py::arg("staging_bytes") = 8u << 20,
+           py::arg("wait_ms") = 2000.0)
+      .def("all_reduce", &EmuWorld::all_reduce)
+      .def("reduce_scatter", &EmuWorld::reduce_scatter)
+      .def("all_gather", &EmuWorld::all_gather)
+      .def("all_to_all", &EmuWorld::all_to_all)
+      .def("all_to_all_device_splits", &EmuWorld::all_to_all_device_splits)
+      .def("broadcast", &EmuWorld::broadcast)
+      .def("barrier", &EmuWorld::barrier)
+      .def("wait_unset_flag", &EmuWorld::wait_unset_flag)
+      .def("window_ring", &EmuWorld::window_ring)
+      .def("status", &EmuWorld::status)
+      .def("clear_status", &EmuWorld::clear_status);
+
+  m.def("_symm_allocator_symbols", []() { return std::make_pair(std::string("b200c_symm_alloc"), std::string("b200c_symm_free")); });
+  m.def("_exportable_allocations", []() { return ExportableRegistry::get().live(); });
 }
+
+} // namespace b200c
