@@ -1463,7 +1463,13 @@ at::Tensor CudaWindow::map_remote_tensor(int rank) {
     return *tensor_;
   }
   auto keep = data_seg_;
-  return at::from_blob(data_seg_->peer_ptrs[rank], shape_, [keep](void*) {}, at::TensorOptions().dtype(dtype_).device(device_));
+  // The memory physically lives on the peer's GPU but is addressable from
+  // this device: name this device as the tensor's, without the ownership check.
+  return at::for_blob(data_seg_->peer_ptrs[rank], shape_)
+      .options(at::TensorOptions().dtype(dtype_).device(device_))
+      .target_device(device_)
+      .deleter([keep](void*) {})
+      .make_tensor();
 }
 
 WindowAttr CudaWindow::get_attr(int peer_rank) {

@@ -18,6 +18,8 @@
 // barrier-as-all-reduce of comms/torchcomms/ncclx/TorchCommNCCLX.cpp:1907-1944.
 #include "collectives.h"
 
+#include "launch_count.h"
+
 #include <algorithm>
 #include <type_traits>
 #include <vector>
@@ -180,6 +182,7 @@ cudaError_t launch_op(const CommDev* comms, int emu_ranks, const typename Op::Ar
   if (blocks < 1) blocks = 1;
   if (blocks > kMaxBlocks) blocks = kMaxBlocks;
   if (threads > 512) threads = 512;
+  note_kernel_launch();
   if (emu_ranks <= 0) {
     k_real<Op><<<blocks, threads, 0, stream>>>(comms[0], args[0]);
     return cudaGetLastError();

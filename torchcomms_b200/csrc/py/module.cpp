@@ -436,4 +436,5 @@ PYBIND11_MODULE(_comms, m) {
   b200c::bind_hooks(m);
   b200c::bind_c10d_wrapper(m);
   b200c::bind_cuda_backend(m);
+  b200c::bind_ops(m);
 }
