@@ -219,7 +219,8 @@ void CudaBackend::parse_tuning(const Hints& h) {
   t.watchdog_interval_ms = hint_or<int>(h, "garbage_collect_interval_ms", t.watchdog_interval_ms);
   t.max_event_pool = hint_or<size_t>(h, "max_event_pool_size", t.max_event_pool);
   t.max_blocks = std::max(1, std::min(t.max_blocks, kMaxBlocks));
-  t.threads = std::max(32, std::min(t.threads, 512));
+  t.threads = std::max(32, std::min(t.threads, 256));
+  t.steps_per_block = hint_or<int>(h, "steps_per_block", env_to_value<int>("B200COMMS_STEPS_PER_BLOCK", t.steps_per_block));
   t.staging_bytes = std::max<size_t>(t.staging_bytes, 1u << 20);
   tune_ = t;
 }
@@ -423,8 +424,8 @@ WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, st
   // Operations of one communicator share staging slots and flags: keep them
   // in issue order even across streams. (Inside a capture only dependencies
   // created inside the same capture are legal, and those are already there.)
-  if (have_last_ && last_stream_ != stream && !capturing) {
-    B200C_CUDA_CHECK(cuda_->streamWaitEvent(stream, last_end_));
+  if (last_work_ && last_stream_ != stream && !capturing) {
+    B200C_CUDA_CHECK(cuda_->streamWaitEvent(stream, last_work_->end_event()));
   }
 
   cudaEvent_t ev_start = nullptr, ev_end = nullptr;
@@ -470,12 +471,6 @@ WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, st
     B200C_CUDA_CHECK(launch_counter_increment(replay_counters + 1, stream));
   }
   B200C_CUDA_CHECK(cuda_->eventRecord(ev_end, stream));
-  if (!capturing) {
-    B200C_CUDA_CHECK(cuda_->eventRecord(last_end_, stream));
-    last_stream_ = stream;
-    have_last_ = true;
-  }
-
   auto self = std::static_pointer_cast<CudaBackend>(shared_from_this());
   if (!async_op) {
     keep_alive.clear();  // stream order already protects the tensors
@@ -483,6 +478,12 @@ WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, st
   auto work = c10::make_intrusive<CudaWork>(cuda_, ev_start, ev_end, !capturing, device_.index(), effective_timeout(o),
                                             std::move(keep_alive), self, capturing);
   ops_issued_++;
+  if (!capturing) {
+    // The end event of the latest operation doubles as the cross-stream
+    // ordering point for the next one (the work keeps the event alive).
+    last_work_ = work;
+    last_stream_ = stream;
+  }
   {
     std::lock_guard<std::mutex> g(wd_mu_);
     algo_counts_[what]++;
@@ -607,6 +608,7 @@ void CudaBackend::finalize() {
     }
   }
   stop_watchdog();
+  last_work_.reset();
   finalized_ = true;
   {
     std::lock_guard<std::mutex> g(wd_mu_);
@@ -674,10 +676,10 @@ LaunchShape CudaBackend::shape_for(size_t bytes, size_t slot_multiplier) const {
   LaunchShape s;
   s.threads = tune_.threads;
   const size_t max_chunk = std::max<size_t>(
-      256, std::min(tune_.max_chunk_bytes, layout_.bulk_bytes / (static_cast<size_t>(tune_.max_blocks) * slot_multiplier)));
+      256, std::min(tune_.max_chunk_bytes, layout_.bulk_bytes / (static_cast<size_t>(tune_.max_blocks) * slot_multiplier * kPipeSlots)));
   // Aim for every block to run several steps on large payloads so that copy
   // and link phases of different blocks overlap; small payloads use few blocks.
-  size_t chunk = round_up(std::max<size_t>(bytes / (static_cast<size_t>(tune_.max_blocks) * 4) + 1, tune_.min_chunk_bytes), 256);
+  size_t chunk = round_up(std::max<size_t>(bytes / (static_cast<size_t>(tune_.max_blocks) * std::max(1, tune_.steps_per_block)) + 1, tune_.min_chunk_bytes), 256);
   chunk = std::min(chunk, max_chunk / 256 * 256);
   chunk = std::max<size_t>(chunk, 256);
   const size_t steps = (bytes + chunk - 1) / chunk;
@@ -874,7 +876,7 @@ static WorkPtr exchange(CudaBackend* self, const char* what, at::Tensor in, at::
   shape.threads = self->tuning().threads;
   shape.blocks = std::min(32, self->tuning().max_blocks);
   shape.chunk_bytes = std::min<size_t>(self->tuning().max_chunk_bytes,
-                                       self->layout().bulk_bytes / (static_cast<size_t>(shape.blocks) * n)) / 256 * 256;
+                                       self->layout().bulk_bytes / (static_cast<size_t>(shape.blocks) * n * kPipeSlots)) / 256 * 256;
   return self->run(what, async_op, o, std::move(keep), [self, in, out, send, recv, shape, n, after](cudaStream_t s) {
     std::vector<size_t> so(n), sl(n), ro(n), rl(n);
     size_t mx = 0;
@@ -1101,7 +1103,7 @@ WorkPtr CudaBackend::device_alltoallv_single(at::Tensor& out, const at::Tensor& 
   LaunchShape shape;
   shape.threads = tune_.threads;
   shape.blocks = std::min(32, tune_.max_blocks);
-  shape.chunk_bytes = std::min<size_t>(tune_.max_chunk_bytes, layout_.bulk_bytes / (static_cast<size_t>(shape.blocks) * size_)) / 256 * 256;
+  shape.chunk_bytes = std::min<size_t>(tune_.max_chunk_bytes, layout_.bulk_bytes / (static_cast<size_t>(shape.blocks) * size_ * kPipeSlots)) / 256 * 256;
   at::Tensor i = in, ot = out, sp = in_splits;
   return run("device_alltoallv/kernel", async_op, o, {in, in_splits}, [this, i, ot, sp, row, shape](cudaStream_t s) {
     const void* ip = i.data_ptr();

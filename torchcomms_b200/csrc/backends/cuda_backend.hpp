@@ -77,9 +77,10 @@ enum class Algo : int { AUTO = 0, ONESHOT = 1, TWOSHOT = 2, STAGED = 3, NCCL = 4
 struct Tuning {
   size_t staging_bytes = 128ull << 20;     // bulk staging per rank
   size_t oneshot_max_bytes = 256 * 1024;   // all-reduce: one-shot up to here
-  int max_blocks = 128;                    // bulk kernels
-  int threads = 512;
-  size_t max_chunk_bytes = 1u << 20;       // bytes staged per block per step
+  int max_blocks = 444;                    // bulk kernels: 148 SMs x 3 resident blocks
+  int threads = 256;
+  size_t max_chunk_bytes = 256u << 10;     // bytes staged per block per step
+  int steps_per_block = 8;                 // large payloads: steps each block should run
   size_t min_chunk_bytes = 16 * 1024;
   bool use_multicast = true;
   bool use_nccl = true;                    // create the NCCL communicator at init
@@ -144,6 +145,13 @@ class CudaBackend final : public Backend {
   std::unordered_map<std::string, std::string> comm_dump() const;
   void set_config(const Hints& h) { set_hints(h); }
   uintptr_t get_nccl_comm_ptr() const { return reinterpret_cast<uintptr_t>(nccl_comm_); }
+  // Kernel phase trace (performance work): kMaxBlocks x kTraceSlots int64
+  // cycle stamps, rewritten by every traced kernel. An undefined tensor
+  // switches tracing off.
+  void set_trace_buffer(const at::Tensor& t) {
+    trace_ = t;
+    dev_.trace = t.defined() ? reinterpret_cast<long long*>(t.data_ptr<int64_t>()) : nullptr;
+  }
 
   // Shared with windows and fused ops.
   const CommDev& comm_dev() const { return dev_; }
@@ -207,7 +215,7 @@ class CudaBackend final : public Backend {
   cudaEvent_t dep_event_ = nullptr;
   cudaStream_t last_stream_ = nullptr;
   cudaEvent_t last_end_ = nullptr;
-  bool have_last_ = false;
+  c10::intrusive_ptr<CudaWork> last_work_;
 
   std::mutex pool_mu_;
   std::vector<cudaEvent_t> event_pool_;
@@ -236,6 +244,7 @@ class CudaBackend final : public Backend {
   std::vector<GraphEntry> graph_entries_;
   std::unordered_map<unsigned long long, size_t> graph_next_index_;
 
+  at::Tensor trace_;
   std::atomic<bool> aborted_{false};
   std::atomic<bool> failed_{false};
   std::string failure_text_;

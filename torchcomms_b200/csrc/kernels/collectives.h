@@ -28,8 +28,8 @@ struct HeapLayout {
   size_t user_bytes = 0;
 };
 
-constexpr size_t kSmallPiece = 16 * 1024;  // bytes of payload one block stages in latency mode
-constexpr int kSmallBlocks = 64;           // at most this many pieces per latency-mode call
+constexpr size_t kSmallPiece = 4 * 1024;   // bytes of payload one block stages in latency mode (one 16-byte vector per thread)
+constexpr int kSmallBlocks = 128;          // at most this many pieces per latency-mode call
 
 struct LaunchShape {
   int blocks = 1;

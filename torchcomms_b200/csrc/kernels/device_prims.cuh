@@ -20,14 +20,17 @@
 namespace b200c {
 
 constexpr int kMaxRanks = 8;        // one NVSwitch domain
-constexpr int kMaxBlocks = 320;     // flag rows per flag set
-constexpr int kFlagSets = 6;        // independent users of the flag region
-constexpr int kFlagSetBulk = 0;     // staged collectives, barriers enclose each step
-constexpr int kFlagSetSmall = 1;    // latency mode: one barrier per call, parity buffers
-constexpr int kFlagSetBarrier = 2;  // stand-alone barrier
-constexpr int kFlagSetWindow = 3;   // one-sided window signals
-constexpr int kFlagSetEp = 4;       // MoE dispatch / combine
-constexpr int kFlagSetTp = 5;       // tensor-parallel fused GEMMs
+constexpr int kMaxBlocks = 640;     // flag rows per flag set (148 SMs x up to 4 resident blocks)
+constexpr int kFlagSets = 8;        // independent users of the flag region
+constexpr int kFlagSetReady = 0;    // pipelined collectives: "chunk k is staged"
+constexpr int kFlagSetDone = 1;     // pipelined collectives: "chunk k is consumed"
+constexpr int kFlagSetSmall = 2;    // latency mode: one barrier per call, parity buffers
+constexpr int kFlagSetBarrier = 3;  // stand-alone barrier
+constexpr int kFlagSetMeta = 4;     // all-to-all count exchange
+constexpr int kFlagSetWindow = 5;   // one-sided window signals
+constexpr int kFlagSetEp = 6;       // MoE dispatch / combine
+constexpr int kFlagSetTp = 7;       // tensor-parallel fused GEMMs
+constexpr int kPipeSlots = 3;       // staging slots per block in the pipelined collectives
 
 // Bits of the status word a kernel may set (host-visible, mapped pinned memory).
 constexpr uint32_t kStatusTimeout = 1u;   // a bounded wait ran out
@@ -53,7 +56,12 @@ struct CommDev {
   volatile uint32_t* status;
   unsigned long long timeout_ns;  // budget of one wait
   size_t heap_bytes;              // size of the staging region
+  // Optional phase trace: kTraceSlots cycle-counter stamps per block, written
+  // by thread 0 (nullptr = off). For performance work, see trace_mark().
+  long long* trace;
 };
+
+constexpr int kTraceSlots = 16;
 
 // Everything below is device code; host translation units only need the
 // descriptor above.
@@ -181,7 +189,7 @@ __device__ __forceinline__ bool comm_is_dead(const CommDev& c) {
 // returns false then, and the caller carries on to its normal exit.
 __device__ __forceinline__ bool wait_flag_reached(const CommDev& c, const uint32_t* addr, uint32_t want,
                                                   int peer, uint32_t phase) {
-  unsigned long long start = 0;
+  unsigned long long start = 0, next_status = 0;
   uint32_t spins = 0;
   while (true) {
     // Relaxed polling; one acquire fence once the value is there.
@@ -190,45 +198,53 @@ __device__ __forceinline__ bool wait_flag_reached(const CommDev& c, const uint32
       fence_acq_rel_sys();
       return true;
     }
-    if (++spins >= 256u) {
+    if (++spins >= 64u) {
       spins = 0;
-      if (comm_is_dead(c)) {
-        return false;
-      }
       const unsigned long long now = globaltimer_ns();
       if (start == 0) {
         start = now;
-      } else if (now - start > c.timeout_ns) {
-        report_timeout(c, peer, phase);
-        return false;
+        next_status = now + 200000ull;
+      } else if (now >= next_status) {
+        // The status word lives in host memory: reading it crosses PCIe, so
+        // look at it rarely (every 200 us of waiting), never in the hot path.
+        next_status = now + 200000ull;
+        if (comm_is_dead(c)) {
+          return false;
+        }
+        if (now - start > c.timeout_ns) {
+          report_timeout(c, peer, phase);
+          return false;
+        }
       }
-      __nanosleep(64);
     }
   }
 }
 
 __device__ __forceinline__ bool wait_u64_reached(const CommDev& c, const uint64_t* addr, uint64_t want,
                                                  int peer, uint32_t phase) {
-  unsigned long long start = 0;
+  unsigned long long start = 0, next_status = 0;
   uint32_t spins = 0;
   while (true) {
     const uint64_t v = ld_acquire_sys_u64(addr);
     if (static_cast<int64_t>(v - want) >= 0) {
       return true;
     }
-    if (++spins >= 256u) {
+    if (++spins >= 64u) {
       spins = 0;
-      if (comm_is_dead(c)) {
-        return false;
-      }
       const unsigned long long now = globaltimer_ns();
       if (start == 0) {
         start = now;
-      } else if (now - start > c.timeout_ns) {
-        report_timeout(c, peer, phase);
-        return false;
+        next_status = now + 200000ull;
+      } else if (now >= next_status) {
+        next_status = now + 200000ull;
+        if (comm_is_dead(c)) {
+          return false;
+        }
+        if (now - start > c.timeout_ns) {
+          report_timeout(c, peer, phase);
+          return false;
+        }
       }
-      __nanosleep(64);
     }
   }
 }
@@ -268,17 +284,66 @@ __device__ __forceinline__ bool block_barrier(const CommDev& c, int set, BlockEp
   }
   __syncthreads();
   if (threadIdx.x < c.nranks) {
+    // Release: a system fence (one warp instruction for all signalling lanes)
+    // makes the whole block's earlier writes visible system-wide before the
+    // relaxed flag store that follows it; each lane then polls one peer.
     const int peer = threadIdx.x;
-    // Release: fence makes the whole block's earlier writes visible system-wide
-    // before the flag lands in the peer's memory.
     __threadfence_system();
-    st_release_sys(flag_slot(c, peer, set, blockIdx.x, c.rank), ep.value);
+    st_relaxed_sys(flag_slot(c, peer, set, blockIdx.x, c.rank), ep.value);
     if (!wait_flag_reached(c, flag_slot(c, c.rank, set, blockIdx.x, peer), ep.value, peer, phase)) {
       s_ok = 0;
     }
   }
   __syncthreads();
   return s_ok != 0;
+}
+
+// Split-phase signalling for pipelined kernels: a block posts monotonically
+// increasing step counts ("ready", "done") to its peers and carries on; the
+// matching waits happen one pipeline stage later, when the flags have long
+// arrived, so no step ends in a blocking two-sided barrier.
+
+// Waits until every rank's flag of this block in `set` has reached `want`.
+// All threads of the block must call it.
+__device__ __forceinline__ bool wait_all_peers(const CommDev& c, int set, uint32_t want, uint32_t phase) {
+  __shared__ int s_ok_wait;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s_ok_wait = 1;
+  }
+  __syncthreads();
+  if (threadIdx.x < c.nranks) {
+    const int peer = threadIdx.x;
+    if (!wait_flag_reached(c, flag_slot(c, c.rank, set, blockIdx.x, peer), want, peer, phase)) {
+      s_ok_wait = 0;
+    }
+  }
+  __syncthreads();
+  return s_ok_wait != 0;
+}
+
+// Publishes step counts to every rank once all of this block's earlier
+// writes (local and remote) are visible system-wide. All threads call it.
+__device__ __forceinline__ void post_flags(const CommDev& c, bool post_ready, uint32_t ready_val, bool post_done,
+                                           uint32_t done_val) {
+  __syncthreads();
+  if (threadIdx.x < c.nranks && (post_ready || post_done)) {
+    const int peer = threadIdx.x;
+    __threadfence_system();
+    if (post_ready) {
+      st_relaxed_sys(flag_slot(c, peer, kFlagSetReady, blockIdx.x, c.rank), ready_val);
+    }
+    if (post_done) {
+      st_relaxed_sys(flag_slot(c, peer, kFlagSetDone, blockIdx.x, c.rank), done_val);
+    }
+  }
+}
+
+// Stamps the SM cycle counter into slot `slot` of this block's trace row.
+__device__ __forceinline__ void trace_mark(const CommDev& c, int slot) {
+  if (c.trace != nullptr && threadIdx.x == 0 && slot < kTraceSlots) {
+    c.trace[static_cast<size_t>(blockIdx.x) * kTraceSlots + slot] = clock64();
+  }
 }
 
 // ------------------------------------------------------------- copies ------

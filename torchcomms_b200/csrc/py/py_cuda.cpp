@@ -283,6 +283,12 @@ void bind_cuda_backend(py::module_& m) {
       .def("comm_dump", &CudaBackend::comm_dump)
       .def("set_config", &CudaBackend::set_config)
       .def("get_nccl_comm_ptr", &CudaBackend::get_nccl_comm_ptr)
+      .def("enable_trace", [](CudaBackend& b) {
+        at::Tensor t = at::zeros({kMaxBlocks, kTraceSlots}, at::TensorOptions().dtype(at::kLong).device(b.device()));
+        b.set_trace_buffer(t);
+        return t;
+      })
+      .def("disable_trace", [](CudaBackend& b) { b.set_trace_buffer(at::Tensor()); })
       .def("internal_stream", [](CudaBackend& b) { return reinterpret_cast<uintptr_t>(b.internal_stream()); })
       .def("has_multicast", [](CudaBackend& b) { return b.comm_dev().mc_heap != nullptr; });
 
