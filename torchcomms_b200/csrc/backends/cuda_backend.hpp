@@ -158,6 +158,7 @@ class CudaBackend final : public Backend {
   const HeapLayout& layout() const { return layout_; }
   const Tuning& tuning() const { return tune_; }
   SymmMemory& symm() { return *symm_; }
+  bool symm_alive() const { return symm_ != nullptr && !finalized_; }
   std::shared_ptr<CudaApi> cuda_api() const { return cuda_; }
   cudaStream_t internal_stream() const { return internal_stream_; }
 

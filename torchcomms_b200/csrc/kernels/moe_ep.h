@@ -1,0 +1,56 @@
+// MoE expert-parallel dispatch / combine inside one NVSwitch domain.
+//
+// dispatch: every token goes once to each rank that hosts at least one of its
+// top-k experts. ONE kernel counts, exchanges the counts with the peers
+// (no host synchronisation), quantises each row to fp8 e4m3 with one fp32
+// scale per 128 elements while it is in registers, and stores the row, its
+// scales, source index and re-based top-k ids / weights straight into the
+// destination rank's receive buffer over NVLink, packed by source rank.
+// combine: the source rank pulls its tokens' expert outputs back from the
+// peers and sums them (optionally weighted, optionally plus a bias) in fp32.
+//
+// Replaces, in the reference: comms/prims/collectives/link_ep (layout kernel
+// cpp/intranode/kernels/Layout.cu:39-218, notify Notify.cu:97-440, dispatch
+// Dispatch.cu:40-538, combine Combine.cu:24-466), which moves pre-quantised
+// rows through ring FIFOs and learns the receive count through a CPU spin.
+#pragma once
+
+#include "device_prims.cuh"
+
+namespace b200c {
+
+struct EpDev {
+  int rank, nranks;
+  int num_experts, experts_per_rank, topk, hidden;
+  int max_tokens;       // capacity: tokens per rank per call
+  int fp8;              // 1: e4m3 rows + 1x128 fp32 scales; 0: bf16 rows
+  // Receive side of every rank (symmetric, peer-mapped). Capacity nranks*max_tokens rows.
+  char* recv_x[kMaxRanks];
+  float* recv_scales[kMaxRanks];       // [rows, hidden/128]
+  int* recv_src[kMaxRanks];            // [rows] src_rank * max_tokens + token
+  int* recv_topk_idx[kMaxRanks];       // [rows, topk] local expert id or -1
+  float* recv_topk_w[kMaxRanks];       // [rows, topk]
+  long long* count_matrix[kMaxRanks];  // [nranks, nranks]: [s][d] tokens s sends to d
+  char* combine_x[kMaxRanks];          // [rows, hidden] bf16: expert outputs, read by the sources
+  // Local scratch.
+  int* cnt;          // [nranks]
+  int* cursor;       // [nranks]
+  long long* base;   // [nranks] first slot of this rank's rows in each destination
+  int* recv_info;    // [1 + nranks]: total rows received, then rows per source
+  int* send_slot;    // [max_tokens, nranks] slot in the destination, -1 = not sent (the combine handle)
+};
+
+// All tensors are device pointers of the calling rank. `emu_ranks > 0`: arrays
+// of per-virtual-rank descriptors / pointers, one cooperative launch.
+cudaError_t launch_ep_dispatch(const CommDev* comms, const EpDev* eps, int emu_ranks, const void* const* x,
+                               const int* const* topk_idx, const float* const* topk_w, int num_tokens,
+                               cudaStream_t stream);
+// out[t] = bias[t] + sum over destinations d of w[t, d] * combine_x_d[slot(t, d)]   (w, bias optional)
+cudaError_t launch_ep_combine(const CommDev* comms, const EpDev* eps, int emu_ranks, void* const* out,
+                              const float* const* weights, const void* const* bias, int num_tokens,
+                              cudaStream_t stream);
+// Layout only: tokens per rank, tokens per expert, token-in-rank mask (int32 outputs).
+cudaError_t launch_ep_layout(const int* topk_idx, int num_tokens, int topk, int num_experts, int nranks,
+                             int* tokens_per_rank, int* tokens_per_expert, int* is_token_in_rank, cudaStream_t stream);
+
+} // namespace b200c

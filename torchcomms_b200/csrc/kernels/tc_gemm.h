@@ -1,0 +1,56 @@
+// tcgen05 / TMEM GEMMs (sm_100a) and their fusion with tensor-parallel
+// collectives. Raw-pointer launch interface.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "device_prims.cuh"
+
+namespace b200c {
+
+// C[M, N] (bf16) = A[M, K] (bf16, row-major) x B[N, K]^T (bf16, row-major),
+// fp32 accumulation in tensor memory. K % 64 == 0, N % 128 == 0.
+// `status` (device or mapped host memory, may be null) receives a non-zero
+// word if a bounded wait inside the kernel ran out.
+cudaError_t launch_gemm_bf16_nt(const void* a, const void* b, void* c, int m, int n, int k, uint32_t* status,
+                                cudaStream_t stream);
+
+// Column-parallel layer fused with the all-gather of its input.
+// x_shards[r] is rank r's [m_local, k] bf16 activation shard in symmetric
+// memory (x_shards[rank] local); `x_full` is local scratch [nranks*m_local, k]
+// that the kernel fills from the peers while the tensor cores already work on
+// the rows that have arrived; w is this rank's [n, k] weight shard;
+// y [nranks*m_local, n]. `ready` is local scratch of nranks*m_local/128 + 2
+// uint32 counters (zeroed by the kernel's previous run or by the caller
+// before the first).
+struct AgGemmArgs {
+  const void* x_shards[kMaxRanks];
+  void* x_full;
+  const void* w;
+  void* y;
+  int m_local, n, k;
+  uint32_t* ready;
+};
+cudaError_t launch_allgather_gemm(const CommDev& comm, const AgGemmArgs& args, cudaStream_t stream);
+
+// Row-parallel layer fused with the reduce-scatter of its output.
+// h [m, k_local] bf16 local, w [n, k_local] local; every rank computes the
+// partial product for all m rows; rows [r*m/nranks, (r+1)*m/nranks) belong to
+// rank r. Partial tiles are stored straight into the owner's `partials`
+// staging (symmetric; partials[r] = owner r's buffer of
+// [nranks, m/nranks, n] bf16, slot index = source rank); the owner sums the
+// nranks slots in fp32 into `out` [m/nranks, n] bf16 as they arrive.
+// `arrived` (symmetric, arrived[r] on owner r): one uint32 per (tile, source).
+struct GemmRsArgs {
+  const void* h;
+  const void* w;
+  void* partials[kMaxRanks];
+  uint32_t* arrived[kMaxRanks];
+  void* out;
+  int m, n, k_local;
+  uint32_t epoch;   // value written to `arrived` flags by this call (monotonic per buffer)
+};
+cudaError_t launch_gemm_reduce_scatter(const CommDev& comm, const GemmRsArgs& args, cudaStream_t stream);
+
+} // namespace b200c

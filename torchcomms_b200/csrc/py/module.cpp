@@ -437,4 +437,5 @@ PYBIND11_MODULE(_comms, m) {
   b200c::bind_c10d_wrapper(m);
   b200c::bind_cuda_backend(m);
   b200c::bind_ops(m);
+  b200c::bind_ep(m);
 }
