@@ -5,7 +5,8 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 256, 256), (256, 512, 1024), (300, 384, 512), (1024, 7168, 2048)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 256, 256), (256, 512, 1024), (300, 384, 512), (300, 264, 200), (1024, 7168, 2048),
+                                   (4096, 4096, 4096)])
 def test_gemm_bf16_nt(m, n, k):
     from torchcomms_b200 import _comms
 

@@ -1,11 +1,13 @@
 // tcgen05 / TMEM GEMM kernels (sm_100a). See tc_gemm.h.
 //
-// Roles inside a CTA of 192 threads (+ optional copy warps in fused kernels):
+// One persistent kernel, three modes (plain, all-gather -> GEMM, GEMM ->
+// reduce-scatter). Roles inside a CTA:
 //   warp 0, one lane : TMA producer - fills a ring of shared-memory stages
 //   warp 1           : allocates tensor memory; one lane issues tcgen05.mma
-//   warps 2..5       : epilogue - tcgen05.ld the fp32 accumulator, convert,
-//                      store (each warp owns the 32 TMEM lanes of its
-//                      warp-id % 4 quadrant)
+//   warps 2..5       : epilogue - tcgen05.ld the fp32 accumulator, convert to
+//                      bf16 into a swizzled staging tile, TMA-store it (each
+//                      warp owns the 32 TMEM lanes of its warp-id % 4 quadrant)
+//   warps 6..9       : all-gather mode only - copy the peers' rows
 #include "tc_gemm.h"
 
 #include <algorithm>
@@ -61,16 +63,6 @@ struct TileCfg {
   static constexpr int kABytes = kBlockM * kBlockK * 2;
   static constexpr int kBBytes = BN * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr uint32_t kTmemCols = BN;  // power of two >= 32
-};
-
-struct Barriers {
-  uint64_t full[8];
-  uint64_t empty[8];
-  uint64_t acc_full;
-  uint32_t tmem_base;
-  uint32_t failed;
 };
 
 __device__ __forceinline__ uint32_t pack_bf16(uint32_t a, uint32_t b) {
@@ -78,151 +70,544 @@ __device__ __forceinline__ uint32_t pack_bf16(uint32_t a, uint32_t b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// One output tile: mainloop over K with the producer / MMA roles, accumulator
-// left in tensor memory. `k_iters` blocks of 64. Called by warps 0 and 1 only.
-template <int BN>
-__device__ __forceinline__ void tile_mainloop(const CUtensorMap* map_a, const CUtensorMap* map_b, char* stages,
-                                              Barriers* bars, int m0, int n0, int k_iters, uint32_t& it,
-                                              uint32_t tmem_acc, int warp, int lane) {
-  using Cfg = TileCfg<BN>;
-  constexpr uint32_t idesc = make_idesc_bf16(kBlockM, BN);
-  if (warp == 0 && lane == 0) {
-    for (int kb = 0; kb < k_iters; ++kb) {
-      const uint32_t i = it + kb;
-      const int s = i % Cfg::kStages;
-      const uint32_t ph = (i / Cfg::kStages) & 1u;
-      if (!mbar_wait(&bars->empty[s], ph ^ 1u)) {
-        bars->failed = 1;
-        break;
-      }
-      mbar_expect_tx(&bars->full[s], Cfg::kStageBytes);
-      char* sa = stages + s * Cfg::kStageBytes;
-      tma_load_2d(sa, map_a, &bars->full[s], kb * kBlockK, m0);
-      tma_load_2d(sa + Cfg::kABytes, map_b, &bars->full[s], kb * kBlockK, n0);
-    }
-  } else if (warp == 1 && lane == 0) {
-    for (int kb = 0; kb < k_iters; ++kb) {
-      const uint32_t i = it + kb;
-      const int s = i % Cfg::kStages;
-      const uint32_t ph = (i / Cfg::kStages) & 1u;
-      if (!mbar_wait(&bars->full[s], ph)) {
-        bars->failed = 1;
-        break;
-      }
-      tc_fence_after_sync();
-      const uint32_t sa = smem_u32(stages + s * Cfg::kStageBytes);
-      const uint64_t da = make_smem_desc(sa);
-      const uint64_t db = make_smem_desc(sa + Cfg::kABytes);
-#pragma unroll
-      for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-        // 16 bf16 = 32 bytes further along K inside the swizzled row
-        umma_bf16(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
-      }
-      umma_commit(&bars->empty[s]);  // stage reusable once these MMAs have read it
-    }
-    umma_commit(&bars->acc_full);    // accumulator complete
-  }
-  it += static_cast<uint32_t>(k_iters);
+// ------------------------------------------------- persistent kernel -------
+//
+// One CTA per SM; tiles are handed out round-robin in an order that (a) keeps
+// a group of `gm` m-tiles resident in L2 while the wave sweeps over n, and
+// (b) follows the data's arrival (all-gather) or departure (reduce-scatter).
+// Control words of the fused modes (local global memory, zeroed once):
+//   ctrl[0] call epoch, ctrl[1] finished-CTA ticket, ctrl[2] start flag,
+//   ctrl[4 + i] arrival counter of m-tile ordinal i (all-gather mode).
+
+constexpr int kTpBN = 256;
+constexpr int kCopyThreads = 128;
+constexpr int kGemmThreads = 192;
+constexpr int kCtrlTiles = 4;
+constexpr int kOutChunkCols = 64;                                  // one 128-byte swizzle row of bf16
+constexpr int kOutChunkBytes = kBlockM * kOutChunkCols * 2;        // 16 KB
+constexpr int kTpSmemBytes = TileCfg<kTpBN>::kStages * TileCfg<kTpBN>::kStageBytes + 2 * kOutChunkBytes + 1024 + 256;
+
+enum class TpMode : int { PLAIN = 0, AG_GEMM = 1, GEMM_RS = 2 };
+
+template <TpMode MODE>
+constexpr int tp_threads() {
+  return MODE == TpMode::AG_GEMM ? kGemmThreads + kCopyThreads : kGemmThreads;
 }
 
-// ------------------------------------------------------------ plain GEMM ---
+struct TpBarriers {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t failed;
+  uint32_t epoch;
+  uint32_t is_last;
+  int reduce_ok;
+};
 
-template <int BN>
-__global__ void __launch_bounds__(192, 1) k_gemm_bf16_nt(const __grid_constant__ CUtensorMap map_a,
-                                                          const __grid_constant__ CUtensorMap map_b,
-                                                          __nv_bfloat16* __restrict__ c, int m, int n, int k,
-                                                          uint32_t* status) {
-  using Cfg = TileCfg<BN>;
+struct TpMaps {
+  CUtensorMap a_local;          // A rows that are in this rank's own buffer
+  CUtensorMap a_full;           // A rows in the gathered buffer (all-gather mode)
+  CUtensorMap b;
+  CUtensorMap out[kMaxRanks];   // [0]: y; reduce-scatter: one per owner's staging
+};
+
+struct TpParams {
+  // all-gather mode
+  const char* x_shards[kMaxRanks];
+  char* x_full;
+  // reduce-scatter mode
+  const char* partials_local;
+  uint32_t* arrived[kMaxRanks];
+  __nv_bfloat16* out;
+  // common
+  uint32_t* ctrl;
+  uint32_t* status;   // plain mode: where a failed wait is recorded (may be null)
+  int m_total, m_local, n, k, gm;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Cross-GPU barrier executed by ONE warp (lanes < nranks signal and poll).
+__device__ __forceinline__ bool warp_rank_barrier(const CommDev& c, int row, uint32_t phase) {
+  const int lane = threadIdx.x & 31;
+  uint32_t* ep = &c.epochs[kFlagSetTp * kMaxBlocks + row];
+  uint32_t v = 0;
+  if (lane == 0) v = *ep + 1;
+  v = __shfl_sync(0xffffffffu, v, 0);
+  bool ok = true;
+  if (lane < c.nranks) {
+    __threadfence_system();
+    st_relaxed_sys(flag_slot(c, lane, kFlagSetTp, row, c.rank), v);
+    ok = wait_flag_reached(c, flag_slot(c, c.rank, kFlagSetTp, row, lane), v, lane, phase);
+  }
+  ok = __all_sync(0xffffffffu, ok);
+  if (lane == 0) *ep = v;
+  __syncwarp();
+  return ok;
+}
+
+struct TileCoord {
+  int ord;  // m-tile ordinal in schedule order
+  int ni;
+};
+
+// Tile `t` of the schedule: groups of `gm` m-tile ordinals, n-major inside a
+// group, so that CTAs working side by side share B tiles through L2 and the
+// group's A rows stay resident while the wave moves along n.
+__device__ __forceinline__ TileCoord tile_at(int t, int tiles_m, int tiles_n, int gm) {
+  const int per_group = gm * tiles_n;
+  const int group = t / per_group;
+  const int first = group * gm;
+  const int gsz = min(gm, tiles_m - first);
+  const int rem = t - group * per_group;
+  return TileCoord{first + rem % gsz, rem / gsz};
+}
+
+template <TpMode MODE>
+__global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm(const __grid_constant__ TpMaps maps, CommDev c, TpParams p) {
+  using Cfg = TileCfg<kTpBN>;
+  constexpr int BN = kTpBN;
+  constexpr uint32_t idesc = make_idesc_bf16(kBlockM, BN);
+  constexpr bool kFused = MODE != TpMode::PLAIN;
   extern __shared__ char smem_raw[];
   char* stages = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  Barriers* bars = reinterpret_cast<Barriers*>(stages + Cfg::kStages * Cfg::kStageBytes);
+  char* obuf = stages + Cfg::kStages * Cfg::kStageBytes;
+  TpBarriers* bars = reinterpret_cast<TpBarriers*>(obuf + 2 * kOutChunkBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * kBlockM;
+  const int G = gridDim.x;
+  const int tiles_m = (p.m_total + kBlockM - 1) / kBlockM, tiles_n = (p.n + BN - 1) / BN;
+  const int tiles_per_src = kFused ? p.m_local / kBlockM : tiles_m;
+  const int total_tiles = tiles_m * tiles_n;
+  const int k_iters = (p.k + kBlockK - 1) / kBlockK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
       mbar_init(&bars->full[s], 1);
       mbar_init(&bars->empty[s], 1);
     }
-    mbar_init(&bars->acc_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->acc_full[s], 1);
+      mbar_init(&bars->acc_empty[s], 4);  // one arrival per epilogue warp
+    }
     bars->failed = 0;
+    bars->is_last = 0;
+    bars->epoch = kFused ? ld_acquire_gpu(&p.ctrl[0]) : 0u;
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(&bars->tmem_base, Cfg::kTmemCols);
+    tmem_alloc(&bars->tmem_base, 2 * BN);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_acc = bars->tmem_base;
+  const uint32_t tmem_base = bars->tmem_base;
+  const uint32_t epoch = bars->epoch;  // calls completed before this one
 
-  uint32_t it = 0;
-  if (warp < 2) {
-    tile_mainloop<BN>(&map_a, &map_b, stages, bars, m0, n0, k / kBlockK, it, tmem_acc, warp, lane);
-  } else {
-    // Epilogue warps: quadrant q of the accumulator's 128 lanes.
-    const int q = warp & 3;
-    const bool ok = mbar_wait(&bars->acc_full, 0);
-    tc_fence_after_sync();
-    const int row = m0 + q * 32 + lane;
-    if (ok) {
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(c0), r);
-        tmem_ld_wait();
-        if (row < m) {
-          uint4* dst = reinterpret_cast<uint4*>(c + static_cast<size_t>(row) * n + n0 + c0);
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            dst[v] = make_uint4(pack_bf16(r[8 * v], r[8 * v + 1]), pack_bf16(r[8 * v + 2], r[8 * v + 3]),
-                                pack_bf16(r[8 * v + 4], r[8 * v + 5]), pack_bf16(r[8 * v + 6], r[8 * v + 7]));
+  // m-tile ordinal -> real m-tile. All-gather: own rows first, then the
+  // sources in ring order (the order in which the copy warps fetch them).
+  // Reduce-scatter: the next rank's rows first, own rows last.
+  auto mtile_of = [&](int ord) {
+    if (!kFused) return ord;
+    const int j = ord / tiles_per_src, w = ord % tiles_per_src;
+    const int src = MODE == TpMode::AG_GEMM ? (c.rank + j) % c.nranks : (c.rank + 1 + j) % c.nranks;
+    return src * tiles_per_src + w;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total_tiles && !bars->failed; t += G) {
+        const TileCoord tc_ = tile_at(t, tiles_m, tiles_n, p.gm);
+        const int ord = tc_.ord, ni = tc_.ni;
+        const int mi = mtile_of(ord);
+        const CUtensorMap* ma = &maps.a_local;
+        int a_row = mi * kBlockM;
+        if (MODE == TpMode::AG_GEMM) {
+          if (ord < tiles_per_src) {
+            a_row = (mi - c.rank * tiles_per_src) * kBlockM;
+          } else {
+            ma = &maps.a_full;
+            // Rows of a peer: wait until every CTA's copy warps delivered their slice.
+            const uint32_t want = (epoch + 1) * static_cast<uint32_t>(G);
+            bool ok = false;
+            for (uint32_t spin = 0; spin < (1u << 23); ++spin) {
+              if (static_cast<int32_t>(ld_acquire_gpu(&p.ctrl[kCtrlTiles + ord]) - want) >= 0) {
+                ok = true;
+                break;
+              }
+              if ((spin & 1023u) == 1023u && comm_is_dead(c)) break;
+            }
+            if (!ok) {
+              bars->failed = 1;
+              break;
+            }
+            fence_proxy_async();  // written with ordinary stores, read by TMA through the async proxy
           }
         }
+        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+          const int s = it % Cfg::kStages;
+          const uint32_t ph = (it / Cfg::kStages) & 1u;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1u)) {
+            bars->failed = 1;
+            break;
+          }
+          mbar_expect_tx(&bars->full[s], Cfg::kStageBytes);
+          char* sa = stages + s * Cfg::kStageBytes;
+          tma_load_2d(sa, ma, &bars->full[s], kb * kBlockK, a_row);
+          tma_load_2d(sa + Cfg::kABytes, &maps.b, &bars->full[s], kb * kBlockK, ni * BN);
+        }
       }
-    } else {
-      bars->failed = 1;
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tile_iter = 0;
+      for (int t = blockIdx.x; t < total_tiles && !bars->failed; t += G, ++tile_iter) {
+        const uint32_t as = tile_iter & 1u, aph = (tile_iter >> 1) & 1u;
+        if (!mbar_wait(&bars->acc_empty[as], aph ^ 1u)) {
+          bars->failed = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + as * BN;
+        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+          const int s = it % Cfg::kStages;
+          const uint32_t ph = (it / Cfg::kStages) & 1u;
+          if (!mbar_wait(&bars->full[s], ph)) {
+            bars->failed = 1;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(stages + s * Cfg::kStageBytes);
+          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + Cfg::kABytes);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            // 16 bf16 = 32 bytes further along K inside the swizzled row
+            umma_bf16(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
+          }
+          umma_commit(&bars->empty[s]);  // stage reusable once these MMAs have read it
+        }
+        umma_commit(&bars->acc_full[as]);  // accumulator complete
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------- epilogue: TMEM -> bf16 -> swizzled staging -> TMA store
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    const bool issuer = warp == 2 && lane == 0;
+    uint32_t tile_iter = 0, chunk_iter = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += G, ++tile_iter) {
+      const uint32_t as = tile_iter & 1u, aph = (tile_iter >> 1) & 1u;
+      const TileCoord tc_ = tile_at(t, tiles_m, tiles_n, p.gm);
+      const int ni = tc_.ni;
+      const int mi = mtile_of(tc_.ord);
+      if (!mbar_wait(&bars->acc_full[as], aph)) {
+        bars->failed = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      const CUtensorMap* mo = &maps.out[0];
+      int out_row = mi * kBlockM;
+      int owner = 0;
+      if (MODE == TpMode::GEMM_RS) {
+        owner = mi / tiles_per_src;
+        mo = &maps.out[owner];
+        // slot `rank` of the owner's staging, viewed as [nranks * m_local, n]
+        out_row = c.rank * p.m_local + (mi - owner * tiles_per_src) * kBlockM;
+      }
+      for (int j = 0; j < BN / kOutChunkCols; ++j, ++chunk_iter) {
+        char* buf = obuf + (chunk_iter & 1u) * kOutChunkBytes;
+        // The store that read this buffer two chunks ago has drained it.
+        if (issuer) tma_store_wait_read<1>();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + as * BN + (static_cast<uint32_t>(q * 32) << 16) +
+                            static_cast<uint32_t>(j * kOutChunkCols + half * 32),
+                        r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int chunk16 = half * 4 + v;
+            uint4* dst = reinterpret_cast<uint4*>(buf + row_in_tile * 128 + ((chunk16 ^ (row_in_tile & 7)) << 4));
+            *dst = make_uint4(pack_bf16(r[8 * v], r[8 * v + 1]), pack_bf16(r[8 * v + 2], r[8 * v + 3]),
+                              pack_bf16(r[8 * v + 4], r[8 * v + 5]), pack_bf16(r[8 * v + 6], r[8 * v + 7]));
+          }
+        }
+        if (j == BN / kOutChunkCols - 1) {
+          // Accumulator fully read: the MMA warp may reuse this TMEM stage.
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->acc_empty[as]);
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (issuer && ni * BN + j * kOutChunkCols < p.n) {  // chunks wholly past the last column are skipped
+          tma_store_2d(mo, buf, ni * BN + j * kOutChunkCols, out_row);
+          tma_store_commit();
+        }
+      }
+      if (MODE == TpMode::GEMM_RS && issuer) {
+        // Publish the tile to its owner once its four stores have landed.
+        tma_store_wait_all<0>();
+        __threadfence_system();
+        const int tile_local = (mi - owner * tiles_per_src) * tiles_n + ni;
+        st_relaxed_sys(p.arrived[owner] + static_cast<size_t>(tile_local) * c.nranks + c.rank, epoch + 1);
+      }
+    }
+    if (issuer) tma_store_wait_all<0>();
+  } else {
+    // ---------------- copy warps (all-gather mode): fetch the peers' shards
+    if (MODE == TpMode::AG_GEMM) {
+      const int ct = threadIdx.x - kGemmThreads;
+      if (blockIdx.x == 0 && warp == 6) {
+        // Everybody's shard is written before anybody reads it.
+        const bool ok = warp_rank_barrier(c, 0, 0xa1);
+        if (lane == 0) {
+          __threadfence();
+          atomicExch(&p.ctrl[2], ok ? epoch + 1 : 0xffffffffu);
+        }
+      }
+      if (ct == 0) {
+        bool started = false;
+        for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+          const uint32_t v = ld_acquire_gpu(&p.ctrl[2]);
+          if (v == epoch + 1) started = true;
+          if (started || v == 0xffffffffu) break;
+          if ((spin & 1023u) == 1023u && comm_is_dead(c)) break;
+        }
+        if (!started) bars->failed = 1;
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      const size_t tile_bytes = static_cast<size_t>(kBlockM) * p.k * 2;
+      const size_t slice = ((tile_bytes + G - 1) / G + 15) / 16 * 16;
+      const size_t b0 = static_cast<size_t>(blockIdx.x) * slice;
+      for (int ord = tiles_per_src; ord < tiles_m; ++ord) {
+        const int mi = mtile_of(ord);
+        const int src = mi / tiles_per_src;
+        const size_t src_off = static_cast<size_t>(mi - src * tiles_per_src) * tile_bytes;
+        if (b0 < tile_bytes) {
+          const size_t nbytes = tile_bytes - b0 < slice ? tile_bytes - b0 : slice;
+          const uint4* from = reinterpret_cast<const uint4*>(p.x_shards[src] + src_off + b0);
+          uint4* to = reinterpret_cast<uint4*>(p.x_full + static_cast<size_t>(mi) * tile_bytes + b0);
+          const size_t nvec = nbytes / 16;
+          size_t i = ct;
+          for (; i + 3 * kCopyThreads < nvec; i += 4 * kCopyThreads) {
+            const uint4 v0 = from[i], v1 = from[i + kCopyThreads], v2 = from[i + 2 * kCopyThreads], v3 = from[i + 3 * kCopyThreads];
+            to[i] = v0;
+            to[i + kCopyThreads] = v1;
+            to[i + 2 * kCopyThreads] = v2;
+            to[i + 3 * kCopyThreads] = v3;
+          }
+          for (; i < nvec; i += kCopyThreads) to[i] = from[i];
+          fence_proxy_async();  // these rows are read next by TMA (async proxy)
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (ct == 0) {
+          __threadfence();
+          atomicAdd(&p.ctrl[kCtrlTiles + ord], 1u);
+        }
+      }
     }
   }
+
+  // ---------------- reduce phase of the reduce-scatter: sum the nranks
+  // partial tiles of this rank's rows as they arrive.
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
-    tmem_dealloc(tmem_acc, Cfg::kTmemCols);
+  if (MODE == TpMode::GEMM_RS) {
+    const int my_tiles = tiles_per_src * tiles_n;
+    const int nthreads = blockDim.x;
+    for (int rt = blockIdx.x; rt < my_tiles; rt += G) {
+      if (threadIdx.x == 0) bars->reduce_ok = 1;
+      __syncthreads();
+      if (threadIdx.x < c.nranks) {
+        const uint32_t* flag = p.arrived[c.rank] + static_cast<size_t>(rt) * c.nranks + threadIdx.x;
+        if (!wait_flag_reached(c, flag, epoch + 1, threadIdx.x, 0xa3)) bars->reduce_ok = 0;
+      }
+      __syncthreads();
+      if (!bars->reduce_ok) {
+        bars->failed = 1;
+        break;
+      }
+      const int wm = rt / tiles_n, ni = rt % tiles_n;
+      const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.partials_local);
+      // tile = 128 rows x 256 columns = 4096 vectors of 8 bf16
+      for (int v = threadIdx.x; v < kBlockM * BN / 8; v += nthreads) {
+        const int r = v / (BN / 8), cv = v % (BN / 8);
+        const size_t off = (static_cast<size_t>(wm * kBlockM + r)) * p.n + ni * BN + cv * 8;
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        for (int s = 0; s < c.nranks; ++s) {
+          const uint4 q4 = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(s) * p.m_local * p.n + off);
+          const uint32_t* pw = &q4.x;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[2 * i] += __uint_as_float(pw[i] << 16);
+            acc[2 * i + 1] += __uint_as_float(pw[i] & 0xffff0000u);
+          }
+        }
+        uint4 o;
+        uint32_t* po = &o.x;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) po[i] = pack_bf16(__float_as_uint(acc[2 * i]), __float_as_uint(acc[2 * i + 1]));
+        *reinterpret_cast<uint4*>(p.out + off) = o;
+      }
+      __syncthreads();
+    }
   }
-  if (threadIdx.x == 0 && bars->failed && status != nullptr) {
-    status[0] = status[0] | kStatusTimeout;
+
+  // ---------------- teardown. Fused modes: the last CTA to finish advances
+  // the epoch and joins the closing cross-GPU barrier.
+  __syncthreads();
+  if (warp == 1) {
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+  if (!kFused) {
+    if (threadIdx.x == 0 && bars->failed && p.status != nullptr) p.status[0] = p.status[0] | kStatusTimeout;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    if (bars->failed) c.status[0] = c.status[0] | kStatusTimeout;
+    __threadfence();
+    const uint32_t ticket = atomicAdd(&p.ctrl[1], 1u);
+    bars->is_last = ticket == static_cast<uint32_t>(G - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (bars->is_last && warp == 0) {
+    __threadfence();
+    warp_rank_barrier(c, 1, 0xa2);
+    if (lane == 0) {
+      p.ctrl[1] = 0;
+      __threadfence();
+      atomicExch(&p.ctrl[0], epoch + 1);
+    }
   }
 }
 
-template <int BN>
-cudaError_t launch_plain(const void* a, const void* b, void* c, int m, int n, int k, uint32_t* status, cudaStream_t s) {
-  using Cfg = TileCfg<BN>;
-  CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, a, m, k, kBlockM) || !make_map(&map_b, b, n, k, BN)) return cudaErrorInvalidValue;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(k_gemm_bf16_nt<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
+// ------------------------------------------------------------ launchers ----
+
+int sm_count() {
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return std::max(1, sms);
+}
+
+// Largest group height <= 16 that divides the number of m-tiles of one
+// source, so that a group never mixes rows that arrive at different times;
+// awkward counts fall back to 16 (groups then straddle sources, still correct).
+int pick_group(int tiles_per_src) {
+  for (int g = std::min(16, tiles_per_src); g >= 4; --g) {
+    if (tiles_per_src % g == 0) return g;
   }
-  dim3 grid(n / BN, (m + kBlockM - 1) / kBlockM);
-  k_gemm_bf16_nt<BN><<<grid, 192, Cfg::kSmemBytes, s>>>(map_a, map_b, static_cast<__nv_bfloat16*>(c), m, n, k, status);
+  return tiles_per_src < 4 ? std::max(1, tiles_per_src) : 16;
+}
+
+template <TpMode MODE>
+cudaError_t tp_launch(int grid, const TpMaps& maps, const CommDev& c, const TpParams& p, cudaStream_t stream) {
+  // Per device, so not cached in a process-wide flag.
+  cudaError_t e = cudaFuncSetAttribute(k_tp_gemm<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTpSmemBytes);
+  if (e != cudaSuccess) return e;
+  k_tp_gemm<MODE><<<grid, tp_threads<MODE>(), kTpSmemBytes, stream>>>(maps, c, p);
   note_kernel_launch();
   return cudaGetLastError();
 }
-
-// TC_FUSED_PART
 
 } // namespace
 
 cudaError_t launch_gemm_bf16_nt(const void* a, const void* b, void* c, int m, int n, int k, uint32_t* status,
                                 cudaStream_t stream) {
-  if (k % kBlockK != 0 || n % 128 != 0 || m <= 0) return cudaErrorInvalidValue;
+  if (m <= 0 || n <= 0 || k <= 0 || k % 8 != 0 || n % 8 != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15u) {
     return cudaErrorInvalidValue;
   }
-  if (n % 256 == 0) return launch_plain<256>(a, b, c, m, n, k, status, stream);
-  return launch_plain<128>(a, b, c, m, n, k, status, stream);
+  TpMaps maps;
+  if (!make_map(&maps.a_local, a, m, k, kBlockM) || !make_map(&maps.b, b, n, k, kTpBN) ||
+      !make_map(&maps.out[0], c, m, n, kBlockM)) {
+    return cudaErrorInvalidValue;
+  }
+  maps.a_full = maps.a_local;
+  for (int r = 1; r < kMaxRanks; ++r) maps.out[r] = maps.out[0];
+  CommDev none{};
+  none.nranks = 1;
+  TpParams p{};
+  p.status = status;
+  p.m_total = m;
+  p.m_local = m;
+  p.n = n;
+  p.k = k;
+  const int tiles_m = (m + kBlockM - 1) / kBlockM, tiles_n = (n + kTpBN - 1) / kTpBN;
+  p.gm = std::min(16, tiles_m);
+  return tp_launch<TpMode::PLAIN>(std::min(sm_count(), tiles_m * tiles_n), maps, none, p, stream);
+}
+
+size_t tp_ctrl_words(int m_total) {
+  return static_cast<size_t>(kCtrlTiles) + static_cast<size_t>(m_total / kBlockM);
+}
+
+cudaError_t launch_allgather_gemm(const CommDev& comm, const AgGemmArgs& a, cudaStream_t stream) {
+  const int m_total = a.m_local * comm.nranks;
+  if (a.m_local <= 0 || a.m_local % kBlockM != 0 || a.n % kTpBN != 0 || a.k % kBlockK != 0) return cudaErrorInvalidValue;
+  if (comm.nranks > kMaxRanks) return cudaErrorInvalidValue;
+  TpMaps maps;
+  if (!make_map(&maps.a_local, a.x_shards[comm.rank], a.m_local, a.k, kBlockM) ||
+      !make_map(&maps.a_full, a.x_full, m_total, a.k, kBlockM) || !make_map(&maps.b, a.w, a.n, a.k, kTpBN) ||
+      !make_map(&maps.out[0], a.y, m_total, a.n, kBlockM)) {
+    return cudaErrorInvalidValue;
+  }
+  for (int r = 1; r < kMaxRanks; ++r) maps.out[r] = maps.out[0];
+  TpParams p{};
+  for (int r = 0; r < comm.nranks; ++r) p.x_shards[r] = static_cast<const char*>(a.x_shards[r]);
+  p.x_full = static_cast<char*>(a.x_full);
+  p.ctrl = a.ctrl;
+  p.m_total = m_total;
+  p.m_local = a.m_local;
+  p.n = a.n;
+  p.k = a.k;
+  p.gm = pick_group(a.m_local / kBlockM);
+  // All CTAs take part in the copy, so the grid is the whole GPU even when
+  // there are fewer tiles than SMs.
+  return tp_launch<TpMode::AG_GEMM>(sm_count(), maps, comm, p, stream);
+}
+
+cudaError_t launch_gemm_reduce_scatter(const CommDev& comm, const GemmRsArgs& a, cudaStream_t stream) {
+  if (a.m <= 0 || a.m % (kBlockM * comm.nranks) != 0 || a.n % kTpBN != 0 || a.k_local % kBlockK != 0) {
+    return cudaErrorInvalidValue;
+  }
+  if (comm.nranks > kMaxRanks) return cudaErrorInvalidValue;
+  TpMaps maps;
+  if (!make_map(&maps.a_local, a.h, a.m, a.k_local, kBlockM) || !make_map(&maps.b, a.w, a.n, a.k_local, kTpBN)) {
+    return cudaErrorInvalidValue;
+  }
+  maps.a_full = maps.a_local;
+  for (int r = 0; r < kMaxRanks; ++r) {
+    // Stores only (never a load, never multicast): the owner's staging viewed as [m, n].
+    const void* base = r < comm.nranks ? a.partials[r] : a.partials[comm.rank];
+    if (!make_map(&maps.out[r], base, a.m, a.n, kBlockM)) return cudaErrorInvalidValue;
+  }
+  TpParams p{};
+  p.partials_local = static_cast<const char*>(a.partials[comm.rank]);
+  for (int r = 0; r < comm.nranks; ++r) p.arrived[r] = a.arrived[r];
+  p.out = static_cast<__nv_bfloat16*>(a.out);
+  p.ctrl = a.ctrl;
+  p.m_total = a.m;
+  p.m_local = a.m / comm.nranks;
+  p.n = a.n;
+  p.k = a.k_local;
+  p.gm = pick_group(p.m_local / kBlockM);
+  const int tiles = (a.m / kBlockM) * (a.n / kTpBN);
+  return tp_launch<TpMode::GEMM_RS>(std::min(sm_count(), tiles), maps, comm, p, stream);
 }
 
 } // namespace b200c

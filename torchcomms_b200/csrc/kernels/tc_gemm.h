@@ -19,29 +19,37 @@ cudaError_t launch_gemm_bf16_nt(const void* a, const void* b, void* c, int m, in
 // Column-parallel layer fused with the all-gather of its input.
 // x_shards[r] is rank r's [m_local, k] bf16 activation shard in symmetric
 // memory (x_shards[rank] local); `x_full` is local scratch [nranks*m_local, k]
-// that the kernel fills from the peers while the tensor cores already work on
-// the rows that have arrived; w is this rank's [n, k] weight shard;
-// y [nranks*m_local, n]. `ready` is local scratch of nranks*m_local/128 + 2
-// uint32 counters (zeroed by the kernel's previous run or by the caller
-// before the first).
+// that the kernel's copy warps fill from the peers while the tensor cores
+// already work on the rows that have arrived (own rows first, then the
+// sources in ring order); w is this rank's [n, k] weight shard;
+// y [nranks*m_local, n]. m_local % 128 == 0, n % 256 == 0, k % 64 == 0.
+// `ctrl`: local device memory of tp_ctrl_words(nranks*m_local) uint32, zeroed
+// once when allocated; the kernel keeps its call epoch and arrival counters
+// there, so the same launch may be replayed from a CUDA graph.
+// The kernel opens and closes with a cross-rank barrier: a peer's shard is
+// complete before it is read, and no rank returns while its shard is in use.
 struct AgGemmArgs {
   const void* x_shards[kMaxRanks];
   void* x_full;
   const void* w;
   void* y;
   int m_local, n, k;
-  uint32_t* ready;
+  uint32_t* ctrl;
 };
 cudaError_t launch_allgather_gemm(const CommDev& comm, const AgGemmArgs& args, cudaStream_t stream);
 
 // Row-parallel layer fused with the reduce-scatter of its output.
 // h [m, k_local] bf16 local, w [n, k_local] local; every rank computes the
 // partial product for all m rows; rows [r*m/nranks, (r+1)*m/nranks) belong to
-// rank r. Partial tiles are stored straight into the owner's `partials`
-// staging (symmetric; partials[r] = owner r's buffer of
-// [nranks, m/nranks, n] bf16, slot index = source rank); the owner sums the
-// nranks slots in fp32 into `out` [m/nranks, n] bf16 as they arrive.
-// `arrived` (symmetric, arrived[r] on owner r): one uint32 per (tile, source).
+// rank r. The epilogue stores each partial tile straight into the owner's
+// `partials` staging over NVLink (symmetric; partials[r] = owner r's buffer
+// of [nranks, m/nranks, n] bf16, slot index = source rank) and raises the
+// tile's flag there; the owner sums the nranks slots in fp32 into `out`
+// [m/nranks, n] bf16 as they arrive. Tiles for the next rank are computed
+// first, the rank's own last. m % (128*nranks) == 0, n % 256 == 0,
+// k_local % 64 == 0.
+// `arrived` (symmetric, arrived[r] on owner r, zeroed once): one uint32 per
+// (tile of the owner's rows, source). `ctrl`: as above (tp_ctrl_words(0)).
 struct GemmRsArgs {
   const void* h;
   const void* w;
@@ -49,8 +57,10 @@ struct GemmRsArgs {
   uint32_t* arrived[kMaxRanks];
   void* out;
   int m, n, k_local;
-  uint32_t epoch;   // value written to `arrived` flags by this call (monotonic per buffer)
+  uint32_t* ctrl;
 };
 cudaError_t launch_gemm_reduce_scatter(const CommDev& comm, const GemmRsArgs& args, cudaStream_t stream);
+
+size_t tp_ctrl_words(int m_total);
 
 } // namespace b200c

@@ -1,0 +1,204 @@
+// Bindings of the tensor-parallel fused layers: all-gather -> GEMM and
+// GEMM -> reduce-scatter as single tcgen05 kernels over peer memory.
+#include "py_common.hpp"
+
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include <cstring>
+
+#include "../backends/cuda_backend.hpp"
+#include "../cuda/driver_api.hpp"
+#include "../kernels/tc_gemm.h"
+
+namespace b200c {
+
+namespace {
+
+size_t align256(size_t v) {
+  return (v + 255) / 256 * 256;
+}
+
+// Owns the buffers of one layer shape. With a backend the activations /
+// partial sums live in the communicator's symmetric memory; without one
+// (single rank on the current device) in ordinary device memory, which is
+// what the numerics tests and single-GPU profiles use.
+class TpLayer {
+ public:
+  // kind: "ag_gemm" (rows = m_local per rank, cols = k) or "gemm_rs"
+  // (rows = m over all ranks, cols = n).
+  TpLayer(std::shared_ptr<CudaBackend> backend, const std::string& kind, int rows, int cols, double wait_ms)
+      : backend_(std::move(backend)), ag_(kind == "ag_gemm"), rows_(rows), cols_(cols) {
+    TORCH_CHECK(kind == "ag_gemm" || kind == "gemm_rs", "kind must be 'ag_gemm' or 'gemm_rs'");
+    nranks_ = backend_ ? backend_->size() : 1;
+    rank_ = backend_ ? backend_->rank() : 0;
+    if (ag_) {
+      TORCH_CHECK(rows % 128 == 0 && cols % 64 == 0, "ag_gemm: m_local % 128 == 0 and k % 64 == 0 required");
+      data_bytes_ = align256(static_cast<size_t>(rows) * cols * 2);
+      flag_bytes_ = 0;
+    } else {
+      TORCH_CHECK(rows % (128 * nranks_) == 0 && cols % 256 == 0, "gemm_rs: m % (128*nranks) == 0 and n % 256 == 0 required");
+      data_bytes_ = align256(static_cast<size_t>(rows) * cols * 2);  // [nranks, m/nranks, n]
+      flag_bytes_ = align256(static_cast<size_t>(rows / nranks_ / 128) * (cols / 256) * nranks_ * 4);
+    }
+    const size_t total = data_bytes_ + flag_bytes_;
+    if (backend_) {
+      c10::cuda::CUDAGuard g(backend_->device());
+      seg_ = backend_->symm().allocate(total, false);
+      for (int p = 0; p < nranks_; ++p) bases_.push_back(seg_->peer_ptrs[p]);
+    } else {
+      void* p = nullptr;
+      B200C_CUDA_CHECK(cudaMalloc(&p, total));
+      B200C_CUDA_CHECK(cudaMemset(p, 0, total));
+      local_.push_back(p);
+      bases_.push_back(static_cast<char*>(p));
+      const size_t fb = static_cast<size_t>(kFlagSets) * kMaxBlocks * kMaxRanks * sizeof(uint32_t);
+      void* f = nullptr;
+      B200C_CUDA_CHECK(cudaMalloc(&f, fb));
+      B200C_CUDA_CHECK(cudaMemset(f, 0, fb));
+      local_.push_back(f);
+      void* ep = nullptr;
+      B200C_CUDA_CHECK(cudaMalloc(&ep, kFlagSets * kMaxBlocks * sizeof(uint32_t)));
+      B200C_CUDA_CHECK(cudaMemset(ep, 0, kFlagSets * kMaxBlocks * sizeof(uint32_t)));
+      local_.push_back(ep);
+      B200C_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped));
+      std::memset(status_host_, 0, 64);
+      uint32_t* sdev = nullptr;
+      B200C_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&sdev), status_host_, 0));
+      std::memset(&solo_, 0, sizeof(solo_));
+      solo_.rank = 0;
+      solo_.nranks = 1;
+      solo_.flags[0] = static_cast<uint32_t*>(f);
+      solo_.epochs = static_cast<uint32_t*>(ep);
+      solo_.status = sdev;
+      solo_.timeout_ns = static_cast<unsigned long long>(wait_ms * 1e6);
+    }
+    const size_t ctrl_bytes = tp_ctrl_words(ag_ ? rows * nranks_ : 0) * sizeof(uint32_t);
+    void* ctrl = nullptr;
+    B200C_CUDA_CHECK(cudaMalloc(&ctrl, ctrl_bytes));
+    B200C_CUDA_CHECK(cudaMemset(ctrl, 0, ctrl_bytes));
+    local_.push_back(ctrl);
+    ctrl_ = static_cast<uint32_t*>(ctrl);
+    if (ag_ && nranks_ > 1) {
+      void* full = nullptr;
+      B200C_CUDA_CHECK(cudaMalloc(&full, static_cast<size_t>(rows) * nranks_ * cols * 2));
+      local_.push_back(full);
+      x_full_ = full;
+    }
+    B200C_CUDA_CHECK(cudaDeviceSynchronize());
+  }
+
+  ~TpLayer() {
+    for (void* p : local_) cudaFree(p);
+    if (status_host_) cudaFreeHost(status_host_);
+    if (seg_ && backend_ && backend_->symm_alive()) {
+      try {
+        backend_->symm().release(seg_);
+      } catch (...) {
+      }
+    }
+  }
+
+  // ag_gemm: this rank's activation shard [m_local, k] in symmetric memory;
+  // the producer of the activations writes here.
+  at::Tensor input() {
+    TORCH_CHECK(ag_, "input(): ag_gemm layers only");
+    auto opts = at::TensorOptions().device(at::kCUDA, at::cuda::current_device()).dtype(at::kBFloat16);
+    return at::from_blob(bases_[rank_], {rows_, cols_}, opts);
+  }
+
+  // ag_gemm: y[nranks*m_local, n] = all_gather(input()) @ w[n, k]^T
+  at::Tensor ag_gemm(const at::Tensor& w) {
+    TORCH_CHECK(ag_, "not an ag_gemm layer");
+    TORCH_CHECK(w.is_cuda() && w.is_contiguous() && w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.size(1) == cols_,
+                "w: contiguous bf16 [n, k]");
+    TORCH_CHECK(w.size(0) % 256 == 0, "n must be a multiple of 256");
+    c10::cuda::CUDAGuard g(w.device());
+    at::Tensor y = at::empty({static_cast<int64_t>(rows_) * nranks_, w.size(0)}, w.options());
+    AgGemmArgs a{};
+    for (int p = 0; p < nranks_; ++p) a.x_shards[p] = bases_[p];
+    a.x_full = x_full_ ? x_full_ : bases_[rank_];  // single rank: never read
+    a.w = w.data_ptr();
+    a.y = y.data_ptr();
+    a.m_local = rows_;
+    a.n = static_cast<int>(w.size(0));
+    a.k = cols_;
+    a.ctrl = ctrl_;
+    launch([&](const CommDev& c, cudaStream_t s) { B200C_CUDA_CHECK(launch_allgather_gemm(c, a, s)); }, "ag_gemm/kernel",
+           {w, y});
+    return y;
+  }
+
+  // gemm_rs: out[m/nranks, n] = reduce_scatter(h[m, k_local] @ w[n, k_local]^T)
+  at::Tensor gemm_rs(const at::Tensor& h, const at::Tensor& w) {
+    TORCH_CHECK(!ag_, "not a gemm_rs layer");
+    TORCH_CHECK(h.is_cuda() && h.is_contiguous() && h.scalar_type() == at::kBFloat16 && h.dim() == 2 && h.size(0) == rows_,
+                "h: contiguous bf16 [m, k_local]");
+    TORCH_CHECK(w.is_cuda() && w.is_contiguous() && w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.size(0) == cols_ &&
+                    w.size(1) == h.size(1),
+                "w: contiguous bf16 [n, k_local]");
+    TORCH_CHECK(h.size(1) % 64 == 0, "k_local must be a multiple of 64");
+    c10::cuda::CUDAGuard g(h.device());
+    at::Tensor out = at::empty({rows_ / nranks_, cols_}, h.options());
+    GemmRsArgs a{};
+    a.h = h.data_ptr();
+    a.w = w.data_ptr();
+    for (int p = 0; p < nranks_; ++p) {
+      a.partials[p] = bases_[p];
+      a.arrived[p] = reinterpret_cast<uint32_t*>(bases_[p] + data_bytes_);
+    }
+    a.out = out.data_ptr();
+    a.m = rows_;
+    a.n = cols_;
+    a.k_local = static_cast<int>(h.size(1));
+    a.ctrl = ctrl_;
+    launch([&](const CommDev& c, cudaStream_t s) { B200C_CUDA_CHECK(launch_gemm_reduce_scatter(c, a, s)); }, "gemm_rs/kernel",
+           {h, w, out});
+    return out;
+  }
+
+  std::vector<uint32_t> status() const {
+    return status_host_ ? std::vector<uint32_t>(status_host_, status_host_ + 5) : std::vector<uint32_t>{};
+  }
+
+ private:
+  template <class F>
+  void launch(F&& fn, const char* what, std::vector<at::Tensor> keep) {
+    if (backend_) {
+      backend_->run(what, false, {}, keep, [&](cudaStream_t s) { fn(backend_->comm_dev(), s); });
+    } else {
+      fn(solo_, at::cuda::getCurrentCUDAStream().stream());
+    }
+  }
+
+  std::shared_ptr<CudaBackend> backend_;
+  bool ag_;
+  int rows_, cols_;
+  int nranks_ = 1, rank_ = 0;
+  size_t data_bytes_ = 0, flag_bytes_ = 0;
+  std::shared_ptr<SymmSegment> seg_;
+  std::vector<char*> bases_;
+  std::vector<void*> local_;
+  uint32_t* ctrl_ = nullptr;
+  void* x_full_ = nullptr;
+  uint32_t* status_host_ = nullptr;
+  CommDev solo_;
+};
+
+} // namespace
+
+void bind_tp(py::module_& m) {
+  py::class_<TpLayer, std::shared_ptr<TpLayer>>(m, "TpLayer")
+      .def(py::init([](py::object backend, const std::string& kind, int rows, int cols, double wait_ms) {
+             std::shared_ptr<CudaBackend> b;
+             if (!backend.is_none()) b = backend.cast<std::shared_ptr<CudaBackend>>();
+             return std::make_shared<TpLayer>(b, kind, rows, cols, wait_ms);
+           }),
+           py::arg("backend"), py::arg("kind"), py::arg("rows"), py::arg("cols"), py::arg("wait_ms") = 2000.0)
+      .def("input", &TpLayer::input)
+      .def("ag_gemm", &TpLayer::ag_gemm, py::call_guard<py::gil_scoped_release>())
+      .def("gemm_rs", &TpLayer::gemm_rs, py::call_guard<py::gil_scoped_release>())
+      .def("status", &TpLayer::status);
+}
+
+} // namespace b200c
