@@ -103,8 +103,6 @@ def main():
                         fn = lambda: comm.reduce_scatter_single(dst, src, tc.ReduceOp.SUM, False, hints=h)
                         factor = (world - 1) / world
                     elif op == "all_to_all":
-                        if algo == "nccl":
-                            continue
                         src = (torch.rand(n, device=dev) * 2 - 1).to(dt)
                         dst = torch.empty(n, dtype=dt, device=dev)
                         fn = lambda: comm.all_to_all_single(dst, src, False, hints=h)

@@ -6,6 +6,7 @@ Per-operation matrix after the reference's integration tests
 asynchronous with wait, and CUDA-graph capture with replays; expected values
 are closed-form from ``ones * (rank + 1)``.
 """
+import os
 from datetime import timedelta
 
 import pytest
@@ -202,7 +203,7 @@ def _battery(rank, world, backend_name="b200"):
 
 
 def _world_size():
-    return max(1, min(torch.cuda.device_count(), 4))
+    return max(1, min(torch.cuda.device_count(), int(os.environ.get("B200COMMS_TEST_WORLD", "4"))))
 
 
 def test_cuda_backend_battery():

@@ -127,6 +127,45 @@ def test_all_gather_bytes(nranks, nbytes):
         assert torch.equal(o, ref)
 
 
+@pytest.mark.parametrize("nranks", [2, 3, 8])
+@pytest.mark.parametrize("nbytes", [48, 4096, 100_003, 512 * 1024])
+def test_all_gather_one_shot(nranks, nbytes):
+    """chunk 0 selects the latency kernel: one staged copy, one barrier, pull from every peer."""
+    if nranks * ((nbytes + 4095) // 4096) > 400:
+        pytest.skip("emulation runs all virtual ranks' blocks in one cooperative grid")
+    w = _world(nranks)
+    for it in range(3):  # consecutive calls alternate the parity buffer
+        ins = [torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device="cuda") for _ in range(nranks)]
+        outs = [torch.empty(nranks * nbytes, dtype=torch.uint8, device="cuda") for _ in range(nranks)]
+        w.all_gather(ins, outs, False, 1, 0)
+        torch.cuda.synchronize()
+        ref = torch.cat(ins)
+        for o in outs:
+            assert torch.equal(o, ref)
+    assert w.status()[0] == 0
+
+
+@pytest.mark.parametrize("nranks", [2, 3, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("count", [7, 1000, 16_000])
+def test_reduce_scatter_one_shot(nranks, dtype, count):
+    if count * torch.empty(0, dtype=dtype).element_size() > 128 * ((4096 // nranks) // 16 * 16):
+        pytest.skip("beyond the one-shot capacity for this rank count")
+    sub = (4096 // nranks) // 16 * 16
+    if nranks * -(-count * torch.empty(0, dtype=dtype).element_size() // sub) > 400:
+        pytest.skip("emulation runs all virtual ranks' blocks in one cooperative grid")
+    w = _world(nranks)
+    for it in range(3):
+        ins = [_rand(nranks * count, dtype, 100 * it + r) for r in range(nranks)]
+        outs = [torch.empty(count, dtype=dtype, device="cuda") for _ in range(nranks)]
+        w.reduce_scatter(ins, outs, "same", RED["sum"], 1.0, 1, 0)
+        torch.cuda.synchronize()
+        total = torch.stack([t.float() for t in ins]).sum(0).view(nranks, count)
+        for r in range(nranks):
+            torch.testing.assert_close(outs[r].float(), total[r], **_tol(dtype))
+    assert w.status()[0] == 0
+
+
 def test_all_gather_fused_cast():
     n, count = 4, 33_333
     w = _world(n)

@@ -1,5 +1,6 @@
 """MoE expert-parallel dispatch / combine: emulated ranks on one GPU checked
 against a PyTorch reference, then the real multi-process path."""
+import os
 from datetime import timedelta
 
 import pytest
@@ -141,7 +142,7 @@ def _ep_worker(rank, world):
 
 
 def test_dispatch_combine_multi_gpu():
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), int(os.environ.get("B200COMMS_TEST_WORLD", "4")))
     if world < 2:
         pytest.skip("needs 2 GPUs")
     run_ranks(_ep_worker, world, timeout=300)

@@ -1,6 +1,7 @@
 """Fused tensor-parallel layers (all-gather -> GEMM, GEMM -> reduce-scatter):
 single-rank numerics on one GPU, then the real multi-process path, both
 against an fp32 PyTorch reference."""
+import os
 from datetime import timedelta
 
 import pytest
@@ -74,7 +75,7 @@ def _tp_worker(rank, world):
 
 
 def test_tp_layers_multi_gpu():
-    world = min(torch.cuda.device_count(), 4)
+    world = min(torch.cuda.device_count(), int(os.environ.get("B200COMMS_TEST_WORLD", "4")))
     if world < 2:
         pytest.skip("needs 2 GPUs")
     run_ranks(_tp_worker, world, timeout=300)

@@ -220,6 +220,10 @@ void CudaBackend::parse_tuning(const Hints& h) {
   t.max_event_pool = hint_or<size_t>(h, "max_event_pool_size", t.max_event_pool);
   t.max_blocks = std::max(1, std::min(t.max_blocks, kMaxBlocks));
   t.threads = std::max(32, std::min(t.threads, 256));
+  t.ag_oneshot_max_bytes = hint_or<size_t>(h, "ag_oneshot_max_bytes", env_to_value<size_t>("B200COMMS_AG_ONESHOT_MAX_BYTES", t.ag_oneshot_max_bytes));
+  t.rs_oneshot_max_bytes = hint_or<size_t>(h, "rs_oneshot_max_bytes", env_to_value<size_t>("B200COMMS_RS_ONESHOT_MAX_BYTES", t.rs_oneshot_max_bytes));
+  t.ag_push_min_ranks = hint_or<int>(h, "ag_push_min_ranks", env_to_value<int>("B200COMMS_AG_PUSH_MIN_RANKS", t.ag_push_min_ranks));
+  t.a2av_blocks = hint_or<int>(h, "a2av_blocks", env_to_value<int>("B200COMMS_A2AV_BLOCKS", t.a2av_blocks));
   t.steps_per_block = hint_or<int>(h, "steps_per_block", env_to_value<int>("B200COMMS_STEPS_PER_BLOCK", t.steps_per_block));
   t.staging_bytes = std::max<size_t>(t.staging_bytes, 1u << 20);
   tune_ = t;
@@ -828,14 +832,23 @@ WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bo
     }
   }
   const size_t bytes = in.nbytes();
-  const LaunchShape shape = shape_for(cast ? bytes / 2 : bytes, 1);
+  const Algo algo = algo_override(o);
+  const bool mc = tune_.use_multicast && dev_.mc_heap != nullptr && size_ >= tune_.ag_push_min_ranks;
+  const bool oneshot = !cast && algo != Algo::TWOSHOT && algo != Algo::STAGED &&
+      bytes <= std::min(tune_.ag_oneshot_max_bytes, static_cast<size_t>(kSmallBlocks) * kSmallPiece);
+  LaunchShape shape = shape_for(cast ? bytes / 2 : bytes, mc ? static_cast<size_t>(size_) : 1);
+  if (oneshot) {
+    shape.chunk_bytes = 0;
+    shape.threads = 256;
+  }
   at::Tensor i = in, ot = out;
   bytes_issued_ += bytes;
-  return run(cast ? "all_gather/kernel+cast" : "all_gather/kernel", async_op, o, {in}, [this, i, ot, bytes, cast, shape](cudaStream_t s) {
-    const void* ip = i.data_ptr();
-    void* op_ = ot.data_ptr();
-    B200C_CUDA_CHECK(launch_all_gather(&dev_, layout_, 0, &ip, &op_, bytes, cast, dev_.mc_heap != nullptr, shape, s));
-  });
+  return run(oneshot ? "all_gather/oneshot" : cast ? "all_gather/kernel+cast" : "all_gather/kernel", async_op, o, {in},
+             [this, i, ot, bytes, cast, shape, mc](cudaStream_t s) {
+               const void* ip = i.data_ptr();
+               void* op_ = ot.data_ptr();
+               B200C_CUDA_CHECK(launch_all_gather(&dev_, layout_, 0, &ip, &op_, bytes, cast, mc, shape, s));
+             });
 }
 
 WorkPtr CudaBackend::all_gather(const std::vector<at::Tensor>& outs, const at::Tensor& in, bool async_op, const OpOptions& o) {
@@ -869,14 +882,20 @@ WorkPtr CudaBackend::all_gather(const std::vector<at::Tensor>& outs, const at::T
 static WorkPtr exchange(CudaBackend* self, const char* what, at::Tensor in, at::Tensor out,
                         std::vector<std::pair<size_t, size_t>> send, std::vector<std::pair<size_t, size_t>> recv,
                         bool async_op, const OpOptions& o, std::vector<at::Tensor> keep,
-                        std::function<void(cudaStream_t)> after = nullptr) {
+                        std::function<void(cudaStream_t)> after = nullptr, size_t known_max = 0) {
   const int n = self->size();
-  // The grid must not depend on rank-local sizes (see launch_all_to_all).
   LaunchShape shape;
-  shape.threads = self->tuning().threads;
-  shape.blocks = std::min(32, self->tuning().max_blocks);
-  shape.chunk_bytes = std::min<size_t>(self->tuning().max_chunk_bytes,
-                                       self->layout().bulk_bytes / (static_cast<size_t>(shape.blocks) * n * kPipeSlots)) / 256 * 256;
+  if (known_max != 0) {
+    // Equal splits: every rank derives the same grid from the block size.
+    shape = self->shape_for(known_max, static_cast<size_t>(n));
+    shape.known_max = known_max;
+  } else {
+    // The grid must not depend on rank-local sizes (see launch_all_to_all).
+    shape.threads = self->tuning().threads;
+    shape.blocks = std::min(self->tuning().a2av_blocks, self->tuning().max_blocks);
+    shape.chunk_bytes = std::min<size_t>(self->tuning().max_chunk_bytes,
+                                         self->layout().bulk_bytes / (static_cast<size_t>(shape.blocks) * n * kPipeSlots)) / 256 * 256;
+  }
   return self->run(what, async_op, o, std::move(keep), [self, in, out, send, recv, shape, n, after](cudaStream_t s) {
     std::vector<size_t> so(n), sl(n), ro(n), rl(n);
     size_t mx = 0;
@@ -971,10 +990,17 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
   const RedKind rk = red_kind(op);
   const bool mc = tune_.use_multicast && rk == RedKind::SUM && dev_.mc_heap != nullptr;
   const size_t wire_bytes = out.numel() * dtype_size(dwire);
-  const LaunchShape shape = shape_for(wire_bytes, size_);
+  LaunchShape shape = shape_for(wire_bytes, size_);
+  const size_t oneshot_cap = static_cast<size_t>(kSmallBlocks) * ((kSmallPiece / size_) / 16 * 16);
+  const bool oneshot = din == dwire && dwire == dout && algo != Algo::TWOSHOT && algo != Algo::STAGED &&
+      out.nbytes() <= std::min(tune_.rs_oneshot_max_bytes, oneshot_cap);
+  if (oneshot) {
+    shape.chunk_bytes = 0;
+    shape.threads = 256;
+  }
   at::Tensor i = in, ot = out;
   bytes_issued_ += in.nbytes();
-  return run("reduce_scatter/kernel", async_op, o, {in}, [this, i, ot, din, dwire, dout, rk, scale, mc, shape](cudaStream_t s) {
+  return run(oneshot ? "reduce_scatter/oneshot" : "reduce_scatter/kernel", async_op, o, {in}, [this, i, ot, din, dwire, dout, rk, scale, mc, shape](cudaStream_t s) {
     const void* ip = i.data_ptr();
     void* op_ = ot.data_ptr();
     B200C_CUDA_CHECK(launch_reduce_scatter(&dev_, layout_, 0, &ip, &op_, ot.numel(), din, dwire, dout, rk, scale, mc, shape, s));
@@ -1018,6 +1044,28 @@ WorkPtr CudaBackend::reduce_scatter_v(at::Tensor& out, const std::vector<at::Ten
   });
 }
 
+// Baseline route: the exchange as grouped NCCL send/recv pairs (how NCCL
+// backends implement all-to-all-v). Byte offsets and counts.
+WorkPtr CudaBackend::exchange_nccl(const char* what, const at::Tensor& in, at::Tensor& out,
+                                   const std::vector<std::pair<size_t, size_t>>& send,
+                                   const std::vector<std::pair<size_t, size_t>>& recv, bool async_op, const OpOptions& o) {
+  at::Tensor i = in, ot = out;
+  return run(what, async_op, o, {in}, [this, i, ot, send, recv](cudaStream_t s) {
+    nccl_check(nccl_->groupStart(), "ncclGroupStart");
+    for (int p = 0; p < size_; ++p) {
+      if (send[p].second > 0) {
+        nccl_check(nccl_->send(static_cast<const char*>(i.data_ptr()) + send[p].first, send[p].second, kNcclUint8, p, nccl_comm_, s),
+                   "ncclSend");
+      }
+      if (recv[p].second > 0) {
+        nccl_check(nccl_->recv(static_cast<char*>(ot.data_ptr()) + recv[p].first, recv[p].second, kNcclUint8, p, nccl_comm_, s),
+                   "ncclRecv");
+      }
+    }
+    nccl_check(nccl_->groupEnd(), "ncclGroupEnd");
+  });
+}
+
 WorkPtr CudaBackend::all_to_all_single(at::Tensor& out, const at::Tensor& in, bool async_op, const OpOptions& o) {
   check_tensor(out, device_, "all_to_all_single");
   check_tensor(in, device_, "all_to_all_single");
@@ -1032,7 +1080,10 @@ WorkPtr CudaBackend::all_to_all_single(at::Tensor& out, const at::Tensor& in, bo
     recv[p] = {p * blk, blk};
   }
   bytes_issued_ += in.nbytes();
-  return exchange(this, "all_to_all_single/kernel", in, out, send, recv, async_op, o, {in});
+  if (algo_override(o) == Algo::NCCL && nccl_comm_ != nullptr) {
+    return exchange_nccl("all_to_all_single/nccl", in, out, send, recv, async_op, o);
+  }
+  return exchange(this, "all_to_all_single/kernel", in, out, send, recv, async_op, o, {in}, nullptr, blk);
 }
 
 WorkPtr CudaBackend::all_to_all_v_single(at::Tensor& out, const at::Tensor& in, const std::vector<int64_t>& out_splits,
@@ -1057,6 +1108,9 @@ WorkPtr CudaBackend::all_to_all_v_single(at::Tensor& out, const at::Tensor& in, 
   TORCH_CHECK(so <= in.nbytes(), "all_to_all_v_single: input splits exceed the input tensor");
   TORCH_CHECK(ro <= out.nbytes(), "all_to_all_v_single: output splits exceed the output tensor");
   bytes_issued_ += so;
+  if (algo_override(o) == Algo::NCCL && nccl_comm_ != nullptr) {
+    return exchange_nccl("all_to_all_v_single/nccl", in, out, send, recv, async_op, o);
+  }
   return exchange(this, "all_to_all_v_single/kernel", in, out, send, recv, async_op, o, {in});
 }
 

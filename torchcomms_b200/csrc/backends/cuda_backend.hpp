@@ -77,6 +77,10 @@ enum class Algo : int { AUTO = 0, ONESHOT = 1, TWOSHOT = 2, STAGED = 3, NCCL = 4
 struct Tuning {
   size_t staging_bytes = 128ull << 20;     // bulk staging per rank
   size_t oneshot_max_bytes = 256 * 1024;   // all-reduce: one-shot up to here
+  size_t ag_oneshot_max_bytes = 512 * 1024;  // all-gather: one-shot up to this many bytes per rank
+  size_t rs_oneshot_max_bytes = 64 * 1024;   // reduce-scatter: one-shot up to this many output bytes per rank
+  int ag_push_min_ranks = 4;               // all-gather: multicast push from this many ranks on
+  int a2av_blocks = 96;                    // grid of all-to-all-v (must not depend on rank-local sizes)
   int max_blocks = 444;                    // bulk kernels: 148 SMs x 3 resident blocks
   int threads = 256;
   size_t max_chunk_bytes = 256u << 10;     // bytes staged per block per step
@@ -154,6 +158,10 @@ class CudaBackend final : public Backend {
   }
 
   // Shared with windows and fused ops.
+  WorkPtr exchange_nccl(const char* what, const at::Tensor& in, at::Tensor& out,
+                        const std::vector<std::pair<size_t, size_t>>& send,
+                        const std::vector<std::pair<size_t, size_t>>& recv, bool async_op, const OpOptions& o);
+  LaunchShape shape_for(size_t bytes, size_t slot_multiplier) const;
   const CommDev& comm_dev() const { return dev_; }
   const HeapLayout& layout() const { return layout_; }
   const Tuning& tuning() const { return tune_; }
@@ -189,7 +197,6 @@ class CudaBackend final : public Backend {
   Millis effective_timeout(const OpOptions& o) const { return o.timeout_set ? o.timeout : opts_.timeout; }
   Algo algo_override(const OpOptions& o) const;
   bool kernels_can_reduce(at::ScalarType t, const ReduceOp& op) const;
-  LaunchShape shape_for(size_t bytes, size_t slot_multiplier) const;
   std::pair<cudaEvent_t, cudaEvent_t> take_events();
   void give_events(cudaEvent_t a, cudaEvent_t b);
   void nccl_check(NcclResult r, const char* what) const;

@@ -18,7 +18,10 @@ struct A2aOp {
     // read from device memory (int64 element counts scaled by elem_bytes,
     // blocks packed back to back) and the receive side is learnt from the
     // senders.
-    size_t send_off[kMaxRanks], send_len[kMaxRanks], recv_off[kMaxRanks];
+    size_t send_off[kMaxRanks], send_len[kMaxRanks], recv_off[kMaxRanks], recv_len[kMaxRanks];
+    // Non-zero: every rank already knows all block lengths (equal splits) and
+    // this is the largest; the count exchange and its two barriers are skipped.
+    size_t known_max;
     const long long* dev_send_len;
     size_t elem_bytes;
     size_t bulk_off;
@@ -40,6 +43,18 @@ struct A2aOp {
   // global maximum block length, so that all ranks agree on the step count.
   static __device__ size_t prologue(const CommDev& c, const Args& a) {
     Plan& pl = plan();
+    if (a.known_max != 0 && a.dev_send_len == nullptr) {
+      if (threadIdx.x < c.nranks) {
+        const int p = threadIdx.x;
+        pl.send_off[p] = a.send_off[p];
+        pl.send_len[p] = a.send_len[p];
+        pl.recv_off[p] = a.recv_off[p];
+        pl.recv_len[p] = a.recv_len[p];
+      }
+      if (threadIdx.x == 0) pl.max_len = a.known_max;
+      __syncthreads();
+      return (a.known_max + a.chunk_bytes - 1) / a.chunk_bytes;
+    }
     BlockEpoch ep;
     ep.load(c, kFlagSetMeta);
     unsigned long long* meta_mine = reinterpret_cast<unsigned long long*>(c.heap[c.rank] + a.meta_off) +
@@ -189,7 +204,6 @@ cudaError_t launch_all_to_all(const CommDev* comms, const HeapLayout& lay, int e
                               const size_t* recv_off, const size_t* recv_len, size_t max_len, LaunchShape shape,
                               cudaStream_t stream) {
   using namespace coll;
-  (void)recv_len;  // learnt from the senders inside the kernel
   (void)max_len;
   const int n = emu_ranks > 0 ? emu_ranks : 1;
   const int nranks = comms[0].nranks;
@@ -203,7 +217,9 @@ cudaError_t launch_all_to_all(const CommDev* comms, const HeapLayout& lay, int e
       a.send_off[p] = send_off[i * nranks + p];
       a.send_len[p] = send_len[i * nranks + p];
       a.recv_off[p] = recv_off[i * nranks + p];
+      a.recv_len[p] = recv_len[i * nranks + p];  // used only with known_max; otherwise learnt from the senders
     }
+    a.known_max = shape.known_max;
     a.dev_send_len = nullptr;
     a.elem_bytes = 1;
   }

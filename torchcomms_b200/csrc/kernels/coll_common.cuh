@@ -163,9 +163,10 @@ __global__ void __launch_bounds__(256, 3) k_emu(const CommDev* cs, const typenam
 
 template <typename Op>
 cudaError_t launch_op(const CommDev* comms, int emu_ranks, const typename Op::Args* args, int blocks,
-                      int threads, cudaStream_t stream) {
+                      int threads, cudaStream_t stream, bool exact_grid = false) {
   using Args = typename Op::Args;
   if (blocks < 1) blocks = 1;
+  if (exact_grid && blocks > kMaxBlocks) return cudaErrorInvalidConfiguration;
   if (blocks > kMaxBlocks) blocks = kMaxBlocks;
   if (threads > 256) threads = 256;
   {
@@ -181,6 +182,8 @@ cudaError_t launch_op(const CommDev* comms, int emu_ranks, const typename Op::Ar
       resident_cap = sms * (per_sm > 0 ? per_sm : 1);
     }
     const int cap = emu_ranks > 0 ? resident_cap / emu_ranks : resident_cap;
+    // One block per piece (latency kernels): a smaller grid would skip data.
+    if (exact_grid && blocks > cap) return cudaErrorInvalidConfiguration;
     if (blocks > cap) blocks = cap > 0 ? cap : 1;
   }
   note_kernel_launch();

@@ -134,10 +134,53 @@ struct AgOp {
   static __device__ size_t prologue(const CommDev&, const Args& a) {
     return (a.wire_bytes + a.chunk_bytes - 1) / a.chunk_bytes;
   }
-  static __device__ size_t slot_bytes(const CommDev&, const Args& a) { return a.chunk_bytes; }
+  // With the switch's multicast each rank PUSHES its chunk once and the switch
+  // delivers it into sub-slot `rank` of every rank's slot (egress 1x instead
+  // of nranks-1 pulls); the consumer then only copies out of its own memory.
+  static __device__ bool mc(const CommDev& c, const Args& a) { return a.use_mc && c.mc_heap != nullptr; }
+  static __device__ size_t slot_bytes(const CommDev& c, const Args& a) {
+    return mc(c, a) ? a.chunk_bytes * c.nranks : a.chunk_bytes;
+  }
   static __device__ void stage(const CommDev& c, const Args& a, size_t chunk, size_t off) {
     const size_t b0 = chunk * a.chunk_bytes;
     const size_t n = min_sz(a.chunk_bytes, a.wire_bytes - b0);
+    if (mc(c, a)) {
+      char* dst = c.mc_heap + off + static_cast<size_t>(c.rank) * a.chunk_bytes;
+      const size_t nvec = (n + 15) / 16;  // the slot is padded to 16 bytes; the tail is never copied out
+      if constexpr (std::is_same<CastT, void>::value) {
+        const char* src = a.in + b0;
+        if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0 && n % 16 == 0) {
+          const uint4* s4 = reinterpret_cast<const uint4*>(src);
+          size_t i = threadIdx.x;
+          for (; i + 3 * blockDim.x < nvec; i += 4 * blockDim.x) {
+            const uint4 v0 = s4[i], v1 = s4[i + blockDim.x], v2 = s4[i + 2 * blockDim.x], v3 = s4[i + 3 * blockDim.x];
+            multimem_st16(dst + i * 16, v0);
+            multimem_st16(dst + (i + blockDim.x) * 16, v1);
+            multimem_st16(dst + (i + 2 * blockDim.x) * 16, v2);
+            multimem_st16(dst + (i + 3 * blockDim.x) * 16, v3);
+          }
+          for (; i < nvec; i += blockDim.x) multimem_st16(dst + i * 16, s4[i]);
+        } else {
+          for (size_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            char* vb = reinterpret_cast<char*>(&v);
+            const size_t left = n - i * 16 < 16 ? n - i * 16 : 16;
+            for (size_t k = 0; k < left; ++k) vb[k] = src[i * 16 + k];
+            multimem_st16(dst + i * 16, v);
+          }
+        }
+      } else {
+        const float* src = reinterpret_cast<const float*>(a.in) + b0 / sizeof(CastT);
+        const size_t ne = n / sizeof(CastT);
+        for (size_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+          float f[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) f[k] = i * 8 + k < ne ? src[i * 8 + k] : 0.0f;
+          multimem_st16(dst + i * 16, Pack<CastT>::pack(f));
+        }
+      }
+      return;
+    }
     char* slot = c.heap[c.rank] + off;
     if constexpr (std::is_same<CastT, void>::value) {
       block_copy(slot, a.in + b0, n);
@@ -149,13 +192,128 @@ struct AgOp {
   static __device__ void consume(const CommDev& c, const Args& a, size_t chunk, size_t off) {
     const size_t b0 = chunk * a.chunk_bytes;
     const size_t n = min_sz(a.chunk_bytes, a.wire_bytes - b0);
+    const bool push = mc(c, a);
     for (int i = 0; i < c.nranks; ++i) {
       int q = c.rank + i;
       if (q >= c.nranks) q -= c.nranks;
-      block_copy(a.out + static_cast<size_t>(q) * a.wire_bytes + b0, c.heap[q] + off, n);
+      const char* src = push ? c.heap[c.rank] + off + static_cast<size_t>(q) * a.chunk_bytes : c.heap[q] + off;
+      block_copy(a.out + static_cast<size_t>(q) * a.wire_bytes + b0, src, n);
     }
   }
 };
+
+// Latency mode of the all-gather: block b owns the 4 KB piece b of every
+// rank's input. One copy into the parity-buffered small region, one barrier,
+// then every thread fetches its 16 bytes from all peers at once.
+struct AgOneShot {
+  struct Args {
+    const char* in;
+    char* out;
+    size_t bytes;   // per rank
+    size_t small_off;
+  };
+  static __device__ void run(const CommDev& c, const Args& a) {
+    const size_t e0 = static_cast<size_t>(blockIdx.x) * kSmallPiece;
+    if (e0 >= a.bytes) return;  // same decision on every rank
+    const size_t n = min_sz(kSmallPiece, a.bytes - e0);
+    BlockEpoch ep;
+    ep.load(c, kFlagSetSmall);
+    const size_t parity = (ep.value + 1) & 1u;
+    const size_t off = a.small_off + parity * (static_cast<size_t>(kSmallBlocks) * kSmallPiece) +
+        static_cast<size_t>(blockIdx.x) * kSmallPiece;
+    block_copy(c.heap[c.rank] + off, a.in + e0, n);
+    const bool ok = block_barrier(c, kFlagSetSmall, ep, 0x15);
+    if (ok) {
+      const bool aligned = ((reinterpret_cast<uintptr_t>(a.out + e0) | a.bytes | n) & 15u) == 0;
+      if (aligned) {
+        const size_t nvec = n / 16;
+        for (size_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+          uint4 r[kMaxRanks];
+#pragma unroll
+          for (int q = 0; q < kMaxRanks; ++q) {
+            if (q < c.nranks) r[q] = ld16(c.heap[q] + off + v * 16);
+          }
+#pragma unroll
+          for (int q = 0; q < kMaxRanks; ++q) {
+            if (q < c.nranks) *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(q) * a.bytes + e0 + v * 16) = r[q];
+          }
+        }
+      } else {
+        for (int q = 0; q < c.nranks; ++q) block_copy(a.out + static_cast<size_t>(q) * a.bytes + e0, c.heap[q] + off, n);
+      }
+    }
+    ep.store(c, kFlagSetSmall);
+  }
+};
+
+// Latency mode of the reduce-scatter: a block's 4 KB piece holds one
+// sub-piece per destination rank; after the barrier each rank sums its own
+// sub-piece over all peers.
+template <typename T, RedKind R>
+struct RsOneShot {
+  struct Args {
+    const T* in;    // nranks x count
+    T* out;         // count
+    size_t count;
+    float scale;
+    size_t small_off;
+  };
+  static __device__ __host__ size_t sub_bytes(int nranks) { return (kSmallPiece / nranks) / 16 * 16; }
+  static __device__ void run(const CommDev& c, const Args& a) {
+    constexpr int N = Pack<T>::N;
+    const size_t sub = sub_bytes(c.nranks);
+    const size_t sub_elems = sub / sizeof(T);
+    const size_t e0 = static_cast<size_t>(blockIdx.x) * sub_elems;
+    if (e0 >= a.count) return;  // same decision on every rank
+    const size_t n = min_sz(sub_elems, a.count - e0);
+    BlockEpoch ep;
+    ep.load(c, kFlagSetSmall);
+    const size_t parity = (ep.value + 1) & 1u;
+    const size_t off = a.small_off + parity * (static_cast<size_t>(kSmallBlocks) * kSmallPiece) +
+        static_cast<size_t>(blockIdx.x) * kSmallPiece;
+    for (int p = 0; p < c.nranks; ++p) {
+      block_copy(c.heap[c.rank] + off + p * sub, a.in + static_cast<size_t>(p) * a.count + e0, n * sizeof(T));
+    }
+    const bool ok = block_barrier(c, kFlagSetSmall, ep, 0x16);
+    if (ok) {
+      const size_t nvec = (n + N - 1) / N;
+      const bool aligned = (reinterpret_cast<uintptr_t>(a.out + e0) & 15u) == 0;
+      const size_t mine = off + static_cast<size_t>(c.rank) * sub;
+      for (size_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float acc[N];
+        reduce_peers<T, R>(c, mine + v * 16, acc);
+#pragma unroll
+        for (int k = 0; k < N; ++k) acc[k] *= a.scale;
+        const size_t left = n - v * N;
+        store_values<T, N>(a.out + e0 + v * N, acc, left < N ? static_cast<int>(left) : N, aligned);
+      }
+    }
+    ep.store(c, kFlagSetSmall);
+  }
+};
+
+template <typename T>
+cudaError_t rs_oneshot(const CommDev* comms, const HeapLayout& lay, int emu, const void* const* in, void* const* out,
+                       size_t count, RedKind red, float scale, int threads, cudaStream_t stream) {
+  const int n = emu > 0 ? emu : 1;
+  const int nranks = comms[0].nranks;
+  const size_t sub_elems = RsOneShot<T, RedKind::SUM>::sub_bytes(nranks) / sizeof(T);
+  const size_t blocks = (count + sub_elems - 1) / sub_elems;
+  if (blocks > static_cast<size_t>(kSmallBlocks)) return cudaErrorInvalidValue;
+  auto go = [&](auto tag) {
+    using Op = decltype(tag);
+    std::vector<typename Op::Args> args(n);
+    for (int i = 0; i < n; ++i) args[i] = {static_cast<const T*>(in[i]), static_cast<T*>(out[i]), count, scale, lay.small_off};
+    return launch_op<Op>(comms, emu, args.data(), static_cast<int>(blocks), threads, stream, true);
+  };
+  switch (red) {
+    case RedKind::SUM: return go(RsOneShot<T, RedKind::SUM>{});
+    case RedKind::PROD: return go(RsOneShot<T, RedKind::PROD>{});
+    case RedKind::MIN: return go(RsOneShot<T, RedKind::MIN>{});
+    case RedKind::MAX: return go(RsOneShot<T, RedKind::MAX>{});
+  }
+  return cudaErrorInvalidValue;
+}
 
 template <typename InT, typename WireT, typename OutT, RedKind R>
 cudaError_t rs_dispatch(const CommDev* comms, const HeapLayout& lay, int emu, const void* const* in,
@@ -197,6 +355,15 @@ cudaError_t launch_reduce_scatter(const CommDev* comms, const HeapLayout& lay, i
                                   RedKind red, float scale, bool use_mc, LaunchShape shape, cudaStream_t stream) {
   using namespace coll;
   using bf16 = __nv_bfloat16;
+  if (shape.chunk_bytes == 0) {
+    // Latency mode (same dtype on all three sides only).
+    if (!(in_dtype == wire_dtype && wire_dtype == out_dtype)) return cudaErrorInvalidValue;
+    switch (in_dtype) {
+      case DType::F32: return rs_oneshot<float>(comms, lay, emu_ranks, in, out, count, red, scale, shape.threads, stream);
+      case DType::F16: return rs_oneshot<__half>(comms, lay, emu_ranks, in, out, count, red, scale, shape.threads, stream);
+      case DType::BF16: return rs_oneshot<bf16>(comms, lay, emu_ranks, in, out, count, red, scale, shape.threads, stream);
+    }
+  }
   if (in_dtype == wire_dtype && wire_dtype == out_dtype) {
     switch (in_dtype) {
       case DType::F32: return rs_same<float>(comms, lay, emu_ranks, in, out, count, red, scale, use_mc, shape, stream);
@@ -219,12 +386,21 @@ cudaError_t launch_all_gather(const CommDev* comms, const HeapLayout& lay, int e
                               cudaStream_t stream) {
   using namespace coll;
   const int n = emu_ranks > 0 ? emu_ranks : 1;
+  if (shape.chunk_bytes == 0) {
+    // Latency mode.
+    if (cast_f32_to_bf16 || bytes > static_cast<size_t>(kSmallBlocks) * kSmallPiece) return cudaErrorInvalidValue;
+    std::vector<AgOneShot::Args> args(n);
+    for (int i = 0; i < n; ++i) args[i] = {static_cast<const char*>(in[i]), static_cast<char*>(out[i]), bytes, lay.small_off};
+    const int blocks = static_cast<int>((bytes + kSmallPiece - 1) / kSmallPiece);
+    return launch_op<AgOneShot>(comms, emu_ranks, args.data(), blocks, shape.threads, stream, true);
+  }
   const size_t chunk = (shape.chunk_bytes / 16) * 16;
   if (chunk == 0) return cudaErrorInvalidValue;
   const size_t wire = cast_f32_to_bf16 ? bytes / 2 : bytes;
   const size_t nchunks = (wire + chunk - 1) / chunk;
   const int blocks = static_cast<int>(std::min<size_t>(shape.blocks, std::max<size_t>(nchunks, 1)));
-  if (static_cast<size_t>(blocks) * kPipeSlots * chunk > lay.bulk_bytes) return cudaErrorInvalidValue;
+  const size_t slot_mult = use_mc && comms[0].mc_heap != nullptr ? static_cast<size_t>(comms[0].nranks) : 1;
+  if (static_cast<size_t>(blocks) * kPipeSlots * chunk * slot_mult > lay.bulk_bytes) return cudaErrorInvalidValue;
   if (cast_f32_to_bf16) {
     using Op = AgOp<__nv_bfloat16>;
     std::vector<Op::Args> args(n);

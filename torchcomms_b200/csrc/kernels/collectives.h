@@ -34,7 +34,8 @@ constexpr int kSmallBlocks = 128;          // at most this many pieces per laten
 struct LaunchShape {
   int blocks = 1;
   int threads = 512;
-  size_t chunk_bytes = 0;  // bulk mode: bytes staged per block per step
+  size_t chunk_bytes = 0;  // bulk mode: bytes staged per block per step; 0 selects the latency (one-shot) kernels
+  size_t known_max = 0;    // all-to-all: largest block when every rank knows all lengths (skips the count exchange)
 };
 
 // In-place or out-of-place all-reduce of `count` elements.
