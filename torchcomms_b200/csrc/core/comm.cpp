@@ -3,6 +3,9 @@
 
 #include <dlfcn.h>
 
+#include <ATen/record_function.h>
+#include <torch/csrc/distributed/c10d/control_plane/Handlers.hpp>
+
 #include <algorithm>
 #include <atomic>
 #include <cctype>
@@ -108,6 +111,22 @@ template <typename F>
 WorkPtr Comm::run_op(OpRecord rec, F&& call) {
   TORCH_CHECK(!finalized_, "communicator '", impl_->comm_name(), "' was finalized");
   const size_t id = next_op_id();
+  // Profiler span around the enqueue of every operation (shows up in Kineto
+  // traces next to the kernels it launched). Built only when somebody listens.
+  at::RecordFunction span(at::RecordScope::USER_SCOPE);
+  if (span.isActive()) {
+    std::string label = "torchcomms_b200::";
+    label += op_name(rec.op);
+    if (span.needsInputs()) {
+      std::vector<c10::IValue> ins;
+      for (const auto& t : rec.inputs) ins.emplace_back(t);
+      ins.emplace_back(static_cast<int64_t>(id));
+      ins.emplace_back(impl_->comm_name());
+      span.before(label, c10::ArrayRef<const c10::IValue>(ins.data(), ins.size()));
+    } else {
+      span.before(label);
+    }
+  }
   if (!pre_hooks_->empty()) {
     for (auto& h : pre_hooks_->snapshot()) {
       h(rec.op, id, rec);
@@ -528,6 +547,26 @@ void HealthCheck::mark_unhealthy(const std::string& why) {
     g_health_reason = why;
   }
 }
+
+namespace {
+// Served by c10d's control plane (the worker server of torch.distributed):
+// GET /handler/torchcomms_health_check -> {"healthy": true|false}.
+c10d::control_plane::RegisterHandler g_health_handler(
+    "torchcomms_health_check", [](const c10d::control_plane::Request&, c10d::control_plane::Response& res) {
+      const bool ok = HealthCheck::healthy();
+      std::string body = std::string("{\"healthy\": ") + (ok ? "true" : "false");
+      if (!ok) {
+        std::string why = HealthCheck::reason();
+        for (auto& ch : why) {
+          if (ch == '"' || ch == '\\' || static_cast<unsigned char>(ch) < 0x20) ch = ' ';
+        }
+        body += ", \"reason\": \"" + why + "\"";
+      }
+      body += "}";
+      res.setContent(std::move(body), "application/json");
+      res.setStatus(200);
+    });
+} // namespace
 
 bool HealthCheck::healthy() {
   std::lock_guard<std::mutex> g(g_health_mu);
