@@ -108,3 +108,58 @@ def test_profiler_span_and_health_handler():
         c.all_reduce(torch.ones(4), tc.ReduceOp.SUM, False)
     assert any(e.name == "torchcomms_b200::all_reduce" for e in prof.events())
     c.finalize()
+
+
+def _functional_worker(rank, world):
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import functional as F
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="fn", timeout=timedelta(seconds=60))
+    F.register_comm(comm)
+    x = torch.full((4, 3), float(rank + 1), requires_grad=True)
+    y = F.all_reduce(x, "sum", comm)
+    assert torch.equal(y, torch.full((4, 3), float(sum(range(1, world + 1)))))
+    assert torch.equal(x.detach(), torch.full((4, 3), float(rank + 1)))  # out of place
+    # d/dx sum_ranks(loss_r) with loss_r = (r+1) * sum(y): every rank's grad is the all-reduced upstream grad
+    (y.sum() * (rank + 1)).backward()
+    assert torch.equal(x.grad, torch.full((4, 3), float(sum(range(1, world + 1)))))
+
+    # all_gather <-> reduce_scatter
+    s = torch.full((2, 3), float(rank), requires_grad=True)
+    g = F.all_gather_single(s, comm)
+    assert g.shape == (2 * world, 3) and torch.equal(g[2 * rank], torch.full((3,), float(rank)))
+    (g * torch.arange(2 * world, dtype=torch.float32).view(-1, 1)).sum().backward()
+    expect = torch.arange(2 * world, dtype=torch.float32).view(world, 2)[rank] * world
+    assert torch.equal(s.grad, expect.view(2, 1).expand(2, 3))
+
+    r = torch.ones(2 * world, 3, requires_grad=True)
+    rs = F.reduce_scatter_single(r, "sum", comm)
+    assert rs.shape == (2, 3) and torch.equal(rs, torch.full((2, 3), float(world)))
+    rs.sum().backward()
+    assert torch.equal(r.grad, torch.ones(2 * world, 3))
+
+    a = torch.arange(world, dtype=torch.float32) + 10 * rank
+    assert torch.equal(F.all_to_all_single(a, comm), torch.tensor([10.0 * p + rank for p in range(world)]))
+    b = F.broadcast(torch.full((2,), float(rank)), 1, comm)
+    assert torch.equal(b, torch.ones(2))
+    t = torch.ones(3)
+    F.all_reduce_(t, "max", comm)
+    F.barrier(comm)
+
+    # traced with fake tensors: shapes only, no collective runs
+    from torch.fx.experimental.proxy_tensor import make_fx
+
+    def f(v):
+        return F.wait_tensor(F.reduce_scatter_single(F.all_gather_single(v, "fn"), "sum", "fn")) * 2
+
+    gm = make_fx(f, tracing_mode="fake")(torch.ones(2, 3))
+    names = [n.target.__name__ if hasattr(n.target, "__name__") else str(n.target) for n in gm.graph.nodes if n.op == "call_function"]
+    assert any("all_gather_single" in n for n in names) and any("reduce_scatter_single" in n for n in names)
+    compiled = torch.compile(f, backend="aot_eager", fullgraph=True)
+    out = compiled(torch.full((2, 3), float(rank)))
+    assert torch.equal(out, torch.full((2, 3), float(rank) * world * 2))
+    comm.finalize()
+
+
+def test_functional_ops_over_gloo():
+    run_ranks(_functional_worker, 2, timeout=240)

@@ -1,0 +1,356 @@
+"""Functional (traceable, differentiable) collectives as ``torch.ops.torchcomms_b200.*``.
+
+Communicators are opaque to the tracer, so the ops take the communicator's
+*name* and look it up in a process-wide registry::
+
+    from torchcomms_b200 import functional as F
+    F.register_comm(comm)                              # once per communicator
+    y = F.all_reduce(x, "sum", comm)                   # out-of-place, differentiable
+    g = F.all_gather_single(x_shard, comm)             # [n*rows, ...]
+    s = F.reduce_scatter_single(x, "sum", comm)        # [rows/n, ...]
+    F.all_reduce_(x, "sum", comm)                      # in-place variant
+
+Every op is a ``torch.library`` custom op with a fake (meta) implementation,
+so ``torch.compile`` / ``make_fx`` / ``torch.export`` trace through them
+without running a collective, and an autograd formula (all-reduce <->
+all-reduce, all-gather <-> reduce-scatter, all-to-all <-> all-to-all with the
+splits swapped, broadcast -> reduce to root).  The ops run synchronously with
+respect to the caller's stream (stream-ordered ``wait``), so no separate
+``wait_tensor`` is needed; one is provided as an identity for code written
+against functional-collective APIs.
+
+Parity: comms/torchcomms/functional/{registry,collectives,async_tensor,
+param_parsing,dynamo,inductor_lowering,passes}.py.  The reference lowers its
+ops inside Inductor and reorders waits in graph passes; this framework keeps
+compiled graphs opaque around collectives (CUDA streams and graphs provide the
+overlap instead of a tracing compiler), so those passes have no counterpart.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Union
+
+import torch
+from torch import Tensor
+
+from .. import ReduceOp, TorchComm
+
+NAMESPACE = "torchcomms_b200"
+MIN_PYTORCH_VERSION_FOR_COMPILE = "2.4.0"
+
+_comms: Dict[str, TorchComm] = {}
+
+
+def is_torch_compile_supported(min_version: str = MIN_PYTORCH_VERSION_FOR_COMPILE, _current_version: Optional[str] = None) -> bool:
+    from packaging import version
+
+    cur = _current_version or torch.__version__
+    if os.environ.get("TORCHCOMMS_COMPILE_IGNORE_PYTORCH_VERSION_REQUIREMENT") == "1":
+        return True
+    return version.parse(cur.split("+")[0]) >= version.parse(min_version)
+
+
+def is_torch_compile_supported_and_enabled(min_version: str = MIN_PYTORCH_VERSION_FOR_COMPILE,
+                                           _current_version: Optional[str] = None) -> bool:
+    return is_torch_compile_supported(min_version, _current_version) and os.environ.get("TORCHCOMMS_PATCH_FOR_COMPILE") == "1"
+
+
+def register_comm(comm: TorchComm, name: Optional[str] = None) -> str:
+    key = name or comm.get_name()
+    _comms[key] = comm
+    return key
+
+
+def unregister_comm(comm_or_name: Union[TorchComm, str]) -> None:
+    key = comm_or_name if isinstance(comm_or_name, str) else comm_or_name.get_name()
+    _comms.pop(key, None)
+
+
+def _name(comm: Union[TorchComm, str]) -> str:
+    if isinstance(comm, str):
+        return comm
+    key = comm.get_name()
+    if key not in _comms:
+        _comms[key] = comm
+    return key
+
+
+def _get(name: str) -> TorchComm:
+    try:
+        return _comms[name]
+    except KeyError:
+        raise RuntimeError(f"communicator '{name}' is not registered: call functional.register_comm(comm)") from None
+
+
+_REDS = {"sum": ReduceOp.SUM, "avg": ReduceOp.AVG, "max": ReduceOp.MAX, "min": ReduceOp.MIN, "product": ReduceOp.PRODUCT}
+
+
+def _red(op: str) -> ReduceOp:
+    try:
+        return _REDS[op.lower()]
+    except KeyError:
+        raise ValueError(f"unknown reduce op '{op}' (expected one of {sorted(_REDS)})") from None
+
+
+# ------------------------------------------------------------ op definitions ---
+
+_lib = torch.library.Library(NAMESPACE, "FRAGMENT")  # keeps the definitions alive
+_lib.define("all_reduce(Tensor input, str op, str comm) -> Tensor")
+_lib.define("all_reduce_(Tensor(a!) input, str op, str comm) -> Tensor(a!)")
+_lib.define("all_gather_single(Tensor input, str comm) -> Tensor")
+_lib.define("reduce_scatter_single(Tensor input, str op, str comm) -> Tensor")
+_lib.define("all_to_all_single(Tensor input, int[]? output_split_sizes, int[]? input_split_sizes, str comm) -> Tensor")
+_lib.define("broadcast(Tensor input, int root, str comm) -> Tensor")
+_lib.define("broadcast_(Tensor(a!) input, int root, str comm) -> Tensor(a!)")
+_lib.define("reduce(Tensor input, int root, str op, str comm) -> Tensor")
+_lib.define("barrier(Tensor token, str comm) -> Tensor")
+_lib.define("wait_tensor(Tensor input) -> Tensor")
+
+
+def _size(name: str) -> int:
+    return _get(name).get_size()
+
+
+def _impl_all_reduce(input: Tensor, op: str, comm: str) -> Tensor:
+    out = input.contiguous().clone()
+    _get(comm).all_reduce(out, _red(op), False)
+    return out
+
+
+def _impl_all_reduce_(input: Tensor, op: str, comm: str) -> Tensor:
+    _get(comm).all_reduce(input, _red(op), False)
+    return input
+
+
+def _impl_all_gather_single(input: Tensor, comm: str) -> Tensor:
+    c = _get(comm)
+    x = input.contiguous()
+    out = x.new_empty((x.shape[0] * c.get_size(),) + tuple(x.shape[1:]))
+    c.all_gather_single(out, x, False)
+    return out
+
+
+def _impl_reduce_scatter_single(input: Tensor, op: str, comm: str) -> Tensor:
+    c = _get(comm)
+    x = input.contiguous()
+    out = x.new_empty((x.shape[0] // c.get_size(),) + tuple(x.shape[1:]))
+    c.reduce_scatter_single(out, x, _red(op), False)
+    return out
+
+
+def _impl_all_to_all_single(input: Tensor, output_split_sizes: Optional[List[int]], input_split_sizes: Optional[List[int]],
+                            comm: str) -> Tensor:
+    c = _get(comm)
+    x = input.contiguous()
+    if not output_split_sizes and not input_split_sizes:
+        out = torch.empty_like(x)
+        c.all_to_all_single(out, x, False)
+        return out
+    n = c.get_size()
+    ins = list(input_split_sizes) if input_split_sizes else [x.shape[0] // n] * n
+    outs = list(output_split_sizes) if output_split_sizes else [x.shape[0] // n] * n
+    out = x.new_empty((sum(outs),) + tuple(x.shape[1:]))
+    c.all_to_all_v_single(out, x, outs, ins, False)
+    return out
+
+
+def _impl_broadcast(input: Tensor, root: int, comm: str) -> Tensor:
+    out = input.contiguous().clone()
+    _get(comm).broadcast(out, root, False)
+    return out
+
+
+def _impl_broadcast_(input: Tensor, root: int, comm: str) -> Tensor:
+    _get(comm).broadcast(input, root, False)
+    return input
+
+
+def _impl_reduce(input: Tensor, root: int, op: str, comm: str) -> Tensor:
+    out = input.contiguous().clone()
+    _get(comm).reduce(out, root, _red(op), False)
+    return out
+
+
+def _impl_barrier(token: Tensor, comm: str) -> Tensor:
+    _get(comm).barrier(False)
+    return token.clone()
+
+
+def _impl_wait_tensor(input: Tensor) -> Tensor:
+    return input.clone()
+
+
+for _op, _fn in (("all_reduce", _impl_all_reduce), ("all_reduce_", _impl_all_reduce_),
+                 ("all_gather_single", _impl_all_gather_single), ("reduce_scatter_single", _impl_reduce_scatter_single),
+                 ("all_to_all_single", _impl_all_to_all_single), ("broadcast", _impl_broadcast),
+                 ("broadcast_", _impl_broadcast_), ("reduce", _impl_reduce), ("barrier", _impl_barrier),
+                 ("wait_tensor", _impl_wait_tensor)):
+    _lib.impl(_op, _fn, "CompositeExplicitAutograd")
+
+
+# ------------------------------------------------------- fake implementations ---
+
+
+@torch.library.register_fake(f"{NAMESPACE}::all_reduce")
+def _fake_all_reduce(input, op, comm):
+    return torch.empty_like(input, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake(f"{NAMESPACE}::all_reduce_")
+def _fake_all_reduce_(input, op, comm):
+    return input
+
+
+@torch.library.register_fake(f"{NAMESPACE}::all_gather_single")
+def _fake_all_gather_single(input, comm):
+    return input.new_empty((input.shape[0] * _size(comm),) + tuple(input.shape[1:]))
+
+
+@torch.library.register_fake(f"{NAMESPACE}::reduce_scatter_single")
+def _fake_reduce_scatter_single(input, op, comm):
+    return input.new_empty((input.shape[0] // _size(comm),) + tuple(input.shape[1:]))
+
+
+@torch.library.register_fake(f"{NAMESPACE}::all_to_all_single")
+def _fake_all_to_all_single(input, output_split_sizes, input_split_sizes, comm):
+    if output_split_sizes:
+        return input.new_empty((sum(output_split_sizes),) + tuple(input.shape[1:]))
+    return torch.empty_like(input, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake(f"{NAMESPACE}::broadcast")
+def _fake_broadcast(input, root, comm):
+    return torch.empty_like(input, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake(f"{NAMESPACE}::broadcast_")
+def _fake_broadcast_(input, root, comm):
+    return input
+
+
+@torch.library.register_fake(f"{NAMESPACE}::reduce")
+def _fake_reduce(input, root, op, comm):
+    return torch.empty_like(input, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake(f"{NAMESPACE}::barrier")
+def _fake_barrier(token, comm):
+    return torch.empty_like(token)
+
+
+@torch.library.register_fake(f"{NAMESPACE}::wait_tensor")
+def _fake_wait_tensor(input):
+    return torch.empty_like(input)
+
+
+# ------------------------------------------------------------------ autograd ---
+
+_ops = getattr(torch.ops, NAMESPACE)
+
+
+def _setup(ctx, inputs, output):
+    ctx.args = inputs[1:]
+
+
+def _bw_all_reduce(ctx, grad):
+    op, comm = ctx.args
+    if op.lower() not in ("sum", "avg"):
+        raise RuntimeError(f"all_reduce with op '{op}' is not differentiable")
+    return _ops.all_reduce(grad.contiguous(), op, comm), None, None
+
+
+def _bw_all_gather_single(ctx, grad):
+    (comm,) = ctx.args
+    return _ops.reduce_scatter_single(grad.contiguous(), "sum", comm), None
+
+
+def _bw_reduce_scatter_single(ctx, grad):
+    op, comm = ctx.args
+    g = _ops.all_gather_single(grad.contiguous(), comm)
+    if op.lower() == "avg":
+        g = g / _size(comm)
+    elif op.lower() != "sum":
+        raise RuntimeError(f"reduce_scatter_single with op '{op}' is not differentiable")
+    return g, None, None
+
+
+def _bw_all_to_all_single(ctx, grad):
+    outs, ins, comm = ctx.args
+    return _ops.all_to_all_single(grad.contiguous(), ins, outs, comm), None, None, None
+
+
+def _bw_broadcast(ctx, grad):
+    root, comm = ctx.args
+    g = _ops.reduce(grad.contiguous(), root, "sum", comm)
+    if _get(comm).get_rank() != root:
+        g = torch.zeros_like(g)
+    return g, None, None
+
+
+def _bw_reduce(ctx, grad):
+    root, op, comm = ctx.args
+    return _ops.broadcast(grad.contiguous(), root, comm), None, None, None
+
+
+def _bw_identity(ctx, grad):
+    return (grad,) + (None,) * len(ctx.args)
+
+
+torch.library.register_autograd(f"{NAMESPACE}::all_reduce", _bw_all_reduce, setup_context=_setup)
+torch.library.register_autograd(f"{NAMESPACE}::all_gather_single", _bw_all_gather_single, setup_context=_setup)
+torch.library.register_autograd(f"{NAMESPACE}::reduce_scatter_single", _bw_reduce_scatter_single, setup_context=_setup)
+torch.library.register_autograd(f"{NAMESPACE}::all_to_all_single", _bw_all_to_all_single, setup_context=_setup)
+torch.library.register_autograd(f"{NAMESPACE}::broadcast", _bw_broadcast, setup_context=_setup)
+torch.library.register_autograd(f"{NAMESPACE}::reduce", _bw_reduce, setup_context=_setup)
+torch.library.register_autograd(f"{NAMESPACE}::wait_tensor", _bw_identity, setup_context=_setup)
+
+
+# ------------------------------------------------------------- Python surface ---
+
+
+def all_reduce(x: Tensor, op: str, comm: Union[TorchComm, str]) -> Tensor:
+    return _ops.all_reduce(x, op, _name(comm))
+
+
+def all_reduce_(x: Tensor, op: str, comm: Union[TorchComm, str]) -> Tensor:
+    return _ops.all_reduce_(x, op, _name(comm))
+
+
+def all_gather_single(x: Tensor, comm: Union[TorchComm, str]) -> Tensor:
+    return _ops.all_gather_single(x, _name(comm))
+
+
+def reduce_scatter_single(x: Tensor, op: str, comm: Union[TorchComm, str]) -> Tensor:
+    return _ops.reduce_scatter_single(x, op, _name(comm))
+
+
+def all_to_all_single(x: Tensor, comm: Union[TorchComm, str], output_split_sizes: Optional[List[int]] = None,
+                      input_split_sizes: Optional[List[int]] = None) -> Tensor:
+    return _ops.all_to_all_single(x, output_split_sizes, input_split_sizes, _name(comm))
+
+
+def broadcast(x: Tensor, root: int, comm: Union[TorchComm, str]) -> Tensor:
+    return _ops.broadcast(x, root, _name(comm))
+
+
+def broadcast_(x: Tensor, root: int, comm: Union[TorchComm, str]) -> Tensor:
+    return _ops.broadcast_(x, root, _name(comm))
+
+
+def reduce(x: Tensor, root: int, op: str, comm: Union[TorchComm, str]) -> Tensor:
+    return _ops.reduce(x, root, op, _name(comm))
+
+
+def barrier(comm: Union[TorchComm, str], token: Optional[Tensor] = None) -> Tensor:
+    return _ops.barrier(token if token is not None else torch.zeros(()), _name(comm))
+
+
+def wait_tensor(x: Tensor) -> Tensor:
+    return _ops.wait_tensor(x)
+
+
+__all__ = [
+    "register_comm", "unregister_comm", "is_torch_compile_supported", "is_torch_compile_supported_and_enabled",
+    "all_reduce", "all_reduce_", "all_gather_single", "reduce_scatter_single", "all_to_all_single", "broadcast",
+    "broadcast_", "reduce", "barrier", "wait_tensor",
+]
