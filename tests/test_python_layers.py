@@ -275,3 +275,46 @@ def _tensor_parallel_worker(rank, world):
 
 def test_tensor_parallel_layers():
     run_ranks(_tensor_parallel_worker, 2, timeout=120)
+
+
+def _lazy_worker(rank, world):
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import _comms
+
+    comm = tc.new_comm("gloo-lazy", torch.device("cpu"), name="lazy", timeout=timedelta(seconds=60))
+    impl = comm.get_backend_impl()
+    assert comm.get_backend() == "gloo-lazy" and _comms._lazy_pair_count(impl) == 0
+    # collectives run on the primary and create no pair
+    t = torch.full((4,), float(rank))
+    comm.all_reduce(t, tc.ReduceOp.SUM, False)
+    assert _comms._lazy_pair_count(impl) == 0
+    # ring: each rank talks to two peers -> two pair communicators (one when world == 2)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    got = torch.empty(4)
+    if rank % 2 == 0:
+        comm.send(torch.full((4,), float(rank)), nxt, False)
+        comm.recv(got, prv, False)
+    else:
+        comm.recv(got, prv, False)
+        comm.send(torch.full((4,), float(rank)), nxt, False)
+    assert torch.equal(got, torch.full((4,), float(prv)))
+    assert _comms._lazy_pair_count(impl) == len({nxt, prv})
+    # the same pair is reused
+    if rank % 2 == 0:
+        comm.send(torch.ones(2), nxt, False)
+    else:
+        comm.recv(torch.empty(2), prv, False)
+    assert _comms._lazy_pair_count(impl) == len({nxt, prv})
+    # batches stay on the primary
+    b = comm.batch_op_create()
+    r2 = torch.empty(3)
+    b.send(torch.full((3,), float(rank)), nxt)
+    b.recv(r2, prv)
+    b.issue(False)
+    assert torch.equal(r2, torch.full((3,), float(prv)))
+    comm.barrier(False)
+    comm.finalize()
+
+
+def test_lazy_backend_pair_comms():
+    run_ranks(_lazy_worker, 4, timeout=120)

@@ -738,6 +738,19 @@ std::shared_ptr<Backend> GlooBackend::split(const std::vector<int>& ranks, const
   return child;
 }
 
+std::shared_ptr<Backend> GlooBackend::create_pair_comm(int peer, const std::string& name) {
+  ensure_ready();
+  TORCH_CHECK(peer >= 0 && peer < size_ && peer != rank_, "create_pair_comm: bad peer ", peer);
+  auto child = std::make_shared<GlooBackend>();
+  child->device_ = device_;
+  child->name_ = name_ + "::" + name;
+  child->opts_ = opts_;
+  child->handle_token_ = handle_token_ + "/" + child->name_;
+  child->store_ = scoped_store(store_, "pair/" + name);
+  child->connect(child->store_, rank_ < peer ? 0 : 1, 2);
+  return child;
+}
+
 InitHandle GlooBackend::get_init_handle() const {
   return "gloo:" + handle_token_;
 }

@@ -106,6 +106,7 @@ class GlooBackend : public Backend {
   WorkPtr scatter(at::Tensor& out, const std::vector<at::Tensor>& ins, int root, bool async_op, const OpOptions& o) override;
   WorkPtr gather(const std::vector<at::Tensor>& outs, const at::Tensor& in, int root, bool async_op, const OpOptions& o) override;
   std::shared_ptr<Backend> split(const std::vector<int>& ranks, const std::string& name, const CommOptions& opts) override;
+  std::shared_ptr<Backend> create_pair_comm(int peer, const std::string& name) override;
   void set_timeout(Millis t) override { opts_.timeout = t; }
 
   bool supports_reconfigure() const override { return true; }

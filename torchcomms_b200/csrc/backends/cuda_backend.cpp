@@ -1332,6 +1332,26 @@ std::shared_ptr<Backend> CudaBackend::split(const std::vector<int>& ranks, const
   return child;
 }
 
+std::shared_ptr<Backend> CudaBackend::create_pair_comm(int peer, const std::string& name) {
+  check_usable();
+  TORCH_CHECK(peer >= 0 && peer < size_ && peer != rank_, "create_pair_comm: bad peer ", peer);
+  auto child = std::make_shared<CudaBackend>(registered_as_);
+  child->device_ = device_;
+  child->name_ = name_ + "::" + name;
+  child->opts_ = opts_;
+  child->opts_.store = nullptr;
+  child->drv_ = drv_;
+  child->cuda_ = cuda_;
+  child->nccl_ = nccl_;
+  child->tune_ = tune_;
+  // Point-to-point only: a small staging heap and no multicast object per pair.
+  child->tune_.staging_bytes = std::min<size_t>(tune_.staging_bytes, 4u << 20);
+  child->tune_.use_multicast = false;
+  auto sub = scoped_store(store_, "pair/" + name);
+  child->bootstrap(sub, rank_ < peer ? 0 : 1, 2);
+  return child;
+}
+
 std::unordered_map<std::string, std::string> CudaBackend::comm_dump() const {
   std::unordered_map<std::string, std::string> d;
   d["name"] = name_;

@@ -162,6 +162,7 @@ class CudaBackend final : public Backend {
                         const std::vector<std::pair<size_t, size_t>>& send,
                         const std::vector<std::pair<size_t, size_t>>& recv, bool async_op, const OpOptions& o);
   LaunchShape shape_for(size_t bytes, size_t slot_multiplier) const;
+  std::shared_ptr<Backend> create_pair_comm(int peer, const std::string& name) override;
   const CommDev& comm_dev() const { return dev_; }
   const HeapLayout& layout() const { return layout_; }
   const Tuning& tuning() const { return tune_; }
@@ -292,5 +293,8 @@ class CudaWindow final : public Window {
 };
 
 void register_cuda_backends();
+void register_lazy_backends();
+int lazy_pair_count(const std::shared_ptr<Backend>& b);
+std::shared_ptr<Backend> lazy_primary(const std::shared_ptr<Backend>& b);
 
 } // namespace b200c

@@ -132,14 +132,20 @@ class Backend : public std::enable_shared_from_this<Backend> {
   virtual void set_timeout(Millis t) = 0;
   virtual void set_hints(const Hints& h) { (void)h; }
 
+  // Two-rank communicator with `peer` (a rank of this communicator), created
+  // by those two ranks alone: bootstrapped through the store under a prefix
+  // built from `name`, never through a collective on this communicator. The
+  // lower rank is rank 0 of the pair. Used by the "-lazy" backends.
+  virtual std::shared_ptr<Backend> create_pair_comm(int peer, const std::string& name);
+
   // Registers user memory for zero-copy collectives.
   virtual void tensor_register(const at::Tensor& t) { (void)t; }
   virtual void tensor_deregister(const at::Tensor& t) { (void)t; }
 
   // Observer tables owned by the facade and shared with the backend so the
   // watchdog can fire them.
-  void attach_hook_tables(std::shared_ptr<HookTable<AbortHook>> abort_hooks,
-                          std::shared_ptr<HookTable<GraphReplayHook>> replay_hooks) {
+  virtual void attach_hook_tables(std::shared_ptr<HookTable<AbortHook>> abort_hooks,
+                                  std::shared_ptr<HookTable<GraphReplayHook>> replay_hooks) {
     abort_hooks_ = std::move(abort_hooks);
     replay_hooks_ = std::move(replay_hooks);
   }

@@ -103,6 +103,10 @@ Comm::~Comm() {
   }
 }
 
+std::shared_ptr<Backend> Backend::create_pair_comm(int, const std::string&) {
+  TORCH_CHECK(false, "backend '", backend_name(), "' cannot create per-peer communicators");
+}
+
 void Comm::check_rank(int r, const char* what) const {
   TORCH_CHECK(r >= 0 && r < impl_->size(), what, " rank ", r, " is outside [0, ", impl_->size(), ")");
 }
@@ -551,7 +555,11 @@ void HealthCheck::mark_unhealthy(const std::string& why) {
 namespace {
 // Served by c10d's control plane (the worker server of torch.distributed):
 // GET /handler/torchcomms_health_check -> {"healthy": true|false}.
-c10d::control_plane::RegisterHandler g_health_handler(
+// Registered once per process even if two copies of this library get loaded.
+const bool g_health_handler_registered = [] {
+  const auto names = c10d::control_plane::getHandlerNames();
+  if (std::find(names.begin(), names.end(), "torchcomms_health_check") != names.end()) return false;
+  c10d::control_plane::registerHandler(
     "torchcomms_health_check", [](const c10d::control_plane::Request&, c10d::control_plane::Response& res) {
       const bool ok = HealthCheck::healthy();
       std::string body = std::string("{\"healthy\": ") + (ok ? "true" : "false");
@@ -566,6 +574,8 @@ c10d::control_plane::RegisterHandler g_health_handler(
       res.setContent(std::move(body), "application/json");
       res.setStatus(200);
     });
+  return true;
+}();
 } // namespace
 
 bool HealthCheck::healthy() {

@@ -267,6 +267,9 @@ class EmuWorld {
 
 void bind_cuda_backend(py::module_& m) {
   register_cuda_backends();
+  register_lazy_backends();
+  m.def("_lazy_pair_count", [](const std::shared_ptr<Backend>& b) { return lazy_pair_count(b); });
+  m.def("_lazy_primary", [](const std::shared_ptr<Backend>& b) { return lazy_primary(b); });
 
   py::class_<CudaBackend, Backend, std::shared_ptr<CudaBackend>>(m, "CudaBackend")
       .def("device_alltoallv_single", [](CudaBackend& b, at::Tensor out, const at::Tensor& in, const at::Tensor& os,
