@@ -82,7 +82,7 @@ def bench_collectives(comm, device, world):
 
     out = {}
     sizes = [64 * 1024, 1 << 20, 16 << 20, 256 << 20]
-    for algo in ("auto", "nccl"):
+    for algo in ("auto", "kernel", "nccl"):
         for op in ("all_reduce", "all_gather", "reduce_scatter"):
             for nbytes in sizes:
                 n = nbytes // 2

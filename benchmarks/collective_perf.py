@@ -6,9 +6,11 @@
 
 Protocol: per (op, dtype, size, algorithm) ``warmup`` untimed and ``iters`` timed
 back-to-back calls on buffers ~U[-1, 1], timed on the device with CUDA events
-bracketed by a barrier and a synchronize, maximum over ranks.  ``algo=auto`` is
-this framework's peer-memory kernel selection, ``algo=nccl`` routes the same
-call through NCCL (the reference backend's data path).  Bus bandwidth uses the
+bracketed by a barrier and a synchronize, maximum over ranks.  ``algo=kernel`` is
+this framework's peer-memory kernel family (one-shot / two-shot / NVLS picked by
+size), ``algo=nccl`` routes the same call through NCCL (the reference backend's
+data path) and ``algo=auto`` is the default routing between the two by measured
+cross-over sizes.  Bus bandwidth uses the
 usual factors: 2(n-1)/n for all-reduce, (n-1)/n for the others.
 
 Parity: comms/torchcomms/tests/perf/py/collective_perf_test.py and
@@ -34,7 +36,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ops", default="all_reduce,all_gather,reduce_scatter")
     ap.add_argument("--dtypes", default="bf16")
-    ap.add_argument("--algos", default="auto,nccl")
+    ap.add_argument("--algos", default="auto,kernel,nccl")
     ap.add_argument("--min-bytes", type=int, default=1024)
     ap.add_argument("--max-bytes", type=int, default=1 << 30)
     ap.add_argument("--warmup", type=int, default=20)

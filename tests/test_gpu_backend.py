@@ -197,7 +197,8 @@ def _battery(rank, world, backend_name="b200"):
 
     dump = impl.comm_dump()
     assert dump["rank"] == str(rank) and int(dump["ops_issued"]) > 50
-    assert any(k.startswith("count/all_reduce/oneshot") for k in dump)
+    want = "count/all_reduce/oneshot" if os.environ.get("B200COMMS_AUTO_NCCL") == "0" or world >= 4 else "count/all_reduce/"
+    assert any(k.startswith(want) for k in dump)
     torch.cuda.synchronize()
     comm.finalize()
 
@@ -209,13 +210,22 @@ def _world_size():
 def test_cuda_backend_battery():
     world = _world_size()
     # NVLS is exercised by default; it is available whenever the box grants multicast.
+    # own kernels for every size (algo=auto would hand most sizes to NCCL below 4 ranks) ...
+    run_ranks(_battery, world, timeout=600, extra_env={"B200COMMS_AUTO_NCCL": "0"})
+
+
+def test_cuda_backend_battery_auto_routing():
+    """... and the default routing, which mixes the peer-memory kernels with NCCL by message size."""
+    world = _world_size()
+    if world < 2:
+        pytest.skip("routing only matters with peers")
     run_ranks(_battery, world, timeout=600)
 
 
 def test_cuda_backend_battery_without_multicast():
     if _world_size() < 2:
         pytest.skip("needs 2 GPUs")
-    run_ranks(_battery, 2, timeout=600, extra_env={"B200COMMS_NVLS": "0", "NCCL_NVLS_ENABLE": "0"})
+    run_ranks(_battery, 2, timeout=600, extra_env={"B200COMMS_NVLS": "0", "NCCL_NVLS_ENABLE": "0", "B200COMMS_AUTO_NCCL": "0"})
 
 
 def _stalled_peer(rank, world):

@@ -114,6 +114,35 @@ def test_reduce_scatter(nranks, din, wire, dout):
     assert w.status()[0] == 0
 
 
+def test_reduce_scatter_stochastic_rounding():
+    """fp32 -> bf16 wire with stochastic rounding: unbiased, reproducible per seed, different across seeds."""
+    nranks, count = 4, 64 * 1024
+    w = _world(nranks)
+    value = 1.0 + 2.0 ** -10          # between the bf16 neighbours 1 and 1 + 2^-7: rounds up with probability 1/8
+    ins = [torch.full((nranks * count,), value, dtype=torch.float32, device="cuda") for _ in range(nranks)]
+
+    def run(seed):
+        outs = [torch.empty(count, dtype=torch.float32, device="cuda") for _ in range(nranks)]
+        w.reduce_scatter_sr(ins, outs, "bf16", RED["sum"], 1.0, 4, 16 * 1024, seed)
+        torch.cuda.synchronize()
+        return outs
+
+    nearest = run(0)
+    # round to nearest loses the 2^-10 on every remote contribution (the own part stays fp32)
+    assert torch.equal(nearest[0], torch.full((count,), (nranks - 1) * 1.0 + value, device="cuda"))
+    a, b, c = run(1234), run(1234), run(99)
+    for r in range(nranks):
+        assert torch.equal(a[r], b[r])
+    assert not torch.equal(a[0], c[0])
+    # every remote term is 1 or 1 + 2^-7; the mean recovers the true value
+    mean = torch.stack(a).mean().item()
+    expect = nranks * value
+    assert abs(mean - expect) < 2e-4, (mean, expect)
+    frac_up = ((torch.stack(a) - ((nranks - 1) + value)) / 2.0 ** -7).mean().item() / (nranks - 1)
+    assert 0.10 < frac_up < 0.15, frac_up
+    assert w.status()[0] == 0
+
+
 @pytest.mark.parametrize("nranks", [1, 2, 8])
 @pytest.mark.parametrize("nbytes", [48, 4096, 1_000_003])
 def test_all_gather_bytes(nranks, nbytes):

@@ -59,7 +59,8 @@ Algo parse_algo(std::string s) {
   for (auto& c : s) c = static_cast<char>(std::tolower(static_cast<unsigned char>(c)));
   if (s == "oneshot" || s == "one_shot") return Algo::ONESHOT;
   if (s == "twoshot" || s == "two_shot") return Algo::TWOSHOT;
-  if (s == "staged" || s == "kernel") return Algo::STAGED;
+  if (s == "staged") return Algo::STAGED;
+  if (s == "kernel" || s == "kernels" || s == "own") return Algo::KERNEL;
   if (s == "nccl" || s == "orig") return Algo::NCCL;
   return Algo::AUTO;
 }
@@ -224,6 +225,7 @@ void CudaBackend::parse_tuning(const Hints& h) {
   t.rs_oneshot_max_bytes = hint_or<size_t>(h, "rs_oneshot_max_bytes", env_to_value<size_t>("B200COMMS_RS_ONESHOT_MAX_BYTES", t.rs_oneshot_max_bytes));
   t.ag_push_min_ranks = hint_or<int>(h, "ag_push_min_ranks", env_to_value<int>("B200COMMS_AG_PUSH_MIN_RANKS", t.ag_push_min_ranks));
   t.a2av_blocks = hint_or<int>(h, "a2av_blocks", env_to_value<int>("B200COMMS_A2AV_BLOCKS", t.a2av_blocks));
+  t.auto_nccl = hint_or<bool>(h, "auto_nccl", env_to_value<bool>("B200COMMS_AUTO_NCCL", t.auto_nccl));
   t.steps_per_block = hint_or<int>(h, "steps_per_block", env_to_value<int>("B200COMMS_STEPS_PER_BLOCK", t.steps_per_block));
   t.staging_bytes = std::max<size_t>(t.staging_bytes, 1u << 20);
   tune_ = t;
@@ -661,6 +663,31 @@ Algo CudaBackend::algo_override(const OpOptions& o) const {
   return tune_.force;
 }
 
+// Cross-over sizes measured on 8 B200 over NVSwitch (bf16 and fp32 sweeps,
+// 1 KB - 1 GB, device-timed): the peer-memory kernels win for latency-bound
+// all-reduce (one barrier, one-shot) and for 8 - 64 MB (NVLS two-shot with
+// large chunks), and around 4 - 8 MB for all-gather; NCCL's protocols win the
+// rest, and everything below 4 ranks. algo=kernel forces the kernels.
+Algo CudaBackend::route(Coll c, size_t bytes, const OpOptions& o) const {
+  const Algo a = algo_override(o);
+  if (a == Algo::KERNEL) return Algo::AUTO;
+  if (a != Algo::AUTO) return a;
+  if (nccl_comm_ == nullptr || !tune_.auto_nccl || size_ == 1) return Algo::AUTO;
+  if (size_ < 4) return Algo::NCCL;
+  constexpr size_t KB = 1024, MB = 1024 * 1024;
+  switch (c) {
+    case Coll::ALL_REDUCE:
+      return (bytes <= 512 * KB || (bytes >= 8 * MB && bytes <= 64 * MB)) ? Algo::AUTO : Algo::NCCL;
+    case Coll::ALL_GATHER:   // bytes = gathered size
+      return (bytes >= 4 * MB && bytes <= 8 * MB) ? Algo::AUTO : Algo::NCCL;
+    case Coll::REDUCE_SCATTER:   // bytes = input size
+      return Algo::NCCL;
+    case Coll::ALL_TO_ALL:
+      return Algo::NCCL;
+  }
+  return Algo::AUTO;
+}
+
 bool CudaBackend::kernels_can_reduce(at::ScalarType t, const ReduceOp& op) const {
   DType d;
   if (!to_dtype(t, &d)) return false;
@@ -676,19 +703,20 @@ bool CudaBackend::kernels_can_reduce(at::ScalarType t, const ReduceOp& op) const
 
 // Blocks and per-block chunk for `bytes` of payload when one slot holds
 // `slot_multiplier` chunks (nranks for reduce-scatter / all-to-all, else 1).
-LaunchShape CudaBackend::shape_for(size_t bytes, size_t slot_multiplier) const {
+LaunchShape CudaBackend::shape_for(size_t bytes, size_t slot_multiplier, int block_cap) const {
   LaunchShape s;
   s.threads = tune_.threads;
+  const int max_blocks = block_cap > 0 ? std::min(block_cap, tune_.max_blocks) : tune_.max_blocks;
   const size_t max_chunk = std::max<size_t>(
-      256, std::min(tune_.max_chunk_bytes, layout_.bulk_bytes / (static_cast<size_t>(tune_.max_blocks) * slot_multiplier * kPipeSlots)));
+      256, std::min(tune_.max_chunk_bytes, layout_.bulk_bytes / (static_cast<size_t>(max_blocks) * slot_multiplier * kPipeSlots)));
   // Aim for every block to run several steps on large payloads so that copy
   // and link phases of different blocks overlap; small payloads use few blocks.
-  size_t chunk = round_up(std::max<size_t>(bytes / (static_cast<size_t>(tune_.max_blocks) * std::max(1, tune_.steps_per_block)) + 1, tune_.min_chunk_bytes), 256);
+  size_t chunk = round_up(std::max<size_t>(bytes / (static_cast<size_t>(max_blocks) * std::max(1, tune_.steps_per_block)) + 1, tune_.min_chunk_bytes), 256);
   chunk = std::min(chunk, max_chunk / 256 * 256);
   chunk = std::max<size_t>(chunk, 256);
   const size_t steps = (bytes + chunk - 1) / chunk;
   s.chunk_bytes = chunk;
-  s.blocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(tune_.max_blocks, steps)));
+  s.blocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(max_blocks, steps)));
   return s;
 }
 
@@ -711,7 +739,7 @@ WorkPtr CudaBackend::all_reduce(at::Tensor& t, const ReduceOp& op, bool async_op
   check_tensor(t, device_, "all_reduce");
   const size_t bytes = t.nbytes();
   if (bytes == 0) return c10::make_intrusive<CompletedWork>();
-  Algo algo = algo_override(o);
+  Algo algo = route(Coll::ALL_REDUCE, bytes, o);
   const bool kernels_ok = kernels_can_reduce(t.scalar_type(), op);
   if (!kernels_ok) {
     TORCH_CHECK(op.type() != RedOpType::BAND && op.type() != RedOpType::BOR && op.type() != RedOpType::BXOR,
@@ -822,7 +850,7 @@ WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bo
   TORCH_CHECK(cast || in.scalar_type() == out.scalar_type(),
               "all_gather_single: dtypes must match (or float32 input with bfloat16 output for the fused cast)");
   if (in.numel() == 0) return c10::make_intrusive<CompletedWork>();
-  if (algo_override(o) == Algo::NCCL && nccl_comm_ != nullptr && !cast) {
+  if (!cast && nccl_comm_ != nullptr && route(Coll::ALL_GATHER, out.nbytes(), o) == Algo::NCCL) {
     NcclDataType dt;
     if (to_nccl_dtype(in.scalar_type(), &dt)) {
       at::Tensor i = in, ot = out;
@@ -833,10 +861,12 @@ WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bo
   }
   const size_t bytes = in.nbytes();
   const Algo algo = algo_override(o);
-  const bool mc = tune_.use_multicast && dev_.mc_heap != nullptr && size_ >= tune_.ag_push_min_ranks;
+  // Multicast push pays while the message is latency / launch bound; big gathers pull.
+  const bool mc = tune_.use_multicast && dev_.mc_heap != nullptr && size_ >= tune_.ag_push_min_ranks && bytes <= (8u << 20);
   const bool oneshot = !cast && algo != Algo::TWOSHOT && algo != Algo::STAGED &&
       bytes <= std::min(tune_.ag_oneshot_max_bytes, static_cast<size_t>(kSmallBlocks) * kSmallPiece);
-  LaunchShape shape = shape_for(cast ? bytes / 2 : bytes, mc ? static_cast<size_t>(size_) : 1);
+  const int cap = out.nbytes() < (64u << 20) ? 148 : 0;  // one block per SM is enough below 64 MB
+  LaunchShape shape = shape_for(cast ? bytes / 2 : bytes, mc ? static_cast<size_t>(size_) : 1, cap);
   if (oneshot) {
     shape.chunk_bytes = 0;
     shape.threads = 256;
@@ -947,7 +977,9 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
   TORCH_CHECK(in.numel() == out.numel() * size_, "reduce_scatter_single: input numel must be output numel * size");
   if (out.numel() == 0) return c10::make_intrusive<CompletedWork>();
   const bool same = in.scalar_type() == out.scalar_type();
-  Algo algo = algo_override(o);
+  const bool plain = same && o.hints.find("wire_dtype") == o.hints.end();
+  Algo algo = plain ? route(Coll::REDUCE_SCATTER, in.nbytes(), o) : algo_override(o);
+  if (algo == Algo::KERNEL) algo = Algo::AUTO;
   if (!kernels_can_reduce(in.scalar_type(), op) || !kernels_can_reduce(out.scalar_type(), op)) {
     algo = Algo::NCCL;
   }
@@ -990,7 +1022,7 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
   const RedKind rk = red_kind(op);
   const bool mc = tune_.use_multicast && rk == RedKind::SUM && dev_.mc_heap != nullptr;
   const size_t wire_bytes = out.numel() * dtype_size(dwire);
-  LaunchShape shape = shape_for(wire_bytes, size_);
+  LaunchShape shape = shape_for(wire_bytes, size_, in.nbytes() < (64u << 20) ? 148 : 0);
   const size_t oneshot_cap = static_cast<size_t>(kSmallBlocks) * ((kSmallPiece / size_) / 16 * 16);
   const bool oneshot = din == dwire && dwire == dout && algo != Algo::TWOSHOT && algo != Algo::STAGED &&
       out.nbytes() <= std::min(tune_.rs_oneshot_max_bytes, oneshot_cap);
@@ -1000,11 +1032,13 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
   }
   at::Tensor i = in, ot = out;
   bytes_issued_ += in.nbytes();
-  return run(oneshot ? "reduce_scatter/oneshot" : "reduce_scatter/kernel", async_op, o, {in}, [this, i, ot, din, dwire, dout, rk, scale, mc, shape](cudaStream_t s) {
-    const void* ip = i.data_ptr();
-    void* op_ = ot.data_ptr();
-    B200C_CUDA_CHECK(launch_reduce_scatter(&dev_, layout_, 0, &ip, &op_, ot.numel(), din, dwire, dout, rk, scale, mc, shape, s));
-  });
+  const unsigned long long sr_seed = hint_or<unsigned long long>(o.hints, "sr_seed", 0ull);
+  return run(oneshot ? "reduce_scatter/oneshot" : "reduce_scatter/kernel", async_op, o, {in},
+             [this, i, ot, din, dwire, dout, rk, scale, mc, shape, sr_seed](cudaStream_t s) {
+               const void* ip = i.data_ptr();
+               void* op_ = ot.data_ptr();
+               B200C_CUDA_CHECK(launch_reduce_scatter(&dev_, layout_, 0, &ip, &op_, ot.numel(), din, dwire, dout, rk, scale, mc, shape, s, sr_seed));
+             });
 }
 
 WorkPtr CudaBackend::reduce_scatter(at::Tensor& out, const std::vector<at::Tensor>& ins, const ReduceOp& op, bool async_op, const OpOptions& o) {
@@ -1080,7 +1114,7 @@ WorkPtr CudaBackend::all_to_all_single(at::Tensor& out, const at::Tensor& in, bo
     recv[p] = {p * blk, blk};
   }
   bytes_issued_ += in.nbytes();
-  if (algo_override(o) == Algo::NCCL && nccl_comm_ != nullptr) {
+  if (nccl_comm_ != nullptr && route(Coll::ALL_TO_ALL, in.nbytes(), o) == Algo::NCCL) {
     return exchange_nccl("all_to_all_single/nccl", in, out, send, recv, async_op, o);
   }
   return exchange(this, "all_to_all_single/kernel", in, out, send, recv, async_op, o, {in}, nullptr, blk);
@@ -1108,7 +1142,7 @@ WorkPtr CudaBackend::all_to_all_v_single(at::Tensor& out, const at::Tensor& in, 
   TORCH_CHECK(so <= in.nbytes(), "all_to_all_v_single: input splits exceed the input tensor");
   TORCH_CHECK(ro <= out.nbytes(), "all_to_all_v_single: output splits exceed the output tensor");
   bytes_issued_ += so;
-  if (algo_override(o) == Algo::NCCL && nccl_comm_ != nullptr) {
+  if (nccl_comm_ != nullptr && route(Coll::ALL_TO_ALL, so, o) == Algo::NCCL) {
     return exchange_nccl("all_to_all_v_single/nccl", in, out, send, recv, async_op, o);
   }
   return exchange(this, "all_to_all_v_single/kernel", in, out, send, recv, async_op, o, {in});
@@ -1169,11 +1203,12 @@ WorkPtr CudaBackend::device_alltoallv_single(at::Tensor& out, const at::Tensor& 
 
 WorkPtr CudaBackend::reduce_scatter_quantized(at::Tensor& out, const at::Tensor& in, const ReduceOp& op, int64_t seed,
                                               bool async_op, const OpOptions& o) {
-  (void)seed;
   TORCH_CHECK(in.scalar_type() == at::kFloat && out.scalar_type() == at::kFloat,
               "reduce_scatter_quantized: float32 input and output");
   OpOptions oo = o;
   oo.hints["wire_dtype"] = "bf16";
+  // seed 0 = round to nearest; anything else seeds the stochastic rounding of the wire values
+  oo.hints["sr_seed"] = std::to_string(static_cast<unsigned long long>(seed));
   return reduce_scatter_single(out, in, op, async_op, oo);
 }
 

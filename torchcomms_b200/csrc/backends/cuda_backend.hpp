@@ -72,11 +72,14 @@ class CudaWork final : public Work {
 };
 
 // Which kernel family serves an operation.
-enum class Algo : int { AUTO = 0, ONESHOT = 1, TWOSHOT = 2, STAGED = 3, NCCL = 4 };
+enum class Algo : int { AUTO = 0, ONESHOT = 1, TWOSHOT = 2, STAGED = 3, NCCL = 4, KERNEL = 5 };
+
+// Collective families that have both a peer-memory kernel and an NCCL route.
+enum class Coll : int { ALL_REDUCE, ALL_GATHER, REDUCE_SCATTER, ALL_TO_ALL };
 
 struct Tuning {
   size_t staging_bytes = 128ull << 20;     // bulk staging per rank
-  size_t oneshot_max_bytes = 256 * 1024;   // all-reduce: one-shot up to here
+  size_t oneshot_max_bytes = 512 * 1024;   // all-reduce: one-shot up to here
   size_t ag_oneshot_max_bytes = 512 * 1024;  // all-gather: one-shot up to this many bytes per rank
   size_t rs_oneshot_max_bytes = 64 * 1024;   // reduce-scatter: one-shot up to this many output bytes per rank
   int ag_push_min_ranks = 4;               // all-gather: multicast push from this many ranks on
@@ -85,7 +88,8 @@ struct Tuning {
   int threads = 256;
   size_t max_chunk_bytes = 256u << 10;     // bytes staged per block per step
   int steps_per_block = 8;                 // large payloads: steps each block should run
-  size_t min_chunk_bytes = 16 * 1024;
+  size_t min_chunk_bytes = 64 * 1024;
+  bool auto_nccl = true;                   // algo=auto may pick NCCL where it measured faster
   bool use_multicast = true;
   bool use_nccl = true;                    // create the NCCL communicator at init
   Algo force = Algo::AUTO;                 // B200COMMS_ALGO / hint "algo"
@@ -161,7 +165,9 @@ class CudaBackend final : public Backend {
   WorkPtr exchange_nccl(const char* what, const at::Tensor& in, at::Tensor& out,
                         const std::vector<std::pair<size_t, size_t>>& send,
                         const std::vector<std::pair<size_t, size_t>>& recv, bool async_op, const OpOptions& o);
-  LaunchShape shape_for(size_t bytes, size_t slot_multiplier) const;
+  LaunchShape shape_for(size_t bytes, size_t slot_multiplier, int block_cap = 0) const;
+  // Resolves algo=auto for one call: own kernels (AUTO) or NCCL, from measured cross-over sizes.
+  Algo route(Coll c, size_t bytes, const OpOptions& o) const;
   std::shared_ptr<Backend> create_pair_comm(int peer, const std::string& name) override;
   const CommDev& comm_dev() const { return dev_; }
   const HeapLayout& layout() const { return layout_; }

@@ -150,6 +150,65 @@ __device__ __forceinline__ void block_convert(DstT* __restrict__ dst, const SrcT
   }
 }
 
+// ------------------------------------------------- stochastic rounding -------
+//
+// fp32 -> bf16 with the discarded 16 mantissa bits compared against 16 random
+// bits, so that the expected value of the rounded number equals the input
+// (gradients summed in bf16 over many steps do not lose small updates).
+// Random bits: Philox-4x32 with 7 rounds, counter = (vector index, stream),
+// key = seed; one call yields the 128 bits that 8 elements need. The
+// conversion itself is Blackwell's cvt.rs.bf16x2.f32.
+// Parity: comms/utils/kernels/rng/philox_rng.cuh:27-60 and
+// stochastic_rounding/stochastic_rounding.cuh:13-75.
+
+__device__ __forceinline__ uint4 philox4x32_7(uint4 ctr, uint2 key) {
+  constexpr uint32_t kM0 = 0xD2511F53u, kM1 = 0xCD9E8D57u, kW0 = 0x9E3779B9u, kW1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 7; ++r) {
+    const uint32_t hi0 = __umulhi(kM0, ctr.x), lo0 = kM0 * ctr.x;
+    const uint32_t hi1 = __umulhi(kM1, ctr.z), lo1 = kM1 * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += kW0;
+    key.y += kW1;
+  }
+  return ctr;
+}
+
+// {hi, lo} -> packed bf16x2 (hi in the upper half), each rounded with its own 16 random bits of `rbits`.
+__device__ __forceinline__ uint32_t cvt_rs_bf16x2(float hi, float lo, uint32_t rbits) {
+  uint32_t r;
+  asm("cvt.rs.bf16x2.f32 %0, %1, %2, %3;" : "=r"(r) : "f"(hi), "f"(lo), "r"(rbits));
+  return r;
+}
+
+// Block-cooperative fp32 -> bf16 conversion with stochastic rounding into a
+// 16-byte aligned staging slot. `stream_id` must differ between calls that
+// share a seed and cover different data (rank, destination, chunk offset).
+__device__ __forceinline__ void block_convert_sr(__nv_bfloat16* __restrict__ dst, const float* __restrict__ src, size_t n,
+                                                 unsigned long long seed, unsigned long long stream_id) {
+  const uint2 key = make_uint2(static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
+  const size_t nvec = (n + 7) / 8;
+  for (size_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = v * 8 + k < n ? src[v * 8 + k] : 0.0f;
+    const uint4 rnd = philox4x32_7(make_uint4(static_cast<uint32_t>(v), static_cast<uint32_t>(v >> 32),
+                                              static_cast<uint32_t>(stream_id), static_cast<uint32_t>(stream_id >> 32)),
+                                   key);
+    uint4 o;
+    o.x = cvt_rs_bf16x2(f[1], f[0], rnd.x);
+    o.y = cvt_rs_bf16x2(f[3], f[2], rnd.y);
+    o.z = cvt_rs_bf16x2(f[5], f[4], rnd.z);
+    o.w = cvt_rs_bf16x2(f[7], f[6], rnd.w);
+    if (v * 8 + 8 <= n) {
+      st16(dst + v * 8, o);
+    } else {
+      const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(&o);
+      for (size_t k = 0; v * 8 + k < n; ++k) dst[v * 8 + k] = ob[k];
+    }
+  }
+}
+
 // --------------------------------------------------------- launchers -------
 
 template <typename Op>

@@ -22,6 +22,7 @@ struct RsOp {
     int use_mc;
     size_t bulk_off;
     size_t chunk_elems;  // multiple of Pack<WireT>::N
+    unsigned long long seed;  // non-zero: fp32 -> bf16 staging rounds stochastically
   };
   static __device__ size_t prologue(const CommDev&, const Args& a) {
     return (a.count + a.chunk_elems - 1) / a.chunk_elems;
@@ -40,6 +41,16 @@ struct RsOp {
     // Per destination p, the part of my input that p will reduce.
     for (int p = 0; p < c.nranks; ++p) {
       if (p == c.rank && !use_mc) continue;  // own part is read from `in` directly
+      if constexpr (std::is_same<InT, float>::value && std::is_same<WireT, __nv_bfloat16>::value) {
+        if (a.seed != 0) {
+          // One random stream per (source rank, destination, position): independent errors that average out in the sum.
+          const unsigned long long stream_id =
+              (static_cast<unsigned long long>(c.rank) * kMaxRanks + p) * ((a.count + 7) / 8 + 1) + e0 / 8 + 1;
+          block_convert_sr(reinterpret_cast<__nv_bfloat16*>(c.heap[c.rank] + off + p * sub),
+                           a.in + static_cast<size_t>(p) * a.count + e0, n, a.seed, stream_id);
+          continue;
+        }
+      }
       block_convert<WireT, InT>(reinterpret_cast<WireT*>(c.heap[c.rank] + off + p * sub),
                                 a.in + static_cast<size_t>(p) * a.count + e0, n);
     }
@@ -318,7 +329,7 @@ cudaError_t rs_oneshot(const CommDev* comms, const HeapLayout& lay, int emu, con
 template <typename InT, typename WireT, typename OutT, RedKind R>
 cudaError_t rs_dispatch(const CommDev* comms, const HeapLayout& lay, int emu, const void* const* in,
                         void* const* out, size_t count, float scale, bool use_mc, LaunchShape s,
-                        cudaStream_t stream) {
+                        cudaStream_t stream, unsigned long long seed = 0) {
   using Op = RsOp<InT, WireT, OutT, R>;
   const int n = emu > 0 ? emu : 1;
   const int nranks = comms[0].nranks;
@@ -331,7 +342,7 @@ cudaError_t rs_dispatch(const CommDev* comms, const HeapLayout& lay, int emu, co
   if (static_cast<size_t>(blocks) * kPipeSlots * chunk_elems * sizeof(WireT) * nranks > lay.bulk_bytes) return cudaErrorInvalidValue;
   std::vector<typename Op::Args> args(n);
   for (int i = 0; i < n; ++i) {
-    args[i] = {static_cast<const InT*>(in[i]), static_cast<OutT*>(out[i]), count, scale, use_mc ? 1 : 0, lay.bulk_off, chunk_elems};
+    args[i] = {static_cast<const InT*>(in[i]), static_cast<OutT*>(out[i]), count, scale, use_mc ? 1 : 0, lay.bulk_off, chunk_elems, seed};
   }
   return launch_op<Pipe2<Op>>(comms, emu, args.data(), blocks, s.threads, stream);
 }
@@ -352,7 +363,8 @@ cudaError_t rs_same(const CommDev* comms, const HeapLayout& lay, int emu, const 
 
 cudaError_t launch_reduce_scatter(const CommDev* comms, const HeapLayout& lay, int emu_ranks, const void* const* in,
                                   void* const* out, size_t count, DType in_dtype, DType wire_dtype, DType out_dtype,
-                                  RedKind red, float scale, bool use_mc, LaunchShape shape, cudaStream_t stream) {
+                                  RedKind red, float scale, bool use_mc, LaunchShape shape, cudaStream_t stream,
+                                  unsigned long long sr_seed) {
   using namespace coll;
   using bf16 = __nv_bfloat16;
   if (shape.chunk_bytes == 0) {
@@ -373,9 +385,9 @@ cudaError_t launch_reduce_scatter(const CommDev* comms, const HeapLayout& lay, i
   }
   if (wire_dtype != DType::BF16 || red != RedKind::SUM) return cudaErrorInvalidValue;
   if (in_dtype == DType::F32 && out_dtype == DType::F32)
-    return rs_dispatch<float, bf16, float, RedKind::SUM>(comms, lay, emu_ranks, in, out, count, scale, use_mc, shape, stream);
+    return rs_dispatch<float, bf16, float, RedKind::SUM>(comms, lay, emu_ranks, in, out, count, scale, use_mc, shape, stream, sr_seed);
   if (in_dtype == DType::F32 && out_dtype == DType::BF16)
-    return rs_dispatch<float, bf16, bf16, RedKind::SUM>(comms, lay, emu_ranks, in, out, count, scale, use_mc, shape, stream);
+    return rs_dispatch<float, bf16, bf16, RedKind::SUM>(comms, lay, emu_ranks, in, out, count, scale, use_mc, shape, stream, sr_seed);
   if (in_dtype == DType::BF16 && out_dtype == DType::F32)
     return rs_dispatch<bf16, bf16, float, RedKind::SUM>(comms, lay, emu_ranks, in, out, count, scale, use_mc, shape, stream);
   return cudaErrorInvalidValue;

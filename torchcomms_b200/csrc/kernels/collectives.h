@@ -55,7 +55,11 @@ cudaError_t launch_all_reduce(const CommDev* comms, const HeapLayout& lay, int e
 cudaError_t launch_reduce_scatter(const CommDev* comms, const HeapLayout& lay, int emu_ranks,
                                   const void* const* in, void* const* out, size_t count,
                                   DType in_dtype, DType wire_dtype, DType out_dtype, RedKind red,
-                                  float scale, bool use_mc, LaunchShape shape, cudaStream_t stream);
+                                  float scale, bool use_mc, LaunchShape shape, cudaStream_t stream,
+                                  unsigned long long sr_seed = 0);
+// `sr_seed` != 0 (fp32 input with a bf16 wire only): the narrowing to bf16
+// rounds stochastically (Philox-4x32-7 bits, cvt.rs.bf16x2.f32) instead of to
+// nearest, which keeps the reduced sum unbiased.
 
 // All-gather of `bytes` bytes per rank (dtype-agnostic), or with a fused
 // F32 -> BF16 cast when `cast_f32_to_bf16` (then `bytes` counts input bytes

@@ -214,9 +214,37 @@ __device__ void ep_combine_body(const CommDev& c, const EpDev& e, const CombineA
   cg::grid_group grid = cg::this_grid();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gwarp = blockIdx.x * kEpWarps + warp, nwarps = gridDim.x * kEpWarps;
-  // Every rank has written its expert outputs into its combine buffer.
+  const size_t row_bytes = static_cast<size_t>(e.hidden) * 2;
+  // 1. Push: the expert output of every received row goes back to slot
+  //    [token][this rank] of the rank the token came from. The closing barrier
+  //    of the previous combine guarantees those slots are free.
+  const int n_rows = e.recv_info[0];
+  const int row_vec = e.hidden / 8;  // 16-byte vectors per row; a multiple of 32
+  for (int row = gwarp; row < n_rows; row += nwarps) {
+    const int src = e.recv_src[e.rank][row];
+    const int s = src / e.max_tokens, t = src - s * e.max_tokens;
+    if (src < 0 || s >= e.nranks) {  // never store through a bad index
+      if (lane == 0) c.status[0] = c.status[0] | kStatusBadArg;
+      continue;
+    }
+    const uint4* from = reinterpret_cast<const uint4*>(e.combine_x[e.rank] + static_cast<size_t>(row) * row_bytes);
+    uint4* to = reinterpret_cast<uint4*>(e.comb_recv[s] + (static_cast<size_t>(t) * e.nranks + e.rank) * row_bytes);
+    int v = lane;
+    for (; v + 96 < row_vec; v += 128) {
+      const uint4 v0 = from[v], v1 = from[v + 32], v2 = from[v + 64], v3 = from[v + 96];
+      to[v] = v0;
+      to[v + 32] = v1;
+      to[v + 64] = v2;
+      to[v + 96] = v3;
+    }
+    for (; v < row_vec; v += 32) to[v] = from[v];
+  }
+  __threadfence_system();
+  grid.sync();
   if (blockIdx.x == 0) ep_rank_barrier(c, 0x93);
   grid.sync();
+  // 2. Every contribution has landed: weighted sum out of this rank's own memory.
+  const char* mine = e.comb_recv[e.rank];
   for (int t = gwarp; t < a.num_tokens; t += nwarps) {
     int slot = -1;
     float wt = 1.0f;
@@ -224,7 +252,7 @@ __device__ void ep_combine_body(const CommDev& c, const EpDev& e, const CombineA
       slot = e.send_slot[static_cast<size_t>(t) * e.nranks + lane];
       if (a.weights != nullptr) wt = a.weights[static_cast<size_t>(t) * e.nranks + lane];
     }
-    // 8 elements per lane and step; up to nranks remote rows in flight.
+    const uint32_t have = __ballot_sync(0xffffffffu, slot >= 0);
     for (int e0 = lane * 8; e0 < e.hidden; e0 += 256) {
       float acc[8];
 #pragma unroll
@@ -240,22 +268,17 @@ __device__ void ep_combine_body(const CommDev& c, const EpDev& e, const CombineA
         }
       }
       uint4 rows[kMaxRanks];
-      int have = 0;
 #pragma unroll
       for (int d = 0; d < kMaxRanks; ++d) {
-        if (d < e.nranks) {
-          const int s = __shfl_sync(0xffffffffu, slot, d);
-          if (s >= 0) {
-            rows[d] = ld16(e.combine_x[d] + (static_cast<size_t>(s) * e.hidden + e0) * 2);
-            have |= 1 << d;
-          }
+        if (d < e.nranks && ((have >> d) & 1u)) {
+          rows[d] = ld16(mine + (static_cast<size_t>(t) * e.nranks + d) * row_bytes + static_cast<size_t>(e0) * 2);
         }
       }
 #pragma unroll
       for (int d = 0; d < kMaxRanks; ++d) {
         if (d < e.nranks) {
           const float wd = __shfl_sync(0xffffffffu, wt, d);
-          if ((have >> d) & 1) {
+          if ((have >> d) & 1u) {
             const uint32_t* p = &rows[d].x;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -277,7 +300,7 @@ __device__ void ep_combine_body(const CommDev& c, const EpDev& e, const CombineA
     }
   }
   grid.sync();
-  // Nobody reads this rank's combine buffer any more once this returns.
+  // Nobody overwrites a receive slot that is still being summed.
   if (blockIdx.x == 0) ep_rank_barrier(c, 0x94);
 }
 

@@ -6,8 +6,11 @@
 // scale per 128 elements while it is in registers, and stores the row, its
 // scales, source index and re-based top-k ids / weights straight into the
 // destination rank's receive buffer over NVLink, packed by source rank.
-// combine: the source rank pulls its tokens' expert outputs back from the
-// peers and sums them (optionally weighted, optionally plus a bias) in fp32.
+// combine: every rank pushes the expert outputs of the rows it received back
+// into the slot [token][this rank] of the token's source rank (NVLink stores
+// stream; remote loads would stall on the round trip), one barrier, then the
+// source sums its slots locally (optionally weighted, optionally plus a bias)
+// in fp32.
 //
 // Replaces, in the reference: comms/prims/collectives/link_ep (layout kernel
 // cpp/intranode/kernels/Layout.cu:39-218, notify Notify.cu:97-440, dispatch
@@ -31,7 +34,8 @@ struct EpDev {
   int* recv_topk_idx[kMaxRanks];       // [rows, topk] local expert id or -1
   float* recv_topk_w[kMaxRanks];       // [rows, topk]
   long long* count_matrix[kMaxRanks];  // [nranks, nranks]: [s][d] tokens s sends to d
-  char* combine_x[kMaxRanks];          // [rows, hidden] bf16: expert outputs, read by the sources
+  char* combine_x[kMaxRanks];          // [rows, hidden] bf16: expert outputs, row-aligned with the received rows
+  char* comb_recv[kMaxRanks];          // [max_tokens, nranks, hidden] bf16: outputs returned to the token's source
   // Local scratch.
   int* cnt;          // [nranks]
   int* cursor;       // [nranks]

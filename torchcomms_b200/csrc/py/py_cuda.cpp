@@ -109,6 +109,10 @@ class EmuWorld {
   }
   void reduce_scatter(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, const std::string& wire, int red,
                       double scale, int blocks, size_t chunk) {
+    reduce_scatter_sr(std::move(ins), std::move(outs), wire, red, scale, blocks, chunk, 0);
+  }
+  void reduce_scatter_sr(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, const std::string& wire, int red,
+                         double scale, int blocks, size_t chunk, uint64_t seed) {
     check(ins);
     check(outs);
     std::vector<const void*> ip(n_);
@@ -121,7 +125,7 @@ class EmuWorld {
     const DType dwire = wire == "bf16" ? DType::BF16 : wire == "f16" ? DType::F16 : wire == "f32" ? DType::F32 : din;
     B200C_CUDA_CHECK(launch_reduce_scatter(comms_.data(), lay_, n_, ip.data(), op.data(), outs[0].numel(), din, dwire, dout,
                                            static_cast<RedKind>(red), static_cast<float>(scale), false,
-                                           shape(blocks, chunk), stream()));
+                                           shape(blocks, chunk), stream(), seed));
   }
   void all_gather(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, bool cast, int blocks, size_t chunk) {
     check(ins);
@@ -300,6 +304,7 @@ void bind_cuda_backend(py::module_& m) {
            py::arg("wait_ms") = 2000.0)
       .def("all_reduce", &EmuWorld::all_reduce)
       .def("reduce_scatter", &EmuWorld::reduce_scatter)
+      .def("reduce_scatter_sr", &EmuWorld::reduce_scatter_sr)
       .def("all_gather", &EmuWorld::all_gather)
       .def("all_to_all", &EmuWorld::all_to_all)
       .def("all_to_all_device_splits", &EmuWorld::all_to_all_device_splits)

@@ -200,6 +200,7 @@ class EpBuffer {
     off_w_ = take(R * topk * 4);
     off_count_ = take(static_cast<size_t>(nranks) * nranks * 8);
     off_combine_ = take(R * hidden * 2);
+    off_comb_recv_ = take(R * hidden * 2);  // [max_tokens, nranks, hidden]
     total_ = off;
   }
   void fill(EpDev& e, int rank, const std::vector<char*>& bases) {
@@ -220,6 +221,7 @@ class EpBuffer {
       e.recv_topk_w[p] = reinterpret_cast<float*>(bases[p] + off_w_);
       e.count_matrix[p] = reinterpret_cast<long long*>(bases[p] + off_count_);
       e.combine_x[p] = bases[p] + off_combine_;
+      e.comb_recv[p] = bases[p] + off_comb_recv_;
     }
     auto local = [this](size_t bytes) {
       void* p = nullptr;
@@ -245,7 +247,7 @@ class EpBuffer {
   int n_local_;
   int nranks_ = 1, max_tokens_ = 0, hidden_ = 0, num_experts_ = 0, topk_ = 0;
   bool fp8_ = true;
-  size_t off_x_ = 0, off_scales_ = 0, off_src_ = 0, off_idx_ = 0, off_w_ = 0, off_count_ = 0, off_combine_ = 0, total_ = 0;
+  size_t off_x_ = 0, off_scales_ = 0, off_src_ = 0, off_idx_ = 0, off_w_ = 0, off_count_ = 0, off_combine_ = 0, off_comb_recv_ = 0, total_ = 0;
   std::vector<CommDev> comms_;
   std::vector<EpDev> eps_;
   std::vector<void*> local_allocs_, emu_allocs_;

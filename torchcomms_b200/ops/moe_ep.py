@@ -13,8 +13,9 @@ with the host: the number of received rows is a device tensor.
 Parity: ``comms/prims/collectives/link_ep/link_ep/buffer.py:76-660`` (Buffer,
 get_dispatch_layout, dispatch, combine).  Differences by design: block-scaled
 fp8 quantisation and the token permutation are fused into the dispatch
-kernel, receive counts stay on the device, and combine is a pull by the
-token's owner with the weighted sum fused in.
+kernel, receive counts stay on the device, and combine pushes every expert
+output straight into a per-(token, rank) slot of the token's owner, which then
+sums its slots locally with the weights applied (no ring FIFOs, one barrier).
 """
 from __future__ import annotations
 
