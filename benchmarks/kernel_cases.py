@@ -62,8 +62,11 @@ def main():
         m, n, k = 8192, 4096, 4096
         a, b = rnd(m, k, scale=0.5), rnd(n, k, scale=0.05)
         us = timed(lambda: _comms.ops.gemm_bf16_nt(a, b), args.warmup, args.iters, flush)
+        us2 = timed(lambda: _comms.ops.gemm_bf16_nt_pair(a, b), args.warmup, args.iters, flush)
         ref = timed(lambda: torch.matmul(a, b.t()), args.warmup, args.iters, flush)
-        print(f"gemm tcgen05 {m}x{n}x{k}: {us:.1f} us {2.0 * m * n * k / us / 1e6:.1f} TFLOP/s (cuBLAS {ref:.1f} us {2.0 * m * n * k / ref / 1e6:.1f})")
+        fl = 2.0 * m * n * k / 1e6
+        print(f"gemm tcgen05 {m}x{n}x{k}: one CTA per tile {us:.1f} us {fl / us:.1f} TFLOP/s; CTA pairs {us2:.1f} us {fl / us2:.1f} TFLOP/s; "
+              f"cuBLAS {ref:.1f} us {fl / ref:.1f} TFLOP/s")
     elif args.case in ("ag_gemm", "gemm_rs"):
         from torchcomms_b200.ops.tp import AllGatherGemm, GemmReduceScatter
 

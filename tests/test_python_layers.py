@@ -318,3 +318,17 @@ def _lazy_worker(rank, world):
 
 def test_lazy_backend_pair_comms():
     run_ranks(_lazy_worker, 4, timeout=120)
+
+
+def test_reference_import_name():
+    import torchcomms_b200
+
+    torchcomms_b200.install_alias()
+    import torchcomms
+    from torchcomms import distwrap, objcol  # noqa: F401
+    from torchcomms.device_mesh import init_device_mesh  # noqa: F401
+    from torchcomms.hooks import NanCheckHook  # noqa: F401
+
+    c = torchcomms.new_comm("fake", torch.device("cpu"), name="alias")
+    assert c.get_size() == 1 and torchcomms.ReduceOp.SUM is not None
+    c.finalize()

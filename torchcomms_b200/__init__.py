@@ -198,3 +198,21 @@ def healthy() -> bool:
 
 
 __all__ = [n for n in dir() if not n.startswith("_")] + ["_BackendWrapper"]
+
+
+def install_alias(name: str = "torchcomms") -> None:
+    """Makes ``import torchcomms`` (and its sub-modules) resolve to this package in the current process.
+
+    Code written against the reference package (``torchcomms.new_comm``, ``torchcomms.device_mesh``,
+    ``torchcomms.distwrap``, ``torchcomms.objcol``, ``torchcomms.hooks``, ``torchcomms.functional``) then runs
+    unchanged; backend names "nccl" and "ncclx" select this framework's CUDA backend.  Opt-in and at run time
+    on purpose: a real top-level ``torchcomms`` directory would also be picked up by PyTorch's own start-up
+    probing for that package, in the middle of ``import torch``.
+    """
+    import importlib
+    import sys
+
+    me = sys.modules[__name__]
+    sys.modules[name] = me
+    for sub in ("device_mesh", "distwrap", "functional", "objcol", "hooks", "mem", "ops", "parallel", "_comms"):
+        sys.modules[f"{name}.{sub}"] = importlib.import_module(f"{__name__}.{sub}")

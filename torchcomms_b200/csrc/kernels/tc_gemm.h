@@ -16,6 +16,12 @@ namespace b200c {
 cudaError_t launch_gemm_bf16_nt(const void* a, const void* b, void* c, int m, int n, int k, uint32_t* status,
                                 cudaStream_t stream);
 
+// The same product on CTA pairs (clusters of two CTAs, tcgen05 cta_group::2):
+// each pair owns a 256 x 256 tile and reads every B element once. Same
+// argument rules; any m, n % 8 == 0, k % 8 == 0.
+cudaError_t launch_gemm_bf16_nt_pair(const void* a, const void* b, void* c, int m, int n, int k, uint32_t* status,
+                                     cudaStream_t stream);
+
 // Column-parallel layer fused with the all-gather of its input.
 // x_shards[r] is rank r's [m_local, k] bf16 activation shard in symmetric
 // memory (x_shards[rank] local); `x_full` is local scratch [nranks*m_local, k]

@@ -147,6 +147,19 @@ void bind_ops(py::module_& m) {
     return std::make_pair(c, status);
   });
 
+  ops.def("gemm_bf16_nt_pair", [](const at::Tensor& a, const at::Tensor& b) {
+    want(a, at::kBFloat16, "a");
+    want(b, at::kBFloat16, "b");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "a: [m, k], b: [n, k]");
+    c10::cuda::CUDAGuard g(a.device());
+    at::Tensor c = at::empty({a.size(0), b.size(0)}, a.options());
+    at::Tensor status = at::zeros({2}, a.options().dtype(at::kInt));
+    B200C_CUDA_CHECK(launch_gemm_bf16_nt_pair(a.data_ptr(), b.data_ptr(), c.data_ptr(), static_cast<int>(a.size(0)),
+                                              static_cast<int>(b.size(0)), static_cast<int>(a.size(1)),
+                                              reinterpret_cast<uint32_t*>(status.data_ptr<int>()), cur(a)));
+    return std::make_pair(c, status);
+  });
+
   ops.def("kernel_launch_count", []() { return kernel_launch_count(); });
 }
 
