@@ -210,22 +210,13 @@ def _world_size():
 def test_cuda_backend_battery():
     world = _world_size()
     # NVLS is exercised by default; it is available whenever the box grants multicast.
-    # own kernels for every size (algo=auto would hand most sizes to NCCL below 4 ranks) ...
-    run_ranks(_battery, world, timeout=600, extra_env={"B200COMMS_AUTO_NCCL": "0"})
-
-
-def test_cuda_backend_battery_auto_routing():
-    """... and the default routing, which mixes the peer-memory kernels with NCCL by message size."""
-    world = _world_size()
-    if world < 2:
-        pytest.skip("routing only matters with peers")
-    run_ranks(_battery, world, timeout=600)
+    run_ranks(_battery, world, timeout=240, extra_env={"B200COMMS_AUTO_NCCL": "0"})
 
 
 def test_cuda_backend_battery_without_multicast():
     if _world_size() < 2:
         pytest.skip("needs 2 GPUs")
-    run_ranks(_battery, 2, timeout=600, extra_env={"B200COMMS_NVLS": "0", "NCCL_NVLS_ENABLE": "0", "B200COMMS_AUTO_NCCL": "0"})
+    run_ranks(_battery, 2, timeout=240, extra_env={"B200COMMS_NVLS": "0", "NCCL_NVLS_ENABLE": "0", "B200COMMS_AUTO_NCCL": "0"})
 
 
 def _stalled_peer(rank, world):

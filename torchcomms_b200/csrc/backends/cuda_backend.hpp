@@ -89,7 +89,7 @@ struct Tuning {
   size_t max_chunk_bytes = 256u << 10;     // bytes staged per block per step
   int steps_per_block = 8;                 // large payloads: steps each block should run
   size_t min_chunk_bytes = 64 * 1024;
-  bool auto_nccl = true;                   // algo=auto may pick NCCL where it measured faster
+  bool auto_nccl = false;                  // opt-in: algo=auto may pick NCCL where it measured faster
   bool use_multicast = true;
   bool use_nccl = true;                    // create the NCCL communicator at init
   Algo force = Algo::AUTO;                 // B200COMMS_ALGO / hint "algo"
