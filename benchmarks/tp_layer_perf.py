@@ -12,7 +12,8 @@ Arms:
   * ``unfused`` - this framework's all-gather / reduce-scatter collective
                   followed / preceded by ``torch.matmul`` (cuBLAS)
   * ``nccl``    - the same with the collective routed through NCCL
-  * ``gemm``    - the local GEMM alone (lower bound of any arm)
+  * ``cublas`` / ``tcgen05`` / ``tcgen05x2`` - the local GEMM alone (cuBLAS, this framework's
+                  kernel with one CTA per tile, and on CTA pairs): the lower bound of any arm
 """
 from __future__ import annotations
 
@@ -104,8 +105,10 @@ def main():
     x_all = (torch.randn(m, hid, device=dev) * 0.5).to(bf)
     report("up", "cublas", time_it(lambda: torch.matmul(x_all, w_up.t())), f_up)
     report("up", "tcgen05", time_it(lambda: _comms.ops.gemm_bf16_nt(x_all, w_up)), f_up)
+    report("up", "tcgen05x2", time_it(lambda: _comms.ops.gemm_bf16_nt_pair(x_all, w_up)), f_up)
     report("down", "cublas", time_it(lambda: torch.matmul(h, w_down.t())), f_down)
     report("down", "tcgen05", time_it(lambda: _comms.ops.gemm_bf16_nt(h, w_down)), f_down)
+    report("down", "tcgen05x2", time_it(lambda: _comms.ops.gemm_bf16_nt_pair(h, w_down)), f_down)
 
     report("up", "fused", time_it(lambda: up(w_up)), f_up)
     report("down", "fused", time_it(lambda: down(h, w_down)), f_down)

@@ -332,3 +332,40 @@ def test_reference_import_name():
     c = torchcomms.new_comm("fake", torch.device("cpu"), name="alias")
     assert c.get_size() == 1 and torchcomms.ReduceOp.SUM is not None
     c.finalize()
+
+
+def test_trace_to_perfetto(tmp_path):
+    import json
+
+    from torchcomms_b200.utils.trace_to_perfetto import flight_recorder_events, phase_trace_events, write_trace
+
+    trace = torch.zeros(4, 16, dtype=torch.long)
+    trace[0, :4] = torch.tensor([1000, 2900, 4800, 8600])
+    trace[2, :3] = torch.tensor([1190, 3090, 3100])
+    ev = phase_trace_events(trace, rank=3, sm_mhz=1900.0, phases=("copy-in", "barrier", "reduce"))
+    slices = [e for e in ev if e["ph"] == "X"]
+    assert len(slices) == 5 and slices[0]["name"] == "copy-in" and abs(slices[0]["dur"] - 1.0) < 1e-6
+    assert abs(slices[3]["ts"] - 0.1) < 1e-6 and {e["tid"] for e in slices} == {0, 2}
+    fr = {"rank": 3, "entries": [
+        {"profiling_name": "all_reduce", "time_created_ns": 5_000, "time_discovered_started_ns": 6_000,
+         "time_discovered_completed_ns": 16_000, "collective_seq_id": 1, "state": "completed"},
+        {"profiling_name": "barrier", "time_created_ns": 20_000, "duration_ms": 0.002},
+    ]}
+    fe = [e for e in flight_recorder_events(fr) if e["ph"] == "X"]
+    assert fe[0]["dur"] == 10.0 and fe[1]["dur"] == 2.0 and fe[0]["pid"] == 3
+    write_trace(str(tmp_path / "t.json"), ev + fe)
+    assert len(json.load(open(tmp_path / "t.json"))["traceEvents"]) == len(ev) + len(fe)
+
+
+def test_tuning_crossovers():
+    from torchcomms_b200.utils.tuning import best_config, crossovers, hint_sweep
+
+    rows = []
+    for b, k, n in [(1024, 12.0, 25.0), (2048, 12.5, 25.1), (1 << 20, 36.0, 28.0), (1 << 24, 90.0, 97.0)]:
+        rows.append({"op": "all_reduce", "dtype": "bf16", "bytes": b, "algo": "kernel", "us": k})
+        rows.append({"op": "all_reduce", "dtype": "bf16", "bytes": b, "algo": "nccl", "us": n})
+    assert best_config(rows)[("all_reduce", "bf16", 1 << 20)]["algo"] == "nccl"
+    assert crossovers(rows)[("all_reduce", "bf16")] == [(1024, 2048, "kernel"), (1 << 20, 1 << 20, "nccl"), (1 << 24, 1 << 24, "kernel")]
+    hs = hint_sweep({"steps=8": [r for r in rows if r["algo"] == "kernel"],
+                     "steps=2": [dict(r, us=r["us"] * (0.5 if r["bytes"] > 4096 else 2)) for r in rows if r["algo"] == "kernel"]})
+    assert hs[("all_reduce", "bf16", 1 << 24)]["hints"] == "steps=2" and hs[("all_reduce", "bf16", 1024)]["hints"] == "steps=8"

@@ -334,12 +334,59 @@ __global__ void __launch_bounds__(kCeThreads) k_cross_entropy(__nv_bfloat16* __r
 
 // --------------------------------------------------------------- AdamW ------
 
-__global__ void k_adamw(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
-                        float* __restrict__ v, size_t n, float lr, float beta1, float beta2, float eps,
-                        float weight_decay, float bias1, float bias2, float grad_scale) {
+// sqrt and division as the hardware approximations (about 1 ulp): the IEEE
+// sequences cost several times the arithmetic of the rest of the update and
+// made this memory-bound kernel issue-bound.
+__device__ __forceinline__ float fast_sqrt(float x) {
+  float r;
+  asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+__device__ __forceinline__ float adamw_one(float p, float g, float& m, float& v, float lr, float beta1, float beta2,
+                                           float eps, float decay, float inv_bias1, float inv_bias2, float grad_scale) {
+  const float gr = g * grad_scale;
+  m = beta1 * m + (1.0f - beta1) * gr;
+  v = beta2 * v + (1.0f - beta2) * gr * gr;
+  const float denom = fast_sqrt(v * inv_bias2) + eps;
+  return p * decay - __fdividef(lr * (m * inv_bias1), denom);
+}
+
+__global__ void __launch_bounds__(256) k_adamw(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                                               float* __restrict__ v, size_t n, float lr, float beta1, float beta2,
+                                               float eps, float weight_decay, float bias1, float bias2, float grad_scale) {
   const size_t nvec = n / 4;
-  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+  const float inv_bias1 = 1.0f / bias1, inv_bias2 = 1.0f / bias2, decay = 1.0f - lr * weight_decay;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  // Two vectors per thread and step: eight 16-byte loads in flight.
+  for (; i + stride < nvec; i += 2 * stride) {
+    float4 pp[2], gg[2], mm[2], vv[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const size_t j = i + u * stride;
+      pp[u] = reinterpret_cast<float4*>(p)[j];
+      gg[u] = __ldcs(reinterpret_cast<const float4*>(g) + j);  // the gradient is not read again
+      mm[u] = reinterpret_cast<float4*>(m)[j];
+      vv[u] = reinterpret_cast<float4*>(v)[j];
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      float* pa = &pp[u].x;
+      const float* ga = &gg[u].x;
+      float* ma = &mm[u].x;
+      float* va = &vv[u].x;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        pa[k] = adamw_one(pa[k], ga[k], ma[k], va[k], lr, beta1, beta2, eps, decay, inv_bias1, inv_bias2, grad_scale);
+      }
+      const size_t j = i + u * stride;
+      reinterpret_cast<float4*>(p)[j] = pp[u];
+      reinterpret_cast<float4*>(m)[j] = mm[u];
+      reinterpret_cast<float4*>(v)[j] = vv[u];
+    }
+  }
+  for (; i < nvec; i += stride) {
     float4 pp = reinterpret_cast<float4*>(p)[i];
     const float4 gg = reinterpret_cast<const float4*>(g)[i];
     float4 mm = reinterpret_cast<float4*>(m)[i];
@@ -350,12 +397,7 @@ __global__ void k_adamw(float* __restrict__ p, const float* __restrict__ g, floa
     float* va = &vv.x;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      const float gr = ga[k] * grad_scale;
-      ma[k] = beta1 * ma[k] + (1.0f - beta1) * gr;
-      va[k] = beta2 * va[k] + (1.0f - beta2) * gr * gr;
-      const float mhat = ma[k] / bias1;
-      const float vhat = va[k] / bias2;
-      pa[k] = pa[k] * (1.0f - lr * weight_decay) - lr * mhat / (sqrtf(vhat) + eps);
+      pa[k] = adamw_one(pa[k], ga[k], ma[k], va[k], lr, beta1, beta2, eps, decay, inv_bias1, inv_bias2, grad_scale);
     }
     reinterpret_cast<float4*>(p)[i] = pp;
     reinterpret_cast<float4*>(m)[i] = mm;
@@ -363,11 +405,8 @@ __global__ void k_adamw(float* __restrict__ p, const float* __restrict__ g, floa
   }
   // tail
   if (blockIdx.x == 0) {
-    for (size_t i = nvec * 4 + threadIdx.x; i < n; i += blockDim.x) {
-      const float gr = g[i] * grad_scale;
-      m[i] = beta1 * m[i] + (1.0f - beta1) * gr;
-      v[i] = beta2 * v[i] + (1.0f - beta2) * gr * gr;
-      p[i] = p[i] * (1.0f - lr * weight_decay) - lr * (m[i] / bias1) / (sqrtf(v[i] / bias2) + eps);
+    for (size_t t = nvec * 4 + threadIdx.x; t < n; t += blockDim.x) {
+      p[t] = adamw_one(p[t], g[t], m[t], v[t], lr, beta1, beta2, eps, decay, inv_bias1, inv_bias2, grad_scale);
     }
   }
 }

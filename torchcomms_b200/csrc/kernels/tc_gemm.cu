@@ -11,7 +11,9 @@
 #include "tc_gemm.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
+#include <string>
 
 #include "launch_count.h"
 #include "tc_gemm.cuh"
@@ -110,6 +112,7 @@ struct TpMaps {
   CUtensorMap a_local;          // A rows that are in this rank's own buffer
   CUtensorMap a_full;           // A rows in the gathered buffer (all-gather mode)
   CUtensorMap b;
+  CUtensorMap b_half;           // box of 128 rows of B: what one CTA of a pair loads
   CUtensorMap out[kMaxRanks];   // [0]: y; reduce-scatter: one per owner's staging
 };
 
@@ -495,6 +498,340 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm(const __grid_
   }
 }
 
+// ------------------------------------- fused kernels on CTA pairs ----------
+//
+// Same protocol as k_tp_gemm, with the mainloop of the pair GEMM (clusters of
+// two CTAs, tcgen05 cta_group::2, 256 x 256 tile per pair, 6-stage ring of
+// 32 KB per CTA). A pair takes two consecutive 128-row m-tiles of ONE source
+// rank (the launcher requires m_local % 256 == 0), CTA r of the pair owns the
+// r-th of them: its A rows, its epilogue, its flags. Everything that concerns
+// peers - copy warps, arrival counters, partial-tile flags, the reduce phase,
+// the epoch and the closing barrier - stays per CTA exactly as above.
+
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = kBlockM * kBlockK * 2 + (kTpBN / 2) * kBlockK * 2;  // 16 KB of A + 16 KB of B
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 2 * kOutChunkBytes + 1024 + 256;
+
+template <TpMode MODE>
+__global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __grid_constant__ TpMaps maps, CommDev c, TpParams p) {
+  constexpr int BN = kTpBN;
+  constexpr int kAB = kBlockM * kBlockK * 2;
+  constexpr uint32_t idesc = make_idesc_bf16(2 * kBlockM, BN);
+  extern __shared__ char smem_raw[];
+  char* stages = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  char* obuf = stages + kPairStages * kPairStageBytes;
+  TpBarriers* bars = reinterpret_cast<TpBarriers*>(obuf + 2 * kOutChunkBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = static_cast<int>(cluster_ctarank());  // 0 leads
+  const bool leader = cta == 0;
+  const int G = gridDim.x;
+  const int cluster_id = blockIdx.x >> 1, nclusters = gridDim.x >> 1;
+  const int tiles_m = p.m_total / kBlockM, tiles_n = p.n / BN, tiles_per_src = p.m_local / kBlockM;
+  const int pair_tiles_m = tiles_m / 2;
+  const int total_tiles = pair_tiles_m * tiles_n;
+  const int k_iters = p.k / kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bars->acc_full[s], 1);
+      mbar_init(&bars->acc_empty[s], 8);  // four epilogue warps in each CTA of the pair
+    }
+    bars->failed = 0;
+    bars->is_last = 0;
+    bars->epoch = ld_acquire_gpu(&p.ctrl[0]);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(&bars->tmem_base, 2 * BN);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  const uint32_t epoch = bars->epoch;
+
+  // 128-row m-tile ordinal -> real m-tile (same order as k_tp_gemm).
+  auto mtile_of = [&](int ord) {
+    const int j = ord / tiles_per_src, w = ord % tiles_per_src;
+    const int src = MODE == TpMode::AG_GEMM ? (c.rank + j) % c.nranks : (c.rank + 1 + j) % c.nranks;
+    return src * tiles_per_src + w;
+  };
+  // Pair tile t -> this CTA's m-tile ordinal and the n-tile.
+  auto my_tile = [&](int t, int* ord, int* ni) {
+    const TileCoord tc_ = tile_at(t, pair_tiles_m, tiles_n, p.gm);
+    *ord = tc_.ord * 2 + cta;
+    *ni = tc_.ni;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer: own A rows, own half of the B tile
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = cluster_id; t < total_tiles && !bars->failed; t += nclusters) {
+        int ord, ni;
+        my_tile(t, &ord, &ni);
+        const int mi = mtile_of(ord);
+        const CUtensorMap* ma = &maps.a_local;
+        int a_row = mi * kBlockM;
+        if (MODE == TpMode::AG_GEMM) {
+          if (ord < tiles_per_src) {
+            a_row = (mi - c.rank * tiles_per_src) * kBlockM;
+          } else {
+            ma = &maps.a_full;
+            const uint32_t want = (epoch + 1) * static_cast<uint32_t>(G);
+            bool ok = false;
+            for (uint32_t spin = 0; spin < (1u << 23); ++spin) {
+              if (static_cast<int32_t>(ld_acquire_gpu(&p.ctrl[kCtrlTiles + ord]) - want) >= 0) {
+                ok = true;
+                break;
+              }
+              if ((spin & 1023u) == 1023u && comm_is_dead(c)) break;
+            }
+            if (!ok) {
+              bars->failed = 1;
+              break;
+            }
+            fence_proxy_async();
+          }
+        }
+        const int b_row = ni * BN + cta * (BN / 2);
+        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+          const int s = it % kPairStages;
+          const uint32_t ph = (it / kPairStages) & 1u;
+          if (!mbar_wait(&bars->empty[s], ph ^ 1u)) {
+            bars->failed = 1;
+            break;
+          }
+          if (leader) mbar_expect_tx(&bars->full[s], 2 * kPairStageBytes);  // all four loads of the stage
+          char* sa = stages + s * kPairStageBytes;
+          tma_load_2d_pair(sa, ma, &bars->full[s], kb * kBlockK, a_row);
+          tma_load_2d_pair(sa + kAB, &maps.b_half, &bars->full[s], kb * kBlockK, b_row);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader only)
+    if (leader && lane == 0) {
+      uint32_t it = 0, tile_iter = 0;
+      for (int t = cluster_id; t < total_tiles && !bars->failed; t += nclusters, ++tile_iter) {
+        const uint32_t as = tile_iter & 1u, aph = (tile_iter >> 1) & 1u;
+        if (!mbar_wait(&bars->acc_empty[as], aph ^ 1u)) {
+          bars->failed = 1;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + as * BN;
+        for (int kb = 0; kb < k_iters; ++kb, ++it) {
+          const int s = it % kPairStages;
+          const uint32_t ph = (it / kPairStages) & 1u;
+          if (!mbar_wait(&bars->full[s], ph)) {
+            bars->failed = 1;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(stages + s * kPairStageBytes);
+          const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + kAB);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            umma_bf16_pair(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
+          }
+          umma_commit_pair(&bars->empty[s], 3);
+        }
+        umma_commit_pair(&bars->acc_full[as], 3);
+      }
+    }
+  } else if (warp < 6) {
+    // ---------------- epilogue (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    const int row_in_tile = q * 32 + lane;
+    const bool issuer = warp == 2 && lane == 0;
+    uint32_t tile_iter = 0, chunk_iter = 0;
+    for (int t = cluster_id; t < total_tiles; t += nclusters, ++tile_iter) {
+      const uint32_t as = tile_iter & 1u, aph = (tile_iter >> 1) & 1u;
+      int ord, ni;
+      my_tile(t, &ord, &ni);
+      const int mi = mtile_of(ord);
+      if (!mbar_wait(&bars->acc_full[as], aph)) {
+        bars->failed = 1;
+        break;
+      }
+      tc_fence_after_sync();
+      const CUtensorMap* mo = &maps.out[0];
+      int out_row = mi * kBlockM;
+      int owner = 0;
+      if (MODE == TpMode::GEMM_RS) {
+        owner = mi / tiles_per_src;
+        mo = &maps.out[owner];
+        out_row = c.rank * p.m_local + (mi - owner * tiles_per_src) * kBlockM;
+      }
+      for (int j = 0; j < BN / kOutChunkCols; ++j, ++chunk_iter) {
+        char* buf = obuf + (chunk_iter & 1u) * kOutChunkBytes;
+        if (issuer) tma_store_wait_read<1>();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + as * BN + (static_cast<uint32_t>(q * 32) << 16) +
+                            static_cast<uint32_t>(j * kOutChunkCols + half * 32),
+                        r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int chunk16 = half * 4 + v;
+            uint4* dst = reinterpret_cast<uint4*>(buf + row_in_tile * 128 + ((chunk16 ^ (row_in_tile & 7)) << 4));
+            *dst = make_uint4(pack_bf16(r[8 * v], r[8 * v + 1]), pack_bf16(r[8 * v + 2], r[8 * v + 3]),
+                              pack_bf16(r[8 * v + 4], r[8 * v + 5]), pack_bf16(r[8 * v + 6], r[8 * v + 7]));
+          }
+        }
+        if (j == BN / kOutChunkCols - 1) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_leader(&bars->acc_empty[as]);
+        }
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (issuer) {
+          tma_store_2d(mo, buf, ni * BN + j * kOutChunkCols, out_row);
+          tma_store_commit();
+        }
+      }
+      if (MODE == TpMode::GEMM_RS && issuer) {
+        tma_store_wait_all<0>();
+        __threadfence_system();
+        const int tile_local = (mi - owner * tiles_per_src) * tiles_n + ni;
+        st_relaxed_sys(p.arrived[owner] + static_cast<size_t>(tile_local) * c.nranks + c.rank, epoch + 1);
+      }
+    }
+    if (issuer) tma_store_wait_all<0>();
+  } else {
+    // ---------------- copy warps (all-gather mode), every CTA of the grid takes a slice of every remote m-tile
+    if (MODE == TpMode::AG_GEMM) {
+      const int ct = threadIdx.x - kGemmThreads;
+      if (blockIdx.x == 0 && warp == 6) {
+        const bool ok = warp_rank_barrier(c, 0, 0xa1);
+        if (lane == 0) {
+          __threadfence();
+          atomicExch(&p.ctrl[2], ok ? epoch + 1 : 0xffffffffu);
+        }
+      }
+      if (ct == 0) {
+        bool started = false;
+        for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+          const uint32_t v = ld_acquire_gpu(&p.ctrl[2]);
+          if (v == epoch + 1) started = true;
+          if (started || v == 0xffffffffu) break;
+          if ((spin & 1023u) == 1023u && comm_is_dead(c)) break;
+        }
+        if (!started) bars->failed = 1;
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      const size_t tile_bytes = static_cast<size_t>(kBlockM) * p.k * 2;
+      const size_t slice = ((tile_bytes + G - 1) / G + 15) / 16 * 16;
+      const size_t b0 = static_cast<size_t>(blockIdx.x) * slice;
+      for (int ord = tiles_per_src; ord < tiles_m; ++ord) {
+        const int mi = mtile_of(ord);
+        const int src = mi / tiles_per_src;
+        const size_t src_off = static_cast<size_t>(mi - src * tiles_per_src) * tile_bytes;
+        if (b0 < tile_bytes) {
+          const size_t nbytes = tile_bytes - b0 < slice ? tile_bytes - b0 : slice;
+          const uint4* from = reinterpret_cast<const uint4*>(p.x_shards[src] + src_off + b0);
+          uint4* to = reinterpret_cast<uint4*>(p.x_full + static_cast<size_t>(mi) * tile_bytes + b0);
+          const size_t nvec = nbytes / 16;
+          size_t i = ct;
+          for (; i + 3 * kCopyThreads < nvec; i += 4 * kCopyThreads) {
+            const uint4 v0 = from[i], v1 = from[i + kCopyThreads], v2 = from[i + 2 * kCopyThreads], v3 = from[i + 3 * kCopyThreads];
+            to[i] = v0;
+            to[i + kCopyThreads] = v1;
+            to[i + 2 * kCopyThreads] = v2;
+            to[i + 3 * kCopyThreads] = v3;
+          }
+          for (; i < nvec; i += kCopyThreads) to[i] = from[i];
+          fence_proxy_async();
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (ct == 0) {
+          __threadfence();
+          atomicAdd(&p.ctrl[kCtrlTiles + ord], 1u);
+        }
+      }
+    }
+  }
+
+  // ---------------- reduce phase of the reduce-scatter (per CTA, as in k_tp_gemm)
+  tc_fence_before_sync();
+  __syncthreads();
+  if (MODE == TpMode::GEMM_RS) {
+    const int my_tiles = tiles_per_src * tiles_n;
+    const int nthreads = blockDim.x;
+    for (int rt = blockIdx.x; rt < my_tiles; rt += G) {
+      if (threadIdx.x == 0) bars->reduce_ok = 1;
+      __syncthreads();
+      if (threadIdx.x < c.nranks) {
+        const uint32_t* flag = p.arrived[c.rank] + static_cast<size_t>(rt) * c.nranks + threadIdx.x;
+        if (!wait_flag_reached(c, flag, epoch + 1, threadIdx.x, 0xa3)) bars->reduce_ok = 0;
+      }
+      __syncthreads();
+      if (!bars->reduce_ok) {
+        bars->failed = 1;
+        break;
+      }
+      const int wm = rt / tiles_n, ni = rt % tiles_n;
+      const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.partials_local);
+      for (int v = threadIdx.x; v < kBlockM * BN / 8; v += nthreads) {
+        const int r = v / (BN / 8), cv = v % (BN / 8);
+        const size_t off = (static_cast<size_t>(wm * kBlockM + r)) * p.n + ni * BN + cv * 8;
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+        for (int s = 0; s < c.nranks; ++s) {
+          const uint4 q4 = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(s) * p.m_local * p.n + off);
+          const uint32_t* pw = &q4.x;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[2 * i] += __uint_as_float(pw[i] << 16);
+            acc[2 * i + 1] += __uint_as_float(pw[i] & 0xffff0000u);
+          }
+        }
+        uint4 o;
+        uint32_t* po = &o.x;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) po[i] = pack_bf16(__float_as_uint(acc[2 * i]), __float_as_uint(acc[2 * i + 1]));
+        *reinterpret_cast<uint4*>(p.out + off) = o;
+      }
+      __syncthreads();
+    }
+  }
+
+  // ---------------- teardown
+  __syncthreads();
+  cluster_sync_all();  // the peer may still address this CTA's shared memory and barriers
+  if (warp == 1) {
+    tmem_dealloc_pair(tmem_base, 2 * BN);
+  }
+  if (threadIdx.x == 0) {
+    if (bars->failed) c.status[0] = c.status[0] | kStatusTimeout;
+    __threadfence();
+    const uint32_t ticket = atomicAdd(&p.ctrl[1], 1u);
+    bars->is_last = ticket == static_cast<uint32_t>(G - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (bars->is_last && warp == 0) {
+    __threadfence();
+    warp_rank_barrier(c, 1, 0xa2);
+    if (lane == 0) {
+      p.ctrl[1] = 0;
+      __threadfence();
+      atomicExch(&p.ctrl[0], epoch + 1);
+    }
+  }
+}
+
 // ------------------------------------------------------------ launchers ----
 
 int sm_count() {
@@ -504,14 +841,19 @@ int sm_count() {
   return std::max(1, sms);
 }
 
-// Largest group height <= 16 that divides the number of m-tiles of one
-// source, so that a group never mixes rows that arrive at different times;
-// awkward counts fall back to 16 (groups then straddle sources, still correct).
-int pick_group(int tiles_per_src) {
-  for (int g = std::min(16, tiles_per_src); g >= 4; --g) {
+// Group height (in tiles of `tile_rows` rows): the A rows of a group are
+// re-read by every wave that sweeps over n, so they should stay in L2 - at
+// most ~40 MB of A per group and at most `cap` tiles - and a group should not
+// mix rows that arrive at different times, so it divides the tiles of one
+// source rank where it can.
+int pick_group(int tiles_per_src, int tile_rows, int k, int cap) {
+  const size_t tile_bytes = static_cast<size_t>(tile_rows) * k * 2;
+  const int by_l2 = static_cast<int>(std::max<size_t>(1, (40u << 20) / std::max<size_t>(tile_bytes, 1)));
+  const int limit = std::max(1, std::min({cap, by_l2, tiles_per_src}));
+  for (int g = limit; g >= std::max(1, limit / 2); --g) {
     if (tiles_per_src % g == 0) return g;
   }
-  return tiles_per_src < 4 ? std::max(1, tiles_per_src) : 16;
+  return limit;  // awkward counts: groups straddle sources, still correct
 }
 
 template <TpMode MODE>
@@ -522,6 +864,43 @@ cudaError_t tp_launch(int grid, const TpMaps& maps, const CommDev& c, const TpPa
   k_tp_gemm<MODE><<<grid, tp_threads<MODE>(), kTpSmemBytes, stream>>>(maps, c, p);
   note_kernel_launch();
   return cudaGetLastError();
+}
+
+// Pair kernels: on unless B200COMMS_TP_PAIRS=0; need two 128-row tiles per source rank.
+bool use_pairs(int m_local) {
+  static const bool enabled = [] {
+    const char* v = std::getenv("B200COMMS_TP_PAIRS");
+    return v == nullptr || std::string(v) != "0";
+  }();
+  return enabled && m_local % (2 * kBlockM) == 0;
+}
+
+// `want_pairs` <= 0: as many pairs as the device holds at once.
+template <TpMode MODE>
+cudaError_t tp_launch_pair(int want_pairs, const TpMaps& maps, const CommDev& c, const TpParams& p, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(k_tp_gemm_pair<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(tp_threads<MODE>());
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(2);
+  int max_clusters = 0;
+  e = cudaOccupancyMaxActiveClusters(&max_clusters, k_tp_gemm_pair<MODE>, &cfg);
+  if (e != cudaSuccess) return e;
+  if (max_clusters < 1) return cudaErrorInvalidConfiguration;
+  const int clusters = want_pairs > 0 ? std::min(max_clusters, want_pairs) : max_clusters;
+  cfg.gridDim = dim3(2 * clusters);
+  e = cudaLaunchKernelEx(&cfg, k_tp_gemm_pair<MODE>, maps, c, p);
+  note_kernel_launch();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 } // namespace
@@ -538,6 +917,7 @@ cudaError_t launch_gemm_bf16_nt(const void* a, const void* b, void* c, int m, in
     return cudaErrorInvalidValue;
   }
   maps.a_full = maps.a_local;
+  maps.b_half = maps.b;
   for (int r = 1; r < kMaxRanks; ++r) maps.out[r] = maps.out[0];
   CommDev none{};
   none.nranks = 1;
@@ -548,7 +928,7 @@ cudaError_t launch_gemm_bf16_nt(const void* a, const void* b, void* c, int m, in
   p.n = n;
   p.k = k;
   const int tiles_m = (m + kBlockM - 1) / kBlockM, tiles_n = (n + kTpBN - 1) / kTpBN;
-  p.gm = std::min(16, tiles_m);
+  p.gm = pick_group(tiles_m, kBlockM, k, 16);
   return tp_launch<TpMode::PLAIN>(std::min(sm_count(), tiles_m * tiles_n), maps, none, p, stream);
 }
 
@@ -575,7 +955,13 @@ cudaError_t launch_allgather_gemm(const CommDev& comm, const AgGemmArgs& a, cuda
   p.m_local = a.m_local;
   p.n = a.n;
   p.k = a.k;
-  p.gm = pick_group(a.m_local / kBlockM);
+  if (use_pairs(a.m_local)) {
+    if (!make_map(&maps.b_half, a.w, a.n, a.k, kBlockM)) return cudaErrorInvalidValue;
+    p.gm = pick_group(a.m_local / (2 * kBlockM), 2 * kBlockM, a.k, 8);
+    return tp_launch_pair<TpMode::AG_GEMM>(0, maps, comm, p, stream);
+  }
+  maps.b_half = maps.b;
+  p.gm = pick_group(a.m_local / kBlockM, kBlockM, a.k, 16);
   // All CTAs take part in the copy, so the grid is the whole GPU even when
   // there are fewer tiles than SMs.
   return tp_launch<TpMode::AG_GEMM>(sm_count(), maps, comm, p, stream);
@@ -605,8 +991,14 @@ cudaError_t launch_gemm_reduce_scatter(const CommDev& comm, const GemmRsArgs& a,
   p.m_local = a.m / comm.nranks;
   p.n = a.n;
   p.k = a.k_local;
-  p.gm = pick_group(p.m_local / kBlockM);
   const int tiles = (a.m / kBlockM) * (a.n / kTpBN);
+  if (use_pairs(p.m_local)) {
+    if (!make_map(&maps.b_half, a.w, a.n, a.k_local, kBlockM)) return cudaErrorInvalidValue;
+    p.gm = pick_group(p.m_local / (2 * kBlockM), 2 * kBlockM, a.k_local, 8);
+    return tp_launch_pair<TpMode::GEMM_RS>(tiles / 2, maps, comm, p, stream);
+  }
+  maps.b_half = maps.b;
+  p.gm = pick_group(p.m_local / kBlockM, kBlockM, a.k_local, 16);
   return tp_launch<TpMode::GEMM_RS>(std::min(sm_count(), tiles), maps, comm, p, stream);
 }
 

@@ -284,7 +284,9 @@ cudaError_t launch_gemm_bf16_nt_pair(const void* a, const void* b, void* c, int 
   if (max_clusters < 1) return cudaErrorInvalidConfiguration;
   const int clusters = std::min(max_clusters, tiles_m * tiles_n);
   cfg.gridDim = dim3(2 * clusters);
-  const int gm = std::min(8, tiles_m);
+  // A rows of a group stay in L2 while the pairs sweep over n: at most 8 pair-tiles and ~40 MB.
+  const size_t a_tile_bytes = static_cast<size_t>(2 * kBlockM) * k * 2;
+  const int gm = std::max(1, std::min({8, tiles_m, static_cast<int>((40u << 20) / std::max<size_t>(a_tile_bytes, 1))}));
   e = cudaLaunchKernelEx(&cfg, k_gemm_pair, maps, m, n, k, gm, status);
   note_kernel_launch();
   return e != cudaSuccess ? e : cudaGetLastError();

@@ -1,0 +1,71 @@
+"""Offline tuning: turns sweep results into an algorithm table and cross-over sizes.
+
+    torchrun --nproc-per-node 8 benchmarks/collective_perf.py --algos kernel,nccl --json sweep.json
+    python -m torchcomms_b200.utils.tuning sweep.json
+
+``best_config(rows)`` maps ``(op, dtype, bytes)`` to the fastest arm;
+``crossovers(rows)`` compresses that into byte ranges per operation, the form
+in which the CUDA backend's ``route()`` table is written; ``hint_sweep`` helps
+comparing sweeps run with different ``--hints`` (chunking, grid size).
+
+Parity: comms/tuning (``comm_tuning`` sweep engine emitting {Key: Config} maps).
+"""
+from __future__ import annotations
+
+import json
+import sys
+from typing import Any, Dict, Iterable, List, Tuple
+
+Key = Tuple[str, str, int]
+
+
+def best_config(rows: Iterable[Dict[str, Any]]) -> Dict[Key, Dict[str, Any]]:
+    best: Dict[Key, Dict[str, Any]] = {}
+    for r in rows:
+        key = (r["op"], r.get("dtype", ""), int(r["bytes"]))
+        if key not in best or r["us"] < best[key]["us"]:
+            best[key] = {"algo": r["algo"], "us": r["us"]}
+    return best
+
+
+def crossovers(rows: Iterable[Dict[str, Any]]) -> Dict[Tuple[str, str], List[Tuple[int, int, str]]]:
+    """Per (op, dtype): maximal runs of consecutive sizes won by the same arm, as (first_bytes, last_bytes, algo)."""
+    best = best_config(rows)
+    out: Dict[Tuple[str, str], List[Tuple[int, int, str]]] = {}
+    for (op, dt, b) in sorted(best, key=lambda k: (k[0], k[1], k[2])):
+        algo = best[(op, dt, b)]["algo"]
+        runs = out.setdefault((op, dt), [])
+        if runs and runs[-1][2] == algo:
+            runs[-1] = (runs[-1][0], b, algo)
+        else:
+            runs.append((b, b, algo))
+    return out
+
+
+def hint_sweep(named_rows: Dict[str, Iterable[Dict[str, Any]]], arm: str = "kernel") -> Dict[Key, Dict[str, Any]]:
+    """Several sweeps of the same arm under different hints -> the best hint set per (op, dtype, bytes)."""
+    best: Dict[Key, Dict[str, Any]] = {}
+    for name, rows in named_rows.items():
+        for r in rows:
+            if r["algo"] not in (arm, "auto"):
+                continue
+            key = (r["op"], r.get("dtype", ""), int(r["bytes"]))
+            if key not in best or r["us"] < best[key]["us"]:
+                best[key] = {"hints": name, "us": r["us"]}
+    return best
+
+
+def main(argv: List[str]) -> int:
+    if len(argv) < 2:
+        print(__doc__)
+        return 2
+    rows: List[Dict[str, Any]] = []
+    for path in argv[1:]:
+        rows += json.load(open(path))
+    for (op, dt), runs in crossovers(rows).items():
+        print(f"{op} {dt}: " + ", ".join(f"[{a}..{b}] -> {algo}" for a, b, algo in runs))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main(sys.argv))
