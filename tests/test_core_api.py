@@ -297,3 +297,24 @@ def test_reconfigure_rejected_without_support():
     tc.register_backend("pyb2", _PyBackend)
     with pytest.raises(RuntimeError, match="does not support enable_reconfigure"):
         tc.new_comm("pyb2", torch.device("cpu"), name="r", enable_reconfigure=True)
+
+
+def test_cuda_work_state_machine_with_scripted_runtime():
+    """The watchdog's view of a stream-ordered work object, driven through a fake CUDA runtime (no GPU):
+    start event seen -> INPROGRESS, end event -> COMPLETED, no end event within the timeout -> TIMEDOUT,
+    a failing query -> ERROR; the work destroys its two events."""
+    from torchcomms_b200 import _comms
+
+    ok, not_ready, launch_failure = 0, 600, 719
+    seen, err, destroyed = _comms._scripted_work_polls([not_ready, ok], [not_ready, not_ready, ok], 1000, 10, 5)
+    assert seen == ["NOT_STARTED", "INPROGRESS", "INPROGRESS", "COMPLETED", "COMPLETED"] and err == "" and destroyed == 2
+    seen, err, _ = _comms._scripted_work_polls([ok], [not_ready], 50, 20, 6)
+    assert seen[0] == "INPROGRESS" and seen[-1] == "TIMEDOUT" and "50 ms" in err
+    assert seen.index("TIMEDOUT") == 3  # 60 ms after the start was seen
+    seen, err, _ = _comms._scripted_work_polls([ok], [not_ready, launch_failure], 1000, 10, 3)
+    assert seen == ["INPROGRESS", "ERROR", "ERROR"] and "end event" in err
+    seen, err, _ = _comms._scripted_work_polls([launch_failure], [not_ready], 1000, 10, 2)
+    assert seen == ["ERROR", "ERROR"] and "start event" in err
+    # a work that never starts (queued behind other work) does not time out
+    seen, _, _ = _comms._scripted_work_polls([not_ready], [not_ready], 10, 50, 4)
+    assert seen == ["NOT_STARTED"] * 4

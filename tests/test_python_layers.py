@@ -369,3 +369,36 @@ def test_tuning_crossovers():
     hs = hint_sweep({"steps=8": [r for r in rows if r["algo"] == "kernel"],
                      "steps=2": [dict(r, us=r["us"] * (0.5 if r["bytes"] > 4096 else 2)) for r in rows if r["algo"] == "kernel"]})
     assert hs[("all_reduce", "bf16", 1 << 24)]["hints"] == "steps=2" and hs[("all_reduce", "bf16", 1024)]["hints"] == "steps=8"
+
+
+def _data_parallel_worker(rank, world):
+    import torchcomms_b200 as tc
+    from torchcomms_b200.parallel.data import DataParallel
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="dp", timeout=timedelta(seconds=60))
+    torch.manual_seed(100 + rank)  # different initial weights: the wrapper broadcasts rank 0's
+    model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
+    dp = DataParallel(model, comm, bucket_mb=0.0003)  # tiny buckets -> several all-reduces
+    assert len(dp._buckets) > 1
+    torch.manual_seed(0)
+    ref = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
+    torch.manual_seed(100)
+    ref0 = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
+    for p, q in zip(model.parameters(), ref0.parameters()):
+        assert torch.equal(p, q)  # rank 0's weights everywhere
+    g = torch.Generator().manual_seed(7)
+    xs = [torch.randn(5, 8, generator=g) for _ in range(world)]
+    ys = [torch.randn(5, 4, generator=g) for _ in range(world)]
+    for step in range(2):
+        model.zero_grad()
+        ((dp(xs[rank]) - ys[rank]) ** 2).mean().backward()
+        dp.finish()
+        ref0.zero_grad()
+        sum(((ref0(x) - y) ** 2).mean() for x, y in zip(xs, ys)).div(world).backward()
+        for p, q in zip(model.parameters(), ref0.parameters()):
+            torch.testing.assert_close(p.grad, q.grad, rtol=1e-5, atol=1e-6)
+    comm.finalize()
+
+
+def test_data_parallel_bucketed_all_reduce():
+    run_ranks(_data_parallel_worker, 2, timeout=120)

@@ -269,7 +269,82 @@ class EmuWorld {
 
 } // namespace
 
+namespace {
+
+// Runtime seam with scripted event queries, for exercising the work state
+// machine and the watchdog's timeout rule on a machine without a GPU.
+class ScriptedCudaApi final : public CudaApi {
+ public:
+  ScriptedCudaApi(std::vector<int> start_script, std::vector<int> end_script)
+      : start_(std::move(start_script)), end_(std::move(end_script)) {}
+  cudaError_t eventCreate(cudaEvent_t* e, unsigned) override {
+    *e = reinterpret_cast<cudaEvent_t>(++next_handle_);
+    return cudaSuccess;
+  }
+  cudaError_t eventDestroy(cudaEvent_t) override {
+    ++destroyed;
+    return cudaSuccess;
+  }
+  cudaError_t eventRecord(cudaEvent_t, cudaStream_t) override { return cudaSuccess; }
+  cudaError_t eventQuery(cudaEvent_t e) override {
+    // handle 1 = start event, handle 2 = end event
+    auto& script = reinterpret_cast<uintptr_t>(e) == 1 ? start_ : end_;
+    size_t& pos = reinterpret_cast<uintptr_t>(e) == 1 ? start_pos_ : end_pos_;
+    if (script.empty()) return cudaErrorNotReady;
+    const int code = script[std::min(pos, script.size() - 1)];
+    ++pos;
+    return static_cast<cudaError_t>(code);
+  }
+  cudaError_t eventSynchronize(cudaEvent_t) override { return cudaSuccess; }
+  cudaError_t streamWaitEvent(cudaStream_t, cudaEvent_t) override { return cudaSuccess; }
+  cudaError_t streamIsCapturing(cudaStream_t, bool* capturing, unsigned long long* id) override {
+    *capturing = false;
+    *id = 0;
+    return cudaSuccess;
+  }
+  const char* errorString(cudaError_t e) override { return e == cudaSuccess ? "ok" : "scripted failure"; }
+  int destroyed = 0;
+
+ private:
+  std::vector<int> start_, end_;
+  size_t start_pos_ = 0, end_pos_ = 0;
+  uintptr_t next_handle_ = 0;
+};
+
+} // namespace
+
 void bind_cuda_backend(py::module_& m) {
+  // Test hook: drives one CudaWork through `polls` watchdog polls `step_ms` apart with scripted
+  // cudaEventQuery results (0 = success, 600 = not ready, anything else = an error) and returns the
+  // status after each poll, the error text and the number of events destroyed with the work.
+  m.def("_scripted_work_polls", [](std::vector<int> start_script, std::vector<int> end_script, int timeout_ms, int step_ms,
+                                   int polls) {
+    auto api = std::make_shared<ScriptedCudaApi>(std::move(start_script), std::move(end_script));
+    cudaEvent_t a = nullptr, b = nullptr;
+    api->eventCreate(&a, 0);
+    api->eventCreate(&b, 0);
+    std::vector<std::string> seen;
+    std::string err;
+    {
+      auto w = c10::make_intrusive<CudaWork>(api, a, b, false, 0, Millis(timeout_ms), std::vector<at::Tensor>{},
+                                            std::weak_ptr<CudaBackend>(), false);
+      auto now = std::chrono::steady_clock::now();
+      for (int i = 0; i < polls; ++i) {
+        w->poll(now);
+        switch (w->status()) {
+          case WorkStatus::NOT_STARTED: seen.emplace_back("NOT_STARTED"); break;
+          case WorkStatus::INPROGRESS: seen.emplace_back("INPROGRESS"); break;
+          case WorkStatus::COMPLETED: seen.emplace_back("COMPLETED"); break;
+          case WorkStatus::TIMEDOUT: seen.emplace_back("TIMEDOUT"); break;
+          case WorkStatus::ERROR: seen.emplace_back("ERROR"); break;
+        }
+        now += std::chrono::milliseconds(step_ms);
+      }
+      err = w->error();
+    }
+    return py::make_tuple(seen, err, api->destroyed);
+  });
+
   register_cuda_backends();
   register_lazy_backends();
   m.def("_lazy_pair_count", [](const std::shared_ptr<Backend>& b) { return lazy_pair_count(b); });

@@ -1,5 +1,6 @@
 """Parallelism strategies built on a communicator.
 
+* ``data``               - replicated data parallel: bucketed, overlapped gradient all-reduce
 * ``engine`` / ``fsdp``  - sharded data parallel (ZeRO-3 style) training engine
 * ``tensor``             - column / row parallel layers, sequence parallel, fused TP MLP
 * ``pipeline``           - 1F1B and GPipe schedules over send / recv
