@@ -1,5 +1,5 @@
-"""The CUDA backend end to end: one rank per GPU (as many as the box has, up
-to 4), and a single-rank communicator when there is only one GPU.
+"""The CUDA backend end to end: one rank per GPU (two by default, more with
+B200COMMS_TEST_WORLD), and a single-rank communicator when there is only one GPU.
 
 Per-operation matrix after the reference's integration tests
 (comms/torchcomms/tests/integration/py/AllReduceTest.py:22-110): synchronous,
@@ -204,7 +204,7 @@ def _battery(rank, world, backend_name="b200"):
 
 
 def _world_size():
-    return max(1, min(torch.cuda.device_count(), int(os.environ.get("B200COMMS_TEST_WORLD", "4"))))
+    return max(1, min(torch.cuda.device_count(), int(os.environ.get("B200COMMS_TEST_WORLD", "2"))))
 
 
 def test_cuda_backend_battery():

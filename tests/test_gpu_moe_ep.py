@@ -142,7 +142,7 @@ def _ep_worker(rank, world):
 
 
 def test_dispatch_combine_multi_gpu():
-    world = min(torch.cuda.device_count(), int(os.environ.get("B200COMMS_TEST_WORLD", "4")))
+    world = min(torch.cuda.device_count(), int(os.environ.get("B200COMMS_TEST_WORLD", "2")))
     if world < 2:
         pytest.skip("needs 2 GPUs")
     run_ranks(_ep_worker, world, timeout=150)

@@ -75,7 +75,7 @@ def _tp_worker(rank, world):
 
 
 def test_tp_layers_multi_gpu():
-    world = min(torch.cuda.device_count(), int(os.environ.get("B200COMMS_TEST_WORLD", "4")))
+    world = min(torch.cuda.device_count(), int(os.environ.get("B200COMMS_TEST_WORLD", "2")))
     if world < 2:
         pytest.skip("needs 2 GPUs")
     run_ranks(_tp_worker, world, timeout=150)

@@ -8,6 +8,7 @@
 #include <cstring>
 
 #include "../core/logging.hpp"
+#include "../kernels/fused_ops.h"
 
 namespace b200c {
 
@@ -842,6 +843,15 @@ WorkPtr CudaBackend::reduce(const at::Tensor& t, int root, const ReduceOp& op, b
   });
 }
 
+// A lone rank: gather / scatter / reduce over one member is a cast (and a
+// scale) of the input into the output. One pass of a plain kernel instead of
+// the staged pipeline. False = shape or alignment not covered, use the general path.
+static bool single_rank_kind(at::ScalarType t, int* kind) {
+  if (t == at::kFloat) { *kind = 0; return true; }
+  if (t == at::kBFloat16) { *kind = 1; return true; }
+  return false;
+}
+
 WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bool async_op, const OpOptions& o) {
   check_tensor(out, device_, "all_gather_single");
   check_tensor(in, device_, "all_gather_single");
@@ -850,6 +860,17 @@ WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bo
   TORCH_CHECK(cast || in.scalar_type() == out.scalar_type(),
               "all_gather_single: dtypes must match (or float32 input with bfloat16 output for the fused cast)");
   if (in.numel() == 0) return c10::make_intrusive<CompletedWork>();
+  {
+    int ik = 0, ok = 0;
+    if (size_ == 1 && single_rank_kind(in.scalar_type(), &ik) && single_rank_kind(out.scalar_type(), &ok) &&
+        reinterpret_cast<uintptr_t>(in.data_ptr()) % 32 == 0 && reinterpret_cast<uintptr_t>(out.data_ptr()) % 32 == 0) {
+      at::Tensor i = in, ot = out;
+      bytes_issued_ += in.nbytes();
+      return run("all_gather/single_rank", async_op, o, {in}, [i, ot, ik, ok](cudaStream_t s) {
+        B200C_CUDA_CHECK(launch_cast_scale(i.data_ptr(), ik, ot.data_ptr(), ok, static_cast<size_t>(i.numel()), 1.0f, s));
+      });
+    }
+  }
   if (!cast && nccl_comm_ != nullptr && route(Coll::ALL_GATHER, out.nbytes(), o) == Algo::NCCL) {
     NcclDataType dt;
     if (to_nccl_dtype(in.scalar_type(), &dt)) {
@@ -976,6 +997,20 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
   check_tensor(in, device_, "reduce_scatter_single");
   TORCH_CHECK(in.numel() == out.numel() * size_, "reduce_scatter_single: input numel must be output numel * size");
   if (out.numel() == 0) return c10::make_intrusive<CompletedWork>();
+  {
+    int ik = 0, ok = 0;
+    const bool sum_like = op.type() == RedOpType::SUM || op.type() == RedOpType::AVG || op.type() == RedOpType::PREMUL_SUM ||
+        op.type() == RedOpType::MIN || op.type() == RedOpType::MAX || op.type() == RedOpType::PRODUCT;
+    if (size_ == 1 && sum_like && single_rank_kind(in.scalar_type(), &ik) && single_rank_kind(out.scalar_type(), &ok) &&
+        reinterpret_cast<uintptr_t>(in.data_ptr()) % 32 == 0 && reinterpret_cast<uintptr_t>(out.data_ptr()) % 32 == 0) {
+      at::Tensor i = in, ot = out;
+      const float scale = op.type() == RedOpType::PREMUL_SUM ? static_cast<float>(op.factor_as_double()) : 1.0f;
+      bytes_issued_ += in.nbytes();
+      return run("reduce_scatter/single_rank", async_op, o, {in}, [i, ot, ik, ok, scale](cudaStream_t s) {
+        B200C_CUDA_CHECK(launch_cast_scale(i.data_ptr(), ik, ot.data_ptr(), ok, static_cast<size_t>(ot.numel()), scale, s));
+      });
+    }
+  }
   const bool same = in.scalar_type() == out.scalar_type();
   const bool plain = same && o.hints.find("wire_dtype") == o.hints.end();
   Algo algo = plain ? route(Coll::REDUCE_SCATTER, in.nbytes(), o) : algo_override(o);

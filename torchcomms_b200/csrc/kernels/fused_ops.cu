@@ -332,6 +332,44 @@ __global__ void __launch_bounds__(kCeThreads) k_cross_entropy(__nv_bfloat16* __r
   }
 }
 
+// ------------------------------------------------------------ cast copy -----
+
+template <typename In, typename Out>
+__global__ void __launch_bounds__(256) k_cast_scale(const In* __restrict__ in, Out* __restrict__ out, size_t n, float scale) {
+  // 8 elements per thread and step, two steps in flight.
+  const size_t nvec = n / 8;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec; v += stride) {
+    float f[8];
+    if constexpr (sizeof(In) == 4) {
+      const float4 a = __ldcs(reinterpret_cast<const float4*>(in) + 2 * v);
+      const float4 b = __ldcs(reinterpret_cast<const float4*>(in) + 2 * v + 1);
+      f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+      f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+      unpack8(__ldcs(reinterpret_cast<const uint4*>(in) + v), f);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] *= scale;
+    if constexpr (sizeof(Out) == 4) {
+      reinterpret_cast<float4*>(out)[2 * v] = make_float4(f[0], f[1], f[2], f[3]);
+      reinterpret_cast<float4*>(out)[2 * v + 1] = make_float4(f[4], f[5], f[6], f[7]);
+    } else {
+      reinterpret_cast<uint4*>(out)[v] = pack8(f);
+    }
+  }
+  if (blockIdx.x == 0) {
+    for (size_t i = nvec * 8 + threadIdx.x; i < n; i += blockDim.x) {
+      float x;
+      if constexpr (sizeof(In) == 4) x = reinterpret_cast<const float*>(in)[i];
+      else x = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(in)[i]);
+      x *= scale;
+      if constexpr (sizeof(Out) == 4) reinterpret_cast<float*>(out)[i] = x;
+      else reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(x);
+    }
+  }
+}
+
 // --------------------------------------------------------------- AdamW ------
 
 // sqrt and division as the hardware approximations (about 1 ulp): the IEEE
@@ -440,6 +478,22 @@ cudaError_t launch_rmsnorm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, 
   if (nblocks) *nblocks = blocks;
   if (dw_partial == nullptr) return cudaSuccess;
   k_rmsnorm_bwd<<<blocks, kNormThreads, 0, s>>>(dy, x, w, rstd, dx, dw_partial, rows, cols);
+  note_kernel_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_cast_scale(const void* in, int in_kind, void* out, int out_kind, size_t n, float scale, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  const size_t in_bytes = in_kind == 0 ? 4 : 2, out_bytes = out_kind == 0 ? 4 : 2;
+  // Vector accesses of 8 elements: 32-byte (fp32) or 16-byte (bf16) alignment of the bases.
+  if ((reinterpret_cast<uintptr_t>(in) % (8 * in_bytes)) != 0 || (reinterpret_cast<uintptr_t>(out) % (8 * out_bytes)) != 0) {
+    return cudaErrorInvalidValue;
+  }
+  const int grid = grid_for(n / 8 + 1, 256);
+  if (in_kind == 0 && out_kind == 0) k_cast_scale<float, float><<<grid, 256, 0, s>>>(static_cast<const float*>(in), static_cast<float*>(out), n, scale);
+  else if (in_kind == 0 && out_kind == 1) k_cast_scale<float, __nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const float*>(in), static_cast<__nv_bfloat16*>(out), n, scale);
+  else if (in_kind == 1 && out_kind == 0) k_cast_scale<__nv_bfloat16, float><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(in), static_cast<float*>(out), n, scale);
+  else k_cast_scale<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), n, scale);
   note_kernel_launch();
   return cudaGetLastError();
 }

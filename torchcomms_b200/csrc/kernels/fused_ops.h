@@ -23,6 +23,10 @@ cudaError_t launch_rmsnorm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* x, 
 // out[c] = sum_r in[r, c]  (fp32 in, bf16 or fp32 out)
 cudaError_t launch_colsum_bf16(const float* in, __nv_bfloat16* out, int rows, int cols, cudaStream_t s);
 
+// out[i] = convert(in[i] * scale) for n elements; `in_kind` / `out_kind`: 0 = fp32, 1 = bf16.
+// What a collective degenerates to on a single rank (cast, scale, copy) in one pass.
+cudaError_t launch_cast_scale(const void* in, int in_kind, void* out, int out_kind, size_t n, float scale, cudaStream_t s);
+
 // Rotary embedding in place on [tokens, heads, head_dim] with interleaved
 // pairs; pos[t] indexes the cos/sin tables [max_pos, head_dim/2]. `inverse`
 // rotates by the negative angle (the backward pass).
