@@ -22,6 +22,42 @@ constexpr int kBlockK = 64;                 // 64 bf16 = 128 bytes = one swizzle
 constexpr int kUmmaK = 16;                  // K of one tcgen05.mma for 16-bit inputs
 constexpr uint32_t kWaitSpins = 1u << 22;   // try_wait polls before giving up
 
+
+// ------------------------------------------------------- tensor maps ------
+// Host side: row-major bf16 matrix [rows, cols] as a 2-D tiled tensor map
+// with a box of [box_rows, 64 columns] and the 128-byte swizzle (the layout
+// the shared-memory descriptors above expect). The driver entry point is
+// looked up at run time; the extension does not link against libcuda.
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      return reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return nullptr;
+  }();
+  return fn;
+}
+
+inline bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 #ifdef __CUDACC__
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -207,6 +243,11 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mas
                    smem_u32(bar)),
                "h"(cta_mask)
                : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(uint32_t a, uint32_t b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(a), __uint_as_float(b));
+  return *reinterpret_cast<uint32_t*>(&h);
 }
 
 // ------------------------------------------------------------- descriptors --

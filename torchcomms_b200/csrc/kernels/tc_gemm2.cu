@@ -17,7 +17,6 @@
 #include "tc_gemm.h"
 
 #include <algorithm>
-#include <mutex>
 
 #include "launch_count.h"
 #include "tc_gemm.cuh"
@@ -52,41 +51,6 @@ struct PairMaps {
   CUtensorMap b;    // box 128 rows x 64 columns (half of the 256-row B tile)
   CUtensorMap out;  // box 128 rows x 64 columns
 };
-
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, []() {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess) {
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-    }
-  });
-  return fn;
-}
-
-bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * 2};
-  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), static_cast<cuuint32_t>(kBlockM)};
-  const cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(uint32_t a, uint32_t b) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(a), __uint_as_float(b));
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 // Pair-tile `t` of the schedule: groups of `gm` 256-row tiles, n-major inside a group.
 __device__ __forceinline__ void pair_tile_at(int t, int tiles_m, int tiles_n, int gm, int* pm, int* pn) {
@@ -261,7 +225,7 @@ cudaError_t launch_gemm_bf16_nt_pair(const void* a, const void* b, void* c, int 
     return cudaErrorInvalidValue;
   }
   PairMaps maps;
-  if (!make_map(&maps.a, a, m, k) || !make_map(&maps.b, b, n, k) || !make_map(&maps.out, c, m, n)) return cudaErrorInvalidValue;
+  if (!make_map(&maps.a, a, m, k, kBlockM) || !make_map(&maps.b, b, n, k, kBlockM) || !make_map(&maps.out, c, m, n, kBlockM)) return cudaErrorInvalidValue;
   cudaError_t e = cudaFuncSetAttribute(k_gemm_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
   if (e != cudaSuccess) return e;
   const int tiles_m = (m + 2 * kBlockM - 1) / (2 * kBlockM), tiles_n = (n + kBN - 1) / kBN;
