@@ -664,11 +664,13 @@ Algo CudaBackend::algo_override(const OpOptions& o) const {
   return tune_.force;
 }
 
-// Cross-over sizes measured on 8 B200 over NVSwitch (bf16 and fp32 sweeps,
-// 1 KB - 1 GB, device-timed): the peer-memory kernels win for latency-bound
-// all-reduce (one barrier, one-shot) and for 8 - 64 MB (NVLS two-shot with
-// large chunks), and around 4 - 8 MB for all-gather; NCCL's protocols win the
-// rest, and everything below 4 ranks. algo=kernel forces the kernels.
+// Cross-over sizes measured on 8 B200 over NVSwitch (bf16 sweep, 1 KB - 1 GB,
+// device-timed, kernels against NCCL 2.28 on the same buffers): the
+// peer-memory kernels win the latency-bound sizes (one barrier, one-shot:
+// all-reduce up to 512 KB, all-gather up to 256 KB, reduce-scatter up to
+// 8 KB) and the all-reduce between 4 and 64 MB (NVLS two-shot with 64 KB
+// chunks); NCCL's protocols win the rest, all-to-all, and everything below
+// 4 ranks. algo=kernel forces the kernels.
 Algo CudaBackend::route(Coll c, size_t bytes, const OpOptions& o) const {
   const Algo a = algo_override(o);
   if (a == Algo::KERNEL) return Algo::AUTO;
@@ -678,11 +680,11 @@ Algo CudaBackend::route(Coll c, size_t bytes, const OpOptions& o) const {
   constexpr size_t KB = 1024, MB = 1024 * 1024;
   switch (c) {
     case Coll::ALL_REDUCE:
-      return (bytes <= 512 * KB || (bytes >= 8 * MB && bytes <= 64 * MB)) ? Algo::AUTO : Algo::NCCL;
+      return (bytes <= 512 * KB || (bytes >= 4 * MB && bytes <= 64 * MB)) ? Algo::AUTO : Algo::NCCL;
     case Coll::ALL_GATHER:   // bytes = gathered size
-      return (bytes >= 4 * MB && bytes <= 8 * MB) ? Algo::AUTO : Algo::NCCL;
+      return (bytes <= 256 * KB || (bytes >= 4 * MB && bytes < 8 * MB)) ? Algo::AUTO : Algo::NCCL;
     case Coll::REDUCE_SCATTER:   // bytes = input size
-      return Algo::NCCL;
+      return bytes <= 8 * KB ? Algo::AUTO : Algo::NCCL;
     case Coll::ALL_TO_ALL:
       return Algo::NCCL;
   }
