@@ -318,3 +318,33 @@ def test_cuda_work_state_machine_with_scripted_runtime():
     # a work that never starts (queued behind other work) does not time out
     seen, _, _ = _comms._scripted_work_polls([not_ready], [not_ready], 10, 50, 4)
     assert seen == ["NOT_STARTED"] * 4
+
+
+def test_dynamic_backend_loaded_from_shared_library(tmp_path, monkeypatch):
+    """An out-of-tree backend: compiled here into its own .so, found through the environment, loaded with
+    dlopen, checked against the ABI string, and driven through the ordinary communicator API."""
+    import os
+    import subprocess
+    import sysconfig
+
+    from torch.utils.cpp_extension import include_paths
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pkg = os.path.join(root, "torchcomms_b200")
+    lib = tmp_path / "libsample_backend.so"
+    cmd = ["/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++", "-shared", "-fPIC", "-std=c++17", "-O1",
+           "-D_GLIBCXX_USE_CXX11_ABI=1", "-I", os.path.join(pkg, "csrc")]
+    for inc in include_paths(device_type="cuda") + [sysconfig.get_paths()["include"], "/usr/local/cuda/include"]:
+        cmd += ["-isystem", inc]
+    cmd += [os.path.join(root, "tests", "data", "sample_backend.cpp"), "-o", str(lib), "-L", pkg, "-l:_comms.so",
+            f"-Wl,-rpath,{pkg}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-2000:]
+    monkeypatch.setenv("TORCHCOMMS_BACKEND_LIB_PATH_SAMPLE", str(lib))
+    c = tc.new_comm("sample", torch.device("cpu"), name="dyn")
+    assert c.get_backend() == "sample" and c.get_size() == 1
+    t = torch.zeros(3)
+    c.all_reduce(t, tc.ReduceOp.SUM, False)
+    assert torch.equal(t, torch.ones(3))  # the library's override ran
+    c.barrier(False)
+    c.finalize()

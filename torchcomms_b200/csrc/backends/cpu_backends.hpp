@@ -17,7 +17,7 @@ namespace b200c {
 // A backend that moves no data. Rank and size default to 0 of 1 and can be
 // overridden with hints {"fake_rank", "fake_size"}. Every call is appended to
 // `calls` so tests can assert on what the facade forwarded.
-class FakeBackend : public Backend {
+class B200C_API FakeBackend : public Backend {
  public:
   void init(at::Device device, const std::string& name, const CommOptions& opts) override;
   void finalize() override;

@@ -21,7 +21,7 @@ constexpr const char* kBackendAbiVersion = "b200c-1";
 
 class Backend;
 
-class Window : public std::enable_shared_from_this<Window> {
+class B200C_API Window : public std::enable_shared_from_this<Window> {
  public:
   virtual ~Window() = default;
 
@@ -69,7 +69,7 @@ struct AllGatherPHandle {
   bool freed = false;
 };
 
-class Backend : public std::enable_shared_from_this<Backend> {
+class B200C_API Backend : public std::enable_shared_from_this<Backend> {
  public:
   virtual ~Backend() = default;
 

@@ -111,7 +111,7 @@ class Comm : public std::enable_shared_from_this<Comm> {
 };
 
 // Process-wide registry of backend constructors.
-class Factory {
+class B200C_API Factory {
  public:
   using Maker = std::function<std::shared_ptr<Backend>()>;
   static Factory& get();
@@ -136,7 +136,7 @@ std::shared_ptr<Comm> new_comm(const std::string& backend, at::Device device,
 
 // Process-wide health flag: flips to unhealthy once any watchdog saw a
 // timeout or an asynchronous error.
-class HealthCheck {
+class B200C_API HealthCheck {
  public:
   static void mark_unhealthy(const std::string& why);
   static bool healthy();

@@ -70,7 +70,7 @@ struct OpOptions {
   bool timeout_set = false; // false: inherit the communicator's timeout
 };
 
-struct CommOptions {
+struct B200C_API CommOptions {
   CommOptions();
   bool abort_process_on_timeout_or_error;
   Millis timeout;

@@ -5,6 +5,10 @@
 // (the operation-name enum).
 #pragma once
 
+// The extension is built with hidden visibility; what an out-of-tree backend
+// library derives from or calls is exported explicitly.
+#define B200C_API __attribute__((visibility("default")))
+
 #include <ATen/ATen.h>
 #include <chrono>
 #include <cstdint>
@@ -42,7 +46,7 @@ const char* red_op_name(RedOpType t);
 
 // A reduction operator. PREMUL_SUM carries its factor either as a host double
 // or as a one-element tensor living on the communicator's device.
-class ReduceOp {
+class B200C_API ReduceOp {
  public:
   using Factor = std::variant<double, at::Tensor>;
 

@@ -20,7 +20,7 @@
 
 namespace b200c {
 
-class Work : public c10::intrusive_ptr_target {
+class B200C_API Work : public c10::intrusive_ptr_target {
  public:
   using Hook = std::function<void()>;
 
@@ -73,7 +73,7 @@ class Work : public c10::intrusive_ptr_target {
 using WorkPtr = c10::intrusive_ptr<Work>;
 
 // A handle for an operation that already finished on the host.
-class CompletedWork final : public Work {
+class B200C_API CompletedWork final : public Work {
  public:
   CompletedWork() { set_status(WorkStatus::COMPLETED); }
 
@@ -82,7 +82,7 @@ class CompletedWork final : public Work {
 };
 
 // Runs a callable on a helper thread; used by CPU backends for async_op=True.
-class ThreadWork final : public Work {
+class B200C_API ThreadWork final : public Work {
  public:
   explicit ThreadWork(std::function<void()> fn, Millis timeout);
   ~ThreadWork() override;
