@@ -246,6 +246,21 @@ class GlooWork final : public Work {
   bool done_ = false;
 };
 
+// A gloo process group whose collective is stuck on a dead or absent peer
+// cannot be cancelled, and its destructor waits for that collective. After a
+// failure or an abort the group is therefore parked here and never destroyed:
+// its threads and sockets live until the process ends, and nothing waits for
+// them.
+static void retire_process_group(c10::intrusive_ptr<c10d::Backend>& pg) {
+  static auto* parked = new std::vector<c10::intrusive_ptr<c10d::Backend>>();
+  static std::mutex mu;
+  if (pg) {
+    std::lock_guard<std::mutex> g(mu);
+    parked->push_back(std::move(pg));
+  }
+  pg.reset();
+}
+
 GlooBackend::~GlooBackend() {
   if (pg_ && !finalized_) {
     B200C_LOG(WARN, name_, "gloo communicator destroyed without finalize()");
@@ -285,8 +300,8 @@ void GlooBackend::init(at::Device device, const std::string& name, const CommOpt
 
 void GlooBackend::ensure_ready() const {
   TORCH_CHECK(!finalized_, "gloo communicator '", name_, "' was finalized");
-  TORCH_CHECK(pg_, "gloo communicator '", name_, "' is not initialised (reconfigure() pending?)");
   TORCH_CHECK(!aborted_, "gloo communicator '", name_, "' was aborted");
+  TORCH_CHECK(pg_, "gloo communicator '", name_, "' is not initialised (reconfigure() pending?)");
 }
 
 void GlooBackend::finalize() {
@@ -305,6 +320,7 @@ void GlooBackend::on_failure(const std::string& what, bool timed_out) {
     std::abort();
   }
   aborted_ = true;
+  retire_process_group(pg_);
 }
 
 void GlooBackend::abort() {
@@ -312,6 +328,7 @@ void GlooBackend::abort() {
   if (pg_) {
     pg_->abort();
   }
+  retire_process_group(pg_);
   run_abort_hooks();
 }
 

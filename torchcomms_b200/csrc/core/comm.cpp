@@ -88,7 +88,8 @@ size_t Comm::next_op_id() {
 
 Comm::Comm(std::shared_ptr<Backend> impl, std::vector<int> global_ranks)
     : impl_(std::move(impl)), ranks_(std::move(global_ranks)) {
-  if (ranks_.empty()) {
+  // A communicator created for reconfigure() has no membership yet (size < 1).
+  if (ranks_.empty() && impl_->size() > 0) {
     ranks_.resize(impl_->size());
     for (int i = 0; i < impl_->size(); ++i) {
       ranks_[i] = i;

@@ -42,6 +42,25 @@ py::object to_python_post_args(const OpRecord& rec) {
   return post_converter()(py::cast(rec));
 }
 
+// The last reference to a communicator usually dies inside Python (object
+// deallocation, GIL held). Tearing a backend down can join transport threads
+// that themselves need the GIL for a moment (hook callables, work callbacks),
+// so the C++ object is released with the GIL dropped.
+static std::shared_ptr<Comm> gil_free_on_release(std::shared_ptr<Comm> inner) {
+  if (!inner) return inner;
+  Comm* raw = inner.get();
+  return std::shared_ptr<Comm>(raw, [inner](Comm*) mutable {
+    if (interpreter_dying()) {
+      inner.reset();
+    } else if (PyGILState_Check()) {
+      py::gil_scoped_release nogil;
+      inner.reset();
+    } else {
+      inner.reset();
+    }
+  });
+}
+
 void bind_core(py::module_& m) {
   m.attr("BACKEND_ABI_VERSION") = kBackendAbiVersion;
 
@@ -352,7 +371,7 @@ void bind_core(py::module_& m) {
         if (to) {
           o.timeout = *to;
         }
-        return c.split(ranks, name, o);
+        return gil_free_on_release(c.split(ranks, name, o));
       }, py::arg("ranks"), py::arg("name"), py::arg("hints") = py::none(), py::arg("timeout") = py::none(), Release())
       .def("batch_op_create", &Comm::batch_op_create)
       .def("new_window", [](Comm& c, std::optional<at::Tensor> t) { return c.new_window(t); },
@@ -399,7 +418,7 @@ void bind_core(py::module_& m) {
       .def("__deepcopy__", [](std::shared_ptr<Comm> c, py::dict) { return c; }, py::arg("memo"));
 
   m.def("_new_comm", [](const std::string& backend, at::Device device, const std::string& name, const CommOptions& opts) {
-    return new_comm(backend, device, name, opts);
+    return gil_free_on_release(new_comm(backend, device, name, opts));
   }, py::arg("backend"), py::arg("device"), py::arg("name"), py::arg("options"), Release());
 
   m.def("_is_backend_registered", [](const std::string& n) { return Factory::get().is_registered(n); });
