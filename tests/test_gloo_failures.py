@@ -6,6 +6,7 @@ Modelled on comms/torchcomms/tests/integration/py/TimeoutTest.py:24-90,
 AbortTest.py and ReconfigureTest.py (which re-execute themselves in
 sub-processes; here every rank already is a child process).
 """
+import os
 import time
 from datetime import timedelta
 
@@ -13,6 +14,14 @@ import pytest
 import torch
 
 from tests.mp_util import run_ranks
+
+
+def _leave():
+    import sys
+
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 def _late_rank_worker(rank, world):
@@ -39,9 +48,11 @@ def _late_rank_worker(rank, world):
         # the communicator refuses further work instead of hanging on a half-broken group
         with pytest.raises(RuntimeError):
             comm.all_reduce(torch.ones(4), tc.ReduceOp.SUM, False)
-    # A failed communicator is not finalized; abort() releases whatever the transport still holds so
-    # that the process can exit.
+    # A failed communicator is not finalized. Its transport threads may still sit in the collective
+    # that never completed and cannot be cancelled, so the rank ends the way a trainer would after a
+    # fatal communication error: abort, then leave without running static destructors under them.
     comm.abort()
+    _leave()
 
 
 def test_late_rank_times_out_without_hanging():
@@ -55,12 +66,13 @@ def _async_timeout_worker(rank, world):
                        abort_process_on_timeout_or_error=False)
     if rank == 0:
         time.sleep(5.0)
-        return
+        _leave()
     w = comm.all_reduce(torch.ones(2), tc.ReduceOp.SUM, True, timeout=timedelta(seconds=1))
     with pytest.raises(RuntimeError):
         w.wait()
     assert w.status() in (tc.WorkStatus.TIMEDOUT, tc.WorkStatus.ERROR)
     comm.abort()
+    _leave()
 
 
 def test_async_work_reports_timeout():
@@ -74,7 +86,7 @@ def _elastic_worker(rank, world):
 
     import torchcomms_b200 as tc
 
-    store = dist.TCPStore("127.0.0.1", int(__import__("os").environ["MASTER_PORT"]) + 1, world, rank == 0,
+    store = dist.TCPStore("127.0.0.1", int(os.environ["MASTER_PORT"]) + 1, world, rank == 0,
                           timeout=timedelta(seconds=60))
     comm = tc.new_comm("gloo", torch.device("cpu"), name="elastic", store=store, enable_reconfigure=True,
                        timeout=timedelta(seconds=30), abort_process_on_timeout_or_error=False)
