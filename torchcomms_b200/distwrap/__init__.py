@@ -146,6 +146,20 @@ def init_process_group(backend: Optional[str] = None, init_method: Optional[str]
     _enabled = True
 
 
+def _forget_group(pg: Any) -> None:
+    """Removes one of our groups from torch.distributed's world tables (other groups stay untouched)."""
+    from torch.distributed import distributed_c10d as c10d
+
+    world = c10d._world
+    tag = world.pg_to_tag.pop(pg, None)
+    if tag is not None and pg in world.tags_to_pg.get(tag, []):
+        world.tags_to_pg[tag].remove(pg)
+    for table in (world.pg_map, world.pg_names, world.pg_group_ranks, world.pg_backend_config):
+        table.pop(pg, None)
+    if GroupMember.WORLD is pg:
+        GroupMember.WORLD = None
+
+
 def destroy_process_group(group: Any = None) -> None:
     global _enabled
     if not _enabled:
@@ -161,15 +175,9 @@ def destroy_process_group(group: Any = None) -> None:
                 comm.finalize()
             except RuntimeError:
                 pass
+        _forget_group(pg)
     if not _REGISTRY:
         _enabled = False
-        from torch.distributed import distributed_c10d as c10d
-
-        for table in (c10d._world.pg_map, c10d._world.pg_names, c10d._world.pg_group_ranks, c10d._world.pg_backend_config,
-                      c10d._world.pg_to_tag):
-            table.clear()
-        c10d._world.tags_to_pg.clear()
-        GroupMember.WORLD = None
 
 
 def new_group(*args: Any, **kwargs: Any) -> Any:
