@@ -15,10 +15,13 @@ rows over NVLink and the tile scheduler follows their arrival order; in
 ``GemmReduceScatter`` the epilogue stores bf16 partial tiles into the owning
 rank's staging and the owner sums them in fp32 as flags arrive.
 
-The reference has no fused compute+collective layer; its closest pieces are
-the device-side transport primitives under ``comms/pipes`` and the
-tensor-parallel collectives used by its benchmarks
-(``comms/torchcomms/scripts``).  ``comm=None`` builds a single-rank layer on
+The reference has no counterpart: its tree contains no GEMM and no fused
+compute+collective kernel; tensor parallelism is exercised there through
+DTensor over NCCL all-gather / reduce-scatter plus cuBLAS
+(comms/torchcomms/tests/integration/py/TPCommTest.py:71), which is the
+baseline arm of ``benchmarks/tp_layer_perf.py``.  When the token shard is a
+multiple of 256 rows the kernels run on CTA pairs (tcgen05 ``cta_group::2``).
+``comm=None`` builds a single-rank layer on
 the current device (no peers; tests and profiling).
 """
 from __future__ import annotations
