@@ -458,4 +458,5 @@ PYBIND11_MODULE(_comms, m) {
   b200c::bind_ops(m);
   b200c::bind_ep(m);
   b200c::bind_tp(m);
+  b200c::bind_transport(m);
 }
