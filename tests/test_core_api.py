@@ -348,3 +348,31 @@ def test_dynamic_backend_loaded_from_shared_library(tmp_path, monkeypatch):
     assert torch.equal(t, torch.ones(3))  # the library's override ran
     c.barrier(False)
     c.finalize()
+
+
+def test_configuration_tiers_env_over_file_over_default(tmp_path, monkeypatch):
+    """Environment > configuration file > built-in default (comms/utils/cvars/README.md:10-19)."""
+    import torchcomms_b200 as tc
+
+    conf = tmp_path / "b200comms.conf"
+    conf.write_text("# site defaults\nTORCHCOMM_TIMEOUT_SECONDS = 7   # seconds\nTORCHCOMM_ABORT_ON_ERROR=0\nnot a setting\n")
+    monkeypatch.setenv("B200COMMS_CONF_FILE", str(conf))
+    monkeypatch.delenv("TORCHCOMM_TIMEOUT_SECONDS", raising=False)
+    monkeypatch.delenv("TORCHCOMM_ABORT_ON_ERROR", raising=False)
+    tc.reload_config()
+    try:
+        o = tc.CommOptions()
+        assert o.timeout.total_seconds() == 7 and o.abort_process_on_timeout_or_error is False
+        k = tc.knobs()
+        assert k["TORCHCOMM_TIMEOUT_SECONDS"] == ("7", "file") and k["TORCHCOMM_ABORT_ON_ERROR"] == ("0", "file")
+        monkeypatch.setenv("TORCHCOMM_TIMEOUT_SECONDS", "11")
+        assert tc.CommOptions().timeout.total_seconds() == 11
+        assert tc.knobs()["TORCHCOMM_TIMEOUT_SECONDS"] == ("11", "env")
+        conf.write_text("")
+        monkeypatch.delenv("TORCHCOMM_TIMEOUT_SECONDS")
+        tc.reload_config()
+        assert tc.CommOptions().timeout.total_seconds() == 600
+        assert tc.knobs()["TORCHCOMM_TIMEOUT_SECONDS"][1] == "default"
+    finally:
+        monkeypatch.delenv("B200COMMS_CONF_FILE")
+        tc.reload_config()

@@ -197,6 +197,23 @@ def healthy() -> bool:
     return _comms._health_is_healthy()
 
 
+def knobs() -> dict:
+    """Configuration keys read so far: ``{key: (value in force, "env" | "file" | "default")}``.
+
+    A key is resolved from the environment, then from the configuration file
+    (``B200COMMS_CONF_FILE``, default ``/etc/b200comms.conf``; ``KEY=VALUE`` lines),
+    then from the built-in default -- the order the reference uses for its knobs
+    (comms/utils/cvars/README.md:10-19).  Keys appear once something looked them up
+    (creating a communicator reads the backend's tuning keys).
+    """
+    return {k: (v, src) for k, v, src in _comms._knobs()}
+
+
+def reload_config() -> None:
+    """Re-reads the configuration file at the next lookup."""
+    _comms._reload_config()
+
+
 __all__ = [n for n in dir() if not n.startswith("_")] + ["_BackendWrapper"]
 
 

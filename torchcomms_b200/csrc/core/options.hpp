@@ -8,7 +8,9 @@
 #include <c10/util/intrusive_ptr.h>
 #include <torch/csrc/distributed/c10d/Store.hpp>
 
+#include <array>
 #include <sstream>
+#include <vector>
 #include <type_traits>
 
 #include "types.hpp"
@@ -17,14 +19,42 @@ namespace b200c {
 
 bool parse_bool(std::string_view text);
 
-// Reads an environment variable and converts it; returns `fallback` when the
-// variable is unset or empty. Throws std::runtime_error on malformed values.
+// Configuration tiers (comms/utils/cvars/README.md:10-19 has the same order for
+// the reference's knobs): the environment wins, then the configuration file
+// (`B200COMMS_CONF_FILE`, default /etc/b200comms.conf; lines `KEY=VALUE`, `#`
+// comments), then the built-in default. Returns nullptr when neither tier has
+// the key; `*source` becomes "env" or "file".
+B200C_API const char* config_raw(const char* key, const char** source = nullptr);
+// Forgets the parsed configuration file so the next lookup reads it again.
+B200C_API void reload_config_file();
+// Every key looked up so far with the value in force and where it came from
+// ("env", "file" or "default"), for `knobs()` in Python.
+B200C_API void note_knob(const char* key, const std::string& value, const char* source);
+B200C_API std::vector<std::array<std::string, 3>> knob_report();
+
+template <typename T>
+std::string knob_text(const T& v) {
+  if constexpr (std::is_same_v<T, std::string>) {
+    return v;
+  } else {
+    std::ostringstream o;
+    o << v;
+    return o.str();
+  }
+}
+
+// Reads a configuration key (environment, then configuration file) and converts
+// it; returns `fallback` when the key is unset or empty. Throws
+// std::runtime_error on malformed values.
 template <typename T>
 T env_to_value(const char* key, const T& fallback) {
-  const char* raw = std::getenv(key);
+  const char* source = "default";
+  const char* raw = config_raw(key, &source);
   if (raw == nullptr || *raw == '\0') {
+    note_knob(key, knob_text(fallback), "default");
     return fallback;
   }
+  note_knob(key, raw, source);
   if constexpr (std::is_same_v<T, bool>) {
     return parse_bool(raw);
   } else if constexpr (std::is_same_v<T, std::string>) {

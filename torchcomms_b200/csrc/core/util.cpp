@@ -7,7 +7,11 @@
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
+#include <fstream>
+#include <map>
+#include <mutex>
 #include <thread>
+#include <unordered_map>
 
 #include "logging.hpp"
 #include "options.hpp"
@@ -76,6 +80,84 @@ bool parse_bool(std::string_view text) {
     return false;
   }
   throw std::runtime_error("cannot parse '" + s + "' as a boolean");
+}
+
+namespace {
+
+struct ConfigFile {
+  std::mutex mu;
+  bool loaded = false;
+  std::unordered_map<std::string, std::string> values;
+  std::map<std::string, std::pair<std::string, std::string>> knobs;  // key -> (value, source)
+};
+
+ConfigFile& config_file() {
+  static ConfigFile* c = new ConfigFile();
+  return *c;
+}
+
+std::string trimmed(const std::string& s) {
+  const size_t a = s.find_first_not_of(" \t\r\n");
+  if (a == std::string::npos) {
+    return "";
+  }
+  const size_t b = s.find_last_not_of(" \t\r\n");
+  return s.substr(a, b - a + 1);
+}
+
+}  // namespace
+
+const char* config_raw(const char* key, const char** source) {
+  const char* env = std::getenv(key);
+  if (env != nullptr && *env != '\0') {
+    if (source) *source = "env";
+    return env;
+  }
+  ConfigFile& c = config_file();
+  std::lock_guard<std::mutex> g(c.mu);
+  if (!c.loaded) {
+    c.loaded = true;
+    c.values.clear();
+    const char* path = std::getenv("B200COMMS_CONF_FILE");
+    std::ifstream f(path && *path ? path : "/etc/b200comms.conf");
+    std::string line;
+    while (f && std::getline(f, line)) {
+      const size_t hash = line.find('#');
+      if (hash != std::string::npos) line.erase(hash);
+      const size_t eq = line.find('=');
+      if (eq == std::string::npos) continue;
+      const std::string k = trimmed(line.substr(0, eq)), v = trimmed(line.substr(eq + 1));
+      if (!k.empty()) c.values[k] = v;
+    }
+  }
+  auto it = c.values.find(key);
+  if (it == c.values.end() || it->second.empty()) {
+    return nullptr;
+  }
+  if (source) *source = "file";
+  return it->second.c_str();  // stable until reload_config_file()
+}
+
+void reload_config_file() {
+  ConfigFile& c = config_file();
+  std::lock_guard<std::mutex> g(c.mu);
+  c.loaded = false;
+}
+
+void note_knob(const char* key, const std::string& value, const char* source) {
+  ConfigFile& c = config_file();
+  std::lock_guard<std::mutex> g(c.mu);
+  c.knobs[key] = {value, source};
+}
+
+std::vector<std::array<std::string, 3>> knob_report() {
+  ConfigFile& c = config_file();
+  std::lock_guard<std::mutex> g(c.mu);
+  std::vector<std::array<std::string, 3>> out;
+  for (auto& kv : c.knobs) {
+    out.push_back({kv.first, kv.second.first, kv.second.second});
+  }
+  return out;
 }
 
 CommOptions::CommOptions()

@@ -425,6 +425,14 @@ void bind_core(py::module_& m) {
   m.def("_registered_backends", []() { return Factory::get().registered(); });
   m.def("_next_op_id", &Comm::next_op_id);
   m.def("_query_ranksize", &query_ranksize);
+  m.def("_knobs", [] {
+    std::vector<std::tuple<std::string, std::string, std::string>> out;
+    for (auto& k : knob_report()) {
+      out.emplace_back(k[0], k[1], k[2]);
+    }
+    return out;
+  });
+  m.def("_reload_config", &reload_config_file);
   m.def("_recent_log_lines", []() { return Logger::get().recent(); });
 
   m.def("_health_is_healthy", &HealthCheck::healthy);
