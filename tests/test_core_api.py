@@ -376,3 +376,34 @@ def test_configuration_tiers_env_over_file_over_default(tmp_path, monkeypatch):
     finally:
         monkeypatch.delenv("B200COMMS_CONF_FILE")
         tc.reload_config()
+
+
+def test_comm_stats_hook_counts_calls_bytes_and_completions():
+    import time
+
+    import torchcomms_b200 as tc
+    from torchcomms_b200.hooks import CommStatsHook
+
+    comm = tc.new_comm("fake", torch.device("cpu"), name="stats")
+    stats = CommStatsHook()
+    stats.register_with_comm(comm)
+    assert stats.is_enabled()
+    t = torch.ones(1024)
+    comm.all_reduce(t, tc.ReduceOp.SUM, False)
+    comm.all_reduce(t, tc.ReduceOp.SUM, True).wait()
+    out = torch.empty(3000)
+    comm.all_gather_single(out, torch.ones(3000), False)
+    deadline = time.time() + 5
+    while time.time() < deadline and sum(s["completed"] for s in stats.snapshot().values()) < 3:
+        time.sleep(0.01)
+    snap = stats.snapshot()
+    ar, ag = snap["all_reduce"], snap["all_gather_single"]
+    assert (ar["calls"], ar["bytes"], ar["async_calls"], ar["completed"]) == (2, 8192, 1, 2)
+    assert ar["size_histogram"] == {"4KiB": 2} and ag["size_histogram"] == {"16KiB": 1} and ag["bytes"] == 12000
+    assert ar["busy_ms"] >= 0 and "all_reduce" in stats.report()
+    stats.unregister()
+    comm.all_reduce(t, tc.ReduceOp.SUM, False)
+    assert stats.snapshot()["all_reduce"]["calls"] == 2 and not stats.is_enabled()
+    stats.reset()
+    assert stats.snapshot() == {}
+    comm.finalize()

@@ -1,4 +1,4 @@
-"""Hooks that attach to a communicator: flight recorder, collective log, NaN check.
+"""Hooks that attach to a communicator: flight recorder, collective log, NaN check, per-operation counters.
 
     from torchcomms_b200.hooks import NanCheckHook, fr, clog
     NanCheckHook().register_with_comm(comm)
@@ -12,8 +12,9 @@ hooks/nan_check/nan_check.py:117-185.
 """
 from .._comms import hooks as _native
 from .nan_check import NanCheckHook
+from .stats import CommStatsHook
 
 fr = _native.fr
 clog = _native.clog
 
-__all__ = ["NanCheckHook", "fr", "clog"]
+__all__ = ["NanCheckHook", "CommStatsHook", "fr", "clog"]
