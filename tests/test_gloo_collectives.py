@@ -11,6 +11,7 @@ Test matrix modelled on comms/torchcomms/tests/integration/py/*Test.py.
 """
 from datetime import timedelta
 
+import pytest
 import torch
 
 from tests.mp_util import run_ranks
@@ -276,3 +277,18 @@ def _c10d_worker(rank, world):
 
 def test_device_mesh_and_c10d_wrapper_world2():
     run_ranks(_c10d_worker, 2)
+
+
+def _iface_worker(rank, world):
+    import torchcomms_b200 as tc
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="iface")
+    t = torch.full((8,), float(rank + 1))
+    comm.all_reduce(t, tc.ReduceOp.SUM, False)
+    assert torch.equal(t, torch.full((8,), 3.0))
+    comm.finalize()
+
+
+@pytest.mark.parametrize("env", [{"TORCHCOMM_GLOO_INTERFACE": "lo"}, {"TORCHCOMM_GLOO_HOSTNAME": "127.0.0.1"}])
+def test_gloo_device_selection_by_environment(env):
+    run_ranks(_iface_worker, 2, timeout=120, extra_env=env)

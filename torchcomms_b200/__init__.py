@@ -82,9 +82,23 @@ Timeout = timedelta
 
 
 def _make_gloo_pg(store, rank, size, timeout):
+    """The gloo process group under the ``gloo`` backend.  ``TORCHCOMM_GLOO_INTERFACE`` /
+    ``TORCHCOMM_GLOO_HOSTNAME`` pick the TCP device, as in the reference
+    (comms/torchcomms/gloo/TorchCommGloo.cpp:85-190)."""
+    import os
+
     import torch.distributed as dist
 
-    return dist.ProcessGroupGloo(store, rank, size, timeout)
+    iface = os.environ.get("TORCHCOMM_GLOO_INTERFACE", "")
+    host = os.environ.get("TORCHCOMM_GLOO_HOSTNAME", "")
+    if not iface and not host:
+        return dist.ProcessGroupGloo(store, rank, size, timeout)
+    opts = dist.ProcessGroupGloo._Options()
+    opts._timeout = timeout
+    device = (dist.ProcessGroupGloo.create_device(interface=iface) if iface
+              else dist.ProcessGroupGloo.create_device(hostname=host))
+    opts._devices = [device]
+    return dist.ProcessGroupGloo(store, rank, size, opts)
 
 
 _comms._install_gloo_maker(_make_gloo_pg)
