@@ -407,3 +407,22 @@ def test_comm_stats_hook_counts_calls_bytes_and_completions():
     stats.reset()
     assert stats.snapshot() == {}
     comm.finalize()
+
+
+def test_comm_dump_and_comm_dump_all():
+    import gc
+
+    import torchcomms_b200 as tc
+
+    a = tc.new_comm("fake", torch.device("cpu"), name="dump_a")
+    b = tc.new_comm("fake", torch.device("cpu"), name="dump_b")
+    one = a.comm_dump()
+    assert one["name"] == "dump_a" and one["backend"] == "fake" and one["rank"] == "0" and one["size"] == "1"
+    everything = tc.comm_dump_all()
+    assert {"dump_a", "dump_b"} <= set(everything) and everything["dump_b"]["finalized"] == "0"
+    a.finalize()
+    assert tc.comm_dump_all()["dump_a"]["finalized"] == "1"
+    del a
+    gc.collect()
+    assert "dump_a" not in tc.comm_dump_all() and "dump_b" in tc.comm_dump_all()
+    b.finalize()

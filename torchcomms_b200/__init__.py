@@ -211,6 +211,12 @@ def healthy() -> bool:
     return _comms._health_is_healthy()
 
 
+def comm_dump_all(hints=None) -> dict:
+    """State of every communicator alive in this process: ``{comm name: {key: value}}``
+    (comms/torchcomms/ncclx/TorchCommNCCLXPy.cpp:137-184)."""
+    return _comms.comm_dump_all(hints)
+
+
 def knobs() -> dict:
     """Configuration keys read so far: ``{key: (value in force, "env" | "file" | "default")}``.
 

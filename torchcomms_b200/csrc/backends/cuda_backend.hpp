@@ -150,7 +150,7 @@ class CudaBackend final : public Backend {
   // fp32 in / fp32 out, bf16 on the wire; optional stochastic rounding seed.
   WorkPtr reduce_scatter_quantized(at::Tensor& out, const at::Tensor& in, const ReduceOp& op, int64_t seed,
                                    bool async_op, const OpOptions& o);
-  std::unordered_map<std::string, std::string> comm_dump() const;
+  std::unordered_map<std::string, std::string> comm_dump() const override;
   void set_config(const Hints& h) { set_hints(h); }
   uintptr_t get_nccl_comm_ptr() const { return reinterpret_cast<uintptr_t>(nccl_comm_); }
   // Kernel phase trace (performance work): kMaxBlocks x kTraceSlots int64

@@ -10,6 +10,8 @@
 // fault-tolerance entry points) and comms/torchcomms/TorchCommWindow.hpp:14-150.
 #pragma once
 
+#include <unordered_map>
+
 #include <memory>
 
 #include "hooks.hpp"
@@ -82,6 +84,12 @@ class B200C_API Backend : public std::enable_shared_from_this<Backend> {
   virtual std::string comm_name() const = 0;
   virtual at::Device device() const = 0;
   virtual const CommOptions& options() const = 0;
+
+  // Internal state as a string map, for `comm_dump()` / `comm_dump_all()`
+  // (comms/torchcomms/ncclx/TorchCommNCCLXPy.cpp:59-184). Backends add their own keys.
+  virtual std::unordered_map<std::string, std::string> comm_dump() const {
+    return {{"name", comm_name()}, {"backend", backend_name()}, {"rank", std::to_string(rank())}, {"size", std::to_string(size())}};
+  }
 
   // Point to point.
   virtual WorkPtr send(const at::Tensor& t, int dst, bool async_op, const OpOptions& o) = 0;

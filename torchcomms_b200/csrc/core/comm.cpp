@@ -86,6 +86,19 @@ size_t Comm::next_op_id() {
   return g_next_op_id.fetch_add(1, std::memory_order_relaxed);
 }
 
+namespace {
+// Communicators alive in this process, for comm_dump_all(). Never destroyed:
+// communicators may be released during static teardown.
+std::mutex& live_comms_mu() {
+  static std::mutex* m = new std::mutex();
+  return *m;
+}
+std::set<Comm*>& live_comms() {
+  static std::set<Comm*>* s = new std::set<Comm*>();
+  return *s;
+}
+}  // namespace
+
 Comm::Comm(std::shared_ptr<Backend> impl, std::vector<int> global_ranks)
     : impl_(std::move(impl)), ranks_(std::move(global_ranks)) {
   // A communicator created for reconfigure() has no membership yet (size < 1).
@@ -96,9 +109,30 @@ Comm::Comm(std::shared_ptr<Backend> impl, std::vector<int> global_ranks)
     }
   }
   impl_->attach_hook_tables(abort_hooks_, replay_hooks_);
+  std::lock_guard<std::mutex> g(live_comms_mu());
+  live_comms().insert(this);
+}
+
+std::unordered_map<std::string, std::unordered_map<std::string, std::string>> comm_dump_all() {
+  std::unordered_map<std::string, std::unordered_map<std::string, std::string>> out;
+  std::lock_guard<std::mutex> g(live_comms_mu());
+  for (Comm* c : live_comms()) {
+    try {
+      auto d = c->get_backend_impl()->comm_dump();
+      d["finalized"] = c->finalized_ ? "1" : "0";
+      out[c->get_name()] = std::move(d);
+    } catch (const std::exception& e) {
+      out[c->get_name()] = {{"error", e.what()}};
+    }
+  }
+  return out;
 }
 
 Comm::~Comm() {
+  {
+    std::lock_guard<std::mutex> g(live_comms_mu());
+    live_comms().erase(this);
+  }
   if (!finalized_) {
     B200C_LOG(WARN, "comm", "communicator destroyed without finalize()");
   }

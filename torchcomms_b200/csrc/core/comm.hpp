@@ -29,6 +29,10 @@ class BatchSendRecv {
   std::shared_ptr<Comm> parent_;
 };
 
+// State of every communicator alive in this process, by communicator name
+// (comms/torchcomms/ncclx/TorchCommNCCLXPy.cpp:137-184, `comm_dump_all`).
+B200C_API std::unordered_map<std::string, std::unordered_map<std::string, std::string>> comm_dump_all();
+
 class Comm : public std::enable_shared_from_this<Comm> {
  public:
   Comm(std::shared_ptr<Backend> impl, std::vector<int> global_ranks = {});
@@ -43,6 +47,7 @@ class Comm : public std::enable_shared_from_this<Comm> {
   at::Device get_device() const { return impl_->device(); }
   const CommOptions& get_options() const { return impl_->options(); }
   std::shared_ptr<Backend> get_backend_impl() const { return impl_; }
+  friend std::unordered_map<std::string, std::unordered_map<std::string, std::string>> comm_dump_all();
   const std::vector<int>& get_ranks() const { return ranks_; }
 
   WorkPtr send(const at::Tensor& t, int dst, bool async_op, const OpOptions& o = {});
