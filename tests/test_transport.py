@@ -208,3 +208,30 @@ def _publisher_worker(rank, world):
 
 def test_publisher_serves_several_consumers():
     run_ranks(_publisher_worker, 3, timeout=120)
+
+
+def test_segment_registration_is_shared_by_ranges_inside_it():
+    """What the caching-allocator hook does for device segments, driven by hand on host memory."""
+    from torchcomms_b200 import transport as T
+
+    a, b = _pair()
+    arena = torch.zeros(1 << 16, dtype=torch.uint8)              # stands for one allocator segment
+    before = T.segment_count()
+    T.register_segment(arena.data_ptr(), arena.nbytes, -1)
+    assert T.segment_count() == before + 1
+    t1, t2 = arena[1024:2048], arena[8192:8192 + 4096]           # two "tensors" carved from it
+    m1, m2 = T.TransportMemory(t1), T.TransportMemory(t2)
+    assert m1.reused_registration() and m2.reused_registration() and m1.access_key == m2.access_key
+    src = torch.arange(1024, dtype=torch.int32).view(torch.uint8)[:1024].clone()
+    assert a.write(T.TransportMemory(src).to_view(), m1.to_remote_buffer()) == T.OK
+    assert torch.equal(arena[1024:2048], src) and int(arena[:1024].sum()) == 0 and int(arena[2048:].sum()) == 0
+    # a range outside the segment is a registration of its own
+    outside = torch.zeros(64, dtype=torch.uint8)
+    assert not T.TransportMemory(outside).reused_registration()
+    # once the segment is gone its key stops validating, also for views made earlier
+    remote = m2.to_remote_buffer()
+    T.unregister_segment(arena.data_ptr())
+    assert T.segment_count() == before
+    assert a.write(T.TransportMemory(src).to_view(0, 512), remote.slice(0, 512)) == T.BAD_KEY
+    a.close()
+    b.close()

@@ -5,6 +5,7 @@
 #include "py_common.hpp"
 
 #include <c10/cuda/CUDACachingAllocator.h>
+#include <c10/cuda/CUDAFunctions.h>
 
 #include "../transport/p2p_transport.hpp"
 
@@ -58,6 +59,33 @@ void bind_transport(py::module_& m) {
   py::module_ t = m.def_submodule("transport", "one-sided point-to-point transport");
 
   t.def("strerror", [](int s) { return std::string(transport_strerror(s)); });
+  t.def("register_segment", [](uint64_t ptr, uint64_t len, int device) {
+    TransportMemory::register_segment(reinterpret_cast<void*>(ptr), len, device);
+  }, py::arg("ptr"), py::arg("len"), py::arg("device"));
+  t.def("unregister_segment", [](uint64_t ptr) { TransportMemory::unregister_segment(reinterpret_cast<void*>(ptr)); }, py::arg("ptr"));
+  t.def("segment_count", &TransportMemory::segment_count);
+  t.def("init_caching_allocator_hook", [] {
+    // Every segment the CUDA caching allocator holds, now and from now on, becomes a long-lived
+    // registration; tensors registered later reuse it. The callback runs under the allocator's
+    // lock, so it only records the range (the export happens when a range is first used).
+    TORCH_CHECK(c10::cuda::device_count() > 0, "init_caching_allocator_hook needs a CUDA device");
+    static bool attached = false;
+    if (attached) return;
+    attached = true;
+    namespace cca = c10::cuda::CUDACachingAllocator;
+    cca::attachAllocatorTraceTracker([](const cca::TraceEntry& e) {
+      if (e.action_ == cca::TraceEntry::SEGMENT_ALLOC) {
+        TransportMemory::register_segment(reinterpret_cast<void*>(e.addr_), e.size_, static_cast<int>(e.device_));
+      } else if (e.action_ == cca::TraceEntry::SEGMENT_FREE) {
+        TransportMemory::unregister_segment(reinterpret_cast<void*>(e.addr_));
+      }
+    });
+    for (const auto& seg : cca::snapshot({0, 0}, false).segments) {
+      if (!seg.is_expandable) {
+        TransportMemory::register_segment(reinterpret_cast<void*>(seg.address), seg.total_size, static_cast<int>(seg.device));
+      }
+    }
+  });
   t.attr("OK") = static_cast<int>(kTransportOk);
   t.attr("BAD_KEY") = static_cast<int>(kTransportBadKey);
   t.attr("OUT_OF_RANGE") = static_cast<int>(kTransportOutOfRange);

@@ -44,7 +44,8 @@ struct Registration {
   uint64_t len = 0;
   int device = -1;
   int refs = 0;
-  std::string key;
+  bool segment = false;  // a whole allocator segment; ranges inside it share its key
+  std::string key;       // empty until first use (segments)
 };
 
 // Process-wide table of registered ranges; any transport's service thread answers for all of them.
@@ -228,6 +229,40 @@ bool AccessKey::parse(const std::string& s, AccessKey* out) {
 
 // ------------------------------------------------------------------ registered memory
 
+namespace {
+
+// Fills in the access key of a registration (nonce, CUDA IPC export of the allocation that holds it).
+void build_key(Registration& r, uint64_t alloc_base) {
+  AccessKey key;
+  key.pid = static_cast<int64_t>(getpid());
+  key.id = r.id;
+  key.device = r.device;
+  key.base = r.base;
+  key.len = r.len;
+  key.boot_id = boot_id();
+  std::random_device rd;
+  key.nonce = (static_cast<uint64_t>(rd()) << 32) ^ rd();
+  if (r.device >= 0 && env_str("B200COMMS_TRANSPORT_STAGED", "0") != "1") {
+    const uint64_t start = alloc_base ? alloc_base : r.base;
+    cudaIpcMemHandle_t h;
+    int prev = -1;
+    cudaGetDevice(&prev);
+    cudaSetDevice(r.device);
+    const cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(start));
+    if (prev >= 0) cudaSetDevice(prev);
+    if (e == cudaSuccess) {
+      key.ipc_hex = to_hex(&h, sizeof(h));
+      key.ipc_offset = r.base - start;
+    } else {
+      cudaGetLastError();  // not exportable (for example a virtual-memory allocation): staged path only
+    }
+  }
+  r.nonce = key.nonce;
+  r.key = key.str();
+}
+
+}  // namespace
+
 std::shared_ptr<TransportMemory> TransportMemory::create(void* ptr, size_t len, int device, uint64_t alloc_base) {
   if (ptr == nullptr || len == 0) {
     throw std::invalid_argument("TransportMemory: empty range");
@@ -238,63 +273,89 @@ std::shared_ptr<TransportMemory> TransportMemory::create(void* ptr, size_t len, 
   m->device_ = device;
   const uint64_t base = reinterpret_cast<uint64_t>(ptr);
   Registry& reg = Registry::get();
-  {
-    std::lock_guard<std::mutex> g(reg.mu);
-    for (auto& kv : reg.by_id) {
-      Registration& r = kv.second;
-      if (r.base == base && r.len == len && r.device == device) {
-        ++r.refs;
-        m->id_ = r.id;
-        m->key_ = r.key;
-        m->reused_ = true;
-        return m;
-      }
-    }
-  }
-  AccessKey key;
-  key.pid = static_cast<int64_t>(getpid());
-  key.device = device;
-  key.base = base;
-  key.len = len;
-  key.boot_id = boot_id();
-  std::random_device rd;
-  key.nonce = (static_cast<uint64_t>(rd()) << 32) ^ rd();
-  if (device >= 0 && env_str("B200COMMS_TRANSPORT_STAGED", "0") != "1") {
-    const uint64_t start = alloc_base ? alloc_base : base;
-    cudaIpcMemHandle_t h;
-    int prev = -1;
-    cudaGetDevice(&prev);
-    cudaSetDevice(device);
-    const cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(start));
-    if (prev >= 0) cudaSetDevice(prev);
-    if (e == cudaSuccess) {
-      key.ipc_hex = to_hex(&h, sizeof(h));
-      key.ipc_offset = base - start;
-    } else {
-      cudaGetLastError();  // not exportable (for example a virtual-memory allocation): staged path only
-    }
-  }
   std::lock_guard<std::mutex> g(reg.mu);
-  key.id = reg.next_id++;
+  // An identical range first, then an allocator segment that contains the range.
+  Registration* hit = nullptr;
+  for (auto& kv : reg.by_id) {
+    Registration& r = kv.second;
+    if (r.device != device) continue;
+    if (r.base == base && r.len == len && !r.segment) {
+      hit = &r;
+      break;
+    }
+    if (r.segment && base >= r.base && len <= r.len && base - r.base <= r.len - len) {
+      hit = &r;
+    }
+  }
+  if (hit != nullptr) {
+    if (hit->key.empty()) {
+      build_key(*hit, hit->base);  // a segment is exported when a range inside it is first used
+    }
+    ++hit->refs;
+    m->id_ = hit->id;
+    m->key_ = hit->key;
+    m->reused_ = true;
+    return m;
+  }
   Registration r;
-  r.id = key.id;
-  r.nonce = key.nonce;
+  r.id = reg.next_id++;
   r.base = base;
   r.len = len;
   r.device = device;
   r.refs = 1;
-  r.key = key.str();
+  build_key(r, alloc_base);
   m->id_ = r.id;
   m->key_ = r.key;
   reg.by_id.emplace(r.id, std::move(r));
   return m;
 }
 
+void TransportMemory::register_segment(void* base_ptr, size_t len, int device) {
+  if (base_ptr == nullptr || len == 0) return;
+  const uint64_t base = reinterpret_cast<uint64_t>(base_ptr);
+  Registry& reg = Registry::get();
+  std::lock_guard<std::mutex> g(reg.mu);
+  for (auto& kv : reg.by_id) {
+    if (kv.second.segment && kv.second.base == base && kv.second.device == device) {
+      kv.second.len = len;
+      return;
+    }
+  }
+  Registration r;
+  r.id = reg.next_id++;
+  r.base = base;
+  r.len = len;
+  r.device = device;
+  r.refs = 1;  // held by the table until unregister_segment
+  r.segment = true;
+  reg.by_id.emplace(r.id, std::move(r));
+}
+
+void TransportMemory::unregister_segment(void* base_ptr) {
+  const uint64_t base = reinterpret_cast<uint64_t>(base_ptr);
+  Registry& reg = Registry::get();
+  std::lock_guard<std::mutex> g(reg.mu);
+  for (auto it = reg.by_id.begin(); it != reg.by_id.end(); ++it) {
+    if (it->second.segment && it->second.base == base) {
+      reg.by_id.erase(it);  // the memory is gone: keys that point into it stop validating
+      return;
+    }
+  }
+}
+
+size_t TransportMemory::segment_count() {
+  Registry& reg = Registry::get();
+  std::lock_guard<std::mutex> g(reg.mu);
+  size_t n = 0;
+  for (auto& kv : reg.by_id) n += kv.second.segment ? 1 : 0;
+  return n;
+}
+
 TransportMemory::~TransportMemory() {
   Registry& reg = Registry::get();
   std::lock_guard<std::mutex> g(reg.mu);
   auto it = reg.by_id.find(id_);
-  if (it != reg.by_id.end() && --it->second.refs <= 0) {
+  if (it != reg.by_id.end() && --it->second.refs <= 0 && !it->second.segment) {
     reg.by_id.erase(it);
   }
 }

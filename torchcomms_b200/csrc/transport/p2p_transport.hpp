@@ -82,6 +82,11 @@ class B200C_API TransportMemory {
   // (what a CUDA IPC handle exports); 0 means `ptr` itself.
   static std::shared_ptr<TransportMemory> create(void* ptr, size_t len, int device, uint64_t alloc_base = 0);
   ~TransportMemory();
+  // Long-lived registration of a whole allocator segment. Registrations of ranges inside it share
+  // its key (one export per segment instead of one per tensor); `unregister_segment` ends it.
+  static void register_segment(void* base, size_t len, int device);
+  static void unregister_segment(void* base);
+  static size_t segment_count();
   TransportMemory(const TransportMemory&) = delete;
   TransportMemory& operator=(const TransportMemory&) = delete;
 

@@ -63,6 +63,22 @@ RdmaMemoryMutableView = MemoryView
 RdmaRemoteBuffer = RemoteBuffer
 
 
+def init_caching_allocator_hook() -> None:
+    """Registers every segment of PyTorch's CUDA caching allocator, present and future, with the
+    transport, so that ``TransportMemory(tensor)`` reuses the segment's registration (one export
+    per segment instead of one per tensor; ``reused_registration()`` is then true).  Needs no
+    communicator.  Parity: ``init_caching_allocator_hook`` of the reference's NCCLX module
+    (comms/torchcomms/ncclx/TorchCommNCCLXPy.cpp:187-204) and its transport CCA hook
+    (comms/torchcomms/transport/RdmaTransportCCA.cpp)."""
+    torch.cuda.init()
+    _t.init_caching_allocator_hook()
+
+
+register_segment = _t.register_segment
+unregister_segment = _t.unregister_segment
+segment_count = _t.segment_count
+
+
 class TransportError(RuntimeError):
     def __init__(self, status: int, what: str):
         super().__init__(f"{what}: {strerror(status)} (status {status})")
@@ -192,5 +208,6 @@ __all__ = [
     "P2pTransport", "TransportMemory", "MemoryView", "RemoteBuffer", "TransportFuture", "TransportError",
     "RdmaTransport", "RdmaMemory", "RdmaMemoryView", "RdmaMemoryMutableView", "RdmaRemoteBuffer",
     "TensorPublisher", "Manifest", "TensorEntry", "fetch_tensors", "strerror",
+    "init_caching_allocator_hook", "register_segment", "unregister_segment", "segment_count",
     "OK", "BAD_KEY", "OUT_OF_RANGE", "NOT_CONNECTED", "IO_ERROR", "CUDA_ERROR", "TIMEOUT", "CLOSED", "SIZE_MISMATCH",
 ]
