@@ -402,3 +402,51 @@ def _data_parallel_worker(rank, world):
 
 def test_data_parallel_bucketed_all_reduce():
     run_ranks(_data_parallel_worker, 2, timeout=120)
+
+
+def _chaos_worker(rank, world):
+    import time
+
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import objcol
+    from torchcomms_b200.hooks import ChecksumHook, DelayInjectionHook
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="chaos")
+    delay = DelayInjectionHook(max_ms=20, seed=rank, probability=0.7, ops=["all_reduce", tc.OpName.broadcast], ranks=[0, 1])
+    delay.register_with_comm(comm)
+    chk = ChecksumHook(ops=["all_reduce", "broadcast", "all_gather_single"])
+    chk.register_with_comm(comm)
+    # with ranks arriving in a different order every time the results stay right
+    for step in range(6):
+        t = torch.full((257,), float(rank + step))
+        comm.all_reduce(t, tc.ReduceOp.SUM, step % 2 == 1).wait()
+        assert torch.equal(t, torch.full((257,), float(sum(r + step for r in range(world)))))
+    b = torch.arange(5.0) if rank == 1 else torch.zeros(5)
+    comm.broadcast(b, 1, False)
+    out = torch.empty(world * 3)
+    comm.all_gather_single(out, torch.full((3,), float(rank)), False)
+    comm.barrier(False)                                         # not recorded: filtered out
+    assert delay.is_enabled() and len(delay.injected) >= 1 and all(name in ("all_reduce", "broadcast") for _, name, _ in delay.injected)
+    deadline = time.time() + 5
+    while time.time() < deadline and len(chk.records()) < 8:
+        time.sleep(0.01)
+    mine = chk.records()
+    assert [r["op"] for r in mine] == ["all_reduce"] * 6 + ["broadcast", "all_gather_single"]
+    chk.unregister()
+    delay.unregister()
+    everyone = [None] * world
+    objcol.all_gather_object(comm, everyone, mine)
+    assert ChecksumHook.divergence(everyone) is None
+    # inputs differ between ranks, outputs of replicating operations do not
+    assert len({r[0]["in"] for r in everyone}) == world and len({r[0]["out"] for r in everyone}) == 1
+    # a replica that silently diverged is named by sequence number
+    broken = [list(map(dict, r)) for r in everyone]
+    broken[1][3]["out"] ^= 1
+    bad = ChecksumHook.divergence(broken)
+    assert bad["seq"] == 3 and bad["reason"] == "output mismatch" and bad["op"] == "all_reduce"
+    assert ChecksumHook.divergence([everyone[0], everyone[1][:-1]])["reason"] == "operation count mismatch"
+    comm.finalize()
+
+
+def test_delay_injection_and_checksum_hooks():
+    run_ranks(_chaos_worker, 2, timeout=120)

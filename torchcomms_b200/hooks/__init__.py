@@ -12,9 +12,10 @@ hooks/nan_check/nan_check.py:117-185.
 """
 from .._comms import hooks as _native
 from .nan_check import NanCheckHook
+from .chaos import ChecksumHook, DelayInjectionHook
 from .stats import CommStatsHook
 
 fr = _native.fr
 clog = _native.clog
 
-__all__ = ["NanCheckHook", "CommStatsHook", "fr", "clog"]
+__all__ = ["NanCheckHook", "CommStatsHook", "DelayInjectionHook", "ChecksumHook", "fr", "clog"]
