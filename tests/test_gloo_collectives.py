@@ -292,3 +292,23 @@ def _iface_worker(rank, world):
 @pytest.mark.parametrize("env", [{"TORCHCOMM_GLOO_INTERFACE": "lo"}, {"TORCHCOMM_GLOO_HOSTNAME": "127.0.0.1"}])
 def test_gloo_device_selection_by_environment(env):
     run_ranks(_iface_worker, 2, timeout=120, extra_env=env)
+
+
+def _store_worker(rank, world):
+    from torchcomms_b200.utils.store import create_prefix_store, dup_prefix_store
+
+    boot = create_prefix_store("boot", timedelta(seconds=60))
+    boot.set(f"hello/{rank}", str(rank))
+    assert boot.get(f"hello/{1 - rank}").decode() == str(1 - rank)
+    second = dup_prefix_store("second", boot, timedelta(seconds=60))
+    second.set(f"k/{rank}", f"v{rank}")
+    assert second.get(f"k/{1 - rank}").decode() == f"v{1 - rank}"
+    # the two stores are different servers: a key of one is not a key of the other
+    assert second.check([f"k/{rank}"]) and not boot.check([f"k/{rank}"])
+    assert boot.get("second/dup_store_port").decode().isdigit()
+    boot.set(f"bye/{rank}", "1")
+    boot.wait([f"bye/{1 - rank}"])
+
+
+def test_prefix_store_and_duplicate_store():
+    run_ranks(_store_worker, 2, timeout=120)

@@ -132,6 +132,15 @@ c10::intrusive_ptr<c10d::Store> create_prefix_store(
     int world_size,
     Millis timeout);
 
+// A second TCPStore of its own (rank 0 listens on a port the system picks and
+// publishes it through `bootstrap` under "<prefix>/dup_store_port"), wrapped
+// in a PrefixStore. For users that must not share a server with the bootstrap
+// store (comms/torchcomms/utils/StoreManager.cpp:37-80).
+c10::intrusive_ptr<c10d::Store> dup_prefix_store(
+    const std::string& prefix,
+    const c10::intrusive_ptr<c10d::Store>& bootstrap,
+    Millis timeout);
+
 // Wraps an existing store so keys of one communicator cannot collide with
 // another's.
 c10::intrusive_ptr<c10d::Store> scoped_store(

@@ -229,6 +229,33 @@ c10::intrusive_ptr<c10d::Store> create_prefix_store(
   return c10::make_intrusive<c10d::PrefixStore>(prefix, tcp);
 }
 
+c10::intrusive_ptr<c10d::Store> dup_prefix_store(
+    const std::string& prefix, const c10::intrusive_ptr<c10d::Store>& bootstrap, Millis timeout) {
+  const std::string host = env_to_value<std::string>("MASTER_ADDR", "");
+  if (host.empty()) {
+    throw std::runtime_error("dup_prefix_store: MASTER_ADDR is not set");
+  }
+  const int rank = query_ranksize().first;
+  const std::string key = prefix + "/dup_store_port";
+  c10d::TCPStoreOptions o;
+  o.waitWorkers = false;
+  o.useLibUV = true;
+  o.timeout = timeout;
+  c10::intrusive_ptr<c10d::TCPStore> tcp;
+  if (rank == 0) {
+    o.port = 0;  // the system picks a free port
+    o.isServer = true;
+    tcp = c10::make_intrusive<c10d::TCPStore>(host, o);
+    store_set_string(*bootstrap, key, std::to_string(tcp->getPort()));
+  } else {
+    bootstrap->wait({key}, timeout);
+    o.port = static_cast<uint16_t>(std::stoi(store_get_string(*bootstrap, key)));
+    o.isServer = false;
+    tcp = c10::make_intrusive<c10d::TCPStore>(host, o);
+  }
+  return c10::make_intrusive<c10d::PrefixStore>(prefix, tcp);
+}
+
 c10::intrusive_ptr<c10d::Store> scoped_store(
     const c10::intrusive_ptr<c10d::Store>& base, const std::string& prefix) {
   return c10::make_intrusive<c10d::PrefixStore>(prefix, base);

@@ -74,6 +74,7 @@ def init_caching_allocator_hook() -> None:
     _t.init_caching_allocator_hook()
 
 
+attach_rdma_memory_hook = init_caching_allocator_hook   # the reference's name (transport/cca_hook)
 register_segment = _t.register_segment
 unregister_segment = _t.unregister_segment
 segment_count = _t.segment_count
@@ -208,6 +209,6 @@ __all__ = [
     "P2pTransport", "TransportMemory", "MemoryView", "RemoteBuffer", "TransportFuture", "TransportError",
     "RdmaTransport", "RdmaMemory", "RdmaMemoryView", "RdmaMemoryMutableView", "RdmaRemoteBuffer",
     "TensorPublisher", "Manifest", "TensorEntry", "fetch_tensors", "strerror",
-    "init_caching_allocator_hook", "register_segment", "unregister_segment", "segment_count",
+    "init_caching_allocator_hook", "attach_rdma_memory_hook", "register_segment", "unregister_segment", "segment_count",
     "OK", "BAD_KEY", "OUT_OF_RANGE", "NOT_CONNECTED", "IO_ERROR", "CUDA_ERROR", "TIMEOUT", "CLOSED", "SIZE_MISMATCH",
 ]
