@@ -7,6 +7,7 @@
     python benchmarks/kernel_cases.py --case ar_pipe         # pipelined all-reduce, 8 virtual ranks, 32 MB each
     python benchmarks/kernel_cases.py --case rs_cast         # reduce-scatter fp32 -> bf16 wire -> fp32, 8 virtual ranks
     python benchmarks/kernel_cases.py --case ep              # MoE dispatch + combine, 8 virtual ranks
+    python benchmarks/kernel_cases.py --case ar_norm         # fused all-reduce + residual + RMSNorm, 8 virtual ranks
     python benchmarks/kernel_cases.py --case model           # RMSNorm, SwiGLU, cross-entropy, AdamW
 
 Each case runs ``--warmup`` untimed and ``--iters`` timed launches (CUDA events,
@@ -103,6 +104,27 @@ def main():
             outs = [torch.empty(count, dtype=torch.float32, device=dev) for _ in range(nranks)]
             us = timed(lambda: w.reduce_scatter(ins, outs, "bf16", 0, 1.0, 18, 32 * 1024), args.warmup, args.iters, flush)
             print(f"reduce_scatter fp32->bf16 wire->fp32, {nranks} virtual ranks x {nranks * count * 4 >> 20} MB in: {us:.1f} us")
+        print("status", w.status()[:1])
+    elif args.case == "ar_norm":
+        nranks, rows, hidden = 8, 32, 8192
+        w = _comms._EmuWorld(nranks, 8 << 20, 2000.0)
+        xs = [rnd(rows, hidden) for _ in range(nranks)]
+        res = [rnd(rows, hidden) for _ in range(nranks)]
+        outs = [torch.empty_like(t) for t in xs]
+        wn = rnd(hidden)
+        us = timed(lambda: w.all_reduce_rmsnorm(xs, res, wn, outs, 1e-5), args.warmup, args.iters, flush)
+        flat_in = [t.view(-1) for t in xs]
+        flat_out = [torch.empty_like(t) for t in flat_in]
+
+        def unfused():
+            w.all_reduce(flat_in, flat_out, 0, 1.0, 0, 32, 0)
+            for r in range(nranks):
+                res[r].add_(flat_out[r].view(rows, hidden))
+                _comms.ops.rmsnorm_fwd(res[r], wn, 1e-5)
+
+        us2 = timed(unfused, args.warmup, args.iters, flush)
+        print(f"all_reduce + residual + rmsnorm, {nranks} virtual ranks x [{rows}, {hidden}] bf16: fused {us:.1f} us; "
+              f"one-shot all-reduce + add + rmsnorm kernels {us2:.1f} us (both include the emulation launch's host sync)")
         print("status", w.status()[:1])
     elif args.case == "ep":
         nranks, tokens, hidden, experts, topk = 8, 512, 7168, 256, 8

@@ -48,6 +48,24 @@ cudaError_t launch_all_reduce(const CommDev* comms, const HeapLayout& lay, int e
                               RedKind red, float scale, int algo, bool use_mc, LaunchShape shape,
                               cudaStream_t stream);
 
+// All-reduce + residual add + RMSNorm of a bf16 [rows, hidden] partial (one block per row).
+constexpr int kArNormFlagRow0 = 512;     // first row of the latency flag set this kernel signals on
+constexpr int kArNormMaxRows = 128;
+constexpr int kArNormMaxHidden = 8192;
+struct ArNormArgs {
+  const __nv_bfloat16* in;       // this rank's partial sums
+  __nv_bfloat16* residual;       // nullptr, or [rows, hidden] updated in place with sum + residual
+  const __nv_bfloat16* weight;   // [hidden]
+  __nv_bfloat16* out;            // [rows, hidden] normalised
+  char* stage[kMaxRanks];        // every rank's staging: 2 x kArNormMaxRows x hidden bf16
+  int rows;
+  int hidden;                    // multiple of 8, <= kArNormMaxHidden
+  float eps;
+};
+inline size_t ar_norm_stage_bytes(int hidden) { return 2ull * kArNormMaxRows * static_cast<size_t>(hidden) * 2; }
+// `args` has one entry per emulated rank (one entry when emu_ranks == 0).
+cudaError_t launch_all_reduce_rmsnorm(const CommDev* comms, int emu_ranks, const ArNormArgs* args, cudaStream_t stream);
+
 // Reduce-scatter: `in` holds nranks x count elements of `in_dtype`; rank r
 // receives the reduction of block r as `out_dtype`. Data crosses NVLink as
 // `wire_dtype`. Supported type triples: all equal, or in in {F32,BF16},

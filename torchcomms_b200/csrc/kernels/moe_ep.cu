@@ -220,7 +220,30 @@ __device__ void ep_combine_body(const CommDev& c, const EpDev& e, const CombineA
   //    of the previous combine guarantees those slots are free.
   const int n_rows = e.recv_info[0];
   const int row_vec = e.hidden / 8;  // 16-byte vectors per row; a multiple of 32
-  for (int row = gwarp; row < n_rows; row += nwarps) {
+  // Received rows are packed by source rank. Walking them in that order would
+  // make every rank push into rank 0 first, then all into rank 1, ...: eight
+  // senders share one receiver's links. Each rank therefore starts with the
+  // rows of the next rank and goes round, so that at any time the ranks push
+  // into different peers.
+  int seg_start[kMaxRanks + 1];
+  seg_start[0] = 0;
+#pragma unroll
+  for (int s = 0; s < kMaxRanks; ++s) {
+    seg_start[s + 1] = seg_start[s] + (s < e.nranks ? e.recv_info[1 + s] : 0);
+  }
+  for (int vrow = gwarp; vrow < n_rows; vrow += nwarps) {
+    int rem = vrow, row = -1;
+    for (int j = 0; j < e.nranks; ++j) {
+      int s = e.rank + 1 + j;
+      if (s >= e.nranks) s -= e.nranks;
+      const int len = seg_start[s + 1] - seg_start[s];
+      if (rem < len) {
+        row = seg_start[s] + rem;
+        break;
+      }
+      rem -= len;
+    }
+    if (row < 0 || row >= n_rows) continue;  // counts and total disagree: skip rather than read out of range
     const int src = e.recv_src[e.rank][row];
     const int s = src / e.max_tokens, t = src - s * e.max_tokens;
     if (src < 0 || s >= e.nranks) {  // never store through a bad index

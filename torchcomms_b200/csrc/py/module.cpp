@@ -284,6 +284,7 @@ void bind_core(py::module_& m) {
       .def("get_device", &Comm::get_device)
       .def("get_backend", &Comm::get_backend)
       .def("get_backend_version", &Comm::get_backend_version)
+      .def("comm_dump", [](Comm& c) { return c.get_backend_impl()->comm_dump(); })
       .def("get_backend_impl", &Comm::get_backend_impl)
       .def("unsafe_get_backend", &Comm::get_backend_impl)
       .def("get_ranks", &Comm::get_ranks)
@@ -425,6 +426,12 @@ void bind_core(py::module_& m) {
   m.def("_registered_backends", []() { return Factory::get().registered(); });
   m.def("_next_op_id", &Comm::next_op_id);
   m.def("_query_ranksize", &query_ranksize);
+  m.def("_create_prefix_store", [](const std::string& prefix, Millis timeout) {
+    auto [rank, size] = query_ranksize();
+    return create_prefix_store(prefix, rank, size, timeout);
+  }, py::arg("prefix"), py::arg("timeout") = kDefaultTimeout, py::call_guard<py::gil_scoped_release>());
+  m.def("_dup_prefix_store", &dup_prefix_store, py::arg("prefix"), py::arg("bootstrap_store"),
+        py::arg("timeout") = kDefaultTimeout, py::call_guard<py::gil_scoped_release>());
   m.def("_knobs", [] {
     std::vector<std::tuple<std::string, std::string, std::string>> out;
     for (auto& k : knob_report()) {
@@ -433,6 +440,8 @@ void bind_core(py::module_& m) {
     return out;
   });
   m.def("_reload_config", &reload_config_file);
+  m.def("comm_dump_all", [](const std::optional<Hints>&) { return comm_dump_all(); }, py::arg("hints") = py::none(),
+        "State of every live communicator of this process: {comm name: {key: value}}.");
   m.def("_recent_log_lines", []() { return Logger::get().recent(); });
 
   m.def("_health_is_healthy", &HealthCheck::healthy);
@@ -467,4 +476,5 @@ PYBIND11_MODULE(_comms, m) {
   b200c::bind_ep(m);
   b200c::bind_tp(m);
   b200c::bind_transport(m);
+  b200c::bind_arnorm(m);
 }

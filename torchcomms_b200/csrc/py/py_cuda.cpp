@@ -63,6 +63,7 @@ class EmuWorld {
   }
   ~EmuWorld() {
     for (void* p : heaps_) cudaFree(p);
+    for (void* p : arn_stage_) cudaFree(p);
     for (void* p : epochs_) cudaFree(p);
     if (status_host_) cudaFreeHost(status_host_);
   }
@@ -106,6 +107,35 @@ class EmuWorld {
     B200C_CUDA_CHECK(launch_all_reduce(comms_.data(), lay_, n_, ip.data(), op.data(), ins[0].numel(), dtype_of(ins[0]),
                                        static_cast<RedKind>(red), static_cast<float>(scale), algo, false,
                                        shape(blocks, chunk), stream()));
+  }
+  // Fused all-reduce + residual add + RMSNorm over the virtual ranks; `residuals` is empty or one per rank.
+  void all_reduce_rmsnorm(std::vector<at::Tensor> ins, std::vector<at::Tensor> residuals, at::Tensor weight,
+                          std::vector<at::Tensor> outs, double eps) {
+    check(ins);
+    check(outs);
+    TORCH_CHECK(residuals.empty() || static_cast<int>(residuals.size()) == n_, "residuals: none or one per rank");
+    TORCH_CHECK(ins[0].dim() == 2 && ins[0].scalar_type() == at::kBFloat16, "bf16 [rows, hidden] expected");
+    const int hidden = static_cast<int>(ins[0].size(1));
+    if (arn_stage_.empty()) {
+      arn_stage_.resize(n_);
+      for (int r = 0; r < n_; ++r) {
+        B200C_CUDA_CHECK(cudaMalloc(&arn_stage_[r], ar_norm_stage_bytes(kArNormMaxHidden)));
+      }
+    }
+    std::vector<ArNormArgs> args(n_);
+    for (int r = 0; r < n_; ++r) {
+      ArNormArgs& a = args[r];
+      std::memset(&a, 0, sizeof(a));
+      a.in = static_cast<const __nv_bfloat16*>(ins[r].data_ptr());
+      a.residual = residuals.empty() ? nullptr : static_cast<__nv_bfloat16*>(residuals[r].data_ptr());
+      a.weight = static_cast<const __nv_bfloat16*>(weight.data_ptr());
+      a.out = static_cast<__nv_bfloat16*>(outs[r].data_ptr());
+      for (int p = 0; p < n_; ++p) a.stage[p] = static_cast<char*>(arn_stage_[p]);
+      a.rows = static_cast<int>(ins[r].size(0));
+      a.hidden = hidden;
+      a.eps = static_cast<float>(eps);
+    }
+    B200C_CUDA_CHECK(launch_all_reduce_rmsnorm(comms_.data(), n_, args.data(), stream()));
   }
   void reduce_scatter(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, const std::string& wire, int red,
                       double scale, int blocks, size_t chunk) {
@@ -261,7 +291,7 @@ class EmuWorld {
   int n_;
   HeapLayout lay_;
   size_t flags_off_ = 0, total_ = 0;
-  std::vector<void*> heaps_, epochs_;
+  std::vector<void*> heaps_, epochs_, arn_stage_;
   uint32_t* status_host_ = nullptr;
   uint32_t* status_dev_ = nullptr;
   std::vector<CommDev> comms_;
@@ -378,6 +408,7 @@ void bind_cuda_backend(py::module_& m) {
       .def(py::init<int, size_t, double>(), py::arg("nranks"), py::arg("staging_bytes") = 8u << 20,
            py::arg("wait_ms") = 2000.0)
       .def("all_reduce", &EmuWorld::all_reduce)
+      .def("all_reduce_rmsnorm", &EmuWorld::all_reduce_rmsnorm)
       .def("reduce_scatter", &EmuWorld::reduce_scatter)
       .def("reduce_scatter_sr", &EmuWorld::reduce_scatter_sr)
       .def("all_gather", &EmuWorld::all_gather)
