@@ -220,6 +220,11 @@ void CudaBackend::parse_tuning(const Hints& h) {
       hint_or<double>(h, "device_wait_ms", env_to_value<double>("B200COMMS_DEVICE_WAIT_MS", t.device_wait_ns / 1.0e6)) * 1.0e6);
   t.watchdog_interval_ms = hint_or<int>(h, "garbage_collect_interval_ms", t.watchdog_interval_ms);
   t.max_event_pool = hint_or<size_t>(h, "max_event_pool_size", t.max_event_pool);
+  // The reference's variable name is honoured as well (TorchCommNCCLX graph monitoring switch).
+  t.graph_timeout_monitoring = hint_or<bool>(
+      h, "graph_timeout_monitoring",
+      env_to_value<bool>("B200COMMS_GRAPH_TIMEOUT_MONITORING",
+                         env_to_value<bool>("TORCHCOMM_NCCLX_GRAPH_TIMEOUT_MONITORING", t.graph_timeout_monitoring)));
   t.max_blocks = std::max(1, std::min(t.max_blocks, kMaxBlocks));
   t.threads = std::max(32, std::min(t.threads, 256));
   t.ag_oneshot_max_bytes = hint_or<size_t>(h, "ag_oneshot_max_bytes", env_to_value<size_t>("B200COMMS_AG_ONESHOT_MAX_BYTES", t.ag_oneshot_max_bytes));
@@ -575,7 +580,8 @@ void CudaBackend::watchdog_loop() {
         replay_events.emplace_back(e.graph_id, e.seen_end, e.stream, e.index, 'E');
         e.seen_end++;
       }
-      if (failure.empty() && e.seen_start > e.seen_end && e.timeout != kNoTimeout && now - e.open_since > e.timeout) {
+      if (tune_.graph_timeout_monitoring && failure.empty() && e.seen_start > e.seen_end && e.timeout != kNoTimeout &&
+          now - e.open_since > e.timeout) {
         failure = "a captured collective (graph " + std::to_string(e.graph_id) + ", index " + std::to_string(e.index) +
             ") did not finish within its timeout during replay";
         timed_out = true;

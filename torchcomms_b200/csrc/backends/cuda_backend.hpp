@@ -95,6 +95,7 @@ struct Tuning {
   Algo force = Algo::AUTO;                 // B200COMMS_ALGO / hint "algo"
   unsigned long long device_wait_ns = 10ull * 1000 * 1000 * 1000;  // budget of one device-side wait
   int watchdog_interval_ms = 100;
+  bool graph_timeout_monitoring = true;   // watchdog fails a captured collective that stays open past its timeout during replay
   size_t max_event_pool = 1000;
 };
 
