@@ -17,7 +17,7 @@ namespace b200c {
 class Comm;
 
 // Accumulates point-to-point operations and issues them as one group.
-class BatchSendRecv {
+class B200C_API BatchSendRecv {
  public:
   explicit BatchSendRecv(std::shared_ptr<Comm> parent) : parent_(std::move(parent)) {}
   void send(const at::Tensor& t, int dst);
@@ -33,7 +33,7 @@ class BatchSendRecv {
 // (comms/torchcomms/ncclx/TorchCommNCCLXPy.cpp:137-184, `comm_dump_all`).
 B200C_API std::unordered_map<std::string, std::unordered_map<std::string, std::string>> comm_dump_all();
 
-class Comm : public std::enable_shared_from_this<Comm> {
+class B200C_API Comm : public std::enable_shared_from_this<Comm> {
  public:
   Comm(std::shared_ptr<Backend> impl, std::vector<int> global_ranks = {});
   ~Comm();
@@ -136,7 +136,7 @@ class B200C_API Factory {
   std::unordered_map<std::string, Maker> makers_;
 };
 
-std::shared_ptr<Comm> new_comm(const std::string& backend, at::Device device,
+B200C_API std::shared_ptr<Comm> new_comm(const std::string& backend, at::Device device,
                                const std::string& name, const CommOptions& opts = {});
 
 // Process-wide health flag: flips to unhealthy once any watchdog saw a

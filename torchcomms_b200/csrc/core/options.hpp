@@ -17,7 +17,7 @@
 
 namespace b200c {
 
-bool parse_bool(std::string_view text);
+B200C_API bool parse_bool(std::string_view text);
 
 // Configuration tiers (comms/utils/cvars/README.md:10-19 has the same order for
 // the reference's knobs): the environment wins, then the configuration file

@@ -62,7 +62,7 @@ struct RemoteBuffer {
 };
 
 // Fields of an access key ("b2k1:<pid>:<id>:<nonce>:<device>:<base>:<len>:<ipc_off>:<ipc hex|->:<boot>").
-struct AccessKey {
+struct B200C_API AccessKey {
   int64_t pid = 0;
   uint64_t id = 0;
   uint64_t nonce = 0;
