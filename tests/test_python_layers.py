@@ -146,6 +146,28 @@ def _functional_worker(rank, world):
     F.all_reduce_(t, "max", comm)
     F.barrier(comm)
 
+    # differentiable point-to-point: a two-stage "pipeline" y = (x * 2 on rank 0) -> (* 3 on rank 1)
+    if rank == 0:
+        p = torch.full((2, 2), 1.5, requires_grad=True)
+        sent = F.send(p * 2, 1, comm)
+        sent.sum().mul(0).backward()                     # the gradient of what was sent comes back from rank 1
+        assert torch.equal(p.grad, torch.full((2, 2), 6.0))
+    elif rank == 1:
+        got = F.recv(torch.empty(2, 2), 0, comm)
+        got.requires_grad_()
+        assert torch.equal(got, torch.full((2, 2), 3.0))
+        (got * 3).sum().backward()
+        F.send(got.grad, 0, comm)                        # what _bw_recv does when recv is inside a graph
+    # gather <-> scatter
+    gs = torch.full((1, 2), float(rank + 1), requires_grad=True)
+    gathered = F.gather_single(gs, 0, comm)
+    if rank == 0:
+        assert torch.equal(gathered, torch.tensor([[float(r + 1)] * 2 for r in range(world)]))
+    (gathered * (torch.arange(world, dtype=torch.float32).view(-1, 1) + 1)).sum().backward()
+    assert torch.equal(gs.grad, torch.full((1, 2), float(rank + 1)))   # the root's upstream gradient, scattered back
+    sc = F.scatter(torch.arange(2.0 * world).view(world, 2) if rank == 0 else torch.zeros(world, 2), 0, comm)
+    assert torch.equal(sc, torch.tensor([[2.0 * rank, 2.0 * rank + 1]]))
+
     # traced with fake tensors: shapes only, no collective runs
     from torch.fx.experimental.proxy_tensor import make_fx
 

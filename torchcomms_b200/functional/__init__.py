@@ -349,7 +349,122 @@ def wait_tensor(x: Tensor) -> Tensor:
     return _ops.wait_tensor(x)
 
 
+# ------------------------------------------------- point-to-point, gather, scatter ---
+# Registered after the collectives above with the same three parts (implementation,
+# fake, autograd).  `send` returns its input so that the call has a result the
+# graph can depend on; its gradient is received from the destination.  `recv`
+# takes a tensor that only gives shape and dtype; its gradient is sent back to
+# the source.  Pairs of ranks must issue matching calls in the same order in the
+# backward pass as they did (mirrored) in the forward pass.
+
+_lib.define("send(Tensor input, int dst, str comm) -> Tensor")
+_lib.define("recv(Tensor like, int src, str comm) -> Tensor")
+_lib.define("gather_single(Tensor input, int root, str comm) -> Tensor")
+_lib.define("scatter(Tensor input, int root, str comm) -> Tensor")
+
+
+def _impl_send(input: Tensor, dst: int, comm: str) -> Tensor:
+    x = input.contiguous()
+    _get(comm).send(x, dst, False)
+    return x.clone()
+
+
+def _impl_recv(like: Tensor, src: int, comm: str) -> Tensor:
+    out = torch.empty_like(like, memory_format=torch.contiguous_format)
+    _get(comm).recv(out, src, False)
+    return out
+
+
+def _impl_gather_single(input: Tensor, root: int, comm: str) -> Tensor:
+    c = _get(comm)
+    x = input.contiguous()
+    out = x.new_zeros((x.shape[0] * c.get_size(),) + tuple(x.shape[1:]))   # meaningful on the root only
+    c.gather_single(out, x, root, False)
+    return out
+
+
+def _impl_scatter(input: Tensor, root: int, comm: str) -> Tensor:
+    c = _get(comm)
+    n = c.get_size()
+    x = input.contiguous()
+    out = x.new_empty((x.shape[0] // n,) + tuple(x.shape[1:]))
+    c.scatter(out, list(x.chunk(n, 0)) if c.get_rank() == root else [], root, False)
+    return out
+
+
+for _op, _fn in (("send", _impl_send), ("recv", _impl_recv), ("gather_single", _impl_gather_single), ("scatter", _impl_scatter)):
+    _lib.impl(_op, _fn, "CompositeExplicitAutograd")
+
+
+@torch.library.register_fake(f"{NAMESPACE}::send")
+def _fake_send(input, dst, comm):
+    return torch.empty_like(input, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake(f"{NAMESPACE}::recv")
+def _fake_recv(like, src, comm):
+    return torch.empty_like(like, memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake(f"{NAMESPACE}::gather_single")
+def _fake_gather_single(input, root, comm):
+    return input.new_empty((input.shape[0] * _size(comm),) + tuple(input.shape[1:]))
+
+
+@torch.library.register_fake(f"{NAMESPACE}::scatter")
+def _fake_scatter(input, root, comm):
+    return input.new_empty((input.shape[0] // _size(comm),) + tuple(input.shape[1:]))
+
+
+def _bw_send(ctx, grad):
+    dst, comm = ctx.args
+    return _ops.recv(grad.contiguous(), dst, comm), None, None
+
+
+def _bw_recv(ctx, grad):
+    src, comm = ctx.args
+    _ops.send(grad.contiguous(), src, comm)
+    return None, None, None
+
+
+def _bw_gather_single(ctx, grad):
+    root, comm = ctx.args
+    return _ops.scatter(grad.contiguous(), root, comm), None, None
+
+
+def _bw_scatter(ctx, grad):
+    root, comm = ctx.args
+    return _ops.gather_single(grad.contiguous(), root, comm), None, None
+
+
+torch.library.register_autograd(f"{NAMESPACE}::send", _bw_send, setup_context=_setup)
+torch.library.register_autograd(f"{NAMESPACE}::recv", _bw_recv, setup_context=_setup)
+torch.library.register_autograd(f"{NAMESPACE}::gather_single", _bw_gather_single, setup_context=_setup)
+torch.library.register_autograd(f"{NAMESPACE}::scatter", _bw_scatter, setup_context=_setup)
+
+
+def send(x: Tensor, dst: int, comm: Union[TorchComm, str]) -> Tensor:
+    """Sends ``x`` to ``dst``; returns a copy of ``x`` whose gradient arrives from ``dst``."""
+    return _ops.send(x, dst, _name(comm))
+
+
+def recv(like: Tensor, src: int, comm: Union[TorchComm, str]) -> Tensor:
+    """Receives a tensor shaped like ``like`` from ``src``; its gradient is sent back to ``src``."""
+    return _ops.recv(like, src, _name(comm))
+
+
+def gather_single(x: Tensor, root: int, comm: Union[TorchComm, str]) -> Tensor:
+    """``[n0, ...] -> [world * n0, ...]`` on ``root`` (zeros elsewhere)."""
+    return _ops.gather_single(x, root, _name(comm))
+
+
+def scatter(x: Tensor, root: int, comm: Union[TorchComm, str]) -> Tensor:
+    """``[world * n0, ...]`` on ``root`` ``-> [n0, ...]`` on every rank."""
+    return _ops.scatter(x, root, _name(comm))
+
+
 __all__ = [
+    "send", "recv", "gather_single", "scatter",
     "register_comm", "unregister_comm", "is_torch_compile_supported", "is_torch_compile_supported_and_enabled",
     "all_reduce", "all_reduce_", "all_gather_single", "reduce_scatter_single", "all_to_all_single", "broadcast",
     "broadcast_", "reduce", "barrier", "wait_tensor",
