@@ -225,7 +225,8 @@ def test_pipeline_schedules_match_single_process(schedule):
 
 def _context_worker(rank, world):
     import torchcomms_b200 as tc
-    from torchcomms_b200.parallel.context import ring_attention, ulysses_attention
+    from torchcomms_b200.parallel.context import (ring_attention, shard_positions, ulysses_attention, zigzag_shard,
+                                                   zigzag_unshard)
 
     comm = tc.new_comm("gloo", torch.device("cpu"), name="cp", timeout=timedelta(seconds=60))
     torch.manual_seed(1)
@@ -238,6 +239,18 @@ def _context_worker(rank, world):
         torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-5)
         got = ulysses_attention(q[:, :, sl].contiguous(), k[:, :, sl].contiguous(), v[:, :, sl].contiguous(), comm, causal=causal)
         torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-5)
+        # zigzag layout: rank r holds chunks r and 2*world-1-r of the sequence
+        full = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=causal)
+        zq, zk, zv = (zigzag_shard(t, rank, world).contiguous() for t in (q, k, v))
+        got = ring_attention(zq, zk, zv, comm, causal=causal, layout="zigzag")
+        torch.testing.assert_close(got, zigzag_shard(full, rank, world), rtol=1e-4, atol=1e-5)
+    pos = [shard_positions(r, world, s // world, "zigzag") for r in range(world)]
+    assert sorted(torch.cat(pos).tolist()) == list(range(s))
+    # the causal work (visible key count) is the same on every rank, unlike the contiguous layout
+    assert len({int((p + 1).sum()) for p in pos}) == 1
+    assert len({int((shard_positions(r, world, s // world) + 1).sum()) for r in range(world)}) == world
+    parts = [zigzag_shard(q, r, world) for r in range(world)]
+    assert torch.equal(zigzag_unshard(parts), q)
     comm.finalize()
 
 

@@ -8,6 +8,8 @@ Both shard the sequence over the ranks of a communicator.
   so the full score matrix never exists.  The transfer of step ``i + 1`` is
   issued before the math of step ``i`` (asynchronous batch on the
   communicator's side stream) and waited for afterwards.
+  With ``layout="zigzag"`` (``zigzag_shard`` / ``zigzag_unshard``) causal attention is
+  load-balanced over the ranks.
 * ``ulysses_attention``: one all-to-all turns sequence shards into head
   shards, attention runs locally over the full sequence for ``heads / n``
   heads, a second all-to-all turns the result back.
@@ -48,9 +50,46 @@ def _merge(o: torch.Tensor, lse: torch.Tensor, o2: torch.Tensor, lse2: torch.Ten
     return o * w1 + o2 * w2, new
 
 
+def shard_positions(rank: int, world: int, seq_local: int, layout: str = "contiguous", device=None) -> torch.Tensor:
+    """Global sequence positions of the ``seq_local`` tokens rank ``rank`` holds.
+
+    ``contiguous``: rank r holds ``[r * seq_local, (r + 1) * seq_local)``.
+    ``zigzag``: the sequence is cut into ``2 * world`` chunks and rank r holds chunks ``r`` and
+    ``2 * world - 1 - r`` - with a causal mask every rank then has the same amount of attention work,
+    where the contiguous layout leaves rank 0 almost idle and the last rank with all of it.
+    """
+    if layout == "contiguous":
+        return torch.arange(seq_local, device=device) + rank * seq_local
+    if layout != "zigzag":
+        raise ValueError(f"unknown layout '{layout}'")
+    if seq_local % 2:
+        raise ValueError("the zigzag layout needs an even number of local tokens")
+    half = seq_local // 2
+    lo = torch.arange(half, device=device) + rank * half
+    hi = torch.arange(half, device=device) + (2 * world - 1 - rank) * half
+    return torch.cat([lo, hi])
+
+
+def zigzag_shard(x: torch.Tensor, rank: int, world: int, dim: int = -2) -> torch.Tensor:
+    """This rank's part of a full-sequence tensor in the zigzag layout (sequence on ``dim``)."""
+    chunks = x.chunk(2 * world, dim)
+    return torch.cat([chunks[rank], chunks[2 * world - 1 - rank]], dim)
+
+
+def zigzag_unshard(parts, dim: int = -2) -> torch.Tensor:
+    """Inverse of ``zigzag_shard``: ``parts[r]`` is rank r's tensor; returns the full sequence."""
+    world = len(parts)
+    chunks = [None] * (2 * world)
+    for r, p in enumerate(parts):
+        lo, hi = p.chunk(2, dim)
+        chunks[r], chunks[2 * world - 1 - r] = lo, hi
+    return torch.cat(chunks, dim)
+
+
 def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, comm: TorchComm, causal: bool = False,
-                   scale: Optional[float] = None) -> torch.Tensor:
-    """q, k, v: [batch, heads, seq_local, head_dim]; rank r holds sequence positions [r*seq_local, (r+1)*seq_local)."""
+                   scale: Optional[float] = None, layout: str = "contiguous") -> torch.Tensor:
+    """q, k, v: [batch, heads, seq_local, head_dim]; which global positions the local tokens have is given by
+    ``layout`` (see ``shard_positions``)."""
     n, rank = comm.get_size(), comm.get_rank()
     sq, d = q.shape[-2], q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
@@ -58,7 +97,7 @@ def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, comm: Torc
     kv = torch.stack([k, v]).contiguous()
     out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
     lse = torch.full(q.shape[:-1], float("-inf"), dtype=torch.float32, device=q.device)
-    pos_q = torch.arange(sq, device=q.device) + rank * sq
+    pos_q = shard_positions(rank, n, sq, layout, q.device)
     for step in range(n):
         src = (rank - step) % n          # whose K/V block we hold now
         work, incoming = None, None
@@ -71,10 +110,10 @@ def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, comm: Torc
         mask = None
         skip = False
         if causal:
-            if src > rank:
+            pos_k = shard_positions(src, n, sq, layout, q.device)
+            if layout == "contiguous" and src > rank:
                 skip = True              # that block lies entirely in the future
-            elif src == rank:
-                pos_k = torch.arange(sq, device=q.device) + src * sq
+            elif layout != "contiguous" or src == rank:
                 mask = pos_q.unsqueeze(-1) >= pos_k.unsqueeze(0)
         if not skip:
             o2, l2 = _block_attention(q, kv[0], kv[1], scale, mask)
