@@ -1,6 +1,7 @@
 // "fake" and "gloo" backends.
 #include "cpu_backends.hpp"
 
+#include <mutex>
 #include <unistd.h>
 
 #include <random>
@@ -210,6 +211,9 @@ class GlooWork final : public Work {
 
  protected:
   void do_wait() override {
+    // Several threads may wait on one work (the caller, and the thread that completes the
+    // c10d future of the same operation): the first one waits, the others wait for it.
+    std::lock_guard<std::mutex> g(wait_mu_);
     if (done_) {
       return;
     }
@@ -243,6 +247,7 @@ class GlooWork final : public Work {
   std::vector<c10::intrusive_ptr<c10d::Work>> inner_;
   std::function<void()> post_;
   std::weak_ptr<Backend> owner_;
+  std::mutex wait_mu_;
   bool done_ = false;
 };
 

@@ -13,6 +13,7 @@
 // Parity: comms/torchcomms/BackendWrapper.hpp:20-219, BackendWrapper.cpp:18-58
 // (reduce-op mapping), :200-236 (future / wait), :298 (allreduce), :714
 // (monitoredBarrier over p2p), :942-949 (coalescing), :1046 (split).
+#include <thread>
 #include <torch/csrc/distributed/c10d/Backend.hpp>
 #include <torch/csrc/distributed/c10d/Work.hpp>
 
@@ -93,13 +94,28 @@ class WorkWrapper final : public c10d::Work {
       inner_->wait();
       future_->markCompleted(c10::IValue(outputs_));
     } else {
+      // Host work. Callers such as DistributedDataParallel keep only the future and drop the
+      // work, and a work of the gloo backend completes when somebody waits on it, so a helper
+      // thread waits and then completes the future (or gives it the error).
       auto fut = future_;
       auto outs = outputs_;
-      inner_->on_end([fut, outs]() {
-        if (!fut->completed()) {
-          fut->markCompleted(c10::IValue(outs));
-        }
-      });
+      auto inner = inner_;
+      if (inner->is_completed()) {
+        fut->markCompleted(c10::IValue(outs));
+      } else {
+        std::thread([fut, outs, inner]() {
+          try {
+            inner->wait();
+            if (!fut->completed()) {
+              fut->markCompleted(c10::IValue(outs));
+            }
+          } catch (...) {
+            if (!fut->completed()) {
+              fut->setError(std::current_exception());
+            }
+          }
+        }).detach();
+      }
     }
     return future_;
   }
