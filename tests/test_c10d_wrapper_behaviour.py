@@ -1,0 +1,91 @@
+"""Behaviour of the c10d adapter and of communicator lifetime on gloo ranks: aliased all-gather
+outputs, shutdown / destroy more than once, several communicators side by side,
+``wait_blocking``, init handles, DDP-style dropped works.
+
+Modelled on comms/torchcomms/tests/integration/py/BackendWrapperAllGatherAliasedTest.py,
+BackendWrapperShutdownTest.py, MultiCommTest.py, WaitBlockingTest.py and GetInitHandleTest.py.
+"""
+from datetime import timedelta
+
+import torch
+
+from tests.mp_util import run_ranks
+
+
+def _worker(rank, world):
+    import torch.distributed as dist
+
+    import torchcomms_b200 as tc
+    from torchcomms_b200.device_mesh import init_device_mesh
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="wrap", timeout=timedelta(seconds=60))
+    pg = init_device_mesh(mesh_dim_comms=(comm,), mesh_dim_names=("w",)).get_group("w")
+
+    # distinct outputs: per-rank inputs in rank order
+    outs = [torch.empty(1) for _ in range(world)]
+    dist.all_gather(outs, torch.tensor([float(rank)]), group=pg)
+    assert [o.item() for o in outs] == [float(r) for r in range(world)]
+    # aliased outputs ([buf] * N): no race, the last rank's value wins, and the next call is clean
+    shared = torch.full((1,), -1.0)
+    dist.all_gather([shared] * world, torch.tensor([float(rank)]), group=pg)
+    assert shared.item() == float(world - 1)
+    outs = [torch.empty(1) for _ in range(world)]
+    dist.all_gather(outs, torch.tensor([float(rank) + 10]), group=pg)
+    assert [o.item() for o in outs] == [float(r) + 10 for r in range(world)]
+
+    # a caller that keeps only the future (what DistributedDataParallel's reducer does)
+    t = torch.full((3,), float(rank + 1))
+    fut = dist.all_reduce(t, group=pg, async_op=True).get_future()
+    fut.wait()
+    assert torch.equal(t, torch.full((3,), float(world * (world + 1) // 2)))
+    # ... and one that waits on both the work and the future
+    t = torch.ones(3)
+    w = dist.all_reduce(t, group=pg, async_op=True)
+    f = w.get_future()
+    w.wait()
+    f.wait()
+    assert torch.equal(t, torch.full((3,), float(world)))
+
+    # several communicators side by side, interleaved operations, independent lifetimes
+    a = tc.new_comm("gloo", torch.device("cpu"), name="multi_a", timeout=timedelta(seconds=60))
+    b = tc.new_comm("gloo", torch.device("cpu"), name="multi_b", timeout=timedelta(seconds=60))
+    ta, tb = torch.full((4,), 1.0), torch.full((4,), 2.0)
+    wa = a.all_reduce(ta, tc.ReduceOp.SUM, True)
+    wb = b.all_reduce(tb, tc.ReduceOp.SUM, True)
+    wb.wait()
+    wa.wait()
+    assert torch.equal(ta, torch.full((4,), float(world))) and torch.equal(tb, torch.full((4,), 2.0 * world))
+    a.finalize()
+    tb.fill_(1.0)
+    b.all_reduce(tb, tc.ReduceOp.MAX, False)                   # b is untouched by a's finalize
+    assert torch.equal(tb, torch.ones(4))
+
+    # wait_blocking blocks the host until the result is there
+    tw = torch.full((2,), float(rank))
+    work = b.all_reduce(tw, tc.ReduceOp.SUM, True)
+    work.wait_blocking()
+    assert work.is_completed() and torch.equal(tw, torch.full((2,), float(sum(range(world)))))
+    b.finalize()
+
+    # init handles: "<backend>:<rank>:<uuid>:<address>", distinct per rank and per communicator
+    from torchcomms_b200.utils.store import create_prefix_store
+
+    store = create_prefix_store("handles", timedelta(seconds=30))
+    r1 = tc.new_comm("gloo", torch.device("cpu"), name="h1", store=store, enable_reconfigure=True, timeout=timedelta(seconds=30))
+    r2 = tc.new_comm("gloo", torch.device("cpu"), name="h2", store=store, enable_reconfigure=True, timeout=timedelta(seconds=30))
+    h1, h2 = r1.get_init_handle(), r2.get_init_handle()
+    parts = h1.split(":")
+    assert h1 != h2 and parts[0] == "gloo" and int(parts[1]) == rank and len(parts) >= 4
+
+    # shutdown through the c10d wrapper finalizes the communicator; doing it again is harmless
+    backend = pg._get_backend(torch.device("cpu"))
+    backend.shutdown()
+    backend.shutdown()
+    import pytest
+
+    with pytest.raises(RuntimeError):
+        comm.all_reduce(torch.ones(1), tc.ReduceOp.SUM, False)
+
+
+def test_c10d_wrapper_and_lifetime_behaviour():
+    run_ranks(_worker, 2, timeout=120)

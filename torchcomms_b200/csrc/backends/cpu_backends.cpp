@@ -1,6 +1,7 @@
 // "fake" and "gloo" backends.
 #include "cpu_backends.hpp"
 
+#include <cstdio>
 #include <mutex>
 #include <unistd.h>
 
@@ -291,7 +292,16 @@ void GlooBackend::init(at::Device device, const std::string& name, const CommOpt
   std::random_device rd;
   char host[256] = {0};
   gethostname(host, sizeof(host) - 1);
-  handle_token_ = std::string(host) + "." + std::to_string(getpid()) + "." + std::to_string(rd()) + "." + name;
+  // "<launcher rank>:<unique id>:<host>:<pid>" behind the backend name, the layout of the reference's
+  // handles (comms/torchcomms/ncclx/TorchCommNCCLXReconfigure.cpp:176-205: "ncclx:<rank>:<uuid>:<host:port>").
+  int launcher_rank = -1;
+  try {
+    launcher_rank = query_ranksize().first;
+  } catch (const std::exception&) {
+  }
+  char uid[32];
+  std::snprintf(uid, sizeof(uid), "%08x%08x", static_cast<unsigned>(rd()), static_cast<unsigned>(rd()));
+  handle_token_ = std::to_string(launcher_rank) + ":" + uid + "." + name + ":" + std::string(host) + ":" + std::to_string(getpid());
   if (opts.enable_reconfigure) {
     TORCH_CHECK(opts.store, "enable_reconfigure needs a store shared by all candidate ranks");
     store_ = opts.store;
