@@ -1,0 +1,87 @@
+"""Less-travelled parts of the communicator API on gloo ranks: persistent all-gather,
+gather / scatter / all_to_all lists, PREMUL_SUM and AVG, per-call timeouts and hints,
+use after finalize.
+
+Modelled on comms/torchcomms/tests/integration/py/AllGatherPTest.py, GatherTest.py,
+ScatterTest.py, AllToAllTest.py, OptionsTest.py and FinalizeWarningTest.py.
+"""
+from datetime import timedelta
+
+import pytest
+import torch
+
+from tests.mp_util import run_ranks
+
+
+def _worker(rank, world):
+    import torchcomms_b200 as tc
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="corners", timeout=timedelta(seconds=60), hints={"note": "x"})
+    assert comm.get_options().hints.get("note") == "x" and comm.get_options().timeout == timedelta(seconds=60)
+
+    # persistent all-gather: the output is bound once, executed many times with fresh inputs
+    out = torch.zeros(world * 4)
+    handle = comm.all_gather_p_init(out)
+    for it in range(3):
+        w = comm.all_gather_p_exec(handle, torch.full((4,), float(10 * it + rank)), it % 2 == 1)
+        w.wait()
+        assert torch.equal(out, torch.tensor([float(10 * it + r) for r in range(world)]).repeat_interleave(4))
+    comm.all_gather_p_free(handle)
+    with pytest.raises(RuntimeError):
+        comm.all_gather_p_exec(handle, torch.zeros(4), False)
+
+    # gather / scatter with lists (only the root's lists matter), all_to_all with lists
+    outs = [torch.zeros(2) for _ in range(world)] if rank == 1 else []
+    comm.gather(outs, torch.full((2,), float(rank)), 1, False)
+    if rank == 1:
+        assert [o[0].item() for o in outs] == [float(r) for r in range(world)]
+    got = torch.zeros(3)
+    comm.scatter(got, [torch.full((3,), float(100 + r)) for r in range(world)] if rank == 0 else [], 0, False)
+    assert torch.equal(got, torch.full((3,), float(100 + rank)))
+    recv = [torch.zeros(1) for _ in range(world)]
+    comm.all_to_all(recv, [torch.tensor([float(10 * rank + p)]) for p in range(world)], False)
+    assert [t.item() for t in recv] == [float(10 * p + rank) for p in range(world)]
+    gs = torch.zeros(world, 2) if rank == 0 else torch.zeros(0)
+    comm.gather_single(gs, torch.full((1, 2), float(rank)), 0, False)
+    if rank == 0:
+        assert torch.equal(gs[:, 0], torch.arange(world, dtype=torch.float32))
+
+    # PREMUL_SUM (host factor and tensor factor) and AVG
+    t = torch.full((4,), float(rank + 1))
+    comm.all_reduce(t, tc.ReduceOp.PREMUL_SUM(0.5), False)
+    assert torch.equal(t, torch.full((4,), 0.5 * sum(range(1, world + 1))))
+    t = torch.full((4,), float(rank + 1))
+    comm.all_reduce(t, tc.ReduceOp.PREMUL_SUM(torch.tensor(2.0)), False)
+    assert torch.equal(t, torch.full((4,), 2.0 * sum(range(1, world + 1))))
+    t = torch.full((4,), float(rank + 1))
+    comm.all_reduce(t, tc.ReduceOp.AVG, False)
+    assert torch.allclose(t, torch.full((4,), sum(range(1, world + 1)) / world))
+    ti = torch.full((4,), rank + 1, dtype=torch.int64)
+    comm.all_reduce(ti, tc.ReduceOp.BOR, False)                # bitwise operators on integral types
+    assert int(ti[0]) == (1 | 2 if world == 2 else int(ti[0]))
+
+    # shape rules are checked before anything is sent
+    with pytest.raises(RuntimeError):
+        comm.all_gather_single(torch.zeros(world * 4 + 1), torch.zeros(4), False)
+    with pytest.raises(RuntimeError):
+        comm.reduce_scatter_single(torch.zeros(3), torch.zeros(3 * world + 1), tc.ReduceOp.SUM, False)
+    with pytest.raises(RuntimeError):
+        comm.all_reduce(torch.zeros(4, 4).t(), tc.ReduceOp.SUM, False)      # not contiguous
+    with pytest.raises(RuntimeError):
+        comm.send(torch.zeros(1), world, False)                             # rank out of range
+
+    # per-call timeout and hints are accepted on every operation
+    t = torch.ones(2)
+    comm.all_reduce(t, tc.ReduceOp.SUM, False, hints={"algo": "auto"}, timeout=timedelta(seconds=5))
+    comm.barrier(False, timeout=timedelta(seconds=5))
+
+    # use after finalize, and double finalize, raise
+    comm.finalize()
+    with pytest.raises(RuntimeError):
+        comm.all_reduce(torch.ones(1), tc.ReduceOp.SUM, False)
+    with pytest.raises(RuntimeError):
+        comm.finalize()
+
+
+def test_api_corners_on_gloo():
+    run_ranks(_worker, 2, timeout=120)
