@@ -426,3 +426,30 @@ def test_comm_dump_and_comm_dump_all():
     gc.collect()
     assert "dump_a" not in tc.comm_dump_all() and "dump_b" in tc.comm_dump_all()
     b.finalize()
+
+
+def test_flight_recorder_dumps_on_abort(tmp_path, monkeypatch):
+    """The recorder's abort hook writes the ring to ``<prefix><rank>`` (hooks/fr/tests/py/FlightRecorderAbortTest.py)."""
+    import json
+
+    import torchcomms_b200 as tc
+    from torchcomms_b200.hooks import fr
+
+    monkeypatch.setenv("TORCHCOMM_FR_DUMP_TEMP_FILE", str(tmp_path / "fr_trace_"))
+    comm = tc.new_comm("fake", torch.device("cpu"), name="fr_abort", abort_process_on_timeout_or_error=False)
+    rec = fr.FlightRecorderHook(8)
+    rec.register_with_comm(comm)
+    for _ in range(3):
+        comm.all_reduce(torch.ones(4), tc.ReduceOp.SUM, False)
+    comm.barrier(False)
+    assert rec.size() == 4 and rec.capacity() == 8
+    comm.abort()
+    dump = tmp_path / "fr_trace_0"
+    assert dump.exists()
+    data = json.loads(dump.read_text())
+    entries = data["entries"] if isinstance(data, dict) else data
+    names = [e.get("profiling_name", e.get("op", "")) for e in entries]
+    assert len(entries) == 4 and any("all_reduce" in n for n in names) and any("barrier" in n for n in names)
+    # the ring keeps the newest entries
+    rec.reset()
+    assert rec.size() == 0
