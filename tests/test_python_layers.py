@@ -180,6 +180,26 @@ def _functional_worker(rank, world):
     compiled = torch.compile(f, backend="aot_eager", fullgraph=True)
     out = compiled(torch.full((2, 3), float(rank)))
     assert torch.equal(out, torch.full((2, 3), float(rank) * world * 2))
+
+    # graph passes: a collective whose input dies at the call runs in place, wait_tensor goes away
+    from torchcomms_b200.functional.passes import count_ops, reinplace_pass, strip_wait_pass
+
+    def g(v):
+        a = F.all_reduce(v * 2, "sum", "fn")            # v * 2 is dead after the call: re-inplaced
+        b = F.all_reduce(v, "sum", "fn")                # v is a graph input: stays functional
+        k = v + 1
+        c = F.all_reduce(k, "sum", "fn")                # k is read again below: stays functional
+        return F.wait_tensor(a) + b + c + k
+
+    gm2 = make_fx(g, tracing_mode="fake")(torch.ones(2, 3))
+    assert count_ops(gm2) == {"all_reduce": 3, "wait_tensor": 1}
+    strip_wait_pass(reinplace_pass(gm2))
+    assert count_ops(gm2) == {"all_reduce_": 1, "all_reduce": 2}
+    x = torch.full((2, 3), float(rank + 1))
+    keep = x.clone()
+    total = float(sum(range(1, world + 1)))
+    torch.testing.assert_close(gm2(x), torch.full((2, 3), 4 * total + world) + keep + 1)
+    assert torch.equal(x, keep)                         # the caller's tensor was not written
     comm.finalize()
 
 
