@@ -85,3 +85,39 @@ def _worker(rank, world):
 
 def test_api_corners_on_gloo():
     run_ranks(_worker, 2, timeout=120)
+
+
+def _sparse_worker(rank, world):
+    import torchcomms_b200 as tc
+    from torchcomms_b200.ops.sparse import all_reduce_sparse_block
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="sparse", timeout=timedelta(seconds=60))
+    # the worked example of comms/ncclx/v2_30/src/nccl.h.in:574-584 (block length 2, 14 elements)
+    contrib = {
+        0: ([1, 2, 3, 6, 7], [0, 2, 4, 10, 12]),
+        1: ([2, 3, 5, 6], [2, 4, 8, 10]),
+        2: ([1, 3, 4, 6], [0, 4, 6, 10]),
+        3: ([1, 2, 3, 4, 5, 6, 7], [0, 2, 4, 6, 8, 10, 12]),
+    }
+    vals, idx = contrib[rank]
+    send = torch.tensor(vals, dtype=torch.float32).repeat_interleave(2)
+    expect = torch.tensor([3, 3, 6, 6, 12, 12, 8, 8, 10, 10, 24, 24, 14, 14], dtype=torch.float32)
+    for mode in ("gather", "dense", "auto"):
+        recv = torch.full((14,), -1.0)
+        all_reduce_sparse_block(comm, send, torch.tensor(idx), 2, recv, mode=mode)
+        assert torch.equal(recv, expect), (mode, recv)
+    # a rank with nothing to contribute, and a sparse case where the gather route is chosen
+    big = torch.full((4096,), -1.0)
+    mine = torch.tensor([128 * rank]) if rank % 2 == 0 else torch.empty(0, dtype=torch.int64)
+    all_reduce_sparse_block(comm, torch.ones(mine.numel() * 4), mine, 4, big)
+    ref = torch.zeros(4096)
+    for r in range(0, world, 2):
+        ref[128 * r:128 * r + 4] = 1
+    assert torch.equal(big, ref)
+    with pytest.raises(ValueError):
+        all_reduce_sparse_block(comm, torch.ones(4), torch.tensor([4094]), 4, big)
+    comm.finalize()
+
+
+def test_all_reduce_sparse_block():
+    run_ranks(_sparse_worker, 4, timeout=120)
