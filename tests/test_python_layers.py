@@ -55,6 +55,42 @@ def _distwrap_worker(rank, world):
     dist.all_reduce(s, group=sub)
     assert torch.equal(s, torch.full((2,), float(world // 2)))
     dist.broadcast(s, src=halves[rank // (world // 2)][0], group=sub)
+    # list collectives, rooted collectives, blocking point-to-point, object gather / scatter
+    lst_out = [torch.empty(2) for _ in range(world)]
+    dist.all_gather(lst_out, torch.full((2,), float(rank)))
+    assert [t[0].item() for t in lst_out] == [float(r) for r in range(world)]
+    a2a_out = [torch.empty(1) for _ in range(world)]
+    dist.all_to_all(a2a_out, [torch.tensor([float(10 * rank + p)]) for p in range(world)])
+    assert [t.item() for t in a2a_out] == [float(10 * p + rank) for p in range(world)]
+    red = torch.full((2,), float(rank + 1))
+    dist.reduce(red, dst=2)
+    if rank == 2:
+        assert torch.equal(red, torch.full((2,), float(sum(range(1, world + 1)))))
+    rs_out = torch.empty(2)
+    dist.reduce_scatter(rs_out, [torch.full((2,), float(p)) for p in range(world)])
+    assert torch.equal(rs_out, torch.full((2,), float(rank * world)))
+    gathered = [torch.empty(1) for _ in range(world)] if rank == 0 else None
+    dist.gather(torch.tensor([float(rank)]), gathered, dst=0)
+    if rank == 0:
+        assert [t.item() for t in gathered] == [float(r) for r in range(world)]
+    sc = torch.empty(1)
+    dist.scatter(sc, [torch.tensor([float(100 + p)]) for p in range(world)] if rank == 1 else None, src=1)
+    assert sc.item() == float(100 + rank)
+    if rank == 0:
+        dist.send(torch.tensor([42.0]), dst=1)
+    elif rank == 1:
+        box = torch.empty(1)
+        dist.recv(box, src=0)
+        assert box.item() == 42.0
+    og = [None] * world if rank == 3 else None
+    dist.gather_object({"from": rank}, og, dst=3)
+    if rank == 3:
+        assert [o["from"] for o in og] == list(range(world))
+    so = [None]
+    dist.scatter_object_list(so, [f"for{p}" for p in range(world)] if rank == 0 else None, src=0)
+    assert so[0] == f"for{rank}"
+    assert dist.get_torchcomms_instance().get_size() == world
+
     # plain torch.distributed calls land on the same communicator
     import torch.distributed as td
 

@@ -444,7 +444,7 @@ def gather_object(obj: Any, object_gather_list: Optional[List[Any]] = None, dst:
     if not _enabled:
         return _td.gather_object(obj, object_gather_list, dst=dst, group=group, group_dst=group_dst)
     root = group_dst if group_dst is not None else _group_rank(group, dst or 0)
-    objcol.gather_object(get_torchcomms_instance(group), obj, object_gather_list, root)
+    objcol.gather_object(get_torchcomms_instance(group), obj, root, object_gather_list=object_gather_list)
 
 
 def broadcast_object_list(object_list: List[Any], src: Optional[int] = None, group: Any = None, device: Any = None,
@@ -461,7 +461,8 @@ def scatter_object_list(scatter_object_output_list: List[Any], scatter_object_in
         return _td.scatter_object_list(scatter_object_output_list, scatter_object_input_list, src=src, group=group,
                                        group_src=group_src)
     root = group_src if group_src is not None else _group_rank(group, src or 0)
-    objcol.scatter_object_list(get_torchcomms_instance(group), scatter_object_output_list, scatter_object_input_list, root)
+    objcol.scatter_object_list(get_torchcomms_instance(group), root, scatter_object_output_list,
+                               scatter_object_input_list=scatter_object_input_list)
 
 
 # -------------------------------------------------------------- extensions ---
