@@ -120,3 +120,22 @@ def test_missing_queries_and_no_peer_access():
     assert topo.pairs == [[T.SELF, T.NONE], [T.NONE, T.SELF]] and topo.domains() == [[0], [1]]
     assert topo.gpus[0].numa_node == -1 and topo.gpus[0].pci_bus_id == "" and not topo.nvlink_all_to_all
     assert T.discover(FakeNvml(0, set(), switch=False)).nvlink_all_to_all is False
+
+
+def test_clock_sampler_summary_and_missing_tool(monkeypatch):
+    """The sampler parses nvidia-smi rows into median clock and throttle reasons, and is inert where the tool is absent."""
+    from torchcomms_b200.utils.clocks import ClockSampler
+
+    s = ClockSampler(0)
+    s.rows = [
+        ["0", "1965", "1965", "412.1", "0x0000000000000000", "Not Active", "Not Active", "Not Active", "Not Active"],
+        ["0", "1410", "1965", "998.7", "0x0000000000000004", "Not Active", "Not Active", "Not Active", "Active"],
+        ["0", "1395", "1965", "1001.2", "0x0000000000000004", "Not Active", "Not Active", "Not Active", "Active"],
+        ["0", "[N/A]", "1965", "x", "", "", "", "", ""],
+    ]
+    out = s.summary()
+    assert out == {"sm_mhz": 1410.0, "sm_max_mhz": 1965.0, "reasons": ["sw_power_cap"], "samples": 3}
+    monkeypatch.setenv("PATH", "/nonexistent")
+    with ClockSampler(0) as absent:
+        pass
+    assert absent.summary() == {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
