@@ -146,6 +146,14 @@ def _dp_tp_worker(rank, world):
     ref = _mlp(0)
     (sum(ref(_batch(d, 0)).pow(2).mean() for d in range(2))).backward()
     torch.testing.assert_close(g, ref[2].bias.grad, rtol=1e-5, atol=1e-6)
+    # the two dimensions flattened onto the world communicator give a 1-D mesh whose group spans all ranks
+    from torchcomms_b200.device_mesh import _flatten_with_comm
+
+    flat = _flatten_with_comm(mesh, "dp_tp", comm, list(range(world)))
+    assert flat.ndim == 1 and flat.size() == world
+    t = torch.full((2,), float(rank))
+    dist.all_reduce(t, group=flat.get_group("dp_tp"))
+    assert torch.equal(t, torch.full((2,), float(sum(range(world)))))
     for c in (tp_comm, dp_comm, comm):
         c.finalize()
 
