@@ -312,3 +312,23 @@ def _store_worker(rank, world):
 
 def test_prefix_store_and_duplicate_store():
     run_ranks(_store_worker, 2, timeout=120)
+
+
+def _objcol_pickle_worker(rank, world):
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import objcol
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="objpickle", timeout=timedelta(seconds=60))
+    objs = [None] * world
+    objcol.all_gather_object(comm, objs, {"rank": rank, "t": torch.arange(rank + 1)})
+    assert [o["rank"] for o in objs] == list(range(world)) and torch.equal(objs[1]["t"], torch.arange(2))
+    # weights_only refuses arbitrary classes on the torch.save route and accepts plain containers
+    lst = [{"a": [1, 2, 3], "w": torch.ones(2)}] if rank == 0 else [None]
+    objcol.broadcast_object_list(comm, lst, 0, weights_only=True)
+    assert lst[0]["a"] == [1, 2, 3] and torch.equal(lst[0]["w"], torch.ones(2))
+    comm.finalize()
+
+
+@pytest.mark.parametrize("serialization", ["pickle", "torch"])
+def test_object_collectives_serialization_modes(serialization):
+    run_ranks(_objcol_pickle_worker, 2, timeout=120, extra_env={"TORCHCOMMS_SERIALIZATION": serialization})
