@@ -1,6 +1,12 @@
 // CUDA backend: bootstrap, stream/event protocol, watchdog, algorithm choice.
 #include "cuda_backend.hpp"
 
+#include <unistd.h>
+
+#include <cstdio>
+#include <random>
+#include <tuple>
+
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
@@ -250,8 +256,16 @@ void CudaBackend::set_hints(const Hints& h) {
 
 void CudaBackend::init(at::Device device, const std::string& name, const CommOptions& opts) {
   TORCH_CHECK(device.is_cuda(), "the '", registered_as_, "' backend needs a CUDA device, got ", device);
-  TORCH_CHECK(!opts.enable_reconfigure, "the CUDA backend does not support enable_reconfigure");
-  auto [rank, size] = query_ranksize();
+  int rank = 0, size = 1;
+  if (opts.enable_reconfigure) {
+    try {
+      std::tie(rank, size) = query_ranksize();
+    } catch (const std::exception&) {
+      rank = 0;  // candidates need not come from one launcher
+    }
+  } else {
+    std::tie(rank, size) = query_ranksize();
+  }
   int ndev = 0;
   B200C_CUDA_CHECK(cudaGetDeviceCount(&ndev));
   TORCH_CHECK(ndev > 0, "no CUDA device is visible");
@@ -260,6 +274,22 @@ void CudaBackend::init(at::Device device, const std::string& name, const CommOpt
   name_ = name;
   opts_ = opts;
   parse_tuning(opts.hints);
+  {
+    // "<launcher rank>:<unique id>.<name>:<host>:<pid>", shown behind the backend name by get_init_handle().
+    std::random_device rd;
+    char host[256] = {0};
+    gethostname(host, sizeof(host) - 1);
+    char uid[32];
+    std::snprintf(uid, sizeof(uid), "%08x%08x", static_cast<unsigned>(rd()), static_cast<unsigned>(rd()));
+    handle_token_ = std::to_string(rank) + ":" + uid + "." + name + ":" + std::string(host) + ":" + std::to_string(getpid());
+  }
+  if (opts.enable_reconfigure) {
+    // Membership arrives with reconfigure(); until then the communicator owns no device resources.
+    TORCH_CHECK(opts.store, "enable_reconfigure needs a store shared by all candidate ranks");
+    rank_ = -1;
+    size_ = 0;
+    return;
+  }
   auto store = opts.store ? scoped_store(opts.store, "b200c/cuda/" + name)
                           : create_prefix_store("b200c/cuda/" + name, rank, size, opts.timeout);
   bootstrap(store, rank, size);
@@ -603,26 +633,40 @@ void CudaBackend::watchdog_loop() {
 }
 
 void CudaBackend::finalize() {
-  TORCH_CHECK(initialized_, "communicator '", name_, "' is not initialised");
   TORCH_CHECK(!finalized_, "communicator '", name_, "' was already finalized");
+  TORCH_CHECK(initialized_ || opts_.enable_reconfigure, "communicator '", name_, "' is not initialised");
+  if (!initialized_) {
+    finalized_ = true;  // a reconfigurable communicator that never got a membership
+    return;
+  }
   c10::cuda::CUDAGuard guard(device_);
   const bool broken = failed_.load() || aborted_.load();
+  drain_and_release(broken, "finalize");
+  finalized_ = true;
+  if (failed_.load()) {
+    throw std::runtime_error("communicator '" + name_ + "' finalized after a failure: " + failure_text_);
+  }
+}
+
+// Waits for this rank's work, meets the other members (unless the communicator is broken), and
+// gives back everything bootstrap() created. The communicator can be bootstrapped again afterwards.
+void CudaBackend::drain_and_release(bool broken, const char* why) {
   if (!broken) {
     // Drain: every rank's kernels are done before any mapping disappears.
     cudaStreamSynchronize(internal_stream_);
     cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
     if (size_ > 1) {
       try {
-        store_barrier(*store_, "finalize", rank_, size_, std::min<Millis>(opts_.timeout, Millis(30000)));
+        store_barrier(*store_, why, rank_, size_, std::min<Millis>(opts_.timeout, Millis(30000)));
       } catch (const std::exception& e) {
         // A peer that failed never arrives; its mappings are gone either way.
-        B200C_LOG(WARN, name_, "finalize: not every rank arrived at the closing barrier: " << e.what());
+        B200C_LOG(WARN, name_, why << ": not every rank arrived at the closing barrier: " << e.what());
       }
     }
   }
   stop_watchdog();
   last_work_.reset();
-  finalized_ = true;
+  initialized_ = false;
   {
     std::lock_guard<std::mutex> g(wd_mu_);
     inflight_.clear();
@@ -657,9 +701,52 @@ void CudaBackend::finalize() {
   if (internal_stream_) cudaStreamDestroy(internal_stream_);
   dep_event_ = last_end_ = nullptr;
   internal_stream_ = nullptr;
-  if (failed_.load()) {
-    throw std::runtime_error("communicator '" + name_ + "' finalized after a failure: " + failure_text_);
+}
+
+InitHandle CudaBackend::get_init_handle() const {
+  return registered_as_ + ":" + handle_token_;
+}
+
+// Elastic membership on one box: the members named by `handles` (rank = position in the list; a set
+// is sorted) tear down what they hold - peer mappings, multicast bindings, the NCCL communicator -
+// and run the bootstrap again among themselves under a store prefix derived from `uuid`. A first
+// call creates the communicator; later calls shrink, grow or re-form it. A rank that is not in the
+// list must not call. Parity: comms/torchcomms/ncclx/TorchCommNCCLXReconfigure.cpp:206-429.
+WorkPtr CudaBackend::reconfigure(const ReconfigureOptions& o) {
+  TORCH_CHECK(!finalized_, "communicator '", name_, "' was finalized");
+  TORCH_CHECK(opts_.enable_reconfigure, "reconfigure() needs a communicator created with enable_reconfigure=True");
+  std::vector<InitHandle> members = o.handles;
+  if (!o.handles_ordered) {
+    std::sort(members.begin(), members.end());
   }
+  const InitHandle me = get_init_handle();
+  int idx = -1;
+  for (size_t i = 0; i < members.size(); ++i) {
+    if (members[i] == me) idx = static_cast<int>(i);
+  }
+  TORCH_CHECK(idx >= 0, "reconfigure: this rank's init handle is not in the member list");
+  if (o.timeout) {
+    opts_.timeout = *o.timeout;
+  }
+  c10::cuda::CUDAGuard guard(device_);
+  auto scoped = scoped_store(opts_.store, "b200c/cuda/" + name_ + "/reconf/" + std::to_string(o.uuid));
+  if (initialized_) {
+    // Nothing of this rank is in flight any more; once every member of the NEW list says the same,
+    // nobody can still be reading memory this rank is about to unmap. Members that left do not come
+    // to any barrier, so the old membership's closing barrier is skipped (released as "broken").
+    cudaStreamSynchronize(internal_stream_);
+    cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
+    if (members.size() > 1) {
+      store_barrier(*scoped, "quiesced", idx, static_cast<int>(members.size()), opts_.timeout);
+    }
+    drain_and_release(true, "reconfigure");
+  }
+  failed_.store(false);
+  aborted_.store(false);
+  failure_text_.clear();
+  parse_tuning(o.hints);
+  bootstrap(scoped, idx, static_cast<int>(members.size()));
+  return c10::make_intrusive<CompletedWork>();
 }
 
 Algo CudaBackend::algo_override(const OpOptions& o) const {

@@ -141,6 +141,9 @@ class CudaBackend final : public Backend {
   void set_timeout(Millis t) override { opts_.timeout = t; }
   void set_hints(const Hints& h) override;
   void abort() override;
+  bool supports_reconfigure() const override { return true; }
+  InitHandle get_init_handle() const override;
+  WorkPtr reconfigure(const ReconfigureOptions& o) override;
   bool is_aborted() const override { return aborted_.load(); }
   bool is_abort_supported() const override { return true; }
 
@@ -269,6 +272,8 @@ class CudaBackend final : public Backend {
   uint64_t split_counter_ = 0;
   std::atomic<uint64_t> ops_issued_{0}, bytes_issued_{0};
   std::unordered_map<std::string, uint64_t> algo_counts_;
+  std::string handle_token_;
+  void drain_and_release(bool broken, const char* why);
 };
 
 class CudaWindow final : public Window {
