@@ -453,3 +453,26 @@ def test_flight_recorder_dumps_on_abort(tmp_path, monkeypatch):
     # the ring keeps the newest entries
     rec.reset()
     assert rec.size() == 0
+
+
+def test_trainer_iteration_tags_recorder_entries_and_dumps():
+    import json
+
+    import torchcomms_b200 as tc
+    from torchcomms_b200.hooks import fr
+
+    comm = tc.new_comm("fake", torch.device("cpu"), name="iter_tag")
+    rec = fr.FlightRecorderHook(8)
+    rec.register_with_comm(comm)
+    tc.set_trainer_iteration(41)
+    comm.all_reduce(torch.ones(2), tc.ReduceOp.SUM, False)
+    tc.set_trainer_iteration(42)
+    comm.barrier(False)
+    assert tc.trainer_iteration() == 42
+    assert [e["iteration"] for e in rec.entries()] == [41, 42]
+    dumped = json.loads(rec.dump_json())
+    entries = dumped["entries"] if isinstance(dumped, dict) else dumped
+    assert [e["iteration"] for e in entries] == [41, 42]
+    assert tc.comm_dump_all()["iter_tag"]["iteration"] == "42"
+    tc.set_trainer_iteration(-1)
+    comm.finalize()

@@ -217,6 +217,16 @@ def comm_dump_all(hints=None) -> dict:
     return _comms.comm_dump_all(hints)
 
 
+def set_trainer_iteration(iteration: int) -> None:
+    """Tags what the process records from now on (flight-recorder entries, ``comm_dump_all``) with the
+    training iteration, so a trace can be lined up with the step that produced it."""
+    _comms.set_trainer_iteration(iteration)
+
+
+def trainer_iteration() -> int:
+    return _comms.trainer_iteration()
+
+
 def knobs() -> dict:
     """Configuration keys read so far: ``{key: (value in force, "env" | "file" | "default")}``.
 

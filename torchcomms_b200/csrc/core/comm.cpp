@@ -113,6 +113,12 @@ Comm::Comm(std::shared_ptr<Backend> impl, std::vector<int> global_ranks)
   live_comms().insert(this);
 }
 
+namespace {
+std::atomic<int64_t> g_trainer_iteration{-1};
+}
+void set_trainer_iteration(int64_t iteration) { g_trainer_iteration.store(iteration, std::memory_order_relaxed); }
+int64_t trainer_iteration() { return g_trainer_iteration.load(std::memory_order_relaxed); }
+
 std::unordered_map<std::string, std::unordered_map<std::string, std::string>> comm_dump_all() {
   std::unordered_map<std::string, std::unordered_map<std::string, std::string>> out;
   std::lock_guard<std::mutex> g(live_comms_mu());
@@ -120,6 +126,7 @@ std::unordered_map<std::string, std::unordered_map<std::string, std::string>> co
     try {
       auto d = c->get_backend_impl()->comm_dump();
       d["finalized"] = c->finalized_ ? "1" : "0";
+      d["iteration"] = std::to_string(trainer_iteration());
       out[c->get_name()] = std::move(d);
     } catch (const std::exception& e) {
       out[c->get_name()] = {{"error", e.what()}};

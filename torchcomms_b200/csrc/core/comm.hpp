@@ -29,6 +29,12 @@ class B200C_API BatchSendRecv {
   std::shared_ptr<Comm> parent_;
 };
 
+// Training iteration the process is in, set by the trainer (`set_trainer_iteration`) and attached to
+// flight-recorder entries and communicator dumps so that a trace can be lined up with the step that
+// produced it. -1 until set. Parity: the trainer context of comms/utils (iteration tagging).
+B200C_API void set_trainer_iteration(int64_t iteration);
+B200C_API int64_t trainer_iteration();
+
 // State of every communicator alive in this process, by communicator name
 // (comms/torchcomms/ncclx/TorchCommNCCLXPy.cpp:137-184, `comm_dump_all`).
 B200C_API std::unordered_map<std::string, std::unordered_map<std::string, std::string>> comm_dump_all();

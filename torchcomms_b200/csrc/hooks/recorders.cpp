@@ -125,6 +125,7 @@ void FlightRecorder::on_pre(const std::shared_ptr<Comm>& comm, OpName op, size_t
     }
   }
   e.created_ns = now_ns();
+  e.iteration = trainer_iteration();
   e.timeout_ms = comm->get_options().timeout.count();
   std::lock_guard<std::mutex> g(mu_);
   auto& seq = seq_[e.comm_name];
@@ -280,7 +281,7 @@ std::string FlightRecorder::dump_json(bool include_completed) const {
     os << ",\"time_discovered_completed_ns\":";
     if (e.completed_ns) os << e.completed_ns; else os << "null";
     os << ",\"retired\":" << (e.retired ? "true" : "false") << ",\"timeout_ms\":" << e.timeout_ms
-       << ",\"is_p2p\":" << (e.is_p2p ? "true" : "false") << ",\"frames\":[]}";
+       << ",\"is_p2p\":" << (e.is_p2p ? "true" : "false") << ",\"iteration\":" << e.iteration << ",\"frames\":[]}";
     first = false;
   }
   os << "]}";

@@ -31,6 +31,7 @@ class FlightRecorder : public std::enable_shared_from_this<FlightRecorder> {
     int64_t created_ns = 0, started_ns = 0, completed_ns = 0;
     std::string state = "scheduled";
     int64_t timeout_ms = 0;
+    int64_t iteration = -1;  // trainer iteration at record time
     bool retired = false;
   };
 

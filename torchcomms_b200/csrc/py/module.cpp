@@ -440,6 +440,8 @@ void bind_core(py::module_& m) {
     return out;
   });
   m.def("_reload_config", &reload_config_file);
+  m.def("set_trainer_iteration", &set_trainer_iteration, py::arg("iteration"));
+  m.def("trainer_iteration", &trainer_iteration);
   m.def("comm_dump_all", [](const std::optional<Hints>&) { return comm_dump_all(); }, py::arg("hints") = py::none(),
         "State of every live communicator of this process: {comm name: {key: value}}.");
   m.def("_recent_log_lines", []() { return Logger::get().recent(); });

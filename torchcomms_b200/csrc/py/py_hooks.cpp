@@ -38,6 +38,7 @@ void bind_hooks(py::module_& m) {
           d["input_dtypes"] = e.in_dtypes;
           d["output_dtypes"] = e.out_dtypes;
           d["retired"] = e.retired;
+          d["iteration"] = e.iteration;
           out.append(d);
         }
         return out;
