@@ -541,3 +541,59 @@ def _chaos_worker(rank, world):
 
 def test_delay_injection_and_checksum_hooks():
     run_ranks(_chaos_worker, 2, timeout=120)
+
+
+def _moe_unfused_worker(rank, world):
+    import torchcomms_b200 as tc
+    from torchcomms_b200.parallel.expert import ExpertParallelMoEUnfused
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="moe", timeout=timedelta(seconds=60))
+    hidden, num_experts, topk, tokens = 8, 4, 2, 6
+    local = num_experts // world
+
+    def make_expert(e):
+        torch.manual_seed(100 + e)
+        return torch.nn.Linear(hidden, hidden)
+
+    def make_router():
+        torch.manual_seed(7)
+        return torch.nn.Linear(hidden, num_experts)
+
+    def inputs(r):
+        g = torch.Generator().manual_seed(1000 + r)
+        return torch.randn(tokens, hidden, generator=g)
+
+    layer = ExpertParallelMoEUnfused(comm, hidden, num_experts, topk, [make_expert(rank * local + i) for i in range(local)],
+                                     make_router())
+    x = inputs(rank).requires_grad_()
+    y = layer(x)
+    (y * (rank + 1)).sum().backward()
+
+    # single-process reference over the tokens of all ranks, every expert local
+    experts, router = [make_expert(e) for e in range(num_experts)], make_router()
+    xs = [inputs(r).requires_grad_() for r in range(world)]
+    total = 0
+    ys = []
+    for r in range(world):
+        gates, idx = torch.softmax(router(xs[r]).float(), -1).topk(topk, -1)
+        out = torch.zeros(tokens, hidden)
+        for t in range(tokens):
+            for k in range(topk):
+                out[t] = out[t] + gates[t, k] * experts[int(idx[t, k])](xs[r][t])
+        ys.append(out)
+        total = total + (out * (r + 1)).sum()
+    total.backward()
+    torch.testing.assert_close(y, ys[rank], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(x.grad, xs[rank].grad, rtol=1e-5, atol=1e-6)
+    for i in range(local):                                     # an expert's gradient comes from the tokens of every rank
+        ref = experts[rank * local + i]
+        torch.testing.assert_close(layer.experts[i].weight.grad, ref.weight.grad, rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(layer.experts[i].bias.grad, ref.bias.grad, rtol=1e-5, atol=1e-6)
+    g = layer.router.weight.grad.clone()                       # the router is replicated: its gradient is summed over ranks
+    comm.all_reduce(g, tc.ReduceOp.SUM, False)
+    torch.testing.assert_close(g, router.weight.grad, rtol=1e-5, atol=1e-6)
+    comm.finalize()
+
+
+def test_unfused_expert_parallel_moe_trains():
+    run_ranks(_moe_unfused_worker, 2, timeout=120)
