@@ -90,6 +90,9 @@ class CommStatsHook:
             b = _bucket(nbytes)
             st.hist[b] = st.hist.get(b, 0) + 1
             self._pending[op_id] = (op.name, nbytes)
+            if len(self._pending) > 4096:                 # operations that raised never reach the post-hook
+                for stale in sorted(self._pending)[:2048]:
+                    del self._pending[stale]
 
     def _post(self, op_id: int, args: Any) -> None:
         with self._lock:
