@@ -189,3 +189,42 @@ def _dcp_worker(rank, world, path):
 
 def test_distributed_checkpoint_save_and_load(tmp_path):
     run_ranks(_dcp_worker, 2, args=(str(tmp_path / "ckpt"),), timeout=120)
+
+
+def _split_mesh_worker(rank, world):
+    import torch.distributed as dist
+
+    import torchcomms_b200 as tc
+    from torchcomms_b200.parallel.mesh import device_mesh_from_world, mesh_coordinates, mesh_groups, split_mesh
+
+    assert mesh_groups((2, 2), 0) == [[0, 2], [1, 3]] and mesh_groups((2, 2), 1) == [[0, 1], [2, 3]]
+    assert mesh_coordinates(3, (2, 2)) == [1, 1]
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="world", timeout=timedelta(seconds=60))
+    comms = split_mesh(comm, (2, 2), ("dp", "tp"))
+    dp_idx, tp_idx = mesh_coordinates(rank, (2, 2))
+    assert comms["dp"].get_size() == 2 and comms["dp"].get_rank() == dp_idx
+    assert comms["tp"].get_size() == 2 and comms["tp"].get_rank() == tp_idx
+    t = torch.tensor([float(rank)])
+    comms["tp"].all_reduce(t, tc.ReduceOp.SUM, False)          # ranks {0,1} and {2,3}
+    assert t.item() == float(4 * dp_idx + 1)
+    t = torch.tensor([float(rank)])
+    comms["dp"].all_reduce(t, tc.ReduceOp.SUM, False)          # ranks {0,2} and {1,3}
+    assert t.item() == float(2 * tp_idx + 2)
+    for c in comms.values():
+        c.finalize()
+    mesh = device_mesh_from_world(comm, (2, 2), ("dp", "tp"))
+    assert mesh.get_local_rank("dp") == dp_idx and mesh.get_local_rank("tp") == tp_idx
+    u = torch.tensor([1.0])
+    dist.all_reduce(u, group=mesh.get_group("tp"))
+    assert u.item() == 2.0
+    import pytest
+
+    with pytest.raises(ValueError):
+        split_mesh(comm, (3, 2), ("a", "b"))
+    for c in mesh._b200c_comms.values():
+        c.finalize()
+    comm.finalize()
+
+
+def test_split_mesh_helpers():
+    run_ranks(_split_mesh_worker, 4, timeout=120)
