@@ -11,6 +11,8 @@ Test matrix modelled on comms/torchcomms/tests/integration/py/*Test.py.
 """
 from datetime import timedelta
 
+import os
+
 import pytest
 import torch
 
@@ -332,3 +334,56 @@ def _objcol_pickle_worker(rank, world):
 @pytest.mark.parametrize("serialization", ["pickle", "torch"])
 def test_object_collectives_serialization_modes(serialization):
     run_ranks(_objcol_pickle_worker, 2, timeout=120, extra_env={"TORCHCOMMS_SERIALIZATION": serialization})
+
+
+def _fr_analyze_worker(rank, world, out_dir):
+    """Rank 1 issues a differently-shaped all-gather at step 3 and then stops: the analyzer names both."""
+    import json
+
+    import torchcomms_b200 as tc
+    from torchcomms_b200.hooks import fr
+
+    os.environ["TORCHCOMM_FR_DUMP_TEMP_FILE"] = os.path.join(out_dir, "trace_")
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="fra", timeout=timedelta(seconds=60))
+    rec = fr.FlightRecorderHook(32)
+    rec.register_with_comm(comm)
+    for _ in range(2):
+        comm.all_reduce(torch.ones(4), tc.ReduceOp.SUM, False)
+    comm.barrier(False)
+    # From here on only the recorder sees the operations (fake ones on a second communicator would not
+    # share sequence numbers), so the divergence is written into the dumps by hand below.
+    path = rec.dump_file(rank)
+    data = json.load(open(path))
+    last = data["entries"][-1]
+    extra = dict(last, collective_seq_id=last["collective_seq_id"] + 1, profiling_name="b200c:all_gather_single",
+                 input_sizes=[[8]] if rank == 0 else [[16]], state="started" if rank == 0 else "completed")
+    data["entries"].append(extra)
+    if rank == 0:                                              # rank 0 went on to one more collective, rank 1 never did
+        data["entries"].append(dict(last, collective_seq_id=last["collective_seq_id"] + 2, state="scheduled"))
+    json.dump(data, open(path, "w"))
+    comm.finalize()
+
+
+def test_flight_recorder_dumps_are_analyzed_across_ranks(tmp_path):
+    import json
+
+    from torchcomms_b200.hooks.fr_analyze import analyze, format_report, main
+
+    run_ranks(_fr_analyze_worker, 2, args=(str(tmp_path),), timeout=120)
+    paths = sorted(str(p) for p in tmp_path.glob("trace_*"))
+    assert len(paths) == 2
+    report = analyze([json.load(open(p)) for p in paths])["fra"]
+    assert report["ranks"] == [0, 1]
+    assert report["first_mismatch"]["seq"] == 4
+    assert report["first_mismatch"]["by_rank"][0]["input_sizes"] == [[8]] and report["first_mismatch"]["by_rank"][1]["input_sizes"] == [[16]]
+    assert report["never_issued"] == [{"seq": 5, "op": "b200c:barrier", "ranks_without": [1]}]
+    assert report["not_completed"][0]["seq"] == 4 and report["not_completed"][0]["states"] == {0: "started"}
+    assert report["progress"][0]["last_completed_collective"] == 3
+    text = format_report({"fra": report})
+    assert "ranks disagree at collective 4" in text and "never issued by ranks [1]" in text
+    assert main(paths) == 0
+    # healthy traces say so
+    clean = [json.load(open(p)) for p in paths]
+    for d in clean:
+        d["entries"] = [e for e in d["entries"] if e["collective_seq_id"] <= 3]
+    assert "all ranks issued and completed the same collectives" in format_report(analyze(clean))

@@ -4,7 +4,8 @@
     NanCheckHook().register_with_comm(comm)
     rec = fr.FlightRecorderHook(); rec.register_with_comm(comm)
 
-``fr`` and ``clog`` are the native recorders (ring buffer in the c10d
+``python -m torchcomms_b200.hooks.fr_analyze <dump files>`` lines the ranks' recorder dumps up and names
+the first collective on which they disagree.  ``fr`` and ``clog`` are the native recorders (ring buffer in the c10d
 flight-recorder JSON layout; pipe-delimited collective log with graph
 capture / replay lines).  Parity: comms/torchcomms/hooks/__init__.py,
 hooks/fr/FlightRecorderHook.hpp:43-146, hooks/clog/ClogHook.hpp:118-279,
