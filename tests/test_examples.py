@@ -21,3 +21,9 @@ def test_fsdp_device_mesh_example_on_gloo():
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=240)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert "step 1: loss" in res.stdout
+
+
+def test_package_report_runs_without_a_gpu():
+    res = subprocess.run([sys.executable, "-m", "torchcomms_b200"], capture_output=True, text=True, timeout=120, cwd=ROOT)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "backends" in res.stdout and "gloo" in res.stdout and "extension" in res.stdout
