@@ -121,3 +121,59 @@ def _sparse_worker(rank, world):
 
 def test_all_reduce_sparse_block():
     run_ranks(_sparse_worker, 4, timeout=120)
+
+
+def _options_worker(rank, world):
+    """Every operation takes ``hints=`` and ``timeout=`` (OptionsTest.py of the reference)."""
+    import torchcomms_b200 as tc
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="opts", timeout=timedelta(seconds=60))
+    kw = {"hints": {"example": "1"}, "timeout": timedelta(seconds=600)}
+    peer = 1 - rank
+    t = torch.full((4,), float(rank))
+    if rank == 0:
+        comm.send(t, peer, False, **kw)
+        comm.recv(t, peer, False, **kw)
+    else:
+        got = torch.empty(4)
+        comm.recv(got, peer, False, **kw)
+        comm.send(got + 1, peer, False, **kw)
+    comm.broadcast(t, 0, False, **kw)
+    comm.all_reduce(t, tc.ReduceOp.SUM, False, **kw)
+    comm.reduce(t, 0, tc.ReduceOp.SUM, False, **kw)
+    out = torch.empty(world * 4)
+    comm.all_gather_single(out, t, False, **kw)
+    comm.all_gather([torch.empty(4) for _ in range(world)], t, False, **kw)
+    comm.all_gather_v([torch.empty(4) for _ in range(world)], t, False, **kw)
+    comm.gather([torch.empty(4) for _ in range(world)] if rank == 0 else [], t, 0, False, **kw)
+    comm.gather_single(torch.empty(world * 4) if rank == 0 else torch.empty(0), t, 0, False, **kw)
+    rs = torch.empty(2)
+    comm.reduce_scatter_single(rs, torch.ones(2 * world), tc.ReduceOp.SUM, False, **kw)
+    comm.reduce_scatter(rs, [torch.ones(2) for _ in range(world)], tc.ReduceOp.SUM, False, **kw)
+    comm.reduce_scatter_v(rs, [torch.ones(2) for _ in range(world)], tc.ReduceOp.SUM, False, **kw)
+    comm.scatter(rs, [torch.ones(2) for _ in range(world)] if rank == 0 else [], 0, False, **kw)
+    comm.all_to_all([torch.empty(1) for _ in range(world)], [torch.ones(1) for _ in range(world)], False, **kw)
+    a2a = torch.empty(world)
+    comm.all_to_all_single(a2a, torch.ones(world), False, **kw)
+    comm.all_to_all_v_single(a2a, torch.ones(world), [1] * world, [1] * world, False, **kw)
+    comm.barrier(False, **kw)
+    batch = comm.batch_op_create()
+    box = torch.empty(1)
+    batch.send(torch.ones(1), peer)
+    batch.recv(box, peer)
+    bo = tc.BatchP2POptions()
+    bo.hints = {"example": "1"}
+    bo.timeout = timedelta(seconds=600)
+    batch.issue(False, bo).wait()
+    sub = comm.split(list(range(world)), "sub", **kw)
+    assert sub.get_size() == world
+    handle = comm.all_gather_p_init(out, **kw)
+    comm.all_gather_p_exec(handle, t, False, **kw).wait()
+    comm.all_gather_p_free(handle)
+    # a per-call timeout that is too short for an absent peer is the call's own error, not the communicator's default
+    sub.finalize()
+    comm.finalize()
+
+
+def test_every_operation_accepts_hints_and_timeout():
+    run_ranks(_options_worker, 2, timeout=120)
