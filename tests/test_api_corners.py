@@ -5,6 +5,7 @@ use after finalize.
 Modelled on comms/torchcomms/tests/integration/py/AllGatherPTest.py, GatherTest.py,
 ScatterTest.py, AllToAllTest.py, OptionsTest.py and FinalizeWarningTest.py.
 """
+import os
 from datetime import timedelta
 
 import pytest
@@ -177,3 +178,62 @@ def _options_worker(rank, world):
 
 def test_every_operation_accepts_hints_and_timeout():
     run_ranks(_options_worker, 2, timeout=120)
+
+
+def _split_worker(rank, world):
+    """SplitTest.py and MultiCommTest.py of the reference: non-contiguous groups, invalid rank lists,
+    splits of splits, communicators on separate and shared stores."""
+    import torch.distributed as dist
+
+    import torchcomms_b200 as tc
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="split_world", timeout=timedelta(seconds=60))
+    # non-contiguous: even and odd ranks; the child's ranks are global ranks, its rank is the index in the list
+    evens, odds = [0, 2], [1, 3]
+    mine = evens if rank % 2 == 0 else odds
+    child = None
+    for group in (evens, odds):
+        c = comm.split(group if rank in group else [], "parity")
+        child = c if c is not None else child
+    assert child.get_size() == 2 and child.get_rank() == mine.index(rank) and list(child.get_ranks()) == mine
+    t = torch.tensor([float(rank)])
+    child.all_reduce(t, tc.ReduceOp.SUM, False)
+    assert t.item() == float(sum(mine))
+    # invalid lists are refused before anything is exchanged
+    with pytest.raises(RuntimeError):
+        comm.split([0, 0, 1], "dup")
+    with pytest.raises(RuntimeError):
+        comm.split([(rank + 1) % world], "not_me")
+    with pytest.raises(RuntimeError):
+        comm.split([0, world], "out_of_range")
+    # multi-level: split the child again into singletons
+    leaf = None
+    for i in range(2):
+        c = child.split([i] if child.get_rank() == i else [], "leaf")
+        leaf = c if c is not None else leaf
+    assert leaf.get_size() == 1 and list(leaf.get_ranks()) == [rank]
+    u = torch.tensor([5.0])
+    leaf.all_reduce(u, tc.ReduceOp.SUM, False)
+    assert u.item() == 5.0
+    # the parent still works while children exist, in any interleaving
+    w1 = comm.all_reduce(torch.ones(2), tc.ReduceOp.SUM, True)
+    w2 = child.all_reduce(torch.ones(2), tc.ReduceOp.SUM, True)
+    w2.wait()
+    w1.wait()
+    # communicators with their own stores and with a shared one, side by side
+    port = int(os.environ["MASTER_PORT"])
+    own = dist.TCPStore("127.0.0.1", port + 7, world, rank == 0, timeout=timedelta(seconds=60))
+    shared = dist.PrefixStore("shared", own)
+    a = tc.new_comm("gloo", torch.device("cpu"), name="store_a", store=own, timeout=timedelta(seconds=60))
+    b = tc.new_comm("gloo", torch.device("cpu"), name="store_b", store=shared, timeout=timedelta(seconds=60))
+    c3 = tc.new_comm("gloo", torch.device("cpu"), name="store_c", timeout=timedelta(seconds=60))     # default store
+    for i, x in enumerate((a, b, c3)):
+        v = torch.tensor([float(i + 1)])
+        x.all_reduce(v, tc.ReduceOp.SUM, False)
+        assert v.item() == float((i + 1) * world)
+    for x in (c3, b, a, leaf, child, comm):
+        x.finalize()
+
+
+def test_split_cases_and_communicators_on_several_stores():
+    run_ranks(_split_worker, 4, timeout=150)
