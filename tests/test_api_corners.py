@@ -237,3 +237,74 @@ def _split_worker(rank, world):
 
 def test_split_cases_and_communicators_on_several_stores():
     run_ranks(_split_worker, 4, timeout=150)
+
+
+def _variants_worker(rank, world):
+    """The per-operation variants of the reference's integration tests (AllReduceTest.py:22-110): synchronous
+    with and without keeping the work, asynchronous wait, work dropped early, input deleted before wait."""
+    import gc
+
+    import torchcomms_b200 as tc
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="variants", timeout=timedelta(seconds=60))
+    total = float(sum(range(1, world + 1)))
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+
+    def fresh():
+        return torch.full((64,), float(rank + 1))
+
+    # synchronous, keeping the work / ignoring it
+    t = fresh()
+    w = comm.all_reduce(t, tc.ReduceOp.SUM, False)
+    w.wait()
+    assert torch.equal(t, torch.full((64,), total))
+    t = fresh()
+    comm.all_reduce(t, tc.ReduceOp.SUM, False)
+    assert torch.equal(t, torch.full((64,), total))
+    # asynchronous + wait
+    t = fresh()
+    comm.all_reduce(t, tc.ReduceOp.SUM, True).wait()
+    assert torch.equal(t, torch.full((64,), total))
+    # asynchronous, the work dropped before it was waited on: the operation still completes
+    t = fresh()
+    w = comm.all_reduce(t, tc.ReduceOp.SUM, True)
+    w = None
+    gc.collect()
+    comm.barrier(False)
+    assert torch.equal(t, torch.full((64,), total))
+    # input deleted before the wait: the work keeps what it reads alive
+    out = torch.empty(world * 64)
+    src = fresh()
+    w = comm.all_gather_single(out, src, True)
+    del src
+    gc.collect()
+    w.wait()
+    assert torch.equal(out.view(world, 64)[:, 0], torch.arange(1, world + 1, dtype=torch.float32))
+    # the same five variants for a batch of send + recv around the ring
+    for variant in ("sync", "sync_no_work", "async", "async_dropped", "input_deleted"):
+        got = torch.zeros(8)
+        payload = torch.full((8,), float(rank))
+        batch = comm.batch_op_create()
+        batch.send(payload, nxt)
+        batch.recv(got, prv)
+        if variant == "sync":
+            batch.issue(False).wait()
+        elif variant == "sync_no_work":
+            batch.issue(False)
+        elif variant == "async":
+            batch.issue(True).wait()
+        elif variant == "async_dropped":
+            batch.issue(True)
+            gc.collect()
+            comm.barrier(False)
+        else:
+            w = batch.issue(True)
+            del payload, batch
+            gc.collect()
+            w.wait()
+        assert torch.equal(got, torch.full((8,), float(prv))), variant
+    comm.finalize()
+
+
+def test_operation_variants_sync_async_dropped_and_deleted_inputs():
+    run_ranks(_variants_worker, 3, timeout=120)

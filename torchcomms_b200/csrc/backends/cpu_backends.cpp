@@ -3,6 +3,7 @@
 
 #include <cstdio>
 #include <mutex>
+#include <thread>
 #include <unistd.h>
 
 #include <random>
@@ -208,6 +209,37 @@ class GlooWork final : public Work {
       : inner_(std::move(inner)), post_(std::move(post)), owner_(std::move(owner)) {
     set_timeout(timeout);
     set_status(WorkStatus::INPROGRESS);
+  }
+
+  // A caller may drop the work of an asynchronous operation without waiting. Collectives run to
+  // completion on the process group's own threads, but a point-to-point transfer is cancelled when
+  // its handle goes away, which would leave the peer waiting forever: hand unfinished transfers (and
+  // the copy-back that follows them) to a helper thread that sees them through.
+  ~GlooWork() override {
+    std::vector<c10::intrusive_ptr<c10d::Work>> inner;
+    std::function<void()> post;
+    {
+      std::lock_guard<std::mutex> g(wait_mu_);
+      if (done_) {
+        return;
+      }
+      done_ = true;
+      inner.swap(inner_);
+      post.swap(post_);
+    }
+    if (inner.empty()) {
+      return;
+    }
+    std::thread([inner = std::move(inner), post = std::move(post)]() mutable {
+      try {
+        for (auto& w : inner) {
+          if (w) w->wait();
+        }
+        if (post) post();
+      } catch (...) {
+        // nobody is left to report to; the peer sees its own timeout
+      }
+    }).detach();
   }
 
  protected:
