@@ -89,3 +89,41 @@ def _worker(rank, world):
 
 def test_c10d_wrapper_and_lifetime_behaviour():
     run_ranks(_worker, 2, timeout=120)
+
+
+def _reduce_ops_worker(rank, world):
+    """Every torch.distributed reduction operator through the adapter (C10dTorchCommTest.py), PREMUL_SUM included."""
+    import math
+
+    import torch.distributed as dist
+
+    import torchcomms_b200 as tc
+    from torchcomms_b200.device_mesh import init_device_mesh
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="redops", timeout=timedelta(seconds=60))
+    pg = init_device_mesh(mesh_dim_comms=(comm,), mesh_dim_names=("w",)).get_group("w")
+    total = sum(range(1, world + 1))
+    expect = {dist.ReduceOp.SUM: float(total), dist.ReduceOp.AVG: total / world, dist.ReduceOp.MIN: 1.0,
+              dist.ReduceOp.MAX: float(world), dist.ReduceOp.PRODUCT: float(math.factorial(world))}
+    for op, want in expect.items():
+        t = torch.tensor([float(rank + 1)])
+        dist.all_reduce(t, op=op, group=pg)
+        assert abs(t.item() - want) < 1e-6, (op, t.item(), want)
+        r = torch.tensor([float(rank + 1)])
+        dist.reduce(r, dst=0, op=op, group=pg)
+        if rank == 0:
+            assert abs(r.item() - want) < 1e-6, (op, r.item(), want)
+    ti = torch.tensor([rank + 1])
+    dist.all_reduce(ti, op=dist.ReduceOp.BOR, group=pg)
+    bits = 0
+    for r in range(1, world + 1):
+        bits |= r
+    assert ti.item() == bits
+    rs = torch.empty(1)
+    dist.reduce_scatter_tensor(rs, torch.arange(float(world)), op=dist.ReduceOp.MAX, group=pg)
+    assert rs.item() == float(rank)
+    comm.finalize()
+
+
+def test_every_c10d_reduce_op_through_the_adapter():
+    run_ranks(_reduce_ops_worker, 3, timeout=120)
