@@ -127,3 +127,20 @@ def _reduce_ops_worker(rank, world):
 
 def test_every_c10d_reduce_op_through_the_adapter():
     run_ranks(_reduce_ops_worker, 3, timeout=120)
+
+
+def _no_finalize_worker(rank, world):
+    import torchcomms_b200 as tc
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="nofinal", timeout=timedelta(seconds=60))
+    t = torch.ones(4)
+    comm.all_reduce(t, tc.ReduceOp.SUM, False)
+    assert torch.equal(t, torch.full((4,), float(world)))
+    sub = comm.split(list(range(world)), "child")
+    sub.barrier(False)
+    # no finalize(): the destructors warn and clean up; the process must exit normally
+
+
+def test_destruction_without_finalize_does_not_abort():
+    """FinalizeWarningTest.py of the reference."""
+    assert run_ranks(_no_finalize_worker, 2, timeout=120) == [0, 0]
