@@ -144,3 +144,48 @@ def _no_finalize_worker(rank, world):
 def test_destruction_without_finalize_does_not_abort():
     """FinalizeWarningTest.py of the reference."""
     assert run_ranks(_no_finalize_worker, 2, timeout=120) == [0, 0]
+
+
+def _hooks_through_wrapper_worker(rank, world):
+    """Hooks registered on the communicator fire for operations issued through torch.distributed
+    (test_backend_wrapper.py of the reference), with correlated, increasing operation ids."""
+    import torch.distributed as dist
+
+    import torchcomms_b200 as tc
+    from torchcomms_b200.device_mesh import init_device_mesh
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="hookwrap", timeout=timedelta(seconds=60))
+    pg = init_device_mesh(mesh_dim_comms=(comm,), mesh_dim_names=("w",)).get_group("w")
+    pre, post = [], []
+    h1 = comm.register_pre_hook(lambda op, op_id, args: pre.append((op.name, op_id)))
+    h2 = comm.register_post_hook(lambda op_id, args: post.append(op_id))
+    t = torch.ones(4)
+    dist.all_reduce(t, group=pg)
+    out = torch.empty(world * 4)
+    dist.all_gather_into_tensor(out, t, group=pg)
+    dist.broadcast(t, src=0, group=pg)
+    assert [n for n, _ in pre] == ["all_reduce", "all_gather_single", "broadcast"]
+    ids = [i for _, i in pre]
+    assert ids == post and ids == sorted(ids) and len(set(ids)) == 3
+    h1.remove()
+    h2.remove()
+    dist.all_reduce(t, group=pg)
+    assert len(pre) == 3 and len(post) == 3
+    # a pre-hook that raises stops the operation on every rank alike (nothing was sent)
+    import pytest
+
+    def veto(op, op_id, args):
+        raise ValueError("vetoed by the hook")
+
+    h3 = comm.register_pre_hook(veto)
+    with pytest.raises((RuntimeError, ValueError), match="vetoed"):
+        comm.all_reduce(torch.ones(2), tc.ReduceOp.SUM, False)
+    h3.remove()
+    u = torch.ones(2)
+    comm.all_reduce(u, tc.ReduceOp.SUM, False)                 # the communicator is still usable
+    assert torch.equal(u, torch.full((2,), float(world)))
+    comm.finalize()
+
+
+def test_hooks_fire_through_the_c10d_adapter():
+    run_ranks(_hooks_through_wrapper_worker, 2, timeout=120)
