@@ -476,3 +476,94 @@ def test_trainer_iteration_tags_recorder_entries_and_dumps():
     assert tc.comm_dump_all()["iter_tag"]["iteration"] == "42"
     tc.set_trainer_iteration(-1)
     comm.finalize()
+
+
+class _FullPyBackend(_PyBackend):
+    """A single-rank Python backend that implements every overridable operation and logs the calls."""
+
+    def __init__(self):
+        super().__init__()
+        self.calls = []
+
+    def get_backend_name(self):
+        return "pyfull"
+
+    def _done(self, name, async_op):
+        self.calls.append(name)
+        return _Work() if async_op else None
+
+    def send(self, tensor, dst, async_op):
+        return self._done("send", async_op)
+
+    def recv(self, tensor, src, async_op):
+        tensor.fill_(7)
+        return self._done("recv", async_op)
+
+    def broadcast(self, tensor, root, async_op):
+        return self._done("broadcast", async_op)
+
+    def reduce(self, tensor, root, op, async_op):
+        return self._done("reduce", async_op)
+
+    def all_gather(self, tensor_list, tensor, async_op):
+        tensor_list[0].copy_(tensor)
+        return self._done("all_gather", async_op)
+
+    def all_gather_single(self, output, input, async_op):
+        output.copy_(input)
+        return self._done("all_gather_single", async_op)
+
+    def reduce_scatter_single(self, output, input, op, async_op):
+        output.copy_(input)
+        return self._done("reduce_scatter_single", async_op)
+
+    def all_to_all_single(self, output, input, async_op):
+        output.copy_(input)
+        return self._done("all_to_all_single", async_op)
+
+    def barrier(self, async_op):
+        return self._done("barrier", async_op)
+
+    def scatter(self, output, input_list, root, async_op):
+        output.copy_(input_list[0])
+        return self._done("scatter", async_op)
+
+    def gather(self, output_list, input, root, async_op):
+        output_list[0].copy_(input)
+        return self._done("gather", async_op)
+
+
+def test_python_backend_every_operation_reaches_the_override():
+    """test_python_backend.py of the reference: each collective lands in the Python method, hooks included."""
+    tc.register_backend("pyfull", _FullPyBackend)
+    c = tc.new_comm("pyfull", torch.device("cpu"), name="pyfull1")
+    impl = c.get_backend_impl().python_object()
+    seen = []
+    handle = c.register_pre_hook(lambda op, op_id, args: seen.append(op.name))
+    t, out = torch.arange(4.0), torch.zeros(4)
+    c.send(t, 0, False)
+    c.recv(out, 0, False)
+    assert torch.equal(out, torch.full((4,), 7.0))
+    c.broadcast(t, 0, False)
+    c.reduce(t, 0, tc.ReduceOp.SUM, False)
+    lst = [torch.zeros(4)]
+    c.all_gather(lst, t, False)
+    assert torch.equal(lst[0], t)
+    c.all_gather_single(out, t, False)
+    c.reduce_scatter_single(out, t, tc.ReduceOp.SUM, False)
+    c.all_to_all_single(out, t, False)
+    c.barrier(False)
+    c.scatter(out, [t], 0, False)
+    c.gather([out], t, 0, False)
+    w = c.barrier(True)
+    w.wait()
+    expected = ["send", "recv", "broadcast", "reduce", "all_gather", "all_gather_single", "reduce_scatter_single",
+                "all_to_all_single", "barrier", "scatter", "gather", "barrier"]
+    assert impl.calls == expected and seen == expected
+    handle.remove()
+    # two communicators of the same Python backend are independent objects
+    c2 = tc.new_comm("pyfull", torch.device("cpu"), name="pyfull2")
+    c2.barrier(False)
+    assert c2.get_backend_impl().python_object().calls == ["barrier"] and len(impl.calls) == len(expected)
+    c2.finalize()
+    c.finalize()
