@@ -567,3 +567,51 @@ def test_python_backend_every_operation_reaches_the_override():
     assert c2.get_backend_impl().python_object().calls == ["barrier"] and len(impl.calls) == len(expected)
     c2.finalize()
     c.finalize()
+
+
+def test_window_api_rules_on_the_fake_backend():
+    """Window rules without a GPU (WindowRmaTest.py, RegisterTensorTest.py, test_copy.py of the reference):
+    one registration at a time, bounds and dtype of put, signal / wait pairing, deepcopy clones the tensor."""
+    import copy
+
+    c = tc.new_comm("fake", torch.device("cpu"), name="win")
+    w = c.new_window()
+    assert w.get_tensor() is None and w.get_size() == 0
+    t = torch.zeros(16)
+    w.tensor_register(t)
+    assert w.get_size() == 64 and w.shape == [16] and w.dtype == torch.float32
+    with pytest.raises(RuntimeError, match="already"):
+        w.tensor_register(torch.zeros(4))
+    with pytest.raises(RuntimeError, match="contiguous"):
+        c.new_window().tensor_register(torch.zeros(4, 4).t())
+    w.put(torch.arange(4.0), 0, 8, False)
+    assert torch.equal(t[8:12], torch.arange(4.0)) and float(t[:8].sum()) == 0
+    w.put(torch.ones(4), 0, 12, True).wait()
+    with pytest.raises(RuntimeError, match="outside the window"):
+        w.put(torch.ones(4), 0, 13, False)
+    with pytest.raises(RuntimeError, match="dtype"):
+        w.put(torch.ones(4, dtype=torch.int32), 0, 0, False)
+    with pytest.raises(RuntimeError, match="outside"):
+        w.put(torch.ones(1), 1, 0, False)                      # no such rank
+    w.signal(0, False)
+    w.wait_signal(0, False)
+    with pytest.raises(RuntimeError, match="wait forever"):
+        w.wait_signal(0, False)
+    assert w.map_remote_tensor(0).data_ptr() == t.data_ptr()
+    assert w.get_attr(0).access_type == tc.TorchCommWinAccessType.WIN_ACCESS_TYPE_UNIFIED
+    # copy is the same window; deepcopy clones window and tensor and records the tensor in the memo
+    assert copy.copy(w) is w
+    memo = {}
+    w2 = copy.deepcopy(w, memo)
+    assert w2 is not w and torch.equal(w2.get_tensor(), t) and w2.get_tensor().data_ptr() != t.data_ptr()
+    w2.put(torch.full((2,), 9.0), 0, 0, False)
+    assert float(t[0]) == 0.0 and float(w2.get_tensor()[0]) == 9.0
+    w.tensor_deregister()
+    with pytest.raises(RuntimeError):
+        w.tensor_deregister()
+    w.tensor_register(torch.zeros(4))                          # a window can be registered again after deregistration
+    pre_made = c.new_window(torch.ones(3))
+    assert pre_made.get_size() == 12
+    with pytest.raises(RuntimeError, match="CUDA backend"):
+        w.get_device_window()
+    c.finalize()

@@ -31,6 +31,88 @@ void FakeBackend::finalize() {
   calls.push_back("finalize");
 }
 
+namespace {
+
+// One-sided window of the fake backend: the registered tensor is host memory of the only rank, `put`
+// to oneself is a copy, signals are counters. It follows the rules of the real windows (one
+// registration at a time, contiguous tensors, `put` inside the registered range, matching dtype).
+class FakeWindow final : public Window {
+ public:
+  FakeWindow(int rank, int size) : rank_(rank), size_(size), pending_(static_cast<size_t>(size), 0) {}
+
+  void tensor_register(const at::Tensor& t, bool /*owning*/) override {
+    TORCH_CHECK(!tensor_, "window already has a registered tensor");
+    TORCH_CHECK(t.defined() && t.is_contiguous(), "window tensors must be contiguous");
+    tensor_ = t;
+    cache_meta(t);
+  }
+  void tensor_deregister() override {
+    TORCH_CHECK(tensor_.has_value(), "no tensor is registered with this window");
+    tensor_.reset();
+  }
+  std::shared_ptr<Window> clone() override {
+    auto w = std::make_shared<FakeWindow>(rank_, size_);
+    if (tensor_) {
+      w->tensor_register(tensor_->clone(), true);
+    }
+    return w;
+  }
+  WorkPtr put(const at::Tensor& src, int dst_rank, int64_t target_offset_nelems, bool, const OpOptions&) override {
+    TORCH_CHECK(tensor_.has_value(), "put: no tensor is registered with this window");
+    check_rank(dst_rank, "put");
+    TORCH_CHECK(src.is_contiguous(), "put: the source must be contiguous");
+    TORCH_CHECK(src.scalar_type() == tensor_->scalar_type(), "put: dtype differs from the window's");
+    TORCH_CHECK(target_offset_nelems >= 0 &&
+                    (src.numel() + target_offset_nelems) * static_cast<int64_t>(src.element_size()) <=
+                        static_cast<int64_t>(tensor_->nbytes()),
+                "put: the range lies outside the window");
+    tensor_->view({-1}).narrow(0, target_offset_nelems, src.numel()).copy_(src.reshape({-1}));
+    return c10::make_intrusive<CompletedWork>();
+  }
+  WorkPtr signal(int dst_rank, bool, const OpOptions&) override {
+    check_rank(dst_rank, "signal");
+    ++pending_[static_cast<size_t>(dst_rank)];
+    return c10::make_intrusive<CompletedWork>();
+  }
+  WorkPtr wait_signal(int peer_rank, bool, const OpOptions&) override {
+    check_rank(peer_rank, "wait_signal");
+    TORCH_CHECK(pending_[static_cast<size_t>(peer_rank)] > 0, "wait_signal: no signal from rank ", peer_rank,
+                " is pending (this would wait forever)");
+    --pending_[static_cast<size_t>(peer_rank)];
+    return c10::make_intrusive<CompletedWork>();
+  }
+  at::Tensor map_remote_tensor(int rank) override {
+    check_rank(rank, "map_remote_tensor");
+    TORCH_CHECK(tensor_.has_value(), "map_remote_tensor: no tensor is registered with this window");
+    return *tensor_;
+  }
+  WindowAttr get_attr(int peer_rank) override {
+    check_rank(peer_rank, "get_attr");
+    return WindowAttr{};
+  }
+  uintptr_t get_device_window(int, int, int) override { TORCH_CHECK(false, "device windows need the CUDA backend"); }
+  uintptr_t register_local_buffer(const at::Tensor&) override { TORCH_CHECK(false, "device windows need the CUDA backend"); }
+  void deregister_local_buffer(uintptr_t) override { TORCH_CHECK(false, "device windows need the CUDA backend"); }
+
+ private:
+  void check_rank(int r, const char* what) const {
+    TORCH_CHECK(r >= 0 && r < size_, what, ": rank ", r, " is outside [0, ", size_, ")");
+  }
+  int rank_, size_;
+  std::vector<int> pending_;
+};
+
+}  // namespace
+
+std::shared_ptr<Window> FakeBackend::new_window(const std::optional<at::Tensor>& tensor) {
+  calls.push_back("new_window");
+  auto w = std::make_shared<FakeWindow>(rank_, size_);
+  if (tensor) {
+    w->tensor_register(*tensor, true);
+  }
+  return w;
+}
+
 WorkPtr FakeBackend::done(const char* what) {
   TORCH_CHECK(initialized_, "fake backend: used after finalize");
   calls.emplace_back(what);

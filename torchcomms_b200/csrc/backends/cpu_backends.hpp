@@ -54,6 +54,8 @@ class B200C_API FakeBackend : public Backend {
   void abort() override { aborted_ = true; run_abort_hooks(); }
   bool is_aborted() const override { return aborted_; }
   bool is_abort_supported() const override { return true; }
+  // A host-memory window for the single rank: enough to exercise the window API's rules without a GPU.
+  std::shared_ptr<Window> new_window(const std::optional<at::Tensor>& tensor) override;
 
   std::vector<std::string> calls;
 
