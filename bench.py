@@ -1,32 +1,44 @@
-"""Headline benchmark: one Llama-3-8B sharded-data-parallel training step.
+"""Headline benchmark.
 
     python bench.py --gpus N --steps K --warmup W        (N > 1: launched with torchrun, one rank per GPU)
 
-Config (from the benchmark set): Llama-3-8B architecture (32 layers, hidden
-4096, 32 heads / 8 KV heads, FFN 14336, vocab 128256, RMSNorm, RoPE), random
-init, sequence 4096, micro-batch 1 per GPU, token ids uniform over the
-vocabulary; parameters all-gathered before each stage's forward and backward
-and gradients reduce-scattered behind backward through this framework's
-communicator; bf16 compute, fp32 master weights and AdamW state.
+What it measures, on synthetic data of the named shapes with random-init weights:
 
-Prints ONE JSON line on rank 0.  ``value`` is whole-job tokens/s timed on the
-device with CUDA events (max over ranks) over exactly K steps after W warm-up
-steps; ``e2e`` repeats the measurement with the per-step host->device copy of
-the token ids from pinned memory and a device->host read of the loss inside
-the timed region.  With N > 1 the line also carries bus bandwidth of this
-framework's all_reduce / all_gather / reduce_scatter kernels next to NCCL's.
+1. **Training step** (``value``): one Llama-3-8B sharded-data-parallel step
+   (32 layers, hidden 4096, 32 heads / 8 KV heads, FFN 14336, vocab 128256,
+   RMSNorm, RoPE; sequence 4096, micro-batch 1 per GPU; token ids uniform over
+   the vocabulary; bf16 compute, fp32 master weights and AdamW state).
+   Parameters are all-gathered before each stage's forward and backward and
+   gradients reduce-scattered behind backward through this framework's
+   communicator.  Whole-job tokens/s over exactly K steps after W warm-up
+   steps, timed on the device with CUDA events, max over ranks.  ``e2e``
+   repeats it with the per-step host->device copy of the token ids from pinned
+   memory and a device->host read of the loss inside the timed region.
+   With N > 1 the same engine is timed a second time with its parameter gathers
+   and gradient reductions on NCCL (``step_nccl_arm``: separate cast kernels +
+   ``ncclAllGather`` / ``ncclReduceScatter`` in bf16, the path the reference's
+   ``nccl`` backend takes), and a profiled pass reports how long the
+   communication kernels run, how long compute sits blocked on them, and the
+   optimizer time (``step_breakdown``).
+2. **Collective sweep** (``collectives``; N > 1): bus bandwidth, average and p50
+   latency of all_reduce / all_gather / reduce_scatter / all_to_all_v on bf16 and
+   fp32 buffers ~U[-1,1], 1 KB - 1 GB in powers of two, 20 warm-up + 100 timed
+   calls per point: this framework's kernels next to NCCL.
+3. **MoE dispatch / combine latency** (``moe_ep``; N > 1): 4096 tokens per rank,
+   hidden 7168, 256 experts, top-8, fp8 (e4m3, 1x128 scales) dispatch and bf16
+   weighted combine: the fused kernels next to the unfused NCCL pipeline.
 
-``--impl reference`` would run the unmodified reference package from
-``baseline/_ref``; it cannot be installed offline here (its CMake build
-downloads third-party sources), so that arm reports itself unavailable.
+Rank 0 prints ONE JSON line.  ``--impl reference`` would run the unmodified
+reference package from ``baseline/_ref``; it cannot be built offline here (see
+the message it prints), so that arm reports itself unavailable.
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import sys
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -42,15 +54,24 @@ def parse_args():
     ap.add_argument("--seq-len", type=int, default=4096)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--recompute-blocks", type=int, default=0)
+    ap.add_argument("--comm", default="symm", choices=["symm", "staged", "nccl"],
+                    help="how the step's all-gathers / reduce-scatters move data (the headline arm)")
+    ap.add_argument("--skip-nccl-arm", action="store_true", help="do not time the step a second time on NCCL")
     ap.add_argument("--skip-collectives", action="store_true")
+    ap.add_argument("--skip-ep", action="store_true")
+    ap.add_argument("--sweep-max-bytes", type=int, default=1 << 30)
+    ap.add_argument("--sweep-iters", type=int, default=100)
+    ap.add_argument("--sweep-warmup", type=int, default=20)
+    ap.add_argument("--sweep-json", default="", help="also write every sweep row to this file")
     return ap.parse_args()
 
 
 def reference_arm():
     print(json.dumps({
         "impl": "reference",
-        "unavailable": "torchcomms cannot be installed offline: its CMake build fetches nlohmann_json and gloo "
-                       "from GitHub (FetchContent) and no network is available",
+        "unavailable": "torchcomms cannot be built offline: its CMake configure step needs nlohmann_json, gflags, glog "
+                       "and gloo as CMake packages (FetchContent downloads them otherwise) and none of them is in the "
+                       "image; no network is available",
     }))
 
 
@@ -62,59 +83,6 @@ def model_config(name):
     if name == "llama_1b":
         return LlamaConfig(dim=2048, n_layers=16, n_heads=32, n_kv_heads=8, ffn_dim=8192, vocab_size=128256)
     return LlamaConfig.tiny()
-
-
-def max_over_ranks(comm, value, device):
-    import torch
-
-    import torchcomms_b200 as tc
-
-    t = torch.tensor([value], dtype=torch.float32, device=device)
-    comm.all_reduce(t, tc.ReduceOp.MAX, False)
-    return float(t.item())
-
-
-def bench_collectives(comm, device, world):
-    """Bus bandwidth (GB/s) of AR / AG / RS: this framework's kernels and NCCL, bf16."""
-    import torch
-
-    import torchcomms_b200 as tc
-
-    out = {}
-    sizes = [64 * 1024, 1 << 20, 16 << 20, 256 << 20]
-    for algo in ("auto", "kernel", "nccl"):
-        for op in ("all_reduce", "all_gather", "reduce_scatter"):
-            for nbytes in sizes:
-                n = nbytes // 2
-                hints = {"algo": algo}
-                if op == "all_reduce":
-                    buf = torch.zeros(n, dtype=torch.bfloat16, device=device)
-                    fn = lambda: comm.all_reduce(buf, tc.ReduceOp.SUM, False, hints=hints)
-                    factor = 2 * (world - 1) / world
-                elif op == "all_gather":
-                    src = torch.zeros(n // world, dtype=torch.bfloat16, device=device)
-                    dst = torch.empty(n // world * world, dtype=torch.bfloat16, device=device)
-                    fn = lambda: comm.all_gather_single(dst, src, False, hints=hints)
-                    factor = (world - 1) / world
-                else:
-                    src = torch.zeros(n // world * world, dtype=torch.bfloat16, device=device)
-                    dst = torch.empty(n // world, dtype=torch.bfloat16, device=device)
-                    fn = lambda: comm.reduce_scatter_single(dst, src, tc.ReduceOp.SUM, False, hints=hints)
-                    factor = (world - 1) / world
-                iters = 20 if nbytes >= (16 << 20) else 50
-                for _ in range(5):
-                    fn()
-                comm.barrier(False)
-                torch.cuda.synchronize()
-                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                start.record()
-                for _ in range(iters):
-                    fn()
-                end.record()
-                torch.cuda.synchronize()
-                us = max_over_ranks(comm, start.elapsed_time(end) * 1000.0 / iters, device)
-                out[f"{op}/{algo}/{nbytes}"] = {"us": round(us, 2), "busbw_gbs": round(nbytes * factor / us / 1e3, 1)}
-    return out
 
 
 def main():
@@ -132,6 +100,7 @@ def main():
     import torchcomms_b200 as tc
     from torchcomms_b200.ops import fused
     from torchcomms_b200.parallel.engine import TrainEngine
+    from torchcomms_b200.utils import perf
     from torchcomms_b200.utils.clocks import ClockSampler
 
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -142,55 +111,116 @@ def main():
     comm = tc.new_comm("b200", device, name="bench")
     cfg = model_config(args.model)
     cfg.max_seq_len = max(cfg.max_seq_len, args.seq_len)
-    engine = TrainEngine(cfg, comm, lr=3e-4, seed=0, recompute_blocks=args.recompute_blocks)
     mb, seq = args.micro_batch, args.seq_len
     tokens_per_step = world * mb * seq
-    total_steps = args.warmup + 2 * args.steps
+    total_steps = args.warmup + 2 * args.steps + 3
 
     g = torch.Generator().manual_seed(1234 + rank)
     host_tokens = torch.randint(0, cfg.vocab_size, (total_steps, mb, seq + 1), generator=g).pin_memory()
     dev_tokens = host_tokens.to(device)
     h2d_bytes = mb * (seq + 1) * host_tokens.element_size()
 
-    def device_step(i):
-        t = dev_tokens[i]
-        return engine.step(t[:, :-1].contiguous(), t[:, 1:].contiguous())
+    def log(msg):
+        if rank == 0:
+            print(msg, file=sys.stderr, flush=True)
 
-    def e2e_step(i):
-        t = host_tokens[i].to(device, non_blocking=True)
-        loss = engine.step(t[:, :-1].contiguous(), t[:, 1:].contiguous())
-        return float(loss.item())  # device -> host read of the step's result
+    def run_arm(comm_mode, with_e2e, with_breakdown):
+        """Builds the engine, warms it up, times K steps (and K more end to end), tears it down."""
+        engine = TrainEngine(cfg, comm, lr=3e-4, seed=0, recompute_blocks=args.recompute_blocks, comm_mode=comm_mode)
 
-    for i in range(args.warmup):
-        device_step(i)
+        def device_step(i):
+            t = dev_tokens[i]
+            return engine.step(t[:, :-1].contiguous(), t[:, 1:].contiguous())
 
-    def timed(fn, first):
-        comm.barrier(False)
-        torch.cuda.synchronize()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        launches0 = fused.kernel_launch_count()
-        with ClockSampler(local) as clocks:
-            start.record()
-            last = None
-            for i in range(first, first + args.steps):
-                last = fn(i)
-            end.record()
+        def e2e_step(i):
+            t = host_tokens[i].to(device, non_blocking=True)
+            loss = engine.step(t[:, :-1].contiguous(), t[:, 1:].contiguous())
+            return float(loss.item())  # device -> host read of the step's result
+
+        for i in range(args.warmup):
+            device_step(i)
+
+        def timed(fn, first):
             comm.barrier(False)
             torch.cuda.synchronize()
-        ms = max_over_ranks(comm, start.elapsed_time(end), device)
-        return ms, fused.kernel_launch_count() - launches0, clocks.summary(), last
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            launches0 = fused.kernel_launch_count()
+            with ClockSampler(local) as clocks:
+                start.record()
+                last = None
+                for i in range(first, first + args.steps):
+                    last = fn(i)
+                end.record()
+                comm.barrier(False)
+                torch.cuda.synchronize()
+            (ms,) = perf.max_over_ranks(comm, [start.elapsed_time(end)], device)
+            return ms, fused.kernel_launch_count() - launches0, clocks.summary(), last
 
-    ms, launches, clocks, last_loss = timed(device_step, args.warmup)
-    ms_e2e, _, _, last_e2e = timed(e2e_step, args.warmup + args.steps)
-    peak_gb = torch.cuda.max_memory_allocated() / 2**30
+        out = {}
+        ms, launches, clocks, last_loss = timed(device_step, args.warmup)
+        out.update(ms=ms, launches=launches, clocks=clocks, loss=float(last_loss))
+        if with_e2e:
+            ms_e2e, _, clocks_e2e, _ = timed(e2e_step, args.warmup + args.steps)
+            out.update(ms_e2e=ms_e2e, clocks_e2e=clocks_e2e)
+        if with_breakdown:
+            n_prof = 3
+            tl = engine.attach_timeline()
+            comm.barrier(False)
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            for i in range(n_prof):
+                device_step(args.warmup + 2 * args.steps + i)
+            e.record()
+            torch.cuda.synchronize()
+            tot = tl.totals_ms()
+            engine.detach_timeline()
+            vals = perf.max_over_ranks(comm, [s.elapsed_time(e)] + [tot[k] for k in ("ag", "rs", "wait", "opt")], device)
+            out["breakdown"] = {
+                "profiled_steps": n_prof,
+                "ms_per_step": round(vals[0] / n_prof, 2),
+                "all_gather_kernels_ms": round(vals[1] / n_prof, 2),
+                "reduce_scatter_kernels_ms": round(vals[2] / n_prof, 2),
+                "compute_blocked_on_comm_ms": round(vals[3] / n_prof, 2),
+                "optimizer_ms": round(vals[4] / n_prof, 2),
+                "note": "max over ranks of each quantity; kernel times run from the moment a collective's inputs are "
+                        "ready, so they include waiting for the slowest rank to arrive",
+            }
+        out["peak_mem_gb"] = torch.cuda.max_memory_allocated() / 2**30
+        engine.close()
+        del engine
+        gc.collect()
+        torch.cuda.empty_cache()
+        return out
 
-    collectives = None
+    log(f"[bench] step arm '{args.comm}' on {world} GPU(s)")
+    main_arm = run_arm(args.comm if world > 1 else "symm", with_e2e=True, with_breakdown=True)
+    nccl_arm = None
+    if world > 1 and not args.skip_nccl_arm and args.comm != "nccl":
+        log("[bench] step arm 'nccl'")
+        nccl_arm = run_arm("nccl", with_e2e=False, with_breakdown=True)
+
+    sweep_rows, sweep_summary, ep_rows = None, None, None
     if world > 1 and not args.skip_collectives:
-        collectives = bench_collectives(comm, device, world)
+        log("[bench] collective sweep")
+        sweep_rows = perf.sweep_collectives(
+            comm, device, max_bytes=args.sweep_max_bytes, warmup=args.sweep_warmup, iters=args.sweep_iters, log=log)
+        sweep_summary = perf.summarize_sweep(sweep_rows)
+        if rank == 0 and args.sweep_json:
+            with open(args.sweep_json, "w") as f:
+                json.dump(sweep_rows, f)
+    if world > 1 and not args.skip_ep and 256 % world == 0:
+        log("[bench] MoE dispatch / combine")
+        try:
+            ep_rows = perf.moe_ep_latency(comm, device)
+        except Exception as exc:  # noqa: BLE001 - the step and sweep numbers must still be reported
+            ep_rows = [{"error": f"{type(exc).__name__}: {exc}"}]
 
+    ms, ms_e2e = main_arm["ms"], main_arm["ms_e2e"]
     value = tokens_per_step * args.steps / (ms / 1000.0)
     e2e_value = tokens_per_step * args.steps / (ms_e2e / 1000.0)
     flops = cfg.flops_per_token(seq) * value
+    clocks = main_arm["clocks"]
     line = {
         "metric": "llama3_8b_fsdp_train_tokens_per_s",
         "value": round(value, 1),
@@ -213,7 +243,10 @@ def main():
             "params": cfg.param_count(),
             "optimizer": "AdamW, fp32 master weights and moments",
             "recompute_blocks": args.recompute_blocks,
-            "l2": "every step streams >100 GB of parameters, activations and optimizer state: inputs are larger than L2",
+            "comm": args.comm if world > 1 else "none (one rank)",
+            "l2": "training step: every step streams >100 GB of parameters, activations and optimizer state, inputs "
+                  "are larger than L2; collective sweep: back-to-back calls as in nccl-tests, no flush (messages up "
+                  "to 64 MB are L2-resident for both arms); MoE: a 256 MB buffer is rewritten between calls",
         },
         "e2e": {
             "value": round(e2e_value, 1),
@@ -222,15 +255,37 @@ def main():
             "h2d_bytes_per_step": h2d_bytes,
             "d2h_bytes_per_step": 4,
         },
-        "gpu_launches": int(launches),
+        "gpu_launches": int(main_arm["launches"]),
         "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+        "ms_per_step_x_sm_ghz": round(ms / args.steps * (clocks["sm_mhz"] or 0) / 1000.0, 2),
+        "timed_regions_ms_per_step": [round(ms / args.steps, 3), round(ms_e2e / args.steps, 3)],
         "model_tflops_per_gpu": round(flops / world / 1e12, 1),
-        "peak_mem_gb": round(peak_gb, 1),
-        "final_loss": round(float(last_loss), 4),
+        "peak_mem_gb": round(main_arm["peak_mem_gb"], 1),
+        "final_loss": round(main_arm["loss"], 4),
+        "step_breakdown": main_arm.get("breakdown"),
         "impl": "ours",
     }
-    if collectives is not None:
-        line["collectives_bf16"] = collectives
+    if nccl_arm is not None:
+        nv = tokens_per_step * args.steps / (nccl_arm["ms"] / 1000.0)
+        line["step_nccl_arm"] = {
+            "what": "same engine, parameter all-gather and gradient reduce-scatter on NCCL (bf16) with separate cast kernels",
+            "value": round(nv, 1),
+            "unit": "tokens/s",
+            "ms_per_step": round(nccl_arm["ms"] / args.steps, 3),
+            "clocks": {k: nccl_arm["clocks"][k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+            "own_over_nccl": round(value / nv, 3),
+            "step_breakdown": nccl_arm.get("breakdown"),
+        }
+    if sweep_summary is not None:
+        line["collectives"] = {
+            "protocol": f"{args.sweep_warmup} warm-up + {args.sweep_iters} timed calls per point, device-timed, max over "
+                        "ranks; own = kernels on symmetric tensors, nccl = NCCL on ordinary tensors",
+            "summary": sweep_summary,
+            "rows": [[r["op"], r["dtype"], r["bytes"], r["arm"], r["avg_us"], r["p50_us"], r["busbw_gbs"]] for r in sweep_rows],
+            "row_fields": ["op", "dtype", "bytes", "arm", "avg_us", "p50_us", "busbw_gbs"],
+        }
+    if ep_rows is not None:
+        line["moe_ep"] = ep_rows
     torch.cuda.synchronize()
     comm.finalize()
     if rank == 0:

@@ -206,6 +206,23 @@ TorchComm.get_mem_allocator = _comm_mem_allocator
 TorchComm.mem_allocator = property(_comm_mem_allocator)
 
 
+def _comm_symm_empty(self, shape, dtype):
+    """Collective: a tensor in memory every rank has mapped (see ``torchcomms_b200.mem.symm_empty``)."""
+    from .mem import symm_empty as _s
+
+    return _s(self, shape, dtype)
+
+
+def _comm_symm_free(self, tensor):
+    from .mem import symm_free as _f
+
+    _f(self, tensor)
+
+
+TorchComm.symm_empty = _comm_symm_empty
+TorchComm.symm_free = _comm_symm_free
+
+
 def healthy() -> bool:
     """False once any watchdog of this process saw a timeout or an async error."""
     return _comms._health_is_healthy()

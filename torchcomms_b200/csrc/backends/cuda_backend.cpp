@@ -78,15 +78,15 @@ Algo parse_algo(std::string s) {
 
 CudaWork::CudaWork(std::shared_ptr<CudaApi> api, cudaEvent_t start, cudaEvent_t end, bool pooled, int device,
                    Millis timeout, std::vector<at::Tensor> keep_alive, std::weak_ptr<CudaBackend> owner,
-                   bool in_capture)
+                   bool in_capture, cudaStream_t stream)
     : api_(std::move(api)), start_(start), end_(end), pooled_(pooled), device_(device),
-      keep_alive_(std::move(keep_alive)), owner_(std::move(owner)), in_capture_(in_capture) {
+      keep_alive_(std::move(keep_alive)), owner_(std::move(owner)), in_capture_(in_capture), stream_(stream) {
   set_timeout(timeout);
 }
 
 CudaWork::~CudaWork() {
-  if (start_ == nullptr && end_ == nullptr) {
-    return;
+  if ((start_ == nullptr && end_ == nullptr) || in_capture_) {
+    return;  // nothing recorded, or events owned by the graph's bookkeeping
   }
   auto o = owner_.lock();
   if (pooled_ && o) {
@@ -109,6 +109,9 @@ bool CudaWork::poll(std::chrono::steady_clock::time_point now) {
   const WorkStatus s = status();
   if (s == WorkStatus::COMPLETED || s == WorkStatus::TIMEDOUT || s == WorkStatus::ERROR) {
     return true;
+  }
+  if (start_ == nullptr || end_ == nullptr) {
+    return true;  // event-less work: nothing to follow
   }
   if (!started_seen_) {
     const cudaError_t q = api_->eventQuery(start_);
@@ -153,13 +156,30 @@ void CudaWork::do_wait() {
       set_error(std::string("cudaStreamWaitEvent: ") + api_->errorString(e));
       set_status(WorkStatus::ERROR);
     }
+  } else if (!in_capture_) {
+    // Event-less synchronous operation: the caller's stream is already behind it.
+    set_status(WorkStatus::COMPLETED);
   }
   keep_alive_.clear();
 }
 
 void CudaWork::do_wait_blocking() {
   do_wait();
-  if (in_capture_ || end_ == nullptr) {
+  if (in_capture_) {
+    return;
+  }
+  if (end_ == nullptr) {
+    // Event-less synchronous operation: everything up to now on its stream.
+    if (stream_ != nullptr || device_ >= 0) {
+      c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
+      const cudaError_t e = cudaStreamSynchronize(stream_);
+      if (e != cudaSuccess) {
+        set_error(std::string("cudaStreamSynchronize: ") + api_->errorString(e));
+        set_status(WorkStatus::ERROR);
+        return;
+      }
+    }
+    set_status(WorkStatus::COMPLETED);
     return;
   }
   // Host-blocking with the work's own deadline.
@@ -239,6 +259,17 @@ void CudaBackend::parse_tuning(const Hints& h) {
   t.a2av_blocks = hint_or<int>(h, "a2av_blocks", env_to_value<int>("B200COMMS_A2AV_BLOCKS", t.a2av_blocks));
   t.auto_nccl = hint_or<bool>(h, "auto_nccl", env_to_value<bool>("B200COMMS_AUTO_NCCL", t.auto_nccl));
   t.steps_per_block = hint_or<int>(h, "steps_per_block", env_to_value<int>("B200COMMS_STEPS_PER_BLOCK", t.steps_per_block));
+  t.symm_blocks = hint_or<int>(h, "symm_blocks", env_to_value<int>("B200COMMS_SYMM_BLOCKS", t.symm_blocks));
+  t.symm_blocks_nomc = hint_or<int>(h, "symm_blocks_nomc", env_to_value<int>("B200COMMS_SYMM_BLOCKS_NOMC", t.symm_blocks_nomc));
+  t.symm_ag_mc = hint_or<int>(h, "symm_ag_mc", env_to_value<int>("B200COMMS_SYMM_AG_MC", t.symm_ag_mc));
+  t.symm_rs_mc = hint_or<int>(h, "symm_rs_mc", env_to_value<int>("B200COMMS_SYMM_RS_MC", t.symm_rs_mc));
+  t.symm_ar_mc = hint_or<int>(h, "symm_ar_mc", env_to_value<int>("B200COMMS_SYMM_AR_MC", t.symm_ar_mc));
+  t.symm_blocks = std::max(1, std::min(t.symm_blocks, 128));
+  t.symm_blocks_nomc = std::max(1, std::min(t.symm_blocks_nomc, 128));
+  t.lamport_max_bytes = hint_or<size_t>(h, "lamport_max_bytes", env_to_value<size_t>("B200COMMS_LAMPORT_MAX_BYTES", t.lamport_max_bytes));
+  t.lamport_max_bytes = std::min(t.lamport_max_bytes, static_cast<size_t>(kLamportBlocks) * kLamportPiece);
+  t.channel_streams = hint_or<bool>(h, "channel_streams", env_to_value<bool>("B200COMMS_CHANNEL_STREAMS", t.channel_streams));
+  t.fast_sync = hint_or<bool>(h, "fast_sync", env_to_value<bool>("B200COMMS_FAST_SYNC", t.fast_sync));
   t.staging_bytes = std::max<size_t>(t.staging_bytes, 1u << 20);
   tune_ = t;
 }
@@ -249,6 +280,7 @@ void CudaBackend::set_hints(const Hints& h) {
   parse_tuning(h);
   tune_.staging_bytes = before.staging_bytes;
   tune_.use_nccl = before.use_nccl;
+  tune_.channel_streams = before.channel_streams;
   for (auto& kv : h) {
     opts_.hints[kv.first] = kv.second;
   }
@@ -267,7 +299,7 @@ void CudaBackend::init(at::Device device, const std::string& name, const CommOpt
     std::tie(rank, size) = query_ranksize();
   }
   int ndev = 0;
-  B200C_CUDA_CHECK(cudaGetDeviceCount(&ndev));
+  B200C_CUDA_CHECK(cuda_->getDeviceCount(&ndev));
   TORCH_CHECK(ndev > 0, "no CUDA device is visible");
   const int index = device.has_index() && device.index() >= 0 ? device.index() : rank % ndev;
   device_ = at::Device(at::kCUDA, static_cast<c10::DeviceIndex>(index));
@@ -301,14 +333,18 @@ void CudaBackend::bootstrap(const c10::intrusive_ptr<c10d::Store>& store, int ra
   size_ = size;
   store_ = store;
   c10::cuda::CUDAGuard guard(device_);
-  B200C_CUDA_CHECK(cudaSetDevice(device_.index()));
+  B200C_CUDA_CHECK(cuda_->setDevice(device_.index()));
 
   symm_ = std::make_unique<SymmMemory>(store_, rank_, size_, device_.index(), drv_, opts_.timeout, tune_.use_multicast);
   layout_.bulk_off = 0;
   layout_.bulk_bytes = round_up(tune_.staging_bytes, 4096);
   layout_.small_off = layout_.bulk_off + layout_.bulk_bytes;
   layout_.small_bytes = round_up(kSmallBytes, 4096);
-  const size_t flags_off = layout_.small_off + layout_.small_bytes;
+  layout_.symm_meta_off = layout_.small_off + layout_.small_bytes;
+  layout_.symm_meta_bytes = round_up(kSymmMetaBytes, 4096);
+  layout_.lamport_off = layout_.symm_meta_off + layout_.symm_meta_bytes;
+  layout_.lamport_bytes = round_up(kLamportBytes, 4096);
+  const size_t flags_off = layout_.lamport_off + layout_.lamport_bytes;
   const size_t total = flags_off + round_up(kFlagBytes, 4096);
   heap_ = symm_->allocate(total, tune_.use_multicast);
 
@@ -325,25 +361,40 @@ void CudaBackend::bootstrap(const c10::intrusive_ptr<c10d::Store>& store, int ra
   dev_.timeout_ns = tune_.device_wait_ns;
 
   const size_t epoch_bytes = static_cast<size_t>(kFlagSets) * kMaxBlocks * sizeof(uint32_t);
-  B200C_CUDA_CHECK(cudaMalloc(&epochs_dev_, epoch_bytes));
-  B200C_CUDA_CHECK(cudaMemset(epochs_dev_, 0, epoch_bytes));
+  B200C_CUDA_CHECK(cuda_->mallocDevice(reinterpret_cast<void**>(&epochs_dev_), epoch_bytes));
+  B200C_CUDA_CHECK(cuda_->memsetDevice(epochs_dev_, 0, epoch_bytes));
   dev_.epochs = epochs_dev_;
-  B200C_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped));
+  B200C_CUDA_CHECK(cuda_->hostAllocMapped(reinterpret_cast<void**>(&status_host_), reinterpret_cast<void**>(&status_dev_), 64));
   std::memset(status_host_, 0, 64);
-  B200C_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&status_dev_), status_host_, 0));
   dev_.status = status_dev_;
-  B200C_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&replay_pool_host_),
-                                 2 * kMaxGraphEntries * sizeof(unsigned long long), cudaHostAllocMapped));
+  B200C_CUDA_CHECK(cuda_->hostAllocMapped(reinterpret_cast<void**>(&replay_pool_host_),
+                                          reinterpret_cast<void**>(&replay_pool_dev_),
+                                          2 * kMaxGraphEntries * sizeof(unsigned long long)));
   std::memset(replay_pool_host_, 0, 2 * kMaxGraphEntries * sizeof(unsigned long long));
-  B200C_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&replay_pool_dev_), replay_pool_host_, 0));
 
   int lo = 0, hi = 0;
-  B200C_CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-  B200C_CUDA_CHECK(cudaStreamCreateWithPriority(&internal_stream_, cudaStreamNonBlocking,
-                                                opts_.is_high_priority_stream ? hi : lo));
+  B200C_CUDA_CHECK(cuda_->streamPriorityRange(&lo, &hi));
+  for (int ch = 0; ch < kChanCount; ++ch) {
+    ChanState& cs = chans_[ch];
+    cs = ChanState{};
+    if (ch == kChanMain || tune_.channel_streams) {
+      B200C_CUDA_CHECK(cuda_->streamCreateWithPriority(&cs.stream, cudaStreamNonBlocking,
+                                                       opts_.is_high_priority_stream ? hi : lo));
+      cs.owns_stream = true;
+    } else {
+      cs.stream = chans_[kChanMain].stream;
+    }
+    B200C_CUDA_CHECK(cuda_->eventCreate(&cs.order_event, cudaEventDisableTiming));
+  }
+  internal_stream_ = chans_[kChanMain].stream;
   B200C_CUDA_CHECK(cuda_->eventCreate(&dep_event_, cudaEventDisableTiming));
-  B200C_CUDA_CHECK(cuda_->eventCreate(&last_end_, cudaEventDisableTiming));
-  B200C_CUDA_CHECK(cudaDeviceSynchronize());
+  // The flag-less all-reduce starts from buffers full of its "nothing here yet" word.
+  B200C_CUDA_CHECK(launch_lamport_init(heap_->local() + layout_.lamport_off, internal_stream_));
+  B200C_CUDA_CHECK(cuda_->deviceSynchronize());
+  if (size_ > 1) {
+    // Nobody sends before every rank's buffers are prepared.
+    store_barrier(*store_, "lamport_ready", rank_, size_, opts_.timeout);
+  }
 
   if (size_ > 1 && tune_.use_nccl) {
     init_nccl();
@@ -449,59 +500,142 @@ void CudaBackend::give_events(cudaEvent_t a, cudaEvent_t b) {
   }
 }
 
+namespace {
+// Handed to the CUDA user object that rides on a captured graph; freed by the callback.
+struct GraphReleaseNote {
+  std::weak_ptr<CudaBackend> owner;
+  unsigned long long graph_id;
+};
+void CUDART_CB on_graph_destroyed(void* arg) {
+  // Runs on a driver thread once the graph and all its executables are gone.
+  // No CUDA calls here: only leave a note for the watchdog.
+  auto* note = static_cast<GraphReleaseNote*>(arg);
+  if (auto owner = note->owner.lock()) {
+    owner->note_graph_released(note->graph_id);
+  }
+  delete note;
+}
+} // namespace
+
+void CudaBackend::note_graph_released(unsigned long long graph_id) {
+  std::lock_guard<std::mutex> g(released_mu_);
+  released_ids_.push_back(graph_id);
+}
+
 WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, std::vector<at::Tensor> keep_alive,
-                         const std::function<void(cudaStream_t)>& launch) {
+                         const std::function<void(cudaStream_t)>& launch, int chan, bool own_kernel) {
   check_usable();
   c10::cuda::CUDAGuard guard(device_);
   cudaStream_t current = at::cuda::getCurrentCUDAStream(device_.index()).stream();
-  cudaStream_t stream = async_op ? internal_stream_ : current;
+  ChanState& cs = chans_[chan];
+  cudaStream_t stream = async_op ? cs.stream : current;
   bool capturing = false;
   unsigned long long graph_id = 0;
   cuda_->streamIsCapturing(current, &capturing, &graph_id);
 
   if (async_op) {
     B200C_CUDA_CHECK(cuda_->eventRecord(dep_event_, current));
-    B200C_CUDA_CHECK(cuda_->streamWaitEvent(internal_stream_, dep_event_));
+    B200C_CUDA_CHECK(cuda_->streamWaitEvent(cs.stream, dep_event_));
   }
-  // Operations of one communicator share staging slots and flags: keep them
-  // in issue order even across streams. (Inside a capture only dependencies
-  // created inside the same capture are legal, and those are already there.)
-  if (last_work_ && last_stream_ != stream && !capturing) {
-    B200C_CUDA_CHECK(cuda_->streamWaitEvent(stream, last_work_->end_event()));
+  if (capturing) {
+    // Inside a capture every operation of the communicator follows the one
+    // captured before it, whatever their channels and streams. Unordered
+    // branches of one graph may be started in a different order on different
+    // ranks; two kernels that each wait for their peers (an NCCL kernel and a
+    // peer-memory kernel, say) could then wait for each other for good.
+    std::lock_guard<std::mutex> g(wd_mu_);
+    auto it = capture_tail_.find(graph_id);
+    if (it != capture_tail_.end() && it->second.stream != stream) {
+      B200C_CUDA_CHECK(cuda_->streamWaitEvent(stream, it->second.end));
+    }
+  } else if (cs.last_stream != nullptr && cs.last_stream != stream) {
+    // Operations of one channel share staging slots and flags: keep them in
+    // issue order across streams.
+    if (cs.last_work) {
+      B200C_CUDA_CHECK(cuda_->streamWaitEvent(stream, cs.last_work->end_event()));
+    } else {
+      // The previous operation recorded no event: mark its stream now.
+      B200C_CUDA_CHECK(cuda_->eventRecord(cs.order_event, cs.last_stream));
+      B200C_CUDA_CHECK(cuda_->streamWaitEvent(stream, cs.order_event));
+    }
+  }
+
+  auto self = std::static_pointer_cast<CudaBackend>(shared_from_this());
+  if (own_kernel && !async_op && !capturing && tune_.fast_sync && !observed()) {
+    // Nobody follows this operation through work hooks, stream order gives
+    // wait() its meaning, and a failed device wait shows in the status word
+    // the watchdog reads: no events, nothing queued.
+    launch(stream);
+    cs.last_stream = stream;
+    cs.last_work.reset();
+    ops_issued_++;
+    {
+      std::lock_guard<std::mutex> g(wd_mu_);
+      algo_counts_[what]++;
+    }
+    return c10::make_intrusive<CudaWork>(cuda_, nullptr, nullptr, false, device_.index(), effective_timeout(o),
+                                         std::vector<at::Tensor>{}, self, false, stream);
   }
 
   cudaEvent_t ev_start = nullptr, ev_end = nullptr;
-  if (capturing) {
-    // Resource creation is not a capturable operation: step out of the strict
-    // capture mode for the two calls.
-    cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
-    cudaThreadExchangeStreamCaptureMode(&mode);
-    const cudaError_t e1 = cuda_->eventCreate(&ev_start, cudaEventDisableTiming);
-    const cudaError_t e2 = cuda_->eventCreate(&ev_end, cudaEventDisableTiming);
-    cudaThreadExchangeStreamCaptureMode(&mode);
-    B200C_CUDA_CHECK(e1);
-    B200C_CUDA_CHECK(e2);
-  } else {
-    std::tie(ev_start, ev_end) = take_events();
-  }
-
   unsigned long long* replay_counters = nullptr;  // device alias of this collective's replay counters
   if (capturing) {
+    // Resource creation is not a capturable operation: step out of the strict
+    // capture mode for these calls.
+    cudaStreamCaptureMode mode = cudaStreamCaptureModeRelaxed;
+    cuda_->exchangeCaptureMode(&mode);
+    const cudaError_t e1 = cuda_->eventCreate(&ev_start, cudaEventDisableTiming);
+    const cudaError_t e2 = cuda_->eventCreate(&ev_end, cudaEventDisableTiming);
+    cudaError_t e3 = cudaSuccess;
+    bool need_retain = false;
+    {
+      std::lock_guard<std::mutex> g(wd_mu_);
+      need_retain = !graphs_[graph_id].retained;
+      graphs_[graph_id].retained = true;
+    }
+    if (need_retain) {
+      // When the graph (and every executable made from it) is destroyed, its
+      // entries are released: see the watchdog.
+      cudaGraph_t graph = nullptr;
+      e3 = cuda_->streamCaptureGraph(current, &graph);
+      if (e3 == cudaSuccess && graph != nullptr) {
+        auto* note = new GraphReleaseNote{self, graph_id};
+        e3 = cuda_->graphRetainCallback(graph, on_graph_destroyed, note);
+        if (e3 != cudaSuccess) delete note;
+      }
+    }
+    cuda_->exchangeCaptureMode(&mode);
+    B200C_CUDA_CHECK(e1);
+    B200C_CUDA_CHECK(e2);
+    B200C_CUDA_CHECK(e3);
+
     GraphEntry e{};
     e.graph_id = graph_id;
-    e.index = graph_next_index_[graph_id]++;
     e.stream = reinterpret_cast<uintptr_t>(stream);
     e.timeout = effective_timeout(o);
     std::lock_guard<std::mutex> g(wd_mu_);
-    TORCH_CHECK(graph_entries_.size() < kMaxGraphEntries,
-                "too many collectives captured into CUDA graphs on this communicator (", kMaxGraphEntries, ")");
+    GraphState& gs = graphs_[graph_id];
+    gs.events.push_back(ev_start);
+    gs.events.push_back(ev_end);
+    e.index = gs.next_index++;
+    if (free_slots_.empty()) {
+      TORCH_CHECK(next_slot_ < kMaxGraphEntries,
+                  "too many collectives are captured in live CUDA graphs on this communicator (", kMaxGraphEntries,
+                  "); destroy graphs that are no longer replayed");
+      e.slot = next_slot_++;
+    } else {
+      e.slot = free_slots_.back();
+      free_slots_.pop_back();
+    }
     // Counter pairs come from a page pinned at start-up: nothing is allocated
     // while a capture is open.
-    e.counters_host = replay_pool_host_ + 2 * graph_entries_.size();
-    e.counters_dev = replay_pool_dev_ + 2 * graph_entries_.size();
+    e.counters_host = replay_pool_host_ + 2 * e.slot;
+    e.counters_dev = replay_pool_dev_ + 2 * e.slot;
     e.counters_host[0] = e.counters_host[1] = 0;
     replay_counters = e.counters_dev;
     graph_entries_.push_back(e);
+  } else {
+    std::tie(ev_start, ev_end) = take_events();
   }
 
   B200C_CUDA_CHECK(cuda_->eventRecord(ev_start, stream));
@@ -513,27 +647,39 @@ WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, st
     B200C_CUDA_CHECK(launch_counter_increment(replay_counters + 1, stream));
   }
   B200C_CUDA_CHECK(cuda_->eventRecord(ev_end, stream));
-  auto self = std::static_pointer_cast<CudaBackend>(shared_from_this());
   if (!async_op) {
     keep_alive.clear();  // stream order already protects the tensors
   }
+  // Events made during a capture belong to the graph's bookkeeping (the next
+  // captured operation may have to wait on them after this work is gone).
   auto work = c10::make_intrusive<CudaWork>(cuda_, ev_start, ev_end, !capturing, device_.index(), effective_timeout(o),
-                                            std::move(keep_alive), self, capturing);
+                                            std::move(keep_alive), self, capturing, stream);
   ops_issued_++;
   if (!capturing) {
     // The end event of the latest operation doubles as the cross-stream
     // ordering point for the next one (the work keeps the event alive).
-    last_work_ = work;
-    last_stream_ = stream;
+    cs.last_work = work;
+    cs.last_stream = stream;
   }
   {
     std::lock_guard<std::mutex> g(wd_mu_);
     algo_counts_[what]++;
-    if (!capturing) {
+    if (capturing) {
+      capture_tail_[graph_id] = CaptureTail{ev_end, stream};
+    } else {
       inflight_.push_back(work);
     }
   }
   return work;
+}
+
+void CudaBackend::sync_own_streams() {
+  for (int ch = 0; ch < kChanCount; ++ch) {
+    if (chans_[ch].stream != nullptr && (ch == kChanMain || chans_[ch].owns_stream)) {
+      cuda_->streamSynchronize(chans_[ch].stream);
+    }
+  }
+  cuda_->streamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
 }
 
 void CudaBackend::start_watchdog() {
@@ -595,6 +741,7 @@ void CudaBackend::watchdog_loop() {
         failure = "NCCL asynchronous error: " + nccl_->errorString(async);
       }
     }
+    drop_released_graphs();
     // Graph replays: counters tell how many times each captured collective
     // started and ended.
     std::vector<std::tuple<unsigned long long, unsigned long long, uintptr_t, size_t, char>> replay_events;
@@ -632,6 +779,30 @@ void CudaBackend::watchdog_loop() {
   }
 }
 
+void CudaBackend::drop_released_graphs() {
+  std::vector<unsigned long long> gone;
+  {
+    std::lock_guard<std::mutex> g(released_mu_);
+    gone.swap(released_ids_);
+  }
+  for (unsigned long long id : gone) {
+    for (auto it = graph_entries_.begin(); it != graph_entries_.end();) {
+      if (it->graph_id == id) {
+        free_slots_.push_back(it->slot);
+        it = graph_entries_.erase(it);
+      } else {
+        ++it;
+      }
+    }
+    auto gs = graphs_.find(id);
+    if (gs != graphs_.end()) {
+      for (cudaEvent_t e : gs->second.events) cuda_->eventDestroy(e);
+      graphs_.erase(gs);
+    }
+    capture_tail_.erase(id);
+  }
+}
+
 void CudaBackend::finalize() {
   TORCH_CHECK(!finalized_, "communicator '", name_, "' was already finalized");
   TORCH_CHECK(initialized_ || opts_.enable_reconfigure, "communicator '", name_, "' is not initialised");
@@ -651,10 +822,22 @@ void CudaBackend::finalize() {
 // Waits for this rank's work, meets the other members (unless the communicator is broken), and
 // gives back everything bootstrap() created. The communicator can be bootstrapped again afterwards.
 void CudaBackend::drain_and_release(bool broken, const char* why) {
-  if (!broken) {
+  if (broken) {
+    // Kernels of this rank may still be running. Tell them to stop waiting,
+    // end NCCL's work, and only then wait for the streams: every device wait
+    // is bounded and looks at the abort bit, so this returns, and nothing is
+    // unmapped under a live kernel.
+    if (status_host_ != nullptr) {
+      reinterpret_cast<volatile uint32_t*>(status_host_)[0] |= kStatusAbort;
+    }
+    if (nccl_comm_ != nullptr) {
+      nccl_->commAbort(nccl_comm_);
+      nccl_comm_ = nullptr;
+    }
+    sync_own_streams();
+  } else {
     // Drain: every rank's kernels are done before any mapping disappears.
-    cudaStreamSynchronize(internal_stream_);
-    cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
+    sync_own_streams();
     if (size_ > 1) {
       try {
         store_barrier(*store_, why, rank_, size_, std::min<Millis>(opts_.timeout, Millis(30000)));
@@ -665,14 +848,29 @@ void CudaBackend::drain_and_release(bool broken, const char* why) {
     }
   }
   stop_watchdog();
-  last_work_.reset();
+  for (auto& cs : chans_) cs.last_work.reset();
   initialized_ = false;
   {
     std::lock_guard<std::mutex> g(wd_mu_);
     inflight_.clear();
     graph_entries_.clear();
+    for (auto& kv : graphs_) {
+      for (cudaEvent_t e : kv.second.events) cuda_->eventDestroy(e);
+    }
+    graphs_.clear();
+    capture_tail_.clear();
+    free_slots_.clear();
+    next_slot_ = 0;
   }
-  if (replay_pool_host_) cudaFreeHost(replay_pool_host_);
+  {
+    // Tensors handed out by symm_empty() dangle from here on; registrations go with the mappings.
+    std::lock_guard<std::mutex> g(symm_mu_);
+    for (auto& kv : symm_regs_) {
+      if (symm_) symm_->release(kv.second.seg);
+    }
+    symm_regs_.clear();
+  }
+  if (replay_pool_host_) cuda_->freeHost(replay_pool_host_);
   replay_pool_host_ = nullptr;
   if (nccl_comm_ != nullptr) {
     if (broken) {
@@ -687,8 +885,8 @@ void CudaBackend::drain_and_release(bool broken, const char* why) {
     heap_.reset();
   }
   symm_.reset();
-  if (epochs_dev_) cudaFree(epochs_dev_);
-  if (status_host_) cudaFreeHost(status_host_);
+  if (epochs_dev_) cuda_->freeDevice(epochs_dev_);
+  if (status_host_) cuda_->freeHost(status_host_);
   epochs_dev_ = nullptr;
   status_host_ = nullptr;
   {
@@ -697,9 +895,12 @@ void CudaBackend::drain_and_release(bool broken, const char* why) {
     event_pool_.clear();
   }
   if (dep_event_) cuda_->eventDestroy(dep_event_);
-  if (last_end_) cuda_->eventDestroy(last_end_);
-  if (internal_stream_) cudaStreamDestroy(internal_stream_);
-  dep_event_ = last_end_ = nullptr;
+  dep_event_ = nullptr;
+  for (auto& cs : chans_) {
+    if (cs.order_event) cuda_->eventDestroy(cs.order_event);
+    if (cs.stream && cs.owns_stream) cuda_->streamDestroy(cs.stream);
+    cs = ChanState{};
+  }
   internal_stream_ = nullptr;
 }
 
@@ -734,8 +935,7 @@ WorkPtr CudaBackend::reconfigure(const ReconfigureOptions& o) {
     // Nothing of this rank is in flight any more; once every member of the NEW list says the same,
     // nobody can still be reading memory this rank is about to unmap. Members that left do not come
     // to any barrier, so the old membership's closing barrier is skipped (released as "broken").
-    cudaStreamSynchronize(internal_stream_);
-    cudaStreamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
+    sync_own_streams();
     if (members.size() > 1) {
       store_barrier(*scoped, "quiesced", idx, static_cast<int>(members.size()), opts_.timeout);
     }
@@ -816,6 +1016,24 @@ LaunchShape CudaBackend::shape_for(size_t bytes, size_t slot_multiplier, int blo
   return s;
 }
 
+// Grid of a one-pass kernel on symmetric buffers: the configured block count
+// (hint "symm_blocks" for one call), fewer when the payload gives each block
+// less than a few iterations. Depends only on sizes, hints and on whether the
+// buffer has a multicast alias, so every rank computes the same number.
+int CudaBackend::symm_blocks_for(bool mc, size_t vectors, const OpOptions& o) const {
+  int cap = mc ? tune_.symm_blocks : tune_.symm_blocks_nomc;
+  cap = std::max(1, std::min(128, hint_or<int>(o.hints, "symm_blocks", cap)));
+  const size_t per_block = 512 * 4;  // threads x unroll
+  const size_t want = (vectors + per_block - 1) / per_block;
+  return static_cast<int>(std::max<size_t>(1, std::min<size_t>(cap, want)));
+}
+
+bool CudaBackend::symm_use_mc(int knob, bool mc_by_default, const SymmView& v, const OpOptions& o) const {
+  if (!tune_.use_multicast || v.mc == nullptr) return false;
+  const int want = hint_or<int>(o.hints, "symm_mc", knob);
+  return want < 0 ? mc_by_default : want != 0;
+}
+
 static RedKind red_kind(const ReduceOp& op) {
   switch (op.type()) {
     case RedOpType::PRODUCT: return RedKind::PROD;
@@ -880,6 +1098,32 @@ WorkPtr CudaBackend::all_reduce(at::Tensor& t, const ReduceOp& op, bool async_op
   DType dt;
   to_dtype(t.scalar_type(), &dt);
   const bool sum_like = red_kind(op) == RedKind::SUM;
+  if (algo == Algo::AUTO && sum_like && size_ > 1) {
+    const float scale = red_scale(op, size_);
+    const bool mc = tune_.use_multicast && dev_.mc_heap != nullptr;
+    at::Tensor tt = t;
+    if (bytes <= tune_.lamport_max_bytes) {
+      // Latency class: the flag-less kernel (one one-way trip, no barrier, no staging).
+      bytes_issued_ += bytes;
+      return run("all_reduce/lamport", async_op, o, {t}, [this, tt, dt, scale, mc](cudaStream_t s) {
+        const void* in = tt.data_ptr();
+        void* out = tt.data_ptr();
+        B200C_CUDA_CHECK(launch_all_reduce_lamport(&dev_, layout_, 0, &in, &out, tt.numel(), dt, scale, mc, s));
+      }, kChanSymAr, true);
+    }
+    SymmView sv;
+    const size_t pack = 16 / dtype_size(dt);
+    if (t.numel() % pack == 0 && lookup_symm(t.data_ptr(), bytes, &sv) &&
+        reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0) {
+      // The tensor lives in symmetric memory: reduce it in place, one pass over NVLink.
+      const bool smc = symm_use_mc(tune_.symm_ar_mc, size_ >= 4, sv, o);
+      const int blocks = symm_blocks_for(smc, t.numel() / pack / size_, o);
+      bytes_issued_ += bytes;
+      return run("all_reduce/symm", async_op, o, {t}, [this, tt, sv, dt, scale, smc, blocks](cudaStream_t s) {
+        B200C_CUDA_CHECK(launch_symm_all_reduce(&dev_, 0, &sv, tt.numel(), dt, scale, smc, blocks, s));
+      }, kChanSymAr, true);
+    }
+  }
   int kalgo;
   if (algo == Algo::ONESHOT) kalgo = 0;
   else if (algo == Algo::TWOSHOT || algo == Algo::STAGED) kalgo = 1;
@@ -896,7 +1140,7 @@ WorkPtr CudaBackend::all_reduce(at::Tensor& t, const ReduceOp& op, bool async_op
                const void* in = tt.data_ptr();
                void* out = tt.data_ptr();
                B200C_CUDA_CHECK(launch_all_reduce(&dev_, layout_, 0, &in, &out, tt.numel(), dt, rk, scale, kalgo, mc, shape, s));
-             });
+             }, kChanMain, true);
 }
 
 WorkPtr CudaBackend::reduce(const at::Tensor& t, int root, const ReduceOp& op, bool async_op, const OpOptions& o) {
@@ -963,7 +1207,7 @@ WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bo
       bytes_issued_ += in.nbytes();
       return run("all_gather/single_rank", async_op, o, {in}, [i, ot, ik, ok](cudaStream_t s) {
         B200C_CUDA_CHECK(launch_cast_scale(i.data_ptr(), ik, ot.data_ptr(), ok, static_cast<size_t>(i.numel()), 1.0f, s));
-      });
+      }, kChanSymAg, true);
     }
   }
   if (!cast && nccl_comm_ != nullptr && route(Coll::ALL_GATHER, out.nbytes(), o) == Algo::NCCL) {
@@ -977,6 +1221,24 @@ WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bo
   }
   const size_t bytes = in.nbytes();
   const Algo algo = algo_override(o);
+  if (algo == Algo::AUTO || algo == Algo::KERNEL) {
+    SymmView sv;
+    const size_t wire = cast ? bytes / 2 : bytes;
+    if (wire % 16 == 0 && lookup_symm(out.data_ptr(), out.nbytes(), &sv) &&
+        reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0) {
+      // The output lives in symmetric memory: every rank stores its shard
+      // straight into every copy (through the switch's multicast when bound).
+      const bool smc = symm_use_mc(tune_.symm_ag_mc, false, sv, o);
+      const int blocks = symm_blocks_for(smc, wire / 16, o);
+      at::Tensor i = in, ot = out;
+      bytes_issued_ += bytes;
+      return run(cast ? "all_gather/symm+cast" : "all_gather/symm", async_op, o, {in},
+                 [this, i, ot, sv, bytes, cast, smc, blocks](cudaStream_t s) {
+                   const void* ip = i.data_ptr();
+                   B200C_CUDA_CHECK(launch_symm_all_gather(&dev_, 0, &ip, &sv, bytes, cast, smc, blocks, s));
+                 }, kChanSymAg, true);
+    }
+  }
   // Multicast push pays while the message is latency / launch bound; big gathers pull.
   const bool mc = tune_.use_multicast && dev_.mc_heap != nullptr && size_ >= tune_.ag_push_min_ranks && bytes <= (8u << 20);
   const bool oneshot = !cast && algo != Algo::TWOSHOT && algo != Algo::STAGED &&
@@ -994,7 +1256,7 @@ WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bo
                const void* ip = i.data_ptr();
                void* op_ = ot.data_ptr();
                B200C_CUDA_CHECK(launch_all_gather(&dev_, layout_, 0, &ip, &op_, bytes, cast, mc, shape, s));
-             });
+             }, kChanMain, true);
 }
 
 WorkPtr CudaBackend::all_gather(const std::vector<at::Tensor>& outs, const at::Tensor& in, bool async_op, const OpOptions& o) {
@@ -1060,6 +1322,43 @@ static WorkPtr exchange(CudaBackend* self, const char* what, at::Tensor in, at::
   });
 }
 
+// All-to-all(v) straight into a symmetric output: every rank stores its block
+// for rank p into p's copy of `out`. `send` / `recv` as in exchange().
+static WorkPtr exchange_symm(CudaBackend* self, const char* what, at::Tensor in, at::Tensor out, const SymmView& sv,
+                             std::vector<std::pair<size_t, size_t>> send, std::vector<std::pair<size_t, size_t>> recv,
+                             bool equal_splits, at::Tensor dev_counts, size_t elem_bytes, bool async_op,
+                             const OpOptions& o) {
+  const int n = self->size();
+  int blocks = std::max(1, std::min(128, hint_or<int>(o.hints, "symm_blocks", self->tuning().symm_blocks_nomc)));
+  if (equal_splits) {
+    // Every rank sends the same amount: small exchanges need few blocks (fewer barriers to cross).
+    const size_t want = (in.nbytes() / 16 + 512 * 4 - 1) / (512 * 4);
+    blocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(blocks, want)));
+  }
+  blocks = std::max(n, blocks / n * n);
+  std::vector<at::Tensor> keep = {in};
+  if (dev_counts.defined()) keep.push_back(dev_counts);
+  return self->run(what, async_op, o, std::move(keep),
+                   [self, in, out, sv, send, recv, equal_splits, dev_counts, elem_bytes, blocks, n](cudaStream_t s) {
+                     std::vector<size_t> so(n), sl(n), ro(n), rl(n);
+                     for (int p = 0; p < n; ++p) {
+                       so[p] = send[p].first;
+                       sl[p] = send[p].second;
+                       ro[p] = recv[p].first;
+                       rl[p] = recv[p].second;
+                     }
+                     const void* ip = in.data_ptr();
+                     const long long* counts =
+                         dev_counts.defined() ? reinterpret_cast<const long long*>(dev_counts.data_ptr<int64_t>()) : nullptr;
+                     const size_t in_cap = in.nbytes(), out_cap = out.nbytes();
+                     B200C_CUDA_CHECK(launch_symm_all_to_all(&self->comm_dev(), self->layout(), 0, &ip, &sv, &in_cap,
+                                                             &out_cap, so.data(), sl.data(), ro.data(), rl.data(),
+                                                             counts != nullptr ? &counts : nullptr, elem_bytes,
+                                                             !equal_splits, blocks, s));
+                   },
+                   kChanSymAr, true);
+}
+
 WorkPtr CudaBackend::all_gather_v(const std::vector<at::Tensor>& outs, const at::Tensor& in, bool async_op, const OpOptions& o) {
   TORCH_CHECK(static_cast<int>(outs.size()) == size_, "all_gather_v: need size() output tensors");
   check_tensor(in, device_, "all_gather_v");
@@ -1103,7 +1402,7 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
       bytes_issued_ += in.nbytes();
       return run("reduce_scatter/single_rank", async_op, o, {in}, [i, ot, ik, ok, scale](cudaStream_t s) {
         B200C_CUDA_CHECK(launch_cast_scale(i.data_ptr(), ik, ot.data_ptr(), ok, static_cast<size_t>(ot.numel()), scale, s));
-      });
+      }, kChanSymRs, true);
     }
   }
   const bool same = in.scalar_type() == out.scalar_type();
@@ -1150,6 +1449,25 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
   }
   const float scale = red_scale(op, size_);
   const RedKind rk = red_kind(op);
+  if (algo == Algo::AUTO && rk == RedKind::SUM && dwire == din && hint_or<unsigned long long>(o.hints, "sr_seed", 0ull) == 0) {
+    SymmView sv;
+    const size_t pack = 16 / dtype_size(din);
+    const bool types_ok = din == dout || (din == DType::BF16 && dout == DType::F32);
+    if (types_ok && out.numel() % pack == 0 && lookup_symm(in.data_ptr(), in.nbytes(), &sv) &&
+        reinterpret_cast<uintptr_t>(in.data_ptr()) % 16 == 0) {
+      // The input lives in symmetric memory: every rank reads its slice of
+      // every copy (summed by the switch when bound to the multicast object)
+      // straight into the output; scale and cast happen in registers.
+      const bool smc = symm_use_mc(tune_.symm_rs_mc, false, sv, o);
+      const int blocks = symm_blocks_for(smc, out.numel() / pack, o);
+      at::Tensor i = in, ot = out;
+      bytes_issued_ += in.nbytes();
+      return run("reduce_scatter/symm", async_op, o, {in}, [this, i, ot, sv, din, dout, scale, smc, blocks](cudaStream_t s) {
+        void* op_ = ot.data_ptr();
+        B200C_CUDA_CHECK(launch_symm_reduce_scatter(&dev_, 0, &sv, &op_, ot.numel(), din, dout, scale, smc, blocks, s));
+      }, kChanSymRs, true);
+    }
+  }
   const bool mc = tune_.use_multicast && rk == RedKind::SUM && dev_.mc_heap != nullptr;
   const size_t wire_bytes = out.numel() * dtype_size(dwire);
   LaunchShape shape = shape_for(wire_bytes, size_, in.nbytes() < (64u << 20) ? 148 : 0);
@@ -1168,7 +1486,7 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
                const void* ip = i.data_ptr();
                void* op_ = ot.data_ptr();
                B200C_CUDA_CHECK(launch_reduce_scatter(&dev_, layout_, 0, &ip, &op_, ot.numel(), din, dwire, dout, rk, scale, mc, shape, s, sr_seed));
-             });
+             }, kChanMain, true);
 }
 
 WorkPtr CudaBackend::reduce_scatter(at::Tensor& out, const std::vector<at::Tensor>& ins, const ReduceOp& op, bool async_op, const OpOptions& o) {
@@ -1244,6 +1562,13 @@ WorkPtr CudaBackend::all_to_all_single(at::Tensor& out, const at::Tensor& in, bo
     recv[p] = {p * blk, blk};
   }
   bytes_issued_ += in.nbytes();
+  {
+    const Algo forced = algo_override(o);
+    SymmView sv;
+    if ((forced == Algo::AUTO || forced == Algo::KERNEL) && size_ > 1 && lookup_symm(out.data_ptr(), out.nbytes(), &sv)) {
+      return exchange_symm(this, "all_to_all_single/symm", in, out, sv, send, recv, true, at::Tensor(), 1, async_op, o);
+    }
+  }
   if (nccl_comm_ != nullptr && route(Coll::ALL_TO_ALL, in.nbytes(), o) == Algo::NCCL) {
     return exchange_nccl("all_to_all_single/nccl", in, out, send, recv, async_op, o);
   }
@@ -1272,6 +1597,13 @@ WorkPtr CudaBackend::all_to_all_v_single(at::Tensor& out, const at::Tensor& in, 
   TORCH_CHECK(so <= in.nbytes(), "all_to_all_v_single: input splits exceed the input tensor");
   TORCH_CHECK(ro <= out.nbytes(), "all_to_all_v_single: output splits exceed the output tensor");
   bytes_issued_ += so;
+  {
+    const Algo forced = algo_override(o);
+    SymmView sv;
+    if ((forced == Algo::AUTO || forced == Algo::KERNEL) && size_ > 1 && lookup_symm(out.data_ptr(), out.nbytes(), &sv)) {
+      return exchange_symm(this, "all_to_all_v_single/symm", in, out, sv, send, recv, false, at::Tensor(), 1, async_op, o);
+    }
+  }
   if (nccl_comm_ != nullptr && route(Coll::ALL_TO_ALL, so, o) == Algo::NCCL) {
     return exchange_nccl("all_to_all_v_single/nccl", in, out, send, recv, async_op, o);
   }
@@ -1316,8 +1648,27 @@ WorkPtr CudaBackend::device_alltoallv_single(at::Tensor& out, const at::Tensor& 
   check_tensor(in_splits, device_, "device_alltoallv_single");
   TORCH_CHECK(in_splits.scalar_type() == at::kLong && in_splits.numel() == size_,
               "device_alltoallv_single: input_split_sizes must be an int64 device tensor of size() entries");
-  (void)out_splits;  // receive sizes are learnt from the senders on the device
+  TORCH_CHECK(out.scalar_type() == in.scalar_type(), "device_alltoallv_single: dtype mismatch");
   const size_t row = in.dim() > 0 && in.size(0) > 0 ? in.nbytes() / in.size(0) : in.element_size();
+  {
+    const size_t out_row = out.dim() > 0 && out.size(0) > 0 ? out.nbytes() / out.size(0) : out.element_size();
+    TORCH_CHECK(out_row == row, "device_alltoallv_single: input and output must have the same dim-0 slice size (",
+                row, " vs ", out_row, " bytes)");
+  }
+  // Receive sizes are learnt from the senders on the device; `out_splits` is
+  // the caller's own view of them and is only checked for shape.
+  if (out_splits.defined() && out_splits.numel() != 0) {
+    TORCH_CHECK(out_splits.scalar_type() == at::kLong && out_splits.numel() == size_,
+                "device_alltoallv_single: output_split_sizes must be an int64 tensor of size() entries");
+  }
+  {
+    SymmView sv;
+    const Algo forced = algo_override(o);
+    if ((forced == Algo::AUTO || forced == Algo::KERNEL) && size_ > 1 && lookup_symm(out.data_ptr(), out.nbytes(), &sv)) {
+      std::vector<std::pair<size_t, size_t>> none(size_, {0, 0});
+      return exchange_symm(this, "device_alltoallv/symm", in, out, sv, none, none, false, in_splits, row, async_op, o);
+    }
+  }
   LaunchShape shape;
   shape.threads = tune_.threads;
   shape.blocks = std::min(32, tune_.max_blocks);
@@ -1327,8 +1678,9 @@ WorkPtr CudaBackend::device_alltoallv_single(at::Tensor& out, const at::Tensor& 
     const void* ip = i.data_ptr();
     void* op_ = ot.data_ptr();
     const long long* counts = reinterpret_cast<const long long*>(sp.data_ptr<int64_t>());
-    B200C_CUDA_CHECK(launch_all_to_all_device_splits(&dev_, layout_, 0, &ip, &op_, &counts, row, shape, s));
-  });
+    const size_t in_cap = i.nbytes(), out_cap = ot.nbytes();
+    B200C_CUDA_CHECK(launch_all_to_all_device_splits(&dev_, layout_, 0, &ip, &op_, &counts, row, shape, s, &in_cap, &out_cap));
+  }, kChanMain, true);
 }
 
 WorkPtr CudaBackend::reduce_scatter_quantized(at::Tensor& out, const at::Tensor& in, const ReduceOp& op, int64_t seed,
@@ -1532,13 +1884,119 @@ std::unordered_map<std::string, std::string> CudaBackend::comm_dump() const {
   d["bytes_issued"] = std::to_string(bytes_issued_.load());
   d["failed"] = failed_.load() ? failure_text_ : "";
   {
+    std::lock_guard<std::mutex> g(symm_mu_);
+    d["symm_regions"] = std::to_string(symm_regs_.size());
+  }
+  {
     std::lock_guard<std::mutex> g(const_cast<std::mutex&>(wd_mu_));
     d["inflight"] = std::to_string(inflight_.size());
+    d["graph_entries"] = std::to_string(graph_entries_.size());
+    d["graphs"] = std::to_string(graphs_.size());
     for (auto& kv : algo_counts_) {
       d["count/" + kv.first] = std::to_string(kv.second);
     }
   }
   return d;
+}
+
+// ------------------------------------------------------ symmetric tensors ----
+
+at::Tensor CudaBackend::symm_empty(const std::vector<int64_t>& sizes, at::ScalarType dtype) {
+  check_usable();
+  c10::cuda::CUDAGuard guard(device_);
+  int64_t numel = 1;
+  for (int64_t d : sizes) {
+    TORCH_CHECK(d >= 0, "symm_empty: negative dimension");
+    numel *= d;
+  }
+  const size_t bytes = static_cast<size_t>(numel) * c10::elementSize(dtype);
+  auto seg = symm_->allocate(std::max<size_t>(bytes, 16), tune_.use_multicast);
+  {
+    std::lock_guard<std::mutex> g(symm_mu_);
+    symm_regs_[reinterpret_cast<uintptr_t>(seg->local())] = SymmReg{seg->bytes, seg, false};
+  }
+  // The segment, not the tensor, owns the memory (unmapping is a collective matter).
+  return at::from_blob(seg->local(), sizes, [](void*) {}, at::TensorOptions().dtype(dtype).device(device_));
+}
+
+void CudaBackend::symm_free(const at::Tensor& t) {
+  check_usable();
+  c10::cuda::CUDAGuard guard(device_);
+  std::shared_ptr<SymmSegment> seg;
+  {
+    std::lock_guard<std::mutex> g(symm_mu_);
+    auto it = symm_regs_.find(reinterpret_cast<uintptr_t>(t.data_ptr()));
+    TORCH_CHECK(it != symm_regs_.end() && !it->second.user_memory, "symm_free: not a tensor made by symm_empty()");
+    seg = it->second.seg;
+    symm_regs_.erase(it);
+  }
+  // Nobody may still be reading or writing this rank's copy.
+  sync_own_streams();
+  if (size_ > 1) {
+    store_barrier(*store_, "symm_free/" + std::to_string(symm_free_seq_++), rank_, size_, opts_.timeout);
+  }
+  symm_->release(seg);
+}
+
+void CudaBackend::tensor_register(const at::Tensor& t) {
+  check_usable();
+  check_tensor(t, device_, "tensor_register");
+  c10::cuda::CUDAGuard guard(device_);
+  // Memory from the communicator's allocator is registered as the whole
+  // allocation (every tensor inside it is then covered, and it can be bound to
+  // the multicast object); anything else as the tensor's own range over CUDA IPC.
+  void* base = t.data_ptr();
+  size_t bytes = t.nbytes();
+  ExportableAlloc a;
+  if (ExportableRegistry::get().find(base, bytes, &a)) {
+    base = reinterpret_cast<void*>(a.base);
+    bytes = a.bytes;
+  }
+  {
+    std::lock_guard<std::mutex> g(symm_mu_);
+    if (symm_regs_.count(reinterpret_cast<uintptr_t>(base)) != 0) return;  // same decision on every rank
+  }
+  auto seg = symm_->attach_user_buffer(base, bytes, tune_.use_multicast);
+  std::lock_guard<std::mutex> g(symm_mu_);
+  symm_regs_[reinterpret_cast<uintptr_t>(base)] = SymmReg{bytes, seg, true};
+}
+
+void CudaBackend::tensor_deregister(const at::Tensor& t) {
+  check_usable();
+  c10::cuda::CUDAGuard guard(device_);
+  std::shared_ptr<SymmSegment> seg;
+  {
+    std::lock_guard<std::mutex> g(symm_mu_);
+    const uintptr_t p = reinterpret_cast<uintptr_t>(t.data_ptr());
+    auto it = symm_regs_.upper_bound(p);
+    TORCH_CHECK(it != symm_regs_.begin(), "tensor_deregister: tensor is not registered");
+    --it;
+    TORCH_CHECK(p < it->first + it->second.bytes && it->second.user_memory, "tensor_deregister: tensor is not registered");
+    seg = it->second.seg;
+    symm_regs_.erase(it);
+  }
+  sync_own_streams();
+  if (size_ > 1) {
+    store_barrier(*store_, "symm_free/" + std::to_string(symm_free_seq_++), rank_, size_, opts_.timeout);
+  }
+  symm_->release(seg);
+}
+
+bool CudaBackend::lookup_symm(const void* p, size_t bytes, SymmView* view) const {
+  std::lock_guard<std::mutex> g(symm_mu_);
+  if (symm_regs_.empty()) return false;
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  auto it = symm_regs_.upper_bound(a);
+  if (it == symm_regs_.begin()) return false;
+  --it;
+  if (a + bytes > it->first + it->second.bytes) return false;
+  const size_t off = a - it->first;
+  const SymmSegment& seg = *it->second.seg;
+  for (int r = 0; r < kMaxRanks; ++r) {
+    view->ptr[r] = r < size_ ? seg.peer_ptrs[r] + off : nullptr;
+  }
+  view->mc = seg.mc_ptr != nullptr ? seg.mc_ptr + off : nullptr;
+  return true;
 }
 
 std::shared_ptr<Window> CudaBackend::new_window(const std::optional<at::Tensor>& tensor) {
@@ -1571,6 +2029,11 @@ void CudaWindow::tensor_register(const at::Tensor& t, bool owning) {
   cache_meta(t);
   data_seg_ = owner_->symm().attach_user_buffer(t.data_ptr(), t.nbytes());
   registered_ = true;
+  // Registration is the collective moment: the signal / barrier segment and the
+  // device-side descriptor are made here, with the default counts, so that the
+  // one-sided calls (put, signal, wait_signal) never have to allocate - a rank
+  // that takes no part in an exchange is not needed for it.
+  build_device_window(-1, -1, 1);
 }
 
 void CudaWindow::tensor_deregister() {
@@ -1603,6 +2066,7 @@ void CudaWindow::tensor_deregister() {
   local_buffers_.clear();
   tensor_.reset();
   registered_ = false;
+  custom_counts_ = false;
   owner_->barrier(false, {})->wait_blocking();
 }
 
@@ -1652,10 +2116,33 @@ void CudaWindow::build_device_window(int signal_count, int counter_count, int ba
   B200C_CUDA_CHECK(cudaMemcpy(dev_window_, &w, sizeof(DeviceWindow), cudaMemcpyHostToDevice));
 }
 
+// With the default counts this returns the descriptor made at registration
+// and is not collective. Asking for other counts rebuilds the control segment:
+// that IS collective (every rank must make the same call), and is only
+// possible while nothing is in flight on the window.
 uintptr_t CudaWindow::get_device_window(int signal_count, int counter_count, int barrier_count) {
-  if (dev_window_ == nullptr) {
-    build_device_window(signal_count, counter_count, barrier_count);
+  TORCH_CHECK(registered_ && dev_window_ != nullptr, "window: register a tensor first");
+  const int n = owner_->size();
+  const int want_sig = (signal_count < 0 ? n : signal_count) + 1;
+  const int want_cnt = counter_count < 0 ? n : counter_count;
+  const int want_bar = barrier_count < 1 ? 1 : barrier_count;
+  if (want_sig == host_copy_.signal_count && want_cnt == host_copy_.counter_count && want_bar == host_copy_.barrier_count) {
+    return reinterpret_cast<uintptr_t>(dev_window_);
   }
+  TORCH_CHECK(!custom_counts_, "window: the device window was already built with signal_count=",
+              host_copy_.signal_count - 1, ", counter_count=", host_copy_.counter_count, ", barrier_count=",
+              host_copy_.barrier_count, "; different counts need a new registration");
+  c10::cuda::CUDAGuard guard(owner_->device());
+  owner_->barrier(false, {})->wait_blocking();
+  cudaDeviceSynchronize();
+  cudaFree(dev_window_);
+  cudaFree(local_state_);
+  dev_window_ = nullptr;
+  local_state_ = nullptr;
+  owner_->symm().release(ctrl_seg_);
+  ctrl_seg_.reset();
+  build_device_window(signal_count, counter_count, barrier_count);
+  custom_counts_ = true;
   return reinterpret_cast<uintptr_t>(dev_window_);
 }
 
@@ -1667,7 +2154,6 @@ WorkPtr CudaWindow::put(const at::Tensor& src, int dst_rank, int64_t target_offs
   const size_t esz = c10::elementSize(dtype_);
   TORCH_CHECK((static_cast<size_t>(target_offset_nelems) + src.numel()) * esz <= static_cast<size_t>(get_size()),
               "window.put: ", src.numel(), " elements at offset ", target_offset_nelems, " do not fit the window");
-  get_device_window(-1, -1, 1);
   at::Tensor s = src;
   const size_t off = static_cast<size_t>(target_offset_nelems) * esz;
   DeviceWindow* dw = dev_window_;
@@ -1679,7 +2165,6 @@ WorkPtr CudaWindow::put(const at::Tensor& src, int dst_rank, int64_t target_offs
 WorkPtr CudaWindow::signal(int dst_rank, bool async_op, const OpOptions& o) {
   TORCH_CHECK(registered_, "window.signal: no tensor is registered");
   TORCH_CHECK(dst_rank >= 0 && dst_rank < owner_->size(), "window.signal: bad rank ", dst_rank);
-  get_device_window(-1, -1, 1);
   DeviceWindow* dw = dev_window_;
   return owner_->run("window_signal/kernel", async_op, o, {}, [dw, dst_rank](cudaStream_t st) {
     B200C_CUDA_CHECK(launch_window_signal(dw, dst_rank, kHostSignalId, st));
@@ -1689,7 +2174,6 @@ WorkPtr CudaWindow::signal(int dst_rank, bool async_op, const OpOptions& o) {
 WorkPtr CudaWindow::wait_signal(int peer_rank, bool async_op, const OpOptions& o) {
   TORCH_CHECK(registered_, "window.wait_signal: no tensor is registered");
   TORCH_CHECK(peer_rank >= 0 && peer_rank < owner_->size(), "window.wait_signal: bad rank ", peer_rank);
-  get_device_window(-1, -1, 1);
   DeviceWindow* dw = dev_window_;
   uint64_t* expected = local_state_ + host_copy_.counter_count + host_copy_.barrier_count;
   return owner_->run("window_wait/kernel", async_op, o, {}, [dw, peer_rank, expected](cudaStream_t st) {

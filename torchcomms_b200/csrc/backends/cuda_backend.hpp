@@ -8,8 +8,12 @@
 // stream; an asynchronous one on the communicator's internal stream after an
 // event dependency on the current stream. `work.wait()` never blocks the
 // host: it makes the current stream wait for the operation's end event.
-// Operations of one communicator are serialised among themselves even when
-// they sit on different streams (they share staging memory and flags).
+// Operations are grouped into channels. A channel owns flag sets and staging
+// that its kernels share, so operations of one channel are kept in issue order
+// even across streams; operations of different channels (for instance a
+// parameter all-gather and a gradient reduce-scatter on symmetric buffers) have
+// nothing in common, run on streams of their own when asynchronous, and may
+// overlap.
 //
 // A watchdog thread polls the end events (cudaEventQuery only), the device
 // status word written by bounded waits, and NCCL's asynchronous error state.
@@ -26,6 +30,7 @@
 #include <atomic>
 #include <condition_variable>
 #include <deque>
+#include <map>
 #include <thread>
 
 #include "../core/comm.hpp"
@@ -42,8 +47,12 @@ class CudaBackend;
 // Asynchronous handle of a stream-ordered operation.
 class CudaWork final : public Work {
  public:
+  // `start` / `end` may be null for a synchronous operation of the library's
+  // own kernels that nobody observes: stream order already gives wait() its
+  // meaning, and `stream` is what wait_blocking() synchronises with.
   CudaWork(std::shared_ptr<CudaApi> api, cudaEvent_t start, cudaEvent_t end, bool pooled, int device,
-           Millis timeout, std::vector<at::Tensor> keep_alive, std::weak_ptr<CudaBackend> owner, bool in_capture);
+           Millis timeout, std::vector<at::Tensor> keep_alive, std::weak_ptr<CudaBackend> owner, bool in_capture,
+           cudaStream_t stream = nullptr);
   ~CudaWork() override;
 
   // Called by the watchdog: advances NOT_STARTED -> INPROGRESS -> COMPLETED /
@@ -66,6 +75,7 @@ class CudaWork final : public Work {
   std::vector<at::Tensor> keep_alive_;
   std::weak_ptr<CudaBackend> owner_;
   bool in_capture_;
+  cudaStream_t stream_ = nullptr;
   std::mutex poll_mu_;
   bool started_seen_ = false;
   std::chrono::steady_clock::time_point started_at_{};
@@ -76,6 +86,10 @@ enum class Algo : int { AUTO = 0, ONESHOT = 1, TWOSHOT = 2, STAGED = 3, NCCL = 4
 
 // Collective families that have both a peer-memory kernel and an NCCL route.
 enum class Coll : int { ALL_REDUCE, ALL_GATHER, REDUCE_SCATTER, ALL_TO_ALL };
+
+// Operations that share flags and staging. kChanMain: the staged kernels, NCCL
+// and everything else; the others: one-pass kernels on symmetric buffers.
+enum Chan : int { kChanMain = 0, kChanSymAg = 1, kChanSymRs = 2, kChanSymAr = 3, kChanCount = 4 };
 
 struct Tuning {
   size_t staging_bytes = 128ull << 20;     // bulk staging per rank
@@ -90,6 +104,21 @@ struct Tuning {
   int steps_per_block = 8;                 // large payloads: steps each block should run
   size_t min_chunk_bytes = 64 * 1024;
   bool auto_nccl = false;                  // opt-in: algo=auto may pick NCCL where it measured faster
+  int symm_blocks = 32;                    // grid of the one-pass kernels on symmetric buffers (same on every rank)
+  int symm_blocks_nomc = 64;               // same, when the data path is plain peer loads / stores
+  // Data path of the one-pass kernels: 1 = through the switch's multicast
+  // object (multimem.st / multimem.ld_reduce), 0 = plain peer stores / loads,
+  // -1 = by rank count. Multicast needs 1/nranks of the store or load
+  // instructions, but the switch also delivers a rank's own copy back to it:
+  // nranks/(nranks-1) times the bytes of the peer path for all-gather and
+  // reduce-scatter, while for all-reduce it moves (1 + 1/nranks) S against
+  // 2 (nranks-1)/nranks S and wins from 4 ranks on.
+  int symm_ag_mc = -1;
+  int symm_rs_mc = -1;
+  int symm_ar_mc = -1;
+  size_t lamport_max_bytes = 64 * 1024;    // all-reduce: flag-less kernel up to here (0 = off)
+  bool channel_streams = true;             // asynchronous operations of different channels get streams of their own
+  bool fast_sync = true;                   // unobserved synchronous kernel operations skip the event pair
   bool use_multicast = true;
   bool use_nccl = true;                    // create the NCCL communicator at init
   Algo force = Algo::AUTO;                 // B200COMMS_ALGO / hint "algo"
@@ -147,6 +176,23 @@ class CudaBackend final : public Backend {
   bool is_aborted() const override { return aborted_.load(); }
   bool is_abort_supported() const override { return true; }
 
+  // Symmetric tensors: memory every rank has mapped (and, where the box
+  // allows, bound to an NVLS multicast object). Collectives whose tensors live
+  // there run as one-pass kernels without staging. Both calls are collective:
+  // every rank calls them in the same order with the same sizes. The memory
+  // stays mapped until symm_free() or finalize(); a tensor must not be used
+  // after that.
+  at::Tensor symm_empty(const std::vector<int64_t>& sizes, at::ScalarType dtype);
+  void symm_free(const at::Tensor& t);
+  // Collective: makes the allocation behind `t` (memory from this
+  // communicator's allocator, see mem_allocator) reachable by every rank, so
+  // that collectives on tensors inside it take the one-pass kernels.
+  void tensor_register(const at::Tensor& t) override;
+  void tensor_deregister(const at::Tensor& t) override;
+  // Peer views of [p, p + bytes) if it lies inside a symmetric tensor or a
+  // registered allocation.
+  bool lookup_symm(const void* p, size_t bytes, SymmView* view) const;
+
   // Backend-specific operations (reached through get_backend_impl()).
   // Split sizes live on the device (int64 counts of dim-0 slices).
   WorkPtr device_alltoallv_single(at::Tensor& out, const at::Tensor& in, const at::Tensor& out_splits,
@@ -170,6 +216,9 @@ class CudaBackend final : public Backend {
                         const std::vector<std::pair<size_t, size_t>>& send,
                         const std::vector<std::pair<size_t, size_t>>& recv, bool async_op, const OpOptions& o);
   LaunchShape shape_for(size_t bytes, size_t slot_multiplier, int block_cap = 0) const;
+  // Multicast or peer path for one call of a one-pass kernel (`knob`: the Tuning field of its kind).
+  bool symm_use_mc(int knob, bool mc_by_default, const SymmView& v, const OpOptions& o) const;
+  int symm_blocks_for(bool mc, size_t vectors, const OpOptions& o) const;
   // Resolves algo=auto for one call: own kernels (AUTO) or NCCL, from measured cross-over sizes.
   Algo route(Coll c, size_t bytes, const OpOptions& o) const;
   std::shared_ptr<Backend> create_pair_comm(int peer, const std::string& name) override;
@@ -180,17 +229,23 @@ class CudaBackend final : public Backend {
   bool symm_alive() const { return symm_ != nullptr && !finalized_; }
   std::shared_ptr<CudaApi> cuda_api() const { return cuda_; }
   cudaStream_t internal_stream() const { return internal_stream_; }
+  cudaStream_t channel_stream(int chan) const { return chans_[chan].stream; }
 
   // Runs `launch(stream)` with the backend's stream / event / watchdog
   // protocol and returns the work. `keep_alive` tensors are held until wait()
-  // for asynchronous operations.
+  // for asynchronous operations. `chan` names the channel whose order the
+  // operation joins; `own_kernel` says that everything launched is one of the
+  // library's kernels with bounded waits (failures then show in the status
+  // word, and an unobserved synchronous call needs no events).
   WorkPtr run(const char* what, bool async_op, const OpOptions& o, std::vector<at::Tensor> keep_alive,
-              const std::function<void(cudaStream_t)>& launch);
+              const std::function<void(cudaStream_t)>& launch, int chan = kChanMain, bool own_kernel = false);
 
   // Test seams.
   void set_cuda_api(std::shared_ptr<CudaApi> api) { cuda_ = std::move(api); }
   void set_nccl_api(std::shared_ptr<NcclApi> api) { nccl_ = std::move(api); }
 
+  // Called from the CUDA user-object callback of a destroyed graph.
+  void note_graph_released(unsigned long long graph_id);
   // Called by works / watchdog on failures.
   void on_failure(const std::string& what, bool timed_out);
   // Returns a finished work's events to the pool.
@@ -230,11 +285,37 @@ class CudaBackend final : public Backend {
   uint32_t* epochs_dev_ = nullptr;
   uint32_t* status_host_ = nullptr;   // mapped pinned
   uint32_t* status_dev_ = nullptr;    // device alias of status_host_
-  cudaStream_t internal_stream_ = nullptr;
+  cudaStream_t internal_stream_ = nullptr;   // == chans_[kChanMain].stream
   cudaEvent_t dep_event_ = nullptr;
-  cudaStream_t last_stream_ = nullptr;
-  cudaEvent_t last_end_ = nullptr;
-  c10::intrusive_ptr<CudaWork> last_work_;
+  // Per channel: the stream asynchronous operations run on, and the latest
+  // operation (its end event, or just its stream when it recorded none) that
+  // the next operation of the channel must follow.
+  struct ChanState {
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    cudaStream_t last_stream = nullptr;
+    c10::intrusive_ptr<CudaWork> last_work;   // null when the last operation recorded no events
+    cudaEvent_t order_event = nullptr;        // recorded on last_stream when an event-less operation must be followed
+  };
+  ChanState chans_[kChanCount];
+  // Inside a stream capture: last captured operation per graph, so that
+  // captured operations stay chained across streams too.
+  struct CaptureTail {
+    cudaEvent_t end = nullptr;
+    cudaStream_t stream = nullptr;
+  };
+  std::unordered_map<unsigned long long, CaptureTail> capture_tail_;
+  void sync_own_streams();
+
+  // Symmetric tensors and registered allocations, keyed by local base address.
+  struct SymmReg {
+    size_t bytes = 0;
+    std::shared_ptr<SymmSegment> seg;
+    bool user_memory = false;   // registered allocation (not freed by symm_free)
+  };
+  mutable std::mutex symm_mu_;
+  std::map<uintptr_t, SymmReg> symm_regs_;
+  uint64_t symm_free_seq_ = 0;
 
   std::mutex pool_mu_;
   std::vector<cudaEvent_t> event_pool_;
@@ -250,6 +331,7 @@ class CudaBackend final : public Backend {
   struct GraphEntry {
     unsigned long long graph_id;
     size_t index;
+    size_t slot;                        // counter pair of the pinned pool
     unsigned long long* counters_host;  // [2]
     unsigned long long* counters_dev;
     unsigned long long seen_start = 0, seen_end = 0;
@@ -261,7 +343,23 @@ class CudaBackend final : public Backend {
   unsigned long long* replay_pool_host_ = nullptr;  // 2 x kMaxGraphEntries counters, mapped pinned
   unsigned long long* replay_pool_dev_ = nullptr;
   std::vector<GraphEntry> graph_entries_;
-  std::unordered_map<unsigned long long, size_t> graph_next_index_;
+  // Per captured graph: the events its operations recorded (destroyed with the
+  // bookkeeping), the next collective index, and whether the destroy callback
+  // rides on the graph. A CUDA user object retained by the graph calls back
+  // when the graph and all its executables are gone; the watchdog then drops
+  // the graph's entries and returns their counter slots.
+  // Parity: comms/torchcomms/ncclx/GraphEventTracker.cpp:99-121,237.
+  struct GraphState {
+    std::vector<cudaEvent_t> events;
+    size_t next_index = 0;
+    bool retained = false;
+  };
+  std::unordered_map<unsigned long long, GraphState> graphs_;
+  std::vector<size_t> free_slots_;
+  size_t next_slot_ = 0;
+  std::mutex released_mu_;
+  std::vector<unsigned long long> released_ids_;
+  void drop_released_graphs();   // watchdog thread, wd_mu_ held
 
   at::Tensor trace_;
   std::atomic<bool> aborted_{false};
@@ -302,6 +400,7 @@ class CudaWindow final : public Window {
   uint64_t* local_state_ = nullptr;         // counters, barrier epochs, wait expectations
   std::vector<std::pair<RegisteredBuffer*, at::Tensor>> local_buffers_;
   bool registered_ = false;
+  bool custom_counts_ = false;   // the device window was rebuilt with explicit counts
 };
 
 void register_cuda_backends();

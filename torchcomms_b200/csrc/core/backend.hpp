@@ -10,6 +10,7 @@
 // fault-tolerance entry points) and comms/torchcomms/TorchCommWindow.hpp:14-150.
 #pragma once
 
+#include <atomic>
 #include <unordered_map>
 
 #include <memory>
@@ -150,6 +151,13 @@ class B200C_API Backend : public std::enable_shared_from_this<Backend> {
   virtual void tensor_register(const at::Tensor& t) { (void)t; }
   virtual void tensor_deregister(const at::Tensor& t) { (void)t; }
 
+  // Called by the facade once somebody registers a pre- or post-hook: from
+  // then on every operation's work must report its start and end (recorders
+  // follow operations through work hooks), so backends may no longer hand out
+  // works that skip the bookkeeping.
+  void set_observed() { observed_.store(true, std::memory_order_relaxed); }
+  bool observed() const { return observed_.load(std::memory_order_relaxed); }
+
   // Observer tables owned by the facade and shared with the backend so the
   // watchdog can fire them.
   virtual void attach_hook_tables(std::shared_ptr<HookTable<AbortHook>> abort_hooks,
@@ -162,6 +170,7 @@ class B200C_API Backend : public std::enable_shared_from_this<Backend> {
   void run_abort_hooks() const;
   std::shared_ptr<HookTable<AbortHook>> abort_hooks_;
   std::shared_ptr<HookTable<GraphReplayHook>> replay_hooks_;
+  std::atomic<bool> observed_{false};
 };
 
 // Exported by out-of-tree backends that are loaded with dlopen: the symbol

@@ -98,8 +98,14 @@ class B200C_API Comm : public std::enable_shared_from_this<Comm> {
   void tensor_register(const at::Tensor& t) { impl_->tensor_register(t); }
   void tensor_deregister(const at::Tensor& t) { impl_->tensor_deregister(t); }
 
-  RemovableHandle register_pre_hook(PreHook h) { return pre_hooks_->add(std::move(h)); }
-  RemovableHandle register_post_hook(PostHook h) { return post_hooks_->add(std::move(h)); }
+  RemovableHandle register_pre_hook(PreHook h) {
+    impl_->set_observed();
+    return pre_hooks_->add(std::move(h));
+  }
+  RemovableHandle register_post_hook(PostHook h) {
+    impl_->set_observed();
+    return post_hooks_->add(std::move(h));
+  }
   RemovableHandle register_abort_hook(AbortHook h) { return abort_hooks_->add(std::move(h)); }
   RemovableHandle register_graph_replay_hook(GraphReplayHook h) { return replay_hooks_->add(std::move(h)); }
 

@@ -55,6 +55,48 @@ class CudaApi {
   virtual cudaError_t streamIsCapturing(cudaStream_t s, bool* capturing, unsigned long long* graph_id) = 0;
   virtual const char* errorString(cudaError_t e) = 0;
 
+  // Resources of the CUDA backend. These have working defaults (the runtime
+  // call itself), so a test fake overrides only what it wants to script.
+  virtual cudaError_t getDeviceCount(int* n) { return cudaGetDeviceCount(n); }
+  virtual cudaError_t setDevice(int d) { return cudaSetDevice(d); }
+  virtual cudaError_t deviceSynchronize() { return cudaDeviceSynchronize(); }
+  virtual cudaError_t streamPriorityRange(int* least, int* greatest) {
+    return cudaDeviceGetStreamPriorityRange(least, greatest);
+  }
+  virtual cudaError_t streamCreateWithPriority(cudaStream_t* s, unsigned flags, int priority) {
+    return cudaStreamCreateWithPriority(s, flags, priority);
+  }
+  virtual cudaError_t streamDestroy(cudaStream_t s) { return cudaStreamDestroy(s); }
+  virtual cudaError_t streamSynchronize(cudaStream_t s) { return cudaStreamSynchronize(s); }
+  virtual cudaError_t mallocDevice(void** p, size_t bytes) { return cudaMalloc(p, bytes); }
+  virtual cudaError_t freeDevice(void* p) { return cudaFree(p); }
+  virtual cudaError_t memsetDevice(void* p, int v, size_t bytes) { return cudaMemset(p, v, bytes); }
+  // Pinned host memory that the device can address (status word, replay counters).
+  virtual cudaError_t hostAllocMapped(void** host, void** dev, size_t bytes) {
+    cudaError_t e = cudaHostAlloc(host, bytes, cudaHostAllocMapped);
+    if (e != cudaSuccess) return e;
+    return cudaHostGetDevicePointer(dev, *host, 0);
+  }
+  virtual cudaError_t freeHost(void* p) { return cudaFreeHost(p); }
+  virtual cudaError_t exchangeCaptureMode(cudaStreamCaptureMode* mode) {
+    return cudaThreadExchangeStreamCaptureMode(mode);
+  }
+  // The graph a capturing stream is building (null when not capturing).
+  virtual cudaError_t streamCaptureGraph(cudaStream_t s, cudaGraph_t* graph) {
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    unsigned long long id = 0;
+    *graph = nullptr;
+    return cudaStreamGetCaptureInfo(s, &st, &id, graph, nullptr, nullptr);
+  }
+  // Ties `destroy(arg)` to the lifetime of `graph`: it runs (on a driver
+  // thread) once the graph and every executable made from it are gone.
+  virtual cudaError_t graphRetainCallback(cudaGraph_t graph, cudaHostFn_t destroy, void* arg) {
+    cudaUserObject_t obj = nullptr;
+    cudaError_t e = cudaUserObjectCreate(&obj, arg, destroy, 1, cudaUserObjectNoDestructorSync);
+    if (e != cudaSuccess) return e;
+    return cudaGraphRetainUserObject(graph, obj, 1, cudaGraphUserObjectMove);
+  }
+
   static std::shared_ptr<CudaApi> real();
 };
 

@@ -24,6 +24,10 @@ struct A2aOp {
     size_t known_max;
     const long long* dev_send_len;
     size_t elem_bytes;
+    // Capacities of `in` and `out` (0 = not checked). Lengths that do not fit
+    // are clamped and reported through the status word: split sizes that come
+    // from device memory are data, not arguments the host could have checked.
+    size_t in_bytes, out_bytes;
     size_t bulk_off;
     size_t meta_off;      // kMaxBlocks x kMaxRanks x kMaxRanks uint64 per rank
     size_t chunk_bytes;   // per-peer bytes staged per step; multiple of 16
@@ -61,24 +65,37 @@ struct A2aOp {
         static_cast<size_t>(blockIdx.x) * kMaxRanks * kMaxRanks;
     if (threadIdx.x < c.nranks) {
       const int p = threadIdx.x;
-      size_t len, soff;
-      if (a.dev_send_len != nullptr) {
-        size_t acc = 0;
-        for (int i = 0; i < p; ++i) acc += static_cast<size_t>(a.dev_send_len[i]);
-        soff = acc * a.elem_bytes;
-        len = static_cast<size_t>(a.dev_send_len[p]) * a.elem_bytes;
-      } else {
-        soff = a.send_off[p];
-        len = a.send_len[p];
-      }
-      pl.send_off[p] = soff;
-      pl.send_len[p] = len;
       // Row `rank` of peer p's table: what this rank sends to each destination.
       unsigned long long* meta_p = reinterpret_cast<unsigned long long*>(c.heap[p] + a.meta_off) +
           static_cast<size_t>(blockIdx.x) * kMaxRanks * kMaxRanks + static_cast<size_t>(c.rank) * kMaxRanks;
+      size_t acc = 0;
+      bool bad = false;
       for (int d = 0; d < c.nranks; ++d) {
-        meta_p[d] = a.dev_send_len != nullptr ? static_cast<size_t>(a.dev_send_len[d]) * a.elem_bytes : a.send_len[d];
+        size_t soff, len;
+        if (a.dev_send_len != nullptr) {
+          long long cnt = a.dev_send_len[d];
+          if (cnt < 0) {
+            bad = true;
+            cnt = 0;
+          }
+          soff = acc;
+          len = static_cast<size_t>(cnt) * a.elem_bytes;
+        } else {
+          soff = a.send_off[d];
+          len = a.send_len[d];
+        }
+        if (a.in_bytes != 0 && soff + len > a.in_bytes) {
+          bad = true;
+          len = soff < a.in_bytes ? a.in_bytes - soff : 0;
+        }
+        acc = soff + len;
+        meta_p[d] = len;
+        if (d == p) {
+          pl.send_off[p] = soff;
+          pl.send_len[p] = len;
+        }
       }
+      if (bad) c.status[0] = c.status[0] | kStatusBadArg;
     }
     block_barrier(c, kFlagSetMeta, ep, 0x51);
     if (threadIdx.x == 0) {
@@ -88,14 +105,20 @@ struct A2aOp {
           const size_t l = meta_mine[q * kMaxRanks + d];
           mx = l > mx ? l : mx;
         }
-        const size_t rl = meta_mine[q * kMaxRanks + c.rank];
-        pl.recv_len[q] = rl;
-        if (a.dev_send_len != nullptr) {
-          pl.recv_off[q] = roff;
-          roff += rl;
-        } else {
-          pl.recv_off[q] = a.recv_off[q];
+        size_t rl = meta_mine[q * kMaxRanks + c.rank];
+        const size_t at = a.dev_send_len != nullptr ? roff : a.recv_off[q];
+        if (a.out_bytes != 0) {
+          // What the sender announces must fit where the receiver puts it.
+          size_t cap = at < a.out_bytes ? a.out_bytes - at : 0;
+          if (a.dev_send_len == nullptr && a.recv_len[q] < cap) cap = a.recv_len[q];
+          if (rl > cap) {
+            c.status[0] = c.status[0] | kStatusBadArg;
+            rl = cap;
+          }
         }
+        pl.recv_len[q] = rl;
+        pl.recv_off[q] = at;
+        roff += rl;
       }
       pl.max_len = mx;
     }
@@ -229,7 +252,7 @@ cudaError_t launch_all_to_all(const CommDev* comms, const HeapLayout& lay, int e
 cudaError_t launch_all_to_all_device_splits(const CommDev* comms, const HeapLayout& lay, int emu_ranks,
                                             const void* const* in, void* const* out,
                                             const long long* const* dev_send_counts, size_t elem_bytes,
-                                            LaunchShape shape, cudaStream_t stream) {
+                                            LaunchShape shape, cudaStream_t stream, const size_t* in_bytes, const size_t* out_bytes) {
   using namespace coll;
   const int n = emu_ranks > 0 ? emu_ranks : 1;
   std::vector<A2aOp::Args> args(n);
@@ -240,6 +263,8 @@ cudaError_t launch_all_to_all_device_splits(const CommDev* comms, const HeapLayo
     a.out = static_cast<char*>(out[i]);
     a.dev_send_len = dev_send_counts[i];
     a.elem_bytes = elem_bytes;
+    a.in_bytes = in_bytes != nullptr ? in_bytes[i] : 0;
+    a.out_bytes = out_bytes != nullptr ? out_bytes[i] : 0;
   }
   return a2a_launch(comms, lay, emu_ranks, args, shape, stream);
 }

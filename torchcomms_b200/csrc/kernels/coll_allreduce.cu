@@ -144,6 +144,7 @@ struct ArPipe {
     bool ok = true;
     trace_mark(c, 0);
     for (long k = 0; k < n + 2; ++k) {
+      if (!ok) break;  // failed wait: stop staging, copying and posting
       if (k < n) {
         const size_t e0 = (blockIdx.x + static_cast<size_t>(k) * gridDim.x) * a.chunk_elems;
         const size_t cnt = min_sz(a.chunk_elems, a.count - e0);
@@ -164,12 +165,13 @@ struct ArPipe {
         const long j = k - 2;
         ok = wait_all_peers(c, kFlagSetDone, base_d + static_cast<uint32_t>(j) + 1, 0x22) && ok;
         if (k == 2) trace_mark(c, 4);
+        if (!ok) break;
         const size_t e0 = (blockIdx.x + static_cast<size_t>(j) * gridDim.x) * a.chunk_elems;
         const size_t cnt = min_sz(a.chunk_elems, a.count - e0);
         block_copy(a.out + e0, c.heap[c.rank] + slot0 + (j % S) * chunk_bytes, cnt * sizeof(T));
         if (k == 2) trace_mark(c, 5);
       }
-      post_flags(c, k < n, base_r + static_cast<uint32_t>(k) + 1, k >= 1 && k - 1 < n, base_d + static_cast<uint32_t>(k));
+      if (ok) post_flags(c, k < n, base_r + static_cast<uint32_t>(k) + 1, k >= 1 && k - 1 < n, base_d + static_cast<uint32_t>(k));
     }
     trace_mark(c, 6);
     __syncthreads();

@@ -39,11 +39,14 @@ struct Pipe2 {
     bool ok = true;
     trace_mark(c, 0);
     for (long k = 0; k < n + 1; ++k) {
+      // A failed wait (timeout, abort) ends the pipeline: nothing more is
+      // staged, copied or posted, so the kernel returns within one wait.
+      if (!ok) break;
       if (k < n) {
         if (k >= S) {
           ok = wait_all_peers(c, kFlagSetDone, base_d + static_cast<uint32_t>(k - S) + 1, 0x31) && ok;
         }
-        Op::stage(c, a, blockIdx.x + static_cast<size_t>(k) * gridDim.x, slot0 + (k % S) * slot_bytes);
+        if (ok) Op::stage(c, a, blockIdx.x + static_cast<size_t>(k) * gridDim.x, slot0 + (k % S) * slot_bytes);
       }
       if (k == 0) trace_mark(c, 1);
       if (k >= 1) {
@@ -55,9 +58,9 @@ struct Pipe2 {
         }
         if (k == 1) trace_mark(c, 3);
       }
-      post_flags(c, k < n, base_r + static_cast<uint32_t>(k) + 1, k >= 1, base_d + static_cast<uint32_t>(k));
+      if (ok) post_flags(c, k < n, base_r + static_cast<uint32_t>(k) + 1, k >= 1, base_d + static_cast<uint32_t>(k));
     }
-    if (n > 0) {
+    if (n > 0 && ok) {
       // Drain: nobody reads this block's slots any more once this returns.
       wait_all_peers(c, kFlagSetDone, base_d + static_cast<uint32_t>(n), 0x33);
     }

@@ -26,6 +26,20 @@ struct HeapLayout {
   size_t small_bytes = 0;
   size_t user_off = 0;     // windows / EP / TP scratch handed out by the backend
   size_t user_bytes = 0;
+  size_t symm_meta_off = 0;   // all-to-all on symmetric buffers: lengths, offsets and grants per (block, sender)
+  size_t symm_meta_bytes = 0;
+  size_t lamport_off = 0;     // flag-less small all-reduce: 3 rotating receive buffers
+  size_t lamport_bytes = 0;
+};
+
+constexpr size_t kSymmMetaBytes = static_cast<size_t>(kMaxBlocks) * kMaxRanks * 3 * sizeof(unsigned long long);
+
+// A buffer that every rank of the communicator has mapped: `ptr[r]` is rank
+// r's copy as seen from this process (ptr[own rank] is local memory), `mc` the
+// NVLS multicast alias of all copies or nullptr.
+struct SymmView {
+  char* ptr[kMaxRanks];
+  char* mc;
 };
 
 constexpr size_t kSmallPiece = 4 * 1024;   // bytes of payload one block stages in latency mode (one 16-byte vector per thread)
@@ -86,6 +100,49 @@ cudaError_t launch_all_gather(const CommDev* comms, const HeapLayout& lay, int e
                               const void* const* in, void* const* out, size_t bytes,
                               bool cast_f32_to_bf16, bool use_mc, LaunchShape shape, cudaStream_t stream);
 
+// ---- one-pass collectives on symmetric buffers (coll_symm.cu) ----------------
+// Nothing is staged: data moves once, between the users' tensors. `blocks` must
+// be the same on every rank. `in` / `out` / views hold one entry per emulated
+// rank (one entry when emu_ranks == 0).
+
+// out (symmetric) = concatenation over ranks of `in` (in_bytes per rank; with
+// the cast, fp32 in and bf16 out). The wire size per rank must be a multiple of 16.
+cudaError_t launch_symm_all_gather(const CommDev* comms, int emu_ranks, const void* const* in, const SymmView* out,
+                                   size_t in_bytes, bool cast_f32_to_bf16, bool use_mc, int blocks,
+                                   cudaStream_t stream);
+// out[count] = scale * sum over ranks of slice `rank` of the symmetric input
+// (nranks x count elements of wire_dtype). count % (16 / wire size) == 0.
+cudaError_t launch_symm_reduce_scatter(const CommDev* comms, int emu_ranks, const SymmView* in, void* const* out,
+                                       size_t count, DType wire_dtype, DType out_dtype, float scale, bool use_mc,
+                                       int blocks, cudaStream_t stream);
+// In-place sum (times scale) of a symmetric buffer. count % (16 / element size) == 0.
+cudaError_t launch_symm_all_reduce(const CommDev* comms, int emu_ranks, const SymmView* buf, size_t count, DType dtype,
+                                   float scale, bool use_mc, int blocks, cudaStream_t stream);
+// All-to-all(v) into a symmetric output. Offsets / lengths in bytes, nranks
+// entries per (emulated) rank; `in_bytes` / `out_bytes` are the buffers'
+// capacities, one entry per (emulated) rank. `exchange` = false: equal splits, every rank
+// already knows where its blocks land. With `dev_send_counts` the lengths are
+// int64 counts of `elem_bytes` in device memory and blocks are packed back to
+// back on both sides. Lengths that do not fit the buffers are clamped and
+// reported through the status word (kStatusBadArg).
+cudaError_t launch_symm_all_to_all(const CommDev* comms, const HeapLayout& lay, int emu_ranks, const void* const* in,
+                                   const SymmView* out, const size_t* in_bytes, const size_t* out_bytes, const size_t* send_off,
+                                   const size_t* send_len, const size_t* recv_off, const size_t* recv_len,
+                                   const long long* const* dev_send_counts, size_t elem_bytes, bool exchange,
+                                   int blocks, cudaStream_t stream);
+
+// ---- flag-less small all-reduce (coll_lamport.cu) -----------------------------
+constexpr int kLamportBlocks = 32;          // pieces per call
+constexpr size_t kLamportPiece = 4 * 1024;  // payload bytes per piece and rank (one 16-byte vector per thread)
+constexpr size_t kLamportBytes = 3ull * kLamportBlocks * kMaxRanks * kLamportPiece;
+constexpr unsigned kLamportPoison = 0x80000000u;  // -0.0f: "nothing arrived yet"
+// Fills the three receive buffers with the poison word (once, at set-up).
+cudaError_t launch_lamport_init(char* region, cudaStream_t stream);
+// out = scale * sum over ranks of in; count * element size <= kLamportBlocks * kLamportPiece.
+cudaError_t launch_all_reduce_lamport(const CommDev* comms, const HeapLayout& lay, int emu_ranks,
+                                      const void* const* in, void* const* out, size_t count, DType dtype,
+                                      float scale, bool use_mc, cudaStream_t stream);
+
 // All-to-all with per-peer byte counts. send_off/send_len/recv_off/recv_len
 // are arrays of nranks entries per rank (emu: emu_ranks x nranks, row-major).
 // recv_len[q] on rank r must equal send_len[r] on rank q. `max_len` is the
@@ -102,7 +159,11 @@ cudaError_t launch_all_to_all(const CommDev* comms, const HeapLayout& lay, int e
 cudaError_t launch_all_to_all_device_splits(const CommDev* comms, const HeapLayout& lay, int emu_ranks,
                                             const void* const* in, void* const* out,
                                             const long long* const* dev_send_counts, size_t elem_bytes,
-                                            LaunchShape shape, cudaStream_t stream);
+                                            LaunchShape shape, cudaStream_t stream,
+                                            const size_t* in_bytes = nullptr, const size_t* out_bytes = nullptr);
+// `in_bytes` / `out_bytes`: capacities of the buffers, one entry per (emulated) rank. Counts that are negative
+// or do not fit are clamped (nothing is read or written out of bounds) and
+// reported through the status word (kStatusBadArg).
 
 // Broadcast `bytes` bytes from `root`.
 cudaError_t launch_broadcast(const CommDev* comms, const HeapLayout& lay, int emu_ranks,

@@ -21,7 +21,7 @@ namespace b200c {
 
 constexpr int kMaxRanks = 8;        // one NVSwitch domain
 constexpr int kMaxBlocks = 640;     // flag rows per flag set (148 SMs x up to 4 resident blocks)
-constexpr int kFlagSets = 8;        // independent users of the flag region
+constexpr int kFlagSets = 16;       // independent users of the flag region
 constexpr int kFlagSetReady = 0;    // pipelined collectives: "chunk k is staged"
 constexpr int kFlagSetDone = 1;     // pipelined collectives: "chunk k is consumed"
 constexpr int kFlagSetSmall = 2;    // latency mode: one barrier per call, parity buffers
@@ -30,6 +30,14 @@ constexpr int kFlagSetMeta = 4;     // all-to-all count exchange
 constexpr int kFlagSetWindow = 5;   // one-sided window signals
 constexpr int kFlagSetEp = 6;       // MoE dispatch / combine
 constexpr int kFlagSetTp = 7;       // tensor-parallel fused GEMMs
+// One set per kind of one-pass collective on symmetric buffers, so that an
+// all-gather, a reduce-scatter and an all-reduce of one communicator may run
+// at the same time on different streams.
+constexpr int kFlagSetSymAg = 8;
+constexpr int kFlagSetSymRs = 9;
+constexpr int kFlagSetSymAr = 10;
+constexpr int kFlagSetSymA2a = 11;
+constexpr int kFlagSetLamport = 12; // flag-less small all-reduce: only the per-block call counter is used
 constexpr int kPipeSlots = 3;       // staging slots per block in the pipelined collectives
 
 // Bits of the status word a kernel may set (host-visible, mapped pinned memory).

@@ -429,7 +429,7 @@ std::shared_ptr<SymmSegment> SymmMemory::allocate(size_t bytes, bool want_multic
   return seg;
 }
 
-std::shared_ptr<SymmSegment> SymmMemory::attach_user_buffer(void* local, size_t bytes) {
+std::shared_ptr<SymmSegment> SymmMemory::attach_user_buffer(void* local, size_t bytes, bool want_multicast) {
   const uint64_t seq = seq_++;
   auto seg = std::make_shared<SymmSegment>();
   seg->rank = rank_;
@@ -468,6 +468,10 @@ std::shared_ptr<SymmSegment> SymmMemory::attach_user_buffer(void* local, size_t 
     seg->handles.assign(nranks_, 0);
     seg->peer_ptrs.assign(nranks_, nullptr);
     seg->peer_ptrs[rank_] = static_cast<char*>(local);
+    bool whole_everywhere = my_off == 0 && bytes == a.bytes && bytes % gran_ == 0;
+    for (int p = 0; p < nranks_; ++p) {
+      whole_everywhere = whole_everywhere && metas[p] == std::to_string(bytes) + ":0";
+    }
     CUmemAccessDesc acc{};
     acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
     acc.location.id = device_;
@@ -493,6 +497,13 @@ std::shared_ptr<SymmSegment> SymmMemory::attach_user_buffer(void* local, size_t 
       seg->peer_ptrs[p] = reinterpret_cast<char*>(va) + poff;
     }
     ::close(my_fd);
+    if (want_multicast && whole_everywhere && mc_ok_) {
+      // try_multicast() binds handles[rank]; release() never frees the own
+      // handle of memory it does not own.
+      seg->handles[rank_] = a.handle;
+      barrier("attachmc/" + std::to_string(seq));
+      try_multicast(*seg, seq);
+    }
   } else {
     seg->mode = SymmMode::CUDA_IPC;
     // cudaIpcGetMemHandle describes the whole allocation that contains `local`.

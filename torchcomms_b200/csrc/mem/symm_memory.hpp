@@ -80,7 +80,10 @@ class SymmMemory {
   // Collective: makes `local` (size `bytes`, owned by the caller) reachable
   // from every rank. Uses the exportable-allocation registry when the pointer
   // came from the symmetric allocator, CUDA IPC otherwise.
-  std::shared_ptr<SymmSegment> attach_user_buffer(void* local, size_t bytes);
+  // With `want_multicast`, memory from the symmetric allocator that every rank
+  // passes whole (same size, a multiple of the multicast granularity) is also
+  // bound to a multicast object.
+  std::shared_ptr<SymmSegment> attach_user_buffer(void* local, size_t bytes, bool want_multicast = false);
   // Local teardown; callers barrier first so that no peer still uses it.
   void release(const std::shared_ptr<SymmSegment>& seg);
 

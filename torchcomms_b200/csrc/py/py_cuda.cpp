@@ -30,7 +30,11 @@ class EmuWorld {
     lay_.small_off = lay_.bulk_bytes;
     const size_t meta = static_cast<size_t>(kMaxBlocks) * kMaxRanks * kMaxRanks * sizeof(uint64_t);
     lay_.small_bytes = (2 * static_cast<size_t>(kSmallBlocks) * kSmallPiece + meta + 4095) / 4096 * 4096;
-    flags_off_ = lay_.small_off + lay_.small_bytes;
+    lay_.symm_meta_off = lay_.small_off + lay_.small_bytes;
+    lay_.symm_meta_bytes = (kSymmMetaBytes + 4095) / 4096 * 4096;
+    lay_.lamport_off = lay_.symm_meta_off + lay_.symm_meta_bytes;
+    lay_.lamport_bytes = (kLamportBytes + 4095) / 4096 * 4096;
+    flags_off_ = lay_.lamport_off + lay_.lamport_bytes;
     const size_t flag_bytes = static_cast<size_t>(kFlagSets) * kMaxBlocks * kMaxRanks * sizeof(uint32_t);
     total_ = flags_off_ + (flag_bytes + 4095) / 4096 * 4096;
     heaps_.resize(n_);
@@ -38,6 +42,7 @@ class EmuWorld {
     for (int r = 0; r < n_; ++r) {
       B200C_CUDA_CHECK(cudaMalloc(&heaps_[r], total_));
       B200C_CUDA_CHECK(cudaMemset(heaps_[r], 0, total_));
+      B200C_CUDA_CHECK(launch_lamport_init(static_cast<char*>(heaps_[r]) + lay_.lamport_off, nullptr));
       B200C_CUDA_CHECK(cudaMalloc(&epochs_[r], kFlagSets * kMaxBlocks * sizeof(uint32_t)));
       B200C_CUDA_CHECK(cudaMemset(epochs_[r], 0, kFlagSets * kMaxBlocks * sizeof(uint32_t)));
     }
@@ -84,6 +89,11 @@ class EmuWorld {
   void check(const std::vector<at::Tensor>& v) const {
     TORCH_CHECK(static_cast<int>(v.size()) == n_, "need one tensor per virtual rank");
     for (auto& t : v) TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "tensors must be contiguous CUDA tensors");
+  }
+  static std::vector<size_t> nbytes_of(const std::vector<at::Tensor>& ts) {
+    std::vector<size_t> out;
+    for (auto& t : ts) out.push_back(t.nbytes());
+    return out;
   }
   LaunchShape shape(int blocks, size_t chunk) const {
     LaunchShape s;
@@ -210,7 +220,7 @@ class EmuWorld {
       cp[r] = reinterpret_cast<const long long*>(counts[r].data_ptr<int64_t>());
     }
     B200C_CUDA_CHECK(launch_all_to_all_device_splits(comms_.data(), lay_, n_, ip.data(), op.data(), cp.data(), elem_bytes,
-                                                     shape(blocks, chunk), stream()));
+                                                     shape(blocks, chunk), stream(), nbytes_of(ins).data(), nbytes_of(outs).data()));
   }
   void broadcast(std::vector<at::Tensor> bufs, int root, int blocks, size_t chunk) {
     check(bufs);
@@ -218,6 +228,81 @@ class EmuWorld {
     for (int r = 0; r < n_; ++r) bp[r] = bufs[r].data_ptr();
     B200C_CUDA_CHECK(launch_broadcast(comms_.data(), lay_, n_, bp.data(), bufs[0].nbytes(), root, false,
                                       shape(blocks, chunk), stream()));
+  }
+  // One-pass kernels on "symmetric" buffers: here simply every rank's tensor, all on this GPU.
+  std::vector<SymmView> views(const std::vector<at::Tensor>& ts) const {
+    SymmView v{};
+    for (int p = 0; p < n_; ++p) v.ptr[p] = static_cast<char*>(ts[p].data_ptr());
+    v.mc = nullptr;
+    return std::vector<SymmView>(n_, v);
+  }
+  void symm_all_gather(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, bool cast, int blocks) {
+    check(ins);
+    check(outs);
+    std::vector<const void*> ip(n_);
+    for (int r = 0; r < n_; ++r) ip[r] = ins[r].data_ptr();
+    auto v = views(outs);
+    B200C_CUDA_CHECK(launch_symm_all_gather(comms_.data(), n_, ip.data(), v.data(), ins[0].nbytes(), cast, false, blocks, stream()));
+  }
+  void symm_reduce_scatter(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, double scale, int blocks) {
+    check(ins);
+    check(outs);
+    std::vector<void*> op(n_);
+    for (int r = 0; r < n_; ++r) op[r] = outs[r].data_ptr();
+    auto v = views(ins);
+    B200C_CUDA_CHECK(launch_symm_reduce_scatter(comms_.data(), n_, v.data(), op.data(), outs[0].numel(), dtype_of(ins[0]),
+                                                dtype_of(outs[0]), static_cast<float>(scale), false, blocks, stream()));
+  }
+  void symm_all_reduce(std::vector<at::Tensor> bufs, double scale, int blocks) {
+    check(bufs);
+    auto v = views(bufs);
+    B200C_CUDA_CHECK(launch_symm_all_reduce(comms_.data(), n_, v.data(), bufs[0].numel(), dtype_of(bufs[0]),
+                                            static_cast<float>(scale), false, blocks, stream()));
+  }
+  // splits[r][p]: bytes rank r sends to rank p, blocks packed back to back on
+  // both sides. mode 0: equal splits known to all; 1: host splits, offsets
+  // exchanged in the kernel; 2: `counts` (int64 per rank, in units of
+  // elem_bytes) are read from device memory.
+  void symm_all_to_all(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, std::vector<std::vector<int64_t>> splits,
+                       int mode, std::vector<at::Tensor> counts, size_t elem_bytes, int blocks) {
+    check(ins);
+    check(outs);
+    std::vector<const void*> ip(n_);
+    std::vector<const long long*> cp(n_);
+    std::vector<size_t> so(n_ * n_, 0), sl(n_ * n_, 0), ro(n_ * n_, 0), rl(n_ * n_, 0);
+    for (int r = 0; r < n_; ++r) {
+      ip[r] = ins[r].data_ptr();
+      if (mode == 2) {
+        TORCH_CHECK(counts[r].scalar_type() == at::kLong && counts[r].numel() == n_, "counts: int64[nranks] per rank");
+        cp[r] = reinterpret_cast<const long long*>(counts[r].data_ptr<int64_t>());
+        continue;
+      }
+      size_t s = 0, d = 0;
+      for (int p = 0; p < n_; ++p) {
+        so[r * n_ + p] = s;
+        sl[r * n_ + p] = static_cast<size_t>(splits[r][p]);
+        s += sl[r * n_ + p];
+        ro[r * n_ + p] = d;
+        rl[r * n_ + p] = static_cast<size_t>(splits[p][r]);
+        d += rl[r * n_ + p];
+      }
+    }
+    auto v = views(outs);
+    B200C_CUDA_CHECK(launch_symm_all_to_all(comms_.data(), lay_, n_, ip.data(), v.data(), nbytes_of(ins).data(), nbytes_of(outs).data(),
+                                            so.data(), sl.data(), ro.data(), rl.data(), mode == 2 ? cp.data() : nullptr,
+                                            elem_bytes, mode != 0, blocks, stream()));
+  }
+  void all_reduce_lamport(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, double scale) {
+    check(ins);
+    check(outs);
+    std::vector<const void*> ip(n_);
+    std::vector<void*> op(n_);
+    for (int r = 0; r < n_; ++r) {
+      ip[r] = ins[r].data_ptr();
+      op[r] = outs[r].data_ptr();
+    }
+    B200C_CUDA_CHECK(launch_all_reduce_lamport(comms_.data(), lay_, n_, ip.data(), op.data(), ins[0].numel(), dtype_of(ins[0]),
+                                               static_cast<float>(scale), false, stream()));
   }
   void barrier() { B200C_CUDA_CHECK(launch_barrier(comms_.data(), n_, stream())); }
   // Runs the kernel whose wait can never be satisfied; returns the status words.
@@ -392,6 +477,23 @@ void bind_cuda_backend(py::module_& m) {
         return b.reduce_scatter_quantized(out, in, op, seed, a, make_op_options(h, to));
       }, py::arg("output"), py::arg("input"), py::arg("op"), py::arg("seed") = 0, py::arg("async_op") = false,
          py::arg("hints") = py::none(), py::arg("timeout") = py::none(), py::call_guard<py::gil_scoped_release>())
+      .def("symm_empty", [](CudaBackend& b, std::vector<int64_t> sizes, py::object dtype) {
+        const at::ScalarType st = torch::python::detail::py_object_to_dtype(dtype);
+        py::gil_scoped_release nogil;
+        return b.symm_empty(sizes, st);
+      }, py::arg("sizes"), py::arg("dtype"))
+      .def("symm_free", &CudaBackend::symm_free, py::arg("tensor"), py::call_guard<py::gil_scoped_release>())
+      .def("tensor_register", &CudaBackend::tensor_register, py::arg("tensor"), py::call_guard<py::gil_scoped_release>())
+      .def("tensor_deregister", &CudaBackend::tensor_deregister, py::arg("tensor"), py::call_guard<py::gil_scoped_release>())
+      .def("is_symmetric", [](CudaBackend& b, const at::Tensor& t) {
+        SymmView v;
+        return b.lookup_symm(t.data_ptr(), t.nbytes(), &v);
+      })
+      .def("has_multicast_alias", [](CudaBackend& b, const at::Tensor& t) {
+        SymmView v;
+        return b.lookup_symm(t.data_ptr(), t.nbytes(), &v) && v.mc != nullptr;
+      })
+      .def("channel_stream", [](CudaBackend& b, int chan) { return reinterpret_cast<uintptr_t>(b.channel_stream(chan)); })
       .def("comm_dump", &CudaBackend::comm_dump)
       .def("set_config", &CudaBackend::set_config)
       .def("get_nccl_comm_ptr", &CudaBackend::get_nccl_comm_ptr)
@@ -414,6 +516,11 @@ void bind_cuda_backend(py::module_& m) {
       .def("all_gather", &EmuWorld::all_gather)
       .def("all_to_all", &EmuWorld::all_to_all)
       .def("all_to_all_device_splits", &EmuWorld::all_to_all_device_splits)
+      .def("symm_all_gather", &EmuWorld::symm_all_gather)
+      .def("symm_reduce_scatter", &EmuWorld::symm_reduce_scatter)
+      .def("symm_all_reduce", &EmuWorld::symm_all_reduce)
+      .def("symm_all_to_all", &EmuWorld::symm_all_to_all)
+      .def("all_reduce_lamport", &EmuWorld::all_reduce_lamport)
       .def("broadcast", &EmuWorld::broadcast)
       .def("barrier", &EmuWorld::barrier)
       .def("wait_unset_flag", &EmuWorld::wait_unset_flag)

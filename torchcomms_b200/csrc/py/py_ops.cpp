@@ -34,6 +34,24 @@ cudaStream_t cur(const at::Tensor& t) {
 void bind_ops(py::module_& m) {
   auto ops = m.def_submodule("ops", "fused sm_100a model kernels");
 
+  // Points the storage behind `t` (and so every view of it, including tensors
+  // autograd saved) at the memory of `src`, or at nothing. The storage keeps
+  // `src` alive. This is how a stage's flat parameter buffer moves between
+  // rotating communication buffers without its parameter views being rebuilt.
+  ops.def("rebind_storage_", [](at::Tensor t, std::optional<at::Tensor> src) {
+    c10::StorageImpl* impl = t.storage().unsafeGetStorageImpl();
+    if (!src.has_value()) {
+      impl->set_data_ptr_noswap(at::DataPtr(nullptr, t.device()));
+      impl->set_nbytes(0);
+      return;
+    }
+    TORCH_CHECK(src->is_contiguous() && src->device() == t.device(), "rebind_storage_: contiguous source on the same device");
+    auto* keep = new at::Tensor(*src);
+    impl->set_data_ptr_noswap(
+        at::DataPtr(src->data_ptr(), keep, [](void* ctx) { delete static_cast<at::Tensor*>(ctx); }, t.device()));
+    impl->set_nbytes(src->nbytes());
+  }, py::arg("tensor"), py::arg("source") = py::none());
+
   ops.def("rmsnorm_fwd", [](const at::Tensor& x, const at::Tensor& w, double eps) {
     want(x, at::kBFloat16, "x");
     want(w, at::kBFloat16, "w");

@@ -6,6 +6,14 @@
 POSIX-fd shareable handles, so a window can map them into every peer
 (zero-copy one-sided access and NVLS multicast binding).
 
+``symm_empty(comm, shape, dtype)`` goes one step further: a collective call
+that returns a tensor in memory every rank of ``comm`` has already mapped
+(bound to the NVLS multicast object where the box allows).  Collectives whose
+output (all-gather, all-to-all), input (reduce-scatter) or in-place buffer
+(all-reduce) is such a tensor run as one-pass kernels with no staging copies.
+Tensors made inside a ``MemPool`` of ``get_mem_allocator`` get the same
+treatment after ``comm.tensor_register(tensor)``.
+
 Parity: ``comm.mem_allocator`` / ``get_mem_allocator`` of the reference
 (``comms/torchcomms/ncclx/TorchCommNCCLX.cpp:2343-2382``, a
 CUDAPluggableAllocator over ncclMemAlloc / ncclMemFree).
@@ -42,3 +50,36 @@ def symmetric_empty(comm, shape, dtype):
         t = torch.empty(shape, dtype=dtype, device=comm.get_device())
     t._b200c_pool = pool  # the pool must outlive the tensor
     return t
+
+
+_CUDA_BACKENDS = ("b200", "nccl", "ncclx")
+
+
+def symm_empty(comm, shape, dtype):
+    """Collective: a tensor of ``shape`` in symmetric memory of ``comm``.
+
+    Every rank calls this in the same order with the same shape.  The memory
+    stays mapped until ``symm_free(comm, tensor)`` or ``comm.finalize()``;
+    the tensor must not be used afterwards.  Backends without peer memory
+    (gloo, fake) return an ordinary tensor.
+    """
+    import torch
+
+    if isinstance(shape, int):
+        shape = (shape,)
+    if comm.get_backend() in _CUDA_BACKENDS:
+        return comm.get_backend_impl().symm_empty([int(d) for d in shape], dtype)
+    return torch.empty(tuple(shape), dtype=dtype, device=comm.get_device())
+
+
+def symm_free(comm, tensor) -> None:
+    """Collective: unmaps a tensor made by ``symm_empty``."""
+    if comm.get_backend() in _CUDA_BACKENDS:
+        comm.get_backend_impl().symm_free(tensor)
+
+
+def is_symmetric(comm, tensor) -> bool:
+    """True when collectives of ``comm`` on ``tensor`` take the one-pass kernels."""
+    if comm.get_backend() in _CUDA_BACKENDS:
+        return bool(comm.get_backend_impl().is_symmetric(tensor))
+    return False

@@ -17,7 +17,7 @@ import torch
 from .. import TorchComm
 from ..models.llama import Block, Embedding, Head, LlamaConfig
 from ..ops import fused
-from .fsdp import ShardedUnit
+from .fsdp import BufferPool, ShardedUnit, StepTimeline
 
 
 class TrainEngine:
@@ -34,6 +34,7 @@ class TrainEngine:
         seed: int = 0,
         param_dtype: torch.dtype = torch.bfloat16,
         recompute_blocks: int = 0,
+        comm_mode: Optional[str] = None,
     ):
         self.cfg = cfg
         self.comm = comm
@@ -42,6 +43,11 @@ class TrainEngine:
         self.step_count = 0
         self.recompute_blocks = recompute_blocks
         self.units: List[ShardedUnit] = []
+        if comm_mode is None:
+            comm_mode = "symm" if comm.get_backend() in ("b200", "nccl", "ncclx") else "plain"
+        self.comm_mode = comm_mode
+        # One pool for all stages: stages of the same size share its rotating buffers.
+        self.pool = BufferPool(comm, symmetric=comm_mode == "symm")
         # Stages are created one at a time on the device and immediately
         # reduced to their shard, so the full fp32 model never exists.
         makers = [lambda: Embedding(cfg)] + [lambda: Block(cfg) for _ in range(cfg.n_layers)] + [lambda: Head(cfg)]
@@ -49,8 +55,27 @@ class TrainEngine:
             torch.manual_seed(seed * 100003 + i)
             with torch.device(self.device):
                 stage = make()
-            self.units.append(ShardedUnit(stage, comm, param_dtype))
+            self.units.append(ShardedUnit(stage, comm, param_dtype, comm_mode=comm_mode, pool=self.pool))
         self.cos_t, self.sin_t = fused.rope_tables(cfg.max_seq_len, cfg.head_dim, cfg.rope_theta, self.device)
+
+    def attach_timeline(self) -> StepTimeline:
+        """Starts recording comm / wait / optimizer spans of the following steps."""
+        tl = StepTimeline(self.comm, self.comm_mode)
+        for u in self.units:
+            u.timeline = tl
+        return tl
+
+    def detach_timeline(self) -> None:
+        for u in self.units:
+            u.timeline = None
+
+    def close(self) -> None:
+        """Gives the pool's symmetric buffers back (collective). The engine is unusable afterwards."""
+        for u in self.units:
+            u.release_params()
+        if self.pool.symmetric:
+            self.pool.free_all()
+        self.units = []
 
     @property
     def num_parameters(self) -> int:
