@@ -1,0 +1,321 @@
+"""The CUDA backend's host logic on a machine without a GPU.
+
+Fakes of the CUDA runtime, the CUDA driver and NCCL are installed
+(``_comms._install_fake_gpu``) before the communicator is created; the backend
+then bootstraps, routes, records events, tracks captured graphs and runs its
+watchdog exactly as on a GPU, except that kernels are noted in a log instead of
+launched.  Multi-rank cases run as separate CPU processes that share a store,
+with file descriptors of the fake memory handles travelling between them like
+the real ones.
+
+Covers what the reference's mock-driven suites cover
+(comms/torchcomms/ncclx/tests/unit/cpp: TorchCommNCCLXTest,
+TorchWorkNCCLXQueueTest, GraphEventTrackerTest, HintParsingTest).
+"""
+import os
+import time
+from datetime import timedelta
+
+import pytest
+import torch
+
+from tests.mp_util import free_port, run_ranks
+
+
+def _reset_health():
+    from torchcomms_b200 import _comms
+
+    _comms._health_reset()
+
+
+def _new_comm(name, world_hints=None, **kw):
+    import torchcomms_b200 as tc
+
+    hints = {"staging_mb": "1"}
+    hints.update(world_hints or {})
+    return tc.new_comm("b200", torch.device("cuda", 0), name=name, hints=hints,
+                       abort_process_on_timeout_or_error=False, **kw)
+
+
+@pytest.fixture()
+def single_rank_env(monkeypatch):
+    monkeypatch.setenv("RANK", "0")
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    monkeypatch.setenv("MASTER_ADDR", "127.0.0.1")
+    monkeypatch.setenv("MASTER_PORT", str(free_port()))
+    from torchcomms_b200 import _comms
+
+    fake = _comms._install_fake_gpu()
+    yield fake
+    _comms._uninstall_fake_gpu()
+
+
+def test_bootstrap_streams_and_dump(single_rank_env):
+    fake = single_rank_env
+    comm = _new_comm("fake1", is_high_priority_stream=True)
+    impl = comm.get_backend_impl()
+    d = impl.comm_dump()
+    assert d["rank"] == "0" and d["size"] == "1" and d["symm_mode"] == "local"
+    # one stream per channel, created with the high priority of the fake range (-5)
+    created = [l for l in fake.log() if l.startswith("stream_create")]
+    assert len(created) == 4 and all(l.endswith("priority -5") for l in created)
+    assert len({impl.channel_stream(c) for c in range(4)}) == 4
+    assert any(l.startswith("launch lamport_init") for l in fake.log())
+    comm.finalize()
+
+
+def test_sync_operation_takes_the_event_less_path_until_somebody_observes(single_rank_env):
+    fake = single_rank_env
+    import torchcomms_b200 as tc
+
+    comm = _new_comm("fake2")
+    t = torch.ones(1024)
+    fake.clear_log()
+    w = comm.all_reduce(t, tc.ReduceOp.SUM, False)
+    log = fake.log()
+    assert [l.split()[0] for l in log] == ["launch"], log  # no events, nothing but the kernel
+    assert log[0].split()[1].startswith("all_reduce/")
+    w.wait()
+    assert w.is_completed()
+    # a post-hook makes every operation report start and end through events
+    seen = []
+    handle = comm.register_post_hook(lambda op_id, args: seen.append(op_id))
+    fake.clear_log()
+    comm.all_reduce(t, tc.ReduceOp.SUM, False).wait()
+    kinds = [l.split()[0] for l in fake.log()]
+    assert kinds[:3] == ["record", "launch", "record"], kinds
+    assert seen
+    handle.remove()
+    comm.finalize()
+
+
+def test_async_operation_protocol_and_cross_stream_order(single_rank_env):
+    fake = single_rank_env
+    import torchcomms_b200 as tc
+
+    comm = _new_comm("fake3")
+    impl = comm.get_backend_impl()
+    main = f"s{impl.channel_stream(0)}"
+    t = torch.ones(300_000)  # beyond the one-shot size: the staged two-shot kernel of the main channel
+    fake.clear_log()
+    w = comm.all_reduce(t, tc.ReduceOp.SUM, True, hints={"algo": "twoshot"})
+    log = fake.log()
+    # dependency on the caller's stream, then start event, kernel, end event on the channel's stream
+    assert log[0].startswith("record") and log[0].endswith("s16")          # dep event on the current stream (0x10)
+    assert log[1] == f"wait {main} {log[0].split()[1]}"
+    assert log[2].startswith("record") and log[2].endswith(main)
+    assert log[3] == f"launch all_reduce/twoshot {main}"
+    assert log[4].startswith("record") and log[4].endswith(main)
+    end_event = log[4].split()[1]
+    # wait() is a stream dependency on the end event, not a host block
+    fake.clear_log()
+    w.wait()
+    assert fake.log() == [f"wait s16 {end_event}"]
+    # the next synchronous operation of the SAME channel on another stream follows that end event ...
+    w2 = comm.all_reduce(t, tc.ReduceOp.SUM, True, hints={"algo": "twoshot"})
+    end2 = [l for l in fake.log() if l.startswith("record")][-1].split()[1]
+    fake.clear_log()
+    comm.all_reduce(t, tc.ReduceOp.SUM, False, hints={"algo": "twoshot"})
+    assert fake.log()[0] == f"wait s16 {end2}"
+    w2.wait()
+    # ... while an operation of another channel does not wait for it
+    src = torch.ones(8)
+    out = torch.empty(8)
+    fake.clear_log()
+    comm.all_gather_single(out, src, False)  # single rank: cast kernel on the all-gather channel
+    assert not any(l.startswith("wait") for l in fake.log()), fake.log()
+    comm.finalize()
+
+
+def test_event_pool_is_reused(single_rank_env):
+    fake = single_rank_env
+    import torchcomms_b200 as tc
+
+    comm = _new_comm("fake4", {"garbage_collect_interval_ms": "10"})
+    t = torch.ones(64)
+    for _ in range(50):
+        comm.all_reduce(t, tc.ReduceOp.SUM, True).wait()
+        time.sleep(0.002)
+    time.sleep(0.1)
+    # 50 asynchronous operations, but the watchdog recycles finished works' events
+    assert fake.events_created() < 60
+    d = comm.get_backend_impl().comm_dump()
+    assert int(d["inflight"]) == 0
+    comm.finalize()
+    assert fake.live_events() == 0
+
+
+def test_captured_operations_are_chained_counted_and_released(single_rank_env):
+    fake = single_rank_env
+    import torchcomms_b200 as tc
+
+    comm = _new_comm("fake5", {"garbage_collect_interval_ms": "10"})
+    impl = comm.get_backend_impl()
+    t = torch.ones(1024)
+    fake.set_capturing(True, 7)
+    fake.clear_log()
+    comm.all_reduce(t, tc.ReduceOp.SUM, False)           # on the capturing stream
+    w = comm.all_reduce(t, tc.ReduceOp.SUM, True)        # forks to the channel's stream inside the capture
+    w.wait()
+    log = fake.log()
+    assert sum(l.startswith("graph_retain") for l in log) == 1  # one destroy callback per graph
+    records = [l for l in log if l.startswith("record")]
+    first_end = records[1].split()[1]
+    # the asynchronous operation follows the first one although it runs on another stream
+    assert any(l.startswith("wait") and l.endswith(first_end) for l in log), log
+    assert impl.comm_dump()["graph_entries"] == "2" and impl.comm_dump()["graphs"] == "1"
+    fake.set_capturing(False, 0)
+    # replay monitoring keeps the entries while the graph lives ...
+    time.sleep(0.1)
+    assert impl.comm_dump()["graph_entries"] == "2"
+    # ... and drops them, with their events, when the graph is destroyed
+    events_before = fake.live_events()
+    assert fake.destroy_graph(7) == 1
+    deadline = time.time() + 5
+    while impl.comm_dump()["graph_entries"] != "0" and time.time() < deadline:
+        time.sleep(0.02)
+    assert impl.comm_dump()["graph_entries"] == "0" and impl.comm_dump()["graphs"] == "0"
+    assert fake.live_events() == events_before - 4
+    comm.finalize()
+
+
+def test_watchdog_times_out_a_stuck_operation_and_runs_abort_hooks(single_rank_env):
+    fake = single_rank_env
+    import torchcomms_b200 as tc
+
+    comm = _new_comm("fake6", {"garbage_collect_interval_ms": "10"}, timeout=timedelta(milliseconds=150))
+    fired = []
+    comm.register_abort_hook(lambda: fired.append(True))
+    t = torch.ones(64)
+    fake.set_stuck(True)                      # end events never complete from here on
+    w = comm.all_reduce(t, tc.ReduceOp.SUM, True)
+    deadline = time.time() + 5
+    while tc.healthy() and time.time() < deadline:
+        time.sleep(0.02)
+    assert not tc.healthy()
+    assert fired
+    assert comm.is_aborted()
+    with pytest.raises(RuntimeError, match="unusable after a failure"):
+        comm.all_reduce(t, tc.ReduceOp.SUM, False)
+    fake.set_stuck(False)
+    fake.clear_log()
+    with pytest.raises(RuntimeError):
+        comm.finalize()                       # reports the failure ...
+    # ... after stopping the streams: the broken path synchronises before it unmaps anything
+    assert any(l.startswith("sync") for l in fake.log())
+    del w
+    _reset_health()
+
+
+def _nccl_error_body(rank, world):
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import _comms
+
+    fake = _comms._install_fake_gpu()
+    comm = _new_comm("fake7", {"garbage_collect_interval_ms": "10"})
+    assert comm.get_backend_impl().comm_dump()["nccl"] == "1"
+    fake.set_nccl_async_error(6)          # ncclRemoteError
+    deadline = time.time() + 5
+    while tc.healthy() and time.time() < deadline:
+        time.sleep(0.02)
+    assert not tc.healthy()
+    with pytest.raises(RuntimeError, match="NCCL asynchronous error"):
+        comm.all_reduce(torch.ones(4), tc.ReduceOp.SUM, False)
+    try:
+        comm.finalize()
+    except RuntimeError:
+        pass
+
+
+def test_nccl_async_error_fails_the_communicator():
+    run_ranks(_nccl_error_body, 2, timeout=120)
+
+
+def test_hints_become_nccl_config(single_rank_env):
+    from torchcomms_b200 import _comms
+
+    cfg = _comms._nccl_config_from_hints(
+        {"blocking": "0", "cga_cluster_size": "2", "minCTAs": "4", "max_ctas": "16", "netName": "IB", "splitShare": "1",
+         "trafficClass": "3", "CTAPolicy": "1", "nvlsCTAs": "8", "algo": "nccl"}, "job")
+    assert cfg == {"blocking": "0", "cgaClusterSize": "2", "minCTAs": "4", "maxCTAs": "16", "netName": "IB",
+                   "splitShare": "1", "trafficClass": "3", "CTAPolicy": "1", "nvlsCTAs": "8", "commName": "job"}
+    assert _comms._nccl_config_from_hints({"algo": "kernel"}, "job") == {}  # nothing for NCCL: plain ncclCommInitRank
+    assert _comms._nccl_config_from_hints({"commName": "mine", "blocking": "true"}, "job") == {"blocking": "1", "commName": "mine"}
+    with pytest.raises(RuntimeError, match="must be an integer"):
+        _comms._nccl_config_from_hints({"minCTAs": "many"}, "job")
+
+
+def _multi_rank_body(rank, world):
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import _comms
+
+    fake = _comms._install_fake_gpu()
+    comm = tc.new_comm("b200", torch.device("cuda", rank), name="fakeN", abort_process_on_timeout_or_error=False,
+                       hints={"staging_mb": "1", "minCTAs": "2", "max_ctas": "8", "auto_nccl": "1"})
+    impl = comm.get_backend_impl()
+    d = impl.comm_dump()
+    assert d["symm_mode"] == "vmm+fd" and d["multicast"] == "1" and d["nccl"] == "1"
+    # hints that name NCCL configuration fields reached ncclCommInitRankConfig
+    assert fake.nccl_config() == {"minCTAs": "2", "maxCTAs": "8", "commName": "fakeN"}
+    assert any(l.startswith("ncclCommInitRankConfig") for l in fake.nccl_log())
+
+    def counts():
+        return {k[6:]: int(v) for k, v in impl.comm_dump().items() if k.startswith("count/")}
+
+    # ---- routing table with mixed routing on (world of 4)
+    small = torch.ones(1024)                      # 4 KB
+    mid = torch.ones(64 * 1024)                   # 256 KB
+    big = torch.ones(2 * 1024 * 1024)             # 8 MB
+    huge = torch.ones(32 * 1024 * 1024)           # 128 MB
+    comm.all_reduce(small, tc.ReduceOp.SUM, False)
+    comm.all_reduce(mid, tc.ReduceOp.SUM, False)
+    comm.all_reduce(big, tc.ReduceOp.SUM, False)
+    comm.all_reduce(huge, tc.ReduceOp.SUM, False)
+    comm.all_reduce(torch.ones(8, dtype=torch.int64), tc.ReduceOp.SUM, False)     # dtype the kernels do not cover
+    c = counts()
+    assert c["all_reduce/lamport"] == 1           # latency class: flag-less kernel
+    assert c["all_reduce/oneshot"] == 1           # up to 512 KB
+    assert c["all_reduce/twoshot"] == 1           # 4 - 64 MB: NVLS two-shot
+    assert c["all_reduce/nccl"] == 2              # beyond, and integers
+    # symmetric tensors take the one-pass kernels whatever the size
+    sym = comm.symm_empty((4 * 1024 * 1024,), torch.float32)
+    comm.all_reduce(sym, tc.ReduceOp.SUM, False)
+    out = comm.symm_empty((world * 4096,), torch.bfloat16)
+    comm.all_gather_single(out, torch.ones(4096), False)                         # fused fp32 -> bf16
+    comm.reduce_scatter_single(torch.empty(4096), out, tc.ReduceOp.AVG, False)   # bf16 in, fp32 out
+    comm.all_to_all_single(out, torch.ones(world * 4096, dtype=torch.bfloat16), False)
+    c = counts()
+    assert c["all_reduce/symm"] == 1 and c["all_gather/symm+cast"] == 1
+    assert c["reduce_scatter/symm"] == 1 and c["all_to_all_single/symm"] == 1
+    # forcing NCCL by hint
+    comm.all_gather_single(torch.empty(world * 16), torch.ones(16), False, hints={"algo": "nccl"})
+    assert counts()["all_gather/nccl"] == 1
+    assert any(l.startswith("ncclAllGather sendcount=16") for l in fake.nccl_log())
+    # point to point rides on NCCL, grouped
+    batch = comm.batch_op_create()
+    batch.send(torch.ones(4), (rank + 1) % world)
+    batch.recv(torch.empty(4), (rank - 1) % world)
+    batch.issue(False)
+    tail = fake.nccl_log()[-4:]
+    assert tail[0] == "ncclGroupStart" and tail[3] == "ncclGroupEnd"
+    # asynchronous operations of different channels run on different streams
+    fake.clear_log()
+    w1 = comm.all_gather_single(out, torch.ones(4096), True)
+    w2 = comm.reduce_scatter_single(torch.empty(4096), out, tc.ReduceOp.SUM, True)
+    launches = [l for l in fake.log() if l.startswith("launch")]
+    assert launches[0].split()[2] != launches[1].split()[2]
+    w1.wait()
+    w2.wait()
+    # split: members bootstrap a communicator of their own
+    members = [r for r in range(world) if r % 2 == rank % 2]
+    sub = comm.split(members, "half")
+    assert sub.get_size() == len(members)
+    sub.finalize()
+    comm.symm_free(out)
+    comm.symm_free(sym)
+    comm.finalize()
+    assert "ncclCommDestroy" in fake.nccl_log()
+
+
+def test_four_fake_ranks_bootstrap_route_and_split():
+    run_ranks(_multi_rank_body, 4, timeout=180)

@@ -20,6 +20,18 @@ namespace b200c {
 
 namespace {
 
+// Makes `device` current for the calling thread while in scope; a no-op when
+// the runtime behind `api` is a test fake (no CUDA context exists then).
+class DeviceScope {
+ public:
+  DeviceScope(const std::shared_ptr<CudaApi>& api, int device) {
+    if (api->is_real()) guard_.emplace(static_cast<c10::DeviceIndex>(device));
+  }
+
+ private:
+  std::optional<c10::cuda::CUDAGuard> guard_;
+};
+
 size_t round_up(size_t v, size_t to) {
   return (v + to - 1) / to * to;
 }
@@ -56,10 +68,11 @@ bool to_nccl_dtype(at::ScalarType t, NcclDataType* out) {
   }
 }
 
-void check_tensor(const at::Tensor& t, const at::Device& dev, const char* what) {
+// `real` is false under a test fake of the runtime, where tensors live on the host.
+void check_tensor(const at::Tensor& t, const at::Device& dev, const char* what, bool real = true) {
   TORCH_CHECK(t.defined(), what, ": undefined tensor");
   TORCH_CHECK(t.is_contiguous(), "Tensor must be contiguous for ", what);
-  TORCH_CHECK(t.device() == dev, what, ": tensor is on ", t.device(), " but the communicator lives on ", dev);
+  TORCH_CHECK(!real || t.device() == dev, what, ": tensor is on ", t.device(), " but the communicator lives on ", dev);
 }
 
 Algo parse_algo(std::string s) {
@@ -148,8 +161,8 @@ bool CudaWork::poll(std::chrono::steady_clock::time_point now) {
 
 void CudaWork::do_wait() {
   // Stream-ordered: the caller's current stream waits for the end event.
-  c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
-  cudaStream_t cur = at::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(device_)).stream();
+  DeviceScope guard(api_, device_);
+  cudaStream_t cur = api_->currentStream(device_);
   if (end_ != nullptr) {
     const cudaError_t e = api_->streamWaitEvent(cur, end_);
     if (e != cudaSuccess) {
@@ -171,8 +184,8 @@ void CudaWork::do_wait_blocking() {
   if (end_ == nullptr) {
     // Event-less synchronous operation: everything up to now on its stream.
     if (stream_ != nullptr || device_ >= 0) {
-      c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device_));
-      const cudaError_t e = cudaStreamSynchronize(stream_);
+      DeviceScope guard(api_, device_);
+      const cudaError_t e = api_->streamSynchronize(stream_);
       if (e != cudaSuccess) {
         set_error(std::string("cudaStreamSynchronize: ") + api_->errorString(e));
         set_status(WorkStatus::ERROR);
@@ -212,9 +225,9 @@ void CudaWork::do_wait_blocking() {
 // ---------------------------------------------------------- CudaBackend ----
 
 CudaBackend::CudaBackend(std::string registered_as) : registered_as_(std::move(registered_as)) {
-  drv_ = DriverApi::real();
-  cuda_ = CudaApi::real();
-  nccl_ = NcclApi::real();
+  drv_ = DriverApi::current();
+  cuda_ = CudaApi::current();
+  nccl_ = NcclApi::current();
 }
 
 CudaBackend::~CudaBackend() {
@@ -266,6 +279,8 @@ void CudaBackend::parse_tuning(const Hints& h) {
   t.symm_ar_mc = hint_or<int>(h, "symm_ar_mc", env_to_value<int>("B200COMMS_SYMM_AR_MC", t.symm_ar_mc));
   t.symm_blocks = std::max(1, std::min(t.symm_blocks, 128));
   t.symm_blocks_nomc = std::max(1, std::min(t.symm_blocks_nomc, 128));
+  t.symm_blocks_ld = hint_or<int>(h, "symm_blocks_ld", env_to_value<int>("B200COMMS_SYMM_BLOCKS_LD", t.symm_blocks_ld));
+  t.symm_blocks_ld = std::max(1, std::min(t.symm_blocks_ld, 148));
   t.lamport_max_bytes = hint_or<size_t>(h, "lamport_max_bytes", env_to_value<size_t>("B200COMMS_LAMPORT_MAX_BYTES", t.lamport_max_bytes));
   t.lamport_max_bytes = std::min(t.lamport_max_bytes, static_cast<size_t>(kLamportBlocks) * kLamportPiece);
   t.channel_streams = hint_or<bool>(h, "channel_streams", env_to_value<bool>("B200COMMS_CHANNEL_STREAMS", t.channel_streams));
@@ -332,10 +347,10 @@ void CudaBackend::bootstrap(const c10::intrusive_ptr<c10d::Store>& store, int ra
   rank_ = rank;
   size_ = size;
   store_ = store;
-  c10::cuda::CUDAGuard guard(device_);
+  DeviceScope guard(cuda_, device_.index());
   B200C_CUDA_CHECK(cuda_->setDevice(device_.index()));
 
-  symm_ = std::make_unique<SymmMemory>(store_, rank_, size_, device_.index(), drv_, opts_.timeout, tune_.use_multicast);
+  symm_ = std::make_unique<SymmMemory>(store_, rank_, size_, device_.index(), drv_, opts_.timeout, tune_.use_multicast, cuda_);
   layout_.bulk_off = 0;
   layout_.bulk_bytes = round_up(tune_.staging_bytes, 4096);
   layout_.small_off = layout_.bulk_off + layout_.bulk_bytes;
@@ -389,7 +404,11 @@ void CudaBackend::bootstrap(const c10::intrusive_ptr<c10d::Store>& store, int ra
   internal_stream_ = chans_[kChanMain].stream;
   B200C_CUDA_CHECK(cuda_->eventCreate(&dep_event_, cudaEventDisableTiming));
   // The flag-less all-reduce starts from buffers full of its "nothing here yet" word.
-  B200C_CUDA_CHECK(launch_lamport_init(heap_->local() + layout_.lamport_off, internal_stream_));
+  if (cuda_->is_real()) {
+    B200C_CUDA_CHECK(launch_lamport_init(heap_->local() + layout_.lamport_off, internal_stream_));
+  } else {
+    cuda_->noteLaunch("lamport_init", internal_stream_);
+  }
   B200C_CUDA_CHECK(cuda_->deviceSynchronize());
   if (size_ > 1) {
     // Nobody sends before every rank's buffers are prepared.
@@ -426,7 +445,58 @@ void CudaBackend::init_nccl() {
     TORCH_CHECK(raw.size() == sizeof(id.internal), "malformed NCCL unique id in the store");
     std::memcpy(id.internal, raw.data(), sizeof(id.internal));
   }
-  nccl_check(nccl_->commInitRank(&nccl_comm_, size_, id, rank_), "ncclCommInitRank");
+  const NcclConfig cfg = nccl_config_from_hints(opts_.hints, name_);
+  nccl_check(nccl_->commInitRankConfig(&nccl_comm_, size_, id, rank_, cfg), "ncclCommInitRankConfig");
+}
+
+// Hints that name a field of ncclConfig_t go to NCCL when the communicator is
+// created (camelCase as in nccl.h, or snake_case). Parity:
+// comms/torchcomms/ncclx/TorchCommNCCLXBootstrap.cpp:218-321.
+NcclConfig CudaBackend::nccl_config_from_hints(const Hints& h, const std::string& comm_name) {
+  NcclConfig c;
+  auto num = [&h](std::initializer_list<const char*> keys, int* out) {
+    for (const char* k : keys) {
+      auto it = h.find(k);
+      if (it == h.end()) continue;
+      const std::string& v = it->second;
+      if (v == "true" || v == "True") {
+        *out = 1;
+      } else if (v == "false" || v == "False") {
+        *out = 0;
+      } else {
+        size_t used = 0;
+        int parsed = 0;
+        try {
+          parsed = std::stoi(v, &used);
+        } catch (const std::exception&) {
+          used = 0;
+        }
+        TORCH_CHECK(used == v.size() && !v.empty(), "hint '", k, "' must be an integer, got '", v, "'");
+        *out = parsed;
+      }
+    }
+  };
+  num({"blocking"}, &c.blocking);
+  num({"cgaClusterSize", "cga_cluster_size"}, &c.cgaClusterSize);
+  num({"minCTAs", "min_ctas"}, &c.minCTAs);
+  num({"maxCTAs", "max_ctas"}, &c.maxCTAs);
+  num({"splitShare", "split_share"}, &c.splitShare);
+  num({"trafficClass", "traffic_class"}, &c.trafficClass);
+  num({"collnetEnable", "collnet_enable"}, &c.collnetEnable);
+  num({"CTAPolicy", "cta_policy"}, &c.CTAPolicy);
+  num({"shrinkShare", "shrink_share"}, &c.shrinkShare);
+  num({"nvlsCTAs", "nvls_ctas"}, &c.nvlsCTAs);
+  num({"nChannelsPerNetPeer", "n_channels_per_net_peer"}, &c.nChannelsPerNetPeer);
+  num({"nvlinkCentricSched", "nvlink_centric_sched"}, &c.nvlinkCentricSched);
+  auto it = h.find("netName");
+  if (it != h.end()) c.netName = it->second;
+  it = h.find("commName");
+  if (it != h.end()) {
+    c.commName = it->second;
+  } else if (c.any()) {
+    c.commName = comm_name;  // NCCL's own logs then carry the communicator's name
+  }
+  return c;
 }
 
 void CudaBackend::check_usable() const {
@@ -525,8 +595,8 @@ void CudaBackend::note_graph_released(unsigned long long graph_id) {
 WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, std::vector<at::Tensor> keep_alive,
                          const std::function<void(cudaStream_t)>& launch, int chan, bool own_kernel) {
   check_usable();
-  c10::cuda::CUDAGuard guard(device_);
-  cudaStream_t current = at::cuda::getCurrentCUDAStream(device_.index()).stream();
+  DeviceScope guard(cuda_, device_.index());
+  cudaStream_t current = cuda_->currentStream(device_.index());
   ChanState& cs = chans_[chan];
   cudaStream_t stream = async_op ? cs.stream : current;
   bool capturing = false;
@@ -565,7 +635,11 @@ WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, st
     // Nobody follows this operation through work hooks, stream order gives
     // wait() its meaning, and a failed device wait shows in the status word
     // the watchdog reads: no events, nothing queued.
-    launch(stream);
+    if (cuda_->is_real()) {
+      launch(stream);
+    } else {
+      cuda_->noteLaunch(what, stream);
+    }
     cs.last_stream = stream;
     cs.last_work.reset();
     ops_issued_++;
@@ -639,12 +713,19 @@ WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, st
   }
 
   B200C_CUDA_CHECK(cuda_->eventRecord(ev_start, stream));
-  if (replay_counters != nullptr) {
-    B200C_CUDA_CHECK(launch_counter_increment(replay_counters, stream));
-  }
-  launch(stream);
-  if (replay_counters != nullptr) {
-    B200C_CUDA_CHECK(launch_counter_increment(replay_counters + 1, stream));
+  if (!cuda_->is_real()) {
+    // Under a test fake of the runtime nothing can be launched. Operations that
+    // only call NCCL ("<op>/nccl") still run, against the NCCL fake.
+    cuda_->noteLaunch(what, stream);
+    if (std::strstr(what, "/nccl") != nullptr) launch(stream);
+  } else {
+    if (replay_counters != nullptr) {
+      B200C_CUDA_CHECK(launch_counter_increment(replay_counters, stream));
+    }
+    launch(stream);
+    if (replay_counters != nullptr) {
+      B200C_CUDA_CHECK(launch_counter_increment(replay_counters + 1, stream));
+    }
   }
   B200C_CUDA_CHECK(cuda_->eventRecord(ev_end, stream));
   if (!async_op) {
@@ -679,7 +760,7 @@ void CudaBackend::sync_own_streams() {
       cuda_->streamSynchronize(chans_[ch].stream);
     }
   }
-  cuda_->streamSynchronize(at::cuda::getCurrentCUDAStream(device_.index()).stream());
+  cuda_->streamSynchronize(cuda_->currentStream(device_.index()));
 }
 
 void CudaBackend::start_watchdog() {
@@ -699,7 +780,7 @@ void CudaBackend::stop_watchdog() {
 }
 
 void CudaBackend::watchdog_loop() {
-  cudaSetDevice(device_.index());
+  cuda_->setDevice(device_.index());
   std::unique_lock<std::mutex> lk(wd_mu_);
   while (!wd_stop_) {
     wd_cv_.wait_for(lk, std::chrono::milliseconds(tune_.watchdog_interval_ms));
@@ -810,7 +891,7 @@ void CudaBackend::finalize() {
     finalized_ = true;  // a reconfigurable communicator that never got a membership
     return;
   }
-  c10::cuda::CUDAGuard guard(device_);
+  DeviceScope guard(cuda_, device_.index());
   const bool broken = failed_.load() || aborted_.load();
   drain_and_release(broken, "finalize");
   finalized_ = true;
@@ -929,7 +1010,7 @@ WorkPtr CudaBackend::reconfigure(const ReconfigureOptions& o) {
   if (o.timeout) {
     opts_.timeout = *o.timeout;
   }
-  c10::cuda::CUDAGuard guard(device_);
+  DeviceScope guard(cuda_, device_.index());
   auto scoped = scoped_store(opts_.store, "b200c/cuda/" + name_ + "/reconf/" + std::to_string(o.uuid));
   if (initialized_) {
     // Nothing of this rank is in flight any more; once every member of the NEW list says the same,
@@ -1020,9 +1101,9 @@ LaunchShape CudaBackend::shape_for(size_t bytes, size_t slot_multiplier, int blo
 // (hint "symm_blocks" for one call), fewer when the payload gives each block
 // less than a few iterations. Depends only on sizes, hints and on whether the
 // buffer has a multicast alias, so every rank computes the same number.
-int CudaBackend::symm_blocks_for(bool mc, size_t vectors, const OpOptions& o) const {
-  int cap = mc ? tune_.symm_blocks : tune_.symm_blocks_nomc;
-  cap = std::max(1, std::min(128, hint_or<int>(o.hints, "symm_blocks", cap)));
+int CudaBackend::symm_blocks_for(bool mc, size_t vectors, const OpOptions& o, bool peer_loads) const {
+  int cap = mc ? tune_.symm_blocks : peer_loads ? tune_.symm_blocks_ld : tune_.symm_blocks_nomc;
+  cap = std::max(1, std::min(148, hint_or<int>(o.hints, "symm_blocks", cap)));
   const size_t per_block = 512 * 4;  // threads x unroll
   const size_t want = (vectors + per_block - 1) / per_block;
   return static_cast<int>(std::max<size_t>(1, std::min<size_t>(cap, want)));
@@ -1050,7 +1131,7 @@ static float red_scale(const ReduceOp& op, int nranks) {
 }
 
 WorkPtr CudaBackend::all_reduce(at::Tensor& t, const ReduceOp& op, bool async_op, const OpOptions& o) {
-  check_tensor(t, device_, "all_reduce");
+  check_tensor(t, device_, "all_reduce", cuda_->is_real());
   const size_t bytes = t.nbytes();
   if (bytes == 0) return c10::make_intrusive<CompletedWork>();
   Algo algo = route(Coll::ALL_REDUCE, bytes, o);
@@ -1117,7 +1198,7 @@ WorkPtr CudaBackend::all_reduce(at::Tensor& t, const ReduceOp& op, bool async_op
         reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0) {
       // The tensor lives in symmetric memory: reduce it in place, one pass over NVLink.
       const bool smc = symm_use_mc(tune_.symm_ar_mc, size_ >= 4, sv, o);
-      const int blocks = symm_blocks_for(smc, t.numel() / pack / size_, o);
+      const int blocks = symm_blocks_for(smc, t.numel() / pack / size_, o, true);
       bytes_issued_ += bytes;
       return run("all_reduce/symm", async_op, o, {t}, [this, tt, sv, dt, scale, smc, blocks](cudaStream_t s) {
         B200C_CUDA_CHECK(launch_symm_all_reduce(&dev_, 0, &sv, tt.numel(), dt, scale, smc, blocks, s));
@@ -1144,7 +1225,7 @@ WorkPtr CudaBackend::all_reduce(at::Tensor& t, const ReduceOp& op, bool async_op
 }
 
 WorkPtr CudaBackend::reduce(const at::Tensor& t, int root, const ReduceOp& op, bool async_op, const OpOptions& o) {
-  check_tensor(t, device_, "reduce");
+  check_tensor(t, device_, "reduce", cuda_->is_real());
   if (t.numel() == 0) return c10::make_intrusive<CompletedWork>();
   NcclDataType ndt;
   if (nccl_comm_ != nullptr && algo_override(o) == Algo::NCCL && to_nccl_dtype(t.scalar_type(), &ndt) &&
@@ -1192,8 +1273,8 @@ static bool single_rank_kind(at::ScalarType t, int* kind) {
 }
 
 WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bool async_op, const OpOptions& o) {
-  check_tensor(out, device_, "all_gather_single");
-  check_tensor(in, device_, "all_gather_single");
+  check_tensor(out, device_, "all_gather_single", cuda_->is_real());
+  check_tensor(in, device_, "all_gather_single", cuda_->is_real());
   TORCH_CHECK(out.numel() == in.numel() * size_, "all_gather_single: output numel must be input numel * size");
   const bool cast = in.scalar_type() == at::kFloat && out.scalar_type() == at::kBFloat16;
   TORCH_CHECK(cast || in.scalar_type() == out.scalar_type(),
@@ -1261,9 +1342,9 @@ WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bo
 
 WorkPtr CudaBackend::all_gather(const std::vector<at::Tensor>& outs, const at::Tensor& in, bool async_op, const OpOptions& o) {
   TORCH_CHECK(static_cast<int>(outs.size()) == size_, "all_gather: need size() output tensors");
-  check_tensor(in, device_, "all_gather");
+  check_tensor(in, device_, "all_gather", cuda_->is_real());
   for (auto& t : outs) {
-    check_tensor(t, device_, "all_gather");
+    check_tensor(t, device_, "all_gather", cuda_->is_real());
     TORCH_CHECK(t.numel() == in.numel() && t.scalar_type() == in.scalar_type(),
                 "all_gather: every output must match the input's numel and dtype");
   }
@@ -1361,12 +1442,12 @@ static WorkPtr exchange_symm(CudaBackend* self, const char* what, at::Tensor in,
 
 WorkPtr CudaBackend::all_gather_v(const std::vector<at::Tensor>& outs, const at::Tensor& in, bool async_op, const OpOptions& o) {
   TORCH_CHECK(static_cast<int>(outs.size()) == size_, "all_gather_v: need size() output tensors");
-  check_tensor(in, device_, "all_gather_v");
+  check_tensor(in, device_, "all_gather_v", cuda_->is_real());
   TORCH_CHECK(outs[rank_].numel() == in.numel(), "all_gather_v: own output slot must match the input");
   std::vector<std::pair<size_t, size_t>> send(size_), recv(size_);
   size_t total = 0;
   for (int r = 0; r < size_; ++r) {
-    check_tensor(outs[r], device_, "all_gather_v");
+    check_tensor(outs[r], device_, "all_gather_v", cuda_->is_real());
     TORCH_CHECK(outs[r].scalar_type() == in.scalar_type(), "all_gather_v: dtype mismatch");
     send[r] = {0, in.nbytes()};
     recv[r] = {total, outs[r].nbytes()};
@@ -1387,8 +1468,8 @@ WorkPtr CudaBackend::all_gather_v(const std::vector<at::Tensor>& outs, const at:
 }
 
 WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in, const ReduceOp& op, bool async_op, const OpOptions& o) {
-  check_tensor(out, device_, "reduce_scatter_single");
-  check_tensor(in, device_, "reduce_scatter_single");
+  check_tensor(out, device_, "reduce_scatter_single", cuda_->is_real());
+  check_tensor(in, device_, "reduce_scatter_single", cuda_->is_real());
   TORCH_CHECK(in.numel() == out.numel() * size_, "reduce_scatter_single: input numel must be output numel * size");
   if (out.numel() == 0) return c10::make_intrusive<CompletedWork>();
   {
@@ -1458,8 +1539,8 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
       // The input lives in symmetric memory: every rank reads its slice of
       // every copy (summed by the switch when bound to the multicast object)
       // straight into the output; scale and cast happen in registers.
-      const bool smc = symm_use_mc(tune_.symm_rs_mc, false, sv, o);
-      const int blocks = symm_blocks_for(smc, out.numel() / pack, o);
+      const bool smc = symm_use_mc(tune_.symm_rs_mc, size_ >= 4, sv, o);
+      const int blocks = symm_blocks_for(smc, out.numel() / pack, o, true);
       at::Tensor i = in, ot = out;
       bytes_issued_ += in.nbytes();
       return run("reduce_scatter/symm", async_op, o, {in}, [this, i, ot, sv, din, dout, scale, smc, blocks](cudaStream_t s) {
@@ -1492,7 +1573,7 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
 WorkPtr CudaBackend::reduce_scatter(at::Tensor& out, const std::vector<at::Tensor>& ins, const ReduceOp& op, bool async_op, const OpOptions& o) {
   TORCH_CHECK(static_cast<int>(ins.size()) == size_, "reduce_scatter: need size() input tensors");
   for (auto& t : ins) {
-    check_tensor(t, device_, "reduce_scatter");
+    check_tensor(t, device_, "reduce_scatter", cuda_->is_real());
     TORCH_CHECK(t.numel() == out.numel() && t.scalar_type() == out.scalar_type(),
                 "reduce_scatter: every input must match the output's numel and dtype");
   }
@@ -1504,13 +1585,13 @@ WorkPtr CudaBackend::reduce_scatter(at::Tensor& out, const std::vector<at::Tenso
 
 WorkPtr CudaBackend::reduce_scatter_v(at::Tensor& out, const std::vector<at::Tensor>& ins, const ReduceOp& op, bool async_op, const OpOptions& o) {
   TORCH_CHECK(static_cast<int>(ins.size()) == size_, "reduce_scatter_v: need size() input tensors");
-  check_tensor(out, device_, "reduce_scatter_v");
+  check_tensor(out, device_, "reduce_scatter_v", cuda_->is_real());
   TORCH_CHECK(ins[rank_].numel() == out.numel(), "reduce_scatter_v: own input slot must match the output");
   // Uneven shares: all-reduce the concatenation, keep the own share.
   std::vector<at::Tensor> flat_ins;
   int64_t my_off = 0, off = 0;
   for (int r = 0; r < size_; ++r) {
-    check_tensor(ins[r], device_, "reduce_scatter_v");
+    check_tensor(ins[r], device_, "reduce_scatter_v", cuda_->is_real());
     if (r == rank_) my_off = off;
     off += ins[r].numel();
     flat_ins.push_back(ins[r].reshape({-1}));
@@ -1549,8 +1630,8 @@ WorkPtr CudaBackend::exchange_nccl(const char* what, const at::Tensor& in, at::T
 }
 
 WorkPtr CudaBackend::all_to_all_single(at::Tensor& out, const at::Tensor& in, bool async_op, const OpOptions& o) {
-  check_tensor(out, device_, "all_to_all_single");
-  check_tensor(in, device_, "all_to_all_single");
+  check_tensor(out, device_, "all_to_all_single", cuda_->is_real());
+  check_tensor(in, device_, "all_to_all_single", cuda_->is_real());
   TORCH_CHECK(out.numel() == in.numel() && out.scalar_type() == in.scalar_type(),
               "all_to_all_single: input and output must have the same numel and dtype");
   TORCH_CHECK(in.numel() % size_ == 0, "all_to_all_single: numel must divide by size()");
@@ -1577,8 +1658,8 @@ WorkPtr CudaBackend::all_to_all_single(at::Tensor& out, const at::Tensor& in, bo
 
 WorkPtr CudaBackend::all_to_all_v_single(at::Tensor& out, const at::Tensor& in, const std::vector<int64_t>& out_splits,
                                          const std::vector<int64_t>& in_splits, bool async_op, const OpOptions& o) {
-  check_tensor(out, device_, "all_to_all_v_single");
-  check_tensor(in, device_, "all_to_all_v_single");
+  check_tensor(out, device_, "all_to_all_v_single", cuda_->is_real());
+  check_tensor(in, device_, "all_to_all_v_single", cuda_->is_real());
   TORCH_CHECK(out.scalar_type() == in.scalar_type(), "all_to_all_v_single: dtype mismatch");
   TORCH_CHECK(static_cast<int>(out_splits.size()) == size_ && static_cast<int>(in_splits.size()) == size_,
               "all_to_all_v_single: need size() split sizes on both sides");
@@ -1617,8 +1698,8 @@ WorkPtr CudaBackend::all_to_all(const std::vector<at::Tensor>& outs, const std::
   std::vector<at::Tensor> flat_ins;
   size_t so = 0, ro = 0;
   for (int p = 0; p < size_; ++p) {
-    check_tensor(ins[p], device_, "all_to_all");
-    check_tensor(outs[p], device_, "all_to_all");
+    check_tensor(ins[p], device_, "all_to_all", cuda_->is_real());
+    check_tensor(outs[p], device_, "all_to_all", cuda_->is_real());
     TORCH_CHECK(ins[p].scalar_type() == ins[0].scalar_type() && outs[p].scalar_type() == ins[0].scalar_type(),
                 "all_to_all: every tensor must have the same dtype");
     send[p] = {so, ins[p].nbytes()};
@@ -1643,9 +1724,9 @@ WorkPtr CudaBackend::all_to_all(const std::vector<at::Tensor>& outs, const std::
 
 WorkPtr CudaBackend::device_alltoallv_single(at::Tensor& out, const at::Tensor& in, const at::Tensor& out_splits,
                                              const at::Tensor& in_splits, bool async_op, const OpOptions& o) {
-  check_tensor(out, device_, "device_alltoallv_single");
-  check_tensor(in, device_, "device_alltoallv_single");
-  check_tensor(in_splits, device_, "device_alltoallv_single");
+  check_tensor(out, device_, "device_alltoallv_single", cuda_->is_real());
+  check_tensor(in, device_, "device_alltoallv_single", cuda_->is_real());
+  check_tensor(in_splits, device_, "device_alltoallv_single", cuda_->is_real());
   TORCH_CHECK(in_splits.scalar_type() == at::kLong && in_splits.numel() == size_,
               "device_alltoallv_single: input_split_sizes must be an int64 device tensor of size() entries");
   TORCH_CHECK(out.scalar_type() == in.scalar_type(), "device_alltoallv_single: dtype mismatch");
@@ -1695,7 +1776,7 @@ WorkPtr CudaBackend::reduce_scatter_quantized(at::Tensor& out, const at::Tensor&
 }
 
 WorkPtr CudaBackend::broadcast(at::Tensor& t, int root, bool async_op, const OpOptions& o) {
-  check_tensor(t, device_, "broadcast");
+  check_tensor(t, device_, "broadcast", cuda_->is_real());
   if (t.numel() == 0 || size_ == 1) return c10::make_intrusive<CompletedWork>();
   NcclDataType ndt;
   if (algo_override(o) == Algo::NCCL && nccl_comm_ != nullptr && to_nccl_dtype(t.scalar_type(), &ndt)) {
@@ -1721,7 +1802,7 @@ WorkPtr CudaBackend::barrier(bool async_op, const OpOptions& o) {
 }
 
 WorkPtr CudaBackend::scatter(at::Tensor& out, const std::vector<at::Tensor>& ins, int root, bool async_op, const OpOptions& o) {
-  check_tensor(out, device_, "scatter");
+  check_tensor(out, device_, "scatter", cuda_->is_real());
   std::vector<std::pair<size_t, size_t>> send(size_, {0, 0}), recv(size_, {0, 0});
   at::Tensor in;
   if (rank_ == root) {
@@ -1729,7 +1810,7 @@ WorkPtr CudaBackend::scatter(at::Tensor& out, const std::vector<at::Tensor>& ins
     std::vector<at::Tensor> flat_ins;
     size_t off = 0;
     for (int p = 0; p < size_; ++p) {
-      check_tensor(ins[p], device_, "scatter");
+      check_tensor(ins[p], device_, "scatter", cuda_->is_real());
       TORCH_CHECK(ins[p].numel() == out.numel() && ins[p].scalar_type() == out.scalar_type(),
                   "scatter: every input must match the output's numel and dtype");
       send[p] = {off, ins[p].nbytes()};
@@ -1745,7 +1826,7 @@ WorkPtr CudaBackend::scatter(at::Tensor& out, const std::vector<at::Tensor>& ins
 }
 
 WorkPtr CudaBackend::gather(const std::vector<at::Tensor>& outs, const at::Tensor& in, int root, bool async_op, const OpOptions& o) {
-  check_tensor(in, device_, "gather");
+  check_tensor(in, device_, "gather", cuda_->is_real());
   std::vector<std::pair<size_t, size_t>> send(size_, {0, 0}), recv(size_, {0, 0});
   send[root] = {0, in.nbytes()};
   at::Tensor out;
@@ -1754,7 +1835,7 @@ WorkPtr CudaBackend::gather(const std::vector<at::Tensor>& outs, const at::Tenso
     TORCH_CHECK(static_cast<int>(outs.size()) == size_, "gather: the root needs size() output tensors");
     const size_t blk = round_up(in.nbytes(), 16);
     for (int p = 0; p < size_; ++p) {
-      check_tensor(outs[p], device_, "gather");
+      check_tensor(outs[p], device_, "gather", cuda_->is_real());
       TORCH_CHECK(outs[p].numel() == in.numel() && outs[p].scalar_type() == in.scalar_type(),
                   "gather: every output must match the input's numel and dtype");
       recv[p] = {p * blk, in.nbytes()};
@@ -1777,7 +1858,7 @@ WorkPtr CudaBackend::gather(const std::vector<at::Tensor>& outs, const at::Tenso
 }
 
 WorkPtr CudaBackend::send(const at::Tensor& t, int dst, bool async_op, const OpOptions& o) {
-  check_tensor(t, device_, "send");
+  check_tensor(t, device_, "send", cuda_->is_real());
   TORCH_CHECK(nccl_comm_ != nullptr, "send needs NCCL (communicator created with use_nccl=0, or libnccl missing)");
   NcclDataType dt;
   TORCH_CHECK(to_nccl_dtype(t.scalar_type(), &dt), "send: unsupported dtype ", t.scalar_type());
@@ -1788,7 +1869,7 @@ WorkPtr CudaBackend::send(const at::Tensor& t, int dst, bool async_op, const OpO
 }
 
 WorkPtr CudaBackend::recv(at::Tensor& t, int src, bool async_op, const OpOptions& o) {
-  check_tensor(t, device_, "recv");
+  check_tensor(t, device_, "recv", cuda_->is_real());
   TORCH_CHECK(nccl_comm_ != nullptr, "recv needs NCCL (communicator created with use_nccl=0, or libnccl missing)");
   NcclDataType dt;
   TORCH_CHECK(to_nccl_dtype(t.scalar_type(), &dt), "recv: unsupported dtype ", t.scalar_type());
@@ -1803,7 +1884,7 @@ WorkPtr CudaBackend::batch_op_issue(const std::vector<P2POp>& ops, bool async_op
   TORCH_CHECK(nccl_comm_ != nullptr, "batched send/recv needs NCCL");
   std::vector<at::Tensor> keep;
   for (auto& op : ops) {
-    check_tensor(op.tensor, device_, "batch_op_issue");
+    check_tensor(op.tensor, device_, "batch_op_issue", cuda_->is_real());
     keep.push_back(op.tensor);
   }
   auto copy = ops;
@@ -1883,6 +1964,24 @@ std::unordered_map<std::string, std::string> CudaBackend::comm_dump() const {
   d["ops_issued"] = std::to_string(ops_issued_.load());
   d["bytes_issued"] = std::to_string(bytes_issued_.load());
   d["failed"] = failed_.load() ? failure_text_ : "";
+  d["tuning/staging_bytes"] = std::to_string(tune_.staging_bytes);
+  d["tuning/oneshot_max_bytes"] = std::to_string(tune_.oneshot_max_bytes);
+  d["tuning/lamport_max_bytes"] = std::to_string(tune_.lamport_max_bytes);
+  d["tuning/symm_blocks"] = std::to_string(tune_.symm_blocks);
+  d["tuning/symm_blocks_nomc"] = std::to_string(tune_.symm_blocks_nomc);
+  d["tuning/max_blocks"] = std::to_string(tune_.max_blocks);
+  d["tuning/threads"] = std::to_string(tune_.threads);
+  d["tuning/auto_nccl"] = tune_.auto_nccl ? "1" : "0";
+  d["tuning/use_multicast"] = tune_.use_multicast ? "1" : "0";
+  d["tuning/channel_streams"] = tune_.channel_streams ? "1" : "0";
+  d["tuning/fast_sync"] = tune_.fast_sync ? "1" : "0";
+  d["tuning/device_wait_ms"] = std::to_string(tune_.device_wait_ns / 1000000ull);
+  d["tuning/max_event_pool"] = std::to_string(tune_.max_event_pool);
+  d["tuning/watchdog_interval_ms"] = std::to_string(tune_.watchdog_interval_ms);
+  {
+    std::lock_guard<std::mutex> g(const_cast<std::mutex&>(pool_mu_));
+    d["event_pool"] = std::to_string(event_pool_.size());
+  }
   {
     std::lock_guard<std::mutex> g(symm_mu_);
     d["symm_regions"] = std::to_string(symm_regs_.size());
@@ -1903,7 +2002,7 @@ std::unordered_map<std::string, std::string> CudaBackend::comm_dump() const {
 
 at::Tensor CudaBackend::symm_empty(const std::vector<int64_t>& sizes, at::ScalarType dtype) {
   check_usable();
-  c10::cuda::CUDAGuard guard(device_);
+  DeviceScope guard(cuda_, device_.index());
   int64_t numel = 1;
   for (int64_t d : sizes) {
     TORCH_CHECK(d >= 0, "symm_empty: negative dimension");
@@ -1916,12 +2015,14 @@ at::Tensor CudaBackend::symm_empty(const std::vector<int64_t>& sizes, at::Scalar
     symm_regs_[reinterpret_cast<uintptr_t>(seg->local())] = SymmReg{seg->bytes, seg, false};
   }
   // The segment, not the tensor, owns the memory (unmapping is a collective matter).
-  return at::from_blob(seg->local(), sizes, [](void*) {}, at::TensorOptions().dtype(dtype).device(device_));
+  // (Under a test fake of the runtime the "device" memory is host memory.)
+  const at::Device where = cuda_->is_real() ? device_ : at::Device(at::kCPU);
+  return at::from_blob(seg->local(), sizes, [](void*) {}, at::TensorOptions().dtype(dtype).device(where));
 }
 
 void CudaBackend::symm_free(const at::Tensor& t) {
   check_usable();
-  c10::cuda::CUDAGuard guard(device_);
+  DeviceScope guard(cuda_, device_.index());
   std::shared_ptr<SymmSegment> seg;
   {
     std::lock_guard<std::mutex> g(symm_mu_);
@@ -1940,8 +2041,8 @@ void CudaBackend::symm_free(const at::Tensor& t) {
 
 void CudaBackend::tensor_register(const at::Tensor& t) {
   check_usable();
-  check_tensor(t, device_, "tensor_register");
-  c10::cuda::CUDAGuard guard(device_);
+  check_tensor(t, device_, "tensor_register", cuda_->is_real());
+  DeviceScope guard(cuda_, device_.index());
   // Memory from the communicator's allocator is registered as the whole
   // allocation (every tensor inside it is then covered, and it can be bound to
   // the multicast object); anything else as the tensor's own range over CUDA IPC.
@@ -1963,7 +2064,7 @@ void CudaBackend::tensor_register(const at::Tensor& t) {
 
 void CudaBackend::tensor_deregister(const at::Tensor& t) {
   check_usable();
-  c10::cuda::CUDAGuard guard(device_);
+  DeviceScope guard(cuda_, device_.index());
   std::shared_ptr<SymmSegment> seg;
   {
     std::lock_guard<std::mutex> g(symm_mu_);

@@ -105,14 +105,19 @@ struct Tuning {
   size_t min_chunk_bytes = 64 * 1024;
   bool auto_nccl = false;                  // opt-in: algo=auto may pick NCCL where it measured faster
   int symm_blocks = 32;                    // grid of the one-pass kernels on symmetric buffers (same on every rank)
-  int symm_blocks_nomc = 64;               // same, when the data path is plain peer loads / stores
+  int symm_blocks_nomc = 64;               // same, when the data path is plain peer stores
+  int symm_blocks_ld = 128;                // same, for plain peer loads: an SM keeps only so many remote reads in flight,
+                                           // so read bandwidth grows with the number of SMs that read
   // Data path of the one-pass kernels: 1 = through the switch's multicast
   // object (multimem.st / multimem.ld_reduce), 0 = plain peer stores / loads,
   // -1 = by rank count. Multicast needs 1/nranks of the store or load
   // instructions, but the switch also delivers a rank's own copy back to it:
   // nranks/(nranks-1) times the bytes of the peer path for all-gather and
   // reduce-scatter, while for all-reduce it moves (1 + 1/nranks) S against
-  // 2 (nranks-1)/nranks S and wins from 4 ranks on.
+  // 2 (nranks-1)/nranks S and wins from 4 ranks on. By rank count: all-gather
+  // uses peer stores (they stream at link rate from few SMs); reduce-scatter
+  // and all-reduce use the switch from 4 ranks on (peer loads need most of
+  // the SMs to reach link rate) and peer loads below.
   int symm_ag_mc = -1;
   int symm_rs_mc = -1;
   int symm_ar_mc = -1;
@@ -218,7 +223,7 @@ class CudaBackend final : public Backend {
   LaunchShape shape_for(size_t bytes, size_t slot_multiplier, int block_cap = 0) const;
   // Multicast or peer path for one call of a one-pass kernel (`knob`: the Tuning field of its kind).
   bool symm_use_mc(int knob, bool mc_by_default, const SymmView& v, const OpOptions& o) const;
-  int symm_blocks_for(bool mc, size_t vectors, const OpOptions& o) const;
+  int symm_blocks_for(bool mc, size_t vectors, const OpOptions& o, bool peer_loads = false) const;
   // Resolves algo=auto for one call: own kernels (AUTO) or NCCL, from measured cross-over sizes.
   Algo route(Coll c, size_t bytes, const OpOptions& o) const;
   std::shared_ptr<Backend> create_pair_comm(int peer, const std::string& name) override;
@@ -239,6 +244,9 @@ class CudaBackend final : public Backend {
   // word, and an unobserved synchronous call needs no events).
   WorkPtr run(const char* what, bool async_op, const OpOptions& o, std::vector<at::Tensor> keep_alive,
               const std::function<void(cudaStream_t)>& launch, int chan = kChanMain, bool own_kernel = false);
+
+  // Fields of ncclConfig_t named by hints (what ncclCommInitRankConfig is given).
+  static NcclConfig nccl_config_from_hints(const Hints& h, const std::string& comm_name);
 
   // Test seams.
   void set_cuda_api(std::shared_ptr<CudaApi> api) { cuda_ = std::move(api); }

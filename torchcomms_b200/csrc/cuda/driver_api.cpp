@@ -3,6 +3,8 @@
 
 #include <dlfcn.h>
 
+#include <ATen/cuda/CUDAContext.h>
+
 #include <mutex>
 #include <stdexcept>
 
@@ -119,6 +121,42 @@ class RealCuda final : public CudaApi {
 };
 
 } // namespace
+
+cudaStream_t CudaApi::currentStream(int device) {
+  return at::cuda::getCurrentCUDAStream(static_cast<c10::DeviceIndex>(device)).stream();
+}
+
+namespace {
+std::mutex& override_mu() {
+  static std::mutex m;
+  return m;
+}
+std::shared_ptr<DriverApi>& driver_override() {
+  static std::shared_ptr<DriverApi> p;
+  return p;
+}
+std::shared_ptr<CudaApi>& cuda_override() {
+  static std::shared_ptr<CudaApi> p;
+  return p;
+}
+} // namespace
+
+std::shared_ptr<DriverApi> DriverApi::current() {
+  std::lock_guard<std::mutex> g(override_mu());
+  return driver_override() ? driver_override() : real();
+}
+void DriverApi::install(std::shared_ptr<DriverApi> fake) {
+  std::lock_guard<std::mutex> g(override_mu());
+  driver_override() = std::move(fake);
+}
+std::shared_ptr<CudaApi> CudaApi::current() {
+  std::lock_guard<std::mutex> g(override_mu());
+  return cuda_override() ? cuda_override() : real();
+}
+void CudaApi::install(std::shared_ptr<CudaApi> fake) {
+  std::lock_guard<std::mutex> g(override_mu());
+  cuda_override() = std::move(fake);
+}
 
 std::shared_ptr<DriverApi> DriverApi::real() {
   static std::shared_ptr<DriverApi> inst = std::make_shared<RealDriver>();

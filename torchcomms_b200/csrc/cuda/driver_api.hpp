@@ -40,6 +40,9 @@ class DriverApi {
   virtual std::string errorString(CUresult r) = 0;
 
   static std::shared_ptr<DriverApi> real();
+  // What new communicators use: the real driver unless a test installed a fake.
+  static std::shared_ptr<DriverApi> current();
+  static void install(std::shared_ptr<DriverApi> fake);   // nullptr restores the real one
 };
 
 // Runtime calls used by work objects and the watchdog.
@@ -54,6 +57,17 @@ class CudaApi {
   virtual cudaError_t streamWaitEvent(cudaStream_t s, cudaEvent_t e) = 0;
   virtual cudaError_t streamIsCapturing(cudaStream_t s, bool* capturing, unsigned long long* graph_id) = 0;
   virtual const char* errorString(cudaError_t e) = 0;
+
+  // False for test fakes: no CUDA context exists, so device guards are
+  // skipped and kernels are not launched (the fake is told what would have
+  // been launched instead).
+  virtual bool is_real() { return true; }
+  virtual void noteLaunch(const char* what, cudaStream_t s) {
+    (void)what;
+    (void)s;
+  }
+  // The calling thread's current stream on `device` (PyTorch's notion).
+  virtual cudaStream_t currentStream(int device);
 
   // Resources of the CUDA backend. These have working defaults (the runtime
   // call itself), so a test fake overrides only what it wants to script.
@@ -98,6 +112,8 @@ class CudaApi {
   }
 
   static std::shared_ptr<CudaApi> real();
+  static std::shared_ptr<CudaApi> current();
+  static void install(std::shared_ptr<CudaApi> fake);
 };
 
 #define B200C_CU_CHECK(drv, expr)                                                          \

@@ -3,12 +3,34 @@
 
 #include <dlfcn.h>
 
+#include <cstddef>
 #include <mutex>
 #include <stdexcept>
 
 namespace b200c {
 
 namespace {
+
+// ncclConfig_t as published in nccl.h of NCCL 2.28 (2.27 ends after nvlsCTAs).
+struct RawNcclConfig {
+  size_t size;
+  unsigned int magic;
+  unsigned int version;
+  int blocking;
+  int cgaClusterSize;
+  int minCTAs;
+  int maxCTAs;
+  const char* netName;
+  int splitShare;
+  int trafficClass;
+  const char* commName;
+  int collnetEnable;
+  int CTAPolicy;
+  int shrinkShare;
+  int nvlsCTAs;
+  int nChannelsPerNetPeer;
+  int nvlinkCentricSched;
+};
 
 class RealNccl final : public NcclApi {
  public:
@@ -27,6 +49,32 @@ class RealNccl final : public NcclApi {
   NcclResult getUniqueId(NcclUniqueId* id) override { return need(fn_uid_)(id); }
   NcclResult commInitRank(NcclComm** comm, int nranks, NcclUniqueId id, int rank) override {
     return need(fn_init_)(comm, nranks, id, rank);
+  }
+  NcclResult commInitRankConfig(NcclComm** comm, int nranks, NcclUniqueId id, int rank, const NcclConfig& cfg) override {
+    load();
+    int code = 0;
+    if (fn_init_config_ == nullptr || fn_version_ == nullptr || fn_version_(&code) != kNcclSuccess || code < 22700 || !cfg.any()) {
+      return commInitRank(comm, nranks, id, rank);
+    }
+    RawNcclConfig raw{};
+    raw.size = code >= 22800 ? sizeof(RawNcclConfig) : offsetof(RawNcclConfig, nChannelsPerNetPeer);
+    raw.magic = 0xcafebeef;
+    raw.version = static_cast<unsigned int>(code);
+    raw.blocking = cfg.blocking;
+    raw.cgaClusterSize = cfg.cgaClusterSize;
+    raw.minCTAs = cfg.minCTAs;
+    raw.maxCTAs = cfg.maxCTAs;
+    raw.netName = cfg.netName.empty() ? nullptr : cfg.netName.c_str();
+    raw.splitShare = cfg.splitShare;
+    raw.trafficClass = cfg.trafficClass;
+    raw.commName = cfg.commName.empty() ? nullptr : cfg.commName.c_str();
+    raw.collnetEnable = cfg.collnetEnable;
+    raw.CTAPolicy = cfg.CTAPolicy;
+    raw.shrinkShare = cfg.shrinkShare;
+    raw.nvlsCTAs = cfg.nvlsCTAs;
+    raw.nChannelsPerNetPeer = cfg.nChannelsPerNetPeer;
+    raw.nvlinkCentricSched = cfg.nvlinkCentricSched;
+    return fn_init_config_(comm, nranks, id, rank, &raw);
   }
   NcclResult commDestroy(NcclComm* comm) override { return need(fn_destroy_)(comm); }
   NcclResult commAbort(NcclComm* comm) override { return need(fn_abort_)(comm); }
@@ -88,6 +136,7 @@ class RealNccl final : public NcclApi {
       bind(fn_version_, "ncclGetVersion");
       bind(fn_uid_, "ncclGetUniqueId");
       bind(fn_init_, "ncclCommInitRank");
+      bind(fn_init_config_, "ncclCommInitRankConfig");
       bind(fn_destroy_, "ncclCommDestroy");
       bind(fn_abort_, "ncclCommAbort");
       bind(fn_async_, "ncclCommGetAsyncError");
@@ -111,6 +160,7 @@ class RealNccl final : public NcclApi {
   NcclResult (*fn_version_)(int*) = nullptr;
   NcclResult (*fn_uid_)(NcclUniqueId*) = nullptr;
   NcclResult (*fn_init_)(NcclComm**, int, NcclUniqueId, int) = nullptr;
+  NcclResult (*fn_init_config_)(NcclComm**, int, NcclUniqueId, int, RawNcclConfig*) = nullptr;
   NcclResult (*fn_destroy_)(NcclComm*) = nullptr;
   NcclResult (*fn_abort_)(NcclComm*) = nullptr;
   NcclResult (*fn_async_)(NcclComm*, NcclResult*) = nullptr;
@@ -129,6 +179,26 @@ class RealNccl final : public NcclApi {
 };
 
 } // namespace
+
+namespace {
+std::mutex& nccl_override_mu() {
+  static std::mutex m;
+  return m;
+}
+std::shared_ptr<NcclApi>& nccl_override() {
+  static std::shared_ptr<NcclApi> p;
+  return p;
+}
+} // namespace
+
+std::shared_ptr<NcclApi> NcclApi::current() {
+  std::lock_guard<std::mutex> g(nccl_override_mu());
+  return nccl_override() ? nccl_override() : real();
+}
+void NcclApi::install(std::shared_ptr<NcclApi> fake) {
+  std::lock_guard<std::mutex> g(nccl_override_mu());
+  nccl_override() = std::move(fake);
+}
 
 std::shared_ptr<NcclApi> NcclApi::real() {
   static std::shared_ptr<NcclApi> inst = std::make_shared<RealNccl>();

@@ -29,6 +29,32 @@ enum NcclDataType : int {
 };
 enum NcclRedOp : int { kNcclSum = 0, kNcclProd = 1, kNcclMax = 2, kNcclMin = 3, kNcclAvg = 4 };
 
+// The settable fields of ncclConfig_t (public NCCL ABI, layout of 2.28; 2.27
+// has the same fields up to nvlsCTAs). kUnset / empty = leave NCCL's default.
+struct NcclConfig {
+  static constexpr int kUnset = -2147483647 - 1;  // NCCL_CONFIG_UNDEF_INT
+  int blocking = kUnset;
+  int cgaClusterSize = kUnset;
+  int minCTAs = kUnset;
+  int maxCTAs = kUnset;
+  std::string netName;
+  int splitShare = kUnset;
+  int trafficClass = kUnset;
+  std::string commName;
+  int collnetEnable = kUnset;
+  int CTAPolicy = kUnset;
+  int shrinkShare = kUnset;
+  int nvlsCTAs = kUnset;
+  int nChannelsPerNetPeer = kUnset;
+  int nvlinkCentricSched = kUnset;
+  bool any() const {
+    return blocking != kUnset || cgaClusterSize != kUnset || minCTAs != kUnset || maxCTAs != kUnset || !netName.empty() ||
+        splitShare != kUnset || trafficClass != kUnset || !commName.empty() || collnetEnable != kUnset ||
+        CTAPolicy != kUnset || shrinkShare != kUnset || nvlsCTAs != kUnset || nChannelsPerNetPeer != kUnset ||
+        nvlinkCentricSched != kUnset;
+  }
+};
+
 class NcclApi {
  public:
   virtual ~NcclApi() = default;
@@ -36,6 +62,12 @@ class NcclApi {
   virtual std::string version() = 0;
   virtual NcclResult getUniqueId(NcclUniqueId* id) = 0;
   virtual NcclResult commInitRank(NcclComm** comm, int nranks, NcclUniqueId id, int rank) = 0;
+  // ncclCommInitRankConfig with the given fields set. The default forwards to
+  // commInitRank (for implementations that have no configuration to honour).
+  virtual NcclResult commInitRankConfig(NcclComm** comm, int nranks, NcclUniqueId id, int rank, const NcclConfig& cfg) {
+    (void)cfg;
+    return commInitRank(comm, nranks, id, rank);
+  }
   virtual NcclResult commDestroy(NcclComm* comm) = 0;
   virtual NcclResult commAbort(NcclComm* comm) = 0;
   virtual NcclResult commGetAsyncError(NcclComm* comm, NcclResult* async_error) = 0;
@@ -54,6 +86,9 @@ class NcclApi {
   virtual std::string errorString(NcclResult r) = 0;
 
   static std::shared_ptr<NcclApi> real();
+  // What new communicators use: the real library unless a test installed a fake.
+  static std::shared_ptr<NcclApi> current();
+  static void install(std::shared_ptr<NcclApi> fake);   // nullptr restores the real one
 };
 
 } // namespace b200c

@@ -210,121 +210,101 @@ struct CombineArgs {
   int num_tokens;
 };
 
+// Pull combine: the token's owner reads the expert output of every rank the
+// token went to straight out of that rank's `combine_x` (the row is the slot
+// the dispatch recorded in `send_slot`) and forms the weighted sum in
+// registers. Each row crosses NVLink once and nothing is staged. Every block
+// meets its peers' blocks before (all expert outputs are complete) and after
+// (nobody still reads this rank's outputs), so the kernel needs no grid-wide
+// synchronisation.
 __device__ void ep_combine_body(const CommDev& c, const EpDev& e, const CombineArgs& a) {
-  cg::grid_group grid = cg::this_grid();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gwarp = blockIdx.x * kEpWarps + warp, nwarps = gridDim.x * kEpWarps;
   const size_t row_bytes = static_cast<size_t>(e.hidden) * 2;
-  // 1. Push: the expert output of every received row goes back to slot
-  //    [token][this rank] of the rank the token came from. The closing barrier
-  //    of the previous combine guarantees those slots are free.
-  const int n_rows = e.recv_info[0];
-  const int row_vec = e.hidden / 8;  // 16-byte vectors per row; a multiple of 32
-  // Received rows are packed by source rank. Walking them in that order would
-  // make every rank push into rank 0 first, then all into rank 1, ...: eight
-  // senders share one receiver's links. Each rank therefore starts with the
-  // rows of the next rank and goes round, so that at any time the ranks push
-  // into different peers.
-  int seg_start[kMaxRanks + 1];
-  seg_start[0] = 0;
-#pragma unroll
-  for (int s = 0; s < kMaxRanks; ++s) {
-    seg_start[s + 1] = seg_start[s] + (s < e.nranks ? e.recv_info[1 + s] : 0);
-  }
-  for (int vrow = gwarp; vrow < n_rows; vrow += nwarps) {
-    int rem = vrow, row = -1;
-    for (int j = 0; j < e.nranks; ++j) {
-      int s = e.rank + 1 + j;
-      if (s >= e.nranks) s -= e.nranks;
-      const int len = seg_start[s + 1] - seg_start[s];
-      if (rem < len) {
-        row = seg_start[s] + rem;
-        break;
-      }
-      rem -= len;
-    }
-    if (row < 0 || row >= n_rows) continue;  // counts and total disagree: skip rather than read out of range
-    const int src = e.recv_src[e.rank][row];
-    const int s = src / e.max_tokens, t = src - s * e.max_tokens;
-    if (src < 0 || s >= e.nranks) {  // never store through a bad index
-      if (lane == 0) c.status[0] = c.status[0] | kStatusBadArg;
-      continue;
-    }
-    const uint4* from = reinterpret_cast<const uint4*>(e.combine_x[e.rank] + static_cast<size_t>(row) * row_bytes);
-    uint4* to = reinterpret_cast<uint4*>(e.comb_recv[s] + (static_cast<size_t>(t) * e.nranks + e.rank) * row_bytes);
-    int v = lane;
-    for (; v + 96 < row_vec; v += 128) {
-      const uint4 v0 = from[v], v1 = from[v + 32], v2 = from[v + 64], v3 = from[v + 96];
-      to[v] = v0;
-      to[v + 32] = v1;
-      to[v + 64] = v2;
-      to[v + 96] = v3;
-    }
-    for (; v < row_vec; v += 32) to[v] = from[v];
-  }
-  __threadfence_system();
-  grid.sync();
-  if (blockIdx.x == 0) ep_rank_barrier(c, 0x93);
-  grid.sync();
-  // 2. Every contribution has landed: weighted sum out of this rank's own memory.
-  const char* mine = e.comb_recv[e.rank];
-  for (int t = gwarp; t < a.num_tokens; t += nwarps) {
-    int slot = -1;
-    float wt = 1.0f;
-    if (lane < e.nranks) {
-      slot = e.send_slot[static_cast<size_t>(t) * e.nranks + lane];
-      if (a.weights != nullptr) wt = a.weights[static_cast<size_t>(t) * e.nranks + lane];
-    }
-    const uint32_t have = __ballot_sync(0xffffffffu, slot >= 0);
-    for (int e0 = lane * 8; e0 < e.hidden; e0 += 256) {
-      float acc[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-      if (a.bias != nullptr) {
-        const uint4 b = ld16(static_cast<const __nv_bfloat16*>(a.bias) + static_cast<size_t>(t) * e.hidden + e0);
-        const uint32_t* p = &b.x;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = bf2f(p[i]);
-          acc[2 * i] = f.x;
-          acc[2 * i + 1] = f.y;
+  const int cap_rows = e.nranks * e.max_tokens;
+  BlockEpoch ep;
+  ep.load(c, kFlagSetEp);
+  bool ok = block_barrier(c, kFlagSetEp, ep, 0x93);
+  if (ok) {
+    for (int t = gwarp; t < a.num_tokens; t += nwarps) {
+      int slot = -1;
+      float wt = 1.0f;
+      if (lane < e.nranks) {
+        slot = e.send_slot[static_cast<size_t>(t) * e.nranks + lane];
+        if (slot >= cap_rows) {  // never read through a bad index
+          c.status[0] = c.status[0] | kStatusBadArg;
+          slot = -1;
         }
+        if (a.weights != nullptr) wt = a.weights[static_cast<size_t>(t) * e.nranks + lane];
       }
-      uint4 rows[kMaxRanks];
+      const uint32_t have = __ballot_sync(0xffffffffu, slot >= 0);
+      // Two 16-byte columns per lane and step: up to 2 x nranks remote loads in flight per thread.
+      for (int e0 = lane * 8; e0 < e.hidden; e0 += 512) {
+        const bool second = e0 + 256 < e.hidden;
+        uint4 rows[2][kMaxRanks];
 #pragma unroll
-      for (int d = 0; d < kMaxRanks; ++d) {
-        if (d < e.nranks && ((have >> d) & 1u)) {
-          rows[d] = ld16(mine + (static_cast<size_t>(t) * e.nranks + d) * row_bytes + static_cast<size_t>(e0) * 2);
-        }
-      }
-#pragma unroll
-      for (int d = 0; d < kMaxRanks; ++d) {
-        if (d < e.nranks) {
-          const float wd = __shfl_sync(0xffffffffu, wt, d);
-          if ((have >> d) & 1u) {
-            const uint32_t* p = &rows[d].x;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = bf2f(p[i]);
-              acc[2 * i] += wd * f.x;
-              acc[2 * i + 1] += wd * f.y;
+        for (int i = 0; i < kMaxRanks; ++i) {
+          if (i < e.nranks) {
+            // Start at the next rank so that the ranks read different peers at any time.
+            int d = e.rank + 1 + i;
+            if (d >= e.nranks) d -= e.nranks;
+            const int sd = __shfl_sync(0xffffffffu, slot, d);
+            if ((have >> d) & 1u) {
+              const char* src = e.combine_x[d] + static_cast<size_t>(sd) * row_bytes + static_cast<size_t>(e0) * 2;
+              rows[0][i] = ld16_stream(src);
+              if (second) rows[1][i] = ld16_stream(src + 512);
             }
           }
         }
-      }
-      uint4 o;
-      uint32_t* po = &o.x;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-        po[i] = *reinterpret_cast<uint32_t*>(&h);
+        for (int h = 0; h < 2; ++h) {
+          if (h == 1 && !second) break;
+          const int col = e0 + h * 256;
+          float acc[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+          if (a.bias != nullptr) {
+            const uint4 b = ld16(static_cast<const __nv_bfloat16*>(a.bias) + static_cast<size_t>(t) * e.hidden + col);
+            const uint32_t* p = &b.x;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = bf2f(p[i]);
+              acc[2 * i] = f.x;
+              acc[2 * i + 1] = f.y;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < kMaxRanks; ++i) {
+            if (i < e.nranks) {
+              int d = e.rank + 1 + i;
+              if (d >= e.nranks) d -= e.nranks;
+              const float wd = __shfl_sync(0xffffffffu, wt, d);
+              if ((have >> d) & 1u) {
+                const uint32_t* p = &rows[h][i].x;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const float2 f = bf2f(p[k]);
+                  acc[2 * k] += wd * f.x;
+                  acc[2 * k + 1] += wd * f.y;
+                }
+              }
+            }
+          }
+          uint4 o;
+          uint32_t* po = &o.x;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 hh = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+            po[i] = *reinterpret_cast<uint32_t*>(&hh);
+          }
+          st16(static_cast<__nv_bfloat16*>(a.out) + static_cast<size_t>(t) * e.hidden + col, o);
+        }
       }
-      st16(static_cast<__nv_bfloat16*>(a.out) + static_cast<size_t>(t) * e.hidden + e0, o);
     }
+    // Nobody overwrites its expert outputs while a peer still reads them.
+    ok = block_barrier(c, kFlagSetEp, ep, 0x94);
   }
-  grid.sync();
-  // Nobody overwrites a receive slot that is still being summed.
-  if (blockIdx.x == 0) ep_rank_barrier(c, 0x94);
+  ep.store(c, kFlagSetEp);
 }
 
 __global__ void __launch_bounds__(kEpThreads) k_ep_combine(CommDev c, EpDev e, CombineArgs a) {

@@ -6,11 +6,10 @@
 // scale per 128 elements while it is in registers, and stores the row, its
 // scales, source index and re-based top-k ids / weights straight into the
 // destination rank's receive buffer over NVLink, packed by source rank.
-// combine: every rank pushes the expert outputs of the rows it received back
-// into the slot [token][this rank] of the token's source rank (NVLink stores
-// stream; remote loads would stall on the round trip), one barrier, then the
-// source sums its slots locally (optionally weighted, optionally plus a bias)
-// in fp32.
+// combine: the token's source rank reads the expert output of every rank the
+// token went to straight out of that rank's output buffer (the row index was
+// recorded by the dispatch) and sums them (optionally weighted, optionally
+// plus a bias) in fp32 in registers: one pass over NVLink, nothing staged.
 //
 // Replaces, in the reference: comms/prims/collectives/link_ep (layout kernel
 // cpp/intranode/kernels/Layout.cu:39-218, notify Notify.cu:97-440, dispatch
@@ -35,7 +34,7 @@ struct EpDev {
   float* recv_topk_w[kMaxRanks];       // [rows, topk]
   long long* count_matrix[kMaxRanks];  // [nranks, nranks]: [s][d] tokens s sends to d
   char* combine_x[kMaxRanks];          // [rows, hidden] bf16: expert outputs, row-aligned with the received rows
-  char* comb_recv[kMaxRanks];          // [max_tokens, nranks, hidden] bf16: outputs returned to the token's source
+  char* comb_recv[kMaxRanks];          // unused (kept for layout compatibility of the descriptor)
   // Local scratch.
   int* cnt;          // [nranks]
   int* cursor;       // [nranks]

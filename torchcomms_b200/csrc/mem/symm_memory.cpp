@@ -151,9 +151,10 @@ int FdChannel::recv_fd(int src, uint64_t tag, int timeout_ms) {
 // ----------------------------------------------------------- SymmMemory ----
 
 SymmMemory::SymmMemory(c10::intrusive_ptr<c10d::Store> store, int rank, int nranks, int device_index,
-                       std::shared_ptr<DriverApi> driver, std::chrono::milliseconds timeout, bool allow_multicast)
+                       std::shared_ptr<DriverApi> driver, std::chrono::milliseconds timeout, bool allow_multicast,
+                       std::shared_ptr<CudaApi> cuda)
     : store_(std::move(store)), rank_(rank), nranks_(nranks), device_(device_index), drv_(std::move(driver)),
-      timeout_(timeout), allow_mc_(allow_multicast) {
+      cuda_(cuda ? std::move(cuda) : CudaApi::real()), timeout_(timeout), allow_mc_(allow_multicast) {
   decide_mode();
 }
 
@@ -399,11 +400,11 @@ std::shared_ptr<SymmSegment> SymmMemory::allocate(size_t bytes, bool want_multic
   seg->mode = mode_;
   seg->bytes = round_up(std::max<size_t>(bytes, 1), gran_);
   seg->cu_device = cu_dev_;
-  B200C_CUDA_CHECK(cudaSetDevice(device_));
+  B200C_CUDA_CHECK(cuda_->setDevice(device_));
   if (mode_ == SymmMode::LOCAL) {
     void* p = nullptr;
-    B200C_CUDA_CHECK(cudaMalloc(&p, seg->bytes));
-    B200C_CUDA_CHECK(cudaMemset(p, 0, seg->bytes));
+    B200C_CUDA_CHECK(cuda_->mallocDevice(&p, seg->bytes));
+    B200C_CUDA_CHECK(cuda_->memsetDevice(p, 0, seg->bytes));
     seg->peer_ptrs = {static_cast<char*>(p)};
   } else if (mode_ == SymmMode::VMM_FD) {
     CUmemAllocationProp prop{};
@@ -414,14 +415,14 @@ std::shared_ptr<SymmSegment> SymmMemory::allocate(size_t bytes, bool want_multic
     CUmemGenericAllocationHandle h = 0;
     B200C_CU_CHECK(drv_, drv_->memCreate(&h, seg->bytes, &prop));
     map_vmm(*seg, h, seq);
-    B200C_CUDA_CHECK(cudaMemset(seg->local(), 0, seg->bytes));
+    B200C_CUDA_CHECK(cuda_->memsetDevice(seg->local(), 0, seg->bytes));
   } else {
     void* p = nullptr;
     B200C_CUDA_CHECK(cudaMalloc(&p, seg->bytes));
     B200C_CUDA_CHECK(cudaMemset(p, 0, seg->bytes));
     exchange_ipc(*seg, p, 0, seq);
   }
-  B200C_CUDA_CHECK(cudaDeviceSynchronize());
+  B200C_CUDA_CHECK(cuda_->deviceSynchronize());
   barrier("alloc/" + std::to_string(seq));  // zero-fill is complete everywhere
   if (want_multicast && mc_ok_ && mode_ == SymmMode::VMM_FD) {
     try_multicast(*seg, seq);
@@ -561,7 +562,7 @@ void SymmMemory::release(const std::shared_ptr<SymmSegment>& seg) {
     }
     if (seg->owns_local) cudaFree(seg->local());
   } else if (seg->owns_local && !seg->peer_ptrs.empty()) {
-    cudaFree(seg->peer_ptrs[0]);
+    cuda_->freeDevice(seg->peer_ptrs[0]);
   }
   seg->peer_ptrs.clear();
   seg->handles.clear();

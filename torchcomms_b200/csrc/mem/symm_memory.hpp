@@ -72,7 +72,8 @@ class FdChannel {
 class SymmMemory {
  public:
   SymmMemory(c10::intrusive_ptr<c10d::Store> store, int rank, int nranks, int device_index,
-             std::shared_ptr<DriverApi> driver, std::chrono::milliseconds timeout, bool allow_multicast);
+             std::shared_ptr<DriverApi> driver, std::chrono::milliseconds timeout, bool allow_multicast,
+             std::shared_ptr<CudaApi> cuda = nullptr);
   ~SymmMemory();
 
   // Collective over the communicator. Memory is zero-filled.
@@ -101,6 +102,7 @@ class SymmMemory {
   c10::intrusive_ptr<c10d::Store> store_;
   int rank_, nranks_, device_;
   std::shared_ptr<DriverApi> drv_;
+  std::shared_ptr<CudaApi> cuda_;
   std::chrono::milliseconds timeout_;
   bool allow_mc_;
   SymmMode mode_ = SymmMode::LOCAL;

@@ -479,4 +479,5 @@ PYBIND11_MODULE(_comms, m) {
   b200c::bind_tp(m);
   b200c::bind_transport(m);
   b200c::bind_arnorm(m);
+  b200c::bind_fakes(m);
 }

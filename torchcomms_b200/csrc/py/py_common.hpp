@@ -69,6 +69,7 @@ void bind_ep(py::module_& m);
 void bind_tp(py::module_& m);
 void bind_transport(py::module_& m);
 void bind_arnorm(py::module_& m);
+void bind_fakes(py::module_& m);
 
 // Converts a C++ hook record into the typed Python view; installed from
 // Python (`_set_hook_arg_converters`).

@@ -528,6 +528,30 @@ void bind_cuda_backend(py::module_& m) {
       .def("status", &EmuWorld::status)
       .def("clear_status", &EmuWorld::clear_status);
 
+  // What ncclCommInitRankConfig would be given for these hints: {field: value} of the fields that are set.
+  m.def("_nccl_config_from_hints", [](const Hints& h, const std::string& comm_name) {
+    const NcclConfig c = CudaBackend::nccl_config_from_hints(h, comm_name);
+    std::map<std::string, std::string> out;
+    auto put = [&out](const char* k, int v) {
+      if (v != NcclConfig::kUnset) out[k] = std::to_string(v);
+    };
+    put("blocking", c.blocking);
+    put("cgaClusterSize", c.cgaClusterSize);
+    put("minCTAs", c.minCTAs);
+    put("maxCTAs", c.maxCTAs);
+    put("splitShare", c.splitShare);
+    put("trafficClass", c.trafficClass);
+    put("collnetEnable", c.collnetEnable);
+    put("CTAPolicy", c.CTAPolicy);
+    put("shrinkShare", c.shrinkShare);
+    put("nvlsCTAs", c.nvlsCTAs);
+    put("nChannelsPerNetPeer", c.nChannelsPerNetPeer);
+    put("nvlinkCentricSched", c.nvlinkCentricSched);
+    if (!c.netName.empty()) out["netName"] = c.netName;
+    if (!c.commName.empty()) out["commName"] = c.commName;
+    return out;
+  });
+
   m.def("_symm_allocator_symbols", []() { return std::make_pair(std::string("b200c_symm_alloc"), std::string("b200c_symm_free")); });
   m.def("_exportable_allocations", []() { return ExportableRegistry::get().live(); });
 }

@@ -200,7 +200,7 @@ class EpBuffer {
     off_w_ = take(R * topk * 4);
     off_count_ = take(static_cast<size_t>(nranks) * nranks * 8);
     off_combine_ = take(R * hidden * 2);
-    off_comb_recv_ = take(R * hidden * 2);  // [max_tokens, nranks, hidden]
+    off_comb_recv_ = off_combine_;  // the pull combine needs no return buffer
     total_ = off;
   }
   void fill(EpDev& e, int rank, const std::vector<char*>& bases) {

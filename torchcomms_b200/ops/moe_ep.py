@@ -13,9 +13,10 @@ with the host: the number of received rows is a device tensor.
 Parity: ``comms/prims/collectives/link_ep/link_ep/buffer.py:76-660`` (Buffer,
 get_dispatch_layout, dispatch, combine).  Differences by design: block-scaled
 fp8 quantisation and the token permutation are fused into the dispatch
-kernel, receive counts stay on the device, and combine pushes every expert
-output straight into a per-(token, rank) slot of the token's owner, which then
-sums its slots locally with the weights applied (no ring FIFOs, one barrier).
+kernel, receive counts stay on the device, and combine is a pull: the token's
+owner reads the expert outputs of every rank the token went to straight out of
+that rank's ``combine_input`` and sums them with the weights applied (no ring
+FIFOs, nothing staged, one pass over NVLink).
 """
 from __future__ import annotations
 
