@@ -117,6 +117,26 @@ def _battery(rank, world, backend_name="b200"):
     assert torch.equal(b, torch.full((100_000,), float(root + 1), device=dev))
     t = ones(1000); comm.reduce(t, 0, tc.ReduceOp.SUM, False)
     assert torch.equal(t, torch.full((1000,), float(tri if rank == 0 else rank + 1), device=dev))
+    # bandwidth-class reduce: reduce-scatter + gather to the root; non-root inputs stay untouched
+    n_big = world * 8 * 40_000
+    t = ones(n_big); comm.reduce(t, root, tc.ReduceOp.SUM, False)
+    torch.cuda.synchronize()
+    assert torch.equal(t, torch.full((n_big,), float(tri if rank == root else rank + 1), device=dev))
+    t = ones(n_big, torch.bfloat16); comm.reduce(t, 0, tc.ReduceOp.AVG, True).wait()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(t.float(), torch.full((n_big,), tri / world if rank == 0 else float(rank + 1), device=dev),
+                               rtol=1e-2, atol=1e-2)
+    # uneven reduce-scatter with sizeable shares (padded reduce-scatter) and with one dominating share (all-reduce)
+    shares = [10_000 + 7 * r for r in range(world)]
+    out = torch.empty(shares[rank], device=dev)
+    comm.reduce_scatter_v(out, [ones(s) for s in shares], tc.ReduceOp.SUM, False)
+    torch.cuda.synchronize()
+    assert torch.equal(out, torch.full((shares[rank],), float(tri), device=dev))
+    shares = [50_000 if r == 0 else 3 for r in range(world)]
+    out = torch.empty(shares[rank], device=dev)
+    comm.reduce_scatter_v(out, [ones(s) for s in shares], tc.ReduceOp.SUM, True).wait()
+    torch.cuda.synchronize()
+    assert torch.equal(out, torch.full((shares[rank],), float(tri), device=dev))
     got = torch.empty(5, device=dev)
     comm.scatter(got, [torch.full((5,), float(r), device=dev) for r in range(world)] if rank == root else [], root, False)
     assert torch.equal(got, torch.full((5,), float(rank), device=dev))

@@ -1224,6 +1224,11 @@ WorkPtr CudaBackend::all_reduce(at::Tensor& t, const ReduceOp& op, bool async_op
              }, kChanMain, true);
 }
 
+static WorkPtr exchange(CudaBackend* self, const char* what, at::Tensor in, at::Tensor out,
+                        std::vector<std::pair<size_t, size_t>> send, std::vector<std::pair<size_t, size_t>> recv,
+                        bool async_op, const OpOptions& o, std::vector<at::Tensor> keep,
+                        std::function<void(cudaStream_t)> after = nullptr, size_t known_max = 0);
+
 WorkPtr CudaBackend::reduce(const at::Tensor& t, int root, const ReduceOp& op, bool async_op, const OpOptions& o) {
   check_tensor(t, device_, "reduce", cuda_->is_real());
   if (t.numel() == 0) return c10::make_intrusive<CompletedWork>();
@@ -1244,6 +1249,26 @@ WorkPtr CudaBackend::reduce(const at::Tensor& t, int root, const ReduceOp& op, b
     });
   }
   TORCH_CHECK(kernels_can_reduce(t.scalar_type(), op), "reduce: unsupported dtype / reduction for the CUDA backend");
+  {
+    // Bandwidth class: reduce-scatter (every rank reduces 1/size of the data),
+    // then the root collects the slices. Half the traffic of an all-reduce,
+    // and nobody but the root receives the result.
+    const int64_t pack = std::max<int64_t>(1, 16 / static_cast<int64_t>(t.element_size()));
+    if (size_ > 1 && t.nbytes() >= (1u << 20) && t.numel() % (static_cast<int64_t>(size_) * pack) == 0) {
+      const int64_t slice = t.numel() / size_;
+      const size_t slice_bytes = static_cast<size_t>(slice) * t.element_size();
+      at::Tensor part = at::empty({slice}, t.options());
+      at::Tensor flat = t.reshape({-1});
+      reduce_scatter_single(part, flat, op, async_op, o);
+      std::vector<std::pair<size_t, size_t>> send(size_, {0, 0}), recv(size_, {0, 0});
+      send[root] = {0, slice_bytes};
+      at::Tensor out = rank_ == root ? flat : at::empty({16}, t.options().dtype(at::kByte));
+      if (rank_ == root) {
+        for (int p = 0; p < size_; ++p) recv[p] = {static_cast<size_t>(p) * slice_bytes, slice_bytes};
+      }
+      return exchange(this, "reduce/scatter+gather", part, out, send, recv, async_op, o, {part, out});
+    }
+  }
   // All-reduce into the tensor on the root and into scratch elsewhere, so that
   // non-root inputs stay untouched.
   DType dt;
@@ -1371,7 +1396,7 @@ WorkPtr CudaBackend::all_gather(const std::vector<at::Tensor>& outs, const at::T
 static WorkPtr exchange(CudaBackend* self, const char* what, at::Tensor in, at::Tensor out,
                         std::vector<std::pair<size_t, size_t>> send, std::vector<std::pair<size_t, size_t>> recv,
                         bool async_op, const OpOptions& o, std::vector<at::Tensor> keep,
-                        std::function<void(cudaStream_t)> after = nullptr, size_t known_max = 0) {
+                        std::function<void(cudaStream_t)> after, size_t known_max) {
   const int n = self->size();
   LaunchShape shape;
   if (known_max != 0) {
@@ -1587,11 +1612,38 @@ WorkPtr CudaBackend::reduce_scatter_v(at::Tensor& out, const std::vector<at::Ten
   TORCH_CHECK(static_cast<int>(ins.size()) == size_, "reduce_scatter_v: need size() input tensors");
   check_tensor(out, device_, "reduce_scatter_v", cuda_->is_real());
   TORCH_CHECK(ins[rank_].numel() == out.numel(), "reduce_scatter_v: own input slot must match the output");
-  // Uneven shares: all-reduce the concatenation, keep the own share.
+  // Uneven shares. When they are not too uneven, pad every share to the
+  // largest one and reduce-scatter the padded layout: each element then crosses
+  // NVLink once, as in the even case. Otherwise (one share dominates) all-reduce
+  // the concatenation and keep the own share.
+  int64_t total = 0, max_share = 0;
+  for (int r = 0; r < size_; ++r) {
+    check_tensor(ins[r], device_, "reduce_scatter_v", cuda_->is_real());
+    TORCH_CHECK(ins[r].scalar_type() == out.scalar_type(), "reduce_scatter_v: dtype mismatch");
+    total += ins[r].numel();
+    max_share = std::max<int64_t>(max_share, ins[r].numel());
+  }
+  if (total == 0) return c10::make_intrusive<CompletedWork>();
+  const int64_t pack = std::max<int64_t>(1, 16 / static_cast<int64_t>(out.element_size()));
+  const int64_t padded = (max_share + pack - 1) / pack * pack;
+  if (padded * size_ <= 2 * total) {
+    at::Tensor flat = at::zeros({padded * size_}, out.options());
+    for (int r = 0; r < size_; ++r) {
+      if (ins[r].numel() > 0) flat.narrow(0, r * padded, ins[r].numel()).copy_(ins[r].reshape({-1}));
+    }
+    at::Tensor mine = at::empty({padded}, out.options());
+    WorkPtr w = reduce_scatter_single(mine, flat, op, async_op, o);
+    at::Tensor dst = out;
+    const int64_t len = out.numel();
+    if (len == 0) return w;
+    // The copy-out is stream-ordered behind the reduce-scatter (same channel).
+    return run("reduce_scatter_v/copy", async_op, o, {flat, mine}, [mine, dst, len](cudaStream_t s) {
+      B200C_CUDA_CHECK(cudaMemcpyAsync(dst.data_ptr(), mine.data_ptr(), len * mine.element_size(), cudaMemcpyDeviceToDevice, s));
+    });
+  }
   std::vector<at::Tensor> flat_ins;
   int64_t my_off = 0, off = 0;
   for (int r = 0; r < size_; ++r) {
-    check_tensor(ins[r], device_, "reduce_scatter_v", cuda_->is_real());
     if (r == rank_) my_off = off;
     off += ins[r].numel();
     flat_ins.push_back(ins[r].reshape({-1}));

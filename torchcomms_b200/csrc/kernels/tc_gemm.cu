@@ -97,6 +97,27 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   return v;
 }
 
+// Polls `done()` until it holds, the communicator's wait budget (wall time)
+// runs out, or the communicator has failed. False = gave up. The status word
+// lives in host memory, so it is looked at only every 200 us of waiting.
+template <typename Pred>
+__device__ __forceinline__ bool poll_until(const CommDev& c, Pred done) {
+  unsigned long long start = 0, next_check = 0;
+  for (uint32_t spins = 0;; ++spins) {
+    if (done()) return true;
+    if ((spins & 255u) == 255u) {
+      const unsigned long long now = globaltimer_ns();
+      if (start == 0) {
+        start = now;
+        next_check = now + 200000ull;
+      } else if (now >= next_check) {
+        next_check = now + 200000ull;
+        if (comm_is_dead(c) || now - start > c.timeout_ns) return false;
+      }
+    }
+  }
+}
+
 // Cross-GPU barrier executed by ONE warp (lanes < nranks signal and poll).
 __device__ __forceinline__ bool warp_rank_barrier(const CommDev& c, int row, uint32_t phase) {
   const int lane = threadIdx.x & 31;
@@ -201,14 +222,9 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm(const __grid_
             ma = &maps.a_full;
             // Rows of a peer: wait until every CTA's copy warps delivered their slice.
             const uint32_t want = (epoch + 1) * static_cast<uint32_t>(G);
-            bool ok = false;
-            for (uint32_t spin = 0; spin < (1u << 23); ++spin) {
-              if (static_cast<int32_t>(ld_acquire_gpu(&p.ctrl[kCtrlTiles + ord]) - want) >= 0) {
-                ok = true;
-                break;
-              }
-              if ((spin & 1023u) == 1023u && comm_is_dead(c)) break;
-            }
+            const bool ok = poll_until(c, [&]() {
+              return static_cast<int32_t>(ld_acquire_gpu(&p.ctrl[kCtrlTiles + ord]) - want) >= 0;
+            });
             if (!ok) {
               bars->failed = 1;
               break;
@@ -343,12 +359,11 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm(const __grid_
       }
       if (ct == 0) {
         bool started = false;
-        for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+        poll_until(c, [&]() {
           const uint32_t v = ld_acquire_gpu(&p.ctrl[2]);
           if (v == epoch + 1) started = true;
-          if (started || v == 0xffffffffu) break;
-          if ((spin & 1023u) == 1023u && comm_is_dead(c)) break;
-        }
+          return started || v == 0xffffffffu;
+        });
         if (!started) bars->failed = 1;
       }
       asm volatile("bar.sync 2, 128;" ::: "memory");
@@ -546,14 +561,9 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
           } else {
             ma = &maps.a_full;
             const uint32_t want = (epoch + 1) * static_cast<uint32_t>(G);
-            bool ok = false;
-            for (uint32_t spin = 0; spin < (1u << 23); ++spin) {
-              if (static_cast<int32_t>(ld_acquire_gpu(&p.ctrl[kCtrlTiles + ord]) - want) >= 0) {
-                ok = true;
-                break;
-              }
-              if ((spin & 1023u) == 1023u && comm_is_dead(c)) break;
-            }
+            const bool ok = poll_until(c, [&]() {
+              return static_cast<int32_t>(ld_acquire_gpu(&p.ctrl[kCtrlTiles + ord]) - want) >= 0;
+            });
             if (!ok) {
               bars->failed = 1;
               break;
@@ -683,12 +693,11 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
       }
       if (ct == 0) {
         bool started = false;
-        for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+        poll_until(c, [&]() {
           const uint32_t v = ld_acquire_gpu(&p.ctrl[2]);
           if (v == epoch + 1) started = true;
-          if (started || v == 0xffffffffu) break;
-          if ((spin & 1023u) == 1023u && comm_is_dead(c)) break;
-        }
+          return started || v == 0xffffffffu;
+        });
         if (!started) bars->failed = 1;
       }
       asm volatile("bar.sync 2, 128;" ::: "memory");

@@ -20,7 +20,7 @@ namespace tc {
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;                  // K of one tcgen05.mma for 16-bit inputs
-constexpr uint32_t kWaitSpins = 1u << 22;   // try_wait polls before giving up
+constexpr unsigned long long kLocalWaitNs = 60ull * 1000 * 1000 * 1000;   // wall-time bound of a CTA-local pipeline wait
 
 
 // ------------------------------------------------------- tensor maps ------
@@ -86,12 +86,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait; false = gave up.
+// Bounded wait; false = gave up. The bound is wall time, not a number of
+// polls: how long a poll takes depends on what else the SM is doing, and a
+// pipeline stage may legitimately wait while copy warps sit in their own
+// (time-bounded) wait for a slow peer. kLocalWaitNs is far above any peer-wait
+// budget, so a local wait only runs out when the pipeline is truly stuck.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kWaitSpins; ++i) {
+  unsigned long long start = 0;
+  for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (start == 0) {
+        start = now;
+      } else if (now - start > kLocalWaitNs) {
+        return false;
+      }
+    }
   }
-  return false;
 }
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

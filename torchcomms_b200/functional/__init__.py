@@ -177,6 +177,10 @@ def _impl_barrier(token: Tensor, comm: str) -> Tensor:
 
 
 def _impl_wait_tensor(input: Tensor) -> Tensor:
+    # Results of the *_start operators carry a work handle until somebody waits for them.
+    from .ext import wait_pending
+
+    wait_pending(input)
     return input.clone()
 
 
@@ -463,7 +467,20 @@ def scatter(x: Tensor, root: int, comm: Union[TorchComm, str]) -> Tensor:
     return _ops.scatter(x, root, _name(comm))
 
 
+from .async_tensor import AsyncCollectiveTensor, OnceWork, TracedWork, wrap_async  # noqa: E402
+from .ext import (  # noqa: E402
+    CompiledComm, all_gather, all_gather_single_async, all_gather_v, all_reduce_async, all_to_all, all_to_all_single_async,
+    batch_send_recv, compiled, reduce_scatter, reduce_scatter_single_async, register_window, unregister_window,
+    window_put, window_read, window_signal, window_token, window_wait_signal,
+)
+from .param_parsing import normalize_reduce_op, parse_hints, parse_timeout  # noqa: E402
+
 __all__ = [
+    "AsyncCollectiveTensor", "OnceWork", "TracedWork", "wrap_async", "CompiledComm", "compiled",
+    "all_gather", "all_gather_v", "reduce_scatter", "all_to_all", "all_reduce_async", "all_gather_single_async",
+    "reduce_scatter_single_async", "all_to_all_single_async", "batch_send_recv", "register_window", "unregister_window",
+    "window_put", "window_read", "window_signal", "window_token", "window_wait_signal",
+    "normalize_reduce_op", "parse_hints", "parse_timeout",
     "send", "recv", "gather_single", "scatter",
     "register_comm", "unregister_comm", "is_torch_compile_supported", "is_torch_compile_supported_and_enabled",
     "all_reduce", "all_reduce_", "all_gather_single", "reduce_scatter_single", "all_to_all_single", "broadcast",
