@@ -597,3 +597,51 @@ def _moe_unfused_worker(rank, world):
 
 def test_unfused_expert_parallel_moe_trains():
     run_ranks(_moe_unfused_worker, 2, timeout=120)
+
+
+def _distwrap_passthrough_worker(rank, world):
+    """use_torchcomms=False: calls go to torch.distributed, groups are still registered, and what gloo
+    lacks (all-to-all, group splitting) is built from what it has."""
+    from torchcomms_b200 import distwrap as dist
+    from torchcomms_b200.distwrap import pginfo
+
+    dist.init_process_group(backend="gloo", timeout=timedelta(seconds=60))
+    assert not dist.torchcomms_is_enabled() and dist.is_initialized()
+    world_pg = dist.GroupMember.WORLD
+    assert pginfo.pg_info_get_global_ranks(world_pg) == list(range(world))
+    assert pginfo.pg_info_get_rank_map(world_pg) == {r: r for r in range(world)}
+    assert dist.get_backend_for_device(None, "cpu") == "gloo"
+    t = torch.full((4,), float(rank + 1))
+    dist.all_reduce(t)
+    assert torch.equal(t, torch.full((4,), float(sum(range(1, world + 1)))))
+    # all-to-all on gloo: batched point to point underneath
+    outs = [torch.empty(2) for _ in range(world)]
+    dist.all_to_all(outs, [torch.full((2,), float(rank * world + d)) for d in range(world)])
+    assert [float(o[0]) for o in outs] == [float(s * world + rank) for s in range(world)]
+    out = torch.empty(world * 3)
+    w = dist.all_to_all_single(out, torch.arange(world * 3, dtype=torch.float32) + 100 * rank, async_op=True)
+    w.wait()
+    assert torch.equal(out.view(world, 3)[:, 0], torch.tensor([100.0 * s + 3 * rank for s in range(world)]))
+    # uneven splits
+    ins = [r + 1 for r in range(world)]
+    outsz = [rank + 1] * world
+    dst = torch.empty(sum(outsz))
+    src = torch.cat([torch.full((d + 1,), float(rank * 10 + d)) for d in range(world)])
+    dist.all_to_all_single(dst, src, outsz, ins)
+    assert torch.equal(dst, torch.cat([torch.full((rank + 1,), float(s * 10 + rank)) for s in range(world)]))
+    # splitting a gloo group: partitions are created with new_group, every rank takes part in each
+    halves = [[r for r in range(world) if r % 2 == 0], [r for r in range(world) if r % 2 == 1]]
+    sub = dist.split_group(split_ranks=halves, group_desc="parity")
+    mine = halves[rank % 2]
+    assert pginfo.pg_info_get_global_ranks(sub) == mine and pginfo.pg_info_get_group_desc(sub) == "parity"
+    t = torch.full((2,), float(rank + 1))
+    dist.all_reduce(t, group=sub)
+    assert torch.equal(t, torch.full((2,), float(sum(m + 1 for m in mine))))
+    g = dist.new_group(ranks=list(range(world)), backend="gloo", group_desc="again")
+    assert pginfo.pg_info_get_group_desc(g) == "again"
+    dist.destroy_process_group()
+    assert pginfo.pg_info_get(world_pg) is None
+
+
+def test_distwrap_passthrough_registry_and_fallbacks():
+    run_ranks(_distwrap_passthrough_worker, 4, timeout=180)

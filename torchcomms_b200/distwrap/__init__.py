@@ -49,15 +49,14 @@ ReduceOp = _td.ReduceOp
 _CUDA_NAMES = {"nccl", "ncclx", "b200", "cuda"}
 
 
-@dataclass
-class _PgInfo:
-    global_ranks: List[int]
-    group_desc: str
-    rank_to_group_rank: Dict[int, int]
-    data: Dict[str, Any] = field(default_factory=dict)
+from . import fallback  # noqa: E402
+from .pginfo import PgInfo as _PgInfo  # noqa: E402
+from .pginfo import _REGISTRY  # noqa: E402
+from .pginfo import (  # noqa: E402,F401
+    pg_info_assert_registered, pg_info_create, pg_info_destroy, pg_info_get, pg_info_get_data, pg_info_get_global_ranks,
+    pg_info_get_group_desc, pg_info_get_rank_map, pg_info_set_data,
+)
 
-
-_REGISTRY: Dict[Any, _PgInfo] = {}
 _enabled = False
 _split_seq = 0
 
@@ -119,6 +118,10 @@ def init_process_group(backend: Optional[str] = None, init_method: Optional[str]
         _td.init_process_group(backend=backend, init_method=init_method, timeout=timeout, world_size=world_size,
                                rank=rank, store=store, group_name=group_name, pg_options=pg_options,
                                device_id=device_id)
+        # Pass-through groups are registered too, so that rank maps, descriptions and the
+        # backend per device type can be looked up the same way in both modes.
+        info = pg_info_create(GroupMember.WORLD, list(range(_td.get_world_size())), group_name or "world")
+        info.data["device_backends"] = _parse_backend(backend or _td.get_backend())
         return
     if _enabled:
         raise RuntimeError("distwrap is already initialised")
@@ -163,6 +166,8 @@ def _forget_group(pg: Any) -> None:
 def destroy_process_group(group: Any = None) -> None:
     global _enabled
     if not _enabled:
+        for pg in ([group] if group is not None and group is not GroupMember.WORLD else list(_REGISTRY)):
+            pg_info_destroy(pg)
         _td.destroy_process_group(group)
         return
     targets = [group] if group is not None and group is not GroupMember.WORLD else list(_REGISTRY)
@@ -184,7 +189,13 @@ def new_group(*args: Any, **kwargs: Any) -> Any:
     if _enabled:
         raise AssertionError("new_group() is not available with use_torchcomms=True: use split_group() "
                              "(communicators are split from an existing one)")
-    return _td.new_group(*args, **kwargs)
+    pg = _td.new_group(*args, **kwargs)
+    ranks = kwargs.get("ranks", args[0] if args else None)
+    ranks = list(ranks) if ranks is not None else list(range(_td.get_world_size()))
+    if pg is not None and pg is not GroupMember.NON_GROUP_MEMBER and pg_info_get(pg) is None:
+        info = pg_info_create(pg, ranks, kwargs.get("group_desc"))
+        info.data["device_backends"] = _parse_backend(kwargs.get("backend") or _td.get_backend())
+    return pg
 
 
 def split_group(parent_pg: Any = None, split_ranks: Optional[Sequence[Sequence[int]]] = None,
@@ -192,7 +203,18 @@ def split_group(parent_pg: Any = None, split_ranks: Optional[Sequence[Sequence[i
     """Collective over ``parent_pg``: every member passes the same partition; returns the caller's sub-group (or None)."""
     global _split_seq
     if not _enabled:
-        return _td.split_group(parent_pg, split_ranks, timeout, pg_options, group_desc)
+        parent = parent_pg if parent_pg is not None else GroupMember.WORLD
+        me = _td.get_rank()
+        mine = next((list(r) for r in (split_ranks or []) if me in r), None)
+        try:
+            pg = _td.split_group(parent_pg, split_ranks, timeout, pg_options, group_desc)
+        except (RuntimeError, ValueError, AssertionError, NotImplementedError):
+            # The backend cannot split (gloo): build the partitions with new_group instead.
+            pg = fallback.split_group_via_new_group(parent, mine, timeout, pg_options, group_desc)
+        if pg is not None and mine is not None and pg_info_get(pg) is None:
+            info = pg_info_create(pg, mine, group_desc)
+            info.data["device_backends"] = dict(pg_info_get_data(parent, "device_backends", {}) or {})
+        return pg
     parent = _info(parent_pg)
     if not split_ranks:
         raise ValueError("split_ranks is required")
@@ -315,9 +337,30 @@ def reduce_scatter_tensor(output: torch.Tensor, input: torch.Tensor, op: Any = R
     return _ret(get_torchcomms_instance(group, input).reduce_scatter_single(output, input, _red(op), async_op), async_op)
 
 
+def get_backend_for_device(group: Any = None, device_type: str = "cpu") -> str:
+    """Name of the backend that serves tensors of ``device_type`` in ``group`` (both modes)."""
+    pg = group if group is not None else GroupMember.WORLD
+    backends = pg_info_get_data(pg, "device_backends", {}) or {}
+    if device_type in backends:
+        return backends[device_type]
+    if not _enabled:
+        return str(_td.get_backend(pg))
+    raise ValueError(f"no backend for device type '{device_type}' in this group (have {list(backends)})")
+
+
+def _lacks_all_to_all(group: Any, tensor: torch.Tensor) -> bool:
+    """Pass-through mode: gloo implements no all-to-all."""
+    try:
+        return get_backend_for_device(group, tensor.device.type) == "gloo"
+    except ValueError:
+        return False
+
+
 def all_to_all(output_tensor_list: List[torch.Tensor], input_tensor_list: List[torch.Tensor], group: Any = None,
                async_op: bool = False) -> Any:
     if not _enabled:
+        if _lacks_all_to_all(group, input_tensor_list[0]):
+            return fallback.all_to_all_via_p2p(output_tensor_list, input_tensor_list, group, async_op)
         return _td.all_to_all(output_tensor_list, input_tensor_list, group, async_op)
     comm = get_torchcomms_instance(group, input_tensor_list[0])
     return _ret(comm.all_to_all(output_tensor_list, input_tensor_list, async_op), async_op)
@@ -326,6 +369,8 @@ def all_to_all(output_tensor_list: List[torch.Tensor], input_tensor_list: List[t
 def all_to_all_single(output: torch.Tensor, input: torch.Tensor, output_split_sizes: Optional[List[int]] = None,
                       input_split_sizes: Optional[List[int]] = None, group: Any = None, async_op: bool = False) -> Any:
     if not _enabled:
+        if _lacks_all_to_all(group, input):
+            return fallback.all_to_all_single_via_p2p(output, input, output_split_sizes, input_split_sizes, group, async_op)
         return _td.all_to_all_single(output, input, output_split_sizes, input_split_sizes, group, async_op)
     comm = get_torchcomms_instance(group, input)
     if not output_split_sizes and not input_split_sizes:
