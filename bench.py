@@ -108,7 +108,10 @@ def main():
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch with torchrun for N > 1)"
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
-    comm = tc.new_comm("b200", device, name="bench")
+    # Communication kernels get a high-priority stream: their (few) blocks are placed as soon as an SM
+    # has room instead of queueing behind the GEMMs' waves.
+    comm = tc.new_comm("b200", device, name="bench",
+                       is_high_priority_stream=os.environ.get("B200COMMS_BENCH_HIGH_PRIORITY", "1") != "0")
     cfg = model_config(args.model)
     cfg.max_seq_len = max(cfg.max_seq_len, args.seq_len)
     mb, seq = args.micro_batch, args.seq_len

@@ -273,8 +273,7 @@ def _multi_rank_body(rank, world):
     comm.all_reduce(huge, tc.ReduceOp.SUM, False)
     comm.all_reduce(torch.ones(8, dtype=torch.int64), tc.ReduceOp.SUM, False)     # dtype the kernels do not cover
     c = counts()
-    assert c["all_reduce/lamport"] == 1           # latency class: flag-less kernel
-    assert c["all_reduce/oneshot"] == 1           # up to 512 KB
+    assert c["all_reduce/lamport"] == 2           # latency class (up to 512 KB): flag-less kernel
     assert c["all_reduce/twoshot"] == 1           # 4 - 64 MB: NVLS two-shot
     assert c["all_reduce/nccl"] == 2              # beyond, and integers
     # symmetric tensors take the one-pass kernels whatever the size
@@ -283,10 +282,14 @@ def _multi_rank_body(rank, world):
     out = comm.symm_empty((world * 4096,), torch.bfloat16)
     comm.all_gather_single(out, torch.ones(4096), False)                         # fused fp32 -> bf16
     comm.reduce_scatter_single(torch.empty(4096), out, tc.ReduceOp.AVG, False)   # bf16 in, fp32 out
-    comm.all_to_all_single(out, torch.ones(world * 4096, dtype=torch.bfloat16), False)
+    comm.all_to_all_single(out, torch.ones(world * 4096, dtype=torch.bfloat16), False)     # 8 KB blocks: flag-less
+    wide = comm.symm_empty((world * 1024 * 1024,), torch.float32)
+    comm.all_to_all_single(wide, torch.ones(world * 1024 * 1024), False)                   # 4 MB blocks: one-pass push
+    comm.all_gather_single(torch.empty(world * 64), torch.ones(64), False)                 # plain small tensors: flag-less too
     c = counts()
-    assert c["all_reduce/symm"] == 1 and c["all_gather/symm+cast"] == 1
-    assert c["reduce_scatter/symm"] == 1 and c["all_to_all_single/symm"] == 1
+    assert c["all_reduce/symm"] == 1 and c["all_gather/symm+cast"] == 1 and c["all_gather/lamport"] == 1
+    assert c["reduce_scatter/symm"] == 1 and c["all_to_all_single/symm"] == 1 and c["all_to_all_single/lamport"] == 1
+    comm.symm_free(wide)
     # forcing NCCL by hint
     comm.all_gather_single(torch.empty(world * 16), torch.ones(16), False, hints={"algo": "nccl"})
     assert counts()["all_gather/nccl"] == 1

@@ -132,7 +132,7 @@ def _battery(rank, world, backend_name="b200"):
     comm.reduce_scatter_v(out, [ones(s) for s in shares], tc.ReduceOp.SUM, False)
     torch.cuda.synchronize()
     assert torch.equal(out, torch.full((shares[rank],), float(tri), device=dev))
-    shares = [50_000 if r == 0 else 3 for r in range(world)]
+    shares = [50_000 if r == 0 else 3 for r in range(world)] if world > 2 else [90_000, 3]
     out = torch.empty(shares[rank], device=dev)
     comm.reduce_scatter_v(out, [ones(s) for s in shares], tc.ReduceOp.SUM, True).wait()
     torch.cuda.synchronize()

@@ -235,3 +235,51 @@ def test_lamport_all_reduce_payload_that_looks_like_the_empty_marker(dtype):
     for o in outs:
         torch.testing.assert_close(o.float(), ref, equal_nan=True, **_tol(dtype))
     assert w.status()[0] == 0
+
+
+@pytest.mark.parametrize("nranks", [1, 2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("part", [8, 1000, 20_000])
+def test_lamport_all_gather_all_to_all_reduce_scatter(nranks, dtype, part):
+    """The flag-less exchange in its three roles, several calls in a row on one world (buffers rotate)."""
+    part = part // 8 * 8 if part >= 8 else 8          # whole 16-byte vectors in both dtypes
+    w = _world(nranks)
+    for it in range(3):
+        # all-gather
+        ins = [_rand(part, dtype, 10 * it + r) for r in range(nranks)]
+        outs = [torch.zeros(nranks * part, dtype=dtype, device="cuda") for _ in range(nranks)]
+        w.exchange_lamport(0, ins, outs, 1.0)
+        torch.cuda.synchronize()
+        for o in outs:
+            assert torch.equal(o, torch.cat(ins))
+        # all-to-all, equal parts
+        ins = [_rand(nranks * part, dtype, 50 + 10 * it + r) for r in range(nranks)]
+        outs = [torch.zeros(nranks * part, dtype=dtype, device="cuda") for _ in range(nranks)]
+        w.exchange_lamport(1, ins, outs, 1.0)
+        torch.cuda.synchronize()
+        for r in range(nranks):
+            assert torch.equal(outs[r], torch.cat([ins[q][r * part:(r + 1) * part] for q in range(nranks)]))
+        # reduce-scatter with a scale
+        outs = [torch.zeros(part, dtype=dtype, device="cuda") for _ in range(nranks)]
+        w.exchange_lamport(2, ins, outs, 0.5)
+        torch.cuda.synchronize()
+        ref = torch.stack([t.float() for t in ins]).sum(0).view(nranks, part) * 0.5
+        for r in range(nranks):
+            torch.testing.assert_close(outs[r].float(), ref[r], **_tol(dtype))
+    assert w.status()[0] == 0
+
+
+def test_lamport_exchange_unaligned_views_and_marker_payload():
+    n, part = 4, 512
+    w = _world(n)
+    bases = [_rand(part + 1, torch.float32, r) for r in range(n)]
+    ins = [b[1:] for b in bases]                       # 4 bytes off a 16-byte boundary
+    for t in ins:
+        t[::5] = -0.0                                  # the "nothing here yet" word as payload
+    out_bases = [torch.zeros(n * part + 1, device="cuda") for _ in range(n)]
+    outs = [b[1:] for b in out_bases]
+    w.exchange_lamport(0, ins, outs, 1.0)
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o, torch.cat(ins))          # -0.0 == +0.0 numerically
+    assert w.status()[0] == 0

@@ -1115,6 +1115,12 @@ bool CudaBackend::symm_use_mc(int knob, bool mc_by_default, const SymmView& v, c
   return want < 0 ? mc_by_default : want != 0;
 }
 
+// Payloads the flag-less kernels may carry: a word equal to their "nothing here
+// yet" marker is delivered as +0.0, which is only harmless for these types.
+static bool lamport_dtype(at::ScalarType t) {
+  return t == at::kFloat || t == at::kHalf || t == at::kBFloat16;
+}
+
 static RedKind red_kind(const ReduceOp& op) {
   switch (op.type()) {
     case RedOpType::PRODUCT: return RedKind::PROD;
@@ -1259,7 +1265,10 @@ WorkPtr CudaBackend::reduce(const at::Tensor& t, int root, const ReduceOp& op, b
       const size_t slice_bytes = static_cast<size_t>(slice) * t.element_size();
       at::Tensor part = at::empty({slice}, t.options());
       at::Tensor flat = t.reshape({-1});
-      reduce_scatter_single(part, flat, op, async_op, o);
+      WorkPtr first = reduce_scatter_single(part, flat, op, async_op, o);
+      // The two steps may run on different channels (streams): order the
+      // caller's stream behind the first; the second then follows it.
+      if (async_op) first->wait();
       std::vector<std::pair<size_t, size_t>> send(size_, {0, 0}), recv(size_, {0, 0});
       send[root] = {0, slice_bytes};
       at::Tensor out = rank_ == root ? flat : at::empty({16}, t.options().dtype(at::kByte));
@@ -1327,6 +1336,18 @@ WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bo
   }
   const size_t bytes = in.nbytes();
   const Algo algo = algo_override(o);
+  if ((algo == Algo::AUTO || algo == Algo::KERNEL) && !cast && size_ > 1 && lamport_dtype(in.scalar_type()) &&
+      bytes % 16 == 0 && bytes <= tune_.lamport_max_bytes) {
+    // Latency class: flag-less exchange (no barrier, nothing staged), whatever memory the tensors live in.
+    const bool mc = tune_.use_multicast && dev_.mc_heap != nullptr;
+    at::Tensor i = in, ot = out;
+    bytes_issued_ += bytes;
+    return run("all_gather/lamport", async_op, o, {in}, [this, i, ot, bytes, mc](cudaStream_t s) {
+      const void* ip = i.data_ptr();
+      void* op_ = ot.data_ptr();
+      B200C_CUDA_CHECK(launch_exchange_lamport(&dev_, layout_, 0, 0, &ip, &op_, bytes, DType::F32, 1.0f, mc, s));
+    }, kChanSymAr, true);
+  }
   if (algo == Algo::AUTO || algo == Algo::KERNEL) {
     SymmView sv;
     const size_t wire = cast ? bytes / 2 : bytes;
@@ -1555,6 +1576,16 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
   }
   const float scale = red_scale(op, size_);
   const RedKind rk = red_kind(op);
+  if (algo == Algo::AUTO && rk == RedKind::SUM && size_ > 1 && din == dout && dwire == din && out.nbytes() % 16 == 0 &&
+      out.nbytes() <= tune_.lamport_max_bytes && hint_or<unsigned long long>(o.hints, "sr_seed", 0ull) == 0) {
+    at::Tensor i = in, ot = out;
+    bytes_issued_ += in.nbytes();
+    return run("reduce_scatter/lamport", async_op, o, {in}, [this, i, ot, din, scale](cudaStream_t s) {
+      const void* ip = i.data_ptr();
+      void* op_ = ot.data_ptr();
+      B200C_CUDA_CHECK(launch_exchange_lamport(&dev_, layout_, 0, 2, &ip, &op_, ot.nbytes(), din, scale, false, s));
+    }, kChanSymAr, true);
+  }
   if (algo == Algo::AUTO && rk == RedKind::SUM && dwire == din && hint_or<unsigned long long>(o.hints, "sr_seed", 0ull) == 0) {
     SymmView sv;
     const size_t pack = 16 / dtype_size(din);
@@ -1564,7 +1595,7 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
       // The input lives in symmetric memory: every rank reads its slice of
       // every copy (summed by the switch when bound to the multicast object)
       // straight into the output; scale and cast happen in registers.
-      const bool smc = symm_use_mc(tune_.symm_rs_mc, size_ >= 4, sv, o);
+      const bool smc = symm_use_mc(tune_.symm_rs_mc, false, sv, o);
       const int blocks = symm_blocks_for(smc, out.numel() / pack, o, true);
       at::Tensor i = in, ot = out;
       bytes_issued_ += in.nbytes();
@@ -1636,6 +1667,7 @@ WorkPtr CudaBackend::reduce_scatter_v(at::Tensor& out, const std::vector<at::Ten
     at::Tensor dst = out;
     const int64_t len = out.numel();
     if (len == 0) return w;
+    if (async_op) w->wait();  // the copy below may run on another channel's stream: order it behind the reduction
     // The copy-out is stream-ordered behind the reduce-scatter (same channel).
     return run("reduce_scatter_v/copy", async_op, o, {flat, mine}, [mine, dst, len](cudaStream_t s) {
       B200C_CUDA_CHECK(cudaMemcpyAsync(dst.data_ptr(), mine.data_ptr(), len * mine.element_size(), cudaMemcpyDeviceToDevice, s));
@@ -1649,7 +1681,8 @@ WorkPtr CudaBackend::reduce_scatter_v(at::Tensor& out, const std::vector<at::Ten
     flat_ins.push_back(ins[r].reshape({-1}));
   }
   at::Tensor flat = at::cat(flat_ins);
-  all_reduce(flat, op, async_op, o);
+  WorkPtr reduced = all_reduce(flat, op, async_op, o);
+  if (async_op) reduced->wait();  // the copy below may run on another channel's stream
   at::Tensor dst = out;
   const int64_t len = out.numel();
   // The copy-out is stream-ordered behind the all-reduce.
@@ -1697,6 +1730,15 @@ WorkPtr CudaBackend::all_to_all_single(at::Tensor& out, const at::Tensor& in, bo
   bytes_issued_ += in.nbytes();
   {
     const Algo forced = algo_override(o);
+    if ((forced == Algo::AUTO || forced == Algo::KERNEL) && size_ > 1 && lamport_dtype(in.scalar_type()) && blk % 16 == 0 &&
+        blk <= tune_.lamport_max_bytes) {
+      at::Tensor i = in, ot = out;
+      return run("all_to_all_single/lamport", async_op, o, {in}, [this, i, ot, blk](cudaStream_t s) {
+        const void* ip = i.data_ptr();
+        void* op_ = ot.data_ptr();
+        B200C_CUDA_CHECK(launch_exchange_lamport(&dev_, layout_, 0, 1, &ip, &op_, blk, DType::F32, 1.0f, false, s));
+      }, kChanSymAr, true);
+    }
     SymmView sv;
     if ((forced == Algo::AUTO || forced == Algo::KERNEL) && size_ > 1 && lookup_symm(out.data_ptr(), out.nbytes(), &sv)) {
       return exchange_symm(this, "all_to_all_single/symm", in, out, sv, send, recv, true, at::Tensor(), 1, async_op, o);

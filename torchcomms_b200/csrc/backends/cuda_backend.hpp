@@ -116,12 +116,13 @@ struct Tuning {
   // reduce-scatter, while for all-reduce it moves (1 + 1/nranks) S against
   // 2 (nranks-1)/nranks S and wins from 4 ranks on. By rank count: all-gather
   // uses peer stores (they stream at link rate from few SMs); reduce-scatter
-  // and all-reduce use the switch from 4 ranks on (peer loads need most of
-  // the SMs to reach link rate) and peer loads below.
+  // uses peer loads (fastest, but they need most of the SMs to reach link
+  // rate: callers that overlap it with compute ask for the switch path and a
+  // small grid by hint); all-reduce uses the switch from 4 ranks on.
   int symm_ag_mc = -1;
   int symm_rs_mc = -1;
   int symm_ar_mc = -1;
-  size_t lamport_max_bytes = 64 * 1024;    // all-reduce: flag-less kernel up to here (0 = off)
+  size_t lamport_max_bytes = 1024 * 1024;  // flag-less kernels up to this many bytes per message / per-rank part (0 = off)
   bool channel_streams = true;             // asynchronous operations of different channels get streams of their own
   bool fast_sync = true;                   // unobserved synchronous kernel operations skip the event pair
   bool use_multicast = true;

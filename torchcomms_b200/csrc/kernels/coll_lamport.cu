@@ -38,6 +38,26 @@ __device__ __forceinline__ uint4 ld16_volatile(const void* p) {
   return v;
 }
 
+// 16 bytes from / to user memory that may not be 16-byte aligned (the choice of
+// this kernel depends on sizes only, so that every rank makes the same one).
+__device__ __forceinline__ uint4 ld16_any(const char* p, bool aligned) {
+  if (aligned) return ld16(p);
+  uint4 r;
+  char* rb = reinterpret_cast<char*>(&r);
+#pragma unroll
+  for (int k = 0; k < 16; ++k) rb[k] = p[k];
+  return r;
+}
+__device__ __forceinline__ void st16_any(char* p, uint4 v, bool aligned) {
+  if (aligned) {
+    st16(p, v);
+    return;
+  }
+  const char* vb = reinterpret_cast<const char*>(&v);
+#pragma unroll
+  for (int k = 0; k < 16; ++k) p[k] = vb[k];
+}
+
 __device__ __forceinline__ uint32_t unpoison(uint32_t w) {
   return w == kLamportPoison ? 0u : w;
 }
@@ -173,6 +193,163 @@ struct ArLamport {
   }
 };
 
+// The same arrival protocol for the other small collectives. One block owns
+// 4 KB of every rank's part; what differs is what is sent where and what the
+// receiver does with its nranks slots:
+//   GATHER   every rank's part goes to everybody (multicast when available);
+//            the receiver copies slot s to part s of the output
+//   SCATTER  part p of the input goes to rank p only; the receiver copies slot
+//            s to part s of the output (all-to-all with equal parts)
+//   REDUCE   part p of the input goes to rank p only; the receiver sums its
+//            slots in fp32 (reduce-scatter)
+// Parts are whole 16-byte vectors of a floating type (a payload word equal to
+// the poison word is sent as +0.0, which would corrupt integer data).
+enum class LamportMode : int { GATHER = 0, SCATTER = 1, REDUCE = 2 };
+
+template <typename T, LamportMode M>
+struct XchgLamport {
+  struct Args {
+    const char* in;
+    char* out;
+    size_t part_bytes;   // bytes per rank part; multiple of 16
+    float scale;         // REDUCE only
+    size_t region_off;
+    int use_mc;
+  };
+  static __device__ __forceinline__ size_t slot_off(const Args& a, uint32_t buf, int slot) {
+    return a.region_off +
+        ((static_cast<size_t>(buf) * kLamportBlocks + blockIdx.x) * kMaxRanks + slot) * kLamportPiece;
+  }
+  static __device__ void run(const CommDev& c, const Args& a) {
+    constexpr int N = Pack<T>::N;
+    const size_t b0 = static_cast<size_t>(blockIdx.x) * kLamportPiece;
+    if (b0 >= a.part_bytes) return;  // same decision on every rank
+    const size_t nvec = min_sz(kLamportPiece, a.part_bytes - b0) / 16;
+    const uint32_t call = c.epochs[kFlagSetLamport * kMaxBlocks + blockIdx.x];
+    const uint32_t cur = call % 3u, prev = (call + 2u) % 3u;
+    const size_t v = threadIdx.x;
+    const bool active = v < nvec;
+    const bool in_al = (reinterpret_cast<uintptr_t>(a.in) & 15u) == 0;
+    const bool out_al = (reinterpret_cast<uintptr_t>(a.out) & 15u) == 0;
+    if (active) {
+      if (M == LamportMode::GATHER) {
+        uint4 w = ld16_any(a.in + b0 + v * 16, in_al);
+        w.x = unpoison(w.x);
+        w.y = unpoison(w.y);
+        w.z = unpoison(w.z);
+        w.w = unpoison(w.w);
+        const size_t dst = slot_off(a, cur, c.rank) + v * 16;
+        if (a.use_mc && c.mc_heap != nullptr) {
+          multimem_st16(c.mc_heap + dst, w);
+        } else {
+#pragma unroll
+          for (int i = 0; i < kMaxRanks; ++i) {
+            if (i < c.nranks) {
+              int p = c.rank + i;
+              if (p >= c.nranks) p -= c.nranks;
+              st16(c.heap[p] + dst, w);
+            }
+          }
+        }
+      } else {
+        uint4 w[kMaxRanks];
+#pragma unroll
+        for (int i = 0; i < kMaxRanks; ++i) {
+          if (i < c.nranks) {
+            int p = c.rank + i;
+            if (p >= c.nranks) p -= c.nranks;
+            w[i] = ld16_any(a.in + static_cast<size_t>(p) * a.part_bytes + b0 + v * 16, in_al);
+          }
+        }
+        const size_t dst = slot_off(a, cur, c.rank) + v * 16;
+#pragma unroll
+        for (int i = 0; i < kMaxRanks; ++i) {
+          if (i < c.nranks) {
+            int p = c.rank + i;
+            if (p >= c.nranks) p -= c.nranks;
+            uint4 x = w[i];
+            x.x = unpoison(x.x);
+            x.y = unpoison(x.y);
+            x.z = unpoison(x.z);
+            x.w = unpoison(x.w);
+            st16(c.heap[p] + dst, x);
+          }
+        }
+      }
+    }
+    {
+      const uint4 poison = make_uint4(kLamportPoison, kLamportPoison, kLamportPoison, kLamportPoison);
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s) {
+        if (s < c.nranks) st16(c.heap[c.rank] + slot_off(a, prev, s) + v * 16, poison);
+      }
+    }
+    if (active) {
+      bool ok = true;
+      unsigned long long start = 0;
+      uint32_t spins = 0;
+      uint4 got[kMaxRanks];
+      uint32_t pending = (1u << c.nranks) - 1u;
+      while (pending != 0u && ok) {
+#pragma unroll
+        for (int s = 0; s < kMaxRanks; ++s) {
+          if (s < c.nranks && (pending >> s & 1u)) {
+            const uint4 x = ld16_volatile(c.heap[c.rank] + slot_off(a, cur, s) + v * 16);
+            if (x.x != kLamportPoison && x.y != kLamportPoison && x.z != kLamportPoison && x.w != kLamportPoison) {
+              got[s] = x;
+              pending &= ~(1u << s);
+            }
+          }
+        }
+        if (pending != 0u && ++spins >= 64u) {
+          spins = 0;
+          const unsigned long long now = globaltimer_ns();
+          if (start == 0) {
+            start = now;
+          } else if (now - start > 200000ull) {
+            if (comm_is_dead(c)) {
+              ok = false;
+            } else if (now - start > c.timeout_ns) {
+              int missing = 0;
+              for (int s = 0; s < c.nranks; ++s) {
+                if (pending >> s & 1u) missing = s;
+              }
+              report_timeout(c, missing, 0x62);
+              ok = false;
+            }
+          }
+        }
+      }
+      if (ok) {
+        if (M == LamportMode::REDUCE) {
+          float acc[N];
+#pragma unroll
+          for (int k = 0; k < N; ++k) acc[k] = 0.0f;
+#pragma unroll
+          for (int s = 0; s < kMaxRanks; ++s) {
+            if (s < c.nranks) {
+              float f[N];
+              Pack<T>::unpack(got[s], f);
+#pragma unroll
+              for (int k = 0; k < N; ++k) acc[k] += f[k];
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < N; ++k) acc[k] *= a.scale;
+          st16_any(a.out + b0 + v * 16, Pack<T>::pack(acc), out_al);
+        } else {
+#pragma unroll
+          for (int s = 0; s < kMaxRanks; ++s) {
+            if (s < c.nranks) st16_any(a.out + static_cast<size_t>(s) * a.part_bytes + b0 + v * 16, got[s], out_al);
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) c.epochs[kFlagSetLamport * kMaxBlocks + blockIdx.x] = call + 1u;
+  }
+};
+
 __global__ void k_fill_u32(uint32_t* p, size_t words, uint32_t value) {
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < words;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -210,6 +387,39 @@ cudaError_t launch_all_reduce_lamport(const CommDev* comms, const HeapLayout& la
     case DType::F32: return go(float{});
     case DType::F16: return go(__half{});
     case DType::BF16: return go(__nv_bfloat16{});
+  }
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_exchange_lamport(const CommDev* comms, const HeapLayout& lay, int emu_ranks, int mode,
+                                    const void* const* in, void* const* out, size_t part_bytes, DType dtype, float scale,
+                                    bool use_mc, cudaStream_t stream) {
+  using namespace coll;
+  const int n = emu_ranks > 0 ? emu_ranks : 1;
+  if (lay.lamport_bytes < kLamportBytes) return cudaErrorInvalidValue;
+  if (part_bytes == 0 || part_bytes % 16 != 0 || part_bytes > static_cast<size_t>(kLamportBlocks) * kLamportPiece) {
+    return cudaErrorInvalidValue;
+  }
+  const int blocks = static_cast<int>((part_bytes + kLamportPiece - 1) / kLamportPiece);
+  auto go = [&](auto tag, auto mode_tag) {
+    using T = decltype(tag);
+    using Op = XchgLamport<T, decltype(mode_tag)::value>;
+    std::vector<typename Op::Args> args(n);
+    for (int i = 0; i < n; ++i) {
+      args[i] = {static_cast<const char*>(in[i]), static_cast<char*>(out[i]), part_bytes, scale, lay.lamport_off, use_mc ? 1 : 0};
+    }
+    return launch_op<Op>(comms, emu_ranks, args.data(), blocks, kLamportThreads, stream, true);
+  };
+  using G = std::integral_constant<LamportMode, LamportMode::GATHER>;
+  using S = std::integral_constant<LamportMode, LamportMode::SCATTER>;
+  using R = std::integral_constant<LamportMode, LamportMode::REDUCE>;
+  if (mode == 0) return go(float{}, G{});
+  if (mode == 1) return go(float{}, S{});
+  if (mode != 2) return cudaErrorInvalidValue;
+  switch (dtype) {
+    case DType::F32: return go(float{}, R{});
+    case DType::F16: return go(__half{}, R{});
+    case DType::BF16: return go(__nv_bfloat16{}, R{});
   }
   return cudaErrorInvalidValue;
 }

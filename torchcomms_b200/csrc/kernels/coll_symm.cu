@@ -434,15 +434,37 @@ struct SymA2a {
       s_slen[p] = slen;
       s_doff[p] = 0;
       if (a.exchange) {
-        // Tell rank p how many bytes it gets from here. The flag store of the
-        // barrier below publishes this together with everything else.
+        // The flag store of the barrier below publishes this together with everything else.
         unsigned long long* meta_p = reinterpret_cast<unsigned long long*>(c.heap[p] + a.meta_off) +
             (static_cast<size_t>(blockIdx.x) * kMaxRanks + c.rank) * 2;
-        meta_p[0] = slen;
+        if (dev) {
+          // Device counts: tell rank p how many bytes it gets from here; it answers with an offset.
+          meta_p[0] = slen;
+        } else {
+          // Host splits: this rank already knows where p's block goes in its
+          // output and how much room it has. Tell p; no second round is needed.
+          unsigned long long roff = a.recv_off[p], cap = a.recv_len[p];
+          if (roff + cap > a.out_bytes) {
+            c.status[0] = c.status[0] | kStatusBadArg;
+            cap = roff < a.out_bytes ? a.out_bytes - roff : 0;
+          }
+          meta_p[0] = roff;
+          meta_p[1] = cap;
+        }
       }
     }
     bool ok = block_barrier(c, kFlagSetSymA2a, ep, 0x47);
-    if (ok && a.exchange) {
+    if (ok && a.exchange && !dev) {
+      if (threadIdx.x < c.nranks) {
+        const int p = threadIdx.x;
+        s_doff[p] = meta_mine[p * 2];
+        const unsigned long long cap = meta_mine[p * 2 + 1];
+        if (s_slen[p] > cap) {  // sender and receiver disagree about the split sizes
+          c.status[0] = c.status[0] | kStatusBadArg;
+          s_slen[p] = cap;
+        }
+      }
+    } else if (ok && a.exchange) {
       // Second round: now that every sender's length is known, lay the
       // incoming blocks out (host-given offsets, or back to back for device
       // counts), clamp them to the output, and tell each sender where to put

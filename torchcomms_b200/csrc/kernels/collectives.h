@@ -132,7 +132,7 @@ cudaError_t launch_symm_all_to_all(const CommDev* comms, const HeapLayout& lay, 
                                    int blocks, cudaStream_t stream);
 
 // ---- flag-less small all-reduce (coll_lamport.cu) -----------------------------
-constexpr int kLamportBlocks = 32;          // pieces per call
+constexpr int kLamportBlocks = 256;         // pieces per call
 constexpr size_t kLamportPiece = 4 * 1024;  // payload bytes per piece and rank (one 16-byte vector per thread)
 constexpr size_t kLamportBytes = 3ull * kLamportBlocks * kMaxRanks * kLamportPiece;
 constexpr unsigned kLamportPoison = 0x80000000u;  // -0.0f: "nothing arrived yet"
@@ -142,6 +142,14 @@ cudaError_t launch_lamport_init(char* region, cudaStream_t stream);
 cudaError_t launch_all_reduce_lamport(const CommDev* comms, const HeapLayout& lay, int emu_ranks,
                                       const void* const* in, void* const* out, size_t count, DType dtype,
                                       float scale, bool use_mc, cudaStream_t stream);
+
+// The same flag-less protocol for small all-gather (mode 0: out = nranks parts, one from each
+// rank), all-to-all with equal parts (mode 1) and reduce-scatter (mode 2: out = scale * sum of
+// the parts addressed to this rank). `part_bytes` per rank: a multiple of 16, at most
+// kLamportBlocks * kLamportPiece; pointers 16-byte aligned; floating-point payloads only.
+cudaError_t launch_exchange_lamport(const CommDev* comms, const HeapLayout& lay, int emu_ranks, int mode,
+                                    const void* const* in, void* const* out, size_t part_bytes, DType dtype, float scale,
+                                    bool use_mc, cudaStream_t stream);
 
 // All-to-all with per-peer byte counts. send_off/send_len/recv_off/recv_len
 // are arrays of nranks entries per rank (emu: emu_ranks x nranks, row-major).

@@ -37,9 +37,19 @@ cudaError_t scratch_for_current_device(float** out) {
   return cudaSuccess;
 }
 
-bool aligned16(const void* p) {
-  return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+bool aligned_to(const void* p, uintptr_t bytes) {
+  return (reinterpret_cast<uintptr_t>(p) & (bytes - 1)) == 0;
 }
+
+bool aligned16(const void* p) {
+  return aligned_to(p, 16);
+}
+
+// The scratch must hold one row per block of the widest launch (two blocks on
+// each of the 148 SMs) and one row is as wide as the norm kernels reach
+// (256 threads x 4 vectors x 8 bf16).
+static_assert(B200C_NOALLOC_MAX_BLOCKS >= 2 * 148, "scratch rows: one per block of the first kernel");
+static_assert(B200C_NOALLOC_MAX_COLS == 256 * 4 * 8, "scratch width: the widest row the norm kernels take");
 
 } // namespace
 
@@ -53,6 +63,7 @@ extern "C" __attribute__((visibility("default"))) int b200c_rmsnorm_bwd_noalloc(
   if (rows < 1 || cols < 8 || cols % 8 != 0) return B200C_NOALLOC_BAD_ARG;
   if (cols > B200C_NOALLOC_MAX_COLS) return B200C_NOALLOC_TOO_LARGE;
   if (!aligned16(dy) || !aligned16(x) || !aligned16(w) || !aligned16(dx)) return B200C_NOALLOC_BAD_ARG;
+  if (!aligned_to(rstd, sizeof(float)) || !aligned_to(dw, sizeof(__nv_bfloat16))) return B200C_NOALLOC_BAD_ARG;
   float* partials = nullptr;
   cudaError_t e = scratch_for_current_device(&partials);
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -77,7 +88,8 @@ extern "C" __attribute__((visibility("default"))) const char* b200c_noalloc_stre
     case B200C_NOALLOC_TOO_LARGE:
       return "shape exceeds the fixed scratch: cols must be <= 8192 (B200C_NOALLOC_MAX_COLS)";
     case B200C_NOALLOC_BAD_ARG:
-      return "bad argument: pointers must be non-null and 16-byte aligned, rows >= 1, cols a positive multiple of 8";
+      return "bad argument: pointers must be non-null, dy/x/w/dx 16-byte aligned, rstd and dw aligned to their "
+             "element, rows >= 1, cols a positive multiple of 8";
     default:
       return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown code";
   }

@@ -38,8 +38,11 @@ extern "C" {
 // Any positive value is a cudaError_t from the set-up or a launch.
 
 // dy, x, dx: bf16 [rows, cols]; w, dw: bf16 [cols]; rstd: fp32 [rows] (from
-// the forward pass). All device pointers, 16-byte aligned. `stream` is a
-// cudaStream_t (null = the default stream). Uses the current device.
+// the forward pass). All device pointers. dy, x, w and dx are read and written
+// 16 bytes at a time and must be 16-byte aligned; rstd (4 bytes) and dw
+// (2 bytes) need only the alignment of their element type. Each of these is
+// checked before anything is launched. `stream` is a cudaStream_t (null = the
+// default stream). Uses the current device.
 int b200c_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx, void* dw,
                               int rows, int cols, void* stream);
 

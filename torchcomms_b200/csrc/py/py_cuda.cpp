@@ -304,6 +304,20 @@ class EmuWorld {
     B200C_CUDA_CHECK(launch_all_reduce_lamport(comms_.data(), lay_, n_, ip.data(), op.data(), ins[0].numel(), dtype_of(ins[0]),
                                                static_cast<float>(scale), false, stream()));
   }
+  // mode 0: all-gather, 1: all-to-all with equal parts, 2: reduce-scatter (scaled sum)
+  void exchange_lamport(int mode, std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, double scale) {
+    check(ins);
+    check(outs);
+    std::vector<const void*> ip(n_);
+    std::vector<void*> op(n_);
+    for (int r = 0; r < n_; ++r) {
+      ip[r] = ins[r].data_ptr();
+      op[r] = outs[r].data_ptr();
+    }
+    const size_t part = mode == 0 ? ins[0].nbytes() : ins[0].nbytes() / n_;
+    B200C_CUDA_CHECK(launch_exchange_lamport(comms_.data(), lay_, n_, mode, ip.data(), op.data(), part, dtype_of(ins[0]),
+                                             static_cast<float>(scale), false, stream()));
+  }
   void barrier() { B200C_CUDA_CHECK(launch_barrier(comms_.data(), n_, stream())); }
   // Runs the kernel whose wait can never be satisfied; returns the status words.
   std::vector<uint32_t> wait_unset_flag() {
@@ -521,6 +535,7 @@ void bind_cuda_backend(py::module_& m) {
       .def("symm_all_reduce", &EmuWorld::symm_all_reduce)
       .def("symm_all_to_all", &EmuWorld::symm_all_to_all)
       .def("all_reduce_lamport", &EmuWorld::all_reduce_lamport)
+      .def("exchange_lamport", &EmuWorld::exchange_lamport)
       .def("broadcast", &EmuWorld::broadcast)
       .def("barrier", &EmuWorld::barrier)
       .def("wait_unset_flag", &EmuWorld::wait_unset_flag)
