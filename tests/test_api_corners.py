@@ -308,3 +308,21 @@ def _variants_worker(rank, world):
 
 def test_operation_variants_sync_async_dropped_and_deleted_inputs():
     run_ranks(_variants_worker, 3, timeout=120)
+
+
+def _matrix_worker(rank, world):
+    from datetime import timedelta
+
+    import torch
+    import torchcomms_b200 as tc
+    from tests.variant_matrix import VARIANTS_CPU, run_matrix
+
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="matrix", timeout=timedelta(seconds=60))
+    ran = run_matrix(comm, tc, torch.device("cpu"), VARIANTS_CPU)
+    assert ran == 16 * len(VARIANTS_CPU), ran
+    comm.finalize()
+
+
+def test_every_operation_in_every_calling_variant_on_gloo():
+    """16 operations x (sync, sync without the work, async, async with the work dropped, inputs deleted)."""
+    run_ranks(_matrix_worker, 3, timeout=180)

@@ -239,6 +239,30 @@ def test_cuda_backend_battery_without_multicast():
     run_ranks(_battery, 2, timeout=240, extra_env={"B200COMMS_NVLS": "0", "NCCL_NVLS_ENABLE": "0", "B200COMMS_AUTO_NCCL": "0"})
 
 
+def _variant_matrix(rank, world):
+    from datetime import timedelta
+
+    import torchcomms_b200 as tc
+    from tests.variant_matrix import VARIANTS_GPU, run_matrix
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    comm = tc.new_comm("b200", dev, name="matrix", timeout=timedelta(seconds=60), abort_process_on_timeout_or_error=False)
+    for dtype in (torch.float32, torch.bfloat16):
+        ran = run_matrix(comm, tc, dev, VARIANTS_GPU, dtype=dtype)
+        assert ran == 16 * len(VARIANTS_GPU) - 1, ran     # no graph variant for the point-to-point batch
+    torch.cuda.synchronize()
+    comm.finalize()
+
+
+def test_every_operation_in_every_calling_variant():
+    """16 operations x (sync, sync without the work, async, work dropped early, inputs deleted, CUDA graph)."""
+    world = _world_size()
+    if world < 2:
+        pytest.skip("needs 2 GPUs")
+    run_ranks(_variant_matrix, world, timeout=240)
+
+
 def _stalled_peer(rank, world):
     """Rank 1 never joins an all-reduce: rank 0's kernel gives up after its
     device-side wait budget and the next call raises; no GPU hangs or faults."""

@@ -45,6 +45,45 @@ def test_gemm_rs_single_rank(m, n, k):
         torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("nranks,m_local,n,k", [(2, 128, 256, 64), (2, 256, 512, 1024), (4, 128, 768, 512), (4, 384, 256, 2048)])
+def test_ag_gemm_emulated_ranks(nranks, m_local, n, k):
+    """The fused all-gather -> GEMM protocol (copy warps, arrival counters, opening and closing barrier) with
+    2 and 4 ranks on one GPU, every rank on its share of the SMs, against fp32 PyTorch."""
+    from torchcomms_b200 import _comms
+
+    world = _comms.TpEmuWorld(nranks, "ag_gemm", m_local, k, 5000.0)
+    for it in range(3):
+        xs = [_rand((m_local, k), 100 * it + r) for r in range(nranks)]
+        ws = [_rand((n, k), 100 * it + 50 + r, scale=0.05) for r in range(nranks)]
+        for r in range(nranks):
+            world.input(r).copy_(xs[r])
+        ys = world.ag_gemm(ws)
+        torch.cuda.synchronize()
+        assert world.status()[0] == 0, world.status()
+        full = torch.cat(xs).float()
+        for r in range(nranks):
+            torch.testing.assert_close(ys[r].float(), full @ ws[r].float().t(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("nranks,m,n,k_local", [(2, 256, 256, 64), (2, 512, 512, 1024), (4, 512, 768, 512), (4, 1536, 256, 1024)])
+def test_gemm_rs_emulated_ranks(nranks, m, n, k_local):
+    """The fused GEMM -> reduce-scatter protocol (partial tiles stored into the owner's staging, per-tile flags, the
+    owner's sum) with 2 and 4 ranks on one GPU, against fp32 PyTorch."""
+    from torchcomms_b200 import _comms
+
+    world = _comms.TpEmuWorld(nranks, "gemm_rs", m, n, 5000.0)
+    for it in range(3):
+        hs = [_rand((m, k_local), 200 * it + r) for r in range(nranks)]
+        ws = [_rand((n, k_local), 200 * it + 50 + r, scale=0.05) for r in range(nranks)]
+        outs = world.gemm_rs(hs, ws)
+        torch.cuda.synchronize()
+        assert world.status()[0] == 0, world.status()
+        total = sum(h.float() @ w.float().t() for h, w in zip(hs, ws))
+        rows = m // nranks
+        for r in range(nranks):
+            torch.testing.assert_close(outs[r].float(), total[r * rows : (r + 1) * rows], rtol=2e-2, atol=3e-2)
+
+
 def _tp_worker(rank, world):
     import torchcomms_b200 as tc
     from torchcomms_b200.ops.tp import AllGatherGemm, GemmReduceScatter

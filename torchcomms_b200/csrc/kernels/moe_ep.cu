@@ -208,6 +208,8 @@ struct CombineArgs {
   const float* weights;  // [num_tokens, nranks] or nullptr
   const void* bias;      // [num_tokens, hidden] bf16 or nullptr
   int num_tokens;
+  const int* send_slot;  // [num_tokens, nranks] handle of the dispatch to undo; nullptr = the last one's
+  float* topk_w_out;     // [num_tokens, topk] or nullptr
 };
 
 // Pull combine: the token's owner reads the expert output of every rank the
@@ -222,6 +224,7 @@ __device__ void ep_combine_body(const CommDev& c, const EpDev& e, const CombineA
   const int gwarp = blockIdx.x * kEpWarps + warp, nwarps = gridDim.x * kEpWarps;
   const size_t row_bytes = static_cast<size_t>(e.hidden) * 2;
   const int cap_rows = e.nranks * e.max_tokens;
+  const int* send_slot = a.send_slot != nullptr ? a.send_slot : e.send_slot;
   BlockEpoch ep;
   ep.load(c, kFlagSetEp);
   bool ok = block_barrier(c, kFlagSetEp, ep, 0x93);
@@ -230,7 +233,7 @@ __device__ void ep_combine_body(const CommDev& c, const EpDev& e, const CombineA
       int slot = -1;
       float wt = 1.0f;
       if (lane < e.nranks) {
-        slot = e.send_slot[static_cast<size_t>(t) * e.nranks + lane];
+        slot = send_slot[static_cast<size_t>(t) * e.nranks + lane];
         if (slot >= cap_rows) {  // never read through a bad index
           c.status[0] = c.status[0] | kStatusBadArg;
           slot = -1;
@@ -238,6 +241,15 @@ __device__ void ep_combine_body(const CommDev& c, const EpDev& e, const CombineA
         if (a.weights != nullptr) wt = a.weights[static_cast<size_t>(t) * e.nranks + lane];
       }
       const uint32_t have = __ballot_sync(0xffffffffu, slot >= 0);
+      if (a.topk_w_out != nullptr) {
+        // Per-expert weights travel back with the rows: entry k is non-zero on the one rank that hosts expert k.
+        float acc_w = 0.0f;
+        for (int d = 0; d < e.nranks; ++d) {
+          const int sd = __shfl_sync(0xffffffffu, slot, d);
+          if (((have >> d) & 1u) && lane < e.topk) acc_w += e.comb_topk_w[d][static_cast<size_t>(sd) * e.topk + lane];
+        }
+        if (lane < e.topk) a.topk_w_out[static_cast<size_t>(t) * e.topk + lane] = acc_w;
+      }
       // Two 16-byte columns per lane and step: up to 2 x nranks remote loads in flight per thread.
       for (int e0 = lane * 8; e0 < e.hidden; e0 += 512) {
         const bool second = e0 + 256 < e.hidden;
@@ -312,6 +324,61 @@ __global__ void __launch_bounds__(kEpThreads) k_ep_combine(CommDev c, EpDev e, C
 }
 __global__ void __launch_bounds__(kEpThreads) k_ep_combine_emu(const CommDev* cs, const EpDev* es, const CombineArgs* as) {
   ep_combine_body(cs[blockIdx.y], es[blockIdx.y], as[blockIdx.y]);
+}
+
+struct PullArgs {
+  void* out;             // [out_rows, hidden] bf16
+  const int* recv_src;   // [rows] src_rank * max_tokens + token; nullptr = the last dispatch's
+  const int* num_rows;   // device count; nullptr = the last dispatch's
+  int out_rows;
+};
+
+// Cached dispatch: the receiver copies the rows it was sent by an earlier
+// dispatch again, this time out of the sources' `stage_x` (bf16, as is). The
+// same per-block meeting before and after as in the combine.
+__device__ void ep_pull_body(const CommDev& c, const EpDev& e, const PullArgs& a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gwarp = blockIdx.x * kEpWarps + warp, nwarps = gridDim.x * kEpWarps;
+  const size_t row_bytes = static_cast<size_t>(e.hidden) * 2;
+  const int* recv_src = a.recv_src != nullptr ? a.recv_src : e.recv_src[e.rank];
+  BlockEpoch ep;
+  ep.load(c, kFlagSetEp);
+  bool ok = block_barrier(c, kFlagSetEp, ep, 0x95);
+  if (ok) {
+    int rows = a.num_rows != nullptr ? a.num_rows[0] : e.recv_info[0];
+    if (rows > a.out_rows) rows = a.out_rows;
+    for (int r = gwarp; r < rows; r += nwarps) {
+      const int src = recv_src[r];
+      const int s = src / e.max_tokens, t = src - s * e.max_tokens;
+      if (src < 0 || s >= e.nranks) {  // a handle that does not belong to this buffer: skip, never read through it
+        if (lane == 0) c.status[0] = c.status[0] | kStatusBadArg;
+        continue;
+      }
+      const char* from = e.stage_x[s] + static_cast<size_t>(t) * row_bytes;
+      char* to = static_cast<char*>(a.out) + static_cast<size_t>(r) * row_bytes;
+      for (size_t b = static_cast<size_t>(lane) * 16; b < row_bytes; b += 2048) {
+        uint4 v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (b + i * 512 < row_bytes) v[i] = ld16_stream(from + b + i * 512);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (b + i * 512 < row_bytes) st16(to + b + i * 512, v[i]);
+        }
+      }
+    }
+    // Nobody refills its staging rows while a peer still reads them.
+    ok = block_barrier(c, kFlagSetEp, ep, 0x96);
+  }
+  ep.store(c, kFlagSetEp);
+}
+
+__global__ void __launch_bounds__(kEpThreads) k_ep_pull(CommDev c, EpDev e, PullArgs a) {
+  ep_pull_body(c, e, a);
+}
+__global__ void __launch_bounds__(kEpThreads) k_ep_pull_emu(const CommDev* cs, const EpDev* es, const PullArgs* as) {
+  ep_pull_body(cs[blockIdx.y], es[blockIdx.y], as[blockIdx.y]);
 }
 
 __global__ void k_ep_layout(const int* __restrict__ topk_idx, int num_tokens, int topk, int num_experts, int nranks,
@@ -390,14 +457,30 @@ cudaError_t launch_ep_dispatch(const CommDev* comms, const EpDev* eps, int emu_r
 
 cudaError_t launch_ep_combine(const CommDev* comms, const EpDev* eps, int emu_ranks, void* const* out,
                               const float* const* weights, const void* const* bias, int num_tokens,
-                              cudaStream_t stream) {
+                              cudaStream_t stream, const int* const* send_slot, float* const* topk_w_out) {
   const EpDev& e0 = eps[0];
   if (e0.hidden % 256 != 0 || num_tokens > e0.max_tokens) return cudaErrorInvalidValue;
   const int n = emu_ranks > 0 ? emu_ranks : 1;
   std::vector<CombineArgs> args(n);
-  for (int i = 0; i < n; ++i) args[i] = {out[i], weights ? weights[i] : nullptr, bias ? bias[i] : nullptr, num_tokens};
+  for (int i = 0; i < n; ++i) {
+    args[i] = {out[i], weights ? weights[i] : nullptr, bias ? bias[i] : nullptr, num_tokens,
+               send_slot ? send_slot[i] : nullptr, topk_w_out ? topk_w_out[i] : nullptr};
+  }
   return launch_coop<CombineArgs>(reinterpret_cast<void*>(&k_ep_combine), reinterpret_cast<void*>(&k_ep_combine_emu),
                                   comms, eps, emu_ranks, args, stream);
+}
+
+cudaError_t launch_ep_pull(const CommDev* comms, const EpDev* eps, int emu_ranks, void* const* out,
+                           const int* const* recv_src, const int* const* num_rows, int out_rows, cudaStream_t stream) {
+  const EpDev& e0 = eps[0];
+  if (e0.hidden % 8 != 0 || out_rows < 0) return cudaErrorInvalidValue;
+  const int n = emu_ranks > 0 ? emu_ranks : 1;
+  std::vector<PullArgs> args(n);
+  for (int i = 0; i < n; ++i) {
+    args[i] = {out[i], recv_src ? recv_src[i] : nullptr, num_rows ? num_rows[i] : nullptr, out_rows};
+  }
+  return launch_coop<PullArgs>(reinterpret_cast<void*>(&k_ep_pull), reinterpret_cast<void*>(&k_ep_pull_emu), comms, eps,
+                               emu_ranks, args, stream);
 }
 
 cudaError_t launch_ep_layout(const int* topk_idx, int num_tokens, int topk, int num_experts, int nranks,

@@ -34,7 +34,8 @@ struct EpDev {
   float* recv_topk_w[kMaxRanks];       // [rows, topk]
   long long* count_matrix[kMaxRanks];  // [nranks, nranks]: [s][d] tokens s sends to d
   char* combine_x[kMaxRanks];          // [rows, hidden] bf16: expert outputs, row-aligned with the received rows
-  char* comb_recv[kMaxRanks];          // unused (kept for layout compatibility of the descriptor)
+  char* stage_x[kMaxRanks];            // [max_tokens, hidden] bf16: source-side rows that the receivers pull (cached dispatch)
+  float* comb_topk_w[kMaxRanks];       // [rows, topk] fp32: expert-side per-expert weights (or their gradients) that combine returns
   // Local scratch.
   int* cnt;          // [nranks]
   int* cursor;       // [nranks]
@@ -49,9 +50,18 @@ cudaError_t launch_ep_dispatch(const CommDev* comms, const EpDev* eps, int emu_r
                                const int* const* topk_idx, const float* const* topk_w, int num_tokens,
                                cudaStream_t stream);
 // out[t] = bias[t] + sum over destinations d of w[t, d] * combine_x_d[slot(t, d)]   (w, bias optional)
+// `send_slot` (optional, per rank): the handle of an earlier dispatch instead of the last one's.
+// `topk_w_out` (optional, per rank): [num_tokens, topk] fp32, the sum over destinations of comb_topk_w_d[slot(t, d)].
 cudaError_t launch_ep_combine(const CommDev* comms, const EpDev* eps, int emu_ranks, void* const* out,
                               const float* const* weights, const void* const* bias, int num_tokens,
-                              cudaStream_t stream);
+                              cudaStream_t stream, const int* const* send_slot = nullptr,
+                              float* const* topk_w_out = nullptr);
+// Cached dispatch (no quantisation, no new layout): row r of `out` (bf16 [out_rows, hidden]) is row `token` of
+// `stage_x` on rank `src_rank`, where recv_src[r] = src_rank * max_tokens + token comes from an earlier dispatch
+// (`recv_src` per rank, nullptr = the last one's). `num_rows` (device, per rank; nullptr = the last dispatch's
+// count) rows are filled, never more than `out_rows`.
+cudaError_t launch_ep_pull(const CommDev* comms, const EpDev* eps, int emu_ranks, void* const* out,
+                           const int* const* recv_src, const int* const* num_rows, int out_rows, cudaStream_t stream);
 // Layout only: tokens per rank, tokens per expert, token-in-rank mask (int32 outputs).
 cudaError_t launch_ep_layout(const int* topk_idx, int num_tokens, int topk, int num_experts, int nranks,
                              int* tokens_per_rank, int* tokens_per_expert, int* is_token_in_rank, cudaStream_t stream);

@@ -154,8 +154,10 @@ __device__ __forceinline__ TileCoord tile_at(int t, int tiles_m, int tiles_n, in
   return TileCoord{first + rem % gsz, rem / gsz};
 }
 
+// Body of the single-CTA kernels. `maps` must live in kernel-parameter,
+// constant or global memory (its address goes to TMA).
 template <TpMode MODE>
-__global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm(const __grid_constant__ TpMaps maps, CommDev c, TpParams p) {
+__device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& c, const TpParams& p) {
   using Cfg = TileCfg<kTpBN>;
   constexpr int BN = kTpBN;
   constexpr uint32_t idesc = make_idesc_bf16(kBlockM, BN);
@@ -472,6 +474,26 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm(const __grid_
       atomicExch(&p.ctrl[0], epoch + 1);
     }
   }
+}
+
+template <TpMode MODE>
+__global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm(const __grid_constant__ TpMaps maps, CommDev c, TpParams p) {
+  tp_gemm_body<MODE>(maps, c, p);
+}
+
+// Several ranks in ONE launch on one GPU (tests): blockIdx.y is the rank, each
+// rank gets gridDim.x CTAs, and the launch is cooperative so that all of them
+// are resident while they wait on one another.
+constexpr int kTpEmuRanks = 4;
+struct TpEmu {
+  TpMaps maps[kTpEmuRanks];
+  CommDev c[kTpEmuRanks];
+  TpParams p[kTpEmuRanks];
+};
+
+template <TpMode MODE>
+__global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_emu(const __grid_constant__ TpEmu e) {
+  tp_gemm_body<MODE>(e.maps[blockIdx.y], e.c[blockIdx.y], e.p[blockIdx.y]);
 }
 
 // ------------------------------------- fused kernels on CTA pairs ----------
@@ -906,18 +928,20 @@ size_t tp_ctrl_words(int m_total) {
   return static_cast<size_t>(kCtrlTiles) + static_cast<size_t>(m_total / kBlockM);
 }
 
-cudaError_t launch_allgather_gemm(const CommDev& comm, const AgGemmArgs& a, cudaStream_t stream) {
+namespace {
+
+// Tensor maps and parameters of one rank's all-gather GEMM. `pairs`: for the CTA-pair kernel.
+cudaError_t build_ag(const CommDev& comm, const AgGemmArgs& a, bool pairs, TpMaps& maps, TpParams& p) {
   const int m_total = a.m_local * comm.nranks;
   if (a.m_local <= 0 || a.m_local % kBlockM != 0 || a.n % kTpBN != 0 || a.k % kBlockK != 0) return cudaErrorInvalidValue;
   if (comm.nranks > kMaxRanks) return cudaErrorInvalidValue;
-  TpMaps maps;
   if (!make_map(&maps.a_local, a.x_shards[comm.rank], a.m_local, a.k, kBlockM) ||
       !make_map(&maps.a_full, a.x_full, m_total, a.k, kBlockM) || !make_map(&maps.b, a.w, a.n, a.k, kTpBN) ||
       !make_map(&maps.out[0], a.y, m_total, a.n, kBlockM)) {
     return cudaErrorInvalidValue;
   }
   for (int r = 1; r < kMaxRanks; ++r) maps.out[r] = maps.out[0];
-  TpParams p{};
+  p = TpParams{};
   for (int r = 0; r < comm.nranks; ++r) p.x_shards[r] = static_cast<const char*>(a.x_shards[r]);
   p.x_full = static_cast<char*>(a.x_full);
   p.ctrl = a.ctrl;
@@ -925,24 +949,21 @@ cudaError_t launch_allgather_gemm(const CommDev& comm, const AgGemmArgs& a, cuda
   p.m_local = a.m_local;
   p.n = a.n;
   p.k = a.k;
-  if (use_pairs(a.m_local)) {
+  if (pairs) {
     if (!make_map(&maps.b_half, a.w, a.n, a.k, kBlockM)) return cudaErrorInvalidValue;
     p.gm = pick_group(a.m_local / (2 * kBlockM), 2 * kBlockM, a.k, 8);
-    return tp_launch_pair<TpMode::AG_GEMM>(0, maps, comm, p, stream);
+  } else {
+    maps.b_half = maps.b;
+    p.gm = pick_group(a.m_local / kBlockM, kBlockM, a.k, 16);
   }
-  maps.b_half = maps.b;
-  p.gm = pick_group(a.m_local / kBlockM, kBlockM, a.k, 16);
-  // All CTAs take part in the copy, so the grid is the whole GPU even when
-  // there are fewer tiles than SMs.
-  return tp_launch<TpMode::AG_GEMM>(sm_count(), maps, comm, p, stream);
+  return cudaSuccess;
 }
 
-cudaError_t launch_gemm_reduce_scatter(const CommDev& comm, const GemmRsArgs& a, cudaStream_t stream) {
+cudaError_t build_rs(const CommDev& comm, const GemmRsArgs& a, bool pairs, TpMaps& maps, TpParams& p) {
   if (a.m <= 0 || a.m % (kBlockM * comm.nranks) != 0 || a.n % kTpBN != 0 || a.k_local % kBlockK != 0) {
     return cudaErrorInvalidValue;
   }
   if (comm.nranks > kMaxRanks) return cudaErrorInvalidValue;
-  TpMaps maps;
   if (!make_map(&maps.a_local, a.h, a.m, a.k_local, kBlockM) || !make_map(&maps.b, a.w, a.n, a.k_local, kTpBN)) {
     return cudaErrorInvalidValue;
   }
@@ -952,7 +973,7 @@ cudaError_t launch_gemm_reduce_scatter(const CommDev& comm, const GemmRsArgs& a,
     const void* base = r < comm.nranks ? a.partials[r] : a.partials[comm.rank];
     if (!make_map(&maps.out[r], base, a.m, a.n, kBlockM)) return cudaErrorInvalidValue;
   }
-  TpParams p{};
+  p = TpParams{};
   p.partials_local = static_cast<const char*>(a.partials[comm.rank]);
   for (int r = 0; r < comm.nranks; ++r) p.arrived[r] = a.arrived[r];
   p.out = static_cast<__nv_bfloat16*>(a.out);
@@ -961,15 +982,73 @@ cudaError_t launch_gemm_reduce_scatter(const CommDev& comm, const GemmRsArgs& a,
   p.m_local = a.m / comm.nranks;
   p.n = a.n;
   p.k = a.k_local;
-  const int tiles = (a.m / kBlockM) * (a.n / kTpBN);
-  if (use_pairs(p.m_local)) {
+  if (pairs) {
     if (!make_map(&maps.b_half, a.w, a.n, a.k_local, kBlockM)) return cudaErrorInvalidValue;
     p.gm = pick_group(p.m_local / (2 * kBlockM), 2 * kBlockM, a.k_local, 8);
-    return tp_launch_pair<TpMode::GEMM_RS>(tiles / 2, maps, comm, p, stream);
+  } else {
+    maps.b_half = maps.b;
+    p.gm = pick_group(p.m_local / kBlockM, kBlockM, a.k_local, 16);
   }
-  maps.b_half = maps.b;
-  p.gm = pick_group(p.m_local / kBlockM, kBlockM, a.k_local, 16);
+  return cudaSuccess;
+}
+
+template <TpMode MODE>
+cudaError_t tp_launch_emu(const TpEmu& e, int nranks, cudaStream_t stream) {
+  cudaError_t err = cudaFuncSetAttribute(k_tp_gemm_emu<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTpSmemBytes);
+  if (err != cudaSuccess) return err;
+  const int per_rank = sm_count() / nranks;
+  if (per_rank < 1) return cudaErrorInvalidConfiguration;
+  void* params[] = {const_cast<TpEmu*>(&e)};
+  note_kernel_launch();
+  return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(&k_tp_gemm_emu<MODE>), dim3(per_rank, nranks),
+                                     dim3(tp_threads<MODE>()), params, kTpSmemBytes, stream);
+}
+
+} // namespace
+
+cudaError_t launch_allgather_gemm(const CommDev& comm, const AgGemmArgs& a, cudaStream_t stream) {
+  TpMaps maps;
+  TpParams p;
+  const bool pairs = a.m_local > 0 && use_pairs(a.m_local);
+  cudaError_t e = build_ag(comm, a, pairs, maps, p);
+  if (e != cudaSuccess) return e;
+  if (pairs) return tp_launch_pair<TpMode::AG_GEMM>(0, maps, comm, p, stream);
+  // All CTAs take part in the copy, so the grid is the whole GPU even when
+  // there are fewer tiles than SMs.
+  return tp_launch<TpMode::AG_GEMM>(sm_count(), maps, comm, p, stream);
+}
+
+cudaError_t launch_gemm_reduce_scatter(const CommDev& comm, const GemmRsArgs& a, cudaStream_t stream) {
+  TpMaps maps;
+  TpParams p;
+  const bool pairs = a.m > 0 && comm.nranks > 0 && use_pairs(a.m / comm.nranks);
+  cudaError_t e = build_rs(comm, a, pairs, maps, p);
+  if (e != cudaSuccess) return e;
+  const int tiles = (a.m / kBlockM) * (a.n / kTpBN);
+  if (pairs) return tp_launch_pair<TpMode::GEMM_RS>(tiles / 2, maps, comm, p, stream);
   return tp_launch<TpMode::GEMM_RS>(std::min(sm_count(), tiles), maps, comm, p, stream);
+}
+
+cudaError_t launch_allgather_gemm_emu(const CommDev* comms, const AgGemmArgs* args, int nranks, cudaStream_t stream) {
+  if (nranks < 1 || nranks > kTpEmuRanks) return cudaErrorInvalidValue;
+  TpEmu e{};
+  for (int r = 0; r < nranks; ++r) {
+    e.c[r] = comms[r];
+    cudaError_t err = build_ag(comms[r], args[r], false, e.maps[r], e.p[r]);
+    if (err != cudaSuccess) return err;
+  }
+  return tp_launch_emu<TpMode::AG_GEMM>(e, nranks, stream);
+}
+
+cudaError_t launch_gemm_reduce_scatter_emu(const CommDev* comms, const GemmRsArgs* args, int nranks, cudaStream_t stream) {
+  if (nranks < 1 || nranks > kTpEmuRanks) return cudaErrorInvalidValue;
+  TpEmu e{};
+  for (int r = 0; r < nranks; ++r) {
+    e.c[r] = comms[r];
+    cudaError_t err = build_rs(comms[r], args[r], false, e.maps[r], e.p[r]);
+    if (err != cudaSuccess) return err;
+  }
+  return tp_launch_emu<TpMode::GEMM_RS>(e, nranks, stream);
 }
 
 } // namespace b200c

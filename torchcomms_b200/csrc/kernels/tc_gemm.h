@@ -69,4 +69,9 @@ cudaError_t launch_gemm_reduce_scatter(const CommDev& comm, const GemmRsArgs& ar
 
 size_t tp_ctrl_words(int m_total);
 
+// Tests: up to 4 ranks in ONE cooperative launch on the current device (the single-CTA kernels, each rank on
+// its share of the SMs). comms[r] / args[r] describe rank r; all pointers are device memory of this GPU.
+cudaError_t launch_allgather_gemm_emu(const CommDev* comms, const AgGemmArgs* args, int nranks, cudaStream_t stream);
+cudaError_t launch_gemm_reduce_scatter_emu(const CommDev* comms, const GemmRsArgs* args, int nranks, cudaStream_t stream);
+
 } // namespace b200c

@@ -117,13 +117,32 @@ class EpBuffer {
     last_tokens_ = T;
   }
 
-  void combine(std::vector<at::Tensor> out, std::vector<at::Tensor> weights, std::vector<at::Tensor> bias) {
+  // `send_slot` (optional): handles of an earlier dispatch, int32 [tokens, nranks] as `view("send_slot")` gave them.
+  // `topk_w_out` (optional): float32 [tokens, topk] outputs for the per-expert weights that travel back.
+  void combine(std::vector<at::Tensor> out, std::vector<at::Tensor> weights, std::vector<at::Tensor> bias,
+               std::vector<at::Tensor> send_slot, std::vector<at::Tensor> topk_w_out) {
     TORCH_CHECK(static_cast<int>(out.size()) == n_local_, "one output per local rank");
     const int T = static_cast<int>(out[0].size(0));
     std::vector<void*> op(n_local_);
     std::vector<const float*> wp(n_local_, nullptr);
     std::vector<const void*> bp(n_local_, nullptr);
+    std::vector<const int*> sp(n_local_, nullptr);
+    std::vector<float*> tp(n_local_, nullptr);
+    TORCH_CHECK(send_slot.empty() || static_cast<int>(send_slot.size()) == n_local_, "one handle per local rank");
+    TORCH_CHECK(topk_w_out.empty() || static_cast<int>(topk_w_out.size()) == n_local_, "one weight output per local rank");
     for (int i = 0; i < n_local_; ++i) {
+      if (!send_slot.empty()) {
+        TORCH_CHECK(send_slot[i].is_cuda() && send_slot[i].scalar_type() == at::kInt && send_slot[i].is_contiguous() &&
+                        send_slot[i].numel() >= static_cast<int64_t>(T) * nranks_,
+                    "send_slot: contiguous int32 [tokens, nranks]");
+        sp[i] = send_slot[i].data_ptr<int>();
+      }
+      if (!topk_w_out.empty()) {
+        TORCH_CHECK(topk_w_out[i].is_cuda() && topk_w_out[i].scalar_type() == at::kFloat && topk_w_out[i].is_contiguous() &&
+                        topk_w_out[i].numel() == static_cast<int64_t>(T) * topk_,
+                    "topk_w_out: contiguous float32 [tokens, topk]");
+        tp[i] = topk_w_out[i].data_ptr<float>();
+      }
       TORCH_CHECK(out[i].scalar_type() == at::kBFloat16 && out[i].is_contiguous() && out[i].size(1) == hidden_,
                   "out: contiguous bf16 [tokens, hidden]");
       op[i] = out[i].data_ptr();
@@ -140,14 +159,60 @@ class EpBuffer {
     }
     const float* const* wpp = weights.empty() ? nullptr : wp.data();
     const void* const* bpp = bias.empty() ? nullptr : bp.data();
+    const int* const* spp = send_slot.empty() ? nullptr : sp.data();
+    float* const* tpp = topk_w_out.empty() ? nullptr : tp.data();
     if (backend_) {
-      backend_->run("ep_combine/kernel", false, {}, out, [&](cudaStream_t s) {
+      std::vector<at::Tensor> keep = out;
+      keep.insert(keep.end(), send_slot.begin(), send_slot.end());
+      keep.insert(keep.end(), topk_w_out.begin(), topk_w_out.end());
+      backend_->run("ep_combine/kernel", false, {}, keep, [&](cudaStream_t s) {
         comms_[0] = backend_->comm_dev();
-        B200C_CUDA_CHECK(launch_ep_combine(comms_.data(), eps_.data(), 0, op.data(), wpp, bpp, T, s));
+        B200C_CUDA_CHECK(launch_ep_combine(comms_.data(), eps_.data(), 0, op.data(), wpp, bpp, T, s, spp, tpp));
       });
     } else {
       B200C_CUDA_CHECK(launch_ep_combine(comms_.data(), eps_.data(), n_local_, op.data(), wpp, bpp, T,
-                                         at::cuda::getCurrentCUDAStream().stream()));
+                                         at::cuda::getCurrentCUDAStream().stream(), spp, tpp));
+    }
+  }
+
+  // Cached dispatch: fills out[i] (bf16 [rows_i, hidden]) with the rows of the sources' `stage_x` named by
+  // `recv_src` (handles of an earlier dispatch; empty = the last one's) and `num_rows` (0-d int32 device tensors).
+  void pull(std::vector<at::Tensor> out, std::vector<at::Tensor> recv_src, std::vector<at::Tensor> num_rows) {
+    TORCH_CHECK(static_cast<int>(out.size()) == n_local_, "one output per local rank");
+    TORCH_CHECK(recv_src.empty() || static_cast<int>(recv_src.size()) == n_local_, "one handle per local rank");
+    TORCH_CHECK(num_rows.size() == recv_src.size(), "recv_src and num_rows go together");
+    std::vector<void*> op(n_local_);
+    std::vector<const int*> sp(n_local_, nullptr), np(n_local_, nullptr);
+    int out_rows = rows();
+    for (int i = 0; i < n_local_; ++i) {
+      TORCH_CHECK(out[i].is_cuda() && out[i].scalar_type() == at::kBFloat16 && out[i].is_contiguous() && out[i].dim() == 2 &&
+                      out[i].size(1) == hidden_,
+                  "out: contiguous bf16 [rows, hidden]");
+      out_rows = std::min<int>(out_rows, static_cast<int>(out[i].size(0)));
+      op[i] = out[i].data_ptr();
+      if (!recv_src.empty()) {
+        TORCH_CHECK(recv_src[i].is_cuda() && recv_src[i].scalar_type() == at::kInt && recv_src[i].is_contiguous() &&
+                        recv_src[i].numel() >= out[i].size(0),
+                    "recv_src: contiguous int32 with one entry per output row");
+        TORCH_CHECK(num_rows[i].is_cuda() && num_rows[i].scalar_type() == at::kInt && num_rows[i].numel() == 1,
+                    "num_rows: one int32 on the device");
+        sp[i] = recv_src[i].data_ptr<int>();
+        np[i] = num_rows[i].data_ptr<int>();
+      }
+    }
+    const int* const* spp = recv_src.empty() ? nullptr : sp.data();
+    const int* const* npp = recv_src.empty() ? nullptr : np.data();
+    if (backend_) {
+      std::vector<at::Tensor> keep = out;
+      keep.insert(keep.end(), recv_src.begin(), recv_src.end());
+      keep.insert(keep.end(), num_rows.begin(), num_rows.end());
+      backend_->run("ep_pull/kernel", false, {}, keep, [&](cudaStream_t s) {
+        comms_[0] = backend_->comm_dev();
+        B200C_CUDA_CHECK(launch_ep_pull(comms_.data(), eps_.data(), 0, op.data(), spp, npp, out_rows, s));
+      });
+    } else {
+      B200C_CUDA_CHECK(launch_ep_pull(comms_.data(), eps_.data(), n_local_, op.data(), spp, npp, out_rows,
+                                      at::cuda::getCurrentCUDAStream().stream()));
     }
   }
 
@@ -167,6 +232,8 @@ class EpBuffer {
     if (what == "recv_topk_idx") return at::from_blob(e.recv_topk_idx[r], {R, topk_}, opts.dtype(at::kInt));
     if (what == "recv_topk_weights") return at::from_blob(e.recv_topk_w[r], {R, topk_}, opts.dtype(at::kFloat));
     if (what == "combine_x") return at::from_blob(e.combine_x[r], {R, hidden_}, opts.dtype(at::kBFloat16));
+    if (what == "stage_x") return at::from_blob(e.stage_x[r], {max_tokens_, hidden_}, opts.dtype(at::kBFloat16));
+    if (what == "combine_topk_weights") return at::from_blob(e.comb_topk_w[r], {R, topk_}, opts.dtype(at::kFloat));
     if (what == "recv_info") return at::from_blob(e.recv_info, {1 + nranks_}, opts.dtype(at::kInt));
     if (what == "send_slot") return at::from_blob(e.send_slot, {max_tokens_, nranks_}, opts.dtype(at::kInt));
     TORCH_CHECK(false, "unknown view '", what, "'");
@@ -200,7 +267,8 @@ class EpBuffer {
     off_w_ = take(R * topk * 4);
     off_count_ = take(static_cast<size_t>(nranks) * nranks * 8);
     off_combine_ = take(R * hidden * 2);
-    off_comb_recv_ = off_combine_;  // the pull combine needs no return buffer
+    off_stage_ = take(static_cast<size_t>(max_tokens) * hidden * 2);
+    off_comb_w_ = take(R * topk * 4);
     total_ = off;
   }
   void fill(EpDev& e, int rank, const std::vector<char*>& bases) {
@@ -221,7 +289,8 @@ class EpBuffer {
       e.recv_topk_w[p] = reinterpret_cast<float*>(bases[p] + off_w_);
       e.count_matrix[p] = reinterpret_cast<long long*>(bases[p] + off_count_);
       e.combine_x[p] = bases[p] + off_combine_;
-      e.comb_recv[p] = bases[p] + off_comb_recv_;
+      e.stage_x[p] = bases[p] + off_stage_;
+      e.comb_topk_w[p] = reinterpret_cast<float*>(bases[p] + off_comb_w_);
     }
     auto local = [this](size_t bytes) {
       void* p = nullptr;
@@ -247,7 +316,7 @@ class EpBuffer {
   int n_local_;
   int nranks_ = 1, max_tokens_ = 0, hidden_ = 0, num_experts_ = 0, topk_ = 0;
   bool fp8_ = true;
-  size_t off_x_ = 0, off_scales_ = 0, off_src_ = 0, off_idx_ = 0, off_w_ = 0, off_count_ = 0, off_combine_ = 0, off_comb_recv_ = 0, total_ = 0;
+  size_t off_x_ = 0, off_scales_ = 0, off_src_ = 0, off_idx_ = 0, off_w_ = 0, off_count_ = 0, off_combine_ = 0, off_stage_ = 0, off_comb_w_ = 0, total_ = 0;
   std::vector<CommDev> comms_;
   std::vector<EpDev> eps_;
   std::vector<void*> local_allocs_, emu_allocs_;
@@ -273,7 +342,10 @@ void bind_ep(py::module_& m) {
          py::arg("fp8") = true, py::arg("wait_ms") = 2000.0)
       .def("dispatch", &EpBuffer::dispatch)
       .def("combine", &EpBuffer::combine, py::arg("out"), py::arg("weights") = std::vector<at::Tensor>{},
-           py::arg("bias") = std::vector<at::Tensor>{})
+           py::arg("bias") = std::vector<at::Tensor>{}, py::arg("send_slot") = std::vector<at::Tensor>{},
+           py::arg("topk_w_out") = std::vector<at::Tensor>{})
+      .def("pull", &EpBuffer::pull, py::arg("out"), py::arg("recv_src") = std::vector<at::Tensor>{},
+           py::arg("num_rows") = std::vector<at::Tensor>{})
       .def("view", &EpBuffer::view, py::arg("local_rank"), py::arg("what"))
       .def("rows", &EpBuffer::rows)
       .def("status", &EpBuffer::status);

@@ -185,9 +185,153 @@ class TpLayer {
   CommDev solo_;
 };
 
+// Up to four ranks of one layer shape on ONE device (kernel tests): every
+// rank's buffers are ordinary device memory of this GPU, the kernels of all
+// ranks run as one cooperative launch and talk through the same flags and
+// staging areas as separate GPUs would.
+class TpEmuWorld {
+ public:
+  TpEmuWorld(int nranks, const std::string& kind, int rows, int cols, double wait_ms)
+      : ag_(kind == "ag_gemm"), nranks_(nranks), rows_(rows), cols_(cols) {
+    TORCH_CHECK(kind == "ag_gemm" || kind == "gemm_rs", "kind must be 'ag_gemm' or 'gemm_rs'");
+    TORCH_CHECK(nranks >= 1 && nranks <= 4, "1 to 4 emulated ranks");
+    if (ag_) {
+      TORCH_CHECK(rows % 128 == 0 && cols % 64 == 0, "ag_gemm: m_local % 128 == 0 and k % 64 == 0 required");
+      data_bytes_ = align256(static_cast<size_t>(rows) * cols * 2);
+      flag_bytes_ = 0;
+    } else {
+      TORCH_CHECK(rows % (128 * nranks) == 0 && cols % 256 == 0, "gemm_rs: m % (128*nranks) == 0 and n % 256 == 0 required");
+      data_bytes_ = align256(static_cast<size_t>(rows) * cols * 2);
+      flag_bytes_ = align256(static_cast<size_t>(rows / nranks / 128) * (cols / 256) * nranks * 4);
+    }
+    auto zeroed = [this](size_t bytes) {
+      void* p = nullptr;
+      B200C_CUDA_CHECK(cudaMalloc(&p, bytes));
+      B200C_CUDA_CHECK(cudaMemset(p, 0, bytes));
+      allocs_.push_back(p);
+      return p;
+    };
+    B200C_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&status_host_), 64, cudaHostAllocMapped));
+    std::memset(status_host_, 0, 64);
+    uint32_t* sdev = nullptr;
+    B200C_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&sdev), status_host_, 0));
+    const size_t fb = static_cast<size_t>(kFlagSets) * kMaxBlocks * kMaxRanks * sizeof(uint32_t);
+    std::vector<uint32_t*> flags(nranks);
+    for (int r = 0; r < nranks; ++r) {
+      bases_.push_back(static_cast<char*>(zeroed(data_bytes_ + flag_bytes_)));
+      flags[r] = static_cast<uint32_t*>(zeroed(fb));
+      ctrl_.push_back(static_cast<uint32_t*>(zeroed(tp_ctrl_words(ag_ ? rows * nranks : 0) * sizeof(uint32_t))));
+      x_full_.push_back(ag_ ? zeroed(static_cast<size_t>(rows) * nranks * cols * 2) : nullptr);
+    }
+    comms_.resize(nranks);
+    for (int r = 0; r < nranks; ++r) {
+      CommDev& c = comms_[r];
+      std::memset(&c, 0, sizeof(c));
+      c.rank = r;
+      c.nranks = nranks;
+      for (int p = 0; p < nranks; ++p) c.flags[p] = flags[p];
+      c.epochs = static_cast<uint32_t*>(zeroed(kFlagSets * kMaxBlocks * sizeof(uint32_t)));
+      c.status = sdev;
+      c.timeout_ns = static_cast<unsigned long long>(wait_ms * 1e6);
+    }
+    B200C_CUDA_CHECK(cudaDeviceSynchronize());
+  }
+  ~TpEmuWorld() {
+    for (void* p : allocs_) cudaFree(p);
+    if (status_host_) cudaFreeHost(status_host_);
+  }
+
+  at::Tensor input(int r) {
+    TORCH_CHECK(ag_ && r >= 0 && r < nranks_, "input(rank): ag_gemm worlds only");
+    auto opts = at::TensorOptions().device(at::kCUDA, at::cuda::current_device()).dtype(at::kBFloat16);
+    return at::from_blob(bases_[r], {rows_, cols_}, opts);
+  }
+
+  // ys[r] = all_gather(inputs) @ ws[r]^T
+  std::vector<at::Tensor> ag_gemm(const std::vector<at::Tensor>& ws) {
+    TORCH_CHECK(ag_ && static_cast<int>(ws.size()) == nranks_, "one weight shard per rank");
+    std::vector<AgGemmArgs> args(nranks_);
+    std::vector<at::Tensor> ys;
+    for (int r = 0; r < nranks_; ++r) {
+      const at::Tensor& w = ws[r];
+      TORCH_CHECK(w.is_cuda() && w.is_contiguous() && w.scalar_type() == at::kBFloat16 && w.dim() == 2 &&
+                      w.size(1) == cols_ && w.size(0) % 256 == 0 && w.size(0) == ws[0].size(0),
+                  "w: contiguous bf16 [n, k], n % 256 == 0, the same n on every rank");
+      ys.push_back(at::empty({static_cast<int64_t>(rows_) * nranks_, w.size(0)}, w.options()));
+      AgGemmArgs& a = args[r];
+      a = AgGemmArgs{};
+      for (int p = 0; p < nranks_; ++p) a.x_shards[p] = bases_[p];
+      a.x_full = x_full_[r];
+      a.w = w.data_ptr();
+      a.y = ys[r].data_ptr();
+      a.m_local = rows_;
+      a.n = static_cast<int>(w.size(0));
+      a.k = cols_;
+      a.ctrl = ctrl_[r];
+    }
+    cudaStream_t s = at::cuda::getCurrentCUDAStream().stream();
+    B200C_CUDA_CHECK(launch_allgather_gemm_emu(comms_.data(), args.data(), nranks_, s));
+    return ys;
+  }
+
+  // outs[r] = rows of rank r of sum over ranks of hs[q] @ ws[q]^T
+  std::vector<at::Tensor> gemm_rs(const std::vector<at::Tensor>& hs, const std::vector<at::Tensor>& ws) {
+    TORCH_CHECK(!ag_ && static_cast<int>(hs.size()) == nranks_ && static_cast<int>(ws.size()) == nranks_,
+                "one activation and one weight shard per rank");
+    std::vector<GemmRsArgs> args(nranks_);
+    std::vector<at::Tensor> outs;
+    for (int r = 0; r < nranks_; ++r) {
+      const at::Tensor &h = hs[r], &w = ws[r];
+      TORCH_CHECK(h.is_cuda() && h.is_contiguous() && h.scalar_type() == at::kBFloat16 && h.dim() == 2 && h.size(0) == rows_ &&
+                      h.size(1) % 64 == 0 && h.size(1) == hs[0].size(1),
+                  "h: contiguous bf16 [m, k_local], k_local % 64 == 0");
+      TORCH_CHECK(w.is_cuda() && w.is_contiguous() && w.scalar_type() == at::kBFloat16 && w.dim() == 2 && w.size(0) == cols_ &&
+                      w.size(1) == h.size(1),
+                  "w: contiguous bf16 [n, k_local]");
+      outs.push_back(at::empty({rows_ / nranks_, cols_}, h.options()));
+      GemmRsArgs& a = args[r];
+      a = GemmRsArgs{};
+      a.h = h.data_ptr();
+      a.w = w.data_ptr();
+      for (int p = 0; p < nranks_; ++p) {
+        a.partials[p] = bases_[p];
+        a.arrived[p] = reinterpret_cast<uint32_t*>(bases_[p] + data_bytes_);
+      }
+      a.out = outs[r].data_ptr();
+      a.m = rows_;
+      a.n = cols_;
+      a.k_local = static_cast<int>(h.size(1));
+      a.ctrl = ctrl_[r];
+    }
+    cudaStream_t s = at::cuda::getCurrentCUDAStream().stream();
+    B200C_CUDA_CHECK(launch_gemm_reduce_scatter_emu(comms_.data(), args.data(), nranks_, s));
+    return outs;
+  }
+
+  std::vector<uint32_t> status() const { return std::vector<uint32_t>(status_host_, status_host_ + 5); }
+
+ private:
+  bool ag_;
+  int nranks_, rows_, cols_;
+  size_t data_bytes_ = 0, flag_bytes_ = 0;
+  std::vector<char*> bases_;
+  std::vector<uint32_t*> ctrl_;
+  std::vector<void*> x_full_;
+  std::vector<void*> allocs_;
+  std::vector<CommDev> comms_;
+  uint32_t* status_host_ = nullptr;
+};
+
 } // namespace
 
 void bind_tp(py::module_& m) {
+  py::class_<TpEmuWorld>(m, "TpEmuWorld")
+      .def(py::init<int, const std::string&, int, int, double>(), py::arg("nranks"), py::arg("kind"), py::arg("rows"),
+           py::arg("cols"), py::arg("wait_ms") = 2000.0)
+      .def("input", &TpEmuWorld::input)
+      .def("ag_gemm", &TpEmuWorld::ag_gemm)
+      .def("gemm_rs", &TpEmuWorld::gemm_rs)
+      .def("status", &TpEmuWorld::status);
   py::class_<TpLayer, std::shared_ptr<TpLayer>>(m, "TpLayer")
       .def(py::init([](py::object backend, const std::string& kind, int rows, int cols, double wait_ms) {
              std::shared_ptr<CudaBackend> b;

@@ -12,11 +12,14 @@ Each rank owns ``num_experts / n`` experts.  ``forward``:
 
 Gate weights are applied on the expert side (step 3), so combine is a plain
 sum over destination ranks.  ``ExpertParallelMoE`` is forward only (inference /
-evaluation); training through the kernels would need the mirrored dispatch of
-gradients.  ``ExpertParallelMoEUnfused`` is the differentiable counterpart for
-training: the same routing through the functional all-to-all (whose backward is
-the reverse all-to-all), bf16 / fp32 rows, gates applied at the token's owner so
-the router receives its gradient.  It runs on any backend, including gloo.
+evaluation, fp8 rows).  ``ExpertParallelMoETrain`` trains through the same
+kernels with bf16 rows: the backward of the combine is a dispatch of the output
+gradients along the saved layout, the backward of the dispatch a combine of the
+row gradients, and the gate gradients travel back with them, so experts, router
+and inputs all receive gradients.  ``ExpertParallelMoEUnfused`` is the same
+computation through the functional all-to-all (whose backward is the reverse
+all-to-all), gates applied at the token's owner; it runs on any backend,
+including gloo, and is the reference the fused layer is tested against.
 
 Parity: the usage pattern of comms/prims/collectives/link_ep (Buffer.dispatch
 -> experts -> Buffer.combine, link_ep/buffer.py:76-660).
@@ -30,7 +33,7 @@ from torch import nn
 
 from .. import TorchComm
 from .. import functional as F
-from ..ops.moe_ep import Buffer
+from ..ops.moe_ep import Buffer, combine_autograd, dispatch_autograd
 
 
 class ExpertParallelMoE(nn.Module):
@@ -66,6 +69,39 @@ class ExpertParallelMoE(nn.Module):
             out.index_add_(0, sel, self.experts[e](rows[sel]).float() * gate)
         self.buffer.combine_input[:n] = out.to(torch.bfloat16)
         return self.buffer.combine()
+
+
+class ExpertParallelMoETrain(nn.Module):
+    """Differentiable expert-parallel MoE on the fused dispatch / combine kernels (bf16 rows).
+
+    ``y[token] = sum_k gate[token, k] * expert_k(x[token])``; gradients flow to the experts, to the router
+    (the gates ride with the rows and their gradients ride back) and to ``x``.
+    """
+
+    def __init__(self, comm: TorchComm, hidden: int, num_experts: int, topk: int, max_tokens: int,
+                 experts: Sequence[nn.Module], router: nn.Module):
+        super().__init__()
+        n = comm.get_size()
+        if num_experts % n != 0 or len(experts) != num_experts // n:
+            raise ValueError("give exactly num_experts / nranks local experts")
+        self.comm, self.hidden, self.num_experts, self.topk = comm, hidden, num_experts, topk
+        self.local = num_experts // n
+        self.experts = nn.ModuleList(experts)
+        self.router = router
+        self.buffer = Buffer(comm, max_tokens=max_tokens, hidden=hidden, num_experts=num_experts, topk=topk, fp8=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        gates, idx = torch.softmax(self.router(x).float(), dim=-1).topk(self.topk, dim=-1)
+        rows, w, local_idx, meta = dispatch_autograd(self.buffer, x.to(torch.bfloat16), idx.to(torch.int32), gates)
+        out = torch.zeros(rows.shape[0], self.hidden, dtype=torch.float32, device=x.device)
+        for e in range(self.local):
+            hit = local_idx == e
+            sel = hit.any(dim=1).nonzero().flatten()
+            if sel.numel() == 0:
+                continue
+            gate = (w[sel] * hit[sel]).sum(dim=1, keepdim=True)
+            out = out.index_add(0, sel, self.experts[e](rows[sel]).float() * gate)
+        return combine_autograd(self.buffer, out.to(torch.bfloat16), meta).to(x.dtype)
 
 
 class ExpertParallelMoEUnfused(nn.Module):
