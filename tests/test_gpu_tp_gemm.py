@@ -84,6 +84,79 @@ def test_gemm_rs_emulated_ranks(nranks, m, n, k_local):
             torch.testing.assert_close(outs[r].float(), total[r * rows : (r + 1) * rows], rtol=2e-2, atol=3e-2)
 
 
+def _fp8_ref(q_a, s_a, q_b, s_b):
+    """fp32 reference of the fp8 product computed from the SAME quantised operands."""
+    return (q_a.float() * s_a.unsqueeze(1)) @ (q_b.float() * s_b.unsqueeze(1)).t()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (300, 264, 256), (1024, 1792, 2048), (128 * 9, 256 * 5, 1024)])
+def test_gemm_e4m3_rowwise_scales(m, n, k):
+    from torchcomms_b200.ops.tp import gemm_e4m3_nt, quantize_rows
+
+    a, b = _rand((m, k), 1), _rand((n, k), 2, scale=0.05)
+    (qa, sa), (qb, sb) = quantize_rows(a), quantize_rows(b)
+    c = gemm_e4m3_nt(qa, qb, sa, sb)
+    torch.cuda.synchronize()
+    ref = _fp8_ref(qa, sa, qb, sb)
+    # the kernel multiplies exact e4m3 products in fp32: only the bf16 rounding of the result separates the two
+    torch.testing.assert_close(c.float(), ref, rtol=1e-2, atol=1e-2)
+    # and the quantisation itself stays within fp8's precision of the bf16 product
+    full = a.float() @ b.float().t()
+    assert float((c.float() - full).norm() / full.norm()) < 0.06
+
+
+@pytest.mark.parametrize("nranks", [1, 2, 4])
+def test_fp8_fused_layers_emulated_ranks(nranks):
+    """e4m3 all-gather -> GEMM (row scales travel with the rows) and GEMM -> reduce-scatter on 1, 2 and 4 ranks."""
+    from torchcomms_b200 import _comms
+    from torchcomms_b200.ops.tp import quantize_rows
+
+    m_local, n, k = 256, 512, 1024
+    world = _comms.TpEmuWorld(nranks, "ag_gemm", m_local, k, 5000.0, True)
+    for it in range(2):
+        xs = [quantize_rows(_rand((m_local, k), 300 * it + r)) for r in range(nranks)]
+        ws = [quantize_rows(_rand((n, k), 300 * it + 50 + r, scale=0.05)) for r in range(nranks)]
+        for r in range(nranks):
+            world.input(r).copy_(xs[r][0])
+            world.input_scales(r).copy_(xs[r][1])
+        ys = world.ag_gemm([w for w, _ in ws], [s for _, s in ws])
+        torch.cuda.synchronize()
+        assert world.status()[0] == 0, world.status()
+        qx, sx = torch.cat([q for q, _ in xs]), torch.cat([s for _, s in xs])
+        for r in range(nranks):
+            torch.testing.assert_close(ys[r].float(), _fp8_ref(qx, sx, ws[r][0], ws[r][1]), rtol=1e-2, atol=2e-2)
+    m = 128 * nranks * 2
+    world = _comms.TpEmuWorld(nranks, "gemm_rs", m, n, 5000.0, True)
+    for it in range(2):
+        hs = [quantize_rows(_rand((m, k), 400 * it + r)) for r in range(nranks)]
+        ws = [quantize_rows(_rand((n, k), 400 * it + 50 + r, scale=0.05)) for r in range(nranks)]
+        outs = world.gemm_rs([q for q, _ in hs], [q for q, _ in ws], [s for _, s in hs], [s for _, s in ws])
+        torch.cuda.synchronize()
+        assert world.status()[0] == 0, world.status()
+        total = sum(_fp8_ref(h[0], h[1], w[0], w[1]) for h, w in zip(hs, ws))
+        rows = m // nranks
+        for r in range(nranks):
+            torch.testing.assert_close(outs[r].float(), total[r * rows : (r + 1) * rows], rtol=2e-2, atol=4e-2)
+
+
+def test_fp8_layers_single_rank_api():
+    from torchcomms_b200.ops.tp import AllGatherGemm, GemmReduceScatter, quantize_rows
+
+    m, n, k = 512, 768, 1024   # m % 256 == 0: the CTA-pair kernels
+    x, w = _rand((m, k), 5), _rand((n, k), 6, scale=0.05)
+    qw, sw = quantize_rows(w)
+    qx, sx = quantize_rows(x)
+    up = AllGatherGemm(None, m, k, fp8=True)
+    y = up(qw, x, scale_w=sw)                    # bf16 activations are quantised on the way in
+    down = GemmReduceScatter(None, m, n, fp8=True)
+    out = down(qx, qw, sx, sw)
+    torch.cuda.synchronize()
+    assert up.status()[0] == 0 and down.status()[0] == 0
+    ref = _fp8_ref(qx, sx, qw, sw)
+    torch.testing.assert_close(y.float(), ref, rtol=1e-2, atol=2e-2)
+    torch.testing.assert_close(out.float(), ref, rtol=1e-2, atol=2e-2)
+
+
 def _tp_worker(rank, world):
     import torchcomms_b200 as tc
     from torchcomms_b200.ops.tp import AllGatherGemm, GemmReduceScatter

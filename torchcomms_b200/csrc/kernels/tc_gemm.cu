@@ -88,8 +88,24 @@ struct TpParams {
   // common
   uint32_t* ctrl;
   uint32_t* status;   // plain mode: where a failed wait is recorded (may be null)
-  int m_total, m_local, n, k, gm;
+  int m_total, m_local, n, k, gm;   // k in 16-bit units: K for bf16, K / 2 for e4m3
+  // e4m3 operands: C = (row_scale[m] * col_scale[n]) * (A_q x B_q^T)
+  int fp8;
+  const float* scale_a;                     // [m_total] (plain, reduce-scatter)
+  const float* scale_a_shards[kMaxRanks];   // all-gather: rank r's [m_local], symmetric
+  float* scale_a_full;                      // all-gather: local [m_total], filled by the copy warps
+  const float* scale_b;                     // [n]
 };
+
+// Row scale of global row `grow` of m-tile ordinal `ord` (see mtile_of).
+template <TpMode MODE>
+__device__ __forceinline__ float row_scale_of(const TpParams& p, const CommDev& c, int ord, int tiles_per_src, int grow) {
+  if (grow >= p.m_total) return 0.0f;
+  if (MODE == TpMode::AG_GEMM) {
+    return ord < tiles_per_src ? p.scale_a_shards[c.rank][grow - c.rank * p.m_local] : __ldcg(p.scale_a_full + grow);
+  }
+  return p.scale_a[grow];
+}
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
   uint32_t v;
@@ -160,7 +176,7 @@ template <TpMode MODE>
 __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& c, const TpParams& p) {
   using Cfg = TileCfg<kTpBN>;
   constexpr int BN = kTpBN;
-  constexpr uint32_t idesc = make_idesc_bf16(kBlockM, BN);
+  const uint32_t idesc = p.fp8 ? make_idesc_e4m3(kBlockM, BN) : make_idesc_bf16(kBlockM, BN);
   constexpr bool kFused = MODE != TpMode::PLAIN;
   extern __shared__ char smem_raw[];
   char* stages = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -272,8 +288,12 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + Cfg::kABytes);
 #pragma unroll
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-            // 16 bf16 = 32 bytes further along K inside the swizzled row
-            umma_bf16(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
+            // 16 bf16 (or 32 e4m3) = 32 bytes further along K inside the swizzled row
+            if (p.fp8) {
+              umma_f8(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
+            } else {
+              umma_bf16(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
+            }
           }
           umma_commit(&bars->empty[s]);  // stage reusable once these MMAs have read it
         }
@@ -296,6 +316,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
         break;
       }
       tc_fence_after_sync();
+      const float row_scale = p.fp8 ? row_scale_of<MODE>(p, c, tc_.ord, tiles_per_src, mi * kBlockM + row_in_tile) : 1.0f;
       const CUtensorMap* mo = &maps.out[0];
       int out_row = mi * kBlockM;
       int owner = 0;
@@ -317,6 +338,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
                             static_cast<uint32_t>(j * kOutChunkCols + half * 32),
                         r);
           tmem_ld_wait();
+          if (p.fp8) scale_acc32(r, row_scale, p.scale_b, ni * BN + j * kOutChunkCols + half * 32, p.n);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const int chunk16 = half * 4 + v;
@@ -391,6 +413,9 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
           }
           for (; i < nvec; i += kCopyThreads) to[i] = from[i];
           fence_proxy_async();  // these rows are read next by TMA (async proxy)
+        }
+        if (p.fp8 && blockIdx.x == 0 && ct < kBlockM) {  // the tile's row scales travel with it
+          p.scale_a_full[mi * kBlockM + ct] = p.scale_a_shards[src][(mi - src * tiles_per_src) * kBlockM + ct];
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (ct == 0) {
@@ -514,7 +539,7 @@ template <TpMode MODE>
 __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __grid_constant__ TpMaps maps, CommDev c, TpParams p) {
   constexpr int BN = kTpBN;
   constexpr int kAB = kBlockM * kBlockK * 2;
-  constexpr uint32_t idesc = make_idesc_bf16(2 * kBlockM, BN);
+  const uint32_t idesc = p.fp8 ? make_idesc_e4m3(2 * kBlockM, BN) : make_idesc_bf16(2 * kBlockM, BN);
   extern __shared__ char smem_raw[];
   char* stages = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   char* obuf = stages + kPairStages * kPairStageBytes;
@@ -632,7 +657,11 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + kAB);
 #pragma unroll
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-            umma_bf16_pair(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
+            if (p.fp8) {
+              umma_f8_pair(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
+            } else {
+              umma_bf16_pair(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
+            }
           }
           umma_commit_pair(&bars->empty[s], 3);
         }
@@ -655,6 +684,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
         break;
       }
       tc_fence_after_sync();
+      const float row_scale = p.fp8 ? row_scale_of<MODE>(p, c, ord, tiles_per_src, mi * kBlockM + row_in_tile) : 1.0f;
       const CUtensorMap* mo = &maps.out[0];
       int out_row = mi * kBlockM;
       int owner = 0;
@@ -674,6 +704,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
                             static_cast<uint32_t>(j * kOutChunkCols + half * 32),
                         r);
           tmem_ld_wait();
+          if (p.fp8) scale_acc32(r, row_scale, p.scale_b, ni * BN + j * kOutChunkCols + half * 32, p.n);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const int chunk16 = half * 4 + v;
@@ -745,6 +776,9 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
           }
           for (; i < nvec; i += kCopyThreads) to[i] = from[i];
           fence_proxy_async();
+        }
+        if (p.fp8 && blockIdx.x == 0 && ct < kBlockM) {  // the tile's row scales travel with it
+          p.scale_a_full[mi * kBlockM + ct] = p.scale_a_shards[src][(mi - src * tiles_per_src) * kBlockM + ct];
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (ct == 0) {
@@ -899,6 +933,18 @@ cudaError_t tp_launch_pair(int want_pairs, const TpMaps& maps, const CommDev& c,
 
 cudaError_t launch_gemm_bf16_nt(const void* a, const void* b, void* c, int m, int n, int k, uint32_t* status,
                                 cudaStream_t stream) {
+  return launch_gemm_nt(a, b, c, m, n, k, nullptr, nullptr, status, stream);
+}
+
+cudaError_t launch_gemm_e4m3_nt(const void* a, const void* b, void* c, int m, int n, int k, const float* scale_a,
+                                const float* scale_b, uint32_t* status, cudaStream_t stream) {
+  if (scale_a == nullptr || scale_b == nullptr || k % 16 != 0) return cudaErrorInvalidValue;
+  return launch_gemm_nt(a, b, c, m, n, k / 2, scale_a, scale_b, status, stream);
+}
+
+// k in 16-bit units; scales non-null = e4m3 operands.
+cudaError_t launch_gemm_nt(const void* a, const void* b, void* c, int m, int n, int k, const float* scale_a,
+                           const float* scale_b, uint32_t* status, cudaStream_t stream) {
   if (m <= 0 || n <= 0 || k <= 0 || k % 8 != 0 || n % 8 != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15u) {
     return cudaErrorInvalidValue;
@@ -919,6 +965,9 @@ cudaError_t launch_gemm_bf16_nt(const void* a, const void* b, void* c, int m, in
   p.m_local = m;
   p.n = n;
   p.k = k;
+  p.fp8 = scale_a != nullptr ? 1 : 0;
+  p.scale_a = scale_a;
+  p.scale_b = scale_b;
   const int tiles_m = (m + kBlockM - 1) / kBlockM, tiles_n = (n + kTpBN - 1) / kTpBN;
   p.gm = pick_group(tiles_m, kBlockM, k, 16);
   return tp_launch<TpMode::PLAIN>(std::min(sm_count(), tiles_m * tiles_n), maps, none, p, stream);
@@ -933,10 +982,14 @@ namespace {
 // Tensor maps and parameters of one rank's all-gather GEMM. `pairs`: for the CTA-pair kernel.
 cudaError_t build_ag(const CommDev& comm, const AgGemmArgs& a, bool pairs, TpMaps& maps, TpParams& p) {
   const int m_total = a.m_local * comm.nranks;
-  if (a.m_local <= 0 || a.m_local % kBlockM != 0 || a.n % kTpBN != 0 || a.k % kBlockK != 0) return cudaErrorInvalidValue;
+  const int k = a.fp8 ? a.k / 2 : a.k;   // in 16-bit units
+  if (a.m_local <= 0 || a.m_local % kBlockM != 0 || a.n % kTpBN != 0 || a.k % (a.fp8 ? 2 * kBlockK : kBlockK) != 0) {
+    return cudaErrorInvalidValue;
+  }
   if (comm.nranks > kMaxRanks) return cudaErrorInvalidValue;
-  if (!make_map(&maps.a_local, a.x_shards[comm.rank], a.m_local, a.k, kBlockM) ||
-      !make_map(&maps.a_full, a.x_full, m_total, a.k, kBlockM) || !make_map(&maps.b, a.w, a.n, a.k, kTpBN) ||
+  if (a.fp8 && (a.scale_w == nullptr || a.scale_x_full == nullptr)) return cudaErrorInvalidValue;
+  if (!make_map(&maps.a_local, a.x_shards[comm.rank], a.m_local, k, kBlockM) ||
+      !make_map(&maps.a_full, a.x_full, m_total, k, kBlockM) || !make_map(&maps.b, a.w, a.n, k, kTpBN) ||
       !make_map(&maps.out[0], a.y, m_total, a.n, kBlockM)) {
     return cudaErrorInvalidValue;
   }
@@ -948,23 +1001,34 @@ cudaError_t build_ag(const CommDev& comm, const AgGemmArgs& a, bool pairs, TpMap
   p.m_total = m_total;
   p.m_local = a.m_local;
   p.n = a.n;
-  p.k = a.k;
+  p.k = k;
+  p.fp8 = a.fp8;
+  if (a.fp8) {
+    for (int r = 0; r < comm.nranks; ++r) {
+      if (a.scale_x_shards[r] == nullptr) return cudaErrorInvalidValue;
+      p.scale_a_shards[r] = a.scale_x_shards[r];
+    }
+    p.scale_a_full = a.scale_x_full;
+    p.scale_b = a.scale_w;
+  }
   if (pairs) {
-    if (!make_map(&maps.b_half, a.w, a.n, a.k, kBlockM)) return cudaErrorInvalidValue;
-    p.gm = pick_group(a.m_local / (2 * kBlockM), 2 * kBlockM, a.k, 8);
+    if (!make_map(&maps.b_half, a.w, a.n, k, kBlockM)) return cudaErrorInvalidValue;
+    p.gm = pick_group(a.m_local / (2 * kBlockM), 2 * kBlockM, k, 8);
   } else {
     maps.b_half = maps.b;
-    p.gm = pick_group(a.m_local / kBlockM, kBlockM, a.k, 16);
+    p.gm = pick_group(a.m_local / kBlockM, kBlockM, k, 16);
   }
   return cudaSuccess;
 }
 
 cudaError_t build_rs(const CommDev& comm, const GemmRsArgs& a, bool pairs, TpMaps& maps, TpParams& p) {
-  if (a.m <= 0 || a.m % (kBlockM * comm.nranks) != 0 || a.n % kTpBN != 0 || a.k_local % kBlockK != 0) {
+  const int k = a.fp8 ? a.k_local / 2 : a.k_local;   // in 16-bit units
+  if (a.m <= 0 || a.m % (kBlockM * comm.nranks) != 0 || a.n % kTpBN != 0 || a.k_local % (a.fp8 ? 2 * kBlockK : kBlockK) != 0) {
     return cudaErrorInvalidValue;
   }
   if (comm.nranks > kMaxRanks) return cudaErrorInvalidValue;
-  if (!make_map(&maps.a_local, a.h, a.m, a.k_local, kBlockM) || !make_map(&maps.b, a.w, a.n, a.k_local, kTpBN)) {
+  if (a.fp8 && (a.scale_h == nullptr || a.scale_w == nullptr)) return cudaErrorInvalidValue;
+  if (!make_map(&maps.a_local, a.h, a.m, k, kBlockM) || !make_map(&maps.b, a.w, a.n, k, kTpBN)) {
     return cudaErrorInvalidValue;
   }
   maps.a_full = maps.a_local;
@@ -981,13 +1045,16 @@ cudaError_t build_rs(const CommDev& comm, const GemmRsArgs& a, bool pairs, TpMap
   p.m_total = a.m;
   p.m_local = a.m / comm.nranks;
   p.n = a.n;
-  p.k = a.k_local;
+  p.k = k;
+  p.fp8 = a.fp8;
+  p.scale_a = a.scale_h;
+  p.scale_b = a.scale_w;
   if (pairs) {
-    if (!make_map(&maps.b_half, a.w, a.n, a.k_local, kBlockM)) return cudaErrorInvalidValue;
-    p.gm = pick_group(p.m_local / (2 * kBlockM), 2 * kBlockM, a.k_local, 8);
+    if (!make_map(&maps.b_half, a.w, a.n, k, kBlockM)) return cudaErrorInvalidValue;
+    p.gm = pick_group(p.m_local / (2 * kBlockM), 2 * kBlockM, k, 8);
   } else {
     maps.b_half = maps.b;
-    p.gm = pick_group(p.m_local / kBlockM, kBlockM, a.k_local, 16);
+    p.gm = pick_group(p.m_local / kBlockM, kBlockM, k, 16);
   }
   return cudaSuccess;
 }

@@ -1,8 +1,10 @@
 // Blackwell (sm_100a) tensor-core building blocks written as inline PTX:
 // mbarriers, TMA tile loads (never with cluster multicast), TMEM allocation,
 // tcgen05.mma issue / commit and tcgen05.ld, plus the shared-memory and
-// instruction descriptors for bf16 x bf16 -> fp32 with K-major operands under
-// the 128-byte swizzle.
+// instruction descriptors for bf16 x bf16 -> fp32 and e4m3 x e4m3 -> fp32 with
+// K-major operands under the 128-byte swizzle. An e4m3 matrix [rows, K] has the
+// bytes of a bf16 matrix [rows, K/2]: the tensor maps, the shared-memory tiles
+// and the 32-byte K step are the same for both, only the instruction differs.
 //
 // Every wait is bounded: when its spin budget runs out it returns false, the
 // caller records an error word, skips the remaining work and still releases
@@ -179,6 +181,16 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint
       ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
       : "memory");
 }
+// The same for 8-bit floating-point operands (formats named by the instruction descriptor); K of one
+// instruction is 32 elements, which is again 32 bytes of the swizzled row.
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
+      : "memory");
+}
 // Arrives on `bar` once every tcgen05.mma issued so far by this thread is done.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -250,6 +262,14 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t a_desc,
       ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)), "r"(0u)
       : "memory");
 }
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)), "r"(0u)
+      : "memory");
+}
 // Arrives on `bar` in every CTA of `cta_mask` once the leader's MMAs so far are done.
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
@@ -286,6 +306,22 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n) {
       | (1u << 10)                              // B format: bf16
       | (static_cast<uint32_t>(n >> 3) << 17)   // N / 8
       | (static_cast<uint32_t>(m >> 4) << 24);  // M / 16
+}
+
+// Instruction descriptor: e4m3 x e4m3 -> fp32 (kind::f8f6f4; operand format 0 = e4m3), both operands K-major.
+__host__ __device__ constexpr uint32_t make_idesc_e4m3(int m, int n) {
+  return (1u << 4)                              // D format: fp32
+      | (static_cast<uint32_t>(n >> 3) << 17)   // N / 8
+      | (static_cast<uint32_t>(m >> 4) << 24);  // M / 16
+}
+
+// Epilogue of the fp8 products: acc[i] *= row_scale * col_scale[col0 + i] (columns past `n` give zero).
+__device__ __forceinline__ void scale_acc32(uint32_t (&r)[32], float row_scale, const float* __restrict__ col_scale, int col0, int n) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float b = col0 + i < n ? __ldg(col_scale + col0 + i) : 0.0f;
+    r[i] = __float_as_uint(__uint_as_float(r[i]) * (row_scale * b));
+  }
 }
 
 #endif // __CUDACC__

@@ -16,6 +16,16 @@ namespace b200c {
 cudaError_t launch_gemm_bf16_nt(const void* a, const void* b, void* c, int m, int n, int k, uint32_t* status,
                                 cudaStream_t stream);
 
+// The same with fp8 operands: C[M, N] (bf16) = scale_a[m] * scale_b[n] * (A[M, K] (e4m3) x B[N, K]^T (e4m3)),
+// one fp32 scale per row of A (per token) and per row of B (per output channel), applied to the fp32
+// accumulator in the epilogue. K % 16 == 0. An e4m3 row has the bytes of a bf16 row of half the length, so
+// tiles, tensor maps and pipeline are those of the bf16 kernel; only the tcgen05.mma kind differs.
+cudaError_t launch_gemm_e4m3_nt(const void* a, const void* b, void* c, int m, int n, int k, const float* scale_a,
+                                const float* scale_b, uint32_t* status, cudaStream_t stream);
+// Common entry of the two above (k in 16-bit units, scales null = bf16).
+cudaError_t launch_gemm_nt(const void* a, const void* b, void* c, int m, int n, int k, const float* scale_a,
+                           const float* scale_b, uint32_t* status, cudaStream_t stream);
+
 // The same product on CTA pairs (clusters of two CTAs, tcgen05 cta_group::2):
 // each pair owns a 256 x 256 tile and reads every B element once. Same
 // argument rules; any m, n % 8 == 0, k % 8 == 0.
@@ -41,6 +51,13 @@ struct AgGemmArgs {
   void* y;
   int m_local, n, k;
   uint32_t* ctrl;
+  // fp8 = 1: x shards and w are e4m3 (k counts e4m3 elements, k % 128 == 0). scale_x_shards[r]: rank r's
+  // [m_local] fp32 row scales (symmetric, next to its shard); scale_x_full: local scratch [nranks*m_local]
+  // that the copy warps fill with the peers' scales; scale_w: [n] fp32.
+  int fp8;
+  const float* scale_x_shards[kMaxRanks];
+  float* scale_x_full;
+  const float* scale_w;
 };
 cudaError_t launch_allgather_gemm(const CommDev& comm, const AgGemmArgs& args, cudaStream_t stream);
 
@@ -64,6 +81,11 @@ struct GemmRsArgs {
   void* out;
   int m, n, k_local;
   uint32_t* ctrl;
+  // fp8 = 1: h and w are e4m3 (k_local % 128 == 0) with scale_h [m] and scale_w [n]; the partial tiles that
+  // travel are bf16 as before (already scaled).
+  int fp8;
+  const float* scale_h;
+  const float* scale_w;
 };
 cudaError_t launch_gemm_reduce_scatter(const CommDev& comm, const GemmRsArgs& args, cudaStream_t stream);
 

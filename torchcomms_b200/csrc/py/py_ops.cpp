@@ -165,6 +165,23 @@ void bind_ops(py::module_& m) {
     return std::make_pair(c, status);
   });
 
+  // c[m, n] (bf16) = scale_a[m] * scale_b[n] * (a[m, k] (e4m3) @ b[n, k]^T (e4m3)), fp32 accumulation in tensor memory.
+  ops.def("gemm_e4m3_nt", [](const at::Tensor& a, const at::Tensor& b, const at::Tensor& scale_a, const at::Tensor& scale_b) {
+    want(a, at::kFloat8_e4m3fn, "a");
+    want(b, at::kFloat8_e4m3fn, "b");
+    want(scale_a, at::kFloat, "scale_a");
+    want(scale_b, at::kFloat, "scale_b");
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1), "a: [m, k], b: [n, k]");
+    TORCH_CHECK(scale_a.numel() == a.size(0) && scale_b.numel() == b.size(0), "one scale per row of a and per row of b");
+    c10::cuda::CUDAGuard g(a.device());
+    at::Tensor c = at::empty({a.size(0), b.size(0)}, a.options().dtype(at::kBFloat16));
+    at::Tensor status = at::zeros({2}, a.options().dtype(at::kInt));
+    B200C_CUDA_CHECK(launch_gemm_e4m3_nt(a.data_ptr(), b.data_ptr(), c.data_ptr(), static_cast<int>(a.size(0)),
+                                         static_cast<int>(b.size(0)), static_cast<int>(a.size(1)), scale_a.data_ptr<float>(),
+                                         scale_b.data_ptr<float>(), reinterpret_cast<uint32_t*>(status.data_ptr<int>()), cur(a)));
+    return std::make_pair(c, status);
+  });
+
   ops.def("gemm_bf16_nt_pair", [](const at::Tensor& a, const at::Tensor& b) {
     want(a, at::kBFloat16, "a");
     want(b, at::kBFloat16, "b");
