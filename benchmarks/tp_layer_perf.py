@@ -12,8 +12,13 @@ Arms:
   * ``unfused`` - this framework's all-gather / reduce-scatter collective
                   followed / preceded by ``torch.matmul`` (cuBLAS)
   * ``nccl``    - the same with the collective routed through NCCL
+  * ``nccl-ovl``- NCCL and cuBLAS overlapped by hand: the rows are cut into ``--chunks`` pieces, the
+                  collective of one piece runs on the communicator's stream while cuBLAS works on its
+                  neighbour (the strongest baseline that needs no fused kernel)
   * ``cublas`` / ``tcgen05`` / ``tcgen05x2`` - the local GEMM alone (cuBLAS, this framework's
                   kernel with one CTA per tile, and on CTA pairs): the lower bound of any arm
+  * ``*-fp8``   - the same with e4m3 operands and per-row / per-channel fp32 scales
+                  (``cublas-fp8`` is ``torch._scaled_mm``); TFLOP/s counts the same 2mnk
 """
 from __future__ import annotations
 
@@ -28,7 +33,7 @@ import torch  # noqa: E402
 
 import torchcomms_b200 as tc  # noqa: E402
 from torchcomms_b200 import _comms  # noqa: E402
-from torchcomms_b200.ops.tp import AllGatherGemm, GemmReduceScatter  # noqa: E402
+from torchcomms_b200.ops.tp import AllGatherGemm, GemmReduceScatter, gemm_e4m3_nt, quantize_rows  # noqa: E402
 
 
 def main():
@@ -38,6 +43,8 @@ def main():
     ap.add_argument("--ffn", type=int, default=28672)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--chunks", type=int, default=4)
+    ap.add_argument("--no-fp8", action="store_true")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
 
@@ -126,6 +133,60 @@ def main():
 
             report("up", arm, time_it(up_unfused), f_up)
             report("down", arm, time_it(down_unfused), f_down)
+        # NCCL and cuBLAS overlapped by hand, piece by piece
+        nccl = {"algo": "nccl"}
+        C = args.chunks
+        if m_local % C == 0 and (m // C) % world == 0:
+            piece = m_local // C
+            x_pieces = [torch.empty(world * piece, hid, dtype=bf, device=dev) for _ in range(C)]
+            y_pieces = [torch.empty(world * piece, n_up, dtype=bf, device=dev) for _ in range(C)]
+
+            def up_overlapped():
+                works = [comm.all_gather_single(x_pieces[c], x_shard[c * piece:(c + 1) * piece], True, hints=nccl)
+                         for c in range(C)]
+                for c in range(C):
+                    works[c].wait()                      # the current stream waits for piece c only
+                    torch.matmul(x_pieces[c], w_up.t(), out=y_pieces[c])
+
+            rows_c = m // C
+            part_pieces = [torch.empty(rows_c, hid, dtype=bf, device=dev) for _ in range(C)]
+            out_pieces = [torch.empty(rows_c // world, hid, dtype=bf, device=dev) for _ in range(C)]
+
+            def down_overlapped():
+                works = []
+                for c in range(C):
+                    torch.matmul(h[c * rows_c:(c + 1) * rows_c], w_down.t(), out=part_pieces[c])
+                    works.append(comm.reduce_scatter_single(out_pieces[c], part_pieces[c], tc.ReduceOp.SUM, True, hints=nccl))
+                for w in works:
+                    w.wait()
+
+            report("up", "nccl-ovl", time_it(up_overlapped), f_up)
+            report("down", "nccl-ovl", time_it(down_overlapped), f_down)
+
+    if not args.no_fp8:
+        qx_all, sx_all = quantize_rows(x_all)
+        qw_up, sw_up = quantize_rows(w_up)
+        qh, sh = quantize_rows(h)
+        qw_down, sw_down = quantize_rows(w_down)
+        try:
+            report("up", "cublas-fp8", time_it(lambda: torch._scaled_mm(
+                qx_all, qw_up.t(), scale_a=sx_all.unsqueeze(1), scale_b=sw_up.unsqueeze(0), out_dtype=bf)), f_up)
+            report("down", "cublas-fp8", time_it(lambda: torch._scaled_mm(
+                qh, qw_down.t(), scale_a=sh.unsqueeze(1), scale_b=sw_down.unsqueeze(0), out_dtype=bf)), f_down)
+        except Exception as e:  # noqa: BLE001
+            if rank == 0:
+                print(f"# cublas-fp8 arm skipped: {type(e).__name__}: {str(e)[:120]}")
+        report("up", "tcgen05-fp8", time_it(lambda: gemm_e4m3_nt(qx_all, qw_up, sx_all, sw_up)), f_up)
+        report("down", "tcgen05-fp8", time_it(lambda: gemm_e4m3_nt(qh, qw_down, sh, sw_down)), f_down)
+        up8 = AllGatherGemm(comm, m_local, hid, fp8=True)
+        down8 = GemmReduceScatter(comm, m, hid, fp8=True)
+        qx_shard, sx_shard = quantize_rows(x_shard)
+        up8.input.copy_(qx_shard)
+        up8.input_scales.copy_(sx_shard)
+        report("up", "fused-fp8", time_it(lambda: up8(qw_up, scale_w=sw_up)), f_up)
+        report("down", "fused-fp8", time_it(lambda: down8(qh, qw_down, sh, sw_down)), f_down)
+        torch.cuda.synchronize()
+        del up8, down8
     torch.cuda.synchronize()
     st = up.status()
     del up, down

@@ -18,6 +18,7 @@ namespace {
 
 constexpr int kLlThreads = 256;
 constexpr int kLlWarps = kLlThreads / 32;
+constexpr int kLlChunkCols = 1024;  // columns of one work item of the send and combine loops (a multiple of 512)
 
 __device__ __forceinline__ float2 bf2f(uint32_t v) {
   return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
@@ -73,10 +74,8 @@ __device__ void ll_dispatch_body(const CommDev& c, const EpLlDev& e, const LlDis
   const size_t row_bytes = e.fp8 ? static_cast<size_t>(e.hidden) : static_cast<size_t>(e.hidden) * 2;
   const size_t par_rows = static_cast<size_t>(par) * Le * N * M;
 
-  // A. number the rows per expert and store them into their fixed slots
+  // A0. number the rows per expert (one warp per token)
   for (int t = gwarp; t < a.num_tokens; t += nwarps) {
-    int d = -1;
-    long long row = -1;
     if (lane < e.topk) {
       const int idx = a.topk_idx[static_cast<size_t>(t) * e.topk + lane];
       int i = -1;
@@ -89,13 +88,31 @@ __device__ void ll_dispatch_body(const CommDev& c, const EpLlDev& e, const LlDis
       }
       e.send_slot[static_cast<size_t>(t) * e.topk + lane] = i;
       if (i >= 0) {
+        const int d = idx / Le;
+        e.slot_src[d][par_rows + (static_cast<size_t>(idx - d * Le) * N + e.rank) * M + i] = t;
+      }
+    }
+  }
+  grid.sync();
+
+  // A1. store the rows into their fixed slots; one work item = one token x kLlChunkCols columns
+  const int nchunks = (e.hidden + kLlChunkCols - 1) / kLlChunkCols;
+  for (int item = gwarp; item < a.num_tokens * nchunks; item += nwarps) {
+    const int t = item / nchunks;
+    const int col_lo = (item - t * nchunks) * kLlChunkCols;
+    const int col_hi = min(e.hidden, col_lo + kLlChunkCols);
+    int d = -1;
+    long long row = -1;
+    if (lane < e.topk) {
+      const int idx = a.topk_idx[static_cast<size_t>(t) * e.topk + lane];
+      const int i = e.send_slot[static_cast<size_t>(t) * e.topk + lane];
+      if (i >= 0) {
         d = idx / Le;
         row = static_cast<long long>(par_rows) + (static_cast<long long>(idx - d * Le) * N + e.rank) * M + i;
-        e.slot_src[d][row] = t;
       }
     }
     const __nv_bfloat16* xr = static_cast<const __nv_bfloat16*>(a.x) + static_cast<size_t>(t) * e.hidden;
-    for (int e0 = lane * 16; e0 < e.hidden; e0 += 512) {
+    for (int e0 = col_lo + lane * 16; e0 < col_hi; e0 += 512) {
       const uint4 v0 = ld16(xr + e0);
       const uint4 v1 = ld16(xr + e0 + 8);
       if (!e.fp8) {
@@ -249,7 +266,12 @@ __device__ void ll_combine_body(const CommDev& c, const EpLlDev& e, const LlComb
   ep.load(c, kFlagSetEp);
   bool ok = block_barrier(c, kFlagSetEp, ep, 0xa3);  // every rank's expert outputs are complete
   if (ok) {
-    for (int t = gwarp; t < a.num_tokens; t += nwarps) {
+    // One work item = one token x kLlChunkCols columns, so that a decode batch still fills the GPU with loads.
+    const int nchunks = (e.hidden + kLlChunkCols - 1) / kLlChunkCols;
+    for (int item = gwarp; item < a.num_tokens * nchunks; item += nwarps) {
+      const int t = item / nchunks;
+      const int col_lo = (item - t * nchunks) * kLlChunkCols;
+      const int col_hi = min(e.hidden, col_lo + kLlChunkCols);
       int d = -1;
       long long off = 0;
       float w = 0.0f;
@@ -267,7 +289,7 @@ __device__ void ll_combine_body(const CommDev& c, const EpLlDev& e, const LlComb
           }
         }
       }
-      for (int e0 = lane * 8; e0 < e.hidden; e0 += 256) {
+      for (int e0 = col_lo + lane * 8; e0 < col_hi; e0 += 256) {
         float acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = 0.0f;

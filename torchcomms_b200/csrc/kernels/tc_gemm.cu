@@ -54,7 +54,7 @@ enum class TpMode : int { PLAIN = 0, AG_GEMM = 1, GEMM_RS = 2 };
 
 template <TpMode MODE>
 constexpr int tp_threads() {
-  return MODE == TpMode::AG_GEMM ? kGemmThreads + kCopyThreads : kGemmThreads;
+  return MODE == TpMode::PLAIN ? kGemmThreads : kGemmThreads + kCopyThreads;  // fused modes: four more warps (copy / reduce)
 }
 
 struct TpBarriers {
@@ -170,13 +170,70 @@ __device__ __forceinline__ TileCoord tile_at(int t, int tiles_m, int tiles_n, in
   return TileCoord{first + rem % gsz, rem / gsz};
 }
 
+// Sum of the `nslots` partial copies of one 128 x BN tile (bf16, fp32 accumulation) into `out`.
+// Every thread keeps U vectors of S slots in flight (U x S 16-byte loads): with four reduce warps per SM
+// it takes that many to run at memory speed rather than at the latency of a load.
+template <int BN, int U, int S>
+__device__ __forceinline__ void reduce_tile(const __nv_bfloat16* __restrict__ base, __nv_bfloat16* __restrict__ out, int wm, int ni,
+                                            int n, size_t slot_elems, int nslots, int tid, int nthreads) {
+  constexpr int kVecs = kBlockM * BN / 8;  // vectors of 8 bf16 in the tile
+  for (int v0 = tid; v0 < kVecs; v0 += nthreads * U) {
+    size_t off[U];
+    float acc[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * nthreads;
+      const int r = v / (BN / 8), cv = v % (BN / 8);
+      off[u] = (static_cast<size_t>(wm * kBlockM + r)) * n + ni * BN + cv * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
+    }
+    for (int s0 = 0; s0 < nslots; s0 += S) {
+      uint4 q[S][U];
+#pragma unroll
+      for (int j = 0; j < S; ++j) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (s0 + j < nslots && v0 + u * nthreads < kVecs) {
+            q[j][u] = ld16_stream(base + static_cast<size_t>(s0 + j) * slot_elems + off[u]);
+          } else {
+            q[j][u] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < S; ++j) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint32_t* pw = &q[j][u].x;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[u][2 * i] += __uint_as_float(pw[i] << 16);
+            acc[u][2 * i + 1] += __uint_as_float(pw[i] & 0xffff0000u);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (v0 + u * nthreads < kVecs) {
+        uint4 o;
+        uint32_t* po = &o.x;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) po[i] = pack_bf16(__float_as_uint(acc[u][2 * i]), __float_as_uint(acc[u][2 * i + 1]));
+        *reinterpret_cast<uint4*>(out + off[u]) = o;
+      }
+    }
+  }
+}
+
 // Body of the single-CTA kernels. `maps` must live in kernel-parameter,
 // constant or global memory (its address goes to TMA).
-template <TpMode MODE>
+template <TpMode MODE, bool FP8>
 __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& c, const TpParams& p) {
   using Cfg = TileCfg<kTpBN>;
   constexpr int BN = kTpBN;
-  const uint32_t idesc = p.fp8 ? make_idesc_e4m3(kBlockM, BN) : make_idesc_bf16(kBlockM, BN);
+  constexpr uint32_t idesc = FP8 ? make_idesc_e4m3(kBlockM, BN) : make_idesc_bf16(kBlockM, BN);
   constexpr bool kFused = MODE != TpMode::PLAIN;
   extern __shared__ char smem_raw[];
   char* stages = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -289,7 +346,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
 #pragma unroll
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
             // 16 bf16 (or 32 e4m3) = 32 bytes further along K inside the swizzled row
-            if (p.fp8) {
+            if (FP8) {
               umma_f8(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
             } else {
               umma_bf16(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
@@ -316,7 +373,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
         break;
       }
       tc_fence_after_sync();
-      const float row_scale = p.fp8 ? row_scale_of<MODE>(p, c, tc_.ord, tiles_per_src, mi * kBlockM + row_in_tile) : 1.0f;
+      const float row_scale = FP8 ? row_scale_of<MODE>(p, c, tc_.ord, tiles_per_src, mi * kBlockM + row_in_tile) : 1.0f;
       const CUtensorMap* mo = &maps.out[0];
       int out_row = mi * kBlockM;
       int owner = 0;
@@ -338,7 +395,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
                             static_cast<uint32_t>(j * kOutChunkCols + half * 32),
                         r);
           tmem_ld_wait();
-          if (p.fp8) scale_acc32(r, row_scale, p.scale_b, ni * BN + j * kOutChunkCols + half * 32, p.n);
+          if (FP8) scale_acc32(r, row_scale, p.scale_b, ni * BN + j * kOutChunkCols + half * 32, p.n);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const int chunk16 = half * 4 + v;
@@ -414,7 +471,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
           for (; i < nvec; i += kCopyThreads) to[i] = from[i];
           fence_proxy_async();  // these rows are read next by TMA (async proxy)
         }
-        if (p.fp8 && blockIdx.x == 0 && ct < kBlockM) {  // the tile's row scales travel with it
+        if (FP8 && blockIdx.x == 0 && ct < kBlockM) {  // the tile's row scales travel with it
           p.scale_a_full[mi * kBlockM + ct] = p.scale_a_shards[src][(mi - src * tiles_per_src) * kBlockM + ct];
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
@@ -424,54 +481,36 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
         }
       }
     }
-  }
-
-  // ---------------- reduce phase of the reduce-scatter: sum the nranks
-  // partial tiles of this rank's rows as they arrive.
-  tc_fence_before_sync();
-  __syncthreads();
-  if (MODE == TpMode::GEMM_RS) {
-    const int my_tiles = tiles_per_src * tiles_n;
-    const int nthreads = blockDim.x;
-    for (int rt = blockIdx.x; rt < my_tiles; rt += G) {
-      if (threadIdx.x == 0) bars->reduce_ok = 1;
-      __syncthreads();
-      if (threadIdx.x < c.nranks) {
-        const uint32_t* flag = p.arrived[c.rank] + static_cast<size_t>(rt) * c.nranks + threadIdx.x;
-        if (!wait_flag_reached(c, flag, epoch + 1, threadIdx.x, 0xa3)) bars->reduce_ok = 0;
-      }
-      __syncthreads();
-      if (!bars->reduce_ok) {
-        bars->failed = 1;
-        break;
-      }
-      const int wm = rt / tiles_n, ni = rt % tiles_n;
-      const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.partials_local);
-      // tile = 128 rows x 256 columns = 4096 vectors of 8 bf16
-      for (int v = threadIdx.x; v < kBlockM * BN / 8; v += nthreads) {
-        const int r = v / (BN / 8), cv = v % (BN / 8);
-        const size_t off = (static_cast<size_t>(wm * kBlockM + r)) * p.n + ni * BN + cv * 8;
-        float acc[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-        for (int s = 0; s < c.nranks; ++s) {
-          const uint4 q4 = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(s) * p.m_local * p.n + off);
-          const uint32_t* pw = &q4.x;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            acc[2 * i] += __uint_as_float(pw[i] << 16);
-            acc[2 * i + 1] += __uint_as_float(pw[i] & 0xffff0000u);
-          }
+    // ---------------- reduce warps (reduce-scatter mode): sum the nranks partial tiles of this rank's
+    // rows as they arrive, in the order in which this rank produces its own (last) contribution, while
+    // the tensor cores are still busy with the remaining tiles.
+    if (MODE == TpMode::GEMM_RS) {
+      const int ct = threadIdx.x - kGemmThreads;
+      const int my_tiles = tiles_per_src * tiles_n;
+      const int first_own = (c.nranks - 1) * tiles_per_src;   // ordinal of this rank's first own m-tile
+      for (int t_own = blockIdx.x; t_own < my_tiles; t_own += G) {
+        const TileCoord tc_ = tile_at(first_own * tiles_n + t_own, tiles_m, tiles_n, p.gm);
+        const int wm = tc_.ord - first_own, ni = tc_.ni;
+        if (ct == 0) bars->reduce_ok = 1;
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (ct < c.nranks) {
+          const uint32_t* flag = p.arrived[c.rank] + static_cast<size_t>(wm * tiles_n + ni) * c.nranks + ct;
+          if (!wait_flag_reached(c, flag, epoch + 1, ct, 0xa3)) bars->reduce_ok = 0;
         }
-        uint4 o;
-        uint32_t* po = &o.x;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) po[i] = pack_bf16(__float_as_uint(acc[2 * i]), __float_as_uint(acc[2 * i + 1]));
-        *reinterpret_cast<uint4*>(p.out + off) = o;
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (!bars->reduce_ok) {
+          if (ct == 0) bars->failed = 1;
+          break;
+        }
+        const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.partials_local);
+        reduce_tile<BN, 4, 4>(base, p.out, wm, ni, p.n, static_cast<size_t>(p.m_local) * p.n, c.nranks, ct, kCopyThreads);
+        asm volatile("bar.sync 2, 128;" ::: "memory");
       }
-      __syncthreads();
     }
   }
+
+  tc_fence_before_sync();
+  __syncthreads();
 
   // ---------------- teardown. Fused modes: the last CTA to finish advances
   // the epoch and joins the closing cross-GPU barrier.
@@ -501,9 +540,9 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
   }
 }
 
-template <TpMode MODE>
+template <TpMode MODE, bool FP8>
 __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm(const __grid_constant__ TpMaps maps, CommDev c, TpParams p) {
-  tp_gemm_body<MODE>(maps, c, p);
+  tp_gemm_body<MODE, FP8>(maps, c, p);
 }
 
 // Several ranks in ONE launch on one GPU (tests): blockIdx.y is the rank, each
@@ -516,9 +555,9 @@ struct TpEmu {
   TpParams p[kTpEmuRanks];
 };
 
-template <TpMode MODE>
+template <TpMode MODE, bool FP8>
 __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_emu(const __grid_constant__ TpEmu e) {
-  tp_gemm_body<MODE>(e.maps[blockIdx.y], e.c[blockIdx.y], e.p[blockIdx.y]);
+  tp_gemm_body<MODE, FP8>(e.maps[blockIdx.y], e.c[blockIdx.y], e.p[blockIdx.y]);
 }
 
 // ------------------------------------- fused kernels on CTA pairs ----------
@@ -535,11 +574,11 @@ constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = kBlockM * kBlockK * 2 + (kTpBN / 2) * kBlockK * 2;  // 16 KB of A + 16 KB of B
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 2 * kOutChunkBytes + 1024 + 256;
 
-template <TpMode MODE>
+template <TpMode MODE, bool FP8>
 __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __grid_constant__ TpMaps maps, CommDev c, TpParams p) {
   constexpr int BN = kTpBN;
   constexpr int kAB = kBlockM * kBlockK * 2;
-  const uint32_t idesc = p.fp8 ? make_idesc_e4m3(2 * kBlockM, BN) : make_idesc_bf16(2 * kBlockM, BN);
+  constexpr uint32_t idesc = FP8 ? make_idesc_e4m3(2 * kBlockM, BN) : make_idesc_bf16(2 * kBlockM, BN);
   extern __shared__ char smem_raw[];
   char* stages = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   char* obuf = stages + kPairStages * kPairStageBytes;
@@ -657,7 +696,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
           const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + kAB);
 #pragma unroll
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
-            if (p.fp8) {
+            if (FP8) {
               umma_f8_pair(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
             } else {
               umma_bf16_pair(tmem_acc, da + static_cast<uint64_t>(kk * 2), db + static_cast<uint64_t>(kk * 2), idesc, (kb | kk) != 0);
@@ -684,7 +723,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
         break;
       }
       tc_fence_after_sync();
-      const float row_scale = p.fp8 ? row_scale_of<MODE>(p, c, ord, tiles_per_src, mi * kBlockM + row_in_tile) : 1.0f;
+      const float row_scale = FP8 ? row_scale_of<MODE>(p, c, ord, tiles_per_src, mi * kBlockM + row_in_tile) : 1.0f;
       const CUtensorMap* mo = &maps.out[0];
       int out_row = mi * kBlockM;
       int owner = 0;
@@ -704,7 +743,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
                             static_cast<uint32_t>(j * kOutChunkCols + half * 32),
                         r);
           tmem_ld_wait();
-          if (p.fp8) scale_acc32(r, row_scale, p.scale_b, ni * BN + j * kOutChunkCols + half * 32, p.n);
+          if (FP8) scale_acc32(r, row_scale, p.scale_b, ni * BN + j * kOutChunkCols + half * 32, p.n);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             const int chunk16 = half * 4 + v;
@@ -777,7 +816,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
           for (; i < nvec; i += kCopyThreads) to[i] = from[i];
           fence_proxy_async();
         }
-        if (p.fp8 && blockIdx.x == 0 && ct < kBlockM) {  // the tile's row scales travel with it
+        if (FP8 && blockIdx.x == 0 && ct < kBlockM) {  // the tile's row scales travel with it
           p.scale_a_full[mi * kBlockM + ct] = p.scale_a_shards[src][(mi - src * tiles_per_src) * kBlockM + ct];
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
@@ -787,52 +826,36 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
         }
       }
     }
-  }
-
-  // ---------------- reduce phase of the reduce-scatter (per CTA, as in k_tp_gemm)
-  tc_fence_before_sync();
-  __syncthreads();
-  if (MODE == TpMode::GEMM_RS) {
-    const int my_tiles = tiles_per_src * tiles_n;
-    const int nthreads = blockDim.x;
-    for (int rt = blockIdx.x; rt < my_tiles; rt += G) {
-      if (threadIdx.x == 0) bars->reduce_ok = 1;
-      __syncthreads();
-      if (threadIdx.x < c.nranks) {
-        const uint32_t* flag = p.arrived[c.rank] + static_cast<size_t>(rt) * c.nranks + threadIdx.x;
-        if (!wait_flag_reached(c, flag, epoch + 1, threadIdx.x, 0xa3)) bars->reduce_ok = 0;
-      }
-      __syncthreads();
-      if (!bars->reduce_ok) {
-        bars->failed = 1;
-        break;
-      }
-      const int wm = rt / tiles_n, ni = rt % tiles_n;
-      const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.partials_local);
-      for (int v = threadIdx.x; v < kBlockM * BN / 8; v += nthreads) {
-        const int r = v / (BN / 8), cv = v % (BN / 8);
-        const size_t off = (static_cast<size_t>(wm * kBlockM + r)) * p.n + ni * BN + cv * 8;
-        float acc[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-        for (int s = 0; s < c.nranks; ++s) {
-          const uint4 q4 = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(s) * p.m_local * p.n + off);
-          const uint32_t* pw = &q4.x;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            acc[2 * i] += __uint_as_float(pw[i] << 16);
-            acc[2 * i + 1] += __uint_as_float(pw[i] & 0xffff0000u);
-          }
+    // ---------------- reduce warps (reduce-scatter mode), as in k_tp_gemm: every CTA takes its half of
+    // the pair tiles of this rank's own rows, in schedule order
+    if (MODE == TpMode::GEMM_RS) {
+      const int ct = threadIdx.x - kGemmThreads;
+      const int first_own = (c.nranks - 1) * tiles_per_src;
+      const int my_pair_tiles = (tiles_per_src / 2) * tiles_n;
+      for (int t_own = cluster_id; t_own < my_pair_tiles; t_own += nclusters) {
+        int ord, ni;
+        my_tile((first_own / 2) * tiles_n + t_own, &ord, &ni);
+        const int wm = ord - first_own;
+        if (ct == 0) bars->reduce_ok = 1;
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (ct < c.nranks) {
+          const uint32_t* flag = p.arrived[c.rank] + static_cast<size_t>(wm * tiles_n + ni) * c.nranks + ct;
+          if (!wait_flag_reached(c, flag, epoch + 1, ct, 0xa3)) bars->reduce_ok = 0;
         }
-        uint4 o;
-        uint32_t* po = &o.x;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) po[i] = pack_bf16(__float_as_uint(acc[2 * i]), __float_as_uint(acc[2 * i + 1]));
-        *reinterpret_cast<uint4*>(p.out + off) = o;
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (!bars->reduce_ok) {
+          if (ct == 0) bars->failed = 1;
+          break;
+        }
+        const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.partials_local);
+        reduce_tile<BN, 4, 4>(base, p.out, wm, ni, p.n, static_cast<size_t>(p.m_local) * p.n, c.nranks, ct, kCopyThreads);
+        asm volatile("bar.sync 2, 128;" ::: "memory");
       }
-      __syncthreads();
     }
   }
+
+  tc_fence_before_sync();
+  __syncthreads();
 
   // ---------------- teardown
   __syncthreads();
@@ -882,14 +905,20 @@ int pick_group(int tiles_per_src, int tile_rows, int k, int cap) {
   return limit;  // awkward counts: groups straddle sources, still correct
 }
 
-template <TpMode MODE>
-cudaError_t tp_launch(int grid, const TpMaps& maps, const CommDev& c, const TpParams& p, cudaStream_t stream) {
+template <TpMode MODE, bool FP8>
+cudaError_t tp_launch_t(int grid, const TpMaps& maps, const CommDev& c, const TpParams& p, cudaStream_t stream) {
   // Per device, so not cached in a process-wide flag.
-  cudaError_t e = cudaFuncSetAttribute(k_tp_gemm<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTpSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(k_tp_gemm<MODE, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTpSmemBytes);
   if (e != cudaSuccess) return e;
-  k_tp_gemm<MODE><<<grid, tp_threads<MODE>(), kTpSmemBytes, stream>>>(maps, c, p);
+  k_tp_gemm<MODE, FP8><<<grid, tp_threads<MODE>(), kTpSmemBytes, stream>>>(maps, c, p);
   note_kernel_launch();
   return cudaGetLastError();
+}
+
+// The operand type (p.fp8) picks the instantiation: the bf16 kernels carry no trace of the fp8 path.
+template <TpMode MODE>
+cudaError_t tp_launch(int grid, const TpMaps& maps, const CommDev& c, const TpParams& p, cudaStream_t stream) {
+  return p.fp8 ? tp_launch_t<MODE, true>(grid, maps, c, p, stream) : tp_launch_t<MODE, false>(grid, maps, c, p, stream);
 }
 
 // Pair kernels: on unless B200COMMS_TP_PAIRS=0; need two 128-row tiles per source rank.
@@ -902,9 +931,9 @@ bool use_pairs(int m_local) {
 }
 
 // `want_pairs` <= 0: as many pairs as the device holds at once.
-template <TpMode MODE>
-cudaError_t tp_launch_pair(int want_pairs, const TpMaps& maps, const CommDev& c, const TpParams& p, cudaStream_t stream) {
-  cudaError_t e = cudaFuncSetAttribute(k_tp_gemm_pair<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+template <TpMode MODE, bool FP8>
+cudaError_t tp_launch_pair_t(int want_pairs, const TpMaps& maps, const CommDev& c, const TpParams& p, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(k_tp_gemm_pair<MODE, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(tp_threads<MODE>());
@@ -919,14 +948,20 @@ cudaError_t tp_launch_pair(int want_pairs, const TpMaps& maps, const CommDev& c,
   cfg.numAttrs = 1;
   cfg.gridDim = dim3(2);
   int max_clusters = 0;
-  e = cudaOccupancyMaxActiveClusters(&max_clusters, k_tp_gemm_pair<MODE>, &cfg);
+  e = cudaOccupancyMaxActiveClusters(&max_clusters, k_tp_gemm_pair<MODE, FP8>, &cfg);
   if (e != cudaSuccess) return e;
   if (max_clusters < 1) return cudaErrorInvalidConfiguration;
   const int clusters = want_pairs > 0 ? std::min(max_clusters, want_pairs) : max_clusters;
   cfg.gridDim = dim3(2 * clusters);
-  e = cudaLaunchKernelEx(&cfg, k_tp_gemm_pair<MODE>, maps, c, p);
+  e = cudaLaunchKernelEx(&cfg, k_tp_gemm_pair<MODE, FP8>, maps, c, p);
   note_kernel_launch();
   return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+template <TpMode MODE>
+cudaError_t tp_launch_pair(int want_pairs, const TpMaps& maps, const CommDev& c, const TpParams& p, cudaStream_t stream) {
+  return p.fp8 ? tp_launch_pair_t<MODE, true>(want_pairs, maps, c, p, stream)
+               : tp_launch_pair_t<MODE, false>(want_pairs, maps, c, p, stream);
 }
 
 } // namespace
@@ -1059,16 +1094,21 @@ cudaError_t build_rs(const CommDev& comm, const GemmRsArgs& a, bool pairs, TpMap
   return cudaSuccess;
 }
 
-template <TpMode MODE>
-cudaError_t tp_launch_emu(const TpEmu& e, int nranks, cudaStream_t stream) {
-  cudaError_t err = cudaFuncSetAttribute(k_tp_gemm_emu<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTpSmemBytes);
+template <TpMode MODE, bool FP8>
+cudaError_t tp_launch_emu_t(const TpEmu& e, int nranks, cudaStream_t stream) {
+  cudaError_t err = cudaFuncSetAttribute(k_tp_gemm_emu<MODE, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTpSmemBytes);
   if (err != cudaSuccess) return err;
   const int per_rank = sm_count() / nranks;
   if (per_rank < 1) return cudaErrorInvalidConfiguration;
   void* params[] = {const_cast<TpEmu*>(&e)};
   note_kernel_launch();
-  return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(&k_tp_gemm_emu<MODE>), dim3(per_rank, nranks),
+  return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(&k_tp_gemm_emu<MODE, FP8>), dim3(per_rank, nranks),
                                      dim3(tp_threads<MODE>()), params, kTpSmemBytes, stream);
+}
+
+template <TpMode MODE>
+cudaError_t tp_launch_emu(const TpEmu& e, int nranks, cudaStream_t stream) {
+  return e.p[0].fp8 ? tp_launch_emu_t<MODE, true>(e, nranks, stream) : tp_launch_emu_t<MODE, false>(e, nranks, stream);
 }
 
 } // namespace

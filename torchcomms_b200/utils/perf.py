@@ -213,8 +213,12 @@ def moe_ep_latency(
     warmup: int = 10,
     iters: int = 50,
     with_nccl: bool = True,
+    ll_tokens: int = 128,
 ) -> List[dict]:
     """Dispatch / combine latency (microseconds, max over ranks), L2 flushed between calls.
+
+    ``ll_tokens`` > 0 adds the low-latency pair (``ll_dispatch`` / ``ll_combine``, arm ``fused``) on that many
+    tokens per rank: one row per (token, expert) pair into fixed slots, pull combine.
 
     Router logits ~N(0,1), softmax, top-k; x ~N(0,1) bf16. ``fused``: one kernel
     does routing counts, block-scaled fp8 (e4m3, 1x128) quantisation, token
@@ -304,4 +308,24 @@ def moe_ep_latency(
         report("combine", "nccl", time_it(nccl_combine), state["n"] * H * 2)
     torch.cuda.synchronize()
     del buf
+    if ll_tokens > 0:
+        from ..ops.moe_ep import LowLatencyBuffer
+
+        t2 = min(ll_tokens, T)
+        ll = LowLatencyBuffer(comm, max_tokens=t2, hidden=H, num_experts=E, topk=K, fp8=True)
+        x2, idx2, w2 = x[:t2].contiguous(), idx[:t2].contiguous(), w[:t2].contiguous()
+        r = ll.dispatch(x2, idx2)
+        torch.cuda.synchronize()
+        pairs = int((idx2 >= 0).sum())
+
+        def ll_report(phase, t, nbytes):
+            rows.append({"phase": phase, "arm": "fused", "avg_us": round(t[0], 1), "p50_us": round(t[1], 1),
+                         "gbs": round(nbytes / t[0] / 1e3, 1), "world": world, "tokens": t2, "hidden": H, "experts": E, "topk": K})
+
+        ll_report("ll_dispatch", time_it(lambda: ll.dispatch(x2, idx2)), pairs * (H + H // 128 * 4))
+        ll.expert_output.normal_()
+        out2 = torch.empty(t2, H, dtype=torch.bfloat16, device=device)
+        ll_report("ll_combine", time_it(lambda: ll.combine(idx2, w2, r, out=out2)), pairs * H * 2)
+        torch.cuda.synchronize()
+        del ll
     return rows
