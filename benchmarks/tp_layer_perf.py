@@ -5,7 +5,8 @@
 
 Default shape: the MLP of Llama-3-70B (hidden 8192, ffn 28672) on ``tokens``
 rows, sharded over the N ranks.  Timed per call on the device with CUDA
-events, an L2-sized scratch write between calls, maximum over ranks.
+events (median of the calls), an L2-sized scratch write and a barrier before
+each call, maximum over ranks.
 
 Arms:
   * ``fused``   - ops.tp.AllGatherGemm / GemmReduceScatter (one kernel each)
@@ -36,6 +37,43 @@ from torchcomms_b200 import _comms  # noqa: E402
 from torchcomms_b200.ops.tp import AllGatherGemm, GemmReduceScatter, gemm_e4m3_nt, quantize_rows  # noqa: E402
 
 
+PHASES = ["start", "loads issued", "MMAs committed", "tiles stored", "copy / forward warps done", "first own tile complete",
+          "reduce warps done", "CTA done", "closing barrier passed"]
+
+
+def phase_timeline(comm, dev, path, calls):
+    """One traced call of each fused kernel: when each phase ended on each CTA, relative to the earliest CTA start
+    on this GPU (the kernels stamp the GPU's nanosecond timer). Written by every rank into one text file each."""
+    impl = comm.get_backend_impl()
+    lines = []
+    for name, fn in calls.items():
+        for _ in range(2):
+            fn()
+        comm.barrier(False)
+        torch.cuda.synchronize()
+        trace = impl.enable_trace()
+        fn()
+        torch.cuda.synchronize()
+        impl.disable_trace()
+        t = trace.cpu()
+        used = t[:, 0] > 0
+        t0 = int(t[used, 0].min())
+        lines.append(f"## {name}: rank {comm.get_rank()} of {comm.get_size()}, {int(used.sum())} CTAs; microseconds after the first CTA started")
+        lines.append(f"{'phase':28s} {'CTAs':>5s} {'min':>9s} {'median':>9s} {'max':>9s}")
+        for slot, label in enumerate(PHASES):
+            col = t[used, slot]
+            col = col[col > 0]
+            if col.numel() == 0:
+                continue
+            us = (col - t0).double() / 1000.0
+            lines.append(f"{label:28s} {col.numel():5d} {float(us.min()):9.1f} {float(us.median()):9.1f} {float(us.max()):9.1f}")
+        lines.append("")
+    with open(f"{path}.rank{comm.get_rank()}", "w") as f:
+        f.write("\n".join(lines))
+    if comm.get_rank() == 0:
+        print("\n".join(lines), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=8192)
@@ -45,6 +83,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--chunks", type=int, default=4)
     ap.add_argument("--no-fp8", action="store_true")
+    ap.add_argument("--trace", default="", help="write the fused kernels' per-CTA phase timeline (text) to this file")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
 
@@ -60,20 +99,21 @@ def main():
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def time_it(fn):
+        """Median device time of one call (microseconds), maximum over ranks; the ranks start each call together."""
         for _ in range(args.warmup):
             fn()
-        comm.barrier(False)
-        torch.cuda.synchronize()
-        total = 0.0
+        per = []
         for _ in range(args.iters):
             flush.zero_()
+            comm.barrier(False)        # aligned start: a fused kernel would otherwise be billed for the peer's lag
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
             fn()
             e.record()
             e.synchronize()
-            total += s.elapsed_time(e)
-        t = torch.tensor([total * 1000.0 / args.iters], device=dev)
+            per.append(s.elapsed_time(e) * 1000.0)
+        per.sort()
+        t = torch.tensor([per[len(per) // 2]], device=dev)
         comm.all_reduce(t, tc.ReduceOp.MAX, False)
         return float(t.item())
 
@@ -119,6 +159,9 @@ def main():
 
     report("up", "fused", time_it(lambda: up(w_up)), f_up)
     report("down", "fused", time_it(lambda: down(h, w_down)), f_down)
+    if args.trace:
+        phase_timeline(comm, dev, args.trace, {"up (all-gather -> GEMM)": lambda: up(w_up),
+                                               "down (GEMM -> reduce-scatter)": lambda: down(h, w_down)})
     if world > 1:
         for arm, algo in (("unfused", "auto"), ("nccl", "nccl")):
             hint = {"algo": algo}

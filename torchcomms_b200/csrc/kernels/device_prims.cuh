@@ -354,6 +354,15 @@ __device__ __forceinline__ void trace_mark(const CommDev& c, int slot) {
   }
 }
 
+// Stamps the device's nanosecond timer into slot `slot` of this block's trace row. Call from ONE thread
+// (any thread: the fused GEMM kernels stamp from the warp that owns the phase). Comparable across the SMs
+// of one GPU, not across GPUs.
+__device__ __forceinline__ void trace_stamp_ns(const CommDev& c, int slot) {
+  if (c.trace != nullptr && slot < kTraceSlots) {
+    c.trace[static_cast<size_t>(blockIdx.x) * kTraceSlots + slot] = static_cast<long long>(globaltimer_ns());
+  }
+}
+
 // ------------------------------------------------------------- copies ------
 
 // Block-cooperative copy of `bytes` bytes. Uses 16-byte accesses when both

@@ -67,6 +67,7 @@ struct TpBarriers {
   uint32_t epoch;
   uint32_t is_last;
   int reduce_ok;
+  uint32_t fwd_ready;   // reduce-scatter: tiles for other ranks that the epilogue has put into the send staging
 };
 
 struct TpMaps {
@@ -74,7 +75,8 @@ struct TpMaps {
   CUtensorMap a_full;           // A rows in the gathered buffer (all-gather mode)
   CUtensorMap b;
   CUtensorMap b_half;           // box of 128 rows of B: what one CTA of a pair loads
-  CUtensorMap out[kMaxRanks];   // [0]: y; reduce-scatter: one per owner's staging
+  CUtensorMap out[kMaxRanks];   // [0]: y; reduce-scatter: [rank] = this rank's own receive staging
+  CUtensorMap out_send;         // reduce-scatter: local staging [m, n] of the partial tiles bound for other ranks
 };
 
 struct TpParams {
@@ -83,6 +85,8 @@ struct TpParams {
   char* x_full;
   // reduce-scatter mode
   const char* partials_local;
+  char* partials[kMaxRanks];     // every owner's receive staging [nranks, m_local, n] (peer pointers)
+  const char* send_stage;        // local [m_total, n] bf16
   uint32_t* arrived[kMaxRanks];
   __nv_bfloat16* out;
   // common
@@ -170,6 +174,43 @@ __device__ __forceinline__ TileCoord tile_at(int t, int tiles_m, int tiles_n, in
   return TileCoord{first + rem % gsz, rem / gsz};
 }
 
+// Traffic that is touched once (staged tiles on their way to the owner, the slots the owner sums): marked
+// evict-first so that it does not push the GEMM's operand tiles out of L2.
+__device__ __forceinline__ uint4 ld16_once(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st16_once(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Like wait_flag_reached, for warps that share an SM with the GEMM pipeline: sleeps between polls so that the
+// polling does not take issue slots from the producer, MMA and epilogue warps.
+__device__ __forceinline__ bool wait_flag_quietly(const CommDev& c, const uint32_t* addr, uint32_t want, int peer, uint32_t phase) {
+  unsigned long long start = 0, next_status = 0;
+  while (true) {
+    const uint32_t v = ld_relaxed_sys(addr);
+    if (static_cast<int32_t>(v - want) >= 0) {
+      fence_acq_rel_sys();
+      return true;
+    }
+    __nanosleep(200);
+    const unsigned long long now = globaltimer_ns();
+    if (start == 0) {
+      start = now;
+      next_status = now + 200000ull;
+    } else if (now >= next_status) {
+      next_status = now + 200000ull;
+      if (comm_is_dead(c)) return false;
+      if (now - start > c.timeout_ns) {
+        report_timeout(c, peer, phase);
+        return false;
+      }
+    }
+  }
+}
+
 // Sum of the `nslots` partial copies of one 128 x BN tile (bf16, fp32 accumulation) into `out`.
 // Every thread keeps U vectors of S slots in flight (U x S 16-byte loads): with four reduce warps per SM
 // it takes that many to run at memory speed rather than at the latency of a load.
@@ -195,7 +236,7 @@ __device__ __forceinline__ void reduce_tile(const __nv_bfloat16* __restrict__ ba
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           if (s0 + j < nslots && v0 + u * nthreads < kVecs) {
-            q[j][u] = ld16_stream(base + static_cast<size_t>(s0 + j) * slot_elems + off[u]);
+            q[j][u] = ld16_once(base + static_cast<size_t>(s0 + j) * slot_elems + off[u]);
           } else {
             q[j][u] = make_uint4(0u, 0u, 0u, 0u);
           }
@@ -221,12 +262,63 @@ __device__ __forceinline__ void reduce_tile(const __nv_bfloat16* __restrict__ ba
         uint32_t* po = &o.x;
 #pragma unroll
         for (int i = 0; i < 4; ++i) po[i] = pack_bf16(__float_as_uint(acc[u][2 * i]), __float_as_uint(acc[u][2 * i + 1]));
-        *reinterpret_cast<uint4*>(out + off[u]) = o;
+        st16_once(out + off[u], o);
       }
     }
   }
 }
 
+// Forward warps of the reduce-scatter: copy one 128 x BN bf16 tile from the local send staging (rows `src_row0`..
+// of a [*, n] matrix) to the owner's receive staging (rows `dst_row0`.. of its [*, n] matrix) with plain 16-byte
+// stores over NVLink, 8 per thread in flight.
+template <int BN>
+__device__ __forceinline__ void forward_tile(const char* __restrict__ src, char* __restrict__ dst, int src_row0, int dst_row0,
+                                             int col0, int n, int tid, int nthreads) {
+  constexpr int kVecs = kBlockM * BN / 8;
+  constexpr int U = 8;
+  for (int v0 = tid; v0 < kVecs; v0 += nthreads * U) {
+    uint4 q[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * nthreads;
+      if (v < kVecs) {
+        const int r = v / (BN / 8), cv = v % (BN / 8);
+        q[u] = ld16_once(src + ((static_cast<size_t>(src_row0 + r)) * n + col0 + cv * 8) * 2);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * nthreads;
+      if (v < kVecs) {
+        const int r = v / (BN / 8), cv = v % (BN / 8);
+        st16(dst + ((static_cast<size_t>(dst_row0 + r)) * n + col0 + cv * 8) * 2, q[u]);
+      }
+    }
+  }
+}
+
+// Waits (bounded, sleeping between polls) until the epilogue has handed over `want` tiles. One thread calls it.
+__device__ __forceinline__ bool wait_fwd_ready(const CommDev& c, TpBarriers* bars, uint32_t want) {
+  volatile uint32_t* ready = &bars->fwd_ready;
+  volatile uint32_t* failed = &bars->failed;
+  unsigned long long start = 0;
+  while (true) {
+    if (*failed != 0) return false;
+    if (*ready >= want) return true;
+    __nanosleep(200);
+    const unsigned long long now = globaltimer_ns();
+    if (start == 0) {
+      start = now;
+    } else if (now - start > kLocalWaitNs) {
+      return false;
+    }
+  }
+}
+
+// Phase stamps of the fused kernels (CommDev::trace, one row per CTA, nanoseconds of this GPU's timer):
+// 0 start, 1 last tile's loads issued, 2 last MMA committed, 3 last tile stored (and flagged), 4 copy warps
+// done (all-gather) or forward warps done (reduce-scatter), 5 first own tile complete on every rank (reduce-scatter), 6 reduce warps done, 7 CTA done,
+// 8 closing cross-GPU barrier passed (last CTA only).
 // Body of the single-CTA kernels. `maps` must live in kernel-parameter,
 // constant or global memory (its address goes to TMA).
 template <TpMode MODE, bool FP8>
@@ -257,6 +349,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
     }
     bars->failed = 0;
     bars->is_last = 0;
+    bars->fwd_ready = 0;
     bars->epoch = kFused ? ld_acquire_gpu(&p.ctrl[0]) : 0u;
     fence_barrier_init();
   }
@@ -269,6 +362,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
   const uint32_t epoch = bars->epoch;  // calls completed before this one
+  if (kFused && threadIdx.x == 0) trace_stamp_ns(c, 0);
 
   // m-tile ordinal -> real m-tile. All-gather: own rows first, then the
   // sources in ring order (the order in which the copy warps fetch them).
@@ -320,6 +414,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
           tma_load_2d(sa + Cfg::kABytes, &maps.b, &bars->full[s], kb * kBlockK, ni * BN);
         }
       }
+      if (kFused) trace_stamp_ns(c, 1);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer
@@ -356,6 +451,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
         }
         umma_commit(&bars->acc_full[as]);  // accumulator complete
       }
+      if (kFused) trace_stamp_ns(c, 2);
     }
   } else if (warp < 6) {
     // ---------------- epilogue: TMEM -> bf16 -> swizzled staging -> TMA store
@@ -379,9 +475,15 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
       int owner = 0;
       if (MODE == TpMode::GEMM_RS) {
         owner = mi / tiles_per_src;
-        mo = &maps.out[owner];
-        // slot `rank` of the owner's staging, viewed as [nranks * m_local, n]
-        out_row = c.rank * p.m_local + (mi - owner * tiles_per_src) * kBlockM;
+        if (owner == c.rank) {
+          // own rows: straight into slot `rank` of this rank's receive staging, viewed as [nranks * m_local, n]
+          mo = &maps.out[c.rank];
+          out_row = c.rank * p.m_local + (mi - owner * tiles_per_src) * kBlockM;
+        } else {
+          // another rank's rows: into the local send staging (a TMA store into peer memory drains far too
+          // slowly to keep up with the tensor cores); the forward warps move the tile on with plain stores
+          mo = &maps.out_send;
+        }
       }
       for (int j = 0; j < BN / kOutChunkCols; ++j, ++chunk_iter) {
         char* buf = obuf + (chunk_iter & 1u) * kOutChunkBytes;
@@ -418,14 +520,22 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
         }
       }
       if (MODE == TpMode::GEMM_RS && issuer) {
-        // Publish the tile to its owner once its four stores have landed.
+        // The tile's four stores have landed (local memory either way).
         tma_store_wait_all<0>();
-        __threadfence_system();
-        const int tile_local = (mi - owner * tiles_per_src) * tiles_n + ni;
-        st_relaxed_sys(p.arrived[owner] + static_cast<size_t>(tile_local) * c.nranks + c.rank, epoch + 1);
+        if (owner == c.rank) {
+          __threadfence_system();
+          const int tile_local = (mi - owner * tiles_per_src) * tiles_n + ni;
+          st_relaxed_sys(p.arrived[owner] + static_cast<size_t>(tile_local) * c.nranks + c.rank, epoch + 1);
+        } else {
+          __threadfence();
+          atomicAdd(&bars->fwd_ready, 1u);   // hand the tile to the forward warps
+        }
       }
     }
-    if (issuer) tma_store_wait_all<0>();
+    if (issuer) {
+      tma_store_wait_all<0>();
+      trace_stamp_ns(c, 3);
+    }
   } else {
     // ---------------- copy warps (all-gather mode): fetch the peers' shards
     if (MODE == TpMode::AG_GEMM) {
@@ -480,6 +590,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
           atomicAdd(&p.ctrl[kCtrlTiles + ord], 1u);
         }
       }
+      if (ct == 0) trace_stamp_ns(c, 4);
     }
     // ---------------- reduce warps (reduce-scatter mode): sum the nranks partial tiles of this rank's
     // rows as they arrive, in the order in which this rank produces its own (last) contribution, while
@@ -488,6 +599,34 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
       const int ct = threadIdx.x - kGemmThreads;
       const int my_tiles = tiles_per_src * tiles_n;
       const int first_own = (c.nranks - 1) * tiles_per_src;   // ordinal of this rank's first own m-tile
+      // First the tiles this CTA computes for other ranks (they come first in the schedule): as soon as the
+      // epilogue has put one into the send staging, move it into its owner's receive staging and flag it.
+      uint32_t handed = 0;
+      bool fwd_ok = true;
+      for (int t = blockIdx.x; t < first_own * tiles_n && fwd_ok; t += G) {
+        const TileCoord tc_ = tile_at(t, tiles_m, tiles_n, p.gm);
+        const int mi = mtile_of(tc_.ord), ni = tc_.ni;
+        const int owner = mi / tiles_per_src;
+        ++handed;
+        if (ct == 0) bars->reduce_ok = wait_fwd_ready(c, bars, handed) ? 1 : 0;
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        fwd_ok = bars->reduce_ok != 0;
+        if (fwd_ok) {
+          const int local_row = (mi - owner * tiles_per_src) * kBlockM;
+          forward_tile<BN>(p.send_stage, p.partials[owner], mi * kBlockM, c.rank * p.m_local + local_row, ni * BN, p.n, ct,
+                           kCopyThreads);
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (fwd_ok && ct == 0) {
+          __threadfence_system();
+          const int tile_local = (mi - owner * tiles_per_src) * tiles_n + ni;
+          st_relaxed_sys(p.arrived[owner] + static_cast<size_t>(tile_local) * c.nranks + c.rank, epoch + 1);
+        }
+      }
+      if (ct == 0) {
+        if (!fwd_ok) bars->failed = 1;
+        trace_stamp_ns(c, 4);
+      }
       for (int t_own = blockIdx.x; t_own < my_tiles; t_own += G) {
         const TileCoord tc_ = tile_at(first_own * tiles_n + t_own, tiles_m, tiles_n, p.gm);
         const int wm = tc_.ord - first_own, ni = tc_.ni;
@@ -495,17 +634,19 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (ct < c.nranks) {
           const uint32_t* flag = p.arrived[c.rank] + static_cast<size_t>(wm * tiles_n + ni) * c.nranks + ct;
-          if (!wait_flag_reached(c, flag, epoch + 1, ct, 0xa3)) bars->reduce_ok = 0;
+          if (!wait_flag_quietly(c, flag, epoch + 1, ct, 0xa3)) bars->reduce_ok = 0;
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (!bars->reduce_ok) {
           if (ct == 0) bars->failed = 1;
           break;
         }
+        if (ct == 0 && t_own < G) trace_stamp_ns(c, 5);
         const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.partials_local);
         reduce_tile<BN, 4, 4>(base, p.out, wm, ni, p.n, static_cast<size_t>(p.m_local) * p.n, c.nranks, ct, kCopyThreads);
         asm volatile("bar.sync 2, 128;" ::: "memory");
       }
+      if (ct == 0) trace_stamp_ns(c, 6);
     }
   }
 
@@ -523,6 +664,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
     return;
   }
   if (threadIdx.x == 0) {
+    trace_stamp_ns(c, 7);
     if (bars->failed) c.status[0] = c.status[0] | kStatusTimeout;
     __threadfence();
     const uint32_t ticket = atomicAdd(&p.ctrl[1], 1u);
@@ -533,6 +675,7 @@ __device__ __forceinline__ void tp_gemm_body(const TpMaps& maps, const CommDev& 
     __threadfence();
     warp_rank_barrier(c, 1, 0xa2);
     if (lane == 0) {
+      trace_stamp_ns(c, 8);
       p.ctrl[1] = 0;
       __threadfence();
       atomicExch(&p.ctrl[0], epoch + 1);
@@ -604,6 +747,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
     }
     bars->failed = 0;
     bars->is_last = 0;
+    bars->fwd_ready = 0;
     bars->epoch = ld_acquire_gpu(&p.ctrl[0]);
     fence_barrier_init();
   }
@@ -617,6 +761,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
   const uint32_t epoch = bars->epoch;
+  if (threadIdx.x == 0) trace_stamp_ns(c, 0);
 
   // 128-row m-tile ordinal -> real m-tile (same order as k_tp_gemm).
   auto mtile_of = [&](int ord) {
@@ -671,6 +816,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
           tma_load_2d_pair(sa + kAB, &maps.b_half, &bars->full[s], kb * kBlockK, b_row);
         }
       }
+      trace_stamp_ns(c, 1);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader only)
@@ -706,6 +852,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
         }
         umma_commit_pair(&bars->acc_full[as], 3);
       }
+      trace_stamp_ns(c, 2);
     }
   } else if (warp < 6) {
     // ---------------- epilogue (both CTAs, own 128 rows)
@@ -729,8 +876,12 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
       int owner = 0;
       if (MODE == TpMode::GEMM_RS) {
         owner = mi / tiles_per_src;
-        mo = &maps.out[owner];
-        out_row = c.rank * p.m_local + (mi - owner * tiles_per_src) * kBlockM;
+        if (owner == c.rank) {
+          mo = &maps.out[c.rank];
+          out_row = c.rank * p.m_local + (mi - owner * tiles_per_src) * kBlockM;
+        } else {
+          mo = &maps.out_send;   // forwarded by the forward warps, see k_tp_gemm
+        }
       }
       for (int j = 0; j < BN / kOutChunkCols; ++j, ++chunk_iter) {
         char* buf = obuf + (chunk_iter & 1u) * kOutChunkBytes;
@@ -766,12 +917,20 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
       }
       if (MODE == TpMode::GEMM_RS && issuer) {
         tma_store_wait_all<0>();
-        __threadfence_system();
-        const int tile_local = (mi - owner * tiles_per_src) * tiles_n + ni;
-        st_relaxed_sys(p.arrived[owner] + static_cast<size_t>(tile_local) * c.nranks + c.rank, epoch + 1);
+        if (owner == c.rank) {
+          __threadfence_system();
+          const int tile_local = (mi - owner * tiles_per_src) * tiles_n + ni;
+          st_relaxed_sys(p.arrived[owner] + static_cast<size_t>(tile_local) * c.nranks + c.rank, epoch + 1);
+        } else {
+          __threadfence();
+          atomicAdd(&bars->fwd_ready, 1u);
+        }
       }
     }
-    if (issuer) tma_store_wait_all<0>();
+    if (issuer) {
+      tma_store_wait_all<0>();
+      trace_stamp_ns(c, 3);
+    }
   } else {
     // ---------------- copy warps (all-gather mode), every CTA of the grid takes a slice of every remote m-tile
     if (MODE == TpMode::AG_GEMM) {
@@ -825,6 +984,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
           atomicAdd(&p.ctrl[kCtrlTiles + ord], 1u);
         }
       }
+      if (ct == 0) trace_stamp_ns(c, 4);
     }
     // ---------------- reduce warps (reduce-scatter mode), as in k_tp_gemm: every CTA takes its half of
     // the pair tiles of this rank's own rows, in schedule order
@@ -832,6 +992,34 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
       const int ct = threadIdx.x - kGemmThreads;
       const int first_own = (c.nranks - 1) * tiles_per_src;
       const int my_pair_tiles = (tiles_per_src / 2) * tiles_n;
+      // forward this CTA's half of the pair tiles computed for other ranks (see k_tp_gemm)
+      uint32_t handed = 0;
+      bool fwd_ok = true;
+      for (int t = cluster_id; t < (first_own / 2) * tiles_n && fwd_ok; t += nclusters) {
+        int ord, ni;
+        my_tile(t, &ord, &ni);
+        const int mi = mtile_of(ord);
+        const int owner = mi / tiles_per_src;
+        ++handed;
+        if (ct == 0) bars->reduce_ok = wait_fwd_ready(c, bars, handed) ? 1 : 0;
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        fwd_ok = bars->reduce_ok != 0;
+        if (fwd_ok) {
+          const int local_row = (mi - owner * tiles_per_src) * kBlockM;
+          forward_tile<BN>(p.send_stage, p.partials[owner], mi * kBlockM, c.rank * p.m_local + local_row, ni * BN, p.n, ct,
+                           kCopyThreads);
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (fwd_ok && ct == 0) {
+          __threadfence_system();
+          const int tile_local = (mi - owner * tiles_per_src) * tiles_n + ni;
+          st_relaxed_sys(p.arrived[owner] + static_cast<size_t>(tile_local) * c.nranks + c.rank, epoch + 1);
+        }
+      }
+      if (ct == 0) {
+        if (!fwd_ok) bars->failed = 1;
+        trace_stamp_ns(c, 4);
+      }
       for (int t_own = cluster_id; t_own < my_pair_tiles; t_own += nclusters) {
         int ord, ni;
         my_tile((first_own / 2) * tiles_n + t_own, &ord, &ni);
@@ -840,17 +1028,19 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (ct < c.nranks) {
           const uint32_t* flag = p.arrived[c.rank] + static_cast<size_t>(wm * tiles_n + ni) * c.nranks + ct;
-          if (!wait_flag_reached(c, flag, epoch + 1, ct, 0xa3)) bars->reduce_ok = 0;
+          if (!wait_flag_quietly(c, flag, epoch + 1, ct, 0xa3)) bars->reduce_ok = 0;
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (!bars->reduce_ok) {
           if (ct == 0) bars->failed = 1;
           break;
         }
+        if (ct == 0 && t_own < nclusters) trace_stamp_ns(c, 5);
         const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(p.partials_local);
         reduce_tile<BN, 4, 4>(base, p.out, wm, ni, p.n, static_cast<size_t>(p.m_local) * p.n, c.nranks, ct, kCopyThreads);
         asm volatile("bar.sync 2, 128;" ::: "memory");
       }
+      if (ct == 0) trace_stamp_ns(c, 6);
     }
   }
 
@@ -864,6 +1054,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
     tmem_dealloc_pair(tmem_base, 2 * BN);
   }
   if (threadIdx.x == 0) {
+    trace_stamp_ns(c, 7);
     if (bars->failed) c.status[0] = c.status[0] | kStatusTimeout;
     __threadfence();
     const uint32_t ticket = atomicAdd(&p.ctrl[1], 1u);
@@ -874,6 +1065,7 @@ __global__ void __launch_bounds__(tp_threads<MODE>(), 1) k_tp_gemm_pair(const __
     __threadfence();
     warp_rank_barrier(c, 1, 0xa2);
     if (lane == 0) {
+      trace_stamp_ns(c, 8);
       p.ctrl[1] = 0;
       __threadfence();
       atomicExch(&p.ctrl[0], epoch + 1);
@@ -1067,14 +1259,23 @@ cudaError_t build_rs(const CommDev& comm, const GemmRsArgs& a, bool pairs, TpMap
     return cudaErrorInvalidValue;
   }
   maps.a_full = maps.a_local;
+  // TMA stores stay on this GPU: own rows go into this rank's receive staging (viewed as [m, n]), the other
+  // ranks' rows into the local send staging, from where the forward warps push them with plain stores.
+  if (comm.nranks > 1 && a.send_stage == nullptr) return cudaErrorInvalidValue;
+  if (!make_map(&maps.out[comm.rank], a.partials[comm.rank], a.m, a.n, kBlockM)) return cudaErrorInvalidValue;
   for (int r = 0; r < kMaxRanks; ++r) {
-    // Stores only (never a load, never multicast): the owner's staging viewed as [m, n].
-    const void* base = r < comm.nranks ? a.partials[r] : a.partials[comm.rank];
-    if (!make_map(&maps.out[r], base, a.m, a.n, kBlockM)) return cudaErrorInvalidValue;
+    if (r != comm.rank) maps.out[r] = maps.out[comm.rank];
+  }
+  if (!make_map(&maps.out_send, comm.nranks > 1 ? a.send_stage : a.partials[comm.rank], a.m, a.n, kBlockM)) {
+    return cudaErrorInvalidValue;
   }
   p = TpParams{};
   p.partials_local = static_cast<const char*>(a.partials[comm.rank]);
-  for (int r = 0; r < comm.nranks; ++r) p.arrived[r] = a.arrived[r];
+  p.send_stage = static_cast<const char*>(a.send_stage);
+  for (int r = 0; r < comm.nranks; ++r) {
+    p.arrived[r] = a.arrived[r];
+    p.partials[r] = static_cast<char*>(a.partials[r]);
+  }
   p.out = static_cast<__nv_bfloat16*>(a.out);
   p.ctrl = a.ctrl;
   p.m_total = a.m;

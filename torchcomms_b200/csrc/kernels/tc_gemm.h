@@ -64,12 +64,16 @@ cudaError_t launch_allgather_gemm(const CommDev& comm, const AgGemmArgs& args, c
 // Row-parallel layer fused with the reduce-scatter of its output.
 // h [m, k_local] bf16 local, w [n, k_local] local; every rank computes the
 // partial product for all m rows; rows [r*m/nranks, (r+1)*m/nranks) belong to
-// rank r. The epilogue stores each partial tile straight into the owner's
-// `partials` staging over NVLink (symmetric; partials[r] = owner r's buffer
-// of [nranks, m/nranks, n] bf16, slot index = source rank) and raises the
-// tile's flag there; the owner sums the nranks slots in fp32 into `out`
-// [m/nranks, n] bf16 as they arrive. Tiles for the next rank are computed
-// first, the rank's own last. m % (128*nranks) == 0, n % 256 == 0,
+// rank r. The epilogue TMA-stores each partial tile into local memory: a
+// tile of this rank's own rows straight into its `partials` staging, a tile
+// of another rank's rows into `send_stage` (local, [m, n] bf16), from where
+// four forward warps per CTA push it into the owner's `partials` staging with
+// plain 16-byte stores over NVLink (symmetric; partials[r] = owner r's buffer
+// of [nranks, m/nranks, n] bf16, slot index = source rank) and raise the
+// tile's flag there. The same warps then sum the nranks slots of this rank's
+// rows in fp32 into `out` [m/nranks, n] bf16 as the flags arrive, while the
+// tensor cores finish the remaining tiles. Tiles for the next rank are
+// computed first, the rank's own last. m % (128*nranks) == 0, n % 256 == 0,
 // k_local % 64 == 0.
 // `arrived` (symmetric, arrived[r] on owner r, zeroed once): one uint32 per
 // (tile of the owner's rows, source). `ctrl`: as above (tp_ctrl_words(0)).
@@ -77,6 +81,7 @@ struct GemmRsArgs {
   const void* h;
   const void* w;
   void* partials[kMaxRanks];
+  void* send_stage;   // local [m, n] bf16 (may be null on a single rank)
   uint32_t* arrived[kMaxRanks];
   void* out;
   int m, n, k_local;

@@ -88,6 +88,13 @@ class TpLayer {
       local_.push_back(full);
       x_full_ = full;
     }
+    if (!ag_ && nranks_ > 1) {
+      // partial tiles bound for other ranks are staged here before the forward warps push them
+      void* st = nullptr;
+      B200C_CUDA_CHECK(cudaMalloc(&st, static_cast<size_t>(rows) * cols * 2));
+      local_.push_back(st);
+      send_stage_ = st;
+    }
     if (ag_ && fp8) {
       void* sf = nullptr;
       B200C_CUDA_CHECK(cudaMalloc(&sf, static_cast<size_t>(rows) * nranks_ * 4));
@@ -186,6 +193,7 @@ class TpLayer {
       a.partials[p] = bases_[p];
       a.arrived[p] = reinterpret_cast<uint32_t*>(bases_[p] + data_bytes_);
     }
+    a.send_stage = send_stage_;
     a.out = out.data_ptr();
     a.m = rows_;
     a.n = cols_;
@@ -217,6 +225,7 @@ class TpLayer {
   int rows_, cols_;
   bool fp8_ = false;
   float* scale_full_ = nullptr;
+  void* send_stage_ = nullptr;
   int nranks_ = 1, rank_ = 0;
   size_t data_bytes_ = 0, flag_bytes_ = 0;
   std::shared_ptr<SymmSegment> seg_;
@@ -267,6 +276,7 @@ class TpEmuWorld {
       ctrl_.push_back(static_cast<uint32_t*>(zeroed(tp_ctrl_words(ag_ ? rows * nranks : 0) * sizeof(uint32_t))));
       x_full_.push_back(ag_ ? zeroed(static_cast<size_t>(rows) * nranks * cols * 2) : nullptr);
       scale_full_.push_back(ag_ && fp8 ? static_cast<float*>(zeroed(static_cast<size_t>(rows) * nranks * 4)) : nullptr);
+      send_stage_.push_back(!ag_ && nranks > 1 ? zeroed(static_cast<size_t>(rows) * cols * 2) : nullptr);
     }
     comms_.resize(nranks);
     for (int r = 0; r < nranks; ++r) {
@@ -372,6 +382,7 @@ class TpEmuWorld {
         a.partials[p] = bases_[p];
         a.arrived[p] = reinterpret_cast<uint32_t*>(bases_[p] + data_bytes_);
       }
+      a.send_stage = send_stage_[r];
       a.out = outs[r].data_ptr();
       a.m = rows_;
       a.n = cols_;
@@ -393,6 +404,7 @@ class TpEmuWorld {
   std::vector<uint32_t*> ctrl_;
   std::vector<void*> x_full_;
   std::vector<float*> scale_full_;
+  std::vector<void*> send_stage_;
   std::vector<void*> allocs_;
   std::vector<CommDev> comms_;
   uint32_t* status_host_ = nullptr;
