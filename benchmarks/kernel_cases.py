@@ -9,6 +9,11 @@
     python benchmarks/kernel_cases.py --case ep              # MoE dispatch + combine, 8 virtual ranks
     python benchmarks/kernel_cases.py --case ar_norm         # fused all-reduce + residual + RMSNorm, 8 virtual ranks
     python benchmarks/kernel_cases.py --case model           # RMSNorm, SwiGLU, cross-entropy, AdamW
+    python benchmarks/kernel_cases.py --case gemm_fp8        # e4m3 GEMM with row / channel scales, 8192 x 4096 x 4096
+    python benchmarks/kernel_cases.py --case gemm_rs_fp8     # fused GEMM -> reduce-scatter kernel on e4m3 operands, single rank
+    python benchmarks/kernel_cases.py --case symm            # one-pass all-gather / reduce-scatter / all-reduce, 8 virtual ranks, 32 MB
+    python benchmarks/kernel_cases.py --case lamport         # flag-less small all-reduce, 8 virtual ranks, 16 KB
+    python benchmarks/kernel_cases.py --case ep_ll           # low-latency MoE dispatch + combine, 8 virtual ranks x 128 tokens
 
 Each case runs ``--warmup`` untimed and ``--iters`` timed launches (CUDA events,
 L2-sized scratch write between launches) and prints one line per kernel with
@@ -139,6 +144,57 @@ def main():
         rows = sum(int(buf.view(r, "recv_info")[0]) for r in range(nranks))
         print(f"ep dispatch, {nranks} virtual ranks x {tokens} tokens: {us_d:.1f} us ({rows} rows, fp8 + scales {rows * (hidden + hidden // 128 * 4) / us_d / 1e3:.0f} GB/s)")
         print(f"ep combine: {us_c:.1f} us ({rows * hidden * 2 / us_c / 1e3:.0f} GB/s) status {buf.status()[:1]}")
+    elif args.case == "gemm_fp8":
+        from torchcomms_b200.ops.tp import gemm_e4m3_nt, quantize_rows
+
+        m, n, k = 8192, 4096, 4096
+        (qa, sa), (qb, sb) = quantize_rows(rnd(m, k, scale=0.5)), quantize_rows(rnd(n, k, scale=0.05))
+        us = timed(lambda: gemm_e4m3_nt(qa, qb, sa, sb), args.warmup, args.iters, flush)
+        ref = timed(lambda: torch._scaled_mm(qa, qb.t(), scale_a=sa.unsqueeze(1), scale_b=sb.unsqueeze(0), out_dtype=bf),
+                    args.warmup, args.iters, flush)
+        fl = 2.0 * m * n * k / 1e6
+        print(f"gemm e4m3 tcgen05 {m}x{n}x{k}: {us:.1f} us {fl / us:.1f} TFLOP/s; torch._scaled_mm {ref:.1f} us {fl / ref:.1f} TFLOP/s")
+    elif args.case == "gemm_rs_fp8":
+        from torchcomms_b200.ops.tp import GemmReduceScatter, quantize_rows
+
+        m, n, k = 8192, 4096, 4096
+        layer = GemmReduceScatter(None, m, n, fp8=True)
+        (qh, sh), (qw, sw) = quantize_rows(rnd(m, k, scale=0.5)), quantize_rows(rnd(n, k, scale=0.05))
+        us = timed(lambda: layer(qh, qw, sh, sw), args.warmup, args.iters, flush)
+        print(f"gemm_rs e4m3 single rank {m}x{n}x{k}: {us:.1f} us {2.0 * m * n * k / us / 1e6:.1f} TFLOP/s status {layer.status()[:1]}")
+    elif args.case == "symm":
+        nranks, count = 8, 2 * 1024 * 1024  # 4 MB bf16 per rank part, 32 MB gathered
+        w = _comms._EmuWorld(nranks, 8 << 20, 2000.0)
+        parts = [rnd(count) for _ in range(nranks)]
+        full = [rnd(nranks * count) for _ in range(nranks)]
+        outs = [torch.empty(count, dtype=bf, device=dev) for _ in range(nranks)]
+        us = timed(lambda: w.symm_all_gather(parts, full, False, 16), args.warmup, args.iters, flush)
+        print(f"symm all_gather, {nranks} virtual ranks x {count * 2 >> 20} MB: {us:.1f} us ({nranks * nranks * count * 2 / us / 1e3:.0f} GB/s of stores)")
+        us = timed(lambda: w.symm_reduce_scatter(full, outs, 1.0, 16), args.warmup, args.iters, flush)
+        print(f"symm reduce_scatter, {nranks} virtual ranks x {nranks * count * 2 >> 20} MB in: {us:.1f} us ({nranks * nranks * count * 2 / us / 1e3:.0f} GB/s of loads)")
+        us = timed(lambda: w.symm_all_reduce(full, 1.0 / nranks, 16), args.warmup, args.iters, flush)
+        print(f"symm all_reduce in place, {nranks} virtual ranks x {nranks * count * 2 >> 20} MB: {us:.1f} us")
+        print("status", w.status()[:1])
+    elif args.case == "lamport":
+        nranks, count = 8, 8 * 1024  # 16 KB bf16 per rank
+        w = _comms._EmuWorld(nranks, 8 << 20, 2000.0)
+        ins = [rnd(count) for _ in range(nranks)]
+        outs = [torch.empty_like(t) for t in ins]
+        us = timed(lambda: w.all_reduce_lamport(ins, outs, 1.0), args.warmup, args.iters, flush)
+        print(f"all_reduce flag-less, {nranks} virtual ranks x {count * 2} B: {us:.1f} us (includes the emulation launch's host sync) status {w.status()[:1]}")
+    elif args.case == "ep_ll":
+        nranks, tokens, hidden, experts, topk = 8, 128, 7168, 256, 8
+        buf = _comms.EpLlBuffer.emulated(nranks, tokens, hidden, experts, topk, True, 2000.0)
+        xs = [rnd(tokens, hidden) for _ in range(nranks)]
+        routes = [torch.softmax(torch.randn(tokens, experts, device=dev), -1).topk(topk, -1) for _ in range(nranks)]
+        ws = [r[0].float().contiguous() for r in routes]
+        idxs = [r[1].to(torch.int32).contiguous() for r in routes]
+        us_d = timed(lambda: buf.dispatch(xs, idxs), args.warmup, args.iters, flush)
+        outs = [torch.empty(tokens, hidden, dtype=bf, device=dev) for _ in range(nranks)]
+        us_c = timed(lambda: buf.combine(outs, idxs, ws), args.warmup, args.iters, flush)
+        pairs = nranks * tokens * topk
+        print(f"ep low-latency dispatch, {nranks} virtual ranks x {tokens} tokens: {us_d:.1f} us ({pairs} rows)")
+        print(f"ep low-latency combine: {us_c:.1f} us status {buf.status()[:1]}")
     elif args.case == "model":
         rows, cols, vocab, ffn = 8192, 4096, 128256, 14336
         x, wn = rnd(rows, cols), rnd(cols)

@@ -24,3 +24,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _deterministic_inputs(request):
+    """Every test starts from the same random state (a test that wants other data seeds its own generator), so a
+    tolerance that holds once holds on every run."""
+    import zlib
+
+    import torch
+
+    torch.manual_seed(zlib.crc32(request.node.nodeid.encode()) & 0x7FFFFFFF)
+    yield

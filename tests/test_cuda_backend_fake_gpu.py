@@ -89,6 +89,30 @@ def test_sync_operation_takes_the_event_less_path_until_somebody_observes(single
     comm.finalize()
 
 
+def test_timestamp_ring_keeps_the_last_operations(single_rank_env):
+    """`colltrace=N`: one ring entry per operation issued outside a capture, oldest entries overwritten."""
+    import torchcomms_b200 as tc
+
+    comm = _new_comm("fake_trace", world_hints={"colltrace": "4"})
+    impl = comm.get_backend_impl()
+    assert impl.colltrace_dump() == []
+    t = torch.ones(256)
+    for _ in range(3):
+        comm.all_reduce(t, tc.ReduceOp.SUM, False)
+    comm.barrier(True).wait()
+    comm.all_reduce(t, tc.ReduceOp.SUM, True).wait()
+    out = torch.empty(256)
+    comm.all_gather_single(out, t, False)
+    entries = impl.colltrace_dump()
+    assert [e["seq"] for e in entries] == [2, 3, 4, 5], entries   # six operations, the ring holds four
+    assert entries[0]["op"].startswith("all_reduce/") and entries[1]["op"].startswith("barrier")
+    assert entries[3]["op"].startswith("all_gather")
+    assert all(e["start_ns"] == 0 and e["end_ns"] == 0 for e in entries)   # nothing runs under the fake runtime
+    d = impl.comm_dump()
+    assert d["colltrace/entries"] == "4" and d["colltrace/issued"] == "6"
+    comm.finalize()
+
+
 def test_async_operation_protocol_and_cross_stream_order(single_rank_env):
     fake = single_rank_env
     import torchcomms_b200 as tc

@@ -132,7 +132,7 @@ def _battery(rank, world, backend_name="b200"):
     comm.reduce_scatter_v(out, [ones(s) for s in shares], tc.ReduceOp.SUM, False)
     torch.cuda.synchronize()
     assert torch.equal(out, torch.full((shares[rank],), float(tri), device=dev))
-    shares = [50_000 if r == 0 else 3 for r in range(world)] if world > 2 else [90_000, 3]
+    shares = [90_000 if world < 3 else 50_000] + [3] * (world - 1)
     out = torch.empty(shares[rank], device=dev)
     comm.reduce_scatter_v(out, [ones(s) for s in shares], tc.ReduceOp.SUM, True).wait()
     torch.cuda.synchronize()
@@ -261,6 +261,29 @@ def test_every_operation_in_every_calling_variant():
     if world < 2:
         pytest.skip("needs 2 GPUs")
     run_ranks(_variant_matrix, world, timeout=240)
+
+
+def test_timestamp_ring_single_gpu():
+    """GPU-written start / end stamps per operation (`colltrace` hint), read from mapped host memory."""
+    import torchcomms_b200 as tc
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29641")
+    os.environ["RANK"], os.environ["WORLD_SIZE"] = "0", "1"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    comm = tc.new_comm("b200", dev, name="ring", hints={"colltrace": "8"}, abort_process_on_timeout_or_error=False)
+    impl = comm.get_backend_impl()
+    t = torch.ones(1 << 20, device=dev)
+    for i in range(5):
+        comm.all_reduce(t, tc.ReduceOp.SUM, i % 2 == 1).wait()
+    torch.cuda.synchronize()
+    entries = impl.colltrace_dump()
+    assert [e["seq"] for e in entries] == list(range(5))
+    for e in entries:
+        assert e["op"].startswith("all_reduce") and 0 < e["start_ns"] <= e["end_ns"], e
+    assert all(a["end_ns"] <= b["start_ns"] for a, b in zip(entries, entries[1:]))   # one stream order per channel
+    comm.finalize()
 
 
 def _stalled_peer(rank, world):

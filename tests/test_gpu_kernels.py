@@ -296,3 +296,36 @@ def test_device_window_ring_put_signal_barrier():
         assert torch.equal(dsts[r], srcs[left])
         assert int(counters[r].item()) == 1
     assert w.status()[0] == 0
+
+
+@pytest.mark.parametrize("nranks,nbytes,nslots,slot", [(2, 4096, 2, 1024), (4, 1 << 20, 2, 16384), (8, 300_000, 3, 65536), (3, 48, 1, 16)])
+def test_device_send_forward_recv_ring_broadcast(nranks, nbytes, nslots, slot):
+    """Device-side send / forward / recv through slot FIFOs: a pipelined broadcast along the ring, messages far
+    larger than the FIFO (the sender must wait for slots to come back), repeated calls, every root."""
+    from torchcomms_b200 import _comms
+
+    emu = _comms.P2pEmu(nranks, nslots, slot, 5000.0)
+    for it in range(3):
+        root = it % nranks
+        bufs = [torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device="cuda") for _ in range(nranks)]
+        want = bufs[root].clone()
+        emu.ring_broadcast(bufs, root)
+        assert emu.status()[0] == 0, emu.status()
+        for r in range(nranks):
+            assert torch.equal(bufs[r], want), (it, r)
+
+
+@pytest.mark.parametrize("nranks", [2, 8])
+def test_ll_packets_carry_their_own_flag(nranks):
+    from torchcomms_b200 import _comms
+
+    words = 1000
+    emu = _comms.P2pEmu(nranks, 1, 16, 5000.0)
+    tables = [torch.zeros(words, dtype=torch.int64, device="cuda") for _ in range(nranks)]
+    for epoch in (1, 2, 7):
+        outs = [torch.zeros(words, dtype=torch.int32, device="cuda") for _ in range(nranks)]
+        emu.ll_exchange(tables, outs, epoch)
+        assert emu.status()[0] == 0
+        for r in range(nranks):
+            prev = (r - 1) % nranks
+            assert torch.equal(outs[r], (torch.arange(words, device="cuda") + prev * 100000 + epoch).int())

@@ -15,6 +15,7 @@
 
 #include "../core/logging.hpp"
 #include "../kernels/fused_ops.h"
+#include "../kernels/window.h"
 
 namespace b200c {
 
@@ -285,6 +286,7 @@ void CudaBackend::parse_tuning(const Hints& h) {
   t.lamport_max_bytes = std::min(t.lamport_max_bytes, static_cast<size_t>(kLamportBlocks) * kLamportPiece);
   t.channel_streams = hint_or<bool>(h, "channel_streams", env_to_value<bool>("B200COMMS_CHANNEL_STREAMS", t.channel_streams));
   t.fast_sync = hint_or<bool>(h, "fast_sync", env_to_value<bool>("B200COMMS_FAST_SYNC", t.fast_sync));
+  t.colltrace = std::max(0, std::min(1 << 16, hint_or<int>(h, "colltrace", env_to_value<int>("B200COMMS_COLLTRACE", t.colltrace))));
   t.staging_bytes = std::max<size_t>(t.staging_bytes, 1u << 20);
   tune_ = t;
 }
@@ -386,6 +388,13 @@ void CudaBackend::bootstrap(const c10::intrusive_ptr<c10d::Store>& store, int ra
                                           reinterpret_cast<void**>(&replay_pool_dev_),
                                           2 * kMaxGraphEntries * sizeof(unsigned long long)));
   std::memset(replay_pool_host_, 0, 2 * kMaxGraphEntries * sizeof(unsigned long long));
+  if (tune_.colltrace > 0) {
+    const size_t bytes = 2 * static_cast<size_t>(tune_.colltrace) * sizeof(unsigned long long);
+    B200C_CUDA_CHECK(cuda_->hostAllocMapped(reinterpret_cast<void**>(&trace_ring_host_), reinterpret_cast<void**>(&trace_ring_dev_), bytes));
+    std::memset(trace_ring_host_, 0, bytes);
+    trace_meta_.assign(tune_.colltrace, {0, std::string()});
+    trace_next_ = 0;
+  }
 
   int lo = 0, hi = 0;
   B200C_CUDA_CHECK(cuda_->streamPriorityRange(&lo, &hi));
@@ -635,11 +644,13 @@ WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, st
     // Nobody follows this operation through work hooks, stream order gives
     // wait() its meaning, and a failed device wait shows in the status word
     // the watchdog reads: no events, nothing queued.
+    const int64_t tslot = colltrace_begin(what, stream);
     if (cuda_->is_real()) {
       launch(stream);
     } else {
       cuda_->noteLaunch(what, stream);
     }
+    colltrace_end(tslot, stream);
     cs.last_stream = stream;
     cs.last_work.reset();
     ops_issued_++;
@@ -713,6 +724,7 @@ WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, st
   }
 
   B200C_CUDA_CHECK(cuda_->eventRecord(ev_start, stream));
+  const int64_t tslot = capturing ? -1 : colltrace_begin(what, stream);
   if (!cuda_->is_real()) {
     // Under a test fake of the runtime nothing can be launched. Operations that
     // only call NCCL ("<op>/nccl") still run, against the NCCL fake.
@@ -727,6 +739,7 @@ WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, st
       B200C_CUDA_CHECK(launch_counter_increment(replay_counters + 1, stream));
     }
   }
+  colltrace_end(tslot, stream);
   B200C_CUDA_CHECK(cuda_->eventRecord(ev_end, stream));
   if (!async_op) {
     keep_alive.clear();  // stream order already protects the tensors
@@ -752,6 +765,37 @@ WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, st
     }
   }
   return work;
+}
+
+int64_t CudaBackend::colltrace_begin(const char* what, cudaStream_t stream) {
+  if (trace_ring_host_ == nullptr) return -1;
+  int64_t slot;
+  {
+    std::lock_guard<std::mutex> g(wd_mu_);
+    slot = static_cast<int64_t>(trace_next_ % trace_meta_.size());
+    trace_meta_[slot] = {trace_next_++, what};
+    trace_ring_host_[2 * slot] = trace_ring_host_[2 * slot + 1] = 0;
+  }
+  if (cuda_->is_real()) launch_timestamp(trace_ring_dev_ + 2 * slot, stream);
+  return slot;
+}
+
+void CudaBackend::colltrace_end(int64_t slot, cudaStream_t stream) {
+  if (slot >= 0 && cuda_->is_real()) launch_timestamp(trace_ring_dev_ + 2 * slot + 1, stream);
+}
+
+std::vector<CudaBackend::CollTraceEntry> CudaBackend::colltrace_dump() const {
+  std::vector<CollTraceEntry> out;
+  if (trace_ring_host_ == nullptr) return out;
+  std::lock_guard<std::mutex> g(const_cast<std::mutex&>(wd_mu_));
+  const uint64_t n = trace_meta_.size();
+  const uint64_t first = trace_next_ > n ? trace_next_ - n : 0;
+  for (uint64_t seq = first; seq < trace_next_; ++seq) {
+    const uint64_t slot = seq % n;
+    const volatile unsigned long long* w = trace_ring_host_ + 2 * slot;
+    out.push_back({trace_meta_[slot].first, trace_meta_[slot].second, w[0], w[1]});
+  }
+  return out;
 }
 
 void CudaBackend::sync_own_streams() {
@@ -953,6 +997,8 @@ void CudaBackend::drain_and_release(bool broken, const char* why) {
   }
   if (replay_pool_host_) cuda_->freeHost(replay_pool_host_);
   replay_pool_host_ = nullptr;
+  if (trace_ring_host_) cuda_->freeHost(trace_ring_host_);
+  trace_ring_host_ = nullptr;
   if (nccl_comm_ != nullptr) {
     if (broken) {
       nccl_->commAbort(nccl_comm_);
@@ -2083,6 +2129,8 @@ std::unordered_map<std::string, std::string> CudaBackend::comm_dump() const {
   {
     std::lock_guard<std::mutex> g(const_cast<std::mutex&>(wd_mu_));
     d["inflight"] = std::to_string(inflight_.size());
+    d["colltrace/entries"] = std::to_string(trace_meta_.size());
+    d["colltrace/issued"] = std::to_string(trace_next_);
     d["graph_entries"] = std::to_string(graph_entries_.size());
     d["graphs"] = std::to_string(graphs_.size());
     for (auto& kv : algo_counts_) {

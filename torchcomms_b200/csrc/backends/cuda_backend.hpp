@@ -125,6 +125,7 @@ struct Tuning {
   size_t lamport_max_bytes = 1024 * 1024;  // flag-less kernels up to this many bytes per message / per-rank part (0 = off)
   bool channel_streams = true;             // asynchronous operations of different channels get streams of their own
   bool fast_sync = true;                   // unobserved synchronous kernel operations skip the event pair
+  int colltrace = 0;                       // > 0: GPU-written start / end timestamps of the last N operations
   bool use_multicast = true;
   bool use_nccl = true;                    // create the NCCL communicator at init
   Algo force = Algo::AUTO;                 // B200COMMS_ALGO / hint "algo"
@@ -207,6 +208,16 @@ class CudaBackend final : public Backend {
   WorkPtr reduce_scatter_quantized(at::Tensor& out, const at::Tensor& in, const ReduceOp& op, int64_t seed,
                                    bool async_op, const OpOptions& o);
   std::unordered_map<std::string, std::string> comm_dump() const override;
+  // The timestamp ring (hint / variable `colltrace` = number of entries): for each of the last N operations that
+  // were issued outside a graph capture, its sequence number, route name, and the device's nanosecond timer when
+  // the stream reached the operation and when it left it (0 = not reached yet). Written by the GPU into mapped
+  // host memory, read here without touching the GPU.
+  struct CollTraceEntry {
+    uint64_t seq;
+    std::string op;
+    unsigned long long start_ns, end_ns;
+  };
+  std::vector<CollTraceEntry> colltrace_dump() const;
   void set_config(const Hints& h) { set_hints(h); }
   uintptr_t get_nccl_comm_ptr() const { return reinterpret_cast<uintptr_t>(nccl_comm_); }
   // Kernel phase trace (performance work): kMaxBlocks x kTraceSlots int64
@@ -348,6 +359,14 @@ class CudaBackend final : public Backend {
     uintptr_t stream;
     Millis timeout;
   };
+  // Timestamp ring: two mapped words per entry, and what each entry describes.
+  unsigned long long* trace_ring_host_ = nullptr;
+  unsigned long long* trace_ring_dev_ = nullptr;
+  std::vector<std::pair<uint64_t, std::string>> trace_meta_;
+  uint64_t trace_next_ = 0;
+  // Stamps the ring before (`end` = false) or after the launch; returns the slot, or -1 when tracing is off.
+  int64_t colltrace_begin(const char* what, cudaStream_t stream);
+  void colltrace_end(int64_t slot, cudaStream_t stream);
   static constexpr size_t kMaxGraphEntries = 2048;
   unsigned long long* replay_pool_host_ = nullptr;  // 2 x kMaxGraphEntries counters, mapped pinned
   unsigned long long* replay_pool_dev_ = nullptr;

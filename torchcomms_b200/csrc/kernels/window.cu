@@ -43,6 +43,14 @@ __global__ void k_counter_inc(unsigned long long* counter) {
   atomicAdd_system(counter, 1ull);
 }
 
+__global__ void k_stamp_ns(unsigned long long* slot) {
+  // The device's nanosecond timer into mapped pinned host memory: when the stream reached this point.
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  *reinterpret_cast<volatile unsigned long long*>(slot) = t;
+  __threadfence_system();
+}
+
 // Ping-pong through the device API; exists for tests of DeviceWindow.
 __global__ void k_window_selftest(const DeviceWindow* wins, int nranks, RegisteredBuffer* srcs, size_t bytes) {
   const DeviceWindow& w = wins[blockIdx.y];
@@ -76,6 +84,11 @@ cudaError_t launch_window_signal(const DeviceWindow* dev_window, int dst_rank, i
 cudaError_t launch_window_wait_signal(const DeviceWindow* dev_window, int peer, int signal_id, uint64_t* expected,
                                       cudaStream_t stream) {
   k_window_wait<<<1, 1, 0, stream>>>(dev_window, peer, signal_id, expected);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_timestamp(unsigned long long* mapped_slot, cudaStream_t stream) {
+  k_stamp_ns<<<1, 1, 0, stream>>>(mapped_slot);
   return cudaGetLastError();
 }
 

@@ -16,6 +16,8 @@ cudaError_t launch_window_wait_signal(const DeviceWindow* dev_window, int peer, 
 // One-thread kernel that increments a counter in mapped pinned host memory;
 // captured into CUDA graphs so the watchdog can count replays.
 cudaError_t launch_counter_increment(unsigned long long* mapped_counter, cudaStream_t stream);
+// One thread writes the device's nanosecond timer (%globaltimer) into `mapped_slot` (mapped pinned host memory).
+cudaError_t launch_timestamp(unsigned long long* mapped_slot, cudaStream_t stream);
 // Test helper: every virtual rank puts to its right neighbour through the
 // device API, waits for its own signal and joins a barrier (one cooperative
 // launch over `nranks` windows on one GPU).

@@ -477,6 +477,7 @@ PYBIND11_MODULE(_comms, m) {
   b200c::bind_ops(m);
   b200c::bind_ep(m);
   b200c::bind_ep_ll(m);
+  b200c::bind_p2p(m);
   b200c::bind_tp(m);
   b200c::bind_transport(m);
   b200c::bind_arnorm(m);

@@ -67,6 +67,7 @@ void bind_cuda_backend(py::module_& m);
 void bind_ops(py::module_& m);
 void bind_ep(py::module_& m);
 void bind_ep_ll(py::module_& m);
+void bind_p2p(py::module_& m);
 void bind_tp(py::module_& m);
 void bind_transport(py::module_& m);
 void bind_arnorm(py::module_& m);

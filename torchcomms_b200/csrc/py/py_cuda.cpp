@@ -509,6 +509,18 @@ void bind_cuda_backend(py::module_& m) {
       })
       .def("channel_stream", [](CudaBackend& b, int chan) { return reinterpret_cast<uintptr_t>(b.channel_stream(chan)); })
       .def("comm_dump", &CudaBackend::comm_dump)
+      .def("colltrace_dump", [](CudaBackend& b) {
+        py::list out;
+        for (const auto& e : b.colltrace_dump()) {
+          py::dict d;
+          d["seq"] = e.seq;
+          d["op"] = e.op;
+          d["start_ns"] = e.start_ns;
+          d["end_ns"] = e.end_ns;
+          out.append(d);
+        }
+        return out;
+      })
       .def("set_config", &CudaBackend::set_config)
       .def("get_nccl_comm_ptr", &CudaBackend::get_nccl_comm_ptr)
       .def("enable_trace", [](CudaBackend& b) {
