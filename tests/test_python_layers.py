@@ -428,15 +428,19 @@ def test_reference_import_name():
 def test_trace_to_perfetto(tmp_path):
     import json
 
-    from torchcomms_b200.utils.trace_to_perfetto import flight_recorder_events, phase_trace_events, write_trace
+    from torchcomms_b200.utils.trace_to_perfetto import (flight_recorder_events, phase_summary, phase_trace_events,
+                                                          write_trace)
 
-    trace = torch.zeros(4, 16, dtype=torch.long)
-    trace[0, :4] = torch.tensor([1000, 2900, 4800, 8600])
-    trace[2, :3] = torch.tensor([1190, 3090, 3100])
-    ev = phase_trace_events(trace, rank=3, sm_mhz=1900.0, phases=("copy-in", "barrier", "reduce"))
+    trace = torch.zeros(4, 16, dtype=torch.long)          # nanoseconds of the device timer
+    trace[0, :4] = torch.tensor([1000, 2000, 3000, 5000])
+    trace[2, :3] = torch.tensor([1100, 2100, 2110])
+    ev = phase_trace_events(trace, rank=3, phases=("copy-in", "barrier", "reduce"))
     slices = [e for e in ev if e["ph"] == "X"]
     assert len(slices) == 5 and slices[0]["name"] == "copy-in" and abs(slices[0]["dur"] - 1.0) < 1e-6
     assert abs(slices[3]["ts"] - 0.1) < 1e-6 and {e["tid"] for e in slices} == {0, 2}
+    text = phase_summary(trace, ("copy-in", "barrier", "reduce"))
+    assert text[0].startswith("2 blocks") and "barrier" in text[3] and text[3].split()[1] == "2"
+    assert float(text[4].split()[-1]) == 4.0            # the reduce phase of block 0 ends 4 us after the first mark
     fr = {"rank": 3, "entries": [
         {"profiling_name": "all_reduce", "time_created_ns": 5_000, "time_discovered_started_ns": 6_000,
          "time_discovered_completed_ns": 16_000, "collective_seq_id": 1, "state": "completed"},

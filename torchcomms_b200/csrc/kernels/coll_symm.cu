@@ -405,6 +405,7 @@ struct SymA2a {
     __shared__ unsigned long long s_soff[kMaxRanks], s_slen[kMaxRanks], s_doff[kMaxRanks];
     BlockEpoch ep;
     ep.load(c, kFlagSetSymA2a);
+    trace_mark(c, 0);
     unsigned long long* meta_mine = reinterpret_cast<unsigned long long*>(c.heap[c.rank] + a.meta_off) +
         static_cast<size_t>(blockIdx.x) * kMaxRanks * 2;
     const bool dev = a.dev_send_counts != nullptr;
@@ -514,6 +515,7 @@ struct SymA2a {
       }
     }
     __syncthreads();
+    trace_mark(c, 1);
     if (ok) {
       // Block groups: blocks b, b + nranks, ... serve peer (rank + b) % nranks.
       const int nsub = gridDim.x / c.nranks > 0 ? gridDim.x / c.nranks : 1;
@@ -533,7 +535,9 @@ struct SymA2a {
           push_range(a.out.ptr[p] + s_doff[p], a.in + s_soff[p], s_slen[p], blockIdx.x, gridDim.x);
         }
       }
+      trace_mark(c, 2);
       ok = block_barrier(c, kFlagSetSymA2a, ep, 0x49);
+      trace_mark(c, 3);
     }
     ep.store(c, kFlagSetSymA2a);
   }

@@ -64,8 +64,8 @@ struct CommDev {
   volatile uint32_t* status;
   unsigned long long timeout_ns;  // budget of one wait
   size_t heap_bytes;              // size of the staging region
-  // Optional phase trace: kTraceSlots cycle-counter stamps per block, written
-  // by thread 0 (nullptr = off). For performance work, see trace_mark().
+  // Optional phase trace: kTraceSlots stamps of the device's nanosecond timer per
+  // block (nullptr = off). For performance work, see trace_mark().
   long long* trace;
 };
 
@@ -347,10 +347,10 @@ __device__ __forceinline__ void post_flags(const CommDev& c, bool post_ready, ui
   }
 }
 
-// Stamps the SM cycle counter into slot `slot` of this block's trace row.
+// Stamps the device's nanosecond timer into slot `slot` of this block's trace row (thread 0 of the block).
 __device__ __forceinline__ void trace_mark(const CommDev& c, int slot) {
   if (c.trace != nullptr && threadIdx.x == 0 && slot < kTraceSlots) {
-    c.trace[static_cast<size_t>(blockIdx.x) * kTraceSlots + slot] = clock64();
+    c.trace[static_cast<size_t>(blockIdx.x) * kTraceSlots + slot] = static_cast<long long>(globaltimer_ns());
   }
 }
 

@@ -58,6 +58,7 @@ __device__ void ep_dispatch_body(const CommDev& c, const EpDev& e, const Dispatc
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int gwarp = blockIdx.x * kEpWarps + warp, nwarps = gridDim.x * kEpWarps;
 
+  trace_mark(c, 0);
   // A. reset the per-call counters
   if (blockIdx.x == 0 && threadIdx.x < e.nranks) {
     e.cnt[threadIdx.x] = 0;
@@ -75,6 +76,7 @@ __device__ void ep_dispatch_body(const CommDev& c, const EpDev& e, const Dispatc
   __syncthreads();
   if (threadIdx.x < e.nranks && s_cnt[threadIdx.x] > 0) atomicAdd(&e.cnt[threadIdx.x], s_cnt[threadIdx.x]);
   grid.sync();
+  trace_mark(c, 1);
 
   // C. publish the counts to every rank, learn where this rank's rows start
   //    inside each destination's receive buffer (rows are packed by source).
@@ -102,6 +104,7 @@ __device__ void ep_dispatch_body(const CommDev& c, const EpDev& e, const Dispatc
     }
   }
   grid.sync();
+  trace_mark(c, 2);
 
   // D. quantise and send
   const int groups = e.hidden / 128;
@@ -189,10 +192,12 @@ __device__ void ep_dispatch_body(const CommDev& c, const EpDev& e, const Dispatc
     }
     __syncwarp();
   }
+  trace_mark(c, 3);
   grid.sync();
   // E. every rank's rows have landed before anybody returns
   if (blockIdx.x == 0) {
     ep_rank_barrier(c, 0x92);
+    trace_mark(c, 4);
   }
 }
 
@@ -227,7 +232,9 @@ __device__ void ep_combine_body(const CommDev& c, const EpDev& e, const CombineA
   const int* send_slot = a.send_slot != nullptr ? a.send_slot : e.send_slot;
   BlockEpoch ep;
   ep.load(c, kFlagSetEp);
+  trace_mark(c, 0);
   bool ok = block_barrier(c, kFlagSetEp, ep, 0x93);
+  trace_mark(c, 1);
   if (ok) {
     for (int t = gwarp; t < a.num_tokens; t += nwarps) {
       int slot = -1;
@@ -313,8 +320,10 @@ __device__ void ep_combine_body(const CommDev& c, const EpDev& e, const CombineA
         }
       }
     }
+    trace_mark(c, 2);
     // Nobody overwrites its expert outputs while a peer still reads them.
     ok = block_barrier(c, kFlagSetEp, ep, 0x94);
+    trace_mark(c, 3);
   }
   ep.store(c, kFlagSetEp);
 }

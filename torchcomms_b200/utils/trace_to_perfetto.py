@@ -1,8 +1,8 @@
 """Turns the in-kernel phase trace and flight-recorder dumps into a Chrome / Perfetto trace.
 
-    tr = comm.get_backend_impl().enable_trace()      # [blocks, 16] int64, clock64() per phase mark of each block
+    tr = comm.get_backend_impl().enable_trace()      # [blocks, 16] int64, device nanosecond timer per phase mark of each block
     ... run ONE collective ...
-    events = phase_trace_events(tr.cpu(), rank=comm.get_rank(), sm_mhz=1900.0,
+    events = phase_trace_events(tr.cpu(), rank=comm.get_rank(),
                                 phases=("copy-in", "barrier", "reduce", "barrier", "copy-out"))
     write_trace("ar.json", events + flight_recorder_events(json.load(open("fr_dump.json"))))
 
@@ -18,15 +18,15 @@ import json
 from typing import Any, Dict, Iterable, List, Optional, Sequence
 
 
-def phase_trace_events(trace: Any, rank: int = 0, sm_mhz: float = 1900.0, phases: Optional[Sequence[str]] = None,
+def phase_trace_events(trace: Any, rank: int = 0, phases: Optional[Sequence[str]] = None,
                        name: str = "collective") -> List[Dict[str, Any]]:
-    """``trace[b, s]`` = SM clock at mark ``s`` of block ``b`` (0 = mark not reached)."""
+    """``trace[b, s]`` = the GPU's nanosecond timer at mark ``s`` of block ``b`` (0 = mark not reached)."""
     rows = trace.tolist() if hasattr(trace, "tolist") else list(trace)
     starts = [r[0] for r in rows if r and r[0] != 0]
     if not starts:
         return []
     t0 = min(starts)
-    to_us = 1.0 / sm_mhz  # cycles -> microseconds
+    to_us = 1e-3  # nanoseconds -> microseconds
     events: List[Dict[str, Any]] = [
         {"ph": "M", "pid": rank, "name": "process_name", "args": {"name": f"rank {rank} ({name})"}},
     ]
@@ -42,6 +42,25 @@ def phase_trace_events(trace: Any, rank: int = 0, sm_mhz: float = 1900.0, phases
             events.append({"ph": "X", "pid": rank, "tid": b, "name": label, "cat": name,
                            "ts": (a - t0) * to_us, "dur": (z - a) * to_us})
     return events
+
+
+def phase_summary(trace: Any, phases: Sequence[str]) -> List[str]:
+    """Text table of a phase trace: for each phase (mark ``s`` to mark ``s + 1``) the minimum / median / maximum
+    duration over the blocks that reached both marks, and when the last block left it (microseconds after the
+    first block's first mark)."""
+    rows = trace.tolist() if hasattr(trace, "tolist") else list(trace)
+    rows = [r for r in rows if r and r[0] != 0]
+    if not rows:
+        return ["(no block stamped the trace)"]
+    t0 = min(r[0] for r in rows)
+    out = [f"{len(rows)} blocks; microseconds", f"{'phase':34s} {'blocks':>6s} {'min':>8s} {'median':>8s} {'max':>8s} {'last end':>9s}"]
+    for s, label in enumerate(phases):
+        durs = sorted((r[s + 1] - r[s]) / 1e3 for r in rows if s + 1 < len(r) and r[s] and r[s + 1] and r[s + 1] >= r[s])
+        if not durs:
+            continue
+        last = max((r[s + 1] - t0) / 1e3 for r in rows if s + 1 < len(r) and r[s] and r[s + 1])
+        out.append(f"{label:34s} {len(durs):6d} {durs[0]:8.1f} {durs[len(durs) // 2]:8.1f} {durs[-1]:8.1f} {last:9.1f}")
+    return out
 
 
 def flight_recorder_events(dump: Dict[str, Any], rank: Optional[int] = None) -> List[Dict[str, Any]]:
