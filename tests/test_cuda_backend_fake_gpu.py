@@ -214,8 +214,8 @@ def test_watchdog_times_out_a_stuck_operation_and_runs_abort_hooks(single_rank_e
     fake.set_stuck(True)                      # end events never complete from here on
     w = comm.all_reduce(t, tc.ReduceOp.SUM, True)
     deadline = time.time() + 5
-    while tc.healthy() and time.time() < deadline:
-        time.sleep(0.02)
+    while (tc.healthy() or not fired or not comm.is_aborted()) and time.time() < deadline:
+        time.sleep(0.02)                      # the watchdog marks the failure, then runs the hooks, then aborts
     assert not tc.healthy()
     assert fired
     assert comm.is_aborted()
