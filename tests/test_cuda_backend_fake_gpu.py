@@ -346,3 +346,47 @@ def _multi_rank_body(rank, world):
 
 def test_four_fake_ranks_bootstrap_route_and_split():
     run_ranks(_multi_rank_body, 4, timeout=180)
+
+
+def _tuner_file_body(rank, world, path):
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import _comms
+
+    _comms._install_fake_gpu()
+    comm = tc.new_comm("b200", torch.device("cuda", rank), name="tuned", abort_process_on_timeout_or_error=False,
+                       hints={"staging_mb": "1", "tuner_file": path, "lamport_max_bytes": "0"})
+    impl = comm.get_backend_impl()
+    assert impl.comm_dump()["tuning/tuner_rules"] == "4"
+
+    def counts():
+        return {k[6:]: int(v) for k, v in impl.comm_dump().items() if k.startswith("count/")}
+
+    comm.all_reduce(torch.ones(256), tc.ReduceOp.SUM, False)              # 1 KB   -> nccl (first rule)
+    comm.all_reduce(torch.ones(64 * 1024), tc.ReduceOp.SUM, False)        # 256 KB -> kernel (second rule)
+    comm.all_reduce(torch.ones(4 * 1024 * 1024), tc.ReduceOp.SUM, False)  # 16 MB  -> nccl (last rule: inf)
+    comm.all_gather_single(torch.empty(world * 1024), torch.ones(1024), False)   # rule for all_gather: kernel everywhere
+    c = counts()
+    assert c["all_reduce/nccl"] == 2 and c.get("all_gather/nccl", 0) == 0, c
+    assert sum(v for k, v in c.items() if k.startswith("all_reduce/") and k != "all_reduce/nccl") == 1, c
+    # a call may still force its route
+    comm.all_reduce(torch.ones(256), tc.ReduceOp.SUM, False, hints={"algo": "kernel"})
+    assert counts()["all_reduce/nccl"] == 2
+    comm.finalize()
+    _comms._uninstall_fake_gpu()
+
+
+def test_tuner_file_routes_by_operation_and_size(tmp_path):
+    """A tuner file written from a sweep (utils/tuning.py --emit) decides kernel / NCCL per operation and size."""
+    from torchcomms_b200.utils.tuning import tuner_file_lines
+
+    rows = []
+    for b, k, n in [(1024, 9.0, 7.0), (262144, 9.0, 14.0), (16 << 20, 70.0, 55.0)]:
+        rows += [{"op": "all_reduce", "dtype": "bf16", "bytes": b, "algo": "kernel", "us": k},
+                 {"op": "all_reduce", "dtype": "bf16", "bytes": b, "algo": "nccl", "us": n}]
+    rows += [{"op": "all_gather", "dtype": "bf16", "bytes": 4096, "algo": "kernel", "us": 7.0},
+             {"op": "all_gather", "dtype": "bf16", "bytes": 4096, "algo": "nccl", "us": 11.0}]
+    lines = tuner_file_lines(rows)
+    assert lines[1:] == ["all_gather inf kernel", "all_reduce 1024 nccl", "all_reduce 262144 kernel", "all_reduce inf nccl"]
+    path = tmp_path / "tuner.txt"
+    path.write_text("\n".join(lines) + "\n")
+    run_ranks(_tuner_file_body, 2, args=(str(path),), timeout=120)

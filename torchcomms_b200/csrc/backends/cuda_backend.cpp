@@ -4,6 +4,9 @@
 #include <unistd.h>
 
 #include <cstdio>
+#include <fstream>
+#include <limits>
+#include <sstream>
 #include <random>
 #include <tuple>
 
@@ -272,6 +275,7 @@ void CudaBackend::parse_tuning(const Hints& h) {
   t.ag_push_min_ranks = hint_or<int>(h, "ag_push_min_ranks", env_to_value<int>("B200COMMS_AG_PUSH_MIN_RANKS", t.ag_push_min_ranks));
   t.a2av_blocks = hint_or<int>(h, "a2av_blocks", env_to_value<int>("B200COMMS_A2AV_BLOCKS", t.a2av_blocks));
   t.auto_nccl = hint_or<bool>(h, "auto_nccl", env_to_value<bool>("B200COMMS_AUTO_NCCL", t.auto_nccl));
+  t.tuner_file = hint_or<std::string>(h, "tuner_file", env_to_value<std::string>("B200COMMS_TUNER_FILE", t.tuner_file));
   t.steps_per_block = hint_or<int>(h, "steps_per_block", env_to_value<int>("B200COMMS_STEPS_PER_BLOCK", t.steps_per_block));
   t.symm_blocks = hint_or<int>(h, "symm_blocks", env_to_value<int>("B200COMMS_SYMM_BLOCKS", t.symm_blocks));
   t.symm_blocks_nomc = hint_or<int>(h, "symm_blocks_nomc", env_to_value<int>("B200COMMS_SYMM_BLOCKS_NOMC", t.symm_blocks_nomc));
@@ -288,7 +292,12 @@ void CudaBackend::parse_tuning(const Hints& h) {
   t.fast_sync = hint_or<bool>(h, "fast_sync", env_to_value<bool>("B200COMMS_FAST_SYNC", t.fast_sync));
   t.colltrace = std::max(0, std::min(1 << 16, hint_or<int>(h, "colltrace", env_to_value<int>("B200COMMS_COLLTRACE", t.colltrace))));
   t.staging_bytes = std::max<size_t>(t.staging_bytes, 1u << 20);
+  const bool reload = t.tuner_file != tune_.tuner_file;
   tune_ = t;
+  if (reload) {
+    for (auto& rules : tuner_rules_) rules.clear();
+    if (!tune_.tuner_file.empty()) load_tuner_file(tune_.tuner_file);
+  }
 }
 
 void CudaBackend::set_hints(const Hints& h) {
@@ -1091,10 +1100,50 @@ Algo CudaBackend::algo_override(const OpOptions& o) const {
 // 8 KB) and the all-reduce between 4 and 64 MB (NVLS two-shot with 64 KB
 // chunks); NCCL's protocols win the rest, all-to-all, and everything below
 // 4 ranks. algo=kernel forces the kernels.
+// Tuner file: lines of `<operation> <largest bytes | inf> <kernel | nccl>`, '#' starts a comment. For every
+// operation the rules apply in ascending order of size; a size above the last rule keeps the built-in choice.
+// Every rank must load the same file (the route has to be the same everywhere).
+void CudaBackend::load_tuner_file(const std::string& path) {
+  std::ifstream f(path);
+  TORCH_CHECK(f.good(), "tuner file '", path, "' cannot be read");
+  static const std::unordered_map<std::string, Coll> ops = {
+      {"all_reduce", Coll::ALL_REDUCE}, {"all_gather", Coll::ALL_GATHER},
+      {"reduce_scatter", Coll::REDUCE_SCATTER}, {"all_to_all", Coll::ALL_TO_ALL}, {"all_to_all_v", Coll::ALL_TO_ALL}};
+  std::string line;
+  int lineno = 0;
+  while (std::getline(f, line)) {
+    ++lineno;
+    const size_t hash = line.find('#');
+    if (hash != std::string::npos) line.resize(hash);
+    std::istringstream is(line);
+    std::string op, limit, algo;
+    if (!(is >> op)) continue;
+    TORCH_CHECK(static_cast<bool>(is >> limit >> algo), "tuner file ", path, ":", lineno, ": expected '<op> <bytes|inf> <kernel|nccl>'");
+    auto it = ops.find(op);
+    TORCH_CHECK(it != ops.end(), "tuner file ", path, ":", lineno, ": unknown operation '", op, "'");
+    TORCH_CHECK(algo == "kernel" || algo == "nccl", "tuner file ", path, ":", lineno, ": algorithm must be kernel or nccl");
+    size_t up_to = std::numeric_limits<size_t>::max();
+    if (limit != "inf") {
+      char* end = nullptr;
+      up_to = std::strtoull(limit.c_str(), &end, 10);
+      TORCH_CHECK(end != nullptr && *end == 0, "tuner file ", path, ":", lineno, ": bad size '", limit, "'");
+    }
+    tuner_rules_[static_cast<int>(it->second)].push_back({up_to, algo == "nccl" ? Algo::NCCL : Algo::KERNEL});
+  }
+  for (auto& rules : tuner_rules_) {
+    std::stable_sort(rules.begin(), rules.end(), [](const TunerRule& a, const TunerRule& b) { return a.up_to < b.up_to; });
+  }
+}
+
 Algo CudaBackend::route(Coll c, size_t bytes, const OpOptions& o) const {
   const Algo a = algo_override(o);
   if (a == Algo::KERNEL) return Algo::AUTO;
   if (a != Algo::AUTO) return a;
+  if (nccl_comm_ != nullptr && size_ > 1) {
+    for (const TunerRule& r : tuner_rules_[static_cast<int>(c)]) {
+      if (bytes <= r.up_to) return r.algo == Algo::NCCL ? Algo::NCCL : Algo::AUTO;
+    }
+  }
   if (nccl_comm_ == nullptr || !tune_.auto_nccl || size_ == 1) return Algo::AUTO;
   if (size_ < 4) return Algo::NCCL;
   constexpr size_t KB = 1024, MB = 1024 * 1024;
@@ -2064,6 +2113,7 @@ std::shared_ptr<Backend> CudaBackend::split(const std::vector<int>& ranks, const
   child->cuda_ = cuda_;
   child->nccl_ = nccl_;
   child->tune_ = tune_;
+  for (int i = 0; i < 4; ++i) child->tuner_rules_[i] = tuner_rules_[i];
   child->parse_tuning(opts.hints);
   auto sub = scoped_store(store_, "split/" + std::to_string(gen) + "/" + std::to_string(color));
   child->bootstrap(sub, idx, static_cast<int>(ranks.size()));
@@ -2082,6 +2132,7 @@ std::shared_ptr<Backend> CudaBackend::create_pair_comm(int peer, const std::stri
   child->cuda_ = cuda_;
   child->nccl_ = nccl_;
   child->tune_ = tune_;
+  for (int i = 0; i < 4; ++i) child->tuner_rules_[i] = tuner_rules_[i];
   // Point-to-point only: a small staging heap and no multicast object per pair.
   child->tune_.staging_bytes = std::min<size_t>(tune_.staging_bytes, 4u << 20);
   child->tune_.use_multicast = false;
@@ -2112,6 +2163,8 @@ std::unordered_map<std::string, std::string> CudaBackend::comm_dump() const {
   d["tuning/max_blocks"] = std::to_string(tune_.max_blocks);
   d["tuning/threads"] = std::to_string(tune_.threads);
   d["tuning/auto_nccl"] = tune_.auto_nccl ? "1" : "0";
+  d["tuning/tuner_file"] = tune_.tuner_file;
+  d["tuning/tuner_rules"] = std::to_string(tuner_rules_[0].size() + tuner_rules_[1].size() + tuner_rules_[2].size() + tuner_rules_[3].size());
   d["tuning/use_multicast"] = tune_.use_multicast ? "1" : "0";
   d["tuning/channel_streams"] = tune_.channel_streams ? "1" : "0";
   d["tuning/fast_sync"] = tune_.fast_sync ? "1" : "0";

@@ -104,6 +104,7 @@ struct Tuning {
   int steps_per_block = 8;                 // large payloads: steps each block should run
   size_t min_chunk_bytes = 64 * 1024;
   bool auto_nccl = false;                  // opt-in: algo=auto may pick NCCL where it measured faster
+  std::string tuner_file;                  // opt-in: per-operation size ranges -> kernel / nccl, written by utils/tuning.py
   int symm_blocks = 32;                    // grid of the one-pass kernels on symmetric buffers (same on every rank)
   int symm_blocks_nomc = 64;               // same, when the data path is plain peer stores
   int symm_blocks_ld = 128;                // same, for plain peer loads: an SM keeps only so many remote reads in flight,
@@ -367,6 +368,13 @@ class CudaBackend final : public Backend {
   // Stamps the ring before (`end` = false) or after the launch; returns the slot, or -1 when tracing is off.
   int64_t colltrace_begin(const char* what, cudaStream_t stream);
   void colltrace_end(int64_t slot, cudaStream_t stream);
+  // Route table of the tuner file: for each operation, (largest message size, algorithm) in ascending order.
+  struct TunerRule {
+    size_t up_to;
+    Algo algo;
+  };
+  std::vector<TunerRule> tuner_rules_[4];
+  void load_tuner_file(const std::string& path);
   static constexpr size_t kMaxGraphEntries = 2048;
   unsigned long long* replay_pool_host_ = nullptr;  // 2 x kMaxGraphEntries counters, mapped pinned
   unsigned long long* replay_pool_dev_ = nullptr;

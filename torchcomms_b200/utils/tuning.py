@@ -1,7 +1,11 @@
 """Offline tuning: turns sweep results into an algorithm table and cross-over sizes.
 
     torchrun --nproc-per-node 8 benchmarks/collective_perf.py --algos kernel,nccl --json sweep.json
-    python -m torchcomms_b200.utils.tuning sweep.json
+    python -m torchcomms_b200.utils.tuning sweep.json [--emit tuner.txt]
+
+``--emit`` writes the cross-over table as a tuner file (lines of ``<operation> <largest bytes | inf> <kernel |
+nccl>``) that the CUDA backend loads through the hint ``tuner_file`` / ``B200COMMS_TUNER_FILE`` and consults before
+its built-in choices; every rank must load the same file.
 
 ``best_config(rows)`` maps ``(op, dtype, bytes)`` to the fastest arm;
 ``crossovers(rows)`` compresses that into byte ranges per operation, the form
@@ -55,15 +59,42 @@ def hint_sweep(named_rows: Dict[str, Iterable[Dict[str, Any]]], arm: str = "kern
     return best
 
 
+def tuner_file_lines(rows: Iterable[Dict[str, Any]], dtype: str = "bf16") -> List[str]:
+    """The cross-overs of one dtype as tuner-file lines; arms other than ``nccl`` count as ``kernel``."""
+    lines = ["# operation  largest message (bytes)  algorithm"]
+    for (op, dt), runs in sorted(crossovers(rows).items()):
+        if dt != dtype:
+            continue
+        merged: List[Tuple[int, str]] = []
+        for _, last, algo in runs:
+            algo = "nccl" if algo == "nccl" else "kernel"
+            if merged and merged[-1][1] == algo:
+                merged[-1] = (last, algo)
+            else:
+                merged.append((last, algo))
+        for i, (last, algo) in enumerate(merged):
+            lines.append(f"{op} {'inf' if i == len(merged) - 1 else last} {algo}")
+    return lines
+
+
 def main(argv: List[str]) -> int:
-    if len(argv) < 2:
+    args = list(argv[1:])
+    emit = None
+    if "--emit" in args:
+        i = args.index("--emit")
+        emit = args[i + 1]
+        del args[i:i + 2]
+    if not args:
         print(__doc__)
         return 2
     rows: List[Dict[str, Any]] = []
-    for path in argv[1:]:
+    for path in args:
         rows += json.load(open(path))
     for (op, dt), runs in crossovers(rows).items():
         print(f"{op} {dt}: " + ", ".join(f"[{a}..{b}] -> {algo}" for a, b, algo in runs))
+    if emit:
+        with open(emit, "w") as f:
+            f.write("\n".join(tuner_file_lines(rows)) + "\n")
     return 0
 
 
