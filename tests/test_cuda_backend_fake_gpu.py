@@ -333,6 +333,22 @@ def _multi_rank_body(rank, world):
     assert launches[0].split()[2] != launches[1].split()[2]
     w1.wait()
     w2.wait()
+    # ... but kernels that could hold more SMs together than the GPU has are chained: a 64 MB all-gather (64 blocks)
+    # and a 64 MB reduce-scatter (128 blocks) of different channels, the second waits for the first
+    big_out = comm.symm_empty((world * 8 * 1024 * 1024,), torch.bfloat16)
+    piece = torch.ones(8 * 1024 * 1024, dtype=torch.bfloat16)
+    fake.clear_log()
+    own = {"algo": "kernel"}     # this communicator has mixed routing on, which would hand both to NCCL
+    w1 = comm.all_gather_single(big_out, piece, True, hints=own)
+    w2 = comm.reduce_scatter_single(torch.empty(8 * 1024 * 1024, dtype=torch.bfloat16), big_out, tc.ReduceOp.SUM, True, hints=own)
+    log = fake.log()
+    launches = [i for i, l in enumerate(log) if l.startswith("launch")]
+    ag_stream, rs_stream = log[launches[0]].split()[2], log[launches[1]].split()[2]
+    ag_end = next(l.split()[1] for l in log[launches[0]:] if l.startswith("record") and l.split()[2] == ag_stream)
+    assert f"wait {rs_stream} {ag_end}" in log[launches[0]:launches[1]], log
+    w1.wait()
+    w2.wait()
+    comm.symm_free(big_out)
     # split: members bootstrap a communicator of their own
     members = [r for r in range(world) if r % 2 == rank % 2]
     sub = comm.split(members, "half")

@@ -285,7 +285,7 @@ void CudaBackend::parse_tuning(const Hints& h) {
   t.symm_blocks = std::max(1, std::min(t.symm_blocks, 128));
   t.symm_blocks_nomc = std::max(1, std::min(t.symm_blocks_nomc, 128));
   t.symm_blocks_ld = hint_or<int>(h, "symm_blocks_ld", env_to_value<int>("B200COMMS_SYMM_BLOCKS_LD", t.symm_blocks_ld));
-  t.symm_blocks_ld = std::max(1, std::min(t.symm_blocks_ld, 148));
+  t.symm_blocks_ld = std::max(1, std::min(t.symm_blocks_ld, 132));
   t.lamport_max_bytes = hint_or<size_t>(h, "lamport_max_bytes", env_to_value<size_t>("B200COMMS_LAMPORT_MAX_BYTES", t.lamport_max_bytes));
   t.lamport_max_bytes = std::min(t.lamport_max_bytes, static_cast<size_t>(kLamportBlocks) * kLamportPiece);
   t.channel_streams = hint_or<bool>(h, "channel_streams", env_to_value<bool>("B200COMMS_CHANNEL_STREAMS", t.channel_streams));
@@ -611,7 +611,7 @@ void CudaBackend::note_graph_released(unsigned long long graph_id) {
 }
 
 WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, std::vector<at::Tensor> keep_alive,
-                         const std::function<void(cudaStream_t)>& launch, int chan, bool own_kernel) {
+                         const std::function<void(cudaStream_t)>& launch, int chan, bool own_kernel, int sm_blocks) {
   check_usable();
   DeviceScope guard(cuda_, device_.index());
   cudaStream_t current = cuda_->currentStream(device_.index());
@@ -646,6 +646,32 @@ WorkPtr CudaBackend::run(const char* what, bool async_op, const OpOptions& o, st
       B200C_CUDA_CHECK(cuda_->eventRecord(cs.order_event, cs.last_stream));
       B200C_CUDA_CHECK(cuda_->streamWaitEvent(stream, cs.order_event));
     }
+  }
+  if (sm_blocks > 0 && !capturing) {
+    // Blocks of the one-pass kernels hold an SM each while they wait for the same block of every peer. Kernels
+    // of different channels run side by side, and each GPU starts their blocks in an order of its own: if
+    // together they could hold more SMs than there are, one rank may fill up with blocks of kernel A and another
+    // with blocks of kernel B, each waiting for peer blocks that find no SM. So a kernel that would push the sum
+    // over the budget first waits for the other channels' latest kernels. The rule looks only at the order of
+    // issue and at grid sizes, which are the same on every rank.
+    constexpr int kSmBudget = 140;
+    int others = 0;
+    for (int ch = 0; ch < kChanCount; ++ch) {
+      if (ch != chan) others += chans_[ch].sm_blocks;
+    }
+    if (others + sm_blocks > kSmBudget) {
+      for (int ch = 0; ch < kChanCount; ++ch) {
+        ChanState& other = chans_[ch];
+        if (ch == chan || other.sm_blocks == 0 || other.last_stream == nullptr || other.last_stream == stream) continue;
+        if (other.last_work) {
+          B200C_CUDA_CHECK(cuda_->streamWaitEvent(stream, other.last_work->end_event()));
+        } else {
+          B200C_CUDA_CHECK(cuda_->eventRecord(other.order_event, other.last_stream));
+          B200C_CUDA_CHECK(cuda_->streamWaitEvent(stream, other.order_event));
+        }
+      }
+    }
+    cs.sm_blocks = sm_blocks;
   }
 
   auto self = std::static_pointer_cast<CudaBackend>(shared_from_this());
@@ -1198,7 +1224,7 @@ LaunchShape CudaBackend::shape_for(size_t bytes, size_t slot_multiplier, int blo
 // buffer has a multicast alias, so every rank computes the same number.
 int CudaBackend::symm_blocks_for(bool mc, size_t vectors, const OpOptions& o, bool peer_loads) const {
   int cap = mc ? tune_.symm_blocks : peer_loads ? tune_.symm_blocks_ld : tune_.symm_blocks_nomc;
-  cap = std::max(1, std::min(148, hint_or<int>(o.hints, "symm_blocks", cap)));
+  cap = std::max(1, std::min(132, hint_or<int>(o.hints, "symm_blocks", cap)));  // never every SM: see kSmBudget in run()
   const size_t per_block = 512 * 4;  // threads x unroll
   const size_t want = (vectors + per_block - 1) / per_block;
   return static_cast<int>(std::max<size_t>(1, std::min<size_t>(cap, want)));
@@ -1303,7 +1329,7 @@ WorkPtr CudaBackend::all_reduce(at::Tensor& t, const ReduceOp& op, bool async_op
       bytes_issued_ += bytes;
       return run("all_reduce/symm", async_op, o, {t}, [this, tt, sv, dt, scale, smc, blocks](cudaStream_t s) {
         B200C_CUDA_CHECK(launch_symm_all_reduce(&dev_, 0, &sv, tt.numel(), dt, scale, smc, blocks, s));
-      }, kChanSymAr, true);
+      }, kChanSymAr, true, blocks);
     }
   }
   int kalgo;
@@ -1458,7 +1484,7 @@ WorkPtr CudaBackend::all_gather_single(at::Tensor& out, const at::Tensor& in, bo
                  [this, i, ot, sv, bytes, cast, smc, blocks](cudaStream_t s) {
                    const void* ip = i.data_ptr();
                    B200C_CUDA_CHECK(launch_symm_all_gather(&dev_, 0, &ip, &sv, bytes, cast, smc, blocks, s));
-                 }, kChanSymAg, true);
+                 }, kChanSymAg, true, blocks);
     }
   }
   // Multicast push pays while the message is latency / launch bound; big gathers pull.
@@ -1578,7 +1604,7 @@ static WorkPtr exchange_symm(CudaBackend* self, const char* what, at::Tensor in,
                                                              counts != nullptr ? &counts : nullptr, elem_bytes,
                                                              !equal_splits, blocks, s));
                    },
-                   kChanSymAr, true);
+                   kChanSymAr, true, blocks);
 }
 
 WorkPtr CudaBackend::all_gather_v(const std::vector<at::Tensor>& outs, const at::Tensor& in, bool async_op, const OpOptions& o) {
@@ -1697,7 +1723,7 @@ WorkPtr CudaBackend::reduce_scatter_single(at::Tensor& out, const at::Tensor& in
       return run("reduce_scatter/symm", async_op, o, {in}, [this, i, ot, sv, din, dout, scale, smc, blocks](cudaStream_t s) {
         void* op_ = ot.data_ptr();
         B200C_CUDA_CHECK(launch_symm_reduce_scatter(&dev_, 0, &sv, &op_, ot.numel(), din, dout, scale, smc, blocks, s));
-      }, kChanSymRs, true);
+      }, kChanSymRs, true, blocks);
     }
   }
   const bool mc = tune_.use_multicast && rk == RedKind::SUM && dev_.mc_heap != nullptr;

@@ -255,8 +255,12 @@ class CudaBackend final : public Backend {
   // operation joins; `own_kernel` says that everything launched is one of the
   // library's kernels with bounded waits (failures then show in the status
   // word, and an unobserved synchronous call needs no events).
+  // `sm_blocks` > 0: the operation is a kernel of that many one-block-per-SM blocks whose blocks wait for their
+  // peers' blocks. Kernels of different channels that could hold more SMs together than the GPU has are chained
+  // (see kSmBudget in run()), so that they can never starve each other's peers of SMs.
   WorkPtr run(const char* what, bool async_op, const OpOptions& o, std::vector<at::Tensor> keep_alive,
-              const std::function<void(cudaStream_t)>& launch, int chan = kChanMain, bool own_kernel = false);
+              const std::function<void(cudaStream_t)>& launch, int chan = kChanMain, bool own_kernel = false,
+              int sm_blocks = 0);
 
   // Fields of ncclConfig_t named by hints (what ncclCommInitRankConfig is given).
   static NcclConfig nccl_config_from_hints(const Hints& h, const std::string& comm_name);
@@ -317,6 +321,7 @@ class CudaBackend final : public Backend {
     cudaStream_t last_stream = nullptr;
     c10::intrusive_ptr<CudaWork> last_work;   // null when the last operation recorded no events
     cudaEvent_t order_event = nullptr;        // recorded on last_stream when an event-less operation must be followed
+    int sm_blocks = 0;                        // SMs the channel's latest peer-waiting kernel may hold
   };
   ChanState chans_[kChanCount];
   // Inside a stream capture: last captured operation per graph, so that
