@@ -115,6 +115,20 @@ def main():
                 ("opening barrier (outputs complete)", "pull rows + weighted sum", "closing barrier (reads done)"),
                 remote_rows * H * 2)
         del buf
+        from torchcomms_b200.ops.moe_ep import LowLatencyBuffer
+
+        t2 = 128
+        ll = LowLatencyBuffer(comm, max_tokens=t2, hidden=H, num_experts=E, topk=K, fp8=True)
+        x2, idx2, w2 = x[:t2].contiguous(), idx[:t2].contiguous(), w[:t2].contiguous()
+        r = ll.dispatch(x2, idx2)
+        section(f"MoE low-latency dispatch, {t2} tokens", traced(comm, impl, lambda: ll.dispatch(x2, idx2)),
+                ("number rows per expert + grid sync", "quantise + store rows", "fence + grid sync",
+                 "publish counts, wait for peers' counts", "pack rows per expert"))
+        ll.expert_output.normal_()
+        out2 = torch.empty(t2, H, dtype=torch.bfloat16, device=dev)
+        section(f"MoE low-latency combine, {t2} tokens", traced(comm, impl, lambda: ll.combine(idx2, w2, r, out=out2)),
+                ("opening barrier (outputs complete)", "pull rows + weighted sum", "closing barrier (reads done)"))
+        del ll
     text = "\n".join(lines)
     if args.out:
         with open(f"{args.out}.rank{rank}", "w") as f:

@@ -74,6 +74,7 @@ __device__ void ll_dispatch_body(const CommDev& c, const EpLlDev& e, const LlDis
   const size_t row_bytes = e.fp8 ? static_cast<size_t>(e.hidden) : static_cast<size_t>(e.hidden) * 2;
   const size_t par_rows = static_cast<size_t>(par) * Le * N * M;
 
+  trace_mark(c, 0);
   // A0. number the rows per expert (one warp per token)
   for (int t = gwarp; t < a.num_tokens; t += nwarps) {
     if (lane < e.topk) {
@@ -94,6 +95,7 @@ __device__ void ll_dispatch_body(const CommDev& c, const EpLlDev& e, const LlDis
     }
   }
   grid.sync();
+  trace_mark(c, 1);
 
   // A1. store the rows into their fixed slots; one work item = one token x kLlChunkCols columns
   const int nchunks = (e.hidden + kLlChunkCols - 1) / kLlChunkCols;
@@ -168,8 +170,10 @@ __device__ void ll_dispatch_body(const CommDev& c, const EpLlDev& e, const LlDis
       }
     }
   }
+  trace_mark(c, 2);
   __threadfence_system();
   grid.sync();
+  trace_mark(c, 3);
   if (blockIdx.x == 0 && threadIdx.x == 0) *e.call = call;
 
   // B. the row counts, tagged with the call, go to every rank: they announce the rows
@@ -191,6 +195,7 @@ __device__ void ll_dispatch_body(const CommDev& c, const EpLlDev& e, const LlDis
     e.begin[ex] = b;
   }
 
+  trace_mark(c, 4);
   // C2. pack the rows of each local expert, sources in rank order
   const int nsub = max(1, static_cast<int>(gridDim.x) / Le);
   for (int item = blockIdx.x; item < Le * nsub; item += gridDim.x) {
@@ -236,6 +241,7 @@ __device__ void ll_dispatch_body(const CommDev& c, const EpLlDev& e, const LlDis
       if (lane == 0) a.recv.packed_src[to_row] = e.slot_src[e.rank][from_row];
     }
   }
+  trace_mark(c, 5);
 }
 
 __global__ void __launch_bounds__(kLlThreads) k_ep_ll_dispatch(CommDev c, EpLlDev e, LlDispatchArgs a) {
@@ -264,7 +270,9 @@ __device__ void ll_combine_body(const CommDev& c, const EpLlDev& e, const LlComb
   const int* begin = a.begin != nullptr ? a.begin : e.begin;
   BlockEpoch ep;
   ep.load(c, kFlagSetEp);
+  trace_mark(c, 0);
   bool ok = block_barrier(c, kFlagSetEp, ep, 0xa3);  // every rank's expert outputs are complete
+  trace_mark(c, 1);
   if (ok) {
     // One work item = one token x kLlChunkCols columns, so that a decode batch still fills the GPU with loads.
     const int nchunks = (e.hidden + kLlChunkCols - 1) / kLlChunkCols;
@@ -328,7 +336,9 @@ __device__ void ll_combine_body(const CommDev& c, const EpLlDev& e, const LlComb
         st16(static_cast<__nv_bfloat16*>(a.out) + static_cast<size_t>(t) * e.hidden + e0, o);
       }
     }
+    trace_mark(c, 2);
     ok = block_barrier(c, kFlagSetEp, ep, 0xa4);  // nobody overwrites its outputs while a peer still reads them
+    trace_mark(c, 3);
   }
   ep.store(c, kFlagSetEp);
 }

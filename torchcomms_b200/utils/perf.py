@@ -326,6 +326,12 @@ def moe_ep_latency(
         ll.expert_output.normal_()
         out2 = torch.empty(t2, H, dtype=torch.bfloat16, device=device)
         ll_report("ll_combine", time_it(lambda: ll.combine(idx2, w2, r, out=out2)), pairs * H * 2)
+        # Back to back (no flush, no barrier, 100 calls between two events): what a decode loop sees once the
+        # launch path of the host is hidden behind the previous call.
+        for phase, fn, nbytes in (("ll_dispatch_b2b", lambda: ll.dispatch(x2, idx2), pairs * (H + H // 128 * 4)),
+                                  ("ll_combine_b2b", lambda: ll.combine(idx2, w2, r, out=out2), pairs * H * 2)):
+            t = time_calls(comm, fn, warmup, 100, device)
+            ll_report(phase, (t["avg_us"], t["p50_us"]), nbytes)
         torch.cuda.synchronize()
         del ll
     return rows
