@@ -122,8 +122,8 @@ def main():
         x2, idx2, w2 = x[:t2].contiguous(), idx[:t2].contiguous(), w[:t2].contiguous()
         r = ll.dispatch(x2, idx2)
         section(f"MoE low-latency dispatch, {t2} tokens", traced(comm, impl, lambda: ll.dispatch(x2, idx2)),
-                ("number rows per expert + grid sync", "quantise + store rows", "fence + grid sync",
-                 "publish counts, wait for peers' counts", "pack rows per expert"))
+                ("number rows per expert + grid sync", "publish counts", "quantise + store rows",
+                 "wait for peers' counts", "pack rows as they arrive"))
         ll.expert_output.normal_()
         out2 = torch.empty(t2, H, dtype=torch.bfloat16, device=dev)
         section(f"MoE low-latency combine, {t2} tokens", traced(comm, impl, lambda: ll.combine(idx2, w2, r, out=out2)),

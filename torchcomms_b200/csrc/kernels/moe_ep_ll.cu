@@ -96,6 +96,15 @@ __device__ void ll_dispatch_body(const CommDev& c, const EpLlDev& e, const LlDis
   }
   grid.sync();
   trace_mark(c, 1);
+  if (blockIdx.x == 0 && threadIdx.x == 0) *e.call = call;
+
+  // B. the row counts are final: tagged with the call, they go to every rank ahead of the rows
+  for (int i = gtid; i < E * N; i += gthreads) {
+    const int ex = i / N, p = i - ex * N;
+    const unsigned long long v = (static_cast<unsigned long long>(call) << 32) | static_cast<unsigned int>(cnt[ex]);
+    st_release_sys_u64(reinterpret_cast<uint64_t*>(e.counts[p] + (static_cast<size_t>(par) * E + ex) * N + e.rank), v);
+  }
+  trace_mark(c, 2);
 
   // A1. store the rows into their fixed slots; one work item = one token x kLlChunkCols columns
   const int nchunks = (e.hidden + kLlChunkCols - 1) / kLlChunkCols;
@@ -169,19 +178,11 @@ __device__ void ll_dispatch_body(const CommDev& c, const EpLlDev& e, const LlDis
         if ((lane & 7) == 0) e.slot_scales[dk][static_cast<size_t>(rk) * groups + group] = scale;
       }
     }
+    // This piece of every row is stored: tell the receivers (release-ordered, after the whole warp's stores).
+    __syncwarp();
+    if (d >= 0) red_add_release_sys_u32(e.slot_arrived[d] + row, 1u);
   }
-  trace_mark(c, 2);
-  __threadfence_system();
-  grid.sync();
   trace_mark(c, 3);
-  if (blockIdx.x == 0 && threadIdx.x == 0) *e.call = call;
-
-  // B. the row counts, tagged with the call, go to every rank: they announce the rows
-  for (int i = gtid; i < E * N; i += gthreads) {
-    const int ex = i / N, p = i - ex * N;
-    const unsigned long long v = (static_cast<unsigned long long>(call) << 32) | static_cast<unsigned int>(cnt[ex]);
-    st_release_sys_u64(reinterpret_cast<uint64_t*>(e.counts[p] + (static_cast<size_t>(par) * E + ex) * N + e.rank), v);
-  }
 
   // C1. where this rank's rows sit in each expert's packed tensor (the combine reads from there)
   const unsigned long long* mine = e.counts[e.rank] + static_cast<size_t>(par) * E * N;
@@ -230,6 +231,14 @@ __device__ void ll_dispatch_body(const CommDev& c, const EpLlDev& e, const LlDis
       while (s + 1 < N && j >= s_beg[s + 1]) ++s;
       const size_t from_row = par_rows + (static_cast<size_t>(le) * N + s) * M + (j - s_beg[s]);
       const size_t to_row = static_cast<size_t>(le) * N * M + j;
+      // every piece of the row has landed?
+      int landed = 1;
+      if (lane == 0) {
+        landed = wait_flag_reached(c, e.slot_arrived[e.rank] + from_row, static_cast<uint32_t>(nchunks), s, 0xa5) ? 1 : 0;
+        e.slot_arrived[e.rank][from_row] = 0;   // this parity's slot is written again two calls from now
+      }
+      landed = __shfl_sync(0xffffffffu, landed, 0);
+      if (!landed) continue;
       const char* from = e.slot_x[e.rank] + from_row * row_bytes;
       char* to = static_cast<char*>(a.recv.packed_x) + to_row * row_bytes;
       for (size_t b = static_cast<size_t>(lane) * 16; b < row_bytes; b += 512) st16(to + b, ld16_stream(from + b));

@@ -4,12 +4,14 @@
 // per expert with a local counter and stores each row (quantised to fp8 e4m3
 // with 1x128 scales, or bf16) into a slot of the destination that is fixed by
 // (local expert, source rank, row number), so nothing has to be agreed before
-// the data moves. When all of its rows are out, the sender writes its row
-// count of every expert to every rank, tagged with the call number: the count
-// doubles as the arrival flag. The receiver waits for the counts of its own
-// experts (bounded), and packs the rows of each expert, sources in rank
-// order, into a dense [local experts, nranks * max_tokens, hidden] tensor that
-// a grouped GEMM can consume, with the count per expert beside it.
+// the data moves. As soon as the rows are numbered, the sender writes its row
+// count of every expert to every rank, tagged with the call number; the rows
+// follow, each piece raising the row's arrival counter at the receiver with a
+// release-ordered add once it has been stored. The receiver waits for the
+// counts of its own experts (bounded), and packs the rows of each expert,
+// sources in rank order, as they arrive, into a dense [local experts,
+// nranks * max_tokens, hidden] tensor that a grouped GEMM can consume, with
+// the count per expert beside it. No system-wide fence, one grid-wide meeting.
 // combine: the token's owner reads the expert outputs straight out of the
 // expert ranks' (symmetric) output tensors. It knows the packed position of
 // each of its rows from its own row numbers and the counts everybody
@@ -37,6 +39,7 @@ struct EpLlDev {
   char* slot_x[kMaxRanks];                 // [2][local experts][nranks][max_tokens] rows
   float* slot_scales[kMaxRanks];           // [2][local experts][nranks][max_tokens][hidden/128]
   int* slot_src[kMaxRanks];                // [2][local experts][nranks][max_tokens] source token
+  unsigned int* slot_arrived[kMaxRanks];   // same shape: pieces of the row that have landed (reset by the receiver)
   unsigned long long* counts[kMaxRanks];   // [2][num_experts][nranks]: (call << 32) | rows that source sent to that expert
   char* out_x[kMaxRanks];                  // [local experts][nranks * max_tokens][hidden] bf16 expert outputs
   // Local.

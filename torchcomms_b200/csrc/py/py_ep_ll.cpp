@@ -220,6 +220,7 @@ class EpLlBuffer {
     off_x_ = take(slots * hidden * (fp8 ? 1 : 2));
     off_scales_ = take(slots * (hidden / 128) * 4);
     off_src_ = take(slots * 4);
+    off_arrived_ = take(slots * 4);
     counts_bytes_ = static_cast<size_t>(2) * num_experts * nranks * 8;
     off_counts_ = take(counts_bytes_);
     off_out_ = take(slots / 2 * hidden * 2);
@@ -239,6 +240,7 @@ class EpLlBuffer {
       e.slot_x[p] = bases[p] + off_x_;
       e.slot_scales[p] = reinterpret_cast<float*>(bases[p] + off_scales_);
       e.slot_src[p] = reinterpret_cast<int*>(bases[p] + off_src_);
+      e.slot_arrived[p] = reinterpret_cast<unsigned int*>(bases[p] + off_arrived_);
       e.counts[p] = reinterpret_cast<unsigned long long*>(bases[p] + off_counts_);
       e.out_x[p] = bases[p] + off_out_;
     }
@@ -260,7 +262,7 @@ class EpLlBuffer {
   int n_local_;
   int nranks_ = 1, max_tokens_ = 0, hidden_ = 0, num_experts_ = 0, topk_ = 0;
   bool fp8_ = true;
-  size_t off_x_ = 0, off_scales_ = 0, off_src_ = 0, off_counts_ = 0, off_out_ = 0, counts_bytes_ = 0, total_ = 0;
+  size_t off_x_ = 0, off_scales_ = 0, off_src_ = 0, off_arrived_ = 0, off_counts_ = 0, off_out_ = 0, counts_bytes_ = 0, total_ = 0;
   std::vector<CommDev> comms_;
   std::vector<EpLlDev> eps_;
   std::vector<void*> local_allocs_, emu_allocs_;
