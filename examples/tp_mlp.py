@@ -1,5 +1,5 @@
 """Sequence-parallel SwiGLU MLP: the all-gather runs inside the up-projection GEMM and the
-reduce-scatter inside the down-projection's epilogue (bf16, tcgen05)."""
+reduce-scatter inside the down-projection's epilogue (bf16 and fp8, tcgen05)."""
 import os
 
 import sys
@@ -22,10 +22,13 @@ def main():
     mlp = TensorParallelMLP(hidden, ffn, comm, device=dev, dtype=torch.bfloat16)
     x_shard = torch.randn(tokens // n, hidden, device=dev, dtype=torch.bfloat16)   # tokens sharded over the ranks
     y_fused = mlp.forward_fused(x_shard)            # two fused kernels + SwiGLU
+    y_fp8 = mlp.forward_fused(x_shard, fp8=True)    # the same on e4m3 operands (per-token / per-channel scales)
     y_ref = mlp(x_shard)                            # functional collectives + cuBLAS, differentiable
     torch.cuda.synchronize()
     if comm.get_rank() == 0:
         print("max |fused - unfused| =", (y_fused.float() - y_ref.float()).abs().max().item())
+        rel = (y_fp8.float() - y_ref.float()).norm() / y_ref.float().norm()
+        print("relative error of the fp8 path =", rel.item())
     comm.finalize()
 
 

@@ -191,3 +191,27 @@ def test_tp_layers_multi_gpu():
     if world < 2:
         pytest.skip("needs 2 GPUs")
     run_ranks(_tp_worker, world, timeout=150)
+
+
+def test_tensor_parallel_mlp_fused_bf16_and_fp8_single_rank():
+    """``TensorParallelMLP.forward_fused`` on one rank: the bf16 path matches the differentiable path, the fp8 path
+    stays within fp8's precision of it."""
+    import torchcomms_b200 as tc
+    from torchcomms_b200.parallel.tensor import TensorParallelMLP
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29643")
+    os.environ["RANK"], os.environ["WORLD_SIZE"] = "0", "1"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    comm = tc.new_comm("b200", dev, name="tpmlp", abort_process_on_timeout_or_error=False)
+    mlp = TensorParallelMLP(1024, 1536, comm, device=dev, dtype=torch.bfloat16)
+    x = _rand((256, 1024), 77)
+    with torch.no_grad():
+        ref = mlp(x).float()
+    y = mlp.forward_fused(x).float()
+    y8 = mlp.forward_fused(x, fp8=True).float()
+    torch.cuda.synchronize()
+    assert float((y - ref).norm() / ref.norm()) < 0.02
+    assert float((y8 - ref).norm() / ref.norm()) < 0.08
+    comm.finalize()

@@ -6,6 +6,7 @@ transports, views, remote buffers that pickle, registration reuse).
 """
 import os
 import pickle
+import time
 from datetime import timedelta
 
 import pytest
@@ -154,6 +155,9 @@ def _two_process_worker(rank, world):
         store.set("inbox", pickle.dumps(mi.to_remote_buffer()))
         store.wait(["done"])
         assert torch.equal(inbox, torch.arange(1024, dtype=torch.int64) * 3)
+        deadline = time.time() + 5           # the service thread counts an operation after it has answered it
+        while tr.counters()["served_ops"] < 2 and time.time() < deadline:
+            time.sleep(0.01)
         assert tr.counters()["served_ops"] == 2
     else:
         table = pickle.loads(store.get("table"))

@@ -11,10 +11,10 @@ Two execution paths share the same parameters:
 * the differentiable path uses the functional collectives
   (``torchcomms_b200.functional``), so autograd produces the mirrored
   collective in backward; it runs on any backend (gloo on CPU in the tests);
-* ``TensorParallelMLP.forward_fused`` (CUDA, bf16, sequence parallel) runs
-  the two projections as the fused tcgen05 kernels of ``ops.tp``: the
-  all-gather happens inside the up-projection GEMM and the reduce-scatter
-  inside the down-projection's epilogue.
+* ``TensorParallelMLP.forward_fused`` (CUDA, bf16 or fp8 operands, sequence
+  parallel) runs the two projections as the fused tcgen05 kernels of
+  ``ops.tp``: the all-gather happens inside the up-projection GEMM and the
+  reduce-scatter inside the down-projection's epilogue.
 
 The reference exercises TP only through DTensor's ColwiseParallel /
 RowwiseParallel over its process-group adapter
@@ -110,6 +110,7 @@ class TensorParallelMLP(nn.Module):
         self.gate_up = ColumnParallelLinear(hidden, 2 * ffn, comm, sequence_parallel=True, device=device, dtype=dtype)
         self.down = RowParallelLinear(ffn, hidden, comm, sequence_parallel=True, device=device, dtype=dtype)
         self._fused = None
+        self._fp8_weights = None
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         gu = self.gate_up(x_shard)
@@ -117,15 +118,30 @@ class TensorParallelMLP(nn.Module):
         return self.down(nn.functional.silu(g) * u)
 
     @torch.no_grad()
-    def forward_fused(self, x_shard: torch.Tensor) -> torch.Tensor:
-        """Forward only, CUDA bf16: all-gather inside the up GEMM, reduce-scatter inside the down GEMM's epilogue."""
+    def forward_fused(self, x_shard: torch.Tensor, fp8: bool = False) -> torch.Tensor:
+        """Forward only, CUDA: all-gather inside the up GEMM, reduce-scatter inside the down GEMM's epilogue.
+
+        ``fp8``: both GEMMs run on e4m3 operands (activations quantised per token on the way in, weights per output
+        channel once and cached until ``invalidate_fp8_weights()``); outputs stay bf16.
+        """
         from ..ops import fused as fused_ops
-        from ..ops.tp import AllGatherGemm, GemmReduceScatter
+        from ..ops.tp import AllGatherGemm, GemmReduceScatter, quantize_rows
 
         m_local = x_shard.shape[0]
-        if self._fused is None or self._fused[0].m_local != m_local:
-            self._fused = (AllGatherGemm(self.comm, m_local, self.hidden), GemmReduceScatter(self.comm, m_local * self.n, self.hidden))
-        up, down = self._fused
-        gu = up(self.gate_up.weight, x_shard)
-        h = fused_ops.swiglu(gu)
-        return down(h.contiguous(), self.down.weight)
+        key = (m_local, fp8)
+        if self._fused is None or self._fused[0] != key:
+            self._fused = (key, AllGatherGemm(self.comm, m_local, self.hidden, fp8=fp8),
+                           GemmReduceScatter(self.comm, m_local * self.n, self.hidden, fp8=fp8))
+        _, up, down = self._fused
+        if not fp8:
+            gu = up(self.gate_up.weight, x_shard)
+            return down(fused_ops.swiglu(gu).contiguous(), self.down.weight)
+        if self._fp8_weights is None:
+            self._fp8_weights = quantize_rows(self.gate_up.weight) + quantize_rows(self.down.weight)
+        w_up, s_up, w_down, s_down = self._fp8_weights
+        gu = up(w_up, x_shard, scale_w=s_up)
+        return down(fused_ops.swiglu(gu).contiguous(), w_down, scale_w=s_down)
+
+    def invalidate_fp8_weights(self) -> None:
+        """Call after the weights changed: the next fp8 forward quantises them again."""
+        self._fp8_weights = None
