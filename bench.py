@@ -198,20 +198,27 @@ def main():
 
     log(f"[bench] step arm '{args.comm}' on {world} GPU(s)")
     main_arm = run_arm(args.comm if world > 1 else "symm", with_e2e=True, with_breakdown=True)
-    nccl_arm = None
+    nccl_arm, side_errors = None, {}
     if world > 1 and not args.skip_nccl_arm and args.comm != "nccl":
         log("[bench] step arm 'nccl'")
-        nccl_arm = run_arm("nccl", with_e2e=False, with_breakdown=True)
+        try:
+            nccl_arm = run_arm("nccl", with_e2e=False, with_breakdown=True)
+        except Exception as exc:  # noqa: BLE001 - the headline number above must still be reported
+            side_errors["step_nccl_arm"] = f"{type(exc).__name__}: {exc}"
 
     sweep_rows, sweep_summary, ep_rows = None, None, None
     if world > 1 and not args.skip_collectives:
         log("[bench] collective sweep")
-        sweep_rows = perf.sweep_collectives(
-            comm, device, max_bytes=args.sweep_max_bytes, warmup=args.sweep_warmup, iters=args.sweep_iters, log=log)
-        sweep_summary = perf.summarize_sweep(sweep_rows)
-        if rank == 0 and args.sweep_json:
-            with open(args.sweep_json, "w") as f:
-                json.dump(sweep_rows, f)
+        try:
+            sweep_rows = perf.sweep_collectives(
+                comm, device, max_bytes=args.sweep_max_bytes, warmup=args.sweep_warmup, iters=args.sweep_iters, log=log)
+            sweep_summary = perf.summarize_sweep(sweep_rows)
+            if rank == 0 and args.sweep_json:
+                with open(args.sweep_json, "w") as f:
+                    json.dump(sweep_rows, f)
+        except Exception as exc:  # noqa: BLE001
+            sweep_rows, sweep_summary = None, None
+            side_errors["collectives"] = f"{type(exc).__name__}: {exc}"
     if world > 1 and not args.skip_ep and 256 % world == 0:
         log("[bench] MoE dispatch / combine")
         try:
@@ -289,10 +296,15 @@ def main():
         }
     if ep_rows is not None:
         line["moe_ep"] = ep_rows
-    torch.cuda.synchronize()
-    comm.finalize()
+    if side_errors:
+        line["side_measurement_errors"] = side_errors
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)      # before the teardown: a failed side measurement may have broken it
+    try:
+        torch.cuda.synchronize()
+        comm.finalize()
+    except Exception as exc:  # noqa: BLE001
+        log(f"[bench] teardown: {type(exc).__name__}: {exc}")
 
 
 if __name__ == "__main__":
