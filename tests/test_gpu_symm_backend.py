@@ -110,7 +110,16 @@ def _symm_battery(rank, world):
     out_splits = [rank + 1] * world
     src = torch.cat([torch.full((d + 1, 3), float(rank * 10 + d), device=dev) for d in range(world)])
     want = torch.cat([torch.full((rank + 1, 3), float(s * 10 + rank), device=dev) for s in range(world)])
+    # a small symmetric receive buffer: the flag-less exchange (12-byte rows: parts are not whole 16-byte vectors)
     dst = comm.symm_empty((world * world, 3), torch.float32)  # same size everywhere, used up to sum(out_splits)
+    for it in range(3):
+        dst.zero_()
+        comm.all_to_all_v_single(dst[: sum(out_splits)], src, out_splits, in_splits, it == 1).wait()
+        torch.cuda.synchronize()
+        assert torch.equal(dst[: sum(out_splits)], want), it
+    comm.symm_free(dst)
+    # a large one: the one-pass push, with host splits and with splits that live on the device
+    dst = comm.symm_empty((400_000 + world * world, 3), torch.float32)
     dst.zero_()
     comm.all_to_all_v_single(dst[: sum(out_splits)], src, out_splits, in_splits, True).wait()
     torch.cuda.synchronize()
@@ -122,7 +131,8 @@ def _symm_battery(rank, world):
     comm.symm_free(dst)
     if world > 1:
         assert count("all_to_all_single/symm") >= 1 and count("all_to_all_single/lamport") >= 1
-        assert count("all_to_all_v_single/symm") >= 1 and count("device_alltoallv/symm") >= 1
+        assert count("all_to_all_v_single/lamport") >= 3 and count("all_to_all_v_single/symm") >= 1
+        assert count("device_alltoallv/symm") >= 1
 
     # ---- operations of different channels in flight together
     big = 8_000_000

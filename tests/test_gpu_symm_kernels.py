@@ -283,3 +283,48 @@ def test_lamport_exchange_unaligned_views_and_marker_payload():
     for o in outs:
         assert torch.equal(o, torch.cat(ins))          # -0.0 == +0.0 numerically
     assert w.status()[0] == 0
+
+
+@pytest.mark.parametrize("nranks,dtype", [(2, torch.float32), (4, torch.bfloat16), (8, torch.float32)])
+def test_lamport_all_to_all_with_unequal_parts(nranks, dtype):
+    """Flag-less all-to-all-v: parts of any byte length (odd element counts, empty parts, -0.0 payloads), interleaved
+    with equal-split exchanges on the same world so that the rotating buffers are shared between the two kernels."""
+    w = _world(nranks)
+    esz = torch.empty(0, dtype=dtype).element_size()
+    g = torch.Generator().manual_seed(99 + nranks)
+    for it in range(4):
+        counts = torch.randint(0, 700, (nranks, nranks), generator=g)      # elements rank r sends to rank p
+        counts[0, nranks - 1] = 0
+        counts[nranks - 1, 0] = 1 if it % 2 else 333
+        ins, outs, want = [], [], []
+        for r in range(nranks):
+            parts = [_rand(int(counts[r, p]), dtype, 1000 * it + 10 * r + p) for p in range(nranks)]
+            if parts[0].numel() > 2:
+                parts[0][1] = -0.0                     # the marker value as payload
+            ins.append(torch.cat(parts) if sum(p.numel() for p in parts) else torch.empty(0, dtype=dtype, device="cuda"))
+        for r in range(nranks):
+            total = int(counts[:, r].sum())
+            outs.append(torch.full((total + 3,), 7.0, dtype=dtype, device="cuda"))   # three guard elements behind
+        cap = int(counts.max()) * esz + 64
+        w.exchangev_lamport([t if t.numel() else torch.zeros(4, dtype=dtype, device="cuda") for t in ins], outs,
+                            (counts * esz).tolist(), cap)
+        torch.cuda.synchronize()
+        assert w.status()[0] == 0
+        for r in range(nranks):
+            at = 0
+            for s in range(nranks):
+                n = int(counts[s, r])
+                off = int(counts[s, :r].sum())
+                got, ref = outs[r][at : at + n], ins[s][off : off + n]
+                assert torch.equal(got.float(), ref.float()), (it, r, s, n)    # -0.0 == +0.0
+                at += n
+            assert torch.equal(outs[r][at:].float(), torch.full((3,), 7.0, device="cuda")), "wrote past its parts"
+        # an equal-split exchange in between uses the same buffers and call counters
+        part = 256
+        eins = [_rand(part * nranks, torch.float32, 5 * it + r) for r in range(nranks)]
+        eouts = [torch.empty_like(t) for t in eins]
+        w.exchange_lamport(1, eins, eouts, 1.0)
+        torch.cuda.synchronize()
+        for r in range(nranks):
+            for s in range(nranks):
+                assert torch.equal(eouts[r][s * part : (s + 1) * part], eins[s][r * part : (r + 1) * part])

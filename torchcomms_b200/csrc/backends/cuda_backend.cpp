@@ -1896,7 +1896,26 @@ WorkPtr CudaBackend::all_to_all_v_single(at::Tensor& out, const at::Tensor& in, 
   {
     const Algo forced = algo_override(o);
     SymmView sv;
-    if ((forced == Algo::AUTO || forced == Algo::KERNEL) && size_ > 1 && lookup_symm(out.data_ptr(), out.nbytes(), &sv)) {
+    size_t region = 0;
+    if ((forced == Algo::AUTO || forced == Algo::KERNEL) && size_ > 1 && lookup_symm(out.data_ptr(), out.nbytes(), &sv, &region)) {
+      // A small symmetric receive buffer bounds every part on every rank by the same number (no part can be larger
+      // than the buffer it lands in, and the buffer has the same size everywhere): the flag-less exchange, no
+      // barrier. Floating types only (a payload word equal to the poison value travels as +0.0).
+      if (region <= tune_.lamport_max_bytes && lamport_dtype(out.scalar_type())) {
+        at::Tensor i = in, ot = out;
+        return run("all_to_all_v_single/lamport", async_op, o, {in}, [this, i, ot, send, recv, region](cudaStream_t s) {
+          size_t so[kMaxRanks] = {}, sl[kMaxRanks] = {}, ro[kMaxRanks] = {}, rl[kMaxRanks] = {};
+          for (int p = 0; p < size_; ++p) {
+            so[p] = send[p].first;
+            sl[p] = send[p].second;
+            ro[p] = recv[p].first;
+            rl[p] = recv[p].second;
+          }
+          const void* ip = i.data_ptr();
+          void* op = ot.data_ptr();
+          B200C_CUDA_CHECK(launch_exchangev_lamport(&dev_, layout_, 0, &ip, &op, so, sl, ro, rl, region, s));
+        }, kChanSymAr, true);
+      }
       return exchange_symm(this, "all_to_all_v_single/symm", in, out, sv, send, recv, false, at::Tensor(), 1, async_op, o);
     }
   }
@@ -2233,7 +2252,7 @@ at::Tensor CudaBackend::symm_empty(const std::vector<int64_t>& sizes, at::Scalar
   auto seg = symm_->allocate(std::max<size_t>(bytes, 16), tune_.use_multicast);
   {
     std::lock_guard<std::mutex> g(symm_mu_);
-    symm_regs_[reinterpret_cast<uintptr_t>(seg->local())] = SymmReg{seg->bytes, seg, false};
+    symm_regs_[reinterpret_cast<uintptr_t>(seg->local())] = SymmReg{seg->bytes, seg, false, std::max<size_t>(bytes, 16)};
   }
   // The segment, not the tensor, owns the memory (unmapping is a collective matter).
   // (Under a test fake of the runtime the "device" memory is host memory.)
@@ -2280,7 +2299,7 @@ void CudaBackend::tensor_register(const at::Tensor& t) {
   }
   auto seg = symm_->attach_user_buffer(base, bytes, tune_.use_multicast);
   std::lock_guard<std::mutex> g(symm_mu_);
-  symm_regs_[reinterpret_cast<uintptr_t>(base)] = SymmReg{bytes, seg, true};
+  symm_regs_[reinterpret_cast<uintptr_t>(base)] = SymmReg{bytes, seg, true, bytes};
 }
 
 void CudaBackend::tensor_deregister(const at::Tensor& t) {
@@ -2304,7 +2323,7 @@ void CudaBackend::tensor_deregister(const at::Tensor& t) {
   symm_->release(seg);
 }
 
-bool CudaBackend::lookup_symm(const void* p, size_t bytes, SymmView* view) const {
+bool CudaBackend::lookup_symm(const void* p, size_t bytes, SymmView* view, size_t* region_bytes) const {
   std::lock_guard<std::mutex> g(symm_mu_);
   if (symm_regs_.empty()) return false;
   const uintptr_t a = reinterpret_cast<uintptr_t>(p);
@@ -2318,6 +2337,7 @@ bool CudaBackend::lookup_symm(const void* p, size_t bytes, SymmView* view) const
     view->ptr[r] = r < size_ ? seg.peer_ptrs[r] + off : nullptr;
   }
   view->mc = seg.mc_ptr != nullptr ? seg.mc_ptr + off : nullptr;
+  if (region_bytes != nullptr) *region_bytes = it->second.user_bytes;
   return true;
 }
 

@@ -199,7 +199,8 @@ class CudaBackend final : public Backend {
   void tensor_deregister(const at::Tensor& t) override;
   // Peer views of [p, p + bytes) if it lies inside a symmetric tensor or a
   // registered allocation.
-  bool lookup_symm(const void* p, size_t bytes, SymmView* view) const;
+  // `region_bytes` (optional): size the registration was made with, the same on every rank.
+  bool lookup_symm(const void* p, size_t bytes, SymmView* view, size_t* region_bytes = nullptr) const;
 
   // Backend-specific operations (reached through get_backend_impl()).
   // Split sizes live on the device (int64 counts of dim-0 slices).
@@ -338,6 +339,7 @@ class CudaBackend final : public Backend {
     size_t bytes = 0;
     std::shared_ptr<SymmSegment> seg;
     bool user_memory = false;   // registered allocation (not freed by symm_free)
+    size_t user_bytes = 0;      // size the caller asked for / registered: the same on every rank
   };
   mutable std::mutex symm_mu_;
   std::map<uintptr_t, SymmReg> symm_regs_;

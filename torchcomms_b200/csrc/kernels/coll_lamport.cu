@@ -350,6 +350,115 @@ struct XchgLamport {
   }
 };
 
+// All-to-all with unequal parts (floating types). Every rank knows from the call's arguments how many bytes it sends
+// to and receives from each peer, so no lengths travel: the sender stores len(rank -> p) bytes into p's slot, the
+// receiver polls exactly len(s -> rank) bytes of slot s. Which blocks take part must not depend on the rank: it is
+// `cap_bytes`, a bound that every rank derives from the same quantity (the size of the symmetric receive buffer).
+// Lengths need not be multiples of 16: the last vector of a part is sent padded with zeros and only its valid bytes
+// are written to the output.
+struct XchgvLamport {
+  struct Args {
+    const char* in;
+    char* out;
+    size_t send_off[kMaxRanks], send_len[kMaxRanks];
+    size_t recv_off[kMaxRanks], recv_len[kMaxRanks];
+    size_t cap_bytes;
+    size_t region_off;
+  };
+  static __device__ __forceinline__ size_t slot_off(const Args& a, uint32_t buf, int slot) {
+    return a.region_off +
+        ((static_cast<size_t>(buf) * kLamportBlocks + blockIdx.x) * kMaxRanks + slot) * kLamportPiece;
+  }
+  // 16 bytes starting at p of which only `valid` (1..16) may be read; the rest reads as zero.
+  static __device__ __forceinline__ uint4 load_tail(const char* p, size_t valid, bool aligned) {
+    if (valid >= 16) return ld16_any(p, aligned);
+    uint4 w = make_uint4(0u, 0u, 0u, 0u);
+    unsigned char* b = reinterpret_cast<unsigned char*>(&w);
+    for (size_t i = 0; i < valid; ++i) b[i] = static_cast<unsigned char>(p[i]);
+    return w;
+  }
+  static __device__ __forceinline__ void store_tail(char* p, uint4 w, size_t valid, bool aligned) {
+    if (valid >= 16) {
+      st16_any(p, w, aligned);
+      return;
+    }
+    const unsigned char* b = reinterpret_cast<const unsigned char*>(&w);
+    for (size_t i = 0; i < valid; ++i) p[i] = static_cast<char>(b[i]);
+  }
+  static __device__ void run(const CommDev& c, const Args& a) {
+    const size_t b0 = static_cast<size_t>(blockIdx.x) * kLamportPiece;
+    if (b0 >= a.cap_bytes) return;  // same decision on every rank
+    const uint32_t call = c.epochs[kFlagSetLamport * kMaxBlocks + blockIdx.x];
+    const uint32_t cur = call % 3u, prev = (call + 2u) % 3u;
+    const size_t pos = b0 + static_cast<size_t>(threadIdx.x) * 16;   // this thread's vector within every part
+    const size_t v16 = static_cast<size_t>(threadIdx.x) * 16;
+#pragma unroll
+    for (int i = 0; i < kMaxRanks; ++i) {
+      if (i < c.nranks) {
+        int p = c.rank + i;
+        if (p >= c.nranks) p -= c.nranks;
+        if (pos < a.send_len[p]) {
+          const char* src = a.in + a.send_off[p] + pos;
+          uint4 w = load_tail(src, a.send_len[p] - pos, (reinterpret_cast<uintptr_t>(src) & 15u) == 0);
+          w.x = unpoison(w.x);
+          w.y = unpoison(w.y);
+          w.z = unpoison(w.z);
+          w.w = unpoison(w.w);
+          st16(c.heap[p] + slot_off(a, cur, c.rank) + v16, w);
+        }
+      }
+    }
+    {
+      const uint4 poison = make_uint4(kLamportPoison, kLamportPoison, kLamportPoison, kLamportPoison);
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s) {
+        if (s < c.nranks) st16(c.heap[c.rank] + slot_off(a, prev, s) + v16, poison);
+      }
+    }
+    uint32_t pending = 0;
+#pragma unroll
+    for (int s = 0; s < kMaxRanks; ++s) {
+      if (s < c.nranks && pos < a.recv_len[s]) pending |= 1u << s;
+    }
+    bool ok = true;
+    unsigned long long start = 0;
+    uint32_t spins = 0;
+    while (pending != 0u && ok) {
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s) {
+        if (s < c.nranks && (pending >> s & 1u)) {
+          const uint4 x = ld16_volatile(c.heap[c.rank] + slot_off(a, cur, s) + v16);
+          if (x.x != kLamportPoison && x.y != kLamportPoison && x.z != kLamportPoison && x.w != kLamportPoison) {
+            char* dst = a.out + a.recv_off[s] + pos;
+            store_tail(dst, x, a.recv_len[s] - pos, (reinterpret_cast<uintptr_t>(dst) & 15u) == 0);
+            pending &= ~(1u << s);
+          }
+        }
+      }
+      if (pending != 0u && ++spins >= 64u) {
+        spins = 0;
+        const unsigned long long now = globaltimer_ns();
+        if (start == 0) {
+          start = now;
+        } else if (now - start > 200000ull) {
+          if (comm_is_dead(c)) {
+            ok = false;
+          } else if (now - start > c.timeout_ns) {
+            int missing = 0;
+            for (int s = 0; s < c.nranks; ++s) {
+              if (pending >> s & 1u) missing = s;
+            }
+            report_timeout(c, missing, 0x63);
+            ok = false;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) c.epochs[kFlagSetLamport * kMaxBlocks + blockIdx.x] = call + 1u;
+  }
+};
+
 __global__ void k_fill_u32(uint32_t* p, size_t words, uint32_t value) {
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < words;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -422,6 +531,34 @@ cudaError_t launch_exchange_lamport(const CommDev* comms, const HeapLayout& lay,
     case DType::BF16: return go(__nv_bfloat16{}, R{});
   }
   return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_exchangev_lamport(const CommDev* comms, const HeapLayout& lay, int emu_ranks, const void* const* in,
+                                     void* const* out, const size_t* send_off, const size_t* send_len, const size_t* recv_off,
+                                     const size_t* recv_len, size_t cap_bytes, cudaStream_t stream) {
+  using namespace coll;
+  const int n = emu_ranks > 0 ? emu_ranks : 1;
+  const int nr = comms[0].nranks;
+  if (lay.lamport_bytes < kLamportBytes) return cudaErrorInvalidValue;
+  if (cap_bytes == 0 || cap_bytes > static_cast<size_t>(kLamportBlocks) * kLamportPiece) return cudaErrorInvalidValue;
+  std::vector<XchgvLamport::Args> args(n);
+  for (int i = 0; i < n; ++i) {
+    XchgvLamport::Args& a = args[i];
+    a = XchgvLamport::Args{};
+    a.in = static_cast<const char*>(in[i]);
+    a.out = static_cast<char*>(out[i]);
+    for (int p = 0; p < nr; ++p) {
+      a.send_off[p] = send_off[i * kMaxRanks + p];
+      a.send_len[p] = send_len[i * kMaxRanks + p];
+      a.recv_off[p] = recv_off[i * kMaxRanks + p];
+      a.recv_len[p] = recv_len[i * kMaxRanks + p];
+      if (a.send_len[p] > cap_bytes || a.recv_len[p] > cap_bytes) return cudaErrorInvalidValue;
+    }
+    a.cap_bytes = cap_bytes;
+    a.region_off = lay.lamport_off;
+  }
+  const int blocks = static_cast<int>((cap_bytes + kLamportPiece - 1) / kLamportPiece);
+  return launch_op<XchgvLamport>(comms, emu_ranks, args.data(), blocks, kLamportThreads, stream, true);
 }
 
 } // namespace b200c

@@ -150,6 +150,12 @@ cudaError_t launch_all_reduce_lamport(const CommDev* comms, const HeapLayout& la
 cudaError_t launch_exchange_lamport(const CommDev* comms, const HeapLayout& lay, int emu_ranks, int mode,
                                     const void* const* in, void* const* out, size_t part_bytes, DType dtype, float scale,
                                     bool use_mc, cudaStream_t stream);
+// The same arrival protocol for an all-to-all with unequal parts (floating types; any byte lengths). Per rank i and
+// peer p: send_off / send_len / recv_off / recv_len [i * kMaxRanks + p] in bytes. `cap_bytes` bounds every part
+// and must be derived from a quantity that is the same on every rank (it decides how many blocks take part).
+cudaError_t launch_exchangev_lamport(const CommDev* comms, const HeapLayout& lay, int emu_ranks, const void* const* in,
+                                     void* const* out, const size_t* send_off, const size_t* send_len, const size_t* recv_off,
+                                     const size_t* recv_len, size_t cap_bytes, cudaStream_t stream);
 
 // All-to-all with per-peer byte counts. send_off/send_len/recv_off/recv_len
 // are arrays of nranks entries per rank (emu: emu_ranks x nranks, row-major).

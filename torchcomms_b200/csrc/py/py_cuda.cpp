@@ -318,6 +318,34 @@ class EmuWorld {
     B200C_CUDA_CHECK(launch_exchange_lamport(comms_.data(), lay_, n_, mode, ip.data(), op.data(), part, dtype_of(ins[0]),
                                              static_cast<float>(scale), false, stream()));
   }
+  // All-to-all with unequal parts: send_bytes[r][p] = bytes rank r sends to rank p (parts packed back to back on
+  // both sides, in rank order). `cap_bytes` bounds every part.
+  void exchangev_lamport(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs,
+                         std::vector<std::vector<int64_t>> send_bytes, int64_t cap_bytes) {
+    check(ins);
+    check(outs);
+    TORCH_CHECK(static_cast<int>(send_bytes.size()) == n_, "one list of part sizes per rank");
+    std::vector<const void*> ip(n_);
+    std::vector<void*> op(n_);
+    std::vector<size_t> so(n_ * kMaxRanks, 0), sl(n_ * kMaxRanks, 0), ro(n_ * kMaxRanks, 0), rl(n_ * kMaxRanks, 0);
+    for (int r = 0; r < n_; ++r) {
+      ip[r] = ins[r].data_ptr();
+      op[r] = outs[r].data_ptr();
+      TORCH_CHECK(static_cast<int>(send_bytes[r].size()) == n_, "one part size per peer");
+      size_t s_at = 0, r_at = 0;
+      for (int p = 0; p < n_; ++p) {
+        so[r * kMaxRanks + p] = s_at;
+        sl[r * kMaxRanks + p] = static_cast<size_t>(send_bytes[r][p]);
+        s_at += sl[r * kMaxRanks + p];
+        ro[r * kMaxRanks + p] = r_at;
+        rl[r * kMaxRanks + p] = static_cast<size_t>(send_bytes[p][r]);
+        r_at += rl[r * kMaxRanks + p];
+      }
+      TORCH_CHECK(s_at <= ins[r].nbytes() && r_at <= outs[r].nbytes(), "parts exceed the buffers");
+    }
+    B200C_CUDA_CHECK(launch_exchangev_lamport(comms_.data(), lay_, n_, ip.data(), op.data(), so.data(), sl.data(), ro.data(),
+                                              rl.data(), static_cast<size_t>(cap_bytes), stream()));
+  }
   void barrier() { B200C_CUDA_CHECK(launch_barrier(comms_.data(), n_, stream())); }
   // Runs the kernel whose wait can never be satisfied; returns the status words.
   std::vector<uint32_t> wait_unset_flag() {
@@ -548,6 +576,7 @@ void bind_cuda_backend(py::module_& m) {
       .def("symm_all_to_all", &EmuWorld::symm_all_to_all)
       .def("all_reduce_lamport", &EmuWorld::all_reduce_lamport)
       .def("exchange_lamport", &EmuWorld::exchange_lamport)
+      .def("exchangev_lamport", &EmuWorld::exchangev_lamport)
       .def("broadcast", &EmuWorld::broadcast)
       .def("barrier", &EmuWorld::barrier)
       .def("wait_unset_flag", &EmuWorld::wait_unset_flag)

@@ -96,6 +96,7 @@ def sweep_collectives(
     iters: int = 100,
     arms: Iterable[str] = ("own", "nccl"),
     log: Optional[Callable[[str], None]] = None,
+    small_recv_bytes: int = 1 << 20,
 ) -> List[dict]:
     """Rows of {op, dtype, bytes, arm, avg_us, p50_us, algbw_gbs, busbw_gbs}.
 
@@ -130,6 +131,7 @@ def sweep_collectives(
                 n = max(world * (16 // esz), nbytes // esz // (world * (16 // esz)) * (world * (16 // esz)))
                 total = n * esz
                 for arm in arms:
+                    own_small = None
                     hints = {"algo": "nccl"} if arm == "nccl" else None
                     sym = symm_raw[:total].view(dt)
                     pa = plain_a[:total].view(dt)
@@ -152,13 +154,24 @@ def sweep_collectives(
                         row = 16 // esz  # rows of 16 bytes
                         send, recv = a2av_splits(comm.get_rank(), world, n // row)
                         src = pb.view(-1, row)
-                        dst = (sym if arm == "own" else pa).view(-1, row)
+                        if arm == "own" and total <= small_recv_bytes:
+                            # A receive buffer of the message's own size, as a caller with small messages allocates
+                            # it: its size bounds every part on every rank, which lets the backend take the
+                            # flag-less exchange. (The other points share one large symmetric buffer.)
+                            own_small = comm.symm_empty((total,), torch.uint8)
+                            dst = own_small.view(dt).view(-1, row)
+                        else:
+                            dst = (sym if arm == "own" else pa).view(-1, row)
                         fn = lambda src=src, dst=dst, send=send, recv=recv: comm.all_to_all_v_single(
                             dst, src, recv, send, False, hints=hints)
                         factor = (world - 1) / world
                     else:
                         raise ValueError(f"unknown op {op}")
                     t = time_calls(comm, fn, warmup, iters, device)
+                    if own_small is not None:
+                        torch.cuda.synchronize()
+                        comm.symm_free(own_small)
+                        own_small = None
                     algbw = total / t["avg_us"] / 1e3
                     r = {
                         "op": op, "dtype": dname, "bytes": total, "arm": arm,
