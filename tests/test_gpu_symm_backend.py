@@ -118,6 +118,11 @@ def _symm_battery(rank, world):
         torch.cuda.synchronize()
         assert torch.equal(dst[: sum(out_splits)], want), it
     comm.symm_free(dst)
+    # ordinary tensors with a bound on the parts given by the caller: the flag-less exchange as well
+    plain = torch.zeros(sum(out_splits), 3, device=dev)
+    comm.all_to_all_v_single(plain, src, out_splits, in_splits, False, hints={"max_part_bytes": "4096"})
+    torch.cuda.synchronize()
+    assert torch.equal(plain, want)
     # a large one: the one-pass push, with host splits and with splits that live on the device
     dst = comm.symm_empty((400_000 + world * world, 3), torch.float32)
     dst.zero_()
@@ -131,7 +136,7 @@ def _symm_battery(rank, world):
     comm.symm_free(dst)
     if world > 1:
         assert count("all_to_all_single/symm") >= 1 and count("all_to_all_single/lamport") >= 1
-        assert count("all_to_all_v_single/lamport") >= 3 and count("all_to_all_v_single/symm") >= 1
+        assert count("all_to_all_v_single/lamport") >= 4 and count("all_to_all_v_single/symm") >= 1
         assert count("device_alltoallv/symm") >= 1
 
     # ---- operations of different channels in flight together

@@ -1895,6 +1895,30 @@ WorkPtr CudaBackend::all_to_all_v_single(at::Tensor& out, const at::Tensor& in, 
   bytes_issued_ += so;
   {
     const Algo forced = algo_override(o);
+    // The flag-less exchange needs a bound on every part that all ranks share. The caller may give one
+    // (hint `max_part_bytes`, the same on every rank; then the tensors may live anywhere) ...
+    const size_t hinted = hint_or<size_t>(o.hints, "max_part_bytes", 0);
+    if ((forced == Algo::AUTO || forced == Algo::KERNEL) && size_ > 1 && hinted > 0 && hinted <= tune_.lamport_max_bytes &&
+        lamport_dtype(out.scalar_type())) {
+      for (int p = 0; p < size_; ++p) {
+        TORCH_CHECK(send[p].second <= hinted && recv[p].second <= hinted,
+                    "all_to_all_v_single: a part exceeds the max_part_bytes hint (", hinted, ")");
+      }
+      at::Tensor i = in, ot = out;
+      return run("all_to_all_v_single/lamport", async_op, o, {in}, [this, i, ot, send, recv, hinted](cudaStream_t s) {
+        size_t so[kMaxRanks] = {}, sl[kMaxRanks] = {}, ro[kMaxRanks] = {}, rl[kMaxRanks] = {};
+        for (int p = 0; p < size_; ++p) {
+          so[p] = send[p].first;
+          sl[p] = send[p].second;
+          ro[p] = recv[p].first;
+          rl[p] = recv[p].second;
+        }
+        const void* ip = i.data_ptr();
+        void* op = ot.data_ptr();
+        B200C_CUDA_CHECK(launch_exchangev_lamport(&dev_, layout_, 0, &ip, &op, so, sl, ro, rl, hinted, s));
+      }, kChanSymAr, true);
+    }
+    // ... or it follows from the size of a symmetric receive buffer.
     SymmView sv;
     size_t region = 0;
     if ((forced == Algo::AUTO || forced == Algo::KERNEL) && size_ > 1 && lookup_symm(out.data_ptr(), out.nbytes(), &sv, &region)) {
