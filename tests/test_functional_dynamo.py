@@ -1,0 +1,210 @@
+"""Communicator objects inside ``torch.compile(fullgraph=True)`` regions: methods of a ``TorchComm`` are
+recorded as this package's operators, rank / size / name fold to constants, asynchronous calls keep their
+start / wait structure in the graph, and the eager behaviour of the same methods is unchanged.
+
+Parity: comms/torchcomms/tests/integration/py/FullgraphCompileTest.py (communicator methods called on the
+object inside a compiled function) and the unit tests of comms/torchcomms/functional/dynamo.py.
+"""
+from datetime import timedelta
+
+import pytest
+
+import torch
+
+from tests.mp_util import run_ranks
+
+
+def _graph_ops(fn, *args):
+    """Runs ``fn`` under torch.compile with a backend that records the operator names of the traced graph."""
+    seen = []
+
+    def backend(gm, example_inputs):
+        for n in gm.graph.nodes:
+            if n.op == "call_function":
+                seen.append(getattr(n.target, "__name__", str(n.target)))
+        return gm.forward
+
+    out = torch.compile(fn, fullgraph=True, backend=backend)(*args)
+    return out, seen
+
+
+def _dynamo_worker(rank, world):
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import ReduceOp
+    from torchcomms_b200.functional import dynamo as D
+
+    D.register_with_dynamo()
+    D.register_with_dynamo()                      # idempotent
+    comm = tc.new_comm("gloo", torch.device("cpu"), name="dyn", timeout=timedelta(seconds=60))
+    tri = world * (world + 1) // 2
+
+    # eager calls go straight through the original methods
+    t = torch.full((4,), float(rank + 1))
+    assert comm.all_reduce(t, ReduceOp.SUM, False) is not None and torch.equal(t, torch.full((4,), float(tri)))
+    assert comm.get_rank() == rank and comm.get_size() == world and comm.get_name() == "dyn"
+
+    def step(x, out_g, out_s):
+        y = x * 2
+        comm.all_reduce(y, ReduceOp.SUM, False)                                 # in place on an intermediate
+        w = comm.all_gather_single(out_g, x, True)                              # asynchronous, into a graph input
+        z = y + comm.get_rank() + 10 * comm.get_size()                          # constants of the graph
+        comm.reduce_scatter_single(out_s, z.repeat(comm.get_size()), ReduceOp.AVG, False)
+        w.wait()
+        comm.barrier(False)
+        return z, out_g.sum() + out_s.sum()
+
+    x = torch.full((4,), float(rank + 1))
+    out_g, out_s = torch.zeros(world * 4), torch.zeros(4)
+    (z, total), seen = _graph_ops(step, x, out_g, out_s)
+    exp_z = torch.full((4,), 2.0 * tri + rank + 10 * world)
+    assert torch.equal(z, exp_z)
+    assert torch.equal(out_g, torch.arange(1, world + 1, dtype=torch.float32).repeat_interleave(4))   # written through
+    exp_s = torch.full((4,), 2.0 * tri + 10 * world + (world - 1) / 2)
+    assert torch.allclose(out_s, exp_s)
+    assert torch.allclose(total, out_g.sum() + out_s.sum())
+    joined = " ".join(seen)
+    for name in ("all_reduce", "all_gather_single_start", "wait_tensor", "reduce_scatter_single", "barrier"):
+        assert name in joined, (name, seen)
+    first = lambda part: next(i for i, s in enumerate(seen) if part in s)  # noqa: E731
+    assert first("all_gather_single_start") < first("reduce_scatter_single") < first("wait_tensor")   # the wait stays where it was called
+
+    # the same function through AOT autograd (functionalisation of the copies into inputs and intermediates)
+    out_g2, out_s2 = torch.zeros(world * 4), torch.zeros(4)
+    z2, total2 = torch.compile(step, fullgraph=True, backend="aot_eager")(x, out_g2, out_s2)
+    assert torch.equal(z2, exp_z) and torch.equal(out_g2, out_g) and torch.allclose(out_s2, exp_s)
+    assert torch.allclose(total2, total)
+
+    # list forms, broadcast, all-to-all and point-to-point in one region
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+
+    def more(x):
+        parts = [torch.empty_like(x) for _ in range(comm.get_size())]
+        comm.all_gather(parts, x, False)
+        b = x.clone()
+        comm.broadcast(b, 0, False)
+        a = torch.empty(comm.get_size() * 2)
+        comm.all_to_all_single(a, torch.arange(comm.get_size() * 2.0) + 100 * comm.get_rank(), False)
+        got = torch.empty_like(x)
+        if comm.get_rank() % 2 == 0:
+            comm.send(x, nxt, False)
+            comm.recv(got, prv, False)
+        else:
+            comm.recv(got, prv, False)
+            comm.send(x, nxt, False)
+        return torch.stack(parts).sum(0), b, a, got
+
+    s, b, a, got = torch.compile(more, fullgraph=True, backend="aot_eager")(x)
+    assert torch.equal(s, torch.full((4,), float(tri))) and torch.equal(b, torch.full((4,), 1.0))
+    assert torch.equal(a, torch.cat([torch.arange(2.0) + 2 * rank + 100 * src for src in range(world)]))
+    assert torch.equal(got, torch.full((4,), float(prv + 1)))
+
+    # a split communicator is enabled as it is made
+    sub = comm.split(list(range(world)), "dyn_sub")
+
+    def on_sub(x):
+        y = x.clone()
+        sub.all_reduce(y, ReduceOp.MAX, False)
+        return y * sub.get_size()
+
+    assert torch.equal(torch.compile(on_sub, fullgraph=True, backend="aot_eager")(x), torch.full((4,), float(world * world)))
+    sub.finalize()
+    comm.finalize()
+    D.unregister_from_dynamo()
+    assert not D.is_registered() and type(tc.TorchComm.get_rank).__name__ != "function"
+
+
+def test_communicator_methods_compile_fullgraph_over_gloo():
+    run_ranks(_dynamo_worker, 2, timeout=300)
+
+
+def test_unknown_communicator_or_reduce_op_is_reported_at_trace_time():
+    import os
+
+    import pytest
+
+    os.environ.update(RANK="0", WORLD_SIZE="1")
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import ReduceOp
+    from torchcomms_b200.functional import dynamo as D
+
+    made_before = tc.new_comm("fake", torch.device("cpu"), name="dyn_before")
+    D.register_with_dynamo()
+    try:
+        def f(x, c, op):
+            y = x.clone()
+            c.all_reduce(y, op, False)
+            return y
+
+        with pytest.raises(Exception):
+            torch.compile(f, fullgraph=True, backend="eager")(torch.ones(2), made_before, ReduceOp.SUM)   # never enabled
+        D.enable(made_before)
+        torch._dynamo.reset()
+        assert torch.equal(torch.compile(f, fullgraph=True, backend="eager")(torch.ones(2), made_before, ReduceOp.SUM), torch.ones(2))
+        mine = ReduceOp(tc.RedOpType.MAX)                                                                   # not the predefined object
+        with pytest.raises(Exception):
+            torch.compile(f, fullgraph=True, backend="eager")(torch.ones(2), made_before, mine)
+        D.register_reduce_op(mine, "max")
+        torch._dynamo.reset()
+        torch.compile(f, fullgraph=True, backend="eager")(torch.ones(2), made_before, mine)
+    finally:
+        made_before.finalize()
+        D.unregister_from_dynamo()
+
+
+def test_inductor_lowerings_are_registered():
+    from torch._inductor.lowering import lowerings
+
+    from torchcomms_b200.functional import inductor as I
+
+    assert I.register_with_inductor() and I.register_with_inductor()
+    for op in I.lowered_ops():
+        assert op in lowerings, op
+    import torch.fx.node as fx_node
+
+    assert torch.ops.torchcomms_b200.barrier.default in fx_node._side_effectful_functions
+
+
+@pytest.mark.gpu
+def test_inductor_compiles_communicator_methods_on_gpu():
+    """Inductor backend on a CUDA communicator: the in-place all-reduce lowering, a started all-gather with its
+    wait, the default handling of the other operators, against the eager run of the same function."""
+    import os
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29631")
+    os.environ["RANK"], os.environ["WORLD_SIZE"] = "0", "1"
+    import torchcomms_b200 as tc
+    from torch._inductor.utils import run_and_get_code
+    from torchcomms_b200 import ReduceOp
+    from torchcomms_b200.functional import dynamo as D
+    from torchcomms_b200.functional import inductor as I
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    D.register_with_dynamo()
+    assert I.register_with_inductor()
+    comm = tc.new_comm("b200", dev, name="ind_gpu", abort_process_on_timeout_or_error=False)
+    try:
+        def step(x, out_g):
+            y = x * 2 + 1
+            comm.all_reduce(y, ReduceOp.SUM, False)
+            w = comm.all_gather_single(out_g, y, True)
+            z = torch.relu(y - 3) * comm.get_size()
+            s = torch.empty_like(z)
+            comm.reduce_scatter_single(s, z, ReduceOp.SUM, False)
+            w.wait()
+            return s + out_g.view_as(s)
+
+        x = torch.randn(1024, 64, device=dev)
+        ref_g = torch.zeros(1024 * 64, device=dev)
+        ref = step(x, ref_g)
+        out_g = torch.zeros(1024 * 64, device=dev)
+        got, codes = run_and_get_code(torch.compile(step, fullgraph=True, backend="inductor"), x, out_g)
+        torch.cuda.synchronize()
+        assert torch.allclose(got, ref) and torch.equal(out_g, ref_g)
+        code = "\n".join(codes)
+        assert "torchcomms_b200.all_reduce_inplace" in code     # lowered to the in-place kernel
+        assert "all_gather_single_start" in code and "wait_tensor" in code and "reduce_scatter_single" in code
+    finally:
+        comm.finalize()
+        D.unregister_from_dynamo()

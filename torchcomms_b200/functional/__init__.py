@@ -19,11 +19,17 @@ respect to the caller's stream (stream-ordered ``wait``), so no separate
 ``wait_tensor`` is needed; one is provided as an identity for code written
 against functional-collective APIs.
 
+Code that calls methods of the communicator object itself compiles after
+``functional.dynamo.register_with_dynamo()``; ``functional.inductor.
+register_with_inductor()`` adds Inductor lowerings (in-place all-reduce and
+broadcast kernels, start / wait kernels that keep a started collective's
+input alive).  Without the latter the operators run as opaque functional calls
+inside compiled graphs, which is correct but copies more.
+
 Parity: comms/torchcomms/functional/{registry,collectives,async_tensor,
-param_parsing,dynamo,inductor_lowering,passes}.py.  The reference lowers its
-ops inside Inductor and reorders waits in graph passes; this framework keeps
-compiled graphs opaque around collectives (CUDA streams and graphs provide the
-overlap instead of a tracing compiler), so those passes have no counterpart.
+param_parsing,dynamo,inductor_lowering,passes}.py.  Overlap in this framework
+comes from CUDA streams and graphs rather than from a tracing compiler, so the
+compile path is kept correct and cheap, not tuned.
 """
 from __future__ import annotations
 

@@ -1,0 +1,321 @@
+"""``torch.compile`` support for code that holds a ``TorchComm`` itself.
+
+The traceable operators of this package take a communicator's *name*; code
+written against the eager API calls methods of the communicator object, which
+is a C++ object the tracer cannot look into.  After ``register_with_dynamo()``
+the same code compiles with ``fullgraph=True``::
+
+    from torchcomms_b200.functional.dynamo import register_with_dynamo
+    register_with_dynamo()                     # once per process
+    comm = torchcomms_b200.new_comm("b200", device, name="dp")
+
+    @torch.compile(fullgraph=True)
+    def step(x):
+        comm.all_reduce(x, ReduceOp.SUM, False)            # recorded as torchcomms_b200::all_reduce + copy_
+        work = comm.all_gather_single(out, x, True)        # ..._start now, wait_tensor at work.wait()
+        ...
+        work.wait()
+        return out * comm.get_rank()                        # a constant of the graph
+
+How: the bound class gets Python methods in front of its C++ ones.  Outside a
+compiled region they call straight through.  Inside, the tracer inlines them
+(they are plain Python), finds the communicator's traceable stand-in through
+``id(comm)`` (which the tracer evaluates and guards on), and records the
+functional operator followed by a ``copy_`` into the tensor the eager call
+would have written; functionalisation turns that into data flow.  Reduce
+operations are recognised the same way, by the identity of ``ReduceOp.SUM``
+and friends.  Nothing inside the tracer is patched.
+
+Counterpart in the reference: comms/torchcomms/functional/dynamo.py, which
+registers the communicator as an opaque script object and replaces the tracer's
+handling of its method calls (``TorchCommMethodVariable``); the effect for user
+code - communicator methods usable in compiled regions, rank and size folded
+to constants - is the same.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+from torch import Tensor
+
+from .. import ReduceOp, TorchComm
+from . import NAMESPACE
+
+_ops = getattr(torch.ops, NAMESPACE)
+
+
+class _Traceable:
+    """What a compiled region knows of a communicator: three constants."""
+
+    def __init__(self, comm: TorchComm, orig):
+        self.name = _name_of(comm, orig)
+        self.rank = orig["get_rank"](comm)
+        self.size = orig["get_size"](comm)
+
+
+def _name_of(comm: TorchComm, orig) -> str:
+    from . import _comms as registry
+
+    key = orig["get_name"](comm)
+    registry.setdefault(key, comm)
+    return key
+
+
+_BY_ID: Dict[int, _Traceable] = {}
+_REDUCE_BY_ID: Dict[int, str] = {}
+_ORIG: Dict[str, object] = {}
+
+
+class TracedCommWork:
+    """Work handle of a communicator method called inside a compiled region.
+
+    Synchronous calls are complete when they return.  For ``async_op=True`` the
+    graph holds the started collective; ``wait()`` records ``wait_tensor`` and
+    the copy into the caller's output."""
+
+    def __init__(self, dsts: Optional[List[Tensor]] = None, pending: Optional[List[Tensor]] = None):
+        self.dsts = dsts
+        self.pending = pending
+
+    def wait(self) -> bool:
+        if self.pending is not None:
+            for dst, src in zip(self.dsts, self.pending):
+                dst.copy_(_ops.wait_tensor(src).view(dst.shape))
+            self.pending = None
+            self.dsts = None
+        return True
+
+    def is_completed(self) -> bool:
+        return self.pending is None
+
+
+def enable(comm: TorchComm) -> TorchComm:
+    """Makes ``comm`` usable inside compiled regions (communicators created after
+    ``register_with_dynamo()`` are enabled when they are created)."""
+    orig = _ORIG if _ORIG else {n: getattr(TorchComm, n) for n in ("get_name", "get_rank", "get_size")}
+    _BY_ID[id(comm)] = _Traceable(comm, orig)
+    return comm
+
+
+def _traceable(comm) -> _Traceable:
+    # Evaluated by the tracer: id() of a Python object is a guarded constant there.
+    return _BY_ID[id(comm)]
+
+
+def _red(op) -> str:
+    if isinstance(op, str):
+        return op
+    return _REDUCE_BY_ID[id(op)]
+
+
+def register_reduce_op(op: ReduceOp, name: str) -> None:
+    """Lets compiled regions recognise a reduce operation object other than the predefined ones
+    (``name``: one of the operators' reduce names)."""
+    _REDUCE_BY_ID[id(op)] = name
+
+
+def _finish(dsts: Sequence[Tensor], results: Sequence[Tensor], async_op: bool, started: bool) -> TracedCommWork:
+    if async_op and started:
+        return TracedCommWork(list(dsts), list(results))
+    for dst, src in zip(dsts, results):
+        dst.copy_(src.view(dst.shape))
+    return TracedCommWork()
+
+
+# One function per communicator method.  Signatures follow the bound methods
+# (tensor arguments, async_op, hints, timeout); hints and timeouts are per-call
+# tuning of the eager path and are not recorded in the graph.
+
+
+def _m_get_rank(self):
+    if torch.compiler.is_compiling():
+        return _traceable(self).rank
+    return _ORIG["get_rank"](self)
+
+
+def _m_get_size(self):
+    if torch.compiler.is_compiling():
+        return _traceable(self).size
+    return _ORIG["get_size"](self)
+
+
+def _m_get_name(self):
+    if torch.compiler.is_compiling():
+        return _traceable(self).name
+    return _ORIG["get_name"](self)
+
+
+def _m_all_reduce(self, tensor, op, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        name = _traceable(self).name
+        if async_op:
+            return _finish([tensor], [_ops.all_reduce_start(tensor, _red(op), name)], True, True)
+        return _finish([tensor], [_ops.all_reduce(tensor, _red(op), name)], False, False)
+    return _ORIG["all_reduce"](self, tensor, op, async_op, hints, timeout)
+
+
+def _m_broadcast(self, tensor, root, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        return _finish([tensor], [_ops.broadcast(tensor, root, _traceable(self).name)], async_op, False)
+    return _ORIG["broadcast"](self, tensor, root, async_op, hints, timeout)
+
+
+def _m_reduce(self, tensor, root, op, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        return _finish([tensor], [_ops.reduce(tensor, root, _red(op), _traceable(self).name)], async_op, False)
+    return _ORIG["reduce"](self, tensor, root, op, async_op, hints, timeout)
+
+
+def _m_all_gather_single(self, output, input, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        name = _traceable(self).name
+        flat = input.reshape(1, -1)
+        if async_op:
+            return _finish([output], [_ops.all_gather_single_start(flat, name)], True, True)
+        return _finish([output], [_ops.all_gather_single(flat, name)], False, False)
+    return _ORIG["all_gather_single"](self, output, input, async_op, hints, timeout)
+
+
+def _m_reduce_scatter_single(self, output, input, op, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        t = _traceable(self)
+        rows = input.reshape(t.size, -1)
+        if async_op:
+            return _finish([output], [_ops.reduce_scatter_single_start(rows, _red(op), t.name)], True, True)
+        return _finish([output], [_ops.reduce_scatter_single(rows, _red(op), t.name)], False, False)
+    return _ORIG["reduce_scatter_single"](self, output, input, op, async_op, hints, timeout)
+
+
+def _m_all_to_all_single(self, output, input, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        t = _traceable(self)
+        rows = input.reshape(t.size, -1)
+        if async_op:
+            return _finish([output], [_ops.all_to_all_single_start(rows, None, None, t.name)], True, True)
+        return _finish([output], [_ops.all_to_all_single(rows, None, None, t.name)], False, False)
+    return _ORIG["all_to_all_single"](self, output, input, async_op, hints, timeout)
+
+
+def _m_all_to_all_v_single(self, output, input, output_split_sizes, input_split_sizes, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        name = _traceable(self).name
+        outs, ins = list(output_split_sizes), list(input_split_sizes)
+        if async_op:
+            return _finish([output], [_ops.all_to_all_single_start(input, outs, ins, name)], True, True)
+        return _finish([output], [_ops.all_to_all_single(input, outs, ins, name)], False, False)
+    return _ORIG["all_to_all_v_single"](self, output, input, output_split_sizes, input_split_sizes, async_op, hints, timeout)
+
+
+def _m_all_gather(self, tensor_list, tensor, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        return _finish(tensor_list, _ops.all_gather(tensor, _traceable(self).name), async_op, False)
+    return _ORIG["all_gather"](self, tensor_list, tensor, async_op, hints, timeout)
+
+
+def _m_reduce_scatter(self, output, input_list, op, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        return _finish([output], [_ops.reduce_scatter(list(input_list), _red(op), _traceable(self).name)], async_op, False)
+    return _ORIG["reduce_scatter"](self, output, input_list, op, async_op, hints, timeout)
+
+
+def _m_all_to_all(self, output_tensor_list, input_tensor_list, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        return _finish(output_tensor_list, _ops.all_to_all(list(input_tensor_list), _traceable(self).name), async_op, False)
+    return _ORIG["all_to_all"](self, output_tensor_list, input_tensor_list, async_op, hints, timeout)
+
+
+def _m_send(self, tensor, dst, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        _ops.send(tensor, dst, _traceable(self).name)
+        return TracedCommWork()
+    return _ORIG["send"](self, tensor, dst, async_op, hints, timeout)
+
+
+def _m_recv(self, tensor, src, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        return _finish([tensor], [_ops.recv(tensor, src, _traceable(self).name)], async_op, False)
+    return _ORIG["recv"](self, tensor, src, async_op, hints, timeout)
+
+
+def _m_barrier(self, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        _ops.barrier(torch.zeros(()), _traceable(self).name)
+        return TracedCommWork()
+    return _ORIG["barrier"](self, async_op, hints, timeout)
+
+
+def _m_finalize(self):
+    _BY_ID.pop(id(self), None)
+    return _ORIG["finalize"](self)
+
+
+def _m_split(self, ranks, name, hints=None, timeout=None):
+    child = _ORIG["split"](self, ranks, name, hints, timeout)
+    if child is not None:
+        enable(child)
+    return child
+
+
+_METHODS = {
+    "get_rank": _m_get_rank, "get_size": _m_get_size, "get_name": _m_get_name,
+    "all_reduce": _m_all_reduce, "broadcast": _m_broadcast, "reduce": _m_reduce,
+    "all_gather_single": _m_all_gather_single, "reduce_scatter_single": _m_reduce_scatter_single,
+    "all_to_all_single": _m_all_to_all_single, "all_to_all_v_single": _m_all_to_all_v_single,
+    "all_gather": _m_all_gather, "reduce_scatter": _m_reduce_scatter, "all_to_all": _m_all_to_all,
+    "send": _m_send, "recv": _m_recv, "barrier": _m_barrier, "finalize": _m_finalize, "split": _m_split,
+}
+
+def is_registered() -> bool:
+    return bool(_ORIG)
+
+
+def register_with_dynamo() -> None:
+    """Puts the traceable methods in front of the communicator's bound methods (idempotent) and
+    enables every communicator the operator registry already knows."""
+    if _ORIG:
+        return
+    import torchcomms_b200 as pkg
+    from . import _comms as registry
+    from . import ext  # noqa: F401  (defines the *_start, list and window operators)
+    from .inductor import mark_side_effects
+
+    for name in _METHODS:
+        _ORIG[name] = getattr(TorchComm, name)
+    for name, fn in _METHODS.items():
+        fn.__name__ = name
+        fn.__qualname__ = f"TorchComm.{name}"
+        fn.__doc__ = getattr(_ORIG[name], "__doc__", None)
+        setattr(TorchComm, name, fn)
+    for op_name, red in (("SUM", "sum"), ("AVG", "avg"), ("MAX", "max"), ("MIN", "min"), ("PRODUCT", "product")):
+        _REDUCE_BY_ID[id(getattr(ReduceOp, op_name))] = red
+    mark_side_effects()     # a barrier or send whose result nobody reads stays in the graph
+
+    # Communicators made from now on are enabled as they are made.
+    made = pkg.new_comm
+    _ORIG["new_comm"] = made
+
+    def new_comm(*args, **kwargs):
+        return enable(made(*args, **kwargs))
+
+    new_comm.__doc__ = made.__doc__
+    pkg.new_comm = new_comm
+    for comm in list(registry.values()):
+        enable(comm)
+
+
+def unregister_from_dynamo() -> None:
+    """Restores the bound methods (for tests)."""
+    if not _ORIG:
+        return
+    import torchcomms_b200 as pkg
+
+    pkg.new_comm = _ORIG.pop("new_comm")
+    for name, fn in list(_ORIG.items()):
+        setattr(TorchComm, name, fn)
+    _ORIG.clear()
+    _BY_ID.clear()
+    _REDUCE_BY_ID.clear()
+
+
+__all__ = ["register_with_dynamo", "unregister_from_dynamo", "is_registered", "enable", "register_reduce_op", "TracedCommWork"]
