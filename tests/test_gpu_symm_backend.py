@@ -220,3 +220,52 @@ def test_symmetric_collectives_without_multicast():
     if _world_size() < 2:
         pytest.skip("needs 2 GPUs")
     run_ranks(_symm_battery, 2, timeout=300, extra_env={"B200COMMS_NVLS": "0", "NCCL_NVLS_ENABLE": "0"})
+
+
+def _ulysses_worker(rank, world):
+    """Fused sequence <-> heads exchange against the all-to-all with explicit permutes: values, the attention built
+    on it, gradients, reuse of the buffer ring, the route counter."""
+    import torchcomms_b200 as tc
+    from torchcomms_b200.parallel.context import SeqHeadsExchange, _heads_to_seq, _seq_to_heads, ulysses_attention
+
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    comm = tc.new_comm("b200", dev, name="uly", timeout=timedelta(seconds=60), abort_process_on_timeout_or_error=False)
+    impl = comm.get_backend_impl()
+    ex = SeqHeadsExchange(comm, slots=3)
+    assert ex.fused == (world > 1)
+    b, h, s, d = 2, 4 * world, 96, 64
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    for dtype in (torch.bfloat16, torch.float32):
+        x = torch.randn(b, h, s, d, device=dev, generator=g).to(dtype)
+        ref = _seq_to_heads(x, comm)
+        got = ex.to_heads(x)
+        assert got.shape == ref.shape and torch.equal(got, ref)
+        assert torch.equal(ex.to_seq(got), x) and torch.equal(_heads_to_seq(ref, comm), x)
+    if world > 1:
+        assert int(impl.comm_dump().get("count/seq_heads_exchange/symm", "0")) == 4
+    # the ring: a result stays valid for `slots` - 1 further exchanges of its shape, keep=True copies it out
+    first = ex.to_heads(x)
+    kept = ex.to_heads(x * 2, keep=True)
+    for i in range(3):
+        ex.to_heads(x * (3 + i))
+    assert torch.equal(kept, _seq_to_heads(x * 2, comm))
+    if world > 1:
+        assert not torch.equal(first, _seq_to_heads(x, comm))          # overwritten by the fourth call after it
+
+    # attention and its gradients
+    q, k, v = (torch.randn(b, h, s, d, device=dev, generator=g, dtype=torch.float32, requires_grad=True) for _ in range(3))
+    o_ref = ulysses_attention(q, k, v, comm, causal=True)
+    gr = torch.autograd.grad(o_ref.square().sum(), (q, k, v))
+    o = ulysses_attention(q, k, v, comm, causal=True, exchange=ex)
+    gf = torch.autograd.grad(o.square().sum(), (q, k, v))
+    assert torch.allclose(o, o_ref, atol=1e-5, rtol=1e-5)
+    for a, r in zip(gf, gr):
+        assert torch.allclose(a, r, atol=1e-4, rtol=1e-4)
+    torch.cuda.synchronize()
+    ex.close()
+    comm.finalize()
+
+
+def test_fused_sequence_heads_exchange_and_ulysses_attention():
+    run_ranks(_ulysses_worker, _world_size(), timeout=300)

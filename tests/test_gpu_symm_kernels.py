@@ -140,6 +140,37 @@ def test_symm_all_to_all_variable_splits(nranks, mode):
     assert w.status()[0] == 0
 
 
+def _to_heads_reference(xs, n):
+    """xs[r]: [b, h, s, d] on rank r -> per rank p [b, h/n, n*s, d]: heads p*h/n.., sequence blocks in rank order."""
+    hn = xs[0].shape[1] // n
+    return [torch.cat([xs[r][:, p * hn:(p + 1) * hn] for r in range(n)], dim=2) for p in range(n)]
+
+
+@pytest.mark.parametrize("nranks", [2, 4, 8])
+@pytest.mark.parametrize("dtype,shape,blocks", [
+    (torch.bfloat16, (2, 16, 24, 64), 8),     # 3 KB slabs
+    (torch.bfloat16, (1, 8, 80, 64), 5),      # 10 KB slabs walked slab by slab, block ranges that straddle slabs
+    (torch.float32, (1, 8, 5, 12), 3),        # 240-byte slabs, more vectors than a block's share
+    (torch.bfloat16, (3, 8, 7, 9), 4),        # 126-byte slabs: not a multiple of 16, byte path
+])
+def test_symm_seq_heads_exchange_both_directions(nranks, dtype, shape, blocks):
+    """Sequence shards -> head shards and back, layout changes inside the kernel, against cat / split."""
+    b, h, s, d = shape
+    w = _world(nranks)
+    xs = [torch.randn(b, h, s, d, device="cuda").to(dtype) for _ in range(nranks)]
+    heads = [torch.zeros(b, h // nranks, nranks * s, d, dtype=dtype, device="cuda") for _ in range(nranks)]
+    w.symm_seq_heads(xs, heads, True, blocks)
+    torch.cuda.synchronize()
+    for got, ref in zip(heads, _to_heads_reference(xs, nranks)):
+        assert torch.equal(got, ref)
+    back = [torch.zeros(b, h, s, d, dtype=dtype, device="cuda") for _ in range(nranks)]
+    w.symm_seq_heads(heads, back, False, blocks)
+    torch.cuda.synchronize()
+    for got, ref in zip(back, xs):
+        assert torch.equal(got, ref)
+    assert w.status()[0] == 0
+
+
 def test_symm_all_to_all_counts_beyond_capacity_are_clamped():
     """A sender's device count exceeds what the receiver's output can hold: nothing lands out of bounds,
     and the status word reports the bad argument."""

@@ -307,6 +307,24 @@ def _context_worker(rank, world):
     assert len({int((shard_positions(r, world, s // world) + 1).sum()) for r in range(world)}) == world
     parts = [zigzag_shard(q, r, world) for r in range(world)]
     assert torch.equal(zigzag_unshard(parts), q)
+    # Ulysses attention is differentiable: gradients of the sequence shards equal those of full attention
+    # (same q / k / v on every rank, so the full-sequence loss is the sum of the ranks' losses)
+    from torchcomms_b200.parallel.context import SeqHeadsExchange
+
+    fq, fk, fv = (t.clone().requires_grad_(True) for t in (q, k, v))
+    full = torch.nn.functional.scaled_dot_product_attention(fq, fk, fv, is_causal=True)
+    gq, gk, gv = torch.autograd.grad(full.square().sum(), (fq, fk, fv))
+    lq, lk, lv = (t[:, :, sl].clone().requires_grad_(True) for t in (q, k, v))
+    out = ulysses_attention(lq, lk, lv, comm, causal=True)
+    grads = torch.autograd.grad(out.square().sum(), (lq, lk, lv))
+    for got_g, ref_g in zip(grads, (gq, gk, gv)):
+        torch.testing.assert_close(got_g, ref_g[:, :, sl], rtol=1e-4, atol=1e-5)
+    # the exchange object falls back to the same all-to-all on backends without the fused kernel
+    ex = SeqHeadsExchange(comm)
+    assert not ex.fused
+    out2 = ulysses_attention(lq, lk, lv, comm, causal=True, exchange=ex)
+    torch.testing.assert_close(out2, out)
+    torch.testing.assert_close(ex.to_seq(ex.to_heads(lq.detach())), lq.detach())
     comm.finalize()
 
 

@@ -2033,6 +2033,44 @@ WorkPtr CudaBackend::reduce_scatter_quantized(at::Tensor& out, const at::Tensor&
   return reduce_scatter_single(out, in, op, async_op, oo);
 }
 
+WorkPtr CudaBackend::seq_heads_exchange(at::Tensor& out, const at::Tensor& in, bool to_heads, bool async_op,
+                                        const OpOptions& o) {
+  check_tensor(in, device_, "seq_heads_exchange", cuda_->is_real());
+  check_tensor(out, device_, "seq_heads_exchange", cuda_->is_real());
+  TORCH_CHECK(in.dim() == 4 && out.dim() == 4 && in.is_contiguous() && out.is_contiguous(),
+              "seq_heads_exchange: contiguous [batch, heads, seq, dim] tensors");
+  TORCH_CHECK(in.scalar_type() == out.scalar_type(), "seq_heads_exchange: dtype mismatch");
+  const at::Tensor& full = to_heads ? in : out;       // [b, h, s, d]
+  const at::Tensor& grouped = to_heads ? out : in;    // [b, h / n, n * s, d]
+  const int64_t b = full.size(0), h = full.size(1), s_local = full.size(2), d = full.size(3);
+  TORCH_CHECK(h % size_ == 0, "seq_heads_exchange: heads (", h, ") must divide by the number of ranks (", size_, ")");
+  TORCH_CHECK(grouped.size(0) == b && grouped.size(1) == h / size_ && grouped.size(2) == s_local * size_ && grouped.size(3) == d,
+              "seq_heads_exchange: expected [", b, ", ", h / size_, ", ", s_local * size_, ", ", d, "] on the head-sharded side");
+  if (in.numel() == 0) return c10::make_intrusive<CompletedWork>();
+  if (size_ == 1) {
+    at::Tensor dst = out, src = in;
+    return run("seq_heads_exchange/copy", async_op, o, {in, out}, [dst, src](cudaStream_t st) {
+      B200C_CUDA_CHECK(cudaMemcpyAsync(dst.data_ptr(), src.data_ptr(), src.nbytes(), cudaMemcpyDeviceToDevice, st));
+    });
+  }
+  SymmView sv;
+  TORCH_CHECK(lookup_symm(out.data_ptr(), out.nbytes(), &sv),
+              "seq_heads_exchange: the output must be a symmetric tensor (symm_empty or a registered allocation)");
+  const size_t slab = static_cast<size_t>(s_local) * d * in.element_size();
+  const size_t want = (in.nbytes() / 16 + 512 * 4 - 1) / (512 * 4);
+  const int blocks = static_cast<int>(std::max<size_t>(
+      1, std::min<size_t>(std::min(128, hint_or<int>(o.hints, "symm_blocks", tune_.symm_blocks_nomc)), want)));
+  bytes_issued_ += in.nbytes();
+  at::Tensor src = in;
+  return run("seq_heads_exchange/symm", async_op, o, {in, out},
+             [this, src, sv, b, h, slab, to_heads, blocks](cudaStream_t st) {
+               const void* ip = src.data_ptr();
+               B200C_CUDA_CHECK(launch_symm_seq_heads(&dev_, 0, &ip, &sv, static_cast<int>(b), static_cast<int>(h), slab,
+                                                      to_heads, blocks, st));
+             },
+             kChanSymAr, true, blocks);
+}
+
 WorkPtr CudaBackend::broadcast(at::Tensor& t, int root, bool async_op, const OpOptions& o) {
   check_tensor(t, device_, "broadcast", cuda_->is_real());
   if (t.numel() == 0 || size_ == 1) return c10::make_intrusive<CompletedWork>();

@@ -209,6 +209,10 @@ class CudaBackend final : public Backend {
   // fp32 in / fp32 out, bf16 on the wire; optional stochastic rounding seed.
   WorkPtr reduce_scatter_quantized(at::Tensor& out, const at::Tensor& in, const ReduceOp& op, int64_t seed,
                                    bool async_op, const OpOptions& o);
+  // Sequence <-> heads exchange of sequence-parallel attention with both layout changes folded in.
+  // to_heads: in [b, h, s, d] -> out [b, h / size, size * s, d]; otherwise the inverse. Both contiguous;
+  // `out` must be a symmetric tensor (symm_empty) of the same shape on every rank.
+  WorkPtr seq_heads_exchange(at::Tensor& out, const at::Tensor& in, bool to_heads, bool async_op, const OpOptions& o);
   std::unordered_map<std::string, std::string> comm_dump() const override;
   // The timestamp ring (hint / variable `colltrace` = number of entries): for each of the last N operations that
   // were issued outside a graph capture, its sequence number, route name, and the device's nanosecond timer when

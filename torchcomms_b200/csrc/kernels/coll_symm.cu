@@ -543,6 +543,128 @@ struct SymA2a {
   }
 };
 
+// ------------------------------------------- sequence <-> heads exchange ----
+//
+// The all-to-all of Ulysses-style sequence parallelism with its two layout
+// changes folded in. With n ranks, h heads and s sequence positions per rank:
+//   to_heads:  in [b, h, s, d] (all heads, local positions)  ->
+//              out [b, h/n, n*s, d] (own heads, all positions, in rank order)
+//   to_seq:    the inverse.
+// A plain all-to-all needs a permuted copy of the input before it and one of
+// the output after it; here every [s, d] slab (contiguous on both sides) goes
+// from the caller's tensor straight to its place in the peer's tensor, so the
+// data is read once and written once, over NVLink.
+// Parity: the scatter-gather collective of comms/ncclx/v2_31/contrib/pace
+// (csrc/collective/sg: all-to-all with the tensor layouts of sequence
+// parallel attention fused in).
+struct SymSeqHeads {
+  struct Args {
+    const char* in;
+    SymmView out;            // symmetric
+    int batch, heads;        // heads = h, all of them
+    size_t slab_bytes;       // s * d * element size
+    int to_heads;
+  };
+  // Slab `L` of this rank's traffic, peers taken in ring order from the next rank on.
+  static __device__ __forceinline__ void locate(const CommDev& c, const Args& a, size_t L, int* peer, size_t* src_slab,
+                                                size_t* dst_slab) {
+    const int n = c.nranks, hn = a.heads / n;
+    const size_t per_peer = static_cast<size_t>(a.batch) * hn;
+    const int i = static_cast<int>(L / per_peer);
+    const size_t rem = L - static_cast<size_t>(i) * per_peer;
+    const size_t bb = rem / hn, j = rem - bb * hn;
+    int p = c.rank + 1 + i;
+    if (p >= n) p -= n;
+    *peer = p;
+    const size_t grouped_mine = (bb * hn + j) * n;            // [b, h/n, n, ...] index of slab (bb, j, 0)
+    if (a.to_heads) {
+      *src_slab = bb * a.heads + static_cast<size_t>(p) * hn + j;
+      *dst_slab = grouped_mine + c.rank;
+    } else {
+      *src_slab = grouped_mine + p;
+      *dst_slab = bb * a.heads + static_cast<size_t>(c.rank) * hn + j;
+    }
+  }
+  static __device__ void run(const CommDev& c, const Args& a) {
+    BlockEpoch ep;
+    ep.load(c, kFlagSetSymA2a);
+    trace_mark(c, 0);
+    bool ok = block_barrier(c, kFlagSetSymA2a, ep, 0x4a);
+    trace_mark(c, 1);
+    if (ok) {
+      const size_t slabs = static_cast<size_t>(a.batch) * a.heads;
+      bool aligned = (reinterpret_cast<uintptr_t>(a.in) & 15u) == 0 && a.slab_bytes % 16 == 0;
+      for (int r = 0; r < c.nranks; ++r) aligned = aligned && (reinterpret_cast<uintptr_t>(a.out.ptr[r]) & 15u) == 0;
+      if (aligned) {
+        const size_t vps = a.slab_bytes / 16;
+        size_t v0, v1;
+        block_range(slabs * vps, blockIdx.x, gridDim.x, &v0, &v1);
+        constexpr int U = kSymmUnroll;
+        if (vps >= static_cast<size_t>(blockDim.x) && v1 > v0) {
+          // Large slabs: the block walks its range slab by slab, so the index arithmetic is done once per slab.
+          for (size_t L = v0 / vps; L * vps < v1; ++L) {
+            int p;
+            size_t ss, ds;
+            locate(c, a, L, &p, &ss, &ds);
+            const size_t w0 = (v0 > L * vps ? v0 - L * vps : 0), w1 = min_sz(vps, v1 - L * vps);
+            const char* src = a.in + ss * a.slab_bytes;
+            char* dst = a.out.ptr[p] + ds * a.slab_bytes;
+            for (size_t w = w0 + threadIdx.x; w < w1; w += static_cast<size_t>(U) * blockDim.x) {
+              uint4 r[U];
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                const size_t ww = w + static_cast<size_t>(u) * blockDim.x;
+                if (ww < w1) r[u] = ld16_stream(src + ww * 16);
+              }
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                const size_t ww = w + static_cast<size_t>(u) * blockDim.x;
+                if (ww < w1) st16(dst + ww * 16, r[u]);
+              }
+            }
+          }
+        } else {
+          for (size_t v = v0 + threadIdx.x; v < v1; v += static_cast<size_t>(U) * blockDim.x) {
+            uint4 r[U];
+            char* dst[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const size_t vv = v + static_cast<size_t>(u) * blockDim.x;
+              if (vv < v1) {
+                const size_t L = vv / vps, w = vv - L * vps;
+                int p;
+                size_t ss, ds;
+                locate(c, a, L, &p, &ss, &ds);
+                r[u] = ld16_stream(a.in + ss * a.slab_bytes + w * 16);
+                dst[u] = a.out.ptr[p] + ds * a.slab_bytes + w * 16;
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const size_t vv = v + static_cast<size_t>(u) * blockDim.x;
+              if (vv < v1) st16(dst[u], r[u]);
+            }
+          }
+        }
+      } else {
+        size_t b0, b1;
+        block_range(slabs * a.slab_bytes, blockIdx.x, gridDim.x, &b0, &b1);
+        for (size_t i = b0 + threadIdx.x; i < b1; i += blockDim.x) {
+          const size_t L = i / a.slab_bytes, w = i - L * a.slab_bytes;
+          int p;
+          size_t ss, ds;
+          locate(c, a, L, &p, &ss, &ds);
+          a.out.ptr[p][ds * a.slab_bytes + w] = a.in[ss * a.slab_bytes + w];
+        }
+      }
+      trace_mark(c, 2);
+      ok = block_barrier(c, kFlagSetSymA2a, ep, 0x4b);
+      trace_mark(c, 3);
+    }
+    ep.store(c, kFlagSetSymA2a);
+  }
+};
+
 } // namespace coll
 
 // ------------------------------------------------------------- launchers ----
@@ -650,6 +772,24 @@ cudaError_t launch_symm_all_to_all(const CommDev* comms, const HeapLayout& lay, 
   // Whole block groups per peer.
   if (blocks >= nranks) blocks = blocks / nranks * nranks;
   return launch_symm<Op>(comms, emu_ranks, args.data(), blocks, stream);
+}
+
+cudaError_t launch_symm_seq_heads(const CommDev* comms, int emu_ranks, const void* const* in, const SymmView* out,
+                                  int batch, int heads, size_t slab_bytes, bool to_heads, int blocks,
+                                  cudaStream_t stream) {
+  const int n = emu_ranks > 0 ? emu_ranks : 1;
+  const int nranks = comms[0].nranks;
+  if (batch < 1 || heads < nranks || heads % nranks != 0 || slab_bytes == 0) return cudaErrorInvalidValue;
+  std::vector<coll::SymSeqHeads::Args> args(n);
+  for (int r = 0; r < n; ++r) {
+    args[r].in = static_cast<const char*>(in[r]);
+    args[r].out = out[r];
+    args[r].batch = batch;
+    args[r].heads = heads;
+    args[r].slab_bytes = slab_bytes;
+    args[r].to_heads = to_heads ? 1 : 0;
+  }
+  return coll::launch_symm<coll::SymSeqHeads>(comms, emu_ranks, args.data(), blocks, stream);
 }
 
 } // namespace b200c

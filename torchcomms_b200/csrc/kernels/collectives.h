@@ -131,6 +131,13 @@ cudaError_t launch_symm_all_to_all(const CommDev* comms, const HeapLayout& lay, 
                                    const long long* const* dev_send_counts, size_t elem_bytes, bool exchange,
                                    int blocks, cudaStream_t stream);
 
+// Sequence <-> heads exchange of sequence-parallel attention, layout changes included. `out` symmetric.
+// to_heads: in [batch, heads, s, d] -> out [batch, heads / nranks, nranks * s, d]; otherwise the inverse.
+// `slab_bytes` = s * d * element size (one [s, d] slab, contiguous on both sides).
+cudaError_t launch_symm_seq_heads(const CommDev* comms, int emu_ranks, const void* const* in, const SymmView* out,
+                                  int batch, int heads, size_t slab_bytes, bool to_heads, int blocks,
+                                  cudaStream_t stream);
+
 // ---- flag-less small all-reduce (coll_lamport.cu) -----------------------------
 constexpr int kLamportBlocks = 256;         // pieces per call
 constexpr size_t kLamportPiece = 4 * 1024;  // payload bytes per piece and rank (one 16-byte vector per thread)

@@ -292,6 +292,19 @@ class EmuWorld {
                                             so.data(), sl.data(), ro.data(), rl.data(), mode == 2 ? cp.data() : nullptr,
                                             elem_bytes, mode != 0, blocks, stream()));
   }
+  // ins[r]: [b, h, s, d] (to_heads) or [b, h/n, n*s, d]; outs[r]: the other layout.
+  void symm_seq_heads(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, bool to_heads, int blocks) {
+    check(ins);
+    check(outs);
+    const at::Tensor& full = to_heads ? ins[0] : outs[0];   // [b, h, s, d]
+    TORCH_CHECK(full.dim() == 4, "symm_seq_heads: [batch, heads, seq, dim] tensors");
+    std::vector<const void*> ip(n_);
+    for (int r = 0; r < n_; ++r) ip[r] = ins[r].data_ptr();
+    auto v = views(outs);
+    const size_t slab = static_cast<size_t>(full.size(2)) * full.size(3) * full.element_size();
+    B200C_CUDA_CHECK(launch_symm_seq_heads(comms_.data(), n_, ip.data(), v.data(), static_cast<int>(full.size(0)),
+                                           static_cast<int>(full.size(1)), slab, to_heads, blocks, stream()));
+  }
   void all_reduce_lamport(std::vector<at::Tensor> ins, std::vector<at::Tensor> outs, double scale) {
     check(ins);
     check(outs);
@@ -519,6 +532,11 @@ void bind_cuda_backend(py::module_& m) {
         return b.reduce_scatter_quantized(out, in, op, seed, a, make_op_options(h, to));
       }, py::arg("output"), py::arg("input"), py::arg("op"), py::arg("seed") = 0, py::arg("async_op") = false,
          py::arg("hints") = py::none(), py::arg("timeout") = py::none(), py::call_guard<py::gil_scoped_release>())
+      .def("seq_heads_exchange", [](CudaBackend& b, at::Tensor out, const at::Tensor& in, bool to_heads, bool a, OptHints h,
+                                    OptMillis to) {
+        return b.seq_heads_exchange(out, in, to_heads, a, make_op_options(h, to));
+      }, py::arg("output"), py::arg("input"), py::arg("to_heads"), py::arg("async_op") = false,
+         py::arg("hints") = py::none(), py::arg("timeout") = py::none(), py::call_guard<py::gil_scoped_release>())
       .def("symm_empty", [](CudaBackend& b, std::vector<int64_t> sizes, py::object dtype) {
         const at::ScalarType st = torch::python::detail::py_object_to_dtype(dtype);
         py::gil_scoped_release nogil;
@@ -574,6 +592,7 @@ void bind_cuda_backend(py::module_& m) {
       .def("symm_reduce_scatter", &EmuWorld::symm_reduce_scatter)
       .def("symm_all_reduce", &EmuWorld::symm_all_reduce)
       .def("symm_all_to_all", &EmuWorld::symm_all_to_all)
+      .def("symm_seq_heads", &EmuWorld::symm_seq_heads)
       .def("all_reduce_lamport", &EmuWorld::all_reduce_lamport)
       .def("exchange_lamport", &EmuWorld::exchange_lamport)
       .def("exchangev_lamport", &EmuWorld::exchangev_lamport)

@@ -12,7 +12,9 @@ Both shard the sequence over the ranks of a communicator.
   load-balanced over the ranks.
 * ``ulysses_attention``: one all-to-all turns sequence shards into head
   shards, attention runs locally over the full sequence for ``heads / n``
-  heads, a second all-to-all turns the result back.
+  heads, a second all-to-all turns the result back.  ``SeqHeadsExchange``
+  runs those all-to-alls as one-pass kernels that also do the layout
+  changes (CUDA backend, symmetric outputs).
 
 The reference contains neither (its tree has no ring-attention / Ulysses /
 context-parallel code); it provides the primitives they need - ``send`` /
@@ -124,13 +126,23 @@ def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, comm: Torc
     return out.to(q.dtype)
 
 
+def _all_to_all(send: torch.Tensor, comm: TorchComm) -> torch.Tensor:
+    """Equal-split all-to-all along dim 0; through the differentiable operator when a gradient is wanted."""
+    if send.requires_grad and torch.is_grad_enabled():
+        from .. import functional as F
+
+        return F.all_to_all_single(send, comm)
+    recv = torch.empty_like(send)
+    comm.all_to_all_single(recv, send, False)
+    return recv
+
+
 def _seq_to_heads(x: torch.Tensor, comm: TorchComm) -> torch.Tensor:
     """[b, h, s_local, d] -> [b, h/n, s_local*n, d]."""
     n = comm.get_size()
     b, h, s, d = x.shape
     send = x.reshape(b, n, h // n, s, d).permute(1, 0, 2, 3, 4).contiguous()   # [n(dest), b, h/n, s, d]
-    recv = torch.empty_like(send)
-    comm.all_to_all_single(recv, send, False)                                    # [n(src), b, h/n, s, d]
+    recv = _all_to_all(send, comm)                                               # [n(src), b, h/n, s, d]
     return recv.permute(1, 2, 0, 3, 4).reshape(b, h // n, n * s, d)
 
 
@@ -140,17 +152,104 @@ def _heads_to_seq(x: torch.Tensor, comm: TorchComm) -> torch.Tensor:
     b, hn, sn, d = x.shape
     s = sn // n
     send = x.reshape(b, hn, n, s, d).permute(2, 0, 1, 3, 4).contiguous()        # [n(dest seq block), b, h/n, s, d]
-    recv = torch.empty_like(send)
-    comm.all_to_all_single(recv, send, False)                                    # [n(src head group), b, h/n, s, d]
+    recv = _all_to_all(send, comm)                                               # [n(src head group), b, h/n, s, d]
     return recv.permute(1, 0, 2, 3, 4).reshape(b, n * hn, s, d)
 
 
+class SeqHeadsExchange:
+    """The two all-to-alls of Ulysses attention with their layout changes done inside the kernel (CUDA backend).
+
+    ``to_heads``: ``[b, h, s_local, d]`` -> ``[b, h/n, n*s_local, d]``; ``to_seq``: the inverse.  Every ``[s_local, d]``
+    slab goes from the caller's tensor straight to its place in the peer's output over NVLink, so the permuted
+    copies that surround a plain ``all_to_all_single`` (one before, one after) disappear.  Outputs live in
+    symmetric buffers that this object owns: one ring of ``slots`` buffers per (shape, dtype), allocated on first
+    use (a collective call: every rank must use the object with the same sequence of shapes).  A result is valid
+    until ``slots`` more exchanges of the same shape have been issued; when autograd records the call, or with
+    ``keep=True``, the result is copied out of the ring.  Differentiable: the gradient of one direction is the
+    other direction applied to the incoming gradient.
+
+    On other backends, or with one rank, the calls fall back to ``all_to_all_single`` with explicit permutes.
+    Counterpart in the reference tree: the scatter-gather collective of comms/ncclx/v2_31/contrib/pace
+    (pace/sg/sgcomm.py), which fuses the same layout changes into its all-to-all.
+    """
+
+    def __init__(self, comm: TorchComm, slots: int = 4):
+        self.comm = comm
+        self.n = comm.get_size()
+        self.slots = max(1, slots)
+        impl = comm.get_backend_impl() if hasattr(comm, "get_backend_impl") else None
+        self._impl = impl if impl is not None and hasattr(impl, "seq_heads_exchange") and self.n > 1 else None
+        self._rings = {}
+
+    @property
+    def fused(self) -> bool:
+        return self._impl is not None
+
+    def _next(self, shape, dtype) -> torch.Tensor:
+        key = (tuple(shape), dtype)
+        ring = self._rings.get(key)
+        if ring is None:
+            ring = self._rings[key] = [[self._impl.symm_empty(list(shape), dtype) for _ in range(self.slots)], 0]
+        buf = ring[0][ring[1] % self.slots]
+        ring[1] += 1
+        return buf
+
+    def _run(self, x: torch.Tensor, to_heads: bool, keep: bool) -> torch.Tensor:
+        b = x.shape[0]
+        if to_heads:
+            _, h, s, d = x.shape
+            shape = (b, h // self.n, s * self.n, d)
+        else:
+            _, hn, sn, d = x.shape
+            shape = (b, hn * self.n, sn // self.n, d)
+        out = self._next(shape, x.dtype)
+        self._impl.seq_heads_exchange(out, x.contiguous(), to_heads, False)
+        return out.clone() if keep else out
+
+    def to_heads(self, x: torch.Tensor, keep: bool = False) -> torch.Tensor:
+        if x.shape[1] % self.n != 0:
+            raise ValueError(f"heads ({x.shape[1]}) must divide by the number of ranks ({self.n})")
+        if self._impl is None:
+            return _seq_to_heads(x, self.comm) if self.n > 1 else x
+        return _SeqHeadsFn.apply(x, self, True, keep)
+
+    def to_seq(self, x: torch.Tensor, keep: bool = False) -> torch.Tensor:
+        if x.shape[2] % self.n != 0:
+            raise ValueError(f"sequence length ({x.shape[2]}) must divide by the number of ranks ({self.n})")
+        if self._impl is None:
+            return _heads_to_seq(x, self.comm) if self.n > 1 else x
+        return _SeqHeadsFn.apply(x, self, False, keep)
+
+    def close(self) -> None:
+        """Gives the symmetric buffers back (collective)."""
+        for ring in self._rings.values():
+            for buf in ring[0]:
+                self._impl.symm_free(buf)
+        self._rings = {}
+
+
+class _SeqHeadsFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, exchange, to_heads, keep):
+        ctx.exchange, ctx.to_heads = exchange, to_heads
+        return exchange._run(x, to_heads, keep or x.requires_grad)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return ctx.exchange._run(grad, not ctx.to_heads, True), None, None, None
+
+
 def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, comm: TorchComm, causal: bool = False,
-                      scale: Optional[float] = None) -> torch.Tensor:
-    """Same layout as ``ring_attention``; ``heads`` must divide by the communicator size."""
+                      scale: Optional[float] = None, exchange: Optional[SeqHeadsExchange] = None) -> torch.Tensor:
+    """Same layout as ``ring_attention``; ``heads`` must divide by the communicator size.  With ``exchange``
+    (a ``SeqHeadsExchange`` of the same communicator) the four all-to-alls run as fused layout-changing kernels."""
     n = comm.get_size()
     if q.shape[1] % n != 0:
         raise ValueError(f"heads ({q.shape[1]}) must divide by the number of ranks ({n})")
+    if exchange is not None:
+        qh, kh, vh = (exchange.to_heads(t) for t in (q, k, v))
+        o = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=causal, scale=scale)
+        return exchange.to_seq(o)
     qh, kh, vh = (_seq_to_heads(t, comm) for t in (q, k, v))
     o = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=causal, scale=scale)
     return _heads_to_seq(o, comm)
