@@ -286,6 +286,33 @@ def test_timestamp_ring_single_gpu():
     comm.finalize()
 
 
+def test_seq_heads_exchange_single_rank_is_a_copy():
+    """With one rank both layouts coincide: the backend call copies, checks shapes and dtypes, and the exchange
+    object of the context-parallel layer passes tensors through."""
+    import torchcomms_b200 as tc
+    from torchcomms_b200.parallel.context import SeqHeadsExchange
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29643")
+    os.environ["RANK"], os.environ["WORLD_SIZE"] = "0", "1"
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    comm = tc.new_comm("b200", dev, name="sh1", abort_process_on_timeout_or_error=False)
+    impl = comm.get_backend_impl()
+    x = torch.randn(2, 4, 16, 8, device=dev, dtype=torch.bfloat16)
+    out = torch.zeros_like(x)
+    impl.seq_heads_exchange(out, x, True, False)
+    torch.cuda.synchronize()
+    assert torch.equal(out, x)
+    with pytest.raises(RuntimeError):
+        impl.seq_heads_exchange(torch.zeros(2, 4, 8, 8, device=dev, dtype=torch.bfloat16), x, True, False)   # wrong shape
+    with pytest.raises(RuntimeError):
+        impl.seq_heads_exchange(out.float(), x, True, False)                                                  # dtype mismatch
+    ex = SeqHeadsExchange(comm)
+    assert not ex.fused and ex.to_heads(x) is x and ex.to_seq(x) is x
+    comm.finalize()
+
+
 def _stalled_peer(rank, world):
     """Rank 1 never joins an all-reduce: rank 0's kernel gives up after its
     device-side wait budget and the next call raises; no GPU hangs or faults."""

@@ -565,13 +565,13 @@ struct SymSeqHeads {
     size_t slab_bytes;       // s * d * element size
     int to_heads;
   };
-  // Slab `L` of this rank's traffic, peers taken in ring order from the next rank on.
+  // Slab `L` of this rank's traffic. Consecutive slabs go to consecutive peers (ring order from the next rank
+  // on), so every block's share of the work is spread over all links and the local copy alike.
   static __device__ __forceinline__ void locate(const CommDev& c, const Args& a, size_t L, int* peer, size_t* src_slab,
                                                 size_t* dst_slab) {
     const int n = c.nranks, hn = a.heads / n;
-    const size_t per_peer = static_cast<size_t>(a.batch) * hn;
-    const int i = static_cast<int>(L / per_peer);
-    const size_t rem = L - static_cast<size_t>(i) * per_peer;
+    const size_t rem = L / n;
+    const int i = static_cast<int>(L - rem * n);
     const size_t bb = rem / hn, j = rem - bb * hn;
     int p = c.rank + 1 + i;
     if (p >= n) p -= n;
