@@ -98,6 +98,25 @@ def _dynamo_worker(rank, world):
     assert torch.equal(a, torch.cat([torch.arange(2.0) + 2 * rank + 100 * src for src in range(world)]))
     assert torch.equal(got, torch.full((4,), float(prv + 1)))
 
+    # rooted and variable-size forms
+    def rooted(x):
+        g = torch.zeros(comm.get_size() * 4)
+        comm.gather_single(g, x, 1, False)
+        parts = [torch.zeros(4) for _ in range(comm.get_size())]
+        comm.gather(parts, x * 2, 0, False)
+        sc = torch.empty(4)
+        comm.scatter(sc, [x + 10 * r for r in range(comm.get_size())] if comm.get_rank() == 0 else [], 0, False)
+        vs = [torch.empty(r + 1, 2) for r in range(comm.get_size())]
+        comm.all_gather_v(vs, torch.full((comm.get_rank() + 1, 2), float(comm.get_rank())), False)
+        return g, torch.stack(parts), sc, vs[-1]
+
+    g, parts, sc, last = torch.compile(rooted, fullgraph=True, backend="aot_eager")(x)
+    every = torch.arange(1, world + 1, dtype=torch.float32).repeat_interleave(4)
+    assert torch.equal(g, every if rank == 1 else torch.zeros(world * 4))          # only the root's output is written
+    assert torch.equal(parts.flatten(), 2 * every if rank == 0 else torch.zeros(world * 4))
+    assert torch.equal(sc, torch.full((4,), 1.0 + 10 * rank))                         # rank 0's x is all ones
+    assert last.shape == (world, 2) and float(last[0, 0]) == world - 1
+
     # a split communicator is enabled as it is made
     sub = comm.split(list(range(world)), "dyn_sub")
 
@@ -161,7 +180,8 @@ def test_inductor_lowerings_are_registered():
         assert op in lowerings, op
     import torch.fx.node as fx_node
 
-    assert torch.ops.torchcomms_b200.barrier.default in fx_node._side_effectful_functions
+    for name in ("barrier", "gather_single", "all_reduce", "send"):
+        assert getattr(torch.ops.torchcomms_b200, name).default in fx_node._side_effectful_functions
 
 
 @pytest.mark.gpu

@@ -480,6 +480,11 @@ from .ext import (  # noqa: E402
     window_put, window_read, window_signal, window_token, window_wait_signal,
 )
 from .param_parsing import normalize_reduce_op, parse_hints, parse_timeout  # noqa: E402
+from .inductor import mark_side_effects as _mark_side_effects  # noqa: E402
+
+# A collective whose result is unused on one rank (a gather off the root, a barrier) must not be eliminated from
+# that rank's traced graph: the peers make the matching call and would wait for it.
+_mark_side_effects()
 
 __all__ = [
     "AsyncCollectiveTensor", "OnceWork", "TracedWork", "wrap_async", "CompiledComm", "compiled",

@@ -225,6 +225,45 @@ def _m_all_to_all(self, output_tensor_list, input_tensor_list, async_op, hints=N
     return _ORIG["all_to_all"](self, output_tensor_list, input_tensor_list, async_op, hints, timeout)
 
 
+def _m_all_gather_v(self, tensor_list, tensor, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        sizes = [t.shape[0] for t in tensor_list]
+        return _finish(tensor_list, _ops.all_gather_v(tensor, sizes, _traceable(self).name), async_op, False)
+    return _ORIG["all_gather_v"](self, tensor_list, tensor, async_op, hints, timeout)
+
+
+def _m_gather_single(self, output, input, root, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        t = _traceable(self)
+        gathered = _ops.gather_single(input.reshape(1, -1), root, t.name)
+        if t.rank == root:                       # elsewhere the output is left alone, as in the eager call
+            output.copy_(gathered.view(output.shape))
+        return TracedCommWork()
+    return _ORIG["gather_single"](self, output, input, root, async_op, hints, timeout)
+
+
+def _m_gather(self, output_tensor_list, input_tensor, root, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        t = _traceable(self)
+        gathered = _ops.gather_single(input_tensor.reshape(1, -1), root, t.name)
+        if t.rank == root:
+            for r, dst in enumerate(output_tensor_list):
+                dst.copy_(gathered[r].view(dst.shape))
+        return TracedCommWork()
+    return _ORIG["gather"](self, output_tensor_list, input_tensor, root, async_op, hints, timeout)
+
+
+def _m_scatter(self, output_tensor, input_tensor_list, root, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        t = _traceable(self)
+        if t.rank == root:
+            stacked = torch.cat([x.reshape(1, -1) for x in input_tensor_list], dim=0)
+        else:                                    # only the shape matters off the root
+            stacked = output_tensor.new_empty((t.size, output_tensor.numel()))
+        return _finish([output_tensor], [_ops.scatter(stacked, root, t.name)], async_op, False)
+    return _ORIG["scatter"](self, output_tensor, input_tensor_list, root, async_op, hints, timeout)
+
+
 def _m_send(self, tensor, dst, async_op, hints=None, timeout=None):
     if torch.compiler.is_compiling():
         _ops.send(tensor, dst, _traceable(self).name)
@@ -263,6 +302,7 @@ _METHODS = {
     "all_gather_single": _m_all_gather_single, "reduce_scatter_single": _m_reduce_scatter_single,
     "all_to_all_single": _m_all_to_all_single, "all_to_all_v_single": _m_all_to_all_v_single,
     "all_gather": _m_all_gather, "reduce_scatter": _m_reduce_scatter, "all_to_all": _m_all_to_all,
+    "all_gather_v": _m_all_gather_v, "gather_single": _m_gather_single, "gather": _m_gather, "scatter": _m_scatter,
     "send": _m_send, "recv": _m_recv, "barrier": _m_barrier, "finalize": _m_finalize, "split": _m_split,
 }
 

@@ -15,8 +15,10 @@ collectives:
   wait kernel that acts in place on the started result, so that the scheduler
   keeps the input of the collective alive and untouched until the wait, and
   no copy is made at the wait.
-* operators whose results may go unused but whose calls must stay (barrier,
-  send, window signals) are marked as having side effects.
+* every operator that other ranks take part in is marked as having side
+  effects, so that dead-code elimination cannot drop a call whose result is
+  unused on one rank (a gather off the root, a barrier, a send) while the
+  peers still make theirs.
 
 Everything else (all-gather, reduce-scatter, all-to-all, list forms, windows)
 stays with Inductor's default handling of custom operators.
@@ -65,12 +67,20 @@ def _fake_broadcast_inplace(input, root, comm):
     return None
 
 
-_SIDE_EFFECTS = ("barrier", "send", "window_put", "window_signal", "window_wait_signal", "batch_send_recv")
+# Every operator that talks to other ranks has to stay in the graph even where its result goes unused on this rank
+# (a gather off the root, a barrier, a send): the peers make the matching call and would wait for this one.
+_SIDE_EFFECTS = (
+    "all_reduce", "all_reduce_", "all_gather_single", "reduce_scatter_single", "all_to_all_single", "broadcast",
+    "broadcast_", "reduce", "barrier", "send", "recv", "gather_single", "scatter", "all_gather", "all_gather_v",
+    "reduce_scatter", "all_to_all", "all_reduce_start", "all_gather_single_start", "reduce_scatter_single_start",
+    "all_to_all_single_start", "all_reduce_inplace", "broadcast_inplace", "window_put", "window_signal",
+    "window_wait_signal", "batch_send_recv",
+)
 _STARTS = ("all_reduce_start", "all_gather_single_start", "reduce_scatter_single_start", "all_to_all_single_start")
 
 
 def mark_side_effects() -> None:
-    """Keeps calls whose result nobody reads (barrier, send, window signals) in traced graphs."""
+    """Keeps every call that other ranks take part in in traced graphs, whether or not its result is read here."""
     for name in _SIDE_EFFECTS:
         packet = getattr(_ops, name, None)
         if packet is not None:
