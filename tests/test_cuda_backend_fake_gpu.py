@@ -406,3 +406,54 @@ def test_tuner_file_routes_by_operation_and_size(tmp_path):
     path = tmp_path / "tuner.txt"
     path.write_text("\n".join(lines) + "\n")
     run_ranks(_tuner_file_body, 2, args=(str(path),), timeout=120)
+
+
+def _suspend_resume_body(rank, world):
+    """suspend() gives back every cross-process resource (NCCL communicator destroyed, streams gone, operations
+    refused), resume() builds them again among the same members; twice in a row; finalize of a suspended communicator."""
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import _comms
+
+    fake = _comms._install_fake_gpu()
+    comm = tc.new_comm("b200", torch.device("cuda", rank), name="ckpt", abort_process_on_timeout_or_error=False,
+                       hints={"staging_mb": "1"})
+    impl = comm.get_backend_impl()
+    t = torch.ones(1024)
+    for cycle in range(2):
+        comm.all_reduce(t, tc.ReduceOp.SUM, False)
+        sym = comm.symm_empty((4096,), torch.float32)
+        assert impl.is_symmetric(sym) and not impl.is_suspended()
+        destroyed_before = sum(1 for l in fake.nccl_log() if l.startswith("ncclCommDestroy"))
+        impl.suspend()
+        assert impl.is_suspended()
+        assert sum(1 for l in fake.nccl_log() if l.startswith("ncclCommDestroy")) == destroyed_before + 1
+        with pytest.raises(RuntimeError, match="not initialised"):
+            comm.all_reduce(t, tc.ReduceOp.SUM, False)
+        with pytest.raises(RuntimeError, match="not initialised"):
+            impl.suspend()
+        inits_before = sum(1 for l in fake.nccl_log() if l.startswith("ncclCommInitRankConfig"))
+        impl.resume()
+        assert not impl.is_suspended() and comm.get_rank() == rank and comm.get_size() == world
+        assert sum(1 for l in fake.nccl_log() if l.startswith("ncclCommInitRankConfig")) == inits_before + 1
+        assert not impl.is_symmetric(sym)            # registrations went with the old mappings
+        d = impl.comm_dump()
+        assert d["size"] == str(world) and d["nccl"] == "1"
+        with pytest.raises(RuntimeError, match="not suspended"):
+            impl.resume()
+    # the helpers act on the communicators that hold cross-process GPU state and skip the others
+    from torchcomms_b200.checkpoint import checkpoint_prepare, checkpoint_restore
+
+    other = tc.new_comm("fake", torch.device("cpu"), name="ckpt_cpu")
+    assert checkpoint_prepare([other, comm]) == [comm] and impl.is_suspended()
+    assert checkpoint_prepare([comm]) == []          # already suspended
+    assert checkpoint_restore([comm, other]) == [comm] and not impl.is_suspended()
+    other.finalize()
+    comm.all_reduce(t, tc.ReduceOp.SUM, False)
+    impl.suspend()
+    comm.finalize()                                  # nothing is held: no barrier, no error
+    with pytest.raises(RuntimeError, match="finalized"):
+        impl.resume()
+
+
+def test_suspend_and_resume_for_checkpoints():
+    run_ranks(_suspend_resume_body, 4, timeout=180)

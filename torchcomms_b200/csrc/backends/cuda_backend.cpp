@@ -963,11 +963,33 @@ void CudaBackend::drop_released_graphs() {
   }
 }
 
+void CudaBackend::suspend() {
+  TORCH_CHECK(!finalized_, "communicator '", name_, "' was finalized");
+  TORCH_CHECK(initialized_, "suspend: communicator '", name_, "' is not initialised");
+  DeviceScope guard(cuda_, device_.index());
+  resume_store_ = store_;
+  drain_and_release(failed_.load() || aborted_.load(), "suspend");
+  suspended_ = true;
+}
+
+void CudaBackend::resume() {
+  TORCH_CHECK(!finalized_, "communicator '", name_, "' was finalized");
+  TORCH_CHECK(suspended_, "resume: communicator '", name_, "' is not suspended");
+  DeviceScope guard(cuda_, device_.index());
+  ++suspend_gen_;
+  failed_.store(false);
+  aborted_.store(false);
+  failure_text_.clear();
+  bootstrap(scoped_store(resume_store_, "resume/" + std::to_string(suspend_gen_)), rank_, size_);
+  suspended_ = false;
+  resume_store_.reset();
+}
+
 void CudaBackend::finalize() {
   TORCH_CHECK(!finalized_, "communicator '", name_, "' was already finalized");
-  TORCH_CHECK(initialized_ || opts_.enable_reconfigure, "communicator '", name_, "' is not initialised");
+  TORCH_CHECK(initialized_ || suspended_ || opts_.enable_reconfigure, "communicator '", name_, "' is not initialised");
   if (!initialized_) {
-    finalized_ = true;  // a reconfigurable communicator that never got a membership
+    finalized_ = true;  // suspended, or a reconfigurable communicator that never got a membership: nothing is held
     return;
   }
   DeviceScope guard(cuda_, device_.index());

@@ -209,6 +209,15 @@ class CudaBackend final : public Backend {
   // fp32 in / fp32 out, bf16 on the wire; optional stochastic rounding seed.
   WorkPtr reduce_scatter_quantized(at::Tensor& out, const at::Tensor& in, const ReduceOp& op, int64_t seed,
                                    bool async_op, const OpOptions& o);
+  // Checkpoint support. suspend(): collective; waits for this rank's work, meets the other members and gives back
+  // everything the bootstrap created (peer mappings, multicast bindings, the NCCL communicator, streams, events,
+  // the watchdog), so that the process holds no cross-process GPU state and can be checkpointed (CUDA checkpoint,
+  // CRIU) or moved. Rank, size, name, options and hooks are kept. resume(): collective; bootstraps again among the
+  // same members under a fresh store prefix. Objects that hold symmetric memory of the communicator (symm_empty
+  // tensors, windows, fused layers) must be recreated after resume(), as after reconfigure().
+  void suspend();
+  void resume();
+  bool is_suspended() const { return suspended_; }
   // Sequence <-> heads exchange of sequence-parallel attention with both layout changes folded in.
   // to_heads: in [b, h, s, d] -> out [b, h / size, size * s, d]; otherwise the inverse. Both contiguous;
   // `out` must be a symmetric tensor (symm_empty) of the same shape on every rank.
@@ -414,6 +423,9 @@ class CudaBackend final : public Backend {
   std::string failure_text_;
   bool finalized_ = false;
   bool initialized_ = false;
+  bool suspended_ = false;
+  int suspend_gen_ = 0;
+  c10::intrusive_ptr<c10d::Store> resume_store_;   // the store of the bootstrap that suspend() took down
   uint64_t split_counter_ = 0;
   std::atomic<uint64_t> ops_issued_{0}, bytes_issued_{0};
   std::unordered_map<std::string, uint64_t> algo_counts_;

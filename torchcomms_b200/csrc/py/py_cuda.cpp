@@ -532,6 +532,9 @@ void bind_cuda_backend(py::module_& m) {
         return b.reduce_scatter_quantized(out, in, op, seed, a, make_op_options(h, to));
       }, py::arg("output"), py::arg("input"), py::arg("op"), py::arg("seed") = 0, py::arg("async_op") = false,
          py::arg("hints") = py::none(), py::arg("timeout") = py::none(), py::call_guard<py::gil_scoped_release>())
+      .def("suspend", &CudaBackend::suspend, py::call_guard<py::gil_scoped_release>())
+      .def("resume", &CudaBackend::resume, py::call_guard<py::gil_scoped_release>())
+      .def("is_suspended", &CudaBackend::is_suspended)
       .def("seq_heads_exchange", [](CudaBackend& b, at::Tensor out, const at::Tensor& in, bool to_heads, bool a, OptHints h,
                                     OptMillis to) {
         return b.seq_heads_exchange(out, in, to_heads, a, make_op_options(h, to));
