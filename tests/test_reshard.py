@@ -47,6 +47,41 @@ def test_plan_covers_every_destination_element_exactly_once():
     assert sorted(set(readers)) == [0, 1] and readers.count(0) == readers.count(1)
 
 
+def test_random_meshes_and_shapes_are_planned_correctly():
+    """Seeded sweep over mesh sizes, placements and tensor ranks (1 to 3 dims), overlapping rank ranges included."""
+    import random
+
+    rng = random.Random(7)
+
+    def random_mesh(ndim, start):
+        dims = (rng.choice([1, 2, 3]), rng.choice([1, 2, 4]))
+        free = list(range(ndim))
+        rng.shuffle(free)
+        placement = []
+        for _ in range(2):
+            if free and rng.random() < 0.6:
+                placement.append(Shard(free.pop()))
+            else:
+                placement.append(REPLICATE)
+        return Mesh(dims, start, tuple(placement))
+
+    for _ in range(200):
+        ndim = rng.choice([1, 2, 3])
+        shape = tuple(rng.choice([12, 24]) for _ in range(ndim))
+        src = random_mesh(ndim, 0)
+        dst = random_mesh(ndim, rng.choice([0, src.size, max(0, src.size - 1)]))
+        full = torch.arange(int(torch.tensor(shape).prod())).view(shape)
+        seen = {r: torch.zeros(dst.local_shape(shape), dtype=torch.int64) for r in dst.ranks()}
+        for t in plan_transfers(shape, src, dst):
+            piece = _tile(full, src, t.src_rank)[tuple(slice(a, b) for a, b in t.src_slices)]
+            where = tuple(slice(a, b) for a, b in t.dst_slices)
+            assert torch.equal(piece, _tile(full, dst, t.dst_rank)[where]), (shape, src, dst, t)
+            seen[t.dst_rank][where] += 1
+            if t.dst_rank in src.holders(src.tile_index(t.src_rank, ndim)):
+                assert t.src_rank == t.dst_rank          # a rank that has the tile itself does not fetch it
+        assert all(bool((m == 1).all()) for m in seen.values()), (shape, src, dst)
+
+
 def test_mesh_validation():
     with pytest.raises(ValueError):
         Mesh((2, 2), 0, (Shard(0), Shard(0)))
