@@ -34,6 +34,7 @@ to constants - is the same.
 """
 from __future__ import annotations
 
+import weakref
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -94,7 +95,11 @@ def enable(comm: TorchComm) -> TorchComm:
     """Makes ``comm`` usable inside compiled regions (communicators created after
     ``register_with_dynamo()`` are enabled when they are created)."""
     orig = _ORIG if _ORIG else {n: getattr(TorchComm, n) for n in ("get_name", "get_rank", "get_size")}
-    _BY_ID[id(comm)] = _Traceable(comm, orig)
+    key = id(comm)
+    if key not in _BY_ID:
+        # The entry goes when the object does, so that a later object at the same address is not mistaken for it.
+        weakref.finalize(comm, _BY_ID.pop, key, None)
+    _BY_ID[key] = _Traceable(comm, orig)
     return comm
 
 
