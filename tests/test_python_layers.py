@@ -482,6 +482,18 @@ def test_tuning_crossovers():
     hs = hint_sweep({"steps=8": [r for r in rows if r["algo"] == "kernel"],
                      "steps=2": [dict(r, us=r["us"] * (0.5 if r["bytes"] > 4096 else 2)) for r in rows if r["algo"] == "kernel"]})
     assert hs[("all_reduce", "bf16", 1 << 24)]["hints"] == "steps=2" and hs[("all_reduce", "bf16", 1024)]["hints"] == "steps=8"
+    # rows of the bench sweep (arm / avg_us) are read as well; a margin keeps near ties with the kernels
+    from torchcomms_b200.utils.tuning import tuner_file_lines
+
+    sweep = []
+    for b, k, n in [(1 << 20, 12.0, 20.0), (1 << 21, 33.0, 29.0), (1 << 22, 35.0, 34.5), (1 << 24, 50.0, 58.0)]:
+        sweep.append({"op": "all_to_all_v", "dtype": "bf16", "bytes": b, "arm": "own", "avg_us": k, "p50_us": k})
+        sweep.append({"op": "all_to_all_v", "dtype": "bf16", "bytes": b, "arm": "nccl", "avg_us": n, "p50_us": n})
+    assert [a for _, _, a in crossovers(sweep)[("all_to_all_v", "bf16")]] == ["kernel", "nccl", "kernel"]
+    assert crossovers(sweep, margin=0.05)[("all_to_all_v", "bf16")] == [
+        (1 << 20, 1 << 20, "kernel"), (1 << 21, 1 << 21, "nccl"), (1 << 22, 1 << 24, "kernel")]
+    assert tuner_file_lines(sweep, margin=0.05)[1:] == [
+        f"all_to_all_v {1 << 20} kernel", f"all_to_all_v {1 << 21} nccl", "all_to_all_v inf kernel"]
 
 
 def _data_parallel_worker(rank, world):
