@@ -457,3 +457,15 @@ def _suspend_resume_body(rank, world):
 
 def test_suspend_and_resume_for_checkpoints():
     run_ranks(_suspend_resume_body, 4, timeout=180)
+
+
+def test_shipped_tuner_file_loads(single_rank_env):
+    """The tuner file that ships with the benchmarks is accepted by the backend's loader (comments, `inf`, both
+    spellings of the all-to-all)."""
+    import os
+
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "tuner_8xb200.txt")
+    comm = _new_comm("shipped_tuner", world_hints={"tuner_file": path})
+    rules = sum(1 for ln in open(path) if ln.split("#")[0].strip())
+    assert comm.get_backend_impl().comm_dump()["tuning/tuner_rules"] == str(rules)
+    comm.finalize()
