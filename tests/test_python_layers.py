@@ -319,6 +319,11 @@ def _context_worker(rank, world):
     grads = torch.autograd.grad(out.square().sum(), (lq, lk, lv))
     for got_g, ref_g in zip(grads, (gq, gk, gv)):
         torch.testing.assert_close(got_g, ref_g[:, :, sl], rtol=1e-4, atol=1e-5)
+    # grouped-query attention: 8 query heads share 4 key / value heads (head groups stay together on a rank)
+    gq, gk2, gv2 = torch.randn(b, 8, s, d), torch.randn(b, 4, s, d), torch.randn(b, 4, s, d)
+    ref = torch.nn.functional.scaled_dot_product_attention(gq, gk2, gv2, is_causal=True, enable_gqa=True)[:, :, sl]
+    got = ulysses_attention(gq[:, :, sl].contiguous(), gk2[:, :, sl].contiguous(), gv2[:, :, sl].contiguous(), comm, causal=True)
+    torch.testing.assert_close(got, ref, rtol=1e-4, atol=1e-5)
     # the exchange object falls back to the same all-to-all on backends without the fused kernel
     ex = SeqHeadsExchange(comm)
     assert not ex.fused

@@ -241,15 +241,18 @@ class _SeqHeadsFn(torch.autograd.Function):
 
 def ulysses_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, comm: TorchComm, causal: bool = False,
                       scale: Optional[float] = None, exchange: Optional[SeqHeadsExchange] = None) -> torch.Tensor:
-    """Same layout as ``ring_attention``; ``heads`` must divide by the communicator size.  With ``exchange``
-    (a ``SeqHeadsExchange`` of the same communicator) the four all-to-alls run as fused layout-changing kernels."""
+    """Same layout as ``ring_attention``; query heads and key / value heads (which may be fewer: grouped-query
+    attention) must each divide by the communicator size.  With ``exchange`` (a ``SeqHeadsExchange`` of the same
+    communicator) the four all-to-alls run as fused layout-changing kernels."""
     n = comm.get_size()
-    if q.shape[1] % n != 0:
-        raise ValueError(f"heads ({q.shape[1]}) must divide by the number of ranks ({n})")
+    for name, t in (("query", q), ("key / value", k)):
+        if t.shape[1] % n != 0:
+            raise ValueError(f"{name} heads ({t.shape[1]}) must divide by the number of ranks ({n})")
+    grouped = q.shape[1] != k.shape[1]       # grouped-query attention: fewer key / value heads than query heads
     if exchange is not None:
         qh, kh, vh = (exchange.to_heads(t) for t in (q, k, v))
-        o = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=causal, scale=scale)
+        o = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=causal, scale=scale, enable_gqa=grouped)
         return exchange.to_seq(o)
     qh, kh, vh = (_seq_to_heads(t, comm) for t in (q, k, v))
-    o = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=causal, scale=scale)
+    o = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=causal, scale=scale, enable_gqa=grouped)
     return _heads_to_seq(o, comm)
