@@ -182,3 +182,30 @@ def test_inductor_lowerings_are_registered():
 
     for name in ("barrier", "gather_single", "all_reduce", "send"):
         assert getattr(torch.ops.torchcomms_b200, name).default in fx_node._side_effectful_functions
+
+
+def test_patch_for_compile_variable_registers_on_import():
+    """TORCHCOMMS_PATCH_FOR_COMPILE=1 (the reference's gate) makes importing the functional package enough."""
+    import subprocess
+    import sys
+
+    code = (
+        "import os; os.environ.update(RANK='0', WORLD_SIZE='1')\n"
+        "import torch, torchcomms_b200 as tc\n"
+        "import torchcomms_b200.functional as F\n"
+        "from torchcomms_b200.functional import dynamo as D\n"
+        "assert D.is_registered() == (os.environ.get('TORCHCOMMS_PATCH_FOR_COMPILE') == '1')\n"
+        "if D.is_registered():\n"
+        "    c = tc.new_comm('fake', torch.device('cpu'), name='gate')\n"
+        "    f = torch.compile(lambda x: x * (c.get_size() + 1), fullgraph=True, backend='eager')\n"
+        "    assert float(f(torch.ones(1))) == 2.0\n"
+        "    c.finalize()\n"
+        "print('ok')\n"
+    )
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for flag in ("1", "0"):
+        env = dict(os.environ, TORCHCOMMS_PATCH_FOR_COMPILE=flag, PYTHONPATH=root)
+        out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stderr[-2000:]

@@ -486,6 +486,15 @@ from .inductor import mark_side_effects as _mark_side_effects  # noqa: E402
 # that rank's traced graph: the peers make the matching call and would wait for it.
 _mark_side_effects()
 
+if is_torch_compile_supported_and_enabled():
+    # TORCHCOMMS_PATCH_FOR_COMPILE=1, as in the reference: communicator methods become traceable and the Inductor
+    # lowerings are registered as soon as this package is imported.
+    from .dynamo import register_with_dynamo as _register_with_dynamo  # noqa: E402
+    from .inductor import register_with_inductor as _register_with_inductor  # noqa: E402
+
+    _register_with_dynamo()
+    _register_with_inductor()
+
 __all__ = [
     "AsyncCollectiveTensor", "OnceWork", "TracedWork", "wrap_async", "CompiledComm", "compiled",
     "all_gather", "all_gather_v", "reduce_scatter", "all_to_all", "all_reduce_async", "all_gather_single_async",
