@@ -117,6 +117,19 @@ def _dynamo_worker(rank, world):
     assert torch.equal(sc, torch.full((4,), 1.0 + 10 * rank))                         # rank 0's x is all ones
     assert last.shape == (world, 2) and float(last[0, 0]) == world - 1
 
+    # a batch of sends and receives becomes one operator
+    def ring(x):
+        batch = comm.batch_op_create()
+        got = torch.empty_like(x)
+        batch.send(x * 3, nxt)
+        batch.recv(got, prv)
+        batch.issue(False).wait()
+        return got + 1
+
+    (out_ring), seen_ring = _graph_ops(ring, x)
+    assert torch.equal(out_ring, torch.full((4,), 3.0 * (prv + 1) + 1))
+    assert sum("batch_send_recv" in s for s in seen_ring) == 1
+
     # a split communicator is enabled as it is made
     sub = comm.split(list(range(world)), "dyn_sub")
 

@@ -289,6 +289,36 @@ def _m_barrier(self, async_op, hints=None, timeout=None):
     return _ORIG["barrier"](self, async_op, hints, timeout)
 
 
+class TracedBatch:
+    """What ``comm.batch_op_create()`` gives inside a compiled region: it collects the sends and receives and
+    records one ``batch_send_recv`` operator at ``issue()``, followed by the copies into the receive tensors."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self.sends: List[Tensor] = []
+        self.dsts: List[int] = []
+        self.recvs: List[Tensor] = []
+        self.srcs: List[int] = []
+
+    def send(self, tensor: Tensor, dst: int) -> None:
+        self.sends.append(tensor)
+        self.dsts.append(dst)
+
+    def recv(self, tensor: Tensor, src: int) -> None:
+        self.recvs.append(tensor)
+        self.srcs.append(src)
+
+    def issue(self, async_op: bool = False, options=None) -> TracedCommWork:
+        got = _ops.batch_send_recv(self.sends, self.dsts, self.recvs, self.srcs, self.name)
+        return _finish(self.recvs, got, async_op, False)
+
+
+def _m_batch_op_create(self):
+    if torch.compiler.is_compiling():
+        return TracedBatch(_traceable(self).name)
+    return _ORIG["batch_op_create"](self)
+
+
 def _m_finalize(self):
     _BY_ID.pop(id(self), None)
     return _ORIG["finalize"](self)
@@ -308,7 +338,8 @@ _METHODS = {
     "all_to_all_single": _m_all_to_all_single, "all_to_all_v_single": _m_all_to_all_v_single,
     "all_gather": _m_all_gather, "reduce_scatter": _m_reduce_scatter, "all_to_all": _m_all_to_all,
     "all_gather_v": _m_all_gather_v, "gather_single": _m_gather_single, "gather": _m_gather, "scatter": _m_scatter,
-    "send": _m_send, "recv": _m_recv, "barrier": _m_barrier, "finalize": _m_finalize, "split": _m_split,
+    "send": _m_send, "recv": _m_recv, "barrier": _m_barrier, "batch_op_create": _m_batch_op_create,
+    "finalize": _m_finalize, "split": _m_split,
 }
 
 def is_registered() -> bool:
@@ -363,4 +394,5 @@ def unregister_from_dynamo() -> None:
     _REDUCE_BY_ID.clear()
 
 
-__all__ = ["register_with_dynamo", "unregister_from_dynamo", "is_registered", "enable", "register_reduce_op", "TracedCommWork"]
+__all__ = ["register_with_dynamo", "unregister_from_dynamo", "is_registered", "enable", "register_reduce_op", "TracedCommWork",
+           "TracedBatch"]
