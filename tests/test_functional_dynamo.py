@@ -204,8 +204,8 @@ def test_patch_for_compile_variable_registers_on_import():
 
     code = (
         "import os; os.environ.update(RANK='0', WORLD_SIZE='1')\n"
-        "import torch, torchcomms_b200 as tc\n"
-        "import torchcomms_b200.functional as F\n"
+        "import sys, torch, torchcomms_b200 as tc\n"
+        "assert ('torchcomms_b200.functional' in sys.modules) == (os.environ.get('TORCHCOMMS_PATCH_FOR_COMPILE') == '1')\n"
         "from torchcomms_b200.functional import dynamo as D\n"
         "assert D.is_registered() == (os.environ.get('TORCHCOMMS_PATCH_FOR_COMPILE') == '1')\n"
         "if D.is_registered():\n"

@@ -280,3 +280,9 @@ def install_alias(name: str = "torchcomms") -> None:
     sys.modules[name] = me
     for sub in ("device_mesh", "distwrap", "functional", "objcol", "hooks", "mem", "ops", "parallel", "_comms"):
         sys.modules[f"{name}.{sub}"] = importlib.import_module(f"{__name__}.{sub}")
+
+
+if os.environ.get("TORCHCOMMS_PATCH_FOR_COMPILE") == "1":
+    # As in the reference (comms/torchcomms/__init__.py): with this variable set, importing the package is enough for
+    # communicator methods to be traceable under torch.compile (functional/__init__.py does the registration).
+    from . import functional as _functional  # noqa: E402,F401
