@@ -222,3 +222,40 @@ def test_patch_for_compile_variable_registers_on_import():
         env = dict(os.environ, TORCHCOMMS_PATCH_FOR_COMPILE=flag, PYTHONPATH=root)
         out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
         assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stderr[-2000:]
+
+
+def test_window_methods_are_traced_in_program_order():
+    """put / signal / wait_signal of a window object inside a compiled region: recorded as the window operators,
+    chained by the window's token, and get_tensor() reads behind the last of them."""
+    import os
+
+    os.environ.update(RANK="0", WORLD_SIZE="1")
+    import torchcomms_b200 as tc
+    from torchcomms_b200.functional import dynamo as D
+
+    D.register_with_dynamo()
+    try:
+        comm = tc.new_comm("fake", torch.device("cpu"), name="dyn_win")
+        win = comm.new_window()
+        buf = torch.zeros(8)
+        win.tensor_register(buf)
+
+        def fn(src):
+            win.put(src, 0, 2, False)
+            win.signal(0, False)
+            win.wait_signal(0, False)
+            return win.get_tensor() * 2
+
+        expect = torch.tensor([0, 0, 2, 4, 6, 0, 0, 0], dtype=torch.float32)
+        assert torch.equal(fn(torch.tensor([1.0, 2.0, 3.0])), expect)          # eager: the bound methods
+        buf.zero_()
+        out, seen = _graph_ops(fn, torch.tensor([1.0, 2.0, 3.0]))
+        assert torch.equal(out, expect)
+        ops = [s.split(".")[0] for s in seen if s.startswith("window_")]
+        assert ops == ["window_put", "window_signal", "window_wait_signal", "window_read"], seen
+        buf.zero_()
+        assert torch.equal(torch.compile(fn, fullgraph=True, backend="aot_eager")(torch.tensor([1.0, 2.0, 3.0])), expect)
+        win.tensor_deregister()
+        comm.finalize()
+    finally:
+        D.unregister_from_dynamo()

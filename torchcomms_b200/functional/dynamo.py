@@ -319,6 +319,86 @@ def _m_batch_op_create(self):
     return _ORIG["batch_op_create"](self)
 
 
+# ------------------------------------------------------------------ windows ---
+# A window object's put / signal / wait_signal have no tensor results, so nothing in the data flow keeps them in
+# program order. Each enabled window carries a token: every recorded window operator takes the window's current
+# token and gives the next one, and ``get_tensor()`` inside a compiled region returns the window's contents ordered
+# behind the last token (``window_read``).
+
+
+class _WindowState:
+    def __init__(self, name: str):
+        self.name = name
+        self.token = torch.empty(0)
+
+
+_WIN_BY_ID: Dict[int, _WindowState] = {}
+_WIN_ORIG: Dict[str, object] = {}
+_win_counter = [0]
+
+
+def enable_window(window, name: Optional[str] = None):
+    """Makes a window's methods usable inside compiled regions (windows made by ``comm.new_window()`` after
+    ``register_with_dynamo()`` are enabled when they are made)."""
+    from .ext import register_window
+
+    key = id(window)
+    if key in _WIN_BY_ID:
+        return window
+    if name is None:
+        _win_counter[0] += 1
+        name = f"_traced_window_{_win_counter[0]}"
+    register_window(name, window)
+    _WIN_BY_ID[key] = _WindowState(name)
+    weakref.finalize(window, _forget_window, key, name)
+    return window
+
+
+def _forget_window(key: int, name: str) -> None:
+    from .ext import unregister_window
+
+    _WIN_BY_ID.pop(key, None)
+    unregister_window(name)
+
+
+def _w_put(self, tensor, dst_rank, target_offset_nelems, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        st = _WIN_BY_ID[id(self)]
+        st.token = _ops.window_put(tensor, st.name, dst_rank, target_offset_nelems, st.token)
+        return TracedCommWork()
+    return _WIN_ORIG["put"](self, tensor, dst_rank, target_offset_nelems, async_op, hints, timeout)
+
+
+def _w_signal(self, dst_rank, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        st = _WIN_BY_ID[id(self)]
+        st.token = _ops.window_signal(st.name, dst_rank, st.token)
+        return TracedCommWork()
+    return _WIN_ORIG["signal"](self, dst_rank, async_op, hints, timeout)
+
+
+def _w_wait_signal(self, peer_rank, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        st = _WIN_BY_ID[id(self)]
+        st.token = _ops.window_wait_signal(st.name, peer_rank, st.token)
+        return TracedCommWork()
+    return _WIN_ORIG["wait_signal"](self, peer_rank, async_op, hints, timeout)
+
+
+def _w_get_tensor(self):
+    if torch.compiler.is_compiling():
+        st = _WIN_BY_ID[id(self)]
+        return _ops.window_read(st.name, st.token)
+    return _WIN_ORIG["get_tensor"](self)
+
+
+_WINDOW_METHODS = {"put": _w_put, "signal": _w_signal, "wait_signal": _w_wait_signal, "get_tensor": _w_get_tensor}
+
+
+def _m_new_window(self, tensor=None):
+    return enable_window(_ORIG["new_window"](self, tensor))
+
+
 def _m_finalize(self):
     _BY_ID.pop(id(self), None)
     return _ORIG["finalize"](self)
@@ -339,7 +419,7 @@ _METHODS = {
     "all_gather": _m_all_gather, "reduce_scatter": _m_reduce_scatter, "all_to_all": _m_all_to_all,
     "all_gather_v": _m_all_gather_v, "gather_single": _m_gather_single, "gather": _m_gather, "scatter": _m_scatter,
     "send": _m_send, "recv": _m_recv, "barrier": _m_barrier, "batch_op_create": _m_batch_op_create,
-    "finalize": _m_finalize, "split": _m_split,
+    "finalize": _m_finalize, "split": _m_split, "new_window": _m_new_window,
 }
 
 def is_registered() -> bool:
@@ -363,6 +443,13 @@ def register_with_dynamo() -> None:
         fn.__qualname__ = f"TorchComm.{name}"
         fn.__doc__ = getattr(_ORIG[name], "__doc__", None)
         setattr(TorchComm, name, fn)
+    from .. import TorchCommWindow
+
+    for name, fn in _WINDOW_METHODS.items():
+        _WIN_ORIG[name] = getattr(TorchCommWindow, name)
+        fn.__name__ = name
+        fn.__qualname__ = f"TorchCommWindow.{name}"
+        setattr(TorchCommWindow, name, fn)
     for op_name, red in (("SUM", "sum"), ("AVG", "avg"), ("MAX", "max"), ("MIN", "min"), ("PRODUCT", "product")):
         _REDUCE_BY_ID[id(getattr(ReduceOp, op_name))] = red
     mark_side_effects()     # a barrier or send whose result nobody reads stays in the graph
@@ -386,13 +473,18 @@ def unregister_from_dynamo() -> None:
         return
     import torchcomms_b200 as pkg
 
+    from .. import TorchCommWindow
+
     pkg.new_comm = _ORIG.pop("new_comm")
     for name, fn in list(_ORIG.items()):
         setattr(TorchComm, name, fn)
+    for name, fn in list(_WIN_ORIG.items()):
+        setattr(TorchCommWindow, name, fn)
     _ORIG.clear()
+    _WIN_ORIG.clear()
     _BY_ID.clear()
     _REDUCE_BY_ID.clear()
 
 
-__all__ = ["register_with_dynamo", "unregister_from_dynamo", "is_registered", "enable", "register_reduce_op", "TracedCommWork",
-           "TracedBatch"]
+__all__ = ["register_with_dynamo", "unregister_from_dynamo", "is_registered", "enable", "enable_window", "register_reduce_op",
+           "TracedCommWork", "TracedBatch"]
