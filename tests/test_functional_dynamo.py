@@ -108,9 +108,13 @@ def _dynamo_worker(rank, world):
         comm.scatter(sc, [x + 10 * r for r in range(comm.get_size())] if comm.get_rank() == 0 else [], 0, False)
         vs = [torch.empty(r + 1, 2) for r in range(comm.get_size())]
         comm.all_gather_v(vs, torch.full((comm.get_rank() + 1, 2), float(comm.get_rank())), False)
-        return g, torch.stack(parts), sc, vs[-1]
+        rv = torch.empty(comm.get_rank() + 1, 2)
+        comm.reduce_scatter_v(rv, [torch.full((r + 1, 2), 1.0 + comm.get_rank()) for r in range(comm.get_size())],
+                              ReduceOp.SUM, False)
+        return g, torch.stack(parts), sc, vs[-1], rv
 
-    g, parts, sc, last = torch.compile(rooted, fullgraph=True, backend="aot_eager")(x)
+    g, parts, sc, last, rv = torch.compile(rooted, fullgraph=True, backend="aot_eager")(x)
+    assert torch.equal(rv, torch.full((rank + 1, 2), float(tri)))
     every = torch.arange(1, world + 1, dtype=torch.float32).repeat_interleave(4)
     assert torch.equal(g, every if rank == 1 else torch.zeros(world * 4))          # only the root's output is written
     assert torch.equal(parts.flatten(), 2 * every if rank == 0 else torch.zeros(world * 4))

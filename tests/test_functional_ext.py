@@ -34,6 +34,12 @@ def _ext_worker(rank, world):
     assert [tuple(y.shape) for y in ys] == [(r + 1, 2) for r in range(world)] and float(ys[world - 1][0, 0]) == world - 1
     rs = F.reduce_scatter([torch.full((4,), float(rank + 1 + r)) for r in range(world)], "sum", comm)
     assert torch.equal(rs, torch.full((4,), float(tri + world * rank)))
+    # uneven shares: rank r keeps r + 1 rows; the gradient of every share comes back from its owner
+    shares = [torch.full((r + 1, 2), float(rank + 1), requires_grad=True) for r in range(world)]
+    mine = F.reduce_scatter_v(shares, "sum", comm)
+    assert mine.shape == (rank + 1, 2) and torch.equal(mine, torch.full((rank + 1, 2), float(tri)))
+    (mine * (rank + 1)).sum().backward()
+    assert [float(t.grad[0, 0]) for t in shares] == [float(r + 1) for r in range(world)]
     outs = F.all_to_all([torch.full((2,), float(rank * world + d)) for d in range(world)], comm)
     assert [float(o[0]) for o in outs] == [float(s * world + rank) for s in range(world)]
 

@@ -476,7 +476,7 @@ def scatter(x: Tensor, root: int, comm: Union[TorchComm, str]) -> Tensor:
 from .async_tensor import AsyncCollectiveTensor, OnceWork, TracedWork, wrap_async  # noqa: E402
 from .ext import (  # noqa: E402
     CompiledComm, all_gather, all_gather_single_async, all_gather_v, all_reduce_async, all_to_all, all_to_all_single_async,
-    batch_send_recv, compiled, reduce_scatter, reduce_scatter_single_async, register_window, unregister_window,
+    batch_send_recv, compiled, reduce_scatter, reduce_scatter_single_async, reduce_scatter_v, register_window, unregister_window,
     window_put, window_read, window_signal, window_token, window_wait_signal,
 )
 from .param_parsing import normalize_reduce_op, parse_hints, parse_timeout  # noqa: E402
@@ -497,7 +497,7 @@ if is_torch_compile_supported_and_enabled():
 
 __all__ = [
     "AsyncCollectiveTensor", "OnceWork", "TracedWork", "wrap_async", "CompiledComm", "compiled",
-    "all_gather", "all_gather_v", "reduce_scatter", "all_to_all", "all_reduce_async", "all_gather_single_async",
+    "all_gather", "all_gather_v", "reduce_scatter", "reduce_scatter_v", "all_to_all", "all_reduce_async", "all_gather_single_async",
     "reduce_scatter_single_async", "all_to_all_single_async", "batch_send_recv", "register_window", "unregister_window",
     "window_put", "window_read", "window_signal", "window_token", "window_wait_signal",
     "normalize_reduce_op", "parse_hints", "parse_timeout",

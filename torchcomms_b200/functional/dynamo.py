@@ -224,6 +224,12 @@ def _m_reduce_scatter(self, output, input_list, op, async_op, hints=None, timeou
     return _ORIG["reduce_scatter"](self, output, input_list, op, async_op, hints, timeout)
 
 
+def _m_reduce_scatter_v(self, output, input_list, op, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        return _finish([output], [_ops.reduce_scatter_v(list(input_list), _red(op), _traceable(self).name)], async_op, False)
+    return _ORIG["reduce_scatter_v"](self, output, input_list, op, async_op, hints, timeout)
+
+
 def _m_all_to_all(self, output_tensor_list, input_tensor_list, async_op, hints=None, timeout=None):
     if torch.compiler.is_compiling():
         return _finish(output_tensor_list, _ops.all_to_all(list(input_tensor_list), _traceable(self).name), async_op, False)
@@ -417,7 +423,7 @@ _METHODS = {
     "all_gather_single": _m_all_gather_single, "reduce_scatter_single": _m_reduce_scatter_single,
     "all_to_all_single": _m_all_to_all_single, "all_to_all_v_single": _m_all_to_all_v_single,
     "all_gather": _m_all_gather, "reduce_scatter": _m_reduce_scatter, "all_to_all": _m_all_to_all,
-    "all_gather_v": _m_all_gather_v, "gather_single": _m_gather_single, "gather": _m_gather, "scatter": _m_scatter,
+    "all_gather_v": _m_all_gather_v, "reduce_scatter_v": _m_reduce_scatter_v, "gather_single": _m_gather_single, "gather": _m_gather, "scatter": _m_scatter,
     "send": _m_send, "recv": _m_recv, "barrier": _m_barrier, "batch_op_create": _m_batch_op_create,
     "finalize": _m_finalize, "split": _m_split, "new_window": _m_new_window,
 }

@@ -41,6 +41,7 @@ _lib.define("all_gather(Tensor input, str comm) -> Tensor[]")
 _lib.define("all_gather_v(Tensor input, int[] sizes, str comm) -> Tensor[]")
 _lib.define("reduce_scatter(Tensor[] inputs, str op, str comm) -> Tensor")
 _lib.define("all_to_all(Tensor[] inputs, str comm) -> Tensor[]")
+_lib.define("reduce_scatter_v(Tensor[] inputs, str op, str comm) -> Tensor")
 
 
 def _impl_all_gather(input: Tensor, comm: str) -> List[Tensor]:
@@ -64,6 +65,13 @@ def _impl_reduce_scatter(inputs: List[Tensor], op: str, comm: str) -> Tensor:
     return out
 
 
+def _impl_reduce_scatter_v(inputs: List[Tensor], op: str, comm: str) -> Tensor:
+    c = _get(comm)
+    out = torch.empty_like(inputs[c.get_rank()], memory_format=torch.contiguous_format)
+    c.reduce_scatter_v(out, [t.contiguous() for t in inputs], _red(op), False)
+    return out
+
+
 def _impl_all_to_all(inputs: List[Tensor], comm: str) -> List[Tensor]:
     c = _get(comm)
     outs = [torch.empty_like(t, memory_format=torch.contiguous_format) for t in inputs]
@@ -72,7 +80,8 @@ def _impl_all_to_all(inputs: List[Tensor], comm: str) -> List[Tensor]:
 
 
 for _op, _fn in (("all_gather", _impl_all_gather), ("all_gather_v", _impl_all_gather_v),
-                 ("reduce_scatter", _impl_reduce_scatter), ("all_to_all", _impl_all_to_all)):
+                 ("reduce_scatter", _impl_reduce_scatter), ("all_to_all", _impl_all_to_all),
+                 ("reduce_scatter_v", _impl_reduce_scatter_v)):
     _lib.impl(_op, _fn, "CompositeExplicitAutograd")
 
 
@@ -89,6 +98,11 @@ def _fake_all_gather_v(input, sizes, comm):
 @torch.library.register_fake(f"{NAMESPACE}::reduce_scatter")
 def _fake_reduce_scatter(inputs, op, comm):
     return torch.empty_like(inputs[0], memory_format=torch.contiguous_format)
+
+
+@torch.library.register_fake(f"{NAMESPACE}::reduce_scatter_v")
+def _fake_reduce_scatter_v(inputs, op, comm):
+    return torch.empty_like(inputs[_get(comm).get_rank()], memory_format=torch.contiguous_format)   # shares differ per rank
 
 
 @torch.library.register_fake(f"{NAMESPACE}::all_to_all")
@@ -115,6 +129,21 @@ def _bw_reduce_scatter(ctx, grad):
     return gs, None, None
 
 
+def _setup_reduce_scatter_v(ctx, inputs, output):
+    ctx.args = inputs[1:]
+    ctx.sizes = [t.shape[0] for t in inputs[0]]
+
+
+def _bw_reduce_scatter_v(ctx, grad):
+    op, comm = ctx.args
+    if op.lower() not in ("sum", "avg"):
+        raise RuntimeError(f"reduce_scatter_v: no gradient for op '{op}'")
+    gs = _ops.all_gather_v(grad.contiguous(), ctx.sizes, comm)
+    if op.lower() == "avg":
+        gs = [g / _size(comm) for g in gs]
+    return gs, None, None
+
+
 def _bw_all_to_all(ctx, grads):
     (comm,) = ctx.args
     return _ops.all_to_all([g.contiguous() for g in grads], comm), None
@@ -123,6 +152,7 @@ def _bw_all_to_all(ctx, grads):
 torch.library.register_autograd(f"{NAMESPACE}::all_gather", _bw_all_gather, setup_context=_setup)
 torch.library.register_autograd(f"{NAMESPACE}::reduce_scatter", _bw_reduce_scatter, setup_context=_setup)
 torch.library.register_autograd(f"{NAMESPACE}::all_to_all", _bw_all_to_all, setup_context=_setup)
+torch.library.register_autograd(f"{NAMESPACE}::reduce_scatter_v", _bw_reduce_scatter_v, setup_context=_setup_reduce_scatter_v)
 
 
 def all_gather(x: Tensor, comm: Union[TorchComm, str]) -> List[Tensor]:
@@ -138,6 +168,11 @@ def all_gather_v(x: Tensor, sizes: Sequence[int], comm: Union[TorchComm, str]) -
 def reduce_scatter(xs: Sequence[Tensor], op: str, comm: Union[TorchComm, str]) -> Tensor:
     """Reduction over ranks of ``xs[own rank]``."""
     return _ops.reduce_scatter(list(xs), op, _name(comm))
+
+
+def reduce_scatter_v(xs: Sequence[Tensor], op: str, comm: Union[TorchComm, str]) -> Tensor:
+    """Reduction over ranks of ``xs[own rank]``; the shares may have different numbers of rows."""
+    return _ops.reduce_scatter_v(list(xs), op, _name(comm))
 
 
 def all_to_all(xs: Sequence[Tensor], comm: Union[TorchComm, str]) -> List[Tensor]:

@@ -72,7 +72,7 @@ def _fake_broadcast_inplace(input, root, comm):
 _SIDE_EFFECTS = (
     "all_reduce", "all_reduce_", "all_gather_single", "reduce_scatter_single", "all_to_all_single", "broadcast",
     "broadcast_", "reduce", "barrier", "send", "recv", "gather_single", "scatter", "all_gather", "all_gather_v",
-    "reduce_scatter", "all_to_all", "all_reduce_start", "all_gather_single_start", "reduce_scatter_single_start",
+    "reduce_scatter", "reduce_scatter_v", "all_to_all", "all_reduce_start", "all_gather_single_start", "reduce_scatter_single_start",
     "all_to_all_single_start", "all_reduce_inplace", "broadcast_inplace", "window_put", "window_signal",
     "window_wait_signal", "batch_send_recv",
 )
