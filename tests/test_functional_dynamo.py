@@ -134,6 +134,19 @@ def _dynamo_worker(rank, world):
     assert torch.equal(out_ring, torch.full((4,), 3.0 * (prv + 1) + 1))
     assert sum("batch_send_recv" in s for s in seen_ring) == 1
 
+    # persistent all-gather: the handle comes from outside the region, exec is recorded inside
+    agp_out = torch.zeros(world * 4)
+    handle = comm.all_gather_p_init(agp_out)
+
+    def persistent(x):
+        comm.all_gather_p_exec(handle, x + 1, True).wait()
+        return agp_out.sum()
+
+    total_p = torch.compile(persistent, fullgraph=True, backend="aot_eager")(x)
+    assert torch.equal(agp_out, torch.arange(2, world + 2, dtype=torch.float32).repeat_interleave(4))
+    assert float(total_p) == float(agp_out.sum())
+    comm.all_gather_p_free(handle)
+
     # a split communicator is enabled as it is made
     sub = comm.split(list(range(world)), "dyn_sub")
 

@@ -275,6 +275,29 @@ def _m_scatter(self, output_tensor, input_tensor_list, root, async_op, hints=Non
     return _ORIG["scatter"](self, output_tensor, input_tensor_list, root, async_op, hints, timeout)
 
 
+# Persistent all-gather: the handle is made outside the compiled region (it registers the output once); inside,
+# exec records an all-gather into that output.
+_AGP_OUT: Dict[int, Tensor] = {}
+
+
+def _m_all_gather_p_init(self, output, hints=None, timeout=None):
+    handle = _ORIG["all_gather_p_init"](self, output, hints, timeout)
+    _AGP_OUT[id(handle)] = output
+    weakref.finalize(handle, _AGP_OUT.pop, id(handle), None)
+    return handle
+
+
+def _m_all_gather_p_exec(self, handle, input, async_op, hints=None, timeout=None):
+    if torch.compiler.is_compiling():
+        out = _AGP_OUT[id(handle)]
+        name = _traceable(self).name
+        flat = input.reshape(1, -1)
+        if async_op:
+            return _finish([out], [_ops.all_gather_single_start(flat, name)], True, True)
+        return _finish([out], [_ops.all_gather_single(flat, name)], False, False)
+    return _ORIG["all_gather_p_exec"](self, handle, input, async_op, hints, timeout)
+
+
 def _m_send(self, tensor, dst, async_op, hints=None, timeout=None):
     if torch.compiler.is_compiling():
         _ops.send(tensor, dst, _traceable(self).name)
@@ -423,7 +446,8 @@ _METHODS = {
     "all_gather_single": _m_all_gather_single, "reduce_scatter_single": _m_reduce_scatter_single,
     "all_to_all_single": _m_all_to_all_single, "all_to_all_v_single": _m_all_to_all_v_single,
     "all_gather": _m_all_gather, "reduce_scatter": _m_reduce_scatter, "all_to_all": _m_all_to_all,
-    "all_gather_v": _m_all_gather_v, "reduce_scatter_v": _m_reduce_scatter_v, "gather_single": _m_gather_single, "gather": _m_gather, "scatter": _m_scatter,
+    "all_gather_v": _m_all_gather_v, "reduce_scatter_v": _m_reduce_scatter_v,
+    "all_gather_p_init": _m_all_gather_p_init, "all_gather_p_exec": _m_all_gather_p_exec, "gather_single": _m_gather_single, "gather": _m_gather, "scatter": _m_scatter,
     "send": _m_send, "recv": _m_recv, "barrier": _m_barrier, "batch_op_create": _m_batch_op_create,
     "finalize": _m_finalize, "split": _m_split, "new_window": _m_new_window,
 }
