@@ -147,6 +147,29 @@ def _dynamo_worker(rank, world):
     assert float(total_p) == float(agp_out.sum())
     comm.all_gather_p_free(handle)
 
+    # gradients flow through communicator methods called inside a compiled region (the recorded operators carry
+    # autograd formulas): all-reduce of the upstream gradient, reduce-scatter for an all-gather
+    def loss_fn(w, inp):
+        y = inp * w
+        comm.all_reduce(y, ReduceOp.SUM, False)
+        g = torch.empty(comm.get_size() * 4)
+        comm.all_gather_single(g, y * (comm.get_rank() + 1), False)
+        return (g * g).sum()
+
+    w = torch.full((4,), 0.5, requires_grad=True)
+    inp = torch.full((4,), float(rank + 1))
+    loss = torch.compile(loss_fn, fullgraph=True, backend="aot_eager")(w, inp)
+    loss.backward()
+    # the same computation written with the differentiable operators of the functional module, uncompiled
+    from torchcomms_b200 import functional as F
+
+    w2 = torch.full((4,), 0.5, requires_grad=True)
+    y2 = F.all_reduce(inp * w2, "sum", comm)
+    g2 = F.all_gather_single((y2 * (rank + 1)).reshape(1, -1), comm).reshape(-1)
+    loss2 = (g2 * g2).sum()
+    loss2.backward()
+    assert torch.allclose(loss, loss2) and torch.allclose(w.grad, w2.grad) and float(w.grad.abs().sum()) > 0
+
     # a split communicator is enabled as it is made
     sub = comm.split(list(range(world)), "dyn_sub")
 
