@@ -615,3 +615,17 @@ def test_window_api_rules_on_the_fake_backend():
     with pytest.raises(RuntimeError, match="CUDA backend"):
         w.get_device_window()
     c.finalize()
+
+
+def test_type_stubs_match_the_bindings():
+    """torchcomms_b200/_comms.pyi is what the generator writes from the module as built (rerun
+    ``python -m torchcomms_b200.utils.stubgen`` after changing a binding)."""
+    import ast
+
+    from torchcomms_b200.utils import stubgen
+
+    text = stubgen.generate()
+    ast.parse(text)
+    assert open(stubgen.stub_path()).read() == text
+    for name in ("class TorchComm:", "class CudaBackend:", "def register_backend(", "class transport:", "def seq_heads_exchange("):
+        assert name in text, name
