@@ -319,6 +319,21 @@ def _context_worker(rank, world):
     grads = torch.autograd.grad(out.square().sum(), (lq, lk, lv))
     for got_g, ref_g in zip(grads, (gq, gk, gv)):
         torch.testing.assert_close(got_g, ref_g[:, :, sl], rtol=1e-4, atol=1e-5)
+    # ring attention is differentiable too (a second trip round the ring), in both layouts
+    for layout in ("contiguous", "zigzag"):
+        take = (lambda t: t[:, :, sl]) if layout == "contiguous" else (lambda t: zigzag_shard(t, rank, world))
+        rq, rk, rv = (take(t).clone().requires_grad_(True) for t in (q, k, v))
+        r_out = ring_attention(rq, rk, rv, comm, causal=True, layout=layout)
+        torch.testing.assert_close(r_out, take(full.detach()), rtol=1e-4, atol=1e-5)
+        r_grads = torch.autograd.grad(r_out.square().sum(), (rq, rk, rv))
+        for got_g, ref_g in zip(r_grads, (gq, gk, gv)):
+            torch.testing.assert_close(got_g, take(ref_g), rtol=1e-4, atol=1e-5)
+    rq, rk, rv = (t[:, :, sl].clone().requires_grad_(True) for t in (q, k, v))
+    nc_full = torch.nn.functional.scaled_dot_product_attention(fq, fk, fv, is_causal=False)
+    nc_ref = torch.autograd.grad(nc_full.square().sum(), (fq, fk, fv))
+    nc_grads = torch.autograd.grad(ring_attention(rq, rk, rv, comm, causal=False).square().sum(), (rq, rk, rv))
+    for got_g, ref_g in zip(nc_grads, nc_ref):
+        torch.testing.assert_close(got_g, ref_g[:, :, sl], rtol=1e-4, atol=1e-5)
     # grouped-query attention: 8 query heads share 4 key / value heads (head groups stay together on a rank)
     gq, gk2, gv2 = torch.randn(b, 8, s, d), torch.randn(b, 4, s, d), torch.randn(b, 4, s, d)
     ref = torch.nn.functional.scaled_dot_product_attention(gq, gk2, gv2, is_causal=True, enable_gqa=True)[:, :, sl]

@@ -9,7 +9,8 @@ Both shard the sequence over the ranks of a communicator.
   issued before the math of step ``i`` (asynchronous batch on the
   communicator's side stream) and waited for afterwards.
   With ``layout="zigzag"`` (``zigzag_shard`` / ``zigzag_unshard``) causal attention is
-  load-balanced over the ranks.
+  load-balanced over the ranks.  The backward pass sends the blocks round once
+  more, each with an accumulator for its gradient.
 * ``ulysses_attention``: one all-to-all turns sequence shards into head
   shards, attention runs locally over the full sequence for ``heads / n``
   heads, a second all-to-all turns the result back.  ``SeqHeadsExchange``
@@ -88,13 +89,22 @@ def zigzag_unshard(parts, dim: int = -2) -> torch.Tensor:
     return torch.cat(chunks, dim)
 
 
-def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, comm: TorchComm, causal: bool = False,
-                   scale: Optional[float] = None, layout: str = "contiguous") -> torch.Tensor:
-    """q, k, v: [batch, heads, seq_local, head_dim]; which global positions the local tokens have is given by
-    ``layout`` (see ``shard_positions``)."""
+def _block_mask(rank: int, src: int, n: int, sq: int, layout: str, causal: bool, pos_q: torch.Tensor, device):
+    """(skip, mask) for the local queries against the K/V block that rank ``src`` owns."""
+    if not causal:
+        return False, None
+    if layout == "contiguous" and src > rank:
+        return True, None                # that block lies entirely in the future
+    if layout != "contiguous" or src == rank:
+        pos_k = shard_positions(src, n, sq, layout, device)
+        return False, pos_q.unsqueeze(-1) >= pos_k.unsqueeze(0)
+    return False, None
+
+
+def _ring_forward(q, k, v, comm: TorchComm, causal: bool, scale: float, layout: str) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fp32 output and row log-sum-exp of the local queries over the whole sequence."""
     n, rank = comm.get_size(), comm.get_rank()
-    sq, d = q.shape[-2], q.shape[-1]
-    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    sq = q.shape[-2]
     nxt, prv = (rank + 1) % n, (rank - 1) % n
     kv = torch.stack([k, v]).contiguous()
     out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
@@ -109,21 +119,86 @@ def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, comm: Torc
             batch.send(kv, nxt)
             batch.recv(incoming, prv)
             work = batch.issue(True)
-        mask = None
-        skip = False
-        if causal:
-            pos_k = shard_positions(src, n, sq, layout, q.device)
-            if layout == "contiguous" and src > rank:
-                skip = True              # that block lies entirely in the future
-            elif layout != "contiguous" or src == rank:
-                mask = pos_q.unsqueeze(-1) >= pos_k.unsqueeze(0)
+        skip, mask = _block_mask(rank, src, n, sq, layout, causal, pos_q, q.device)
         if not skip:
             o2, l2 = _block_attention(q, kv[0], kv[1], scale, mask)
             out, lse = _merge(out, lse, o2, l2)
         if work is not None:
             work.wait()
             kv = incoming
-    return out.to(q.dtype)
+    return out, lse
+
+
+def _ring_backward(q, k, v, out, lse, dout, comm: TorchComm, causal: bool, scale: float, layout: str):
+    """Gradients of the local q, k, v. The K/V blocks go round the ring once more, each with an accumulator for its
+    gradient that every rank adds its queries' contribution to; one last hop brings the accumulator home."""
+    n, rank = comm.get_size(), comm.get_rank()
+    sq = q.shape[-2]
+    nxt, prv = (rank + 1) % n, (rank - 1) % n
+    qf, do = q.float(), dout.float()
+    delta = (do * out).sum(-1)                                  # [b, h, sq]
+    finite = torch.isfinite(lse).unsqueeze(-1)
+    lse_safe = lse.clamp_min(-1e30).unsqueeze(-1)
+    dq = torch.zeros_like(qf)
+    kv = torch.stack([k, v]).contiguous()
+    dkv = torch.zeros(kv.shape, dtype=torch.float32, device=q.device)
+    pos_q = shard_positions(rank, n, sq, layout, q.device)
+    for step in range(n):
+        src = (rank - step) % n
+        skip, mask = _block_mask(rank, src, n, sq, layout, causal, pos_q, q.device)
+        if not skip:
+            kf, vf = kv[0].float(), kv[1].float()
+            s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+            if mask is not None:
+                s = s.masked_fill(~mask, float("-inf"))
+            p = torch.where(finite, torch.exp(s - lse_safe), torch.zeros_like(s))
+            dp = torch.matmul(do, vf.transpose(-1, -2))
+            ds = p * (dp - delta.unsqueeze(-1))
+            dq += torch.matmul(ds, kf) * scale
+            dkv[0] += torch.matmul(ds.transpose(-1, -2), qf) * scale
+            dkv[1] += torch.matmul(p.transpose(-1, -2), do)
+        if n == 1:
+            break
+        batch = comm.batch_op_create()
+        got_dkv = torch.empty_like(dkv)
+        batch.send(dkv, nxt)
+        batch.recv(got_dkv, prv)
+        got_kv = None
+        if step + 1 < n:
+            got_kv = torch.empty_like(kv)
+            batch.send(kv, nxt)
+            batch.recv(got_kv, prv)
+        batch.issue(False).wait()
+        dkv = got_dkv
+        if got_kv is not None:
+            kv = got_kv
+    return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype)
+
+
+class _RingAttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, comm, causal, scale, layout):
+        out, lse = _ring_forward(q, k, v, comm, causal, scale, layout)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.comm, ctx.causal, ctx.scale, ctx.layout = comm, causal, scale, layout
+        return out.to(q.dtype)
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = _ring_backward(q, k, v, out, lse, dout, ctx.comm, ctx.causal, ctx.scale, ctx.layout)
+        return dq, dk, dv, None, None, None, None
+
+
+def ring_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, comm: TorchComm, causal: bool = False,
+                   scale: Optional[float] = None, layout: str = "contiguous") -> torch.Tensor:
+    """q, k, v: [batch, heads, seq_local, head_dim]; which global positions the local tokens have is given by
+    ``layout`` (see ``shard_positions``).  Differentiable: the backward pass is a second trip round the ring
+    (every rank must run it, as it must the forward pass)."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return _RingAttentionFn.apply(q, k, v, comm, causal, scale, layout)
+    return _ring_forward(q, k, v, comm, causal, scale, layout)[0].to(q.dtype)
 
 
 def _all_to_all(send: torch.Tensor, comm: TorchComm) -> torch.Tensor:
