@@ -469,3 +469,47 @@ def test_shipped_tuner_file_loads(single_rank_env):
     rules = sum(1 for ln in open(path) if ln.split("#")[0].strip())
     assert comm.get_backend_impl().comm_dump()["tuning/tuner_rules"] == str(rules)
     comm.finalize()
+
+
+def _seq_heads_route_body(rank, world):
+    """The sequence <-> heads exchange on fake ranks: argument checks, the symmetric-output requirement, the route
+    counter, the channel it shares with the all-to-all, the exchange object's ring of output buffers."""
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import _comms
+    from torchcomms_b200.parallel.context import SeqHeadsExchange
+
+    fake = _comms._install_fake_gpu()
+    comm = tc.new_comm("b200", torch.device("cuda", rank), name="fsh", abort_process_on_timeout_or_error=False,
+                       hints={"staging_mb": "1"})
+    impl = comm.get_backend_impl()
+    b, h, s, d = 2, 2 * world, 8, 16
+    x = torch.ones(b, h, s, d)
+    out = comm.symm_empty((b, h // world, s * world, d), torch.float32)
+    fake.clear_log()
+    impl.seq_heads_exchange(out, x, True, False)
+    impl.seq_heads_exchange(comm.symm_empty((b, h, s, d), torch.float32), out, False, True).wait()
+    launches = [l for l in fake.log() if l.startswith("launch")]
+    assert [l.split()[1] for l in launches] == ["seq_heads_exchange/symm"] * 2
+    a2a_out = comm.symm_empty((world * 1024 * 1024,), torch.float32)
+    fake.clear_log()
+    comm.all_to_all_single(a2a_out, torch.ones(world * 1024 * 1024), True).wait()
+    a2a_stream = next(l for l in fake.log() if l.startswith("launch")).split()[2]
+    assert launches[1].split()[2] == a2a_stream           # asynchronous calls of both run on the same channel stream
+    assert impl.comm_dump()["count/seq_heads_exchange/symm"] == "2"
+    with pytest.raises(RuntimeError, match="symmetric"):
+        impl.seq_heads_exchange(torch.empty(b, h // world, s * world, d), x, True, False)
+    with pytest.raises(RuntimeError, match="expected"):
+        impl.seq_heads_exchange(comm.symm_empty((b, h // world, s * world + 1, d), torch.float32), x, True, False)
+    with pytest.raises(RuntimeError, match="divide"):
+        impl.seq_heads_exchange(out, torch.ones(b, h + 1, s, d), True, False)
+    ex = SeqHeadsExchange(comm, slots=2)
+    assert ex.fused
+    y1, y2, y3 = ex.to_heads(x), ex.to_heads(x), ex.to_heads(x)
+    assert y1.data_ptr() == y3.data_ptr() != y2.data_ptr() and y1.shape == (b, h // world, s * world, d)
+    assert ex.to_seq(y1, keep=True).shape == x.shape
+    ex.close()
+    comm.finalize()
+
+
+def test_sequence_heads_exchange_route_on_fake_ranks():
+    run_ranks(_seq_heads_route_body, 2, timeout=120)
