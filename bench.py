@@ -67,6 +67,8 @@ def parse_args():
 
 
 def reference_arm():
+    if int(os.environ.get("RANK", "0")) != 0:     # under torchrun every rank gets here: one line, from rank 0
+        return
     print(json.dumps({
         "impl": "reference",
         "unavailable": "torchcomms cannot be built offline: its CMake configure step needs nlohmann_json, gflags, glog "
