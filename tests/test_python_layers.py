@@ -236,6 +236,17 @@ def _functional_worker(rank, world):
     total = float(sum(range(1, world + 1)))
     torch.testing.assert_close(gm2(x), torch.full((2, 3), 4 * total + world) + keep + 1)
     assert torch.equal(x, keep)                         # the caller's tensor was not written
+
+    # the wait behind a started collective is the only thing that orders its consumer: it stays
+    def started(v):
+        h = F.all_reduce_async(v * 3, "sum", "fn")
+        return h.wait() + F.wait_tensor(F.all_reduce(v, "sum", "fn"))
+
+    gm3 = make_fx(started, tracing_mode="fake")(torch.ones(2, 3))
+    assert count_ops(gm3) == {"all_reduce_start": 1, "wait_tensor": 2, "all_reduce": 1}
+    strip_wait_pass(gm3)
+    assert count_ops(gm3) == {"all_reduce_start": 1, "wait_tensor": 1, "all_reduce": 1}
+    torch.testing.assert_close(gm3(x), torch.full((2, 3), 4 * total))
     comm.finalize()
 
 

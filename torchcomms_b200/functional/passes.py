@@ -3,9 +3,9 @@
 ``reinplace_pass``    rewrites ``y = all_reduce(x)`` / ``y = broadcast(x)`` (which copy ``x`` first)
                       into the in-place operators when nothing else reads ``x`` afterwards and ``x``
                       is produced inside the graph - one copy of the payload less per collective.
-``strip_wait_pass``   removes ``wait_tensor`` nodes: the functional operators of this package return
+``strip_wait_pass``   removes ``wait_tensor`` nodes behind the synchronous operators: those return
                       finished tensors, so the node is a copy that only matters for graphs shared
-                      with code that expects it.
+                      with code that expects it.  Waits on the results of ``*_start`` operators stay.
 
 Apply ``reinplace_pass`` first.  Both mutate the GraphModule and recompile it::
 
@@ -61,11 +61,20 @@ def reinplace_pass(gm: fx.GraphModule, example_inputs=None) -> fx.GraphModule:
     return gm
 
 
+def _is_started(node) -> bool:
+    """True for the result of a ``*_start`` operator: the one kind of tensor that is not finished when it is made."""
+    name = getattr(getattr(node, "target", None), "_schema", None)
+    return isinstance(node, fx.Node) and node.op == "call_function" and name is not None and name.name.endswith("_start")
+
+
 def strip_wait_pass(gm: fx.GraphModule, example_inputs=None) -> fx.GraphModule:
-    """``wait_tensor(x)`` -> ``x``."""
+    """``wait_tensor(x)`` -> ``x``, except where ``x`` comes from a ``*_start`` operator (that wait is the only
+    thing that orders the consumer behind the collective)."""
     changed = 0
     for node in list(gm.graph.nodes):
         if node.op == "call_function" and node.target is _ops.wait_tensor.default:
+            if _is_started(node.args[0]):
+                continue
             node.replace_all_uses_with(node.args[0])
             gm.graph.erase_node(node)
             changed += 1
