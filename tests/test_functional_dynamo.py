@@ -296,6 +296,16 @@ def test_window_methods_are_traced_in_program_order():
         buf.zero_()
         assert torch.equal(torch.compile(fn, fullgraph=True, backend="aot_eager")(torch.tensor([1.0, 2.0, 3.0])), expect)
         win.tensor_deregister()
+        # the registration goes with the window object
+        import gc
+
+        from torchcomms_b200.functional import ext
+
+        name = D._WIN_BY_ID[id(win)].name
+        assert name in ext._windows
+        del win
+        gc.collect()
+        assert name not in ext._windows and not D._WIN_BY_ID
         comm.finalize()
     finally:
         D.unregister_from_dynamo()

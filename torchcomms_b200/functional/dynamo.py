@@ -377,7 +377,7 @@ def enable_window(window, name: Optional[str] = None):
     if name is None:
         _win_counter[0] += 1
         name = f"_traced_window_{_win_counter[0]}"
-    register_window(name, window)
+    register_window(name, weakref.proxy(window))     # the registry must not keep the window (and its tensor) alive
     _WIN_BY_ID[key] = _WindowState(name)
     weakref.finalize(window, _forget_window, key, name)
     return window
@@ -429,7 +429,11 @@ def _m_new_window(self, tensor=None):
 
 
 def _m_finalize(self):
-    _BY_ID.pop(id(self), None)
+    from . import _comms as registry
+
+    t = _BY_ID.pop(id(self), None)
+    if t is not None and registry.get(t.name) is self:
+        registry.pop(t.name, None)        # the operator registry held the communicator for the traced operators
     return _ORIG["finalize"](self)
 
 
