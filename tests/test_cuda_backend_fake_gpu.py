@@ -448,6 +448,14 @@ def _suspend_resume_body(rank, world):
     assert checkpoint_prepare([comm]) == []          # already suspended
     assert checkpoint_restore([comm, other]) == [comm] and not impl.is_suspended()
     other.finalize()
+    # a communicator made by split() suspends and resumes on its own store scope, in any order with its parent
+    members = [r for r in range(world) if r % 2 == rank % 2]
+    sub = comm.split(members, "ckpt_half")
+    assert checkpoint_prepare([comm, sub]) == [comm, sub]
+    assert checkpoint_restore([sub, comm]) == [sub, comm]
+    assert sub.get_size() == len(members) and sub.get_rank() == members.index(rank)
+    sub.all_reduce(t, tc.ReduceOp.SUM, False)
+    sub.finalize()
     comm.all_reduce(t, tc.ReduceOp.SUM, False)
     impl.suspend()
     comm.finalize()                                  # nothing is held: no barrier, no error
