@@ -53,6 +53,19 @@ def _ext_worker(rank, world):
     r = F.reduce_scatter_single_async(torch.arange(2.0 * world), "sum", comm)
     assert torch.equal(r.wait(), torch.arange(2.0 * world).view(world, 2)[rank] * world)
 
+    # started operators differentiate like the synchronous ones
+    for start, sync, shape in ((lambda t: F.all_gather_single_async(t, comm), lambda t: F.all_gather_single(t, comm), (2, 3)),
+                               (lambda t: F.all_reduce_async(t, "sum", comm), lambda t: F.all_reduce(t, "sum", comm), (2, 3)),
+                               (lambda t: F.reduce_scatter_single_async(t, "avg", comm),
+                                lambda t: F.reduce_scatter_single(t, "avg", comm), (2 * world, 3)),
+                               (lambda t: F.all_to_all_single_async(t, comm), lambda t: F.all_to_all_single(t, comm), (world, 3))):
+        a1 = torch.full(shape, float(rank + 1), requires_grad=True)
+        a2 = torch.full(shape, float(rank + 1), requires_grad=True)
+        weight = torch.arange(1.0, 1.0 + start(a1.detach()).wait().numel()).view_as(sync(a2.detach()))
+        (start(a1 * 2).wait() * weight).sum().backward()
+        (sync(a2 * 2) * weight).sum().backward()
+        assert torch.equal(a1.grad, a2.grad) and float(a1.grad.abs().sum()) > 0
+
     # batched send / receive in a ring
     nxt, prv = (rank + 1) % world, (rank - 1) % world
     (got,) = F.batch_send_recv([torch.full((3,), float(rank))], [nxt], [torch.empty(3)], [prv], comm)

@@ -317,6 +317,7 @@ class GlooWork final : public Work {
         for (auto& w : inner) {
           if (w) w->wait();
         }
+        at::NoGradGuard no_grad;   // the copy-back writes into the caller's tensors: never part of an autograd graph
         if (post) post();
       } catch (...) {
         // nobody is left to report to; the peer sees its own timeout
@@ -341,6 +342,10 @@ class GlooWork final : public Work {
         }
       }
       if (post_) {
+        // The copy-back / scaling writes into the caller's output in place. wait() may be called where gradient
+        // recording is on and the output already belongs to a graph (result of a traceable operator): the write
+        // is the operation's own completion, not a step of the user's computation.
+        at::NoGradGuard no_grad;
         post_();
       }
       set_status(WorkStatus::COMPLETED);

@@ -260,6 +260,21 @@ def _fake_all_to_all_single_start(input, output_split_sizes, input_split_sizes, 
     return torch.empty_like(input, memory_format=torch.contiguous_format)
 
 
+# The started operators differentiate like their synchronous counterparts (the gradient itself is computed with
+# the synchronous operators: nothing in a backward graph waits for it).
+def _register_start_autograd() -> None:
+    from . import _bw_all_gather_single, _bw_all_reduce, _bw_all_to_all_single, _bw_reduce_scatter_single
+    from . import _setup as _setup_sync
+
+    for name, fn in (("all_reduce_start", _bw_all_reduce), ("all_gather_single_start", _bw_all_gather_single),
+                     ("reduce_scatter_single_start", _bw_reduce_scatter_single),
+                     ("all_to_all_single_start", _bw_all_to_all_single)):
+        torch.library.register_autograd(f"{NAMESPACE}::{name}", fn, setup_context=_setup_sync)
+
+
+_register_start_autograd()
+
+
 def _start(op, *args):
     """Eager: an AsyncCollectiveTensor. Tracing: the start operator's result with a TracedWork."""
     out = op(*args)
