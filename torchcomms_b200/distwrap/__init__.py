@@ -39,7 +39,12 @@ from torch.distributed import (  # noqa: F401  (re-exports)
     is_available,
 )
 
-from .. import ReduceOp as _TcReduceOp
+# Backend classes of torch.distributed that code written against it names (options objects, isinstance checks);
+# absent in torch builds without the corresponding backend.
+ProcessGroupGloo = getattr(_td, "ProcessGroupGloo", None)
+ProcessGroupNCCL = getattr(_td, "ProcessGroupNCCL", None)
+
+from .. import ReduceOp as _TcReduceOp  # noqa: E402
 from .. import TorchComm, new_comm, objcol
 from ..device_mesh import wrap_comm_as_process_group
 from ..mem import get_mem_allocator as _tc_get_mem_allocator
