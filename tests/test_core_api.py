@@ -629,3 +629,26 @@ def test_type_stubs_match_the_bindings():
     assert open(stubgen.stub_path()).read() == text
     for name in ("class TorchComm:", "class CudaBackend:", "def register_backend(", "class transport:", "def seq_heads_exchange("):
         assert name in text, name
+
+
+def test_hooks_namespace_accepts_the_reference_spellings(tmp_path):
+    """``hooks.FlightRecorderHook`` and ``hooks.clog(output=..., events=[...])`` as in the reference's hooks package,
+    next to ``hooks.fr.FlightRecorderHook`` / ``hooks.clog.ClogHook``."""
+    import os
+
+    os.environ.update(RANK="0", WORLD_SIZE="1")
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import hooks
+
+    assert hooks.FlightRecorderHook is hooks.fr.FlightRecorderHook and hooks.clog.ClogHook is hooks.ClogHook
+    path = tmp_path / "clog.log"
+    logger = hooks.clog(output=str(path), events=["ALL"])
+    comm = tc.new_comm("fake", torch.device("cpu"), name="hooks_ns")
+    logger.register_with_comm(comm)
+    comm.all_reduce(torch.ones(2), tc.ReduceOp.SUM, False)
+    comm.finalize()
+    logger.unregister()
+    lines = path.read_text().splitlines()
+    assert lines[0].startswith("V|") and any(ln.startswith("SIG|") and "all_reduce" in ln for ln in lines)
+    with pytest.raises(ValueError):
+        hooks.clog(output="", events=["sometimes"])

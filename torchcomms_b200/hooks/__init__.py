@@ -17,6 +17,29 @@ from .chaos import ChecksumHook, DelayInjectionHook
 from .stats import CommStatsHook
 
 fr = _native.fr
-clog = _native.clog
+FlightRecorderHook = _native.fr.FlightRecorderHook
+ClogHook = _native.clog.ClogHook
 
-__all__ = ["NanCheckHook", "CommStatsHook", "DelayInjectionHook", "ChecksumHook", "fr", "clog"]
+
+class _Clog:
+    """``hooks.clog``: the namespace of the native collective log (``clog.ClogHook(path)``), and - the reference's
+    spelling - a constructor: ``clog(output="/tmp/clog.log", events=["ALL"])``.  Every event kind is always
+    written (queued, started, ended, waited, graph capture and replay lines), so ``events`` and ``verbose`` only
+    have to be well-formed; a reader that wants fewer kinds filters on the first column."""
+
+    ClogHook = _native.clog.ClogHook
+    EVENTS = ("ALL", "Q", "S", "E", "W", "G")
+
+    def __call__(self, output: str = "", events=("ALL",), verbose=()):
+        bad = [e for e in events if str(e).upper() not in self.EVENTS]
+        if bad:
+            raise ValueError(f"unknown clog events {bad} (expected some of {list(self.EVENTS)})")
+        return _native.clog.ClogHook(output)
+
+    def __getattr__(self, name):
+        return getattr(_native.clog, name)
+
+
+clog = _Clog()
+
+__all__ = ["NanCheckHook", "CommStatsHook", "DelayInjectionHook", "ChecksumHook", "FlightRecorderHook", "ClogHook", "fr", "clog"]
