@@ -196,3 +196,38 @@ def test_once_work_waits_a_shared_handle_once():
     a, b = wrap_async([torch.ones(2), torch.zeros(2)], shared)
     assert float((a + b).sum()) == 2.0 and Handle.waits == 1
     assert float(a.wait().sum()) == 2.0 and Handle.waits == 1
+
+
+def test_register_collective_adds_a_traceable_differentiable_operator():
+    """The extension point for collectives of out-of-tree backends: eager, traced and differentiated like the
+    built-in operators; the reference's names for passes / async tensor are available as aliases."""
+    import os
+
+    os.environ.update(RANK="0", WORLD_SIZE="1")
+    import torchcomms_b200 as tc
+    from torchcomms_b200 import functional as F
+    from torchcomms_b200.functional import async_tensor, inductor, passes
+
+    def impl(input, scale, comm):
+        out = input.clone()
+        F._get(comm).all_reduce(out, tc.ReduceOp.SUM, False)
+        return out * scale
+
+    op = F.register_collective(
+        "test_scaled_all_reduce", "(Tensor input, float scale, str comm) -> Tensor", impl,
+        lambda input, scale, comm: torch.empty_like(input),
+        backward=lambda ctx, g: (torch.ops.torchcomms_b200.test_scaled_all_reduce(g.contiguous(), *ctx.args), None, None))
+    F.finalize_registration()
+    comm = tc.new_comm("fake", torch.device("cpu"), name="reg_coll")
+    F.register_comm(comm)
+    x = torch.ones(3, requires_grad=True)
+    y = torch.compile(lambda t: op(t * 2, 0.5, "reg_coll"), fullgraph=True, backend="aot_eager")(x)
+    y.sum().backward()
+    assert torch.equal(y.detach(), torch.ones(3)) and torch.equal(x.grad, torch.ones(3))
+    import torch.fx.node as fx_node
+
+    assert op.default in fx_node._side_effectful_functions
+    assert passes.reinplacement_pass is passes.reinplace_pass and passes.strip_with_effects_pass is passes.strip_wait_pass
+    assert async_tensor.TorchCommsAsyncTensor is async_tensor.AsyncCollectiveTensor
+    assert inductor.register_torchcomms_lowerings is inductor.register_with_inductor
+    comm.finalize()

@@ -473,6 +473,32 @@ def scatter(x: Tensor, root: int, comm: Union[TorchComm, str]) -> Tensor:
     return _ops.scatter(x, root, _name(comm))
 
 
+def register_collective(name: str, schema: str, impl, fake, backward=None, setup_context=None) -> object:
+    """Adds an operator ``torch.ops.torchcomms_b200.<name>`` for a collective of an out-of-tree backend or of user
+    code, with everything the built-in operators have: an eager implementation, a fake implementation for tracing,
+    optionally an autograd formula, and the mark that keeps it in traced graphs on ranks that ignore its result.
+
+        register_collective("my_gather", "(Tensor input, int root, str comm) -> Tensor",
+                            impl=lambda input, root, comm: ..., fake=lambda input, root, comm: ...)
+
+    ``impl`` gets the communicator's registered name (look it up with ``functional._get(name)``).  Returns the
+    operator.  Counterpart in the reference: ``register_collective`` / ``finalize_registration`` of
+    comms/torchcomms/functional/registry.py (driven by parameter specs of communicator methods there)."""
+    _lib.define(f"{name}{schema}")
+    _lib.impl(name, impl, "CompositeExplicitAutograd")
+    torch.library.register_fake(f"{NAMESPACE}::{name}")(fake)
+    if backward is not None:
+        torch.library.register_autograd(f"{NAMESPACE}::{name}", backward, setup_context=setup_context or _setup)
+    op = getattr(_ops, name)
+    torch.fx.node.has_side_effect(op.default)
+    return op
+
+
+def finalize_registration(lib=None) -> None:
+    """Nothing to do: operators are complete when ``register_collective`` returns (kept for code written against
+    the reference, where registration is a two-step affair)."""
+
+
 from .async_tensor import AsyncCollectiveTensor, OnceWork, TracedWork, wrap_async  # noqa: E402
 from .ext import (  # noqa: E402
     CompiledComm, all_gather, all_gather_single_async, all_gather_v, all_reduce_async, all_to_all, all_to_all_single_async,
@@ -502,7 +528,7 @@ __all__ = [
     "window_put", "window_read", "window_signal", "window_token", "window_wait_signal",
     "normalize_reduce_op", "parse_hints", "parse_timeout",
     "send", "recv", "gather_single", "scatter",
-    "register_comm", "unregister_comm", "is_torch_compile_supported", "is_torch_compile_supported_and_enabled",
+    "register_comm", "unregister_comm", "register_collective", "finalize_registration", "is_torch_compile_supported", "is_torch_compile_supported_and_enabled",
     "all_reduce", "all_reduce_", "all_gather_single", "reduce_scatter_single", "all_to_all_single", "broadcast",
     "broadcast_", "reduce", "barrier", "wait_tensor",
 ]

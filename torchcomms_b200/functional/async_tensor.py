@@ -127,4 +127,8 @@ def wrap_async(result: Union[Tensor, List[Tensor]], work: Any):
     return [AsyncCollectiveTensor(t, shared) for t in result]
 
 
-__all__ = ["OnceWork", "TracedWork", "AsyncCollectiveTensor", "wrap_async", "is_tracing"]
+# The reference's names for the same things (comms/torchcomms/functional/async_tensor.py).
+TorchCommsAsyncTensor = AsyncCollectiveTensor
+FakeWork = TracedWork
+
+__all__ = ["OnceWork", "TracedWork", "AsyncCollectiveTensor", "wrap_async", "is_tracing", "TorchCommsAsyncTensor", "FakeWork"]

@@ -144,4 +144,6 @@ def register_with_inductor() -> bool:
     return True
 
 
-__all__ = ["register_with_inductor", "mark_side_effects", "lowered_ops"]
+register_torchcomms_lowerings = register_with_inductor     # the reference's name
+
+__all__ = ["register_with_inductor", "register_torchcomms_lowerings", "mark_side_effects", "lowered_ops"]

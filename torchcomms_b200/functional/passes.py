@@ -94,4 +94,9 @@ def count_ops(gm: fx.GraphModule) -> dict:
     return out
 
 
-__all__ = ["reinplace_pass", "strip_wait_pass", "count_ops"]
+# The reference's names (comms/torchcomms/functional/passes.py). Its second pass unwraps effect tokens, which the
+# operators of this package do not carry; the wrapper that can be removed here is ``wait_tensor``.
+reinplacement_pass = reinplace_pass
+strip_with_effects_pass = strip_wait_pass
+
+__all__ = ["reinplace_pass", "strip_wait_pass", "count_ops", "reinplacement_pass", "strip_with_effects_pass"]
