@@ -652,3 +652,18 @@ def test_hooks_namespace_accepts_the_reference_spellings(tmp_path):
     assert lines[0].startswith("V|") and any(ln.startswith("SIG|") and "all_reduce" in ln for ln in lines)
     with pytest.raises(ValueError):
         hooks.clog(output="", events=["sometimes"])
+
+
+def test_window_nvlink_address_on_a_cpu_window():
+    import os
+
+    os.environ.update(RANK="0", WORLD_SIZE="1")
+    comm = tc.new_comm("fake", torch.device("cpu"), name="win_addr")
+    win = comm.new_window()
+    buf = torch.zeros(8)
+    win.tensor_register(buf)
+    assert win.get_nvlink_address(0) == buf.data_ptr() and win.get_nvlink_address(0, 16) == buf.data_ptr() + 16
+    with pytest.raises(ValueError):
+        win.get_nvlink_address(0, 1000)
+    win.tensor_deregister()
+    comm.finalize()

@@ -223,6 +223,21 @@ TorchComm.symm_empty = _comm_symm_empty
 TorchComm.symm_free = _comm_symm_free
 
 
+def _window_nvlink_address(self, peer: int, offset: int = 0) -> int:
+    """Address at which this process reaches byte ``offset`` of rank ``peer``'s registered tensor (an NVLink peer
+    mapping on the CUDA backend; the tensor's own address for ``peer`` = own rank), for kernels that take raw
+    pointers.  The multicast alias of a window is available to device code through the device window
+    (``get_device_window()``; ``DeviceWindow::get_multimem_address``).
+    Parity: ``TorchCommWindowNCCLXGin.get_nvlink_address`` (comms/torchcomms/_comms_ncclx.pyi)."""
+    t = self.map_remote_tensor(peer)
+    if offset < 0 or offset > t.numel() * t.element_size():
+        raise ValueError(f"offset {offset} outside the window ({t.numel() * t.element_size()} bytes)")
+    return t.data_ptr() + offset
+
+
+TorchCommWindow.get_nvlink_address = _window_nvlink_address
+
+
 def healthy() -> bool:
     """False once any watchdog of this process saw a timeout or an async error."""
     return _comms._health_is_healthy()
