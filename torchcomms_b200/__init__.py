@@ -238,6 +238,15 @@ def _window_nvlink_address(self, peer: int, offset: int = 0) -> int:
 TorchCommWindow.get_nvlink_address = _window_nvlink_address
 
 
+def init_caching_allocator_hook() -> None:
+    """Registers the caching allocator's segments (present and future) with the point-to-point transport, so that
+    tensors from the ordinary allocator can be named in one-sided transfers without a registration per tensor.
+    Parity: ``init_caching_allocator_hook`` of the reference's NCCLX module (comms/torchcomms/_comms_ncclx.pyi)."""
+    from .transport import init_caching_allocator_hook as _hook
+
+    _hook()
+
+
 def healthy() -> bool:
     """False once any watchdog of this process saw a timeout or an async error."""
     return _comms._health_is_healthy()
