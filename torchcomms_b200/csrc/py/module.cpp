@@ -306,8 +306,8 @@ void bind_core(py::module_& m) {
       .def("abort", &Comm::abort, Release())
       .def("is_abort_supported", &Comm::is_abort_supported)
       .def("is_aborted", &Comm::is_aborted)
-      .def("set_timeout", &Comm::set_timeout)
-      .def("set_hints", &Comm::set_hints)
+      .def("set_timeout", &Comm::set_timeout, py::arg("timeout"))
+      .def("set_hints", &Comm::set_hints, py::arg("hints"))
       .def("send", [](Comm& c, const at::Tensor& t, int dst, bool a, OptHints h, OptMillis to) {
         return c.send(t, dst, a, make_op_options(h, to));
       }, py::arg("tensor"), py::arg("dst"), py::arg("async_op"), py::arg("hints") = py::none(), py::arg("timeout") = py::none(), Release())
