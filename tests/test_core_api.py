@@ -667,3 +667,22 @@ def test_window_nvlink_address_on_a_cpu_window():
         win.get_nvlink_address(0, 1000)
     win.tensor_deregister()
     comm.finalize()
+
+
+def test_reference_spellings_of_options_and_wrapper():
+    """``ReconfigureOptions.init_handles`` (list keeps the order, set sorts at use) and ``_BackendWrapper.get_mem_allocator``."""
+    import os
+
+    os.environ.update(RANK="0", WORLD_SIZE="1")
+    o = tc.ReconfigureOptions(1, ["b", "a"])
+    assert o.init_handles == ["b", "a"] == o.handles
+    o.init_handles = {"z", "y"}
+    assert sorted(o.init_handles) == ["y", "z"]
+    comm = tc.new_comm("fake", torch.device("cpu"), name="bw_alloc")
+    wrapper = tc._BackendWrapper(comm)
+    assert wrapper.get_comm() is comm or wrapper.get_comm().get_name() == "bw_alloc"
+    with pytest.raises(RuntimeError, match="no device memory allocator"):
+        wrapper.get_mem_allocator()
+    comm.set_timeout(timeout=timedelta(seconds=5))
+    comm.set_hints(hints={"k": "v"})
+    comm.finalize()

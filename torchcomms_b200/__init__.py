@@ -238,6 +238,14 @@ def _window_nvlink_address(self, peer: int, offset: int = 0) -> int:
 TorchCommWindow.get_nvlink_address = _window_nvlink_address
 
 
+def _wrapper_mem_allocator(self):
+    """The allocator of the wrapped communicator's backend (``_BackendWrapper.get_mem_allocator`` of the reference)."""
+    return get_mem_allocator(self.get_comm().get_backend())
+
+
+_BackendWrapper.get_mem_allocator = _wrapper_mem_allocator
+
+
 def init_caching_allocator_hook() -> None:
     """Registers the caching allocator's segments (present and future) with the point-to-point transport, so that
     tensors from the ordinary allocator can be named in one-sided transfers without a registration per tensor.

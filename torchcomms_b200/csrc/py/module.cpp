@@ -165,6 +165,16 @@ void bind_core(py::module_& m) {
       }), py::arg("uuid"), py::arg("init_handles"), py::arg("timeout") = py::none(), py::arg("hints") = py::none())
       .def_readwrite("uuid", &ReconfigureOptions::uuid)
       .def_readwrite("handles", &ReconfigureOptions::handles)
+      // The reference's name for the member list; assigning a set sorts the handles, a list fixes the rank order.
+      .def_property("init_handles",
+                    [](const ReconfigureOptions& o) { return o.handles; },
+                    [](ReconfigureOptions& o, py::object handles) {
+                      o.handles_ordered = !py::isinstance<py::set>(handles) && !py::isinstance<py::frozenset>(handles);
+                      o.handles.clear();
+                      for (auto h : handles) {
+                        o.handles.push_back(h.cast<std::string>());
+                      }
+                    })
       .def_readwrite("timeout", &ReconfigureOptions::timeout)
       .def_readwrite("hints", &ReconfigureOptions::hints);
 
