@@ -685,4 +685,9 @@ def test_reference_spellings_of_options_and_wrapper():
         wrapper.get_mem_allocator()
     comm.set_timeout(timeout=timedelta(seconds=5))
     comm.set_hints(hints={"k": "v"})
+    # the options a backend is given carry the communicator's name, for the child of a split its own
+    sub = comm.split([0], "bw_alloc_child")
+    assert comm.get_options().name == "bw_alloc" and sub.get_options().name == "bw_alloc_child"
+    assert tc.CommOptions().name == ""
+    sub.finalize()
     comm.finalize()

@@ -20,7 +20,7 @@
 
 namespace b200c {
 
-constexpr const char* kBackendAbiVersion = "b200c-1";
+constexpr const char* kBackendAbiVersion = "b200c-2";   // 2: CommOptions gained `name`
 
 class Backend;
 

@@ -408,7 +408,9 @@ std::shared_ptr<Comm> Comm::split(const std::vector<int>& ranks, const std::stri
   for (auto& h : pre_hooks_->snapshot()) {
     h(rec.op, id, rec);
   }
-  std::shared_ptr<Backend> child = impl_->split(ranks, name, opts);
+  CommOptions child_opts = opts;
+  child_opts.name = name;
+  std::shared_ptr<Backend> child = impl_->split(ranks, name, child_opts);
   for (auto& h : post_hooks_->snapshot()) {
     h(id, rec);
   }
@@ -568,7 +570,9 @@ std::shared_ptr<Backend> Factory::create(const std::string& name, at::Device dev
               "' (not registered and no TORCHCOMMS_BACKEND_LIB_PATH_* library set)");
   TORCH_CHECK(!opts.enable_reconfigure || b->supports_reconfigure(),
               "backend '", name, "' does not support enable_reconfigure");
-  b->init(device, comm_name, opts);
+  CommOptions with_name = opts;
+  with_name.name = comm_name;
+  b->init(device, comm_name, with_name);
   return b;
 }
 

@@ -108,6 +108,7 @@ struct B200C_API CommOptions {
   c10::intrusive_ptr<c10d::Store> store;
   bool enable_reconfigure = false;
   Hints hints;
+  std::string name;   // the communicator's name; filled in by new_comm() / split() for backends that read it here
 };
 
 struct ReconfigureOptions {

@@ -147,7 +147,8 @@ void bind_core(py::module_& m) {
       .def_readwrite("is_high_priority_stream", &CommOptions::is_high_priority_stream)
       .def_readwrite("store", &CommOptions::store)
       .def_readwrite("enable_reconfigure", &CommOptions::enable_reconfigure)
-      .def_readwrite("hints", &CommOptions::hints);
+      .def_readwrite("hints", &CommOptions::hints)
+      .def_readwrite("name", &CommOptions::name);
 
   py::class_<ReconfigureOptions>(m, "ReconfigureOptions")
       .def(py::init([](int64_t uuid, py::object handles, OptMillis timeout, OptHints hints) {
