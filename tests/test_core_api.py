@@ -691,3 +691,18 @@ def test_reference_spellings_of_options_and_wrapper():
     assert tc.CommOptions().name == ""
     sub.finalize()
     comm.finalize()
+
+
+def test_subpackages_resolve_as_attributes():
+    """``import torchcomms_b200`` is enough for ``tc.hooks`` / ``tc.objcol`` / ... (the reference imports them eagerly)."""
+    import subprocess
+    import sys
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import torchcomms_b200 as tc\n"
+            "assert tc.hooks.NanCheckHook and tc.objcol.all_gather_object and tc.checkpoint.checkpoint_prepare\n"
+            "try:\n    tc.no_such_thing\nexcept AttributeError:\n    print('ok')\n")
+    out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, PYTHONPATH=root, RANK="0", WORLD_SIZE="1"),
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stderr[-2000:]

@@ -314,6 +314,20 @@ def install_alias(name: str = "torchcomms") -> None:
         sys.modules[f"{name}.{sub}"] = importlib.import_module(f"{__name__}.{sub}")
 
 
+_LAZY_SUBMODULES = ("hooks", "objcol", "functional", "distwrap", "device_mesh", "mem", "ops", "parallel", "transport",
+                    "checkpoint", "utils", "models")
+
+
+def __getattr__(name):
+    """``torchcomms_b200.hooks``, ``.objcol`` and the other sub-packages resolve on first use, as they do after a
+    plain ``import torchcomms`` of the reference (which imports ``hooks`` and ``objcol`` eagerly)."""
+    if name in _LAZY_SUBMODULES:
+        import importlib
+
+        return importlib.import_module(f"{__name__}.{name}")
+    raise AttributeError(f"module '{__name__}' has no attribute '{name}'")
+
+
 if os.environ.get("TORCHCOMMS_PATCH_FOR_COMPILE") == "1":
     # As in the reference (comms/torchcomms/__init__.py): with this variable set, importing the package is enough for
     # communicator methods to be traceable under torch.compile (functional/__init__.py does the registration).
