@@ -310,7 +310,8 @@ def install_alias(name: str = "torchcomms") -> None:
 
     me = sys.modules[__name__]
     sys.modules[name] = me
-    for sub in ("device_mesh", "distwrap", "functional", "objcol", "hooks", "mem", "ops", "parallel", "_comms"):
+    for sub in ("device_mesh", "distwrap", "functional", "objcol", "hooks", "mem", "ops", "parallel", "transport", "utils",
+                "checkpoint", "_comms"):
         sys.modules[f"{name}.{sub}"] = importlib.import_module(f"{__name__}.{sub}")
 
 
