@@ -469,8 +469,16 @@ def test_reference_import_name():
     from torchcomms.device_mesh import init_device_mesh  # noqa: F401
     from torchcomms.hooks import NanCheckHook  # noqa: F401
 
+    from torchcomms._comms import AllReducePreHookArgs, OpName, RemovableHandle, _BackendWrapper  # noqa: F401
+
     c = torchcomms.new_comm("fake", torch.device("cpu"), name="alias")
     assert c.get_size() == 1 and torchcomms.ReduceOp.SUM is not None
+    seen = []
+    handle = c.register_pre_hook(lambda op, op_id, args: seen.append((op, type(args))))
+    assert isinstance(handle, RemovableHandle)
+    c.all_reduce(torch.ones(2), torchcomms.ReduceOp.SUM, False)
+    assert seen == [(OpName.all_reduce, AllReducePreHookArgs)]
+    handle.remove()
     c.finalize()
 
 

@@ -308,11 +308,20 @@ def install_alias(name: str = "torchcomms") -> None:
     import importlib
     import sys
 
+    import types
+
     me = sys.modules[__name__]
     sys.modules[name] = me
+    # `<name>._comms`: in the reference everything public lives in the native module (hook argument classes,
+    # new_comm, get_mem_allocator, ...); here part of it is Python. Code that imports from `<name>._comms` gets a
+    # module with the native names overlaid by this package's public ones.
+    shim = types.ModuleType(f"{name}._comms")
+    shim.__dict__.update({k: getattr(_comms, k) for k in dir(_comms) if not k.startswith("__")})
+    shim.__dict__.update({k: v for k, v in vars(me).items() if not k.startswith("_") or k == "_BackendWrapper"})
     for sub in ("device_mesh", "distwrap", "functional", "objcol", "hooks", "mem", "ops", "parallel", "transport", "utils",
-                "checkpoint", "_comms"):
+                "checkpoint"):
         sys.modules[f"{name}.{sub}"] = importlib.import_module(f"{__name__}.{sub}")
+    sys.modules[f"{name}._comms"] = shim
 
 
 _LAZY_SUBMODULES = ("hooks", "objcol", "functional", "distwrap", "device_mesh", "mem", "ops", "parallel", "transport",
