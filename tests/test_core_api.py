@@ -27,7 +27,7 @@ def test_registered_backends():
 
 
 def test_unknown_backend_raises():
-    with pytest.raises(RuntimeError, match="unknown communication backend"):
+    with pytest.raises(ModuleNotFoundError, match="failed to find backend.*unknown communication backend"):
         tc.new_comm("nonexistent", torch.device("cpu"), name="x")
 
 
@@ -706,3 +706,17 @@ def test_subpackages_resolve_as_attributes():
     out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, PYTHONPATH=root, RANK="0", WORLD_SIZE="1"),
                          capture_output=True, text=True, timeout=300)
     assert out.returncode == 0 and out.stdout.strip().endswith("ok"), out.stderr[-2000:]
+
+
+def test_new_comm_accepts_the_name_in_third_position():
+    """``new_comm(backend, device, "name")`` as the reference's binding takes it."""
+    import os
+
+    os.environ.update(RANK="0", WORLD_SIZE="1")
+    comm = tc.new_comm("fake", torch.device("cpu"), "third_positional")
+    assert comm.get_name() == "third_positional" and comm.get_options().name == "third_positional"
+    comm.finalize()
+    with pytest.raises(TypeError):
+        tc.new_comm("fake", torch.device("cpu"), "a", name="b")
+    with pytest.raises(ModuleNotFoundError, match="failed to find backend"):
+        tc.new_comm("invalid", torch.device("cpu"), "my_comm")

@@ -479,6 +479,11 @@ def test_reference_import_name():
     c.all_reduce(torch.ones(2), torchcomms.ReduceOp.SUM, False)
     assert seen == [(OpName.all_reduce, AllReducePreHookArgs)]
     handle.remove()
+    from torchcomms._comms_fake import TorchCommFake
+    from torchcomms._comms_gloo import TorchCommGloo  # noqa: F401
+    from torchcomms._comms_ncclx import TorchCommNCCLX, comm_dump_all  # noqa: F401
+
+    assert isinstance(c.get_backend_impl(), TorchCommFake)
     c.finalize()
 
 

@@ -168,9 +168,21 @@ def new_comm(
     Open MPI, PMI, PALS or torchrun's RANK/WORLD_SIZE).  Without ``store`` a
     TCPStore on MASTER_ADDR:MASTER_PORT bootstraps the ranks.  ``name`` must be
     unique per process and identical across ranks.
+
+    The reference's binding takes the name as its third positional argument (``new_comm("gloo", device, "dp")``)
+    while its stubs list the keyword order used above; a string in the third position is therefore read as the name.
     """
     global _comm_counter
+    if isinstance(abort_process_on_timeout_or_error, str):
+        if name is not None:
+            raise TypeError("new_comm: the name was given twice (third positional argument and name=)")
+        name, abort_process_on_timeout_or_error = abort_process_on_timeout_or_error, None
     _load_backend(backend)
+    if not _is_backend_registered(backend) and not os.environ.get(f"TORCHCOMMS_BACKEND_LIB_PATH_{backend.upper()}"):
+        # The reference's loader fails with this type and wording when no module provides the backend.
+        raise ModuleNotFoundError(
+            f"failed to find backend '{backend}': unknown communication backend (not registered, no entry point "
+            f"provides it and no TORCHCOMMS_BACKEND_LIB_PATH_{backend.upper()} library is set); known: {built_backends()}")
     opts = CommOptions()
     if abort_process_on_timeout_or_error is not None:
         opts.abort_process_on_timeout_or_error = abort_process_on_timeout_or_error
@@ -322,6 +334,18 @@ def install_alias(name: str = "torchcomms") -> None:
                 "checkpoint"):
         sys.modules[f"{name}.{sub}"] = importlib.import_module(f"{__name__}.{sub}")
     sys.modules[f"{name}._comms"] = shim
+    # The reference's per-backend modules name the backend classes that get_backend_impl() returns.
+    per_backend = {
+        "_comms_gloo": {"TorchCommGloo": _comms.GlooBackend},
+        "_comms_nccl": {"TorchCommNCCL": _comms.CudaBackend},
+        "_comms_ncclx": {"TorchCommNCCLX": _comms.CudaBackend, "comm_dump_all": comm_dump_all,
+                         "init_caching_allocator_hook": init_caching_allocator_hook},
+        "_comms_fake": {"TorchCommFake": _comms.FakeBackend},
+    }
+    for mod_name, members in per_backend.items():
+        mod = types.ModuleType(f"{name}.{mod_name}")
+        mod.__dict__.update(members)
+        sys.modules[f"{name}.{mod_name}"] = mod
 
 
 _LAZY_SUBMODULES = ("hooks", "objcol", "functional", "distwrap", "device_mesh", "mem", "ops", "parallel", "transport",
