@@ -272,7 +272,7 @@ def test_python_backend():
     kid = c.split([0], "kid")
     assert kid.get_size() == 1 and kid.get_name() == "kid"
     c.set_timeout(timedelta(seconds=2))
-    assert c.get_backend_impl().python_object().timeout == timedelta(seconds=2)
+    assert c.get_backend_impl().timeout == timedelta(seconds=2)
     kid.finalize()
     c.finalize()
 
@@ -537,7 +537,7 @@ def test_python_backend_every_operation_reaches_the_override():
     """test_python_backend.py of the reference: each collective lands in the Python method, hooks included."""
     tc.register_backend("pyfull", _FullPyBackend)
     c = tc.new_comm("pyfull", torch.device("cpu"), name="pyfull1")
-    impl = c.get_backend_impl().python_object()
+    impl = c.get_backend_impl()
     seen = []
     handle = c.register_pre_hook(lambda op, op_id, args: seen.append(op.name))
     t, out = torch.arange(4.0), torch.zeros(4)
@@ -564,7 +564,7 @@ def test_python_backend_every_operation_reaches_the_override():
     # two communicators of the same Python backend are independent objects
     c2 = tc.new_comm("pyfull", torch.device("cpu"), name="pyfull2")
     c2.barrier(False)
-    assert c2.get_backend_impl().python_object().calls == ["barrier"] and len(impl.calls) == len(expected)
+    assert c2.get_backend_impl().calls == ["barrier"] and len(impl.calls) == len(expected)
     c2.finalize()
     c.finalize()
 
@@ -720,3 +720,53 @@ def test_new_comm_accepts_the_name_in_third_position():
         tc.new_comm("fake", torch.device("cpu"), "a", name="b")
     with pytest.raises(ModuleNotFoundError, match="failed to find backend"):
         tc.new_comm("invalid", torch.device("cpu"), "my_comm")
+
+
+def test_python_backend_instance_is_what_get_backend_impl_returns():
+    """A backend class registered from Python: ``get_backend_impl()`` gives its instance, ``set_timeout`` reaches it,
+    and ``init`` sees the communicator's name in the options."""
+    import os
+
+    os.environ.update(RANK="0", WORLD_SIZE="1")
+
+    class Minimal(tc.TorchCommBackend):
+        def __init__(self):
+            super().__init__()
+            self.timeout = None
+
+        def init(self, device, name, options):
+            self.name, self.options_name = name, options.name
+
+        def finalize(self):
+            pass
+
+        def get_rank(self):
+            return 0
+
+        def get_size(self):
+            return 1
+
+        def get_backend_name(self):
+            return "minimal_py"
+
+        def get_comm_name(self):
+            return self.name
+
+        def set_timeout(self, timeout):
+            self.timeout = timeout
+
+        def all_reduce(self, tensor, op, async_op):
+            tensor.mul_(2)
+            return None
+
+    tc.register_backend("minimal_py", Minimal)
+    comm = tc.new_comm("minimal_py", torch.device("cpu"), name="py_impl")
+    impl = comm.get_backend_impl()
+    assert isinstance(impl, Minimal) and impl is comm.unsafe_get_backend() and impl.options_name == "py_impl"
+    comm.set_timeout(timedelta(milliseconds=1234))
+    assert impl.timeout == timedelta(milliseconds=1234)
+    t = torch.ones(2)
+    work = comm.all_reduce(t, tc.ReduceOp.SUM, async_op=False)
+    work.wait()
+    assert work.is_completed() and torch.equal(t, torch.full((2,), 2.0))
+    comm.finalize()

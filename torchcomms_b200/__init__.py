@@ -250,6 +250,22 @@ def _window_nvlink_address(self, peer: int, offset: int = 0) -> int:
 TorchCommWindow.get_nvlink_address = _window_nvlink_address
 
 
+_native_get_backend_impl = TorchComm.get_backend_impl
+
+
+def _comm_get_backend_impl(self):
+    """The backend object behind the communicator: the native backend, or for a backend written in Python
+    (``register_backend(name, cls)``) the instance of that class itself, as in the reference."""
+    impl = _native_get_backend_impl(self)
+    if isinstance(impl, _comms._PythonBackendAdapter):
+        return impl.python_object()
+    return impl
+
+
+TorchComm.get_backend_impl = _comm_get_backend_impl
+TorchComm.unsafe_get_backend = _comm_get_backend_impl
+
+
 def _wrapper_mem_allocator(self):
     """The allocator of the wrapped communicator's backend (``_BackendWrapper.get_mem_allocator`` of the reference)."""
     return get_mem_allocator(self.get_comm().get_backend())
