@@ -255,6 +255,14 @@ def test_nccl_async_error_fails_the_communicator():
     run_ranks(_nccl_error_body, 2, timeout=120)
 
 
+def test_backend_specific_operations_are_reachable_from_the_communicator(single_rank_env):
+    comm = _new_comm("fwd_ops")
+    assert comm.get_nccl_comm_ptr() == comm.get_backend_impl().get_nccl_comm_ptr()
+    comm.set_config({"symm_blocks": "24"})
+    assert comm.get_backend_impl().comm_dump()["tuning/symm_blocks"] == "24"
+    comm.finalize()
+
+
 def test_hints_become_nccl_config(single_rank_env):
     from torchcomms_b200 import _comms
 

@@ -266,6 +266,26 @@ TorchComm.get_backend_impl = _comm_get_backend_impl
 TorchComm.unsafe_get_backend = _comm_get_backend_impl
 
 
+def _forward_to_backend(method: str):
+    def call(self, *args, **kwargs):
+        impl = self.get_backend_impl()
+        fn = getattr(impl, method, None)
+        if fn is None:
+            raise RuntimeError(f"backend '{self.get_backend()}' has no {method}()")
+        return fn(*args, **kwargs)
+
+    call.__name__ = method
+    call.__doc__ = (f"``get_backend_impl().{method}(...)``: a backend-specific operation of the CUDA backend "
+                    "(comms/torchcomms/_comms_ncclx.pyi lists the same set), reachable from the communicator.")
+    return call
+
+
+for _m in ("get_nccl_comm_ptr", "device_alltoallv_single", "reduce_scatter_quantized", "set_config"):
+    if not hasattr(TorchComm, _m):
+        setattr(TorchComm, _m, _forward_to_backend(_m))
+del _m
+
+
 def _wrapper_mem_allocator(self):
     """The allocator of the wrapped communicator's backend (``_BackendWrapper.get_mem_allocator`` of the reference)."""
     return get_mem_allocator(self.get_comm().get_backend())
