@@ -66,6 +66,15 @@ def _ext_worker(rank, world):
         (sync(a2 * 2) * weight).sum().backward()
         assert torch.equal(a1.grad, a2.grad) and float(a1.grad.abs().sum()) > 0
 
+    # one wait for several started collectives, with gradients passed straight through
+    s1 = torch.full((2, 3), float(rank + 1), requires_grad=True)
+    h1 = torch.ops.torchcomms_b200.all_reduce_start(s1 * 1.0, "sum", "fx")
+    h2 = torch.ops.torchcomms_b200.all_gather_single_start(s1 * 2.0, "fx")
+    r1, r2 = F.wait_tensors([h1, h2])
+    assert torch.equal(r1, torch.full((2, 3), float(tri))) and r2.shape == (2 * world, 3)
+    (r1.sum() + r2.sum()).backward()
+    assert torch.equal(s1.grad, torch.full((2, 3), float(world + 2 * world)))
+
     # batched send / receive in a ring
     nxt, prv = (rank + 1) % world, (rank - 1) % world
     (got,) = F.batch_send_recv([torch.full((3,), float(rank))], [nxt], [torch.empty(3)], [prv], comm)

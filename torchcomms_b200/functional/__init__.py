@@ -502,7 +502,7 @@ def finalize_registration(lib=None) -> None:
 from .async_tensor import AsyncCollectiveTensor, OnceWork, TracedWork, wrap_async  # noqa: E402
 from .ext import (  # noqa: E402
     CompiledComm, all_gather, all_gather_single_async, all_gather_v, all_reduce_async, all_to_all, all_to_all_single_async,
-    batch_send_recv, compiled, reduce_scatter, reduce_scatter_single_async, reduce_scatter_v, register_window, unregister_window,
+    batch_send_recv, compiled, reduce_scatter, reduce_scatter_single_async, reduce_scatter_v, wait_tensors, register_window, unregister_window,
     window_put, window_read, window_signal, window_token, window_wait_signal,
 )
 from .param_parsing import normalize_reduce_op, parse_hints, parse_timeout  # noqa: E402
@@ -530,5 +530,5 @@ __all__ = [
     "send", "recv", "gather_single", "scatter",
     "register_comm", "unregister_comm", "register_collective", "finalize_registration", "is_torch_compile_supported", "is_torch_compile_supported_and_enabled",
     "all_reduce", "all_reduce_", "all_gather_single", "reduce_scatter_single", "all_to_all_single", "broadcast",
-    "broadcast_", "reduce", "barrier", "wait_tensor",
+    "broadcast_", "reduce", "barrier", "wait_tensor", "wait_tensors",
 ]

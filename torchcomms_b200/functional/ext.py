@@ -275,6 +275,34 @@ def _register_start_autograd() -> None:
 _register_start_autograd()
 
 
+# The list form of ``wait_tensor`` under the name the reference gives it (``torchcomm_wait_tensors``): one wait for
+# the results of several started collectives.
+_lib.define("torchcomm_wait_tensors(Tensor[] inputs) -> Tensor[]")
+
+
+def _impl_wait_tensors(inputs: List[Tensor]) -> List[Tensor]:
+    for t in inputs:
+        wait_pending(t)
+    return [t.clone() for t in inputs]
+
+
+_lib.impl("torchcomm_wait_tensors", _impl_wait_tensors, "CompositeExplicitAutograd")
+
+
+@torch.library.register_fake(f"{NAMESPACE}::torchcomm_wait_tensors")
+def _fake_wait_tensors(inputs):
+    return [torch.empty_like(t) for t in inputs]
+
+
+torch.library.register_autograd(f"{NAMESPACE}::torchcomm_wait_tensors", lambda ctx, grads: (list(grads),),
+                                setup_context=lambda ctx, inputs, output: None)
+
+
+def wait_tensors(xs: Sequence[Tensor]) -> List[Tensor]:
+    """``wait_tensor`` for several results at once."""
+    return _ops.torchcomm_wait_tensors(list(xs))
+
+
 def _start(op, *args):
     """Eager: an AsyncCollectiveTensor. Tracing: the start operator's result with a TracedWork."""
     out = op(*args)
