@@ -479,6 +479,10 @@ def test_reference_import_name():
     c.all_reduce(torch.ones(2), torchcomms.ReduceOp.SUM, False)
     assert seen == [(OpName.all_reduce, AllReducePreHookArgs)]
     handle.remove()
+    from torchcomms.distwrap.collectives import all_reduce, register_mem_pool  # noqa: F401
+    from torchcomms.distwrap.collectives_extension import new_window, reduce_scatter_quantized  # noqa: F401
+
+    assert all_reduce is distwrap.all_reduce and new_window is distwrap.new_window
     from torchcomms._comms_fake import TorchCommFake
     from torchcomms._comms_gloo import TorchCommGloo  # noqa: F401
     from torchcomms._comms_ncclx import TorchCommNCCLX, comm_dump_all  # noqa: F401
