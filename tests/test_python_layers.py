@@ -460,6 +460,13 @@ def test_lazy_backend_pair_comms():
     run_ranks(_lazy_worker, 4, timeout=120)
 
 
+def test_distwrap_requires_a_backend():
+    from torchcomms_b200 import distwrap
+
+    with pytest.raises(ValueError, match="backend must be specified"):
+        distwrap.init_process_group(backend=None)
+
+
 def test_reference_import_name():
     import torchcomms_b200
 

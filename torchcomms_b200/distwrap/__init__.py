@@ -119,6 +119,8 @@ def init_process_group(backend: Optional[str] = None, init_method: Optional[str]
                        store: Optional[Store] = None, group_name: str = "", pg_options: Any = None,
                        device_id: Any = None, use_torchcomms: bool = False, **kwargs: Any) -> None:
     global _enabled
+    if backend is None:
+        raise ValueError("backend must be specified")     # as the reference: no silent default in either mode
     if not use_torchcomms:
         _td.init_process_group(backend=backend, init_method=init_method, timeout=timeout, world_size=world_size,
                                rank=rank, store=store, group_name=group_name, pg_options=pg_options,
