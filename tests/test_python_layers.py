@@ -460,6 +460,21 @@ def test_lazy_backend_pair_comms():
     run_ranks(_lazy_worker, 4, timeout=120)
 
 
+def test_distwrap_turns_pg_options_into_hints():
+    import torch.distributed as td
+
+    from torchcomms_b200.distwrap import _pg_options_to_hints
+
+    assert _pg_options_to_hints(None) == ({}, None)
+    if not hasattr(td, "ProcessGroupNCCL"):
+        pytest.skip("torch without the NCCL process group")
+    opts = td.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+    opts.config.min_ctas, opts.config.max_ctas = 4, 16
+    hints, high_priority = _pg_options_to_hints(opts)
+    assert high_priority is True and hints["min_ctas"] == "4" and hints["max_ctas"] == "16"
+    assert all(isinstance(v, str) for v in hints.values()) and "is_high_priority_stream" not in hints
+
+
 def test_distwrap_requires_a_backend():
     from torchcomms_b200 import distwrap
 

@@ -24,7 +24,7 @@ from __future__ import annotations
 import os
 from dataclasses import dataclass, field
 from datetime import timedelta
-from typing import Any, Dict, List, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as _td
@@ -68,6 +68,40 @@ _split_seq = 0
 
 def torchcomms_is_enabled() -> bool:
     return _enabled
+
+
+def _pg_options_to_hints(pg_options: Any) -> Tuple[Dict[str, str], Optional[bool]]:
+    """What a ``ProcessGroupNCCL.Options``-like object says, as communicator hints: the scalar fields of its
+    ``config`` (NCCL configuration: ``min_ctas``, ``max_ctas``, ``cga_cluster_size``, ``net_name``, ... - the CUDA
+    backend hands those to ``ncclCommInitRankConfig``) and its own scalar fields, each as a string; the stream
+    priority flag is returned separately.  Parity: ``_pg_options_to_hints`` of
+    comms/torchcomms/distwrap/utils.py."""
+    hints: Dict[str, str] = {}
+    if pg_options is None:
+        return hints, None
+
+    def scalars(obj, skip=()):
+        for attr in dir(obj):
+            if attr.startswith("_") or attr in skip:
+                continue
+            try:
+                value = getattr(obj, attr)
+            except Exception:
+                continue
+            if isinstance(value, (bool, int, float, str)):
+                yield attr, value
+
+    config = getattr(pg_options, "config", None)
+    if config is not None:
+        for attr, value in scalars(config):
+            hints[attr] = str(int(value) if isinstance(value, bool) else value)
+    high_priority = None
+    for attr, value in scalars(pg_options, skip=("config",)):
+        if attr == "is_high_priority_stream":
+            high_priority = bool(value)
+        else:
+            hints[attr] = str(int(value) if isinstance(value, bool) else value)
+    return hints, high_priority
 
 
 def _parse_backend(backend: Optional[str]) -> Dict[str, str]:
@@ -144,6 +178,12 @@ def init_process_group(backend: Optional[str] = None, init_method: Optional[str]
             kw["timeout"] = timeout
         if store is not None:
             kw["store"] = _td.PrefixStore(f"distwrap_{dev_type}", store)
+        if dev_type == "cuda" and pg_options is not None:
+            opt_hints, high_priority = _pg_options_to_hints(pg_options)
+            if opt_hints:
+                kw["hints"] = opt_hints
+            if high_priority is not None:
+                kw["is_high_priority_stream"] = high_priority
         comms[dev_type] = new_comm(name, _device_for(dev_type), name=f"{group_name or 'world'}_{dev_type}", **kw)
     first = next(iter(comms.values()))
     # The WORLD group is served by the communicator of the accelerator when there is one.
