@@ -88,8 +88,8 @@ def _pg_options_to_hints(pg_options: Any) -> Tuple[Dict[str, str], Optional[bool
                 value = getattr(obj, attr)
             except Exception:
                 continue
-            if isinstance(value, (bool, int, float, str)):
-                yield attr, value
+            if isinstance(value, (bool, int, float, str)) and value != -2147483648 and value != "":
+                yield attr, value        # -2**31 is NCCL's "not set"
 
     config = getattr(pg_options, "config", None)
     if config is not None:
