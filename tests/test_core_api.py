@@ -621,9 +621,12 @@ def test_type_stubs_match_the_bindings():
     """torchcomms_b200/_comms.pyi is what the generator writes from the module as built (rerun
     ``python -m torchcomms_b200.utils.stubgen`` after changing a binding)."""
     import ast
+    import os
 
     from torchcomms_b200.utils import stubgen
 
+    if os.environ.get("TORCHCOMMS_PATCH_FOR_COMPILE") == "1":
+        pytest.skip("communicator methods are wrapped for tracing in this process: their bound signatures are hidden")
     text = stubgen.generate()
     ast.parse(text)
     assert open(stubgen.stub_path()).read() == text
