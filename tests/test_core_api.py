@@ -655,6 +655,19 @@ def test_hooks_namespace_accepts_the_reference_spellings(tmp_path):
     assert lines[0].startswith("V|") and any(ln.startswith("SIG|") and "all_reduce" in ln for ln in lines)
     with pytest.raises(ValueError):
         hooks.clog(output="", events=["sometimes"])
+    # the recorder's constructor and dump take the reference's arguments
+    os.environ["TORCHCOMM_FR_DUMP_TEMP_FILE"] = str(tmp_path / "fr_")
+    rec = hooks.FlightRecorderHook(max_entries=16, isolated=True)
+    assert rec.is_enabled() and rec.capacity() == 16
+    comm2 = tc.new_comm("fake", torch.device("cpu"), name="hooks_fr")
+    rec.register_with_comm(comm2)
+    comm2.all_reduce(torch.ones(2), tc.ReduceOp.SUM, False)
+    path2 = rec.dump_file(0, include_completed=True)
+    assert path2 == str(tmp_path / "fr_0") and "all_reduce" in open(path2).read()
+    assert "all_reduce" not in open(rec.dump_file(0, include_completed=False)).read()
+    rec.unregister()
+    comm2.finalize()
+    del os.environ["TORCHCOMM_FR_DUMP_TEMP_FILE"]
 
 
 def test_window_nvlink_address_on_a_cpu_window():

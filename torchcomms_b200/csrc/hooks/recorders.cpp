@@ -288,14 +288,14 @@ std::string FlightRecorder::dump_json(bool include_completed) const {
   return os.str();
 }
 
-std::string FlightRecorder::dump_file(int rank) const {
+std::string FlightRecorder::dump_file(int rank, bool include_completed) const {
   std::string prefix = env_to_value<std::string>("TORCHCOMM_FR_DUMP_TEMP_FILE", "");
   if (prefix.empty()) {
     prefix = env_to_value<std::string>("TORCH_FR_DUMP_TEMP_FILE", "/tmp/b200c_fr_trace_");
   }
   const std::string path = prefix + std::to_string(rank);
   std::ofstream f(path, std::ios::trunc);
-  f << dump_json(true);
+  f << dump_json(include_completed);
   return path;
 }
 

@@ -43,7 +43,7 @@ class FlightRecorder : public std::enable_shared_from_this<FlightRecorder> {
   std::string dump_json(bool include_completed = true) const;
   // Writes dump_json() to `<prefix><rank>`; prefix from TORCHCOMM_FR_DUMP_TEMP_FILE,
   // then TORCH_FR_DUMP_TEMP_FILE, default /tmp/b200c_fr_trace_ . Returns the path.
-  std::string dump_file(int rank) const;
+  std::string dump_file(int rank, bool include_completed = true) const;
   size_t size() const;
   size_t capacity() const { return cap_; }
   std::vector<Entry> entries() const;

@@ -13,11 +13,15 @@ void bind_hooks(py::module_& m) {
   auto hooks = m.def_submodule("hooks", "hook-based observers");
   auto fr = hooks.def_submodule("fr", "flight recorder");
   py::class_<FlightRecorder, std::shared_ptr<FlightRecorder>>(fr, "FlightRecorderHook")
-      .def(py::init([](size_t cap) { return std::make_shared<FlightRecorder>(cap); }), py::arg("max_entries") = 0)
+      // Every hook object owns its recorder, so `isolated` (the reference's switch between a process-wide recorder
+      // and one of the hook's own) is accepted and has nothing to choose between.
+      .def(py::init([](size_t cap, bool /*isolated*/) { return std::make_shared<FlightRecorder>(cap); }),
+           py::arg("max_entries") = 0, py::arg("isolated") = false)
+      .def("is_enabled", [](const FlightRecorder& f) { return f.capacity() > 0; })
       .def("register_with_comm", &FlightRecorder::attach, py::arg("comm"))
       .def("unregister", &FlightRecorder::detach)
       .def("dump_json", &FlightRecorder::dump_json, py::arg("include_completed") = true)
-      .def("dump_file", &FlightRecorder::dump_file, py::arg("rank"))
+      .def("dump_file", &FlightRecorder::dump_file, py::arg("rank"), py::arg("include_completed") = true)
       .def("size", &FlightRecorder::size)
       .def("capacity", &FlightRecorder::capacity)
       .def("reset", &FlightRecorder::reset)
